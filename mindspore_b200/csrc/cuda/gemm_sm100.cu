@@ -1,0 +1,375 @@
+// bf16 GEMM for sm_100a: TMA -> 128B-swizzled shared memory -> tcgen05.mma -> TMEM -> epilogue.
+//
+//   C[b][m][n] (+)= sum_k A[b][m][k] * B[b][n][k]   (+ bias[n])
+//
+// Either operand may be stored "K-major" (reduction dim contiguous) or "MN-major"
+// (the M, resp. N, dim contiguous); the three GEMMs of a Dense layer map to
+//   forward  Y  = X  W^T : A = X  (K-major),  B = W (K-major)
+//   dgrad    dX = dY W   : A = dY (K-major),  B = W (MN-major)
+//   wgrad    dW = dY^T X : A = dY (MN-major), B = X (MN-major)
+// with no transposed copies.  This replaces the cublasGemmEx/StridedBatchedEx calls of
+// plugin/device/gpu/kernel/math/matmul_gpu_kernel.cc:163-181 in the reference.
+//
+// Persistent kernel, one CTA per SM, 192 threads:
+//   warp 0    : TMA producer (one lane)
+//   warp 1    : TMEM allocation + MMA issue (one lane)
+//   warps 2-5 : epilogue; warp w drains TMEM lanes 32*(w%4)..+31
+// The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue of tile i
+// overlaps the main loop of tile i+1.  Shared-memory stages are recycled through
+// full/empty mbarriers; tcgen05.commit releases a stage when the MMAs that read it retire.
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace msb {
+
+constexpr int kBM = 128;       // tile rows (UMMA M)
+constexpr int kBK = 64;        // k per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int kGemmThreads = 192;
+constexpr int kGroupM = 8;     // m-tiles per scheduling group (L2 reuse of B tiles)
+
+struct GemmParams {
+  void* C;
+  const void* bias;   // bf16 [N] or nullptr
+  int* status;
+  long long c_batch_stride;  // elements
+  int M, N, K, batch;
+  int ldc;            // elements
+  int out_fp32;       // C is fp32 (else bf16)
+  int accumulate;     // C += result (read-modify-write)
+  float alpha;        // result scale applied before bias/accumulate
+};
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kSmemBytes = kBarOffset + 256 + 1024;  // barriers + slack for 1024B alignment
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int kStages = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + kStages * Cfg::kABytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOffset);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tfull_bar = empty_bar + kStages;   // [2] accumulator ready for epilogue
+  uint64_t* tempty_bar = tfull_bar + 2;        // [2] accumulator drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* issued_cnt = cta_abort + 1;    // k-blocks whose loads were issued
+  volatile int* consumed_cnt = cta_abort + 2;  // k-blocks whose loads were observed complete
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const AbortCtx ab{cta_abort, p.status};
+
+  const int tiles_m = (p.M + kBM - 1) / kBM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int tiles_per_batch = tiles_m * tiles_n;
+  const int total_tiles = tiles_per_batch * p.batch;
+  const int num_kb = (p.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&tfull_bar[0], 1);
+    mbar_init(&tfull_bar[1], 1);
+    mbar_init(&tempty_bar[0], 128);
+    mbar_init(&tempty_bar[1], 128);
+    *cta_abort = 0;
+    *issued_cnt = 0;
+    *consumed_cnt = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto tile_coords = [&](int tile, int& b, int& m_blk, int& n_blk) {
+    b = tile / tiles_per_batch;
+    int t = tile - b * tiles_per_batch;
+    const int group_sz = kGroupM * tiles_n;
+    const int g = t / group_sz;
+    const int first_m = g * kGroupM;
+    const int gm = min(tiles_m - first_m, kGroupM);
+    const int r = t - g * group_sz;
+    m_blk = first_m + r % gm;
+    n_blk = r / gm;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      int s = 0;
+      uint32_t ph = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int b, m_blk, n_blk;
+        tile_coords(tile, b, m_blk, n_blk);
+        const int m0 = m_blk * kBM, n0 = n_blk * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, ab)) { ok = false; break; }
+          mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
+          uint8_t* a_dst = smem_a + s * Cfg::kABytes;
+          uint8_t* b_dst = smem_b + s * Cfg::kBBytes;
+          const int k0 = kb * kBK;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < kBM / 64; ++j)
+              tma_load_3d(a_dst + j * 8192, &tmA, &full_bar[s], m0 + 64 * j, k0, b);
+          } else {
+            tma_load_3d(a_dst, &tmA, &full_bar[s], k0, m0, b);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(b_dst + j * 8192, &tmB, &full_bar[s], n0 + 64 * j, k0, b);
+          } else {
+            tma_load_3d(b_dst, &tmB, &full_bar[s], k0, n0, b);
+          }
+          ++issued;
+          *issued_cnt = issued;
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ MMA issuer
+      constexpr uint32_t idesc = umma_idesc_bf16(kBM, BN, A_MN, B_MN);
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      int consumed = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_ph = (it >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, ab)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[s], ph, ab)) { ok = false; break; }
+          ++consumed;
+          *consumed_cnt = consumed;
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem_a + s * Cfg::kABytes);
+          const uint32_t b_addr = smem_u32(smem_b + s * Cfg::kBBytes);
+#pragma unroll
+          for (int kk = 0; kk < kBK / 16; ++kk) {
+            // K-major: step 16 elements (32 B) inside the 128 B swizzle row.
+            // MN-major: step 16 k-rows of 128 B (2048 B); 64-wide M/N groups are 8192 B apart.
+            const uint64_t adesc = A_MN ? umma_smem_desc(a_addr + kk * 2048, 8192, 1024)
+                                        : umma_smem_desc(a_addr + kk * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? umma_smem_desc(b_addr + kk * 2048, 8192, 1024)
+                                        : umma_smem_desc(b_addr + kk * 32, 16, 1024);
+            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0);
+          }
+          umma_commit(&empty_bar[s]);  // stage reusable once these MMAs retire
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+        if (ok) umma_commit(&tfull_bar[acc]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // -------------------------------------------------------------------- epilogue
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      int b, m_blk, n_blk;
+      tile_coords(tile, b, m_blk, n_blk);
+      const int acc = it & 1;
+      const uint32_t acc_ph = (it >> 1) & 1;
+      if (!mbar_wait(&tfull_bar[acc], acc_ph, ab)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int row = m_blk * kBM + q * 32 + lane;
+      const int n0 = n_blk * BN;
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      const bool row_ok = row < p.M;
+      const long long c_off = static_cast<long long>(b) * p.c_batch_stride + static_cast<long long>(row) * p.ldc;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        if (n0 + c >= p.N) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c, r);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+        const int col0 = n0 + c;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        if (p.bias) {
+          const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(p.bias);
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) v[j] += __bfloat162float(bias[col0 + j]);
+        }
+        const bool full = (col0 + 32 <= p.N);
+        if (p.out_fp32) {
+          float* dst = static_cast<float*>(p.C) + c_off + col0;
+          if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              if (p.accumulate) {
+                const float4 old = *reinterpret_cast<const float4*>(dst + j);
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              *reinterpret_cast<float4*>(dst + j) = o;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) dst[j] = p.accumulate ? dst[j] + v[j] : v[j];
+          }
+        } else {
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.C) + c_off + col0;
+          if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (p.accumulate) {
+                const uint4 old = *reinterpret_cast<const uint4*>(dst + j);
+                const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                  const float2 f = __bfloat1622float2(ob[t]);
+                  v[j + 2 * t] += f.x;
+                  v[j + 2 * t + 1] += f.y;
+                }
+              }
+              uint4 o;
+              o.x = pack_bf16x2(v[j], v[j + 1]);
+              o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+              o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+              o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+              *reinterpret_cast<uint4*>(dst + j) = o;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N)
+                dst[j] = __float2bfloat16(p.accumulate ? __bfloat162float(dst[j]) + v[j] : v[j]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*cta_abort && threadIdx.x == 0) {
+    // Loads that were issued but never observed complete may still be in flight:
+    // give them a bounded time to land before shared memory is released.
+    const int issued = *issued_cnt, consumed = *consumed_cnt;
+    for (int i = consumed; i < issued; ++i) {
+      const int s = i % kStages;
+      const uint32_t ph = (i / kStages) & 1;
+      const unsigned long long t0 = globaltimer_ns();
+      while (!mbar_try_wait(&full_bar[s], ph)) {
+        if (globaltimer_ns() - t0 > 200000000ull) break;
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  static bool configured = false;  // per template instance
+  if (!configured) {
+    MSB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured = true;
+  }
+  const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN) * p.batch;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, p);
+  MSB_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+}  // namespace msb
+
+// C[b] (+)= alpha * A[b] x B[b]^T (+ bias).  A is [M,K] (a_mn=0, row pitch lda) or stored [K,M]
+// (a_mn=1, row pitch lda); B is [N,K] (b_mn=0) or stored [K,N] (b_mn=1).  Pitches and batch
+// strides are in elements and must be multiples of 8; base pointers 16-byte aligned.
+// bn_hint: 0 = choose, else 128 or 256.
+MSB_EXPORT int msb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int batch,
+                             int a_mn, int b_mn, long long lda, long long ldb, long long ldc,
+                             long long a_batch_stride, long long b_batch_stride, long long c_batch_stride,
+                             int out_fp32, int accumulate, float alpha, int bn_hint, void* stream_) {
+  using namespace msb;
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) {
+    set_last_error("gemm: empty problem M=%d N=%d K=%d batch=%d", M, N, K, batch);
+    return kBadArg;
+  }
+  if ((lda % 8) || (ldb % 8) || (a_batch_stride % 8) || (b_batch_stride % 8)) {
+    set_last_error("gemm: pitches and batch strides must be multiples of 8 elements (lda=%lld ldb=%lld)", lda, ldb);
+    return kBadArg;
+  }
+  int* status = status_ptr();
+  if (!status) {
+    set_last_error("gemm: cannot resolve the device status word");
+    return kCudaError;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int bn = bn_hint;
+  if (bn != 128 && bn != 256) {
+    const long long t256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256) * batch;
+    bn = (N <= 128 || t256 < sm_count()) ? 128 : 256;
+  }
+  CUtensorMap tmA, tmB;
+  int rc;
+  const uint64_t abs_ = batch > 1 ? static_cast<uint64_t>(a_batch_stride) * 2 : static_cast<uint64_t>(lda) * 2 * (a_mn ? K : M);
+  const uint64_t bbs_ = batch > 1 ? static_cast<uint64_t>(b_batch_stride) * 2 : static_cast<uint64_t>(ldb) * 2 * (b_mn ? K : N);
+  if (a_mn) rc = encode_tmap_3d(&tmA, A, 2, M, K, batch, lda * 2, abs_, 64, 64, 1);
+  else      rc = encode_tmap_3d(&tmA, A, 2, K, M, batch, lda * 2, abs_, 64, kBM, 1);
+  if (rc != kOk) return rc;
+  if (b_mn) rc = encode_tmap_3d(&tmB, B, 2, N, K, batch, ldb * 2, bbs_, 64, 64, 1);
+  else      rc = encode_tmap_3d(&tmB, B, 2, K, N, batch, ldb * 2, bbs_, 64, bn, 1);
+  if (rc != kOk) return rc;
+
+  GemmParams p;
+  p.C = C; p.bias = bias; p.status = status; p.c_batch_stride = c_batch_stride;
+  p.M = M; p.N = N; p.K = K; p.batch = batch; p.ldc = static_cast<int>(ldc);
+  p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
+
+#define MSB_DISPATCH(BN_)                                                       \
+  if (a_mn) {                                                                   \
+    if (b_mn) return launch_gemm<BN_, true, true>(tmA, tmB, p, stream);         \
+    return launch_gemm<BN_, true, false>(tmA, tmB, p, stream);                  \
+  } else {                                                                      \
+    if (b_mn) return launch_gemm<BN_, false, true>(tmA, tmB, p, stream);        \
+    return launch_gemm<BN_, false, false>(tmA, tmB, p, stream);                 \
+  }
+  if (bn == 256) { MSB_DISPATCH(256) } else { MSB_DISPATCH(128) }
+#undef MSB_DISPATCH
+}
