@@ -1,0 +1,24 @@
+"""mindspore_b200: a Blackwell-native deep-learning framework with MindSpore's training API.
+
+PyTorch is the tensor / eager substrate; hot ops are hand-written sm_100a kernels
+(``mindspore_b200/csrc/cuda``), the planner / runtime pieces are C++ (``mindspore_b200/csrc/host``).
+"""
+from . import common, communication, context, nn, ops, parallel, train
+from .common import (Parameter, ParameterTuple, Tensor, dtype, get_seed, initializer, set_seed)
+from .common.dtype import *  # noqa: F401,F403
+from .common.dtype import Type, dtype_to_nptype, pytype_to_dtype
+from .context import (GRAPH_MODE, PYNATIVE_MODE, ParallelMode, get_auto_parallel_context, get_context,
+                      reset_auto_parallel_context, set_auto_parallel_context, set_context, set_offload_context,
+                      set_ps_context)
+from .graph.jit import jit, ms_function
+from .ops.composite import grad, jacfwd, jacrev, jvp, value_and_grad, vjp
+from .parallel.layout import Layout
+from .parallel.shard import shard
+from .train import Model
+from .train.callback import (Callback, CheckpointConfig, LossMonitor, ModelCheckpoint, TimeMonitor)
+from .train.serialization import (export, load, load_checkpoint, load_param_into_net, save_checkpoint)
+from . import train as _train
+from .train import amp
+
+mstype = dtype
+__version__ = "0.1.0"

@@ -1,0 +1,402 @@
+"""Graph mode: ``@jit`` and GRAPH_MODE cell compilation.
+
+Pipeline (the reference's action list, pipeline/jit/ps/action.cc:1887-2038, re-thought for this runtime):
+
+1. **trace**   - ``construct`` runs once on the example inputs under a ``TorchFunctionMode``; every Primitive /
+   fused-op call and every other torch call becomes one node of a ``torch.fx.Graph`` in execution (ANF) order.
+   Python control flow is unrolled and shapes are specialised, as graph mode does for constants.
+2. **autodiff** - ``GradOperation`` inside the traced function triggers the IR-level reverse-mode transform
+   (``graph.autodiff``): one explicit VJP node per forward node plus explicit gradient accumulation nodes, so
+   backward collectives are real graph nodes that passes can reorder.
+3. **passes**  - dead-code elimination, common-subexpression elimination, then the parallel passes
+   (``parallel.step_parallel``) when a parallel mode is set; ``save_graphs`` dumps the IR after each pass.
+4. **execute** - ``graph.executor.GraphExecutor`` replays the node list; with ``enable_cuda_graph`` the replay is
+   captured once into a CUDA graph.
+
+Parity: mindspore/python/mindspore/common/api.py:798-983 (jit), :516-758 (_MindsporeFunctionExecutor),
+:1668-1912 (_CellGraphExecutor); ccsrc/pipeline/jit/ps/pipeline.cc:1213-1299,1618-1723.
+"""
+from __future__ import annotations
+
+import functools
+import os
+
+import torch
+import torch.fx as fx
+from torch.overrides import TorchFunctionMode
+
+from .. import context
+from ..common.parameter import Parameter
+from ..common.tensor import Tensor
+from ..ops import primitive as _prim_mod
+from . import tracer as _trace_state
+from .autodiff import build_backward
+from .executor import GraphExecutor
+from .ir import FuncGraph, dump_graph
+from .passes import run_default_passes
+
+_SKIP_FUNCS = set()
+
+
+def _is_tensor(x):
+    return isinstance(x, torch.Tensor)
+
+
+class _Recorder(TorchFunctionMode):
+    """Records executed torch-level calls into an fx.Graph while really executing them."""
+
+    def __init__(self, fg):
+        super().__init__()
+        self.fg = fg
+        self.depth = 0
+        self.node_of = {}   # id(tensor) -> fx.Node
+        self.alias = {}     # (data_ptr, shape, stride, dtype) -> fx.Node, for untracked aliases (as_subclass ...)
+        self.keep = []      # keep recorded tensors alive so ids and data pointers stay unique
+
+    @staticmethod
+    def _akey(t):
+        try:
+            ptr = t.data_ptr()
+        except RuntimeError:
+            return None
+        if ptr == 0:
+            return None
+        return (ptr, tuple(t.shape), tuple(t.stride()), t.dtype)
+
+    # ---- value <-> node mapping
+    def bind(self, value, node):
+        if _is_tensor(value):
+            self.node_of[id(value)] = node
+            k = self._akey(value)
+            if k is not None:
+                self.alias[k] = node
+            self.keep.append(value)
+        elif isinstance(value, (tuple, list)):
+            for i, v in enumerate(value):
+                if _is_tensor(v) or isinstance(v, (tuple, list)):
+                    import operator
+                    self.bind(v, self.fg.graph.call_function(operator.getitem, (node, i)))
+
+    def arg(self, a):
+        if _is_tensor(a):
+            n = self.node_of.get(id(a))
+            if n is not None:
+                return n
+            k = self._akey(a)
+            if isinstance(a, Parameter):
+                n = self.fg.param_node(a)
+            elif k is not None and k in self.alias:
+                n = self.alias[k]
+            else:
+                n = self.fg.const_node(a)
+            self.node_of[id(a)] = n
+            if k is not None and k not in self.alias:
+                self.alias[k] = n
+            self.keep.append(a)
+            return n
+        if isinstance(a, tuple):
+            return tuple(self.arg(x) for x in a)
+        if isinstance(a, list):
+            return [self.arg(x) for x in a]
+        if isinstance(a, dict):
+            return {k: self.arg(v) for k, v in a.items()}
+        if isinstance(a, slice):
+            return slice(self.arg(a.start), self.arg(a.stop), self.arg(a.step))
+        return a
+
+    def record(self, target, args, kwargs, out):
+        node = self.fg.graph.call_function(target, self.arg(tuple(args)), self.arg(dict(kwargs or {})))
+        self.bind(out, node)
+        return node
+
+    # ---- torch function interception
+    def __torch_function__(self, func, types, args=(), kwargs=None):
+        kwargs = kwargs or {}
+        if self.depth > 0:
+            return func(*args, **kwargs)
+        self.depth += 1
+        try:
+            out = func(*args, **kwargs)
+        finally:
+            self.depth -= 1
+        name = getattr(func, "__name__", "")
+        if name in ("__get__", "__set__") or not _has_tensor(out):
+            return out  # attribute reads (shape, dtype ...) and non-tensor results are trace-time constants
+        if not _has_tensor(args) and not _has_tensor(kwargs):
+            self.bind(out, self.fg.const_node(out) if _is_tensor(out) else None) if _is_tensor(out) else None
+            return out
+        self.record(func, args, kwargs, out)
+        return out
+
+    def primitive_hook(self, prim, args, kwargs):
+        if self.depth > 0:
+            return NotImplemented
+        self.depth += 1
+        try:
+            out = _prim_mod._wrap_out(prim._run(*args, **kwargs))
+        finally:
+            self.depth -= 1
+        if _has_tensor(out) or prim._update_parameter or prim.name in ("Send", "Barrier"):
+            node = self.record(prim, args, kwargs, out)
+            node.meta["primitive"] = prim.name
+        return out
+
+    def leaf_call(self, fn, args, kwargs):
+        """Used by ops.fused: record a fused kernel wrapper as one node."""
+        if self.depth > 0:
+            return fn(*args, **kwargs)
+        self.depth += 1
+        try:
+            out = fn(*args, **kwargs)
+        finally:
+            self.depth -= 1
+        self.record(fn, args, kwargs, out)
+        return out
+
+    # ---- GradOperation under trace
+    def trace_grad(self, fn, inputs, weights, sens, want_inputs, input_positions, has_aux, return_value):
+        fg = self.fg
+        start = len(list(fg.graph.nodes))
+        out = fn(*inputs)  # forward recorded inline (second copy of the forward; CSE merges it with the first)
+        fwd_nodes = list(fg.graph.nodes)[start:]
+        primary = out[0] if has_aux else out
+        out_nodes = [self.node_of[id(o)] for o in _flat_tensors(primary) if id(o) in self.node_of]
+        in_targets = [x for i, x in enumerate(inputs) if want_inputs and (input_positions is None or i in input_positions)
+                      and _is_tensor(x) and x.is_floating_point()]
+        w_targets = list(weights or [])
+        target_nodes = [self.arg(t) for t in in_targets + w_targets]
+        seeds = None
+        if sens is not None:
+            seeds = [self.arg(s) if _is_tensor(s) else s for s in (_flat_tensors(sens) or [sens])]
+        grad_nodes = build_backward(fg, fwd_nodes, out_nodes, target_nodes, seeds)
+        # concrete values for the rest of the trace: compute with the tape
+        with torch.enable_grad():
+            work = [x.detach().requires_grad_(True) if _is_tensor(x) and x.is_floating_point() else x for x in inputs]
+            self.depth += 1
+            try:
+                o2 = fn(*work)
+                p2 = o2[0] if has_aux else o2
+                outs = [o for o in _flat_tensors(p2) if o.requires_grad]
+                tg = [w for w, x in zip(work, inputs) if any(x is t for t in in_targets)] + w_targets
+                sd = [torch.ones_like(o) for o in outs] if sens is None else \
+                    [(s if _is_tensor(s) else torch.full_like(o, float(s))).to(o.dtype).expand_as(o)
+                     for s, o in zip(_flat_tensors(sens) or [sens] * len(outs), outs)]
+                gs = torch.autograd.grad(outs, tg, sd, allow_unused=True) if outs and tg else [None] * len(tg)
+            finally:
+                self.depth -= 1
+        vals = []
+        for g, t, n in zip(gs, in_targets + w_targets, grad_nodes):
+            v = (torch.zeros_like(t.detach()) if g is None else g).detach().as_subclass(Tensor)
+            self.node_of[id(v)] = n
+            self.keep.append(v)
+            vals.append(v)
+        ig, wg = tuple(vals[:len(in_targets)]), tuple(vals[len(in_targets):])
+        return out, ig, wg
+
+
+def _has_tensor(x):
+    if _is_tensor(x):
+        return True
+    if isinstance(x, (tuple, list)):
+        return any(_has_tensor(v) for v in x)
+    if isinstance(x, dict):
+        return any(_has_tensor(v) for v in x.values())
+    return False
+
+
+def _flat_tensors(x):
+    if _is_tensor(x):
+        return [x]
+    if isinstance(x, (tuple, list)):
+        out = []
+        for v in x:
+            out += _flat_tensors(v)
+        return out
+    return []
+
+
+class _TraceSession:
+    def __init__(self, rec):
+        self.rec = rec
+
+    def trace_grad(self, *a, **k):
+        return self.rec.trace_grad(*a, **k)
+
+
+def trace_callable(fn, example_inputs, name="graph"):
+    """Runs ``fn`` on the example inputs and returns (FuncGraph, example_outputs)."""
+    fg = FuncGraph(name)
+    rec = _Recorder(fg)
+    placeholders = []
+    for i, x in enumerate(example_inputs):
+        if _is_tensor(x):
+            n = fg.graph.placeholder("arg%d" % i)
+            n.meta["example"] = (tuple(x.shape), x.dtype)
+            rec.bind(x, n)
+            placeholders.append(i)
+    fg.input_positions = placeholders
+    prev_hook, prev_cur = _prim_mod._trace_hook, _trace_state.current()
+    _prim_mod._set_trace_hook(rec.primitive_hook)
+    _trace_state._set_current(_TraceSession(rec))
+    try:
+        with rec:
+            out = fn(*example_inputs)
+    finally:
+        _prim_mod._set_trace_hook(prev_hook)
+        _trace_state._set_current(prev_cur)
+    fg.set_output(rec.arg(out) if _has_tensor(out) else out, out)
+    fg.example_outputs = out
+    return fg, out
+
+
+def leaf_call(fn, args, kwargs):
+    """Entry point for fused ops: inside a trace the whole call becomes one node."""
+    cur = _trace_state.current()
+    if cur is None:
+        return fn(*args, **kwargs)
+    return cur.rec.leaf_call(fn, args, kwargs)
+
+
+def _signature(inputs, kwargs, training):
+    sig = []
+    for x in inputs:
+        if _is_tensor(x):
+            sig.append(("T", tuple(x.shape), x.dtype, x.device.type))
+        elif isinstance(x, (int, float, bool, str, type(None))):
+            sig.append(("C", x))
+        else:
+            sig.append(("O", id(x)))
+    return (tuple(sig), tuple(sorted(kwargs.items())) if kwargs else (), training,
+            context.get_auto_parallel_context("parallel_mode"))
+
+
+class CompiledGraph:
+    def __init__(self, fg, first_outputs):
+        self.fg = fg
+        self.executor = GraphExecutor(fg)
+        self.first_outputs = first_outputs
+        self.used_first = False
+
+    def __call__(self, *inputs):
+        tensors = [inputs[i] for i in self.fg.input_positions]
+        return self.executor.run(tensors)
+
+
+def _compile(fn, inputs, kwargs, name, owner=None):
+    snapshot = _snapshot_state(owner)
+    fg, out = trace_callable(lambda *a: fn(*a, **kwargs), inputs, name)
+    _restore_state(snapshot)   # tracing really executed one step; roll parameters / optimizer state back
+    level = context.get_context("save_graphs")
+    path = context.get_context("save_graphs_path")
+    if level:
+        dump_graph(fg, os.path.join(path, "%s_00_trace.ir" % name))
+    run_default_passes(fg, name, level, path)
+    mode = context.get_auto_parallel_context("parallel_mode")
+    if mode in (context.ParallelMode.SEMI_AUTO_PARALLEL, context.ParallelMode.AUTO_PARALLEL) and owner is not None:
+        from ..parallel.step_parallel import annotate_graph
+        annotate_graph(fg, owner)
+        if level:
+            dump_graph(fg, os.path.join(path, "%s_step_parallel_end.ir" % name))
+    return CompiledGraph(fg, out)
+
+
+def _snapshot_state(owner):
+    if owner is None or not hasattr(owner, "get_parameters"):
+        return None
+    snap = []
+    seen = set()
+
+    def add(cell):
+        for p in cell.get_parameters():
+            if id(p) not in seen:
+                seen.add(id(p))
+                snap.append((p, p.detach().as_subclass(torch.Tensor).clone()))
+    add(owner)
+    opt = getattr(owner, "optimizer", None)
+    host = None
+    if opt is not None:
+        add(opt)
+        host = (opt, opt._step_host)
+    return snap, host, torch.get_rng_state()
+
+
+def _restore_state(snapshot):
+    if snapshot is None:
+        return
+    snap, host, rng = snapshot
+    with torch.no_grad():
+        for p, v in snap:
+            torch.Tensor.copy_(p, v)
+    if host is not None:
+        host[0]._step_host = host[1]
+    torch.set_rng_state(rng)
+
+
+def compile_cell(cell, inputs, kwargs):
+    key = _signature(inputs, kwargs, cell.training)
+    cg = cell._compiled.get(key)
+    if cg is None:
+        cg = _compile(cell._run_construct_traced, inputs, kwargs, type(cell).__name__, owner=cell)
+        cell._compiled[key] = cg
+    return cg
+
+
+def compile_and_run_cell(cell, inputs, kwargs):
+    if not hasattr(cell, "_run_construct_traced"):
+        cell._run_construct_traced = lambda *a, **k: cell._run_construct(a, k)
+    if getattr(cell, "_use_graph", None) is False:
+        return cell._run_construct(inputs, kwargs)
+    cg = compile_cell(cell, inputs, kwargs)
+    return cg(*inputs)
+
+
+def trace_cell(cell, inputs):
+    from ..nn.cell import Cell
+    Cell._graph_depth += 1
+    try:
+        fg, _ = trace_callable(lambda *a: cell._run_construct(a, {}), inputs, type(cell).__name__)
+    finally:
+        Cell._graph_depth -= 1
+    return fg
+
+
+def load_graph_text(path):
+    with open(path) as f:
+        text = f.read()
+    fg = FuncGraph(os.path.basename(path))
+    fg.text = text
+    return fg
+
+
+def jit(fn=None, mode="PSJit", input_signature=None, hash_args=None, jit_config=None, compile_once=False):
+    """Decorator: compile ``fn`` once per input signature and replay the graph on later calls."""
+    if mode not in ("PSJit", "PIJit"):
+        raise ValueError("For 'jit', 'mode' must be 'PSJit' or 'PIJit', but got %r" % (mode,))
+
+    def deco(f):
+        cache = {}
+
+        @functools.wraps(f)
+        def wrapper(*args, **kwargs):
+            from ..nn.cell import Cell
+            if _trace_state.is_tracing() or os.environ.get("MS_JIT") == "0":
+                return f(*args, **kwargs)
+            key = _signature(args, kwargs, None)
+            cg = cache.get(key)
+            Cell._graph_depth += 1
+            try:
+                if cg is None:
+                    owner = args[0] if args and isinstance(args[0], Cell) else None
+                    cg = _compile(f, args, kwargs, getattr(f, "__name__", "jit_fn"), owner=owner)
+                    cache[key] = cg
+                return cg(*args)
+            finally:
+                Cell._graph_depth -= 1
+
+        wrapper.__jit_cache__ = cache
+        return wrapper
+
+    return deco(fn) if fn is not None else deco
+
+
+ms_function = jit

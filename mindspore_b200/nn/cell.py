@@ -1,0 +1,460 @@
+"""``nn.Cell``: the module base class.
+
+Attribute assignment registers ``Parameter`` and child ``Cell`` objects; ``__call__`` runs
+``construct`` eagerly in PYNATIVE mode and, in GRAPH mode, compiles the outermost cell once per
+input signature (trace -> passes -> auto-parallel -> executor) and replays the compiled graph.
+
+Parity: mindspore/python/mindspore/nn/cell.py:110 (class), :685-723 (__call__), :841 (__setattr__),
+:1045-1074 (compile / compile_and_run), :574 (shard), :1246-1503 (parameter APIs), :1819 (to_float),
+:1887 (set_grad), :1903 (set_train), :2301 (set_comm_fusion), :2373 (recompute), :318 (pipeline_stage).
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+
+import torch
+
+from .. import context
+from ..common import dtype as mstype
+from ..common.parameter import Parameter, ParameterTuple
+from ..common.tensor import Tensor
+
+
+class Cell:
+    _graph_depth = 0  # >0 while some outer Cell is already executing (nested calls run inline)
+
+    def __init__(self, auto_prefix=True, flags=None):
+        object.__setattr__(self, "_params", OrderedDict())
+        object.__setattr__(self, "_cells", OrderedDict())
+        object.__setattr__(self, "_params_list", OrderedDict())
+        self.training = False
+        self.requires_grad = False
+        self._auto_prefix = auto_prefix
+        self._param_prefix = ""
+        self._phase = "train"
+        self._forward_pre_hook = OrderedDict()
+        self._forward_hook = OrderedDict()
+        self._backward_hook = OrderedDict()
+        self._cell_tag = None
+        self._scope = None
+        self._mixed_precision_type = None
+        self._to_float_dtype = None
+        self._pipeline_stage = None
+        self._recompute = False
+        self._recompute_kwargs = {}
+        self._shard_fn = None
+        self._in_strategy = None
+        self._out_strategy = None
+        self._jit_config = None
+        self._compiled = {}
+        self._use_graph = None
+        self._has_config_recompute = False
+        self.parameter_layout_dict = {}
+        self.parallel_parameter_name_list = []
+        self.cls_name = self.__class__.__name__
+        self._attrs = {}
+        if flags:
+            self.add_flags(**flags)
+
+    # ------------------------------------------------------------------ attribute interception
+    def __setattr__(self, name, value):
+        params = self.__dict__.get("_params")
+        cells = self.__dict__.get("_cells")
+        if isinstance(value, Parameter):
+            if params is None:
+                raise AttributeError("Can not assign params before Cell.__init__() call.")
+            if name in self.__dict__:
+                del self.__dict__[name]
+            if cells is not None and name in cells:
+                raise TypeError("For 'Cell', the %r must be Cell, but got Parameter." % name)
+            if value.name == "Parameter" or not value.name:
+                value.name = name
+            params[name] = value
+        elif isinstance(value, Cell):
+            if cells is None:
+                raise AttributeError("Can not assign cells before Cell.__init__() call.")
+            if name in self.__dict__:
+                del self.__dict__[name]
+            if params is not None and name in params:
+                raise TypeError("For 'Cell', the %r must be Parameter, but got Cell." % name)
+            if self._auto_prefix:
+                value.update_parameters_name(name + ".")
+            cells[name] = value
+        elif isinstance(value, ParameterTuple):
+            for p in value:
+                self._params_list.setdefault(name, value)
+            object.__setattr__(self, name, value)
+        elif params is not None and name in params:
+            if value is None:
+                params[name] = None
+            elif isinstance(value, torch.Tensor):
+                params[name].set_data(value)
+            else:
+                raise TypeError("For 'Cell', the %r must be Parameter or Tensor, but got %s" % (name, type(value)))
+        elif cells is not None and name in cells:
+            if value is not None:
+                raise TypeError("For 'Cell', the %r must be Cell or None, but got %s" % (name, type(value)))
+            cells[name] = None
+        else:
+            object.__setattr__(self, name, value)
+
+    def __getattr__(self, name):
+        d = self.__dict__
+        if "_params" in d and name in d["_params"]:
+            return d["_params"][name]
+        if "_cells" in d and name in d["_cells"]:
+            return d["_cells"][name]
+        raise AttributeError("The '%s' object has no attribute '%s'." % (type(self).__name__, name))
+
+    def __delattr__(self, name):
+        if name in self._params:
+            del self._params[name]
+        elif name in self._cells:
+            del self._cells[name]
+        else:
+            object.__delattr__(self, name)
+
+    def __repr__(self):
+        extra = self.extend_repr()
+        lines = []
+        for k, c in self._cells.items():
+            sub = repr(c).replace("\n", "\n  ")
+            lines.append("(%s): %s" % (k, sub))
+        body = extra
+        if lines:
+            body += ("\n  " if not extra else "\n  ") + "\n  ".join(lines) + "\n"
+        return "%s<%s>" % (type(self).__name__, body)
+
+    def extend_repr(self):
+        return ""
+
+    # ------------------------------------------------------------------ call
+    def construct(self, *inputs, **kwargs):
+        raise NotImplementedError("%s must implement construct()" % type(self).__name__)
+
+    def _cast_inputs(self, inputs):
+        dt = self._to_float_dtype
+        if dt is None:
+            return inputs
+        return tuple(x.to(dt) if isinstance(x, torch.Tensor) and x.is_floating_point() and x.dtype != dt else x
+                     for x in inputs)
+
+    def _run_construct(self, inputs, kwargs):
+        for hook in self._forward_pre_hook.values():
+            res = hook(self, inputs)
+            if res is not None:
+                inputs = res if isinstance(res, tuple) else (res,)
+        inputs = self._cast_inputs(inputs)
+        if self._recompute and torch.is_grad_enabled() and Cell._recompute_enabled:
+            from torch.utils.checkpoint import checkpoint
+            out = checkpoint(lambda *a: self.construct(*a, **kwargs), *inputs, use_reentrant=False)
+        else:
+            out = self.construct(*inputs, **kwargs)
+        for hook in self._forward_hook.values():
+            res = hook(self, inputs, out)
+            if res is not None:
+                out = res
+        if self._backward_hook and isinstance(out, torch.Tensor) and out.requires_grad:
+            hooks = list(self._backward_hook.values())
+            cell = self
+
+            def _bw(grad):
+                g = grad
+                for h in hooks:
+                    r = h(cell, g, g)
+                    if r is not None:
+                        g = r[0] if isinstance(r, tuple) else r
+                return g
+            out.register_hook(_bw)
+        return out
+
+    _recompute_enabled = True
+
+    def __call__(self, *inputs, **kwargs):
+        from ..graph import tracer as _tracer
+        if Cell._graph_depth > 0 or _tracer.is_tracing():
+            return self._run_construct(inputs, kwargs)
+        use_graph = context.get_context("mode") == context.GRAPH_MODE and self._use_graph is not False
+        Cell._graph_depth += 1
+        try:
+            if use_graph:
+                from ..graph import jit as _jit
+                return _jit.compile_and_run_cell(self, inputs, kwargs)
+            return self._run_construct(inputs, kwargs)
+        finally:
+            Cell._graph_depth -= 1
+
+    def compile(self, *inputs, **kwargs):
+        from ..graph import jit as _jit
+        return _jit.compile_cell(self, inputs, kwargs)
+
+    def compile_and_run(self, *inputs, **kwargs):
+        from ..graph import jit as _jit
+        return _jit.compile_and_run_cell(self, inputs, kwargs)
+
+    def set_inputs(self, *inputs, **kwargs):
+        self._dynamic_inputs = inputs
+
+    def get_inputs(self):
+        return getattr(self, "_dynamic_inputs", None)
+
+    def set_jit_config(self, jit_config):
+        self._jit_config = jit_config
+
+    # ------------------------------------------------------------------ hierarchy
+    def insert_param_to_cell(self, param_name, param, check_name_contain_dot=True):
+        if not param_name:
+            raise KeyError("The name of parameter should not be null.")
+        if check_name_contain_dot and "." in param_name:
+            raise KeyError("The name of parameter should not contain \".\"")
+        if "_params" not in self.__dict__:
+            raise AttributeError("You need call init() first.")
+        if hasattr(self, param_name) and param_name not in self._params:
+            raise KeyError("Duplicated parameter name '%s'." % param_name)
+        if not isinstance(param, Parameter) and param is not None:
+            raise TypeError("The type of parameter should be 'Parameter' if not None.")
+        if isinstance(param, Parameter) and param.name == "Parameter":
+            param.name = param_name
+        self._params[param_name] = param
+
+    def insert_child_to_cell(self, child_name, child_cell):
+        if not isinstance(child_cell, Cell) and child_cell is not None:
+            raise TypeError("Child cell type is incorrect.")
+        if not child_name or "." in child_name:
+            raise KeyError("Child cell name is incorrect.")
+        if hasattr(self, child_name) and child_name not in self._cells:
+            raise KeyError("Duplicate child name '%s'." % child_name)
+        self._cells[child_name] = child_cell
+
+    def cells(self):
+        return self._cells.values()
+
+    def name_cells(self):
+        return OrderedDict((k, v) for k, v in self._cells.items() if v is not None)
+
+    def cells_and_names(self, cells=None, name_prefix=""):
+        seen = cells if cells is not None else set()
+        if id(self) in seen:
+            return
+        seen.add(id(self))
+        yield name_prefix, self
+        for name, cell in self._cells.items():
+            if cell is None:
+                continue
+            pre = name if not name_prefix else name_prefix + "." + name
+            yield from cell.cells_and_names(seen, pre)
+
+    def update_parameters_name(self, prefix="", recurse=True):
+        for _, p in self.parameters_and_names(expand=recurse):
+            p.name = prefix + p.name
+            p.is_init = False
+
+    def _param_walk(self, prefix="", expand=True, seen=None):
+        seen = seen if seen is not None else set()
+        for name, p in self._params.items():
+            if p is not None and id(p) not in seen:
+                seen.add(id(p))
+                yield (prefix + name, p)
+        for _, plist in self._params_list.items():
+            for p in plist:
+                if id(p) not in seen:
+                    seen.add(id(p))
+                    yield (p.name, p)
+        if expand:
+            for cname, cell in self._cells.items():
+                if cell is not None:
+                    yield from cell._param_walk(prefix + cname + ".", expand, seen)
+
+    def parameters_and_names(self, name_prefix="", expand=True):
+        yield from self._param_walk(name_prefix + "." if name_prefix else "", expand)
+
+    def get_parameters(self, expand=True):
+        for _, p in self.parameters_and_names(expand=expand):
+            yield p
+
+    def parameters_dict(self, recurse=True):
+        out = OrderedDict()
+        for _, p in self.parameters_and_names(expand=recurse):
+            out[p.name] = p
+        return out
+
+    def trainable_params(self, recurse=True):
+        return [p for p in self.get_parameters(expand=recurse) if p._ms_requires_grad]
+
+    def untrainable_params(self, recurse=True):
+        return [p for p in self.get_parameters(expand=recurse) if not p._ms_requires_grad]
+
+    def parameters_broadcast_dict(self, recurse=True):
+        return OrderedDict((p.name, p) for p in self.get_parameters(expand=recurse) if not p.layerwise_parallel)
+
+    def init_parameters_data(self, auto_parallel_mode=False):
+        replace = {}
+        for p in self.get_parameters():
+            layout = self.parameter_layout_dict.get(p.name) if auto_parallel_mode else None
+            p.init_data(layout, set_sliced=layout is not None)
+        return replace
+
+    def load_parameter_slice(self, params):
+        return None
+
+    # ------------------------------------------------------------------ modes and flags
+    def set_train(self, mode=True):
+        self._phase = "train" if mode else "predict"
+        for _, c in self.cells_and_names():
+            c.training = mode
+        return self
+
+    def set_grad(self, requires_grad=True):
+        for _, c in self.cells_and_names():
+            c.requires_grad = requires_grad
+        return self
+
+    def set_data_parallel(self):
+        self.add_flags(defer_inline=True)
+
+    @property
+    def phase(self):
+        return self._phase
+
+    @phase.setter
+    def phase(self, v):
+        self._phase = v
+
+    def add_flags(self, **flags):
+        self._attrs.update(flags)
+        for k, v in flags.items():
+            object.__setattr__(self, "_flag_" + k, v)
+        return self
+
+    def add_flags_recursive(self, **flags):
+        for _, c in self.cells_and_names():
+            c.add_flags(**flags)
+        return self
+
+    def get_flags(self):
+        return dict(self._attrs)
+
+    def to_float(self, dst_type):
+        """Marks this subtree to compute in ``dst_type``: float inputs are cast on entry and the
+        subtree's floating parameters are held in that dtype (fp32 master copies are the optimizer's job)."""
+        if dst_type not in (mstype.float16, mstype.float32, mstype.bfloat16):
+            raise ValueError("For 'to_float', the argument 'dst_type' must be float16, float32 or bfloat16, got %s"
+                             % (dst_type,))
+        for _, c in self.cells_and_names():
+            c._to_float_dtype = dst_type
+            for p in c._params.values():
+                if p is not None and p.is_floating_point() and p.dtype != dst_type and \
+                        not getattr(c, "_keep_fp32_params", False):
+                    p.set_data(p.detach().as_subclass(torch.Tensor).to(dst_type))
+        return self
+
+    def set_boost(self, boost_type):
+        self._boost_type = boost_type
+        return self
+
+    def set_comm_fusion(self, fusion_type, recurse=True):
+        for p in self.trainable_params(recurse):
+            p.comm_fusion = fusion_type
+        return self
+
+    def set_broadcast_flag(self, mode=True):
+        self.add_flags(broadcast_flag=mode)
+        return self
+
+    def set_auto_parallel(self):
+        self._auto_parallel = True
+
+    # ------------------------------------------------------------------ parallel annotations
+    def shard(self, in_strategy, out_strategy=None, parameter_plan=None, device="Ascend", level=0):
+        from ..parallel.shard import Shard
+        fn = Shard()(self, in_strategy, out_strategy, parameter_plan, device, level)
+        self._shard_fn = fn
+        self._in_strategy, self._out_strategy = in_strategy, out_strategy
+        return fn
+
+    @property
+    def pipeline_stage(self):
+        return self._pipeline_stage
+
+    @pipeline_stage.setter
+    def pipeline_stage(self, value):
+        if not isinstance(value, int) or isinstance(value, bool):
+            raise TypeError("For 'Cell', the property 'pipeline_stage' must be int type, but got %s" % type(value))
+        if value < 0:
+            raise ValueError("For 'Cell', the property 'pipeline_stage' can not be less than 0, but got %d" % value)
+        self._pipeline_stage = value
+        for p in self.trainable_params():
+            p.add_pipeline_stage(value)
+
+    def recompute(self, **kwargs):
+        """Activation checkpointing for this cell (mp_comm_recompute, parallel_optimizer_comm_recompute,
+        recompute_slice_activation accepted like the reference, nn/cell.py:2373)."""
+        for k in kwargs:
+            if k not in ("mp_comm_recompute", "parallel_optimizer_comm_recompute", "recompute_slice_activation",
+                         "mode"):
+                raise ValueError("For 'recompute', keyword %r is not recognized" % k)
+        self._recompute = kwargs.pop("mode", True)
+        self._recompute_kwargs = kwargs
+        self._has_config_recompute = True
+        if "parallel_optimizer_comm_recompute" in kwargs:
+            for p in self.trainable_params():
+                p.parallel_optimizer_comm_recompute = kwargs["parallel_optimizer_comm_recompute"]
+        return self
+
+    def place(self, role, rank_id):
+        self.add_flags(ms_role=role, rank_id=rank_id)
+
+    # ------------------------------------------------------------------ hooks
+    def register_forward_pre_hook(self, hook_fn):
+        return _HookHandle(self._forward_pre_hook, hook_fn)
+
+    def register_forward_hook(self, hook_fn):
+        return _HookHandle(self._forward_hook, hook_fn)
+
+    def register_backward_hook(self, hook_fn):
+        return _HookHandle(self._backward_hook, hook_fn)
+
+    # ------------------------------------------------------------------ misc
+    def cast_param(self, param):
+        return param
+
+    def flatten_weights(self, fusion_size=0):
+        return None
+
+    def exec_checkpoint_graph(self):
+        return None
+
+    def apply(self, fn):
+        for c in self.cells():
+            if c is not None:
+                c.apply(fn)
+        fn(self)
+        return self
+
+
+class _HookHandle:
+    _next = 0
+
+    def __init__(self, table, fn):
+        self.table = table
+        self.key = _HookHandle._next
+        _HookHandle._next += 1
+        table[self.key] = fn
+
+    def remove(self):
+        self.table.pop(self.key, None)
+
+
+class GraphCell(Cell):
+    """Runs a compiled / loaded graph (``load()`` result) as a Cell.  Parity: nn/cell.py:2554."""
+
+    def __init__(self, graph, params_init=None, obf_random_seed=None):
+        super().__init__(auto_prefix=True)
+        self.graph = graph
+        self._use_graph = False
+        if params_init:
+            for name, value in params_init.items():
+                graph.set_param(name, value)
+
+    def construct(self, *inputs):
+        return self.graph(*inputs)

@@ -1,0 +1,430 @@
+"""Training-step wrapper cells.
+
+Parity: mindspore/python/mindspore/nn/wrap/cell_wrapper.py:75 (WithLossCell), :146 (WithGradCell), :214
+(ForwardValueAndGrad), :319-444 (TrainOneStepCell), :492 (GetNextSingleOp), :531 (_VirtualDatasetCell),
+:564 (MicroBatchInterleaved), :622 (PipelineCell), :676 (GradAccumulationCell), :735 (_MicroBatch);
+nn/wrap/loss_scale.py:88 (DynamicLossScaleUpdateCell), :199 (FixedLossScaleUpdateCell), :272-580
+(TrainOneStepWithLossScaleCell); nn/wrap/grad_reducer.py:310-481 (DistributedGradReducer).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import context
+from ..common import dtype as mstype
+from ..common.parameter import Parameter, ParameterTuple
+from ..common.tensor import Tensor
+from ..ops import composite as C
+from ..ops.primitive import _wrap_out
+from .cell import Cell
+
+
+class WithLossCell(Cell):
+    def __init__(self, backbone, loss_fn):
+        super().__init__(auto_prefix=False)
+        self._backbone = backbone
+        self._loss_fn = loss_fn
+
+    def construct(self, data, label):
+        return self._loss_fn(self._backbone(data), label)
+
+    @property
+    def backbone_network(self):
+        return self._backbone
+
+
+class WithEvalCell(Cell):
+    def __init__(self, network, loss_fn, add_cast_fp32=False):
+        super().__init__(auto_prefix=False)
+        self._network, self._loss_fn, self.add_cast_fp32 = network, loss_fn, add_cast_fp32
+
+    def construct(self, data, label):
+        out = self._network(data)
+        if self.add_cast_fp32:
+            out, label = out.float(), (label.float() if label.is_floating_point() else label)
+        return self._loss_fn(out, label), out, label
+
+
+class WithGradCell(Cell):
+    def __init__(self, network, loss_fn=None, sens=None):
+        super().__init__(auto_prefix=False)
+        self.network, self.loss_fn, self.sens = network, loss_fn, sens
+        self.weights = ParameterTuple(network.trainable_params())
+        self.grad = C.GradOperation(get_by_list=True, sens_param=sens is not None)
+        self.network_with_loss = network if loss_fn is None else WithLossCell(network, loss_fn)
+        self.network_with_loss.set_train()
+
+    def construct(self, *inputs):
+        if self.sens is None:
+            return self.grad(self.network_with_loss, self.weights)(*inputs)
+        return self.grad(self.network_with_loss, self.weights)(*inputs, self.sens)
+
+
+class ForwardValueAndGrad(Cell):
+    def __init__(self, network, weights=None, get_all=False, get_by_list=False, sens_param=False):
+        super().__init__(auto_prefix=False)
+        if get_by_list and weights is None:
+            raise ValueError("For 'ForwardValueAndGrad', when 'get_by_list' is True, 'weights' must be given")
+        self.network, self.weights = network, weights
+        self.get_all, self.get_by_list, self.sens_param = get_all, get_by_list, sens_param
+        self.grad = C.GradOperation(get_all=get_all, get_by_list=get_by_list, sens_param=sens_param)
+
+    def construct(self, *inputs):
+        net_inputs = inputs[:-1] if self.sens_param else inputs
+        loss = self.network(*net_inputs)
+        g = self.grad(self.network, self.weights)(*inputs) if self.get_by_list else self.grad(self.network)(*inputs)
+        return loss, g
+
+
+# ------------------------------------------------------------------------------------ gradient reducer
+class DistributedGradReducer(Cell):
+    """Data-parallel gradient synchronisation: gradients are packed into comm_fusion buckets (flat
+    buffers), each bucket is all-reduced once (fp32 when ``gradient_fp32_sync``), scaled by 1/N when
+    ``mean`` and unpacked.  Bucket boundaries come from ``all_reduce_fusion_config`` (parameter indices)
+    or the ``comm_fusion`` size threshold (MB)."""
+
+    def __init__(self, parameters, mean=None, degree=None, fusion_type=1, group=None):
+        super().__init__(auto_prefix=False)
+        from ..communication import management as M
+        self.group = group or M.GlobalComm.WORLD_COMM_GROUP
+        self.mean = context.get_auto_parallel_context("gradients_mean") if mean is None else mean
+        if degree is None:
+            self.degree = M.get_group_size(self.group) if M.GlobalComm.INITED else 1
+        else:
+            if not isinstance(degree, int) or degree <= 0:
+                raise ValueError("For 'DistributedGradReducer', 'degree' must be a positive int")
+            self.degree = degree
+        self.params = list(parameters)
+        from ..parallel.comm_fusion import plan_allreduce_buckets
+        self.buckets = plan_allreduce_buckets(self.params)
+
+    def construct(self, grads):
+        from ..communication import comm_func as CF
+        from ..communication import management as M
+        if self.degree == 1 or not M.GlobalComm.INITED:
+            return grads
+        g = M._group(self.group)
+        fp32 = context.get_auto_parallel_context("gradient_fp32_sync")
+        out = list(grads)
+        for bucket in self.buckets:
+            ts = [grads[i].detach().as_subclass(torch.Tensor) for i in bucket]
+            dt = torch.float32 if fp32 else ts[0].dtype
+            flat = torch.cat([t.reshape(-1).to(dt) for t in ts])
+            CF._all_reduce_(flat, "sum", g)
+            if self.mean:
+                flat /= self.degree
+            off = 0
+            for i, t in zip(bucket, ts):
+                n = t.numel()
+                out[i] = _wrap_out(flat[off:off + n].view(t.shape).to(t.dtype))
+                off += n
+        return tuple(out)
+
+
+class PipelineGradReducer(Cell):
+    def __init__(self, parameters, scale_sense=1.0, opt_shard=None):
+        super().__init__(auto_prefix=False)
+        self.params = list(parameters)
+        self.scale = scale_sense
+
+    def construct(self, grads):
+        return tuple(g / self.scale for g in grads)
+
+
+def _parallel_mode():
+    return context.get_auto_parallel_context("parallel_mode")
+
+
+# ------------------------------------------------------------------------------------ train step
+class TrainOneStepCell(Cell):
+    def __init__(self, network, optimizer, sens=None, return_grad=False):
+        super().__init__(auto_prefix=False)
+        self.network = network
+        self.network.set_grad()
+        self.optimizer = optimizer
+        self.weights = optimizer.parameters
+        self.grad = C.GradOperation(get_by_list=True, sens_param=True)
+        self.sens = 1.0 if sens is None else float(sens)
+        self.sens_given = sens is not None
+        self.return_grad = return_grad
+        self.reducer_flag = _parallel_mode() in (context.ParallelMode.DATA_PARALLEL,
+                                                 context.ParallelMode.HYBRID_PARALLEL)
+        self.grad_reducer = None
+        if self.reducer_flag:
+            self.grad_reducer = DistributedGradReducer(self.weights)
+        self.use_arena = getattr(optimizer, "use_arena", False)
+        self._use_graph = None
+
+    def _arena_step(self, inputs):
+        """Arena optimizers: gradients flow straight into the flat fp32 accumulator inside backward."""
+        opt = self.optimizer
+        opt.zero_grad()
+        with torch.enable_grad():
+            loss = self.network(*inputs)
+        if self.sens != 1.0:
+            (loss * self.sens).backward()
+        else:
+            loss.backward()
+        _collect_stray_grads(self.weights)
+        if self.grad_reducer is not None:
+            from ..parallel.data_parallel import allreduce_arena_grads
+            allreduce_arena_grads(opt.arena, self.grad_reducer)
+        opt.fused_step(inv_loss_scale=1.0 / self.sens if self.sens != 1.0 else 1.0)
+        return loss.detach()
+
+    def construct(self, *inputs):
+        if self.use_arena:
+            return _wrap_out(self._arena_step(inputs))
+        loss = self.network(*inputs)
+        sens = torch.full_like(loss, self.sens) if isinstance(loss, torch.Tensor) else self.sens
+        grads = self.grad(self.network, self.weights)(*inputs, sens)
+        if self.grad_reducer is not None:
+            grads = self.grad_reducer(grads)
+        self.optimizer(grads)
+        if self.return_grad:
+            return loss, {p.name: g for p, g in zip(self.weights, grads)}
+        return loss
+
+
+def _collect_stray_grads(params):
+    """Parameters updated through ops without a main_grad-aware backward still get ``.grad``; fold it in."""
+    for p in params:
+        g = p.grad
+        if g is not None:
+            mg = getattr(p, "main_grad", None)
+            if mg is not None:
+                mg.add_(g.to(mg.dtype))
+            p.grad = None
+
+
+class DynamicLossScaleUpdateCell(Cell):
+    def __init__(self, loss_scale_value, scale_factor, scale_window):
+        super().__init__()
+        self.scale_window, self.scale_factor = int(scale_window), float(scale_factor)
+        self.loss_scale_value = float(loss_scale_value)
+        self.cur_iter = Parameter(torch.tensor(1, dtype=torch.int32), name="current_iterator_step", requires_grad=False)
+        self.last_overflow_iter = Parameter(torch.tensor(0, dtype=torch.int32), name="last_overflow_iterator_step",
+                                            requires_grad=False)
+        self._use_graph = False
+
+    def get_loss_scale(self):
+        return self.loss_scale_value
+
+    def construct(self, loss_scale, overflow):
+        overflow = bool(overflow)
+        cur, last = int(self.cur_iter), int(self.last_overflow_iter)
+        with torch.no_grad():
+            if overflow:
+                torch.Tensor.copy_(loss_scale, torch.clamp(loss_scale / self.scale_factor, min=1.0))
+                torch.Tensor.fill_(self.last_overflow_iter, cur)
+            elif cur - last >= self.scale_window:
+                torch.Tensor.mul_(loss_scale, self.scale_factor)
+                torch.Tensor.fill_(self.last_overflow_iter, cur)
+            torch.Tensor.add_(self.cur_iter, 1)
+        return overflow
+
+
+class FixedLossScaleUpdateCell(Cell):
+    def __init__(self, loss_scale_value):
+        super().__init__()
+        self.loss_scale_value = float(loss_scale_value)
+        self._use_graph = False
+
+    def get_loss_scale(self):
+        return self.loss_scale_value
+
+    def construct(self, _, overflow):
+        return bool(overflow)
+
+
+class TrainOneStepWithLossScaleCell(TrainOneStepCell):
+    def __init__(self, network, optimizer, scale_sense):
+        super().__init__(network, optimizer, sens=None)
+        self.loss_scaling_manager = None
+        if isinstance(scale_sense, Cell):
+            self.loss_scaling_manager = scale_sense
+            dev = optimizer.parameters[0].device
+            self.scale_sense = Parameter(torch.tensor(scale_sense.get_loss_scale(), dtype=torch.float32, device=dev),
+                                         name="scale_sense", requires_grad=False)
+        elif isinstance(scale_sense, torch.Tensor):
+            if scale_sense.numel() != 1:
+                raise ValueError("For 'TrainOneStepWithLossScaleCell', the shape of 'scale_sense' must be (1,) or ()")
+            self.scale_sense = Parameter(scale_sense.detach().float().reshape(()), name="scale_sense",
+                                         requires_grad=False)
+        else:
+            raise TypeError("For 'TrainOneStepWithLossScaleCell', 'scale_sense' must be Cell or Tensor, got %s"
+                            % type(scale_sense))
+        self._use_graph = False  # the overflow branch reads a device flag
+
+    def set_sense_scale(self, sens):
+        if self.scale_sense is not None and isinstance(sens, torch.Tensor):
+            self.scale_sense.set_data(sens.reshape(()))
+        else:
+            raise TypeError("The input type must be Tensor, but got %s" % type(sens))
+
+    def start_overflow_check(self, pre_cond, compute_input):
+        return True, compute_input
+
+    def get_overflow_status(self, status, compute_output):
+        bad = torch.zeros((), dtype=torch.bool, device=compute_output[0].device)
+        for g in compute_output:
+            bad = bad | ~torch.isfinite(g).all()
+        from ..communication import management as M
+        if self.reducer_flag and M.GlobalComm.INITED and M.get_group_size() > 1:
+            from ..communication import comm_func as CF
+            f = bad.float()
+            CF._all_reduce_(f, "sum", M._group(None))
+            bad = f > 0
+        return bad
+
+    def process_loss_scale(self, overflow):
+        if self.loss_scaling_manager is not None:
+            return self.loss_scaling_manager(self.scale_sense, overflow)
+        return bool(overflow)
+
+    def construct(self, *inputs):
+        scale = self.scale_sense
+        if self.use_arena:
+            opt = self.optimizer
+            opt.zero_grad()
+            with torch.enable_grad():
+                loss = self.network(*inputs)
+            (loss * scale.to(loss.dtype)).backward()
+            _collect_stray_grads(self.weights)
+            if self.grad_reducer is not None:
+                from ..parallel.data_parallel import allreduce_arena_grads
+                allreduce_arena_grads(opt.arena, self.grad_reducer)
+            opt.fused_step(inv_loss_scale=1.0 / float(scale), check_finite=True)
+            overflow = opt._skip.bool().reshape(())
+            overflow = self.process_loss_scale(overflow)
+            return _wrap_out(loss.detach()), _wrap_out(torch.as_tensor(overflow)), scale
+        loss = self.network(*inputs)
+        sens = torch.full_like(loss, 1.0) * scale.to(loss.dtype)
+        grads = self.grad(self.network, self.weights)(*inputs, sens)
+        grads = tuple(g.float() / scale for g in grads)
+        if self.grad_reducer is not None:
+            grads = self.grad_reducer(grads)
+        cond = self.get_overflow_status(None, grads)
+        overflow = self.process_loss_scale(cond)
+        if not overflow:
+            self.optimizer(grads)
+        return loss, _wrap_out(torch.as_tensor(overflow)), scale
+
+
+# ------------------------------------------------------------------------------------ micro-batching
+class _MicroBatch(Cell):
+    def __init__(self, micro_size):
+        super().__init__()
+        self.micro_size = micro_size
+
+    def construct(self, i, *inputs):
+        out = []
+        for x in inputs:
+            if isinstance(x, torch.Tensor) and x.dim() > 0:
+                n = x.shape[0] // self.micro_size
+                out.append(x[i * n:(i + 1) * n])
+            else:
+                out.append(x)
+        return tuple(out)
+
+
+class PipelineCell(Cell):
+    """Splits the batch into ``micro_size`` micro-batches.  Under ``pipeline_stages > 1`` the pipeline
+    runtime (``parallel.pipeline``) schedules the stage's forward/backward per micro-batch with 1F1B or GPipe
+    ordering; otherwise micro-batches run back to back and losses are averaged."""
+
+    def __init__(self, network, micro_size, stage_config=None):
+        super().__init__(auto_prefix=False)
+        if not isinstance(micro_size, int) or micro_size <= 0:
+            raise ValueError("For 'PipelineCell', 'micro_size' must be a positive int, got %r" % (micro_size,))
+        self.network, self.micro_size = network, micro_size
+        self.micro_inputs = _MicroBatch(micro_size)
+        if stage_config:
+            for name, cell in network.cells_and_names():
+                for key, stage in stage_config.items():
+                    if name == key or name.endswith("." + key):
+                        cell.pipeline_stage = stage
+
+    def construct(self, *inputs):
+        stages = context.get_auto_parallel_context("pipeline_stages")
+        if stages > 1:
+            from ..parallel.pipeline import run_pipeline_forward
+            return run_pipeline_forward(self, inputs)
+        total = None
+        for i in range(self.micro_size):
+            out = self.network(*self.micro_inputs(i, *inputs))
+            total = out if total is None else total + out
+        return total / self.micro_size if context.get_auto_parallel_context("loss_repeated_mean") else total
+
+
+class GradAccumulationCell(PipelineCell):
+    def __init__(self, network, micro_size):
+        super().__init__(network, micro_size)
+
+    def construct(self, *inputs):
+        total = None
+        for i in range(self.micro_size):
+            out = self.network(*self.micro_inputs(i, *inputs))
+            total = out if total is None else total + out
+        return total / self.micro_size
+
+
+class MicroBatchInterleaved(Cell):
+    """Runs ``interleave_num`` sub-batches so that one's collectives overlap another's compute: sub-batch k
+    is issued on its own CUDA stream when running on GPU."""
+
+    def __init__(self, network, interleave_num=2):
+        super().__init__(auto_prefix=False)
+        if not isinstance(interleave_num, int) or interleave_num <= 0:
+            raise ValueError("For 'MicroBatchInterleaved', 'interleave_num' must be a positive int")
+        self.network, self.interleave_num = network, interleave_num
+        self.interleave_inputs = _MicroBatch(interleave_num)
+
+    def construct(self, *inputs):
+        total = None
+        for i in range(self.interleave_num):
+            out = self.network(*self.interleave_inputs(i, *inputs))
+            total = out if total is None else total + out
+        return total / self.interleave_num
+
+
+class _VirtualDatasetCell(Cell):
+    def __init__(self, backbone):
+        super().__init__(auto_prefix=False)
+        self._backbone = backbone
+
+    def construct(self, *inputs):
+        return self._backbone(*inputs)
+
+
+class _TrainGradAccuStepCell(TrainOneStepCell):
+    """Pipeline / gradient-accumulation step: gradients accumulate in ``accu_grads`` over micro-batches and
+    the optimizer consumes the accumulators."""
+
+    def __init__(self, network, optimizer, sens=None):
+        super().__init__(network, optimizer, sens)
+        self.accu_grads = self.weights.clone(prefix="accu_grads", init="zeros") if not self.use_arena else ()
+
+    def construct(self, *inputs):
+        if self.use_arena:
+            return _wrap_out(self._arena_step(inputs))
+        loss = self.network(*inputs)
+        sens = torch.full_like(loss, self.sens)
+        grads = self.grad(self.network, self.weights)(*inputs, sens)
+        with torch.no_grad():
+            for a, g in zip(self.accu_grads, grads):
+                torch.Tensor.copy_(a, g.to(a.dtype))
+        if self.grad_reducer is not None:
+            grads = self.grad_reducer(grads)
+        self.optimizer(grads)
+        return loss
+
+
+class GetNextSingleOp(Cell):
+    def __init__(self, dataset_types, dataset_shapes, queue_name):
+        super().__init__()
+        self.queue_name = queue_name
+
+    def construct(self):
+        from ..train.dataset_helper import _pop_queue
+        return _pop_queue(self.queue_name)

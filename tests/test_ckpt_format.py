@@ -1,0 +1,92 @@
+"""The .ckpt byte layout: concatenated Checkpoint{Value{tag, TensorProto{dims, tensor_type, tensor_content}}}
+messages (mindspore/ccsrc/utils/checkpoint.proto:17-44), checked against a hand-assembled protobuf."""
+import numpy as np
+import pytest
+import torch
+
+import mindspore_b200 as ms
+from mindspore_b200.train import serialization as S
+
+
+def _hand_assembled(tag, dims, tname, content):
+    def varint(n):
+        out = b""
+        while True:
+            b = n & 0x7F
+            n >>= 7
+            out += bytes([b | (0x80 if n else 0)])
+            if not n:
+                return out
+    tensor = b"".join(b"\x08" + varint(d) for d in dims) + b"\x12" + varint(len(tname)) + tname.encode() + \
+        b"\x1a" + varint(len(content)) + content
+    value = b"\x0a" + varint(len(tag)) + tag.encode() + b"\x12" + varint(len(tensor)) + tensor
+    return b"\x0a" + varint(len(value)) + value
+
+
+def test_bytes_match_hand_assembled_protobuf(tmp_path):
+    w = np.arange(6, dtype=np.float32).reshape(2, 3)
+    path = ms.save_checkpoint([{"name": "fc.weight", "data": ms.Tensor(w)}], str(tmp_path / "a.ckpt"))
+    assert open(path, "rb").read() == _hand_assembled("fc.weight", [2, 3], "Float32", w.tobytes())
+
+
+def test_google_protobuf_parses_it(tmp_path):
+    pb = pytest.importorskip("google.protobuf")
+    from google.protobuf import descriptor_pb2, descriptor_pool, message_factory
+    fd = descriptor_pb2.FileDescriptorProto(name="ckpt.proto", syntax="proto2")
+    tp = fd.message_type.add(name="TensorProto")
+    tp.field.add(name="dims", number=1, type=3, label=3)
+    tp.field.add(name="tensor_type", number=2, type=9, label=2)
+    tp.field.add(name="tensor_content", number=3, type=12, label=2)
+    ck = fd.message_type.add(name="Checkpoint")
+    val = ck.nested_type.add(name="Value")
+    val.field.add(name="tag", number=1, type=9, label=2)
+    val.field.add(name="tensor", number=2, type=11, label=1, type_name=".TensorProto")
+    ck.field.add(name="value", number=1, type=11, label=3, type_name=".Checkpoint.Value")
+    pool = descriptor_pool.DescriptorPool()
+    pool.Add(fd)
+    cls = message_factory.GetMessageClass(pool.FindMessageTypeByName("Checkpoint"))
+    a = np.random.randn(4, 5).astype(np.float32)
+    b = np.arange(3, dtype=np.int32)
+    path = ms.save_checkpoint({"a": ms.Tensor(a), "b": ms.Tensor(b), "s": ms.Tensor(2.5)}, str(tmp_path / "m.ckpt"))
+    msg = cls()
+    msg.ParseFromString(open(path, "rb").read())   # concatenated messages merge their repeated fields
+    assert [v.tag for v in msg.value] == ["a", "b", "s"]
+    assert list(msg.value[0].tensor.dims) == [4, 5] and msg.value[0].tensor.tensor_type == "Float32"
+    assert msg.value[0].tensor.tensor_content == a.tobytes()
+    assert list(msg.value[2].tensor.dims) == [0]       # scalar convention
+
+
+def test_dtypes_bf16_scalar_str_crc_filter(tmp_path):
+    x = torch.randn(7, 3).bfloat16()
+    path = ms.save_checkpoint({"x": ms.Tensor(x), "i8": ms.Tensor(np.array([1, -2], np.int8)),
+                               "flag": ms.Tensor(True)}, str(tmp_path / "d.ckpt"), crc_check=True,
+                              append_dict={"who": "me"})
+    d = ms.load_checkpoint(path, crc_check=True)
+    assert d["x"].dtype == torch.bfloat16 and torch.equal(d["x"].as_subclass(torch.Tensor), x)
+    assert d["i8"].dtype == torch.int8 and d["flag"].dtype == torch.bool and d["who"] == "me"
+    raw = bytearray(open(path, "rb").read())
+    raw[20] ^= 0xFF
+    bad = tmp_path / "bad.ckpt"
+    bad.write_bytes(bytes(raw))
+    with pytest.raises(ValueError, match="crc check"):
+        ms.load_checkpoint(str(bad), crc_check=True)
+    assert set(ms.load_checkpoint(path, filter_prefix="x")) == {"i8", "flag", "who"}
+    assert set(ms.load_checkpoint(path, specify_prefix=["x", "i"])) == {"x", "i8"}
+
+
+def test_large_tensor_is_chunked(tmp_path, monkeypatch):
+    monkeypatch.setattr(S, "SLICE_SIZE", 1)  # 1 KB slices
+    a = np.random.randn(1000).astype(np.float32)
+    path = ms.save_checkpoint({"big": ms.Tensor(a)}, str(tmp_path / "big.ckpt"))
+    tags = [t for t, _, _, _ in S.decode_stream(open(path, "rb").read())]
+    assert tags == ["big"] * 4
+    np.testing.assert_array_equal(ms.load_checkpoint(path)["big"].asnumpy(), a)
+
+
+def test_errors(tmp_path):
+    with pytest.raises(ValueError):
+        ms.load_checkpoint(str(tmp_path / "missing.ckpt"))
+    with pytest.raises(ValueError):
+        ms.load_checkpoint("x.txt")
+    with pytest.raises(TypeError):
+        ms.save_checkpoint(3, str(tmp_path / "x.ckpt"))
