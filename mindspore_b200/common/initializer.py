@@ -236,6 +236,18 @@ def initializer(init, shape=None, dtype=mstype.float32):
         shape = (shape,)
     ini = _resolve(init)
     work_dtype = dtype if dtype in (torch.float32, torch.float64) or not dtype.is_floating_point else torch.float32
+    from .. import context
+    dev = context.device()
+    n = 1
+    for d in shape:
+        n *= d
+    if dev.type == "cuda" and n >= (1 << 20) and isinstance(ini, (Normal, Uniform, Zero, One, HeUniform, HeNormal,
+                                                                   XavierUniform, XavierNormal, TruncatedNormal)):
+        # large tensors are filled on the device, in the target dtype when that is exact enough (avoids a
+        # multi-GB host detour for billion-parameter models)
+        t = torch.empty(tuple(shape), dtype=dtype if dtype.is_floating_point else work_dtype, device=dev)
+        ini(t)
+        return Tensor(t.to(dtype))
     t = torch.empty(tuple(shape), dtype=work_dtype)
     ini(t)
     return Tensor(t.to(dtype))

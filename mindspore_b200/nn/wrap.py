@@ -159,12 +159,25 @@ class TrainOneStepCell(Cell):
         """Arena optimizers: gradients flow straight into the flat fp32 accumulator inside backward."""
         opt = self.optimizer
         opt.zero_grad()
-        with torch.enable_grad():
-            loss = self.network(*inputs)
-        if self.sens != 1.0:
-            (loss * self.sens).backward()
+        net = self.network
+        if isinstance(net, GradAccumulationCell):
+            # micro-batches run back to back; each backward accumulates into the flat fp32 gradient arena
+            total = None
+            k = net.micro_size
+            for i in range(k):
+                mb = net.micro_inputs(i, *inputs)
+                with torch.enable_grad():
+                    li = net.network(*mb)
+                (li * (self.sens / k)).backward()
+                total = li.detach() if total is None else total + li.detach()
+            loss = total / k
         else:
-            loss.backward()
+            with torch.enable_grad():
+                loss = net(*inputs)
+            if self.sens != 1.0:
+                (loss * self.sens).backward()
+            else:
+                loss.backward()
         _collect_stray_grads(self.weights)
         if self.grad_reducer is not None:
             from ..parallel.data_parallel import allreduce_arena_grads
