@@ -15,12 +15,10 @@
 //
 // The reference defines FlashAttentionScore (core/ops/ops_def/flash_attention_score_op.yaml) but ships no GPU
 // kernel for it; its GPU path would be BatchMatMul + Softmax + BatchMatMul through cuBLAS/cuDNN.
-#include "host_common.h"
-#include "ptx.cuh"
+#include "fa_common.cuh"
 
 namespace msb {
 
-constexpr int kFaD = 128;        // head dim
 constexpr int kFaBM = 128;       // query rows per item
 constexpr int kFaBN = 128;       // keys per block
 constexpr int kFaThreads = 192;
@@ -36,21 +34,6 @@ struct FaParams {
   float scale_log2;    // softmax scale * log2(e)
   float scale;
 };
-
-__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int x, int y,
-                                            int z, int w) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], "
-      "[%2];" ::"r"(smem_u32(smem_dst)),
-      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
-      : "memory");
-}
-
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 
 // shared memory map (1024B aligned): Q 32K | K0 32K | K1 32K | V0 32K | V1 32K | P 32K | barriers
 struct FaSmem {
@@ -348,48 +331,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-static int encode_qkv_map(CUtensorMap* m, const void* base, int B, int S, int H, long long pitch) {
-  // dims (d, h, s, b); one box = 64 d x 1 head x 128 tokens
-  typedef CUresult (*Fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                         const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                         CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-  static Fn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess) {
-      set_last_error("cuTensorMapEncodeTiled unavailable");
-      return kCudaError;
-    }
-    fn = reinterpret_cast<Fn>(ptr);
-  }
-  if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch * 2) % 16) {
-    set_last_error("flash attention: base pointer and token pitch must be 16-byte aligned");
-    return kBadArg;
-  }
-  cuuint64_t dims[4] = {(cuuint64_t)kFaD, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
-  cuuint64_t strides[3] = {(cuuint64_t)kFaD * 2, (cuuint64_t)pitch * 2, (cuuint64_t)pitch * 2 * S};
-  cuuint32_t box[4] = {64, 1, 128, 1};
-  cuuint32_t es[4] = {1, 1, 1, 1};
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, es,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    set_last_error("flash attention: cuTensorMapEncodeTiled failed with %d", (int)r);
-    return kCudaError;
-  }
-  return kOk;
-}
-
 }  // namespace msb
 
 using namespace msb;
 
-// q [B,S,H,128], k/v [B,S,Hk,128] with token pitches (elements) q_pitch / kv_pitch; o [B,S,H,128] with o_pitch.
+// q [B,S,H,128], k/v [B,S,Hk,128] with token pitches (elements) q_pitch / k_pitch / v_pitch; o [B,S,H,128] with o_pitch.
 // S must be a multiple of 128.  lse (fp32 [B,H,S]) may be null.
 MSB_EXPORT int msb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S,
-                                  int H, int Hk, int D, long long q_pitch, long long kv_pitch, long long o_pitch,
+                                  int H, int Hk, int D, long long q_pitch, long long k_pitch, long long v_pitch,
+                                  long long o_pitch,
                                   int causal, float scale, void* stream_) {
   if (D != kFaD || S % 128 != 0 || S <= 0 || H % Hk != 0 || B <= 0) {
     set_last_error("flash_attn_fwd: needs head_dim 128, S a multiple of 128 and H a multiple of Hk "
@@ -404,9 +354,9 @@ MSB_EXPORT int msb_flash_attn_fwd(const void* q, const void* k, const void* v, v
   if (!status) { set_last_error("flash_attn_fwd: no status word"); return kCudaError; }
   CUtensorMap tq, tk, tv;
   int rc;
-  if ((rc = encode_qkv_map(&tq, q, B, S, H, q_pitch)) != kOk) return rc;
-  if ((rc = encode_qkv_map(&tk, k, B, S, Hk, kv_pitch)) != kOk) return rc;
-  if ((rc = encode_qkv_map(&tv, v, B, S, Hk, kv_pitch)) != kOk) return rc;
+  if ((rc = fa_encode_map(&tq, q, B, S, H, q_pitch, 128)) != kOk) return rc;
+  if ((rc = fa_encode_map(&tk, k, B, S, Hk, k_pitch, 128)) != kOk) return rc;
+  if ((rc = fa_encode_map(&tv, v, B, S, Hk, v_pitch, 128)) != kOk) return rc;
   static bool configured = false;
   if (!configured) {
     MSB_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -70,7 +70,16 @@ LLAMA2_7B = LlamaConfig()
 
 
 def _param(shape, std, dtype, name):
-    return Parameter(initializer(Normal(std), shape, dtype), name=name)
+    p = Parameter(initializer(Normal(std), shape, dtype), name=name)
+    p.tp_sharded = True          # every matrix of this model is sharded over the model-parallel group
+    return p
+
+
+def _norm_weight(cfg, tp, name):
+    p = Parameter(torch.ones(cfg.hidden_size, dtype=cfg.dtype), name=name)
+    # replicated over the model-parallel group but fed by token-sharded activations: gradients are partial sums
+    p.tp_grad_reduce = tp.active and cfg.sequence_parallel
+    return p
 
 
 class LlamaAttention(nn.Cell):
@@ -120,8 +129,8 @@ class LlamaDecoderLayer(nn.Cell):
     def __init__(self, cfg: LlamaConfig, tp: TP.TPGroup):
         super().__init__()
         self.cfg = cfg
-        self.attention_norm = Parameter(torch.ones(cfg.hidden_size, dtype=cfg.dtype), name="attention_norm")
-        self.ffn_norm = Parameter(torch.ones(cfg.hidden_size, dtype=cfg.dtype), name="ffn_norm")
+        self.attention_norm = _norm_weight(cfg, tp, "attention_norm")
+        self.ffn_norm = _norm_weight(cfg, tp, "ffn_norm")
         self.attention = LlamaAttention(cfg, tp)
         self.feed_forward = LlamaMLP(cfg, tp)
 
@@ -147,7 +156,7 @@ class LlamaModel(nn.Cell):
         self.tok_embeddings = _param((cfg.vocab_size // self.tp.size, cfg.hidden_size), cfg.init_std, cfg.dtype,
                                      "tok_embeddings")
         self.layers = nn.CellList([LlamaDecoderLayer(cfg, self.tp) for _ in range(cfg.num_layers)])
-        self.norm_out = Parameter(torch.ones(cfg.hidden_size, dtype=cfg.dtype), name="norm_out")
+        self.norm_out = _norm_weight(cfg, self.tp, "norm_out")
         self._rope = {}
         if cfg.recompute:
             for layer in self.layers:

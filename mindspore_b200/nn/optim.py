@@ -275,6 +275,59 @@ class Optimizer(Cell):
         if self.arena is not None:
             self.arena.zero_grad()
 
+    # ------------------------------------------------------------------ model-parallel awareness (arena form)
+    def set_model_parallel_group(self, group_name):
+        """Tells the optimizer that parameters flagged ``tp_sharded`` hold different shards on every rank of
+        ``group_name`` while the others are replicated there.  The global gradient norm then sums the sharded
+        part across the group, and gradients of parameters flagged ``tp_grad_reduce`` (replicated parameters fed
+        by token-sharded activations) are all-reduced over the group before the update."""
+        assert self.arena is not None, "set_model_parallel_group needs the arena form"
+        self._mp_group = group_name
+        arena = self.arena
+
+        def runs(flag):
+            out, start, cur = [], 0, None
+            for i, p in enumerate(arena.params):
+                f = bool(getattr(p, flag, False))
+                if cur is None:
+                    cur, start = f, i
+                elif f != cur:
+                    out.append((arena.segment(start, i), cur))
+                    cur, start = f, i
+            out.append((arena.segment(start, len(arena.params)), cur))
+            return out
+        self._norm_runs = runs("tp_sharded")
+        self._reduce_runs = [seg for seg, f in runs("tp_grad_reduce") if f]
+        self._sumsq_sh = torch.zeros_like(self._sumsq)
+
+    def sync_model_parallel_grads(self):
+        group = getattr(self, "_mp_group", None)
+        if group is None:
+            return
+        from ..communication import comm_func as CF
+        from ..communication import management as M
+        g = M._group(group)
+        for s, e in self._reduce_runs:
+            CF._all_reduce_(self.arena.grads[s:e], "sum", g)
+
+    def _accumulate_sumsq(self):
+        arena = self.arena
+        self._sumsq.zero_()
+        self._nonfinite.zero_()
+        group = getattr(self, "_mp_group", None)
+        if group is None:
+            K.sumsq_finite(arena.grads, self._sumsq, self._nonfinite)
+            return
+        from ..communication import comm_func as CF
+        from ..communication import management as M
+        self._sumsq_sh.zero_()
+        for (s, e), sharded in self._norm_runs:
+            K.sumsq_finite(arena.grads[s:e], self._sumsq_sh if sharded else self._sumsq, self._nonfinite)
+        g = M._group(group)
+        CF._all_reduce_(self._sumsq_sh, "sum", g)
+        CF._all_reduce_(self._nonfinite, "max", g)
+        self._sumsq.add_(self._sumsq_sh)
+
 
 def _to_plain(t):
     return t.detach().as_subclass(torch.Tensor) if isinstance(t, torch.Tensor) else t
@@ -431,9 +484,7 @@ class AdamWeightDecay(Optimizer):
         bc2 = 1 - self.beta2 ** t if self.bias_correction else 1.0
         skip = None
         if self.max_grad_norm > 0 or check_finite or inv_loss_scale != 1.0:
-            self._sumsq.zero_()
-            self._nonfinite.zero_()
-            K.sumsq_finite(arena.grads, self._sumsq, self._nonfinite)
+            self._accumulate_sumsq()
             K.finalize_grad_scale(self._sumsq, self._nonfinite, inv_loss_scale, self.max_grad_norm, self._gscale,
                                   self._skip, self._gnorm)
             skip = self._skip if check_finite else None

@@ -8,7 +8,7 @@ from .. import _native
 from .kernels import _count, _p, _stream
 
 _P, _I, _L, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
-_native.register_cuda_signature("msb_flash_attn_fwd", _I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _L, _I, _F, _P])
+_native.register_cuda_signature("msb_flash_attn_fwd", _I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _L, _L, _I, _F, _P])
 _native.register_cuda_signature("msb_flash_attn_bwd", _I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
                                                             _L, _L, _L, _L, _L, _I, _F, _P])
 
@@ -44,12 +44,15 @@ def fwd(q, k, v, causal, scale):
     if qp is None:
         q = q.contiguous()
         qp = H * D
-    if kp is None or vp is None or kp != vp:
-        k, v = k.contiguous(), v.contiguous()
+    if kp is None:
+        k = k.contiguous()
         kp = Hk * D
+    if vp is None:
+        v = v.contiguous()
+        vp = Hk * D
     o = torch.empty((B, S, H, D), dtype=q.dtype, device=q.device)
     lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
-    rc = _native.cuda().msb_flash_attn_fwd(_p(q), _p(k), _p(v), _p(o), _p(lse), B, S, H, Hk, D, qp, kp, H * D,
+    rc = _native.cuda().msb_flash_attn_fwd(_p(q), _p(k), _p(v), _p(o), _p(lse), B, S, H, Hk, D, qp, kp, vp, H * D,
                                            int(causal), float(scale), _stream())
     _native.check(rc, "flash_attn_fwd")
     _count()
