@@ -141,6 +141,8 @@ def main():
     net = LlamaForCausalLM(cfg, tp)
     opt = nn.AdamWeightDecay(net.trainable_params(), learning_rate=1e-4, beta1=0.9, beta2=0.95, eps=1e-8,
                              weight_decay=0.1, max_grad_norm=1.0)
+    if world > 1:
+        opt.set_model_parallel_group(tp.name)
     micro = args.global_batch          # micro-batch size 1 -> one micro-batch per sequence
     step_cell = nn.TrainOneStepCell(nn.GradAccumulationCell(net, micro), opt)
     step_cell.set_train()

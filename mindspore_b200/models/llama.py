@@ -201,3 +201,28 @@ class LlamaForCausalLM(nn.Cell):
         logits = self.logits(tokens)
         loss = TP.vocab_parallel_cross_entropy(logits, labels.reshape(-1), self.tp)
         return _wrap_out(loss)
+
+
+def shard_full_weights(full, cfg: LlamaConfig, mp: int, rank: int):
+    """Slices a dict {name: full tensor} of the mp=1 model into the shard held by ``rank`` of an mp-way model:
+    q/k/v heads and gate/up columns are split per rank inside the fused matrices, wo / w_down by input columns,
+    embedding and LM head by vocabulary rows; norm weights are replicated."""
+    d = cfg.head_dim
+    hq, hk = cfg.num_heads * d, cfg.num_kv_heads * d
+    f = cfg.ffn_hidden_size
+    out = {}
+    for name, w in full.items():
+        if name.endswith("wqkv"):
+            q, k, v = w[:hq], w[hq:hq + hk], w[hq + hk:]
+            out[name] = torch.cat([torch.chunk(q, mp, 0)[rank], torch.chunk(k, mp, 0)[rank],
+                                   torch.chunk(v, mp, 0)[rank]], 0)
+        elif name.endswith("w_gate_up"):
+            g, u = w[:f], w[f:]
+            out[name] = torch.cat([torch.chunk(g, mp, 0)[rank], torch.chunk(u, mp, 0)[rank]], 0)
+        elif name.endswith("wo") or name.endswith("w_down"):
+            out[name] = torch.chunk(w, mp, 1)[rank]
+        elif name.endswith("tok_embeddings") or name.endswith("lm_head"):
+            out[name] = torch.chunk(w, mp, 0)[rank]
+        else:
+            out[name] = w
+    return {k: v.contiguous() for k, v in out.items()}

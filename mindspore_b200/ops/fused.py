@@ -308,8 +308,6 @@ def embedding(table, ids, vocab_start=0):
     if _use_kernel(table) and table.shape[1] % 8 == 0:
         return _EmbeddingFn.apply(table, ids, vocab_start)
     idx = ids.long() - vocab_start
-    if vocab_start == 0 and True:
-        return F.embedding(idx, table)
     mask = (idx >= 0) & (idx < table.shape[0])
     return F.embedding(idx.clamp(0, table.shape[0] - 1), table) * mask.unsqueeze(-1).to(table.dtype)
 

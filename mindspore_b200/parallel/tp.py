@@ -118,14 +118,14 @@ class _VocabParallelCE(torch.autograd.Function):
             stats = K.ce_stats(logits, labels32, start)
         else:
             lf = logits.reshape(rows, V).float()
-            m = lf.max(-1).values
+            m = torch.amax(lf, -1)
             s = torch.exp(lf - m[:, None]).sum(-1)
             loc = labels32.long() - start
             inr = (loc >= 0) & (loc < V)
             tgt = torch.where(inr, lf.gather(1, loc.clamp(0, V - 1)[:, None])[:, 0], torch.zeros_like(m))
             stats = torch.stack([m, s, tgt], -1)
         allst = CF._all_gather(stats.unsqueeze(0).contiguous(), g)          # [mp, rows, 3]
-        gm = allst[..., 0].max(0).values
+        gm = torch.amax(allst[..., 0], 0)
         gs = (allst[..., 1] * torch.exp(allst[..., 0] - gm)).sum(0)
         gt = allst[..., 2].sum(0)
         merged = torch.stack([gm, gs, gt], -1).contiguous()
