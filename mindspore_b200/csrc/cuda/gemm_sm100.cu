@@ -22,6 +22,8 @@
 
 namespace msb {
 
+__device__ __forceinline__ bool row_ok_pre(int row, int M) { return row < M; }
+
 constexpr int kBM = 128;       // tile rows (UMMA M)
 constexpr int kBK = 64;        // k per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int kGemmThreads = 192;
@@ -37,7 +39,20 @@ struct GemmParams {
   int out_fp32;       // C is fp32 (else bf16)
   int accumulate;     // C += result (read-modify-write)
   float alpha;        // result scale applied before bias/accumulate
+  // --- MatMul -> ReduceScatter (MODE 1): the epilogue stores each bf16 output tile straight into the staging
+  // buffer of the rank that owns those token rows: rs_peer[owner] is bf16 [world][rows_per_rank][N] on `owner`.
+  void* rs_peer[8];
+  // --- AllGather -> MatMul (MODE 2): warp 6 of every CTA pulls its share of each peer's token shard
+  // ag_src[c] ([rows_per_rank][K] bf16 on rank c) through shared memory into the local gathered operand ag_dst
+  // ([world*rows_per_rank][K], what the A tensor map covers) and bumps ag_flags[c]; the TMA producer waits until
+  // a chunk's counter reaches gridDim.x before it loads tiles of that chunk.
+  const void* ag_src[8];
+  void* ag_dst;
+  int* ag_flags;
+  int world, rank, rows_per_rank;
 };
+
+constexpr int kBounceBytes = 8192;   // per bounce buffer of the AllGather copy warp (two buffers)
 
 template <int BN>
 struct GemmCfg {
@@ -46,11 +61,14 @@ struct GemmCfg {
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kBounceOffset = kBarOffset + 256;
   static constexpr int kSmemBytes = kBarOffset + 256 + 1024;  // barriers + slack for 1024B alignment
+  static constexpr int kSmemBytesAG = kBounceOffset + 2 * kBounceBytes + 1024;
 };
 
-template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+// MODE: 0 plain GEMM, 1 MatMul->ReduceScatter push epilogue, 2 AllGather->MatMul pull loader.
+template <int BN, bool A_MN, bool B_MN, int MODE>
+__global__ void __launch_bounds__(MODE == 2 ? kGemmThreads + 32 : kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmParams p) {
   using Cfg = GemmCfg<BN>;
@@ -113,6 +131,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int r = t - g * group_sz;
     m_blk = first_m + r % gm;
     n_blk = r / gm;
+    if (MODE != 0) {
+      // start with the chunk whose data / destination is local-most: RS sends remote chunks first and keeps its
+      // own chunk for last; AG starts on its own (already local) chunk while peers' chunks are in flight
+      const int tiles_per_chunk = p.rows_per_rank / kBM;
+      const int shift = (MODE == 1 ? (p.rank + 1) % p.world : p.rank) * tiles_per_chunk;
+      m_blk = (m_blk + shift) % tiles_m;
+    }
   };
 
   if (warp == 0) {
@@ -126,6 +151,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int b, m_blk, n_blk;
         tile_coords(tile, b, m_blk, n_blk);
         const int m0 = m_blk * kBM, n0 = n_blk * BN;
+        if (MODE == 2) {
+          const int chunk = m0 / p.rows_per_rank;
+          const volatile int* flag = p.ag_flags + chunk;
+          const unsigned long long t0 = globaltimer_ns();
+          while (*flag < static_cast<int>(gridDim.x)) {
+            if (*cta_abort) { ok = false; break; }
+            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+              *cta_abort = 1;
+              atomicOr(p.status, 2);
+              ok = false;
+              break;
+            }
+          }
+          if (!ok) break;
+          __threadfence();
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, ab)) { ok = false; break; }
           mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
@@ -192,7 +234,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp < 6) {
     // -------------------------------------------------------------------- epilogue
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     int it = 0;
@@ -208,7 +250,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int n0 = n_blk * BN;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       const bool row_ok = row < p.M;
-      const long long c_off = static_cast<long long>(b) * p.c_batch_stride + static_cast<long long>(row) * p.ldc;
+      long long c_off = static_cast<long long>(b) * p.c_batch_stride + static_cast<long long>(row) * p.ldc;
+      __nv_bfloat16* c_bf16 = static_cast<__nv_bfloat16*>(p.C);
+      if (MODE == 1 && row_ok_pre(row, p.M)) {
+        const int owner = row / p.rows_per_rank;
+        c_bf16 = static_cast<__nv_bfloat16*>(p.rs_peer[owner]);
+        c_off = (static_cast<long long>(p.rank) * p.rows_per_rank + (row - owner * p.rows_per_rank)) * p.ldc;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         if (n0 + c >= p.N) break;  // warp-uniform
@@ -244,7 +292,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               if (col0 + j < p.N) dst[j] = p.accumulate ? dst[j] + v[j] : v[j];
           }
         } else {
-          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.C) + c_off + col0;
+          __nv_bfloat16* dst = c_bf16 + c_off + col0;
           if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
@@ -277,6 +325,65 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   }
 
+  if (MODE == 2 && warp == 6) {
+    // ------------------------------------------------------------------ AllGather copy warp
+    // One lane moves this CTA's share of every chunk peer -> shared bounce buffer -> local gathered operand
+    // with bulk copies (two buffers in flight), own chunk first, then ranks rank+1, rank+2, ...
+    if (lane == 0) {
+      uint8_t* bounce = smem + Cfg::kBounceOffset;
+      uint64_t* bfull = tempty_bar + 2 + 2;   // two barriers after tmem_slot/abort words (see layout below)
+      mbar_init(&bfull[0], 1);
+      mbar_init(&bfull[1], 1);
+      fence_mbar_init();
+      const long long chunk_bytes = static_cast<long long>(p.rows_per_rank) * p.K * 2;
+      long long per = (chunk_bytes / gridDim.x + 15) & ~15LL;
+      if (per * gridDim.x < chunk_bytes) per += 16;
+      const long long lo = per * blockIdx.x;
+      const long long hi = lo + per < chunk_bytes ? lo + per : chunk_bytes;
+      const int pieces = hi > lo ? static_cast<int>((hi - lo + kBounceBytes - 1) / kBounceBytes) : 0;
+      uint32_t gload = 0, gdrain = 0;   // running piece counters: buffer = counter & 1, phase = (counter >> 1) & 1
+      bool okc = true;
+      for (int sidx = 0; sidx < p.world && okc; ++sidx) {
+        const int c = (p.rank + sidx) % p.world;
+        const uint8_t* src = static_cast<const uint8_t*>(p.ag_src[c]);
+        uint8_t* dst = static_cast<uint8_t*>(p.ag_dst) + static_cast<long long>(c) * chunk_bytes;
+        int nload = 0, ndrain = 0;
+        while (ndrain < pieces) {
+          while (nload < pieces && nload - ndrain < 2) {
+            const long long off = lo + static_cast<long long>(nload) * kBounceBytes;
+            const int bytes = static_cast<int>(hi - off < kBounceBytes ? hi - off : kBounceBytes);
+            const int bsel = gload & 1;
+            mbar_expect_tx(&bfull[bsel], bytes);
+            asm volatile(
+                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                    smem_u32(bounce + bsel * kBounceBytes)),
+                "l"(src + off), "r"(bytes), "r"(smem_u32(&bfull[bsel]))
+                : "memory");
+            ++nload;
+            ++gload;
+          }
+          const long long off = lo + static_cast<long long>(ndrain) * kBounceBytes;
+          const int bytes = static_cast<int>(hi - off < kBounceBytes ? hi - off : kBounceBytes);
+          const int d = gdrain & 1;
+          if (!mbar_wait(&bfull[d], (gdrain >> 1) & 1, ab)) { okc = false; break; }
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst + off),
+                       "r"(smem_u32(bounce + d * kBounceBytes)), "r"(bytes)
+                       : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // buffer d may be refilled
+          ++ndrain;
+          ++gdrain;
+        }
+        if (!okc) break;
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");          // stores of this chunk have landed
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence();
+        atomicAdd(p.ag_flags + c, 1);
+      }
+    }
+    __syncwarp();
+  }
+
   // ---------------------------------------------------------------------- teardown
   tc_fence_before_sync();
   __syncthreads();
@@ -300,20 +407,47 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int MODE>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, MODE>;
+  constexpr int smem = MODE == 2 ? Cfg::kSmemBytesAG : Cfg::kSmemBytes;
   static bool configured = false;  // per template instance
   if (!configured) {
-    MSB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    MSB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
   const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN) * p.batch;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, p);
+  kern<<<grid, MODE == 2 ? kGemmThreads + 32 : kGemmThreads, smem, stream>>>(tmA, tmB, p);
   MSB_CUDA_CHECK(cudaGetLastError());
   return kOk;
+}
+
+static int pick_bn(int M, int N, int batch, int bn_hint) {
+  if (bn_hint == 128 || bn_hint == 256) return bn_hint;
+  const long long t256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256) * batch;
+  return (N <= 128 || t256 < sm_count()) ? 128 : 256;
+}
+
+static int encode_operands(CUtensorMap* tmA, CUtensorMap* tmB, const void* A, const void* B, int M, int N, int K,
+                           int batch, int a_mn, int b_mn, long long lda, long long ldb, long long a_batch_stride,
+                           long long b_batch_stride, int bn) {
+  if ((lda % 8) || (ldb % 8) || (a_batch_stride % 8) || (b_batch_stride % 8)) {
+    set_last_error("gemm: pitches and batch strides must be multiples of 8 elements (lda=%lld ldb=%lld)", lda, ldb);
+    return kBadArg;
+  }
+  const uint64_t abs_ = batch > 1 ? static_cast<uint64_t>(a_batch_stride) * 2
+                                  : static_cast<uint64_t>(lda) * 2 * (a_mn ? K : M);
+  const uint64_t bbs_ = batch > 1 ? static_cast<uint64_t>(b_batch_stride) * 2
+                                  : static_cast<uint64_t>(ldb) * 2 * (b_mn ? K : N);
+  int rc;
+  if (a_mn) rc = encode_tmap_3d(tmA, A, 2, M, K, batch, lda * 2, abs_, 64, 64, 1);
+  else      rc = encode_tmap_3d(tmA, A, 2, K, M, batch, lda * 2, abs_, 64, kBM, 1);
+  if (rc != kOk) return rc;
+  if (b_mn) rc = encode_tmap_3d(tmB, B, 2, N, K, batch, ldb * 2, bbs_, 64, 64, 1);
+  else      rc = encode_tmap_3d(tmB, B, 2, K, N, batch, ldb * 2, bbs_, 64, bn, 1);
+  return rc;
 }
 
 }  // namespace msb
@@ -331,45 +465,97 @@ MSB_EXPORT int msb_gemm_bf16(const void* A, const void* B, void* C, const void* 
     set_last_error("gemm: empty problem M=%d N=%d K=%d batch=%d", M, N, K, batch);
     return kBadArg;
   }
-  if ((lda % 8) || (ldb % 8) || (a_batch_stride % 8) || (b_batch_stride % 8)) {
-    set_last_error("gemm: pitches and batch strides must be multiples of 8 elements (lda=%lld ldb=%lld)", lda, ldb);
-    return kBadArg;
-  }
   int* status = status_ptr();
   if (!status) {
     set_last_error("gemm: cannot resolve the device status word");
     return kCudaError;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  int bn = bn_hint;
-  if (bn != 128 && bn != 256) {
-    const long long t256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256) * batch;
-    bn = (N <= 128 || t256 < sm_count()) ? 128 : 256;
-  }
+  const int bn = pick_bn(M, N, batch, bn_hint);
   CUtensorMap tmA, tmB;
-  int rc;
-  const uint64_t abs_ = batch > 1 ? static_cast<uint64_t>(a_batch_stride) * 2 : static_cast<uint64_t>(lda) * 2 * (a_mn ? K : M);
-  const uint64_t bbs_ = batch > 1 ? static_cast<uint64_t>(b_batch_stride) * 2 : static_cast<uint64_t>(ldb) * 2 * (b_mn ? K : N);
-  if (a_mn) rc = encode_tmap_3d(&tmA, A, 2, M, K, batch, lda * 2, abs_, 64, 64, 1);
-  else      rc = encode_tmap_3d(&tmA, A, 2, K, M, batch, lda * 2, abs_, 64, kBM, 1);
-  if (rc != kOk) return rc;
-  if (b_mn) rc = encode_tmap_3d(&tmB, B, 2, N, K, batch, ldb * 2, bbs_, 64, 64, 1);
-  else      rc = encode_tmap_3d(&tmB, B, 2, K, N, batch, ldb * 2, bbs_, 64, bn, 1);
-  if (rc != kOk) return rc;
-
-  GemmParams p;
+  if (int rc = encode_operands(&tmA, &tmB, A, B, M, N, K, batch, a_mn, b_mn, lda, ldb, a_batch_stride,
+                               b_batch_stride, bn))
+    return rc;
+  GemmParams p = {};
   p.C = C; p.bias = bias; p.status = status; p.c_batch_stride = c_batch_stride;
   p.M = M; p.N = N; p.K = K; p.batch = batch; p.ldc = static_cast<int>(ldc);
   p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
 
-#define MSB_DISPATCH(BN_)                                                       \
-  if (a_mn) {                                                                   \
-    if (b_mn) return launch_gemm<BN_, true, true>(tmA, tmB, p, stream);         \
-    return launch_gemm<BN_, true, false>(tmA, tmB, p, stream);                  \
-  } else {                                                                      \
-    if (b_mn) return launch_gemm<BN_, false, true>(tmA, tmB, p, stream);        \
-    return launch_gemm<BN_, false, false>(tmA, tmB, p, stream);                 \
+#define MSB_DISPATCH(BN_)                                                          \
+  if (a_mn) {                                                                      \
+    if (b_mn) return launch_gemm<BN_, true, true, 0>(tmA, tmB, p, stream);         \
+    return launch_gemm<BN_, true, false, 0>(tmA, tmB, p, stream);                  \
+  } else {                                                                         \
+    if (b_mn) return launch_gemm<BN_, false, true, 0>(tmA, tmB, p, stream);        \
+    return launch_gemm<BN_, false, false, 0>(tmA, tmB, p, stream);                 \
   }
   if (bn == 256) { MSB_DISPATCH(256) } else { MSB_DISPATCH(128) }
 #undef MSB_DISPATCH
+}
+
+static int check_chunks(const char* what, int M, int world, int rank) {
+  using namespace msb;
+  if (world < 2 || world > 8 || rank < 0 || rank >= world || M % world || (M / world) % kBM) {
+    set_last_error("%s: M=%d must split into %d chunks that are multiples of %d rows (rank %d)", what, M, world,
+                   kBM, rank);
+    return kBadArg;
+  }
+  return kOk;
+}
+
+// MatMul -> ReduceScatter.  partial[M,N] = A[M,K] x B^T is never materialised locally: tile rows owned by rank o
+// are stored into stage_ptrs[o] + (rank*rows_per_rank + local_row)*N  (bf16 staging of shape [world][M/world][N]
+// on every rank).  After a group barrier each rank sums its `world` slots (msb_reduce_slots).
+MSB_EXPORT int msb_gemm_rs(const void* A, const void* B, const unsigned long long* stage_ptrs, int M, int N, int K,
+                           int b_mn, long long lda, long long ldb, int world, int rank, int bn_hint, void* stream_) {
+  using namespace msb;
+  if (int rc = check_chunks("gemm_rs", M, world, rank)) return rc;
+  if (N % 8) { set_last_error("gemm_rs: N=%d must be a multiple of 8", N); return kBadArg; }
+  int* status = status_ptr();
+  if (!status) { set_last_error("gemm_rs: no status word"); return kCudaError; }
+  const int bn = pick_bn(M, N, 1, bn_hint);
+  CUtensorMap tmA, tmB;
+  if (int rc = encode_operands(&tmA, &tmB, A, B, M, N, K, 1, 0, b_mn, lda, ldb, 0, 0, bn)) return rc;
+  GemmParams p = {};
+  p.status = status; p.M = M; p.N = N; p.K = K; p.batch = 1; p.ldc = N; p.alpha = 1.f;
+  p.world = world; p.rank = rank; p.rows_per_rank = M / world;
+  for (int i = 0; i < world; ++i) p.rs_peer[i] = reinterpret_cast<void*>(stage_ptrs[i]);
+  p.C = p.rs_peer[rank];
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (bn == 256) {
+    if (b_mn) return launch_gemm<256, false, true, 1>(tmA, tmB, p, stream);
+    return launch_gemm<256, false, false, 1>(tmA, tmB, p, stream);
+  }
+  if (b_mn) return launch_gemm<128, false, true, 1>(tmA, tmB, p, stream);
+  return launch_gemm<128, false, false, 1>(tmA, tmB, p, stream);
+}
+
+// AllGather -> MatMul.  C[M,N] = gather(A)[M,K] x B^T (+ bias) where chunk c of the gathered operand is pulled from
+// src_ptrs[c] (rank c's [M/world][K] shard in symmetric memory) into `gathered` ([M][K], local) by the kernel
+// itself while tiles of chunks that have already arrived are being multiplied.  flags: int[world], zeroed here.
+MSB_EXPORT int msb_gemm_ag(const unsigned long long* src_ptrs, void* gathered, int* flags, const void* B, void* C,
+                           const void* bias, int M, int N, int K, int b_mn, long long ldb, long long ldc, int world,
+                           int rank, int bn_hint, void* stream_) {
+  using namespace msb;
+  if (int rc = check_chunks("gemm_ag", M, world, rank)) return rc;
+  if (K % 8) { set_last_error("gemm_ag: K=%d must be a multiple of 8", K); return kBadArg; }
+  int* status = status_ptr();
+  if (!status) { set_last_error("gemm_ag: no status word"); return kCudaError; }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MSB_CUDA_CHECK(cudaMemsetAsync(flags, 0, sizeof(int) * world, stream));
+  const int bn = pick_bn(M, N, 1, bn_hint);
+  CUtensorMap tmA, tmB;
+  if (int rc = encode_operands(&tmA, &tmB, gathered, B, M, N, K, 1, 0, b_mn, K, ldb, 0, 0, bn)) return rc;
+  GemmParams p = {};
+  p.C = C; p.bias = bias; p.status = status; p.M = M; p.N = N; p.K = K; p.batch = 1;
+  p.ldc = static_cast<int>(ldc); p.alpha = 1.f;
+  p.world = world; p.rank = rank; p.rows_per_rank = M / world;
+  for (int i = 0; i < world; ++i) p.ag_src[i] = reinterpret_cast<const void*>(src_ptrs[i]);
+  p.ag_dst = gathered; p.ag_flags = flags;
+  if (bn == 256) {
+    if (b_mn) return launch_gemm<256, false, true, 2>(tmA, tmB, p, stream);
+    return launch_gemm<256, false, false, 2>(tmA, tmB, p, stream);
+  }
+  if (b_mn) return launch_gemm<128, false, true, 2>(tmA, tmB, p, stream);
+  return launch_gemm<128, false, false, 2>(tmA, tmB, p, stream);
 }
