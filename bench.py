@@ -126,7 +126,8 @@ def main():
                              % args.gpus)
         args.gpus = world
     torch.cuda.set_device(local_rank)
-    ms.set_context(mode=ms.PYNATIVE_MODE, device_target="GPU", device_id=local_rank)
+    ms.set_context(mode=ms.PYNATIVE_MODE, device_target="GPU", device_id=local_rank,
+                   enable_cuda_graph=os.environ.get("MSB200_CUDA_GRAPH", "1") != "0")
     if world > 1:
         from mindspore_b200.communication import init
         init("nccl")
@@ -222,6 +223,8 @@ def main():
                        "micro_batch": 1, "seq_len": args.seq,
                        "parallelism": "mp%d+sp" % world if world > 1 else "single",
                        "optimizer": "AdamW fp32 master + moments, grad clip 1.0",
+                       "cuda_graph": bool(ms.get_context("enable_cuda_graph")),
+                       "fused_comm": bool(world > 1 and os.environ.get("MSB200_FUSED_COMM", "1") != "0"),
                        "l2": "working set >100 GB per step, far larger than the 126 MB L2 (no flush needed)"},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,

@@ -37,10 +37,20 @@ __device__ __forceinline__ int ld_acquire_sys(const int* addr) {
   return v;
 }
 
-// pads.p[r] -> int[world * channels] on rank r.  Thread t tells peer t "rank `rank` reached epoch", then waits
-// until every peer has told us the same.  A wait that runs past the limit sets status bit 2 and returns.
-__global__ void symm_barrier_kernel(PeerPtrs pads, int rank, int world, int channel, int epoch, int* status) {
+// pads.p[r] -> int[channels * world] flag words followed by int[channels] epoch counters on rank r.  The epoch
+// lives in device memory and is advanced by the kernel itself, so the barrier can be captured in a CUDA graph
+// and replayed.  Thread t tells peer t "rank `rank` reached epoch e", then waits until every peer has told us
+// the same.  A wait that runs past the limit sets status bit 2 and returns.
+__global__ void symm_barrier_kernel(PeerPtrs pads, int rank, int world, int channel, int channels, int* status) {
+  __shared__ int epoch_s;
   const int t = threadIdx.x;
+  if (t == 0) {
+    int* ep = static_cast<int*>(pads.p[rank]) + channels * world + channel;
+    epoch_s = *ep + 1;
+    *ep = epoch_s;
+  }
+  __syncthreads();
+  const int epoch = epoch_s;
   if (t >= world) return;
   __threadfence_system();
   int* remote = static_cast<int*>(pads.p[t]) + channel * world + rank;
@@ -178,13 +188,13 @@ static int fill_peers(PeerPtrs* out, const unsigned long long* ptrs, int world, 
 
 using namespace msb;
 
-MSB_EXPORT int msb_symm_barrier(const unsigned long long* pad_ptrs, int rank, int world, int channel, int epoch,
+MSB_EXPORT int msb_symm_barrier(const unsigned long long* pad_ptrs, int rank, int world, int channel, int channels,
                                 void* stream) {
   PeerPtrs pads;
   if (int rc = fill_peers(&pads, pad_ptrs, world, "symm_barrier")) return rc;
   int* status = status_ptr();
   if (!status) { set_last_error("symm_barrier: no status word"); return kCudaError; }
-  symm_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pads, rank, world, channel, epoch, status);
+  symm_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pads, rank, world, channel, channels, status);
   MSB_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }

@@ -155,6 +155,17 @@ class TrainOneStepCell(Cell):
         self.use_arena = getattr(optimizer, "use_arena", False)
         self._use_graph = None
 
+    def _micro_runner(self, network, scale):
+        """Callable running forward + backward of one micro-batch.  With the context option ``enable_cuda_graph``
+        and CUDA inputs the micro-batch is captured once into a CUDA graph (after two eager calls) and replayed:
+        thousands of kernel launches per micro-batch become one, which removes the host launch bound."""
+        runner = getattr(self, "_runner", None)
+        if runner is None or runner.network is not network:
+            runner = _MicroBatchRunner(network, scale)
+            self._runner = runner
+        runner.scale = scale
+        return runner
+
     def _arena_step(self, inputs):
         """Arena optimizers: gradients flow straight into the flat fp32 accumulator inside backward."""
         opt = self.optimizer
@@ -164,12 +175,10 @@ class TrainOneStepCell(Cell):
             # micro-batches run back to back; each backward accumulates into the flat fp32 gradient arena
             total = None
             k = net.micro_size
+            runner = self._micro_runner(net.network, self.sens / k)
             for i in range(k):
-                mb = net.micro_inputs(i, *inputs)
-                with torch.enable_grad():
-                    li = net.network(*mb)
-                (li * (self.sens / k)).backward()
-                total = li.detach() if total is None else total + li.detach()
+                li = runner(net.micro_inputs(i, *inputs))
+                total = li.clone() if total is None else total + li
             loss = total / k
         else:
             with torch.enable_grad():
@@ -198,6 +207,58 @@ class TrainOneStepCell(Cell):
         if self.return_grad:
             return loss, {p.name: g for p, g in zip(self.weights, grads)}
         return loss
+
+
+class _MicroBatchRunner:
+    """Forward + backward of one micro-batch, eagerly or as a replayed CUDA graph.
+
+    The graph owns static input buffers; each call copies the micro-batch into them and replays.  Everything the
+    captured region launches must be replay-safe: parameter gradients accumulate in place into the arena,
+    collectives are NCCL (capturable) or the symmetric-memory kernels whose barrier epoch lives on the device."""
+
+    WARMUP_CALLS = 2
+
+    def __init__(self, network, scale):
+        self.network, self.scale = network, scale
+        self.calls = 0
+        self.graph = None
+        self.static_inputs = None
+        self.static_loss = None
+        self.launches_per_replay = 0
+
+    def _eager(self, inputs):
+        from ..parallel import fused_comm
+        fused_comm.step_fence()
+        with torch.enable_grad():
+            loss = self.network(*inputs)
+        (loss * self.scale).backward()
+        return loss.detach()
+
+    def __call__(self, inputs):
+        use_graph = context.get_context("enable_cuda_graph") and all(
+            (not isinstance(t, torch.Tensor)) or t.is_cuda for t in inputs)
+        if not use_graph:
+            return self._eager(inputs)
+        self.calls += 1
+        if self.graph is None:
+            if self.calls <= self.WARMUP_CALLS:
+                return self._eager(inputs)
+            from .. import _native
+            self.static_inputs = tuple(t.clone() if isinstance(t, torch.Tensor) else t for t in inputs)
+            torch.cuda.synchronize()
+            before = _native.launch_count
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self.static_loss = self._eager(self.static_inputs)
+            self.launches_per_replay = _native.launch_count - before
+            _native.launch_count = before
+        for s, t in zip(self.static_inputs, inputs):
+            if isinstance(s, torch.Tensor):
+                s.copy_(t)
+        self.graph.replay()
+        from .. import _native
+        _native.launch_count += self.launches_per_replay
+        return self.static_loss
 
 
 def _collect_stray_grads(params):

@@ -70,8 +70,7 @@ class SymmContext:
                 pass
         self.buffers = {}
         self.counters = {}
-        self.epochs = [0] * self.CHANNELS
-        pads, self.pad_ptrs = self._alloc_raw(self.CHANNELS * self.world * 4)
+        pads, self.pad_ptrs = self._alloc_raw(self.CHANNELS * (self.world + 1) * 4)
         pads.zero_()
         torch.cuda.synchronize()
         torch.distributed.barrier(group=self.pg)
@@ -103,9 +102,9 @@ class SymmContext:
         return "%s#%d" % (tag, c & 1)
 
     def barrier(self, channel=0):
-        self.epochs[channel] += 1
+        """Stream-ordered group barrier; its epoch counter lives on the device, so it replays inside CUDA graphs."""
         rc = _native.cuda().msb_symm_barrier(_ptr_array(self.pad_ptrs), self.rank, self.world, channel,
-                                             self.epochs[channel], _stream())
+                                             self.CHANNELS, _stream())
         _native.check(rc, "symm_barrier")
         _count()
 
@@ -280,3 +279,11 @@ def reduce_scatter_adamw(ctx, grad_ptrs, weight_ptrs, master, m, v, per, hyper, 
                                                  _p(v), ctx.rank, ctx.world, per, _p(hyper), _p(skip), _stream())
     _native.check(rc, "reduce_scatter_adamw")
     _count()
+
+
+def step_fence():
+    """One group barrier at the start of a micro-step for every active symmetric-memory context.  It separates the
+    last fused operation of the previous micro-step from the first of this one, so the two-buffer rotation stays
+    valid across CUDA-graph replays (where the rotation restarts at buffer 0)."""
+    for ctx in _contexts.values():
+        ctx.barrier(3)
