@@ -17,6 +17,11 @@ import torch
 from . import dtype as mstype
 
 
+def _sharded_mode():
+    from ..context import _AutoParallelContext
+    return _AutoParallelContext()._v["parallel_mode"] in ("semi_auto_parallel", "auto_parallel")
+
+
 class _SizeInt(int):
     """``Tensor.size`` in MindSpore is the element count; torch code calls ``size()``.  Both work."""
 
@@ -94,6 +99,14 @@ class Tensor(torch.Tensor):
 
     def __init__(self, *args, **kwargs):
         pass
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        out = super().__torch_function__(func, types, args, kwargs or {})
+        if _sharded_mode():
+            from ..parallel import spmd
+            spmd.propagate_elementwise(func, args, out)
+        return out
 
     # ------------------------------------------------------------------ conversion
     def asnumpy(self):

@@ -133,7 +133,7 @@ class _Recorder(TorchFunctionMode):
             return NotImplemented
         self.depth += 1
         try:
-            out = _prim_mod._wrap_out(prim._run(*args, **kwargs))
+            out = _prim_mod._wrap_out(prim._execute(*args, **kwargs))
         finally:
             self.depth -= 1
         if _has_tensor(out) or prim._update_parameter or prim.name in ("Send", "Barrier"):

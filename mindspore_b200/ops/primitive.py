@@ -17,6 +17,10 @@ import inspect
 import torch
 
 from ..common.tensor import Tensor
+from ..context import _AutoParallelContext
+
+_parallel_ctx = _AutoParallelContext()
+_SHARDED_MODES = ("semi_auto_parallel", "auto_parallel")
 
 # set by graph.tracer while a trace is in flight: callable(prim, args, kwargs) -> proxy or NotImplemented
 _trace_hook = None
@@ -159,7 +163,18 @@ class Primitive:
             out = _trace_hook(self, args, kwargs)
             if out is not NotImplemented:
                 return out
-        return _wrap_out(self._run(*args, **kwargs))
+        return _wrap_out(self._execute(*args, **kwargs))
+
+    def _execute(self, *args, **kwargs):
+        """``_run`` under the current parallel mode: with a shard strategy (or sharded inputs) in
+        semi_auto_parallel / auto_parallel mode the call goes through the SPMD dispatcher."""
+        if _parallel_ctx._v["parallel_mode"] in _SHARDED_MODES and type(self).__module__[-8:] != "comm_ops":
+            from ..parallel import spmd
+            if spmd.needs_dispatch(self, args):
+                out = spmd.dispatch(self, args, kwargs)
+                if out is not NotImplemented:
+                    return out
+        return self._run(*args, **kwargs)
 
     def __repr__(self):
         extra = ", ".join("%s=%r" % (k, v) for k, v in self.init_attrs.items() if k != "name")

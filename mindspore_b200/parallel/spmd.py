@@ -1,0 +1,350 @@
+"""Execution of shard strategies: the step-parallel transformation, applied where the primitive is called.
+
+In ``semi_auto_parallel`` / ``auto_parallel`` mode a primitive that carries a strategy (``Primitive.shard``), or
+whose inputs carry layouts, goes through ``dispatch``:
+
+1. the OperatorInfo of the primitive turns the strategy into required input layouts, output layouts and the
+   forward communication;
+2. every tensor input is redistributed from its current layout to the required one (``redistribution.apply``:
+   StridedSlice / AllGather / AlltoAll); Parameters are sliced once according to the layout and remember it
+   (``parameter_layout_dict``), and a replicated Parameter gets a ``_MirrorOperator`` so that its gradient is
+   all-reduced over the replica group;
+3. the primitive runs on the local slices (with shape-like arguments localised);
+4. the forward communication (AllReduce or ReduceScatter over the contraction device dims) is applied;
+5. outputs are tagged with their layouts.
+
+Because the collectives are differentiable primitives, backward communication needs no separate pass, and when
+this happens under graph tracing the comm primitives are recorded as graph nodes - the traced graph *is* the
+step-parallel graph.  This replaces the compile-time rewrite of ccsrc/frontend/parallel/step_parallel.cc
+:2738-2793 (ParallelCommunication: InsertForwardOps, StepRedistribution, InsertMirrorOps, InsertVirtualDivOp).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .. import context
+from ..common.parameter import Parameter
+from ..communication import management as M
+from . import operator_info as OI
+from . import redistribution as RD
+from .layout import TensorLayout, slice_for_rank
+
+_ATTR = "_ms_layout"
+
+parameter_layouts = {}      # name -> TensorLayout, filled as parameters get sliced
+_mirror_cache = {}
+
+
+def active():
+    mode = context.get_auto_parallel_context("parallel_mode")
+    return mode in (context.ParallelMode.SEMI_AUTO_PARALLEL, context.ParallelMode.AUTO_PARALLEL)
+
+
+def get_layout(t):
+    return getattr(t, _ATTR, None) if isinstance(t, torch.Tensor) else None
+
+
+def set_layout(t, layout):
+    if isinstance(t, torch.Tensor):
+        setattr(t, _ATTR, layout)
+    return t
+
+
+def stage_devices():
+    n = context.get_auto_parallel_context("device_num")
+    return n // context.get_auto_parallel_context("pipeline_stages")
+
+
+def _rank():
+    return context.get_auto_parallel_context("global_rank")
+
+
+def _stage_base():
+    per = stage_devices()
+    return (_rank() // per) * per
+
+
+def full_shape(t):
+    lay = get_layout(t)
+    if lay is not None:
+        return lay.shape
+    if isinstance(t, Parameter) and t.full_shape is not None:
+        return t.full_shape
+    return tuple(t.shape)
+
+
+def needs_dispatch(prim, args):
+    if prim.in_strategy is not None:
+        return True
+    return any(get_layout(a) is not None for a in args if isinstance(a, torch.Tensor)) or \
+        any(isinstance(a, (tuple, list)) and any(get_layout(x) is not None for x in a) for a in args)
+
+
+def _group_for(dev_matrix, dev_dims):
+    ranks = RD.group_ranks(dev_matrix, _rank() - _stage_base(), list(dev_dims), _stage_base())
+    return M.group_for_ranks(ranks), ranks
+
+
+def _mirror(param, layout):
+    """Replicated parameter -> identity whose backward all-reduces the gradient over the replica group."""
+    from ..ops import comm_ops
+    dims = layout.unused_dev_dims()
+    if not dims or not param._ms_requires_grad:
+        return param
+    gname, ranks = _group_for(layout.device_matrix, dims)
+    key = (gname, len(ranks))
+    op = _mirror_cache.get(key)
+    if op is None:
+        op = comm_ops._MirrorOperator(gname, len(ranks), context.get_auto_parallel_context("gradients_mean"))
+        _mirror_cache[key] = op
+    out = op._run(_plain(param))
+    return out
+
+
+_equiv_cache = {}
+
+
+def layouts_equivalent(a: TensorLayout, b: TensorLayout):
+    """True when both layouts give every rank the same slice (e.g. device matrices that differ only by
+    size-1 dims or by how the repeat dim is written)."""
+    if a == b:
+        return True
+    key = (a, b)
+    if key not in _equiv_cache:
+        ok = a.shape == b.shape and a.num_devices() == b.num_devices() and \
+            a.tensor_strategy() == b.tensor_strategy() and a.opt_shard_size == b.opt_shard_size and \
+            all(a.slice_index(r) == b.slice_index(r) for r in range(a.num_devices()))
+        _equiv_cache[key] = ok
+    return _equiv_cache[key]
+
+
+def _plain(t):
+    return t.as_subclass(torch.Tensor) if type(t) is not torch.Tensor else t
+
+
+def _redistribute(x, cur, need):
+    if layouts_equivalent(cur, need):
+        return x
+    return RD.apply(_plain(x), cur, need, _rank(), _stage_base())
+
+
+def _prepare_input(x, need: TensorLayout):
+    if isinstance(x, Parameter):
+        if x.param_layout is None:
+            x.init_data(need, set_sliced=True)
+            parameter_layouts[x.name] = need
+            set_layout(x, need)
+        cur = x.param_layout
+        y = _redistribute(_mirror(x, cur), cur, need)
+        return set_layout(y, need)
+    cur = get_layout(x)
+    if cur is None:
+        # an untagged activation holds the full tensor on every rank (full_batch inputs, constants)
+        if tuple(x.shape) == tuple(need.slice_shape()) and tuple(need.shape) != tuple(x.shape):
+            return set_layout(x, need)          # already a local slice (dataset sharded by the loader)
+        y = slice_for_rank(_plain(x), need, _rank() - _stage_base())
+        return set_layout(y if y.is_contiguous() else y.contiguous(), need)
+    from ..common.tensor import as_tensor
+    return set_layout(as_tensor(_redistribute(x, cur, need)), need)
+
+
+def _forward_comm(y, info, out_index=0):
+    from ..communication import comm_func as CF
+    fc = info.forward_comm
+    if fc is None or out_index != 0:
+        return y
+    kind, dims = fc[0], fc[1]
+    y = _plain(y)
+    gname, ranks = _group_for(info.dev_matrix, dims)
+    if kind == "AllReduce":
+        return CF.all_reduce_autograd(y, "sum", gname)
+    if kind == "AllReduceMean":
+        return CF.all_reduce_autograd(y, "sum", gname) / len(ranks)
+    if kind in ("AllReduceMax", "AllReduceMin"):
+        return CF.all_reduce_autograd(y, kind[9:].lower(), gname)
+    if kind == "ReduceScatter":
+        dim = fc[2]
+        if dim == 0:
+            return CF.reduce_scatter_autograd(y.contiguous(), "sum", gname)
+        return CF.reduce_scatter_autograd(y.movedim(dim, 0).contiguous(), "sum", gname).movedim(0, dim).contiguous()
+    raise NotImplementedError(kind)
+
+
+def _follow_strategy(prim, tensors):
+    """Strategy of an un-annotated primitive: follow the first sharded input when shapes allow (elementwise
+    'strategy follow'), else replicate."""
+    lays = [get_layout(t) for t in tensors]
+    first = next((l for l in lays if l is not None), None)
+    if first is None:
+        return None
+    strat = []
+    for t, l in zip(tensors, lays):
+        shp = full_shape(t)
+        if l is not None:
+            strat.append(l.tensor_strategy())
+        elif len(shp) == len(first.shape) and all(a == b or a == 1 for a, b in zip(shp, first.shape)):
+            fs = first.tensor_strategy()
+            strat.append(tuple(1 if a == 1 else s for a, s in zip(shp, fs)))
+        else:
+            strat.append(tuple(1 for _ in shp))
+    return tuple(strat)
+
+
+def dispatch(prim, args, kwargs):
+    """Runs ``prim`` under its shard strategy.  Returns NotImplemented when the primitive takes no tensor."""
+    tensor_pos = [i for i, a in enumerate(args) if isinstance(a, torch.Tensor)]
+    if not tensor_pos:
+        return NotImplemented
+    tensors = [args[i] for i in tensor_pos]
+    strategy = prim.in_strategy
+    if strategy is None:
+        strategy = _follow_strategy(prim, tensors)
+        if strategy is None:
+            return NotImplemented
+    if len(strategy) < len(tensors):
+        strategy = tuple(strategy) + tuple(tuple(1 for _ in full_shape(t)) for t in tensors[len(strategy):])
+    shapes = [full_shape(t) for t in tensors]
+    extra = {}
+    name = prim.name
+    others = [a for i, a in enumerate(args) if i not in tensor_pos]
+    if name in ("ReduceSum", "ReduceMean", "ReduceMax", "ReduceMin", "ReduceAll", "ReduceAny", "ReduceProd"):
+        extra["axis"] = others[0] if others else ()
+    elif name == "Transpose":
+        extra["perm"] = others[0]
+    elif name == "Reshape":
+        extra["shape"] = others[0]
+    elif name in ("Gather", "SparseGatherV2"):
+        extra["axis"] = others[0] if others else 0
+    elif name == "OneHot":
+        extra["depth"] = others[0]
+    try:
+        info = OI.make_info(prim, shapes[:len(strategy)], strategy[:len(shapes)], prim.out_strategy,
+                            stage_devices(), **extra)
+    except OI.StrategyError:
+        if prim.in_strategy is not None:
+            raise
+        return _run_replicated(prim, args, kwargs)
+    need = info.input_layouts()
+    local = list(args)
+    for j, pos in enumerate(tensor_pos):
+        if j < len(need):
+            v = _prepare_input(args[pos], need[j])
+            local[pos] = v if isinstance(v, Parameter) else _plain(v)
+    # localise shape-like arguments
+    la = info.local_attrs()
+    if name == "Reshape" and "shape" in la:
+        idx = [i for i in range(len(args)) if i not in tensor_pos][0]
+        local[idx] = la["shape"]
+    saved = {}
+    for k, v in la.items():
+        if k != "shape" and hasattr(prim, k):
+            saved[k] = getattr(prim, k)
+            setattr(prim, k, v)
+    try:
+        if name in ("Gather", "EmbeddingLookup", "SparseGatherV2") and info.vocab_split() > 1:
+            out = _sharded_gather(local, info)
+        else:
+            out = prim._run(*local, **kwargs)
+    finally:
+        for k, v in saved.items():
+            setattr(prim, k, v)
+    from ..common.tensor import as_tensor
+    out_lays = info.output_layouts()
+    if isinstance(out, torch.Tensor):
+        out = as_tensor(_forward_comm(out, info))
+        return set_layout(out, out_lays[0])
+    if isinstance(out, (tuple, list)):
+        res = []
+        for i, o in enumerate(out):
+            if isinstance(o, torch.Tensor) and i < len(out_lays):
+                res.append(set_layout(as_tensor(_forward_comm(o, info, i)), out_lays[i]))
+            else:
+                res.append(o)
+        return type(out)(res)
+    return out
+
+
+def _sharded_gather(local, info):
+    from ..ops import fused
+    table, ids = local[0], local[1]
+    n = info.vocab_split()
+    k = info.inputs_tensor_map[0][0]
+    pos = RD._coord_along(info.dev_matrix, _rank() - _stage_base(), k)
+    return fused.embedding(table, ids, pos * table.shape[0])
+
+
+def _run_replicated(prim, args, kwargs):
+    """Gathers every sharded input to its full value and runs the primitive replicated."""
+    local = []
+    for a in args:
+        lay = get_layout(a)
+        if lay is not None:
+            full = TensorLayout(lay.device_matrix, [-1] * len(lay.shape), lay.shape)
+            a = RD.apply(_plain(a), lay, full, _rank(), _stage_base())
+        local.append(a)
+    return prim._run(*local, **kwargs)
+
+
+def to_full(t):
+    """Full (replicated) value of a possibly sharded tensor."""
+    lay = get_layout(t)
+    if lay is None:
+        return t
+    full = TensorLayout(lay.device_matrix, [-1] * len(lay.shape), lay.shape)
+    out = RD.apply(_plain(t), lay, full, _rank(), _stage_base())
+    from ..common.tensor import as_tensor
+    return as_tensor(out)
+
+
+def virtual_div_loss(loss):
+    """Applies _VirtualDiv when the (scalar) loss is replicated over r ranks and ``loss_repeated_mean`` is on."""
+    from ..ops import comm_ops
+    lay = get_layout(loss)
+    r = lay.repeat_num() if lay is not None else stage_devices()
+    if r > 1 and context.get_auto_parallel_context("loss_repeated_mean"):
+        return comm_ops._VirtualDiv(r)(loss)
+    return loss
+
+
+def reset():
+    parameter_layouts.clear()
+    _mirror_cache.clear()
+
+
+_SHAPE_CHANGING = ("sum", "mean", "amax", "amin", "max", "min", "prod", "matmul", "mm", "bmm", "reshape", "view",
+                   "permute", "transpose", "cat", "stack", "softmax", "log_softmax", "layer_norm", "linear",
+                   "__getitem__", "narrow", "index_select", "gather", "cumsum", "norm", "flatten", "squeeze",
+                   "unsqueeze", "expand", "repeat", "var", "std", "argmax", "argmin", "topk", "sort")
+
+
+def propagate_elementwise(func, args, out):
+    """Layout propagation for plain tensor arithmetic (``y * y``, ``x + 1`` ...) that does not go through a
+    Primitive: a shape-preserving function of sharded operands yields a result with the same layout.  Any other
+    torch function applied to a sharded tensor is refused, because its result would silently be a partial value:
+    use the ``ops`` primitives (which know their distributed semantics) instead."""
+    if not isinstance(out, torch.Tensor):
+        return
+    lay = None
+    for a in args:
+        l = get_layout(a)
+        if l is not None:
+            if lay is not None and l != lay:
+                return
+            lay = l
+    if lay is None:
+        return
+    name = getattr(func, "__name__", "")
+    if name in ("detach", "clone", "contiguous", "to", "type", "float", "bfloat16", "half", "requires_grad_",
+                "view_as", "alias", "__get__", "__set__", "data", "as_subclass", "size", "dim", "numel", "stride",
+                "is_contiguous", "element_size", "storage_offset", "data_ptr", "backward", "register_hook",
+                "__repr__", "__format__", "item", "tolist", "cpu", "cuda", "numpy", "is_floating_point",
+                "is_complex", "__hash__", "__bool__", "__len__", "isfinite", "isnan"):
+        if tuple(out.shape) == tuple(lay.slice_shape()):
+            set_layout(out, lay)
+        return
+    if name in _SHAPE_CHANGING:
+        raise NotImplementedError("torch function %r was applied to a tensor sharded as %s; in (semi_)auto_parallel "
+                                  "mode use the ops primitives, which carry distributed semantics" % (name, lay))
+    if tuple(out.shape) == tuple(lay.slice_shape()):
+        set_layout(out, lay)
