@@ -127,7 +127,7 @@ def main():
         args.gpus = world
     torch.cuda.set_device(local_rank)
     ms.set_context(mode=ms.PYNATIVE_MODE, device_target="GPU", device_id=local_rank,
-                   enable_cuda_graph=os.environ.get("MSB200_CUDA_GRAPH", "1") != "0")
+                   enable_cuda_graph=os.environ.get("MSB200_CUDA_GRAPH", "0") == "1")
     if world > 1:
         from mindspore_b200.communication import init
         init("nccl")
@@ -237,6 +237,7 @@ def main():
             "max_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
         }
         print(json.dumps(out), flush=True)
+    step_cell.release_graphs()
     if world > 1:
         torch.distributed.barrier()
         M.release()

@@ -166,6 +166,16 @@ class TrainOneStepCell(Cell):
         runner.scale = scale
         return runner
 
+    def release_graphs(self):
+        """Destroys captured CUDA graphs.  Call it before the communication groups are destroyed: a graph that
+        holds captured NCCL kernels must not outlive its communicator."""
+        runner = getattr(self, "_runner", None)
+        if runner is not None and runner.graph is not None:
+            torch.cuda.synchronize()
+            runner.graph = None
+            runner.static_inputs = runner.static_loss = None
+            runner.calls = 0
+
     def _arena_step(self, inputs):
         """Arena optimizers: gradients flow straight into the flat fp32 accumulator inside backward."""
         opt = self.optimizer
