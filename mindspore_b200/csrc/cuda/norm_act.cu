@@ -540,3 +540,68 @@ MSB_EXPORT int msb_gelu(const void* x, const void* bias, const void* dy, void* y
   MSB_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
+
+// ----------------------------------------------------------------------------------------------------------------
+// RMSNorm backward without any allocation (declared in no_alloc.h): the [H] fp32 weight-gradient accumulator is the
+// static device array below.  One array per device (each device holds its own instance of a __device__ variable).
+#include "no_alloc.h"
+
+#include <atomic>
+
+static __device__ __align__(256) float g_rmsnorm_bwd_static_acc[MSB_RMSNORM_BWD_STATIC_MAX_H];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::atomic<float*> g_static_acc_ptr[kMaxDevices];
+
+// Device address of this device's instance of the array; looked up on the first call per device and kept.
+int static_acc_ptr(float** out) {
+  int dev = 0;
+  MSB_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) {
+    set_last_error("rmsnorm_bwd_static: device ordinal %d is beyond %d", dev, kMaxDevices - 1);
+    return kTooLarge;
+  }
+  float* p = g_static_acc_ptr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    MSB_CUDA_CHECK(cudaGetSymbolAddress((void**)&p, g_rmsnorm_bwd_static_acc));
+    if (p == nullptr) {
+      set_last_error("rmsnorm_bwd_static: cudaGetSymbolAddress returned a null address");
+      return kCudaError;
+    }
+    g_static_acc_ptr[dev].store(p, std::memory_order_release);
+  }
+  *out = p;
+  return kOk;
+}
+}  // namespace
+
+MSB_EXPORT int msb_rmsnorm_bwd_static(const void* dy, const void* x, const void* w, const float* rstd,
+                                      const void* dres, void* dx, void* dw_out, int dw_fp32, int accumulate,
+                                      long long rows, int H, void* stream_) {
+  if (H > MSB_RMSNORM_BWD_STATIC_MAX_H) {
+    set_last_error("rmsnorm_bwd_static: hidden size %d exceeds the static scratch of %d floats", H,
+                   MSB_RMSNORM_BWD_STATIC_MAX_H);
+    return kTooLarge;
+  }
+  if (int rc = check_h("rmsnorm_bwd_static", H)) return rc;
+  float* acc = nullptr;
+  if (int rc = static_acc_ptr(&acc)) return rc;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  MSB_CUDA_CHECK(cudaMemsetAsync(acc, 0, sizeof(float) * H, stream));
+  if (rows > 0) {
+    const int grid = (int)(rows < 2LL * sm_count() ? rows : 2LL * sm_count());
+#define CALL(I)                                                                                      \
+  rmsnorm_bwd_kernel<I><<<grid, kNormThreads, 0, stream>>>(                                          \
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,              \
+      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, acc, (int)rows, H)
+    MSB_ITER_DISPATCH(H, CALL);
+#undef CALL
+  }
+  if (dw_out) {
+    finalize_acc_kernel<<<(H + 255) / 256, 256, 0, stream>>>(acc, dw_fp32 ? nullptr : (__nv_bfloat16*)dw_out,
+                                                             dw_fp32 ? (float*)dw_out : nullptr, H, accumulate);
+  }
+  MSB_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
