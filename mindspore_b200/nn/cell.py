@@ -170,7 +170,16 @@ class Cell:
 
     _recompute_enabled = True
 
+    # set by parallel.pipeline while a pipeline stage runs: callable(cell, inputs, kwargs) deciding whether a
+    # cell tagged with ``pipeline_stage`` runs here, is skipped, or ends this stage's part of the forward pass
+    _stage_hook = None
+
     def __call__(self, *inputs, **kwargs):
+        if Cell._stage_hook is not None and self._pipeline_stage is not None:
+            return Cell._stage_hook(self, inputs, kwargs)
+        return self._call_impl(inputs, kwargs)
+
+    def _call_impl(self, inputs, kwargs):
         from ..graph import tracer as _tracer
         if Cell._graph_depth > 0 or _tracer.is_tracing():
             return self._run_construct(inputs, kwargs)

@@ -176,12 +176,30 @@ class TrainOneStepCell(Cell):
             runner.static_inputs = runner.static_loss = None
             runner.calls = 0
 
+    def _pipeline_step(self, inputs):
+        """Pipeline parallel without an arena optimizer: the stage runtime leaves gradients in ``.grad``."""
+        from ..parallel.pipeline import run_pipeline_step
+        for p in self.weights:
+            p.grad = None
+        loss = run_pipeline_step(self.network, inputs, self.sens / self.network.micro_size)
+        grads = tuple(_wrap_out(p.grad if p.grad is not None else torch.zeros_like(p)) for p in self.weights)
+        for p in self.weights:
+            p.grad = None
+        if self.grad_reducer is not None:
+            grads = self.grad_reducer(grads)
+        self.optimizer(grads)
+        return _wrap_out(loss)
+
     def _arena_step(self, inputs):
         """Arena optimizers: gradients flow straight into the flat fp32 accumulator inside backward."""
         opt = self.optimizer
         opt.zero_grad()
         net = self.network
-        if isinstance(net, GradAccumulationCell):
+        if isinstance(net, PipelineCell) and not isinstance(net, GradAccumulationCell) and \
+                context.get_auto_parallel_context("pipeline_stages") > 1:
+            from ..parallel.pipeline import run_pipeline_step
+            loss = run_pipeline_step(net, inputs, self.sens / net.micro_size)
+        elif isinstance(net, GradAccumulationCell):
             # micro-batches run back to back; each backward accumulates into the flat fp32 gradient arena
             total = None
             k = net.micro_size
@@ -208,6 +226,9 @@ class TrainOneStepCell(Cell):
     def construct(self, *inputs):
         if self.use_arena:
             return _wrap_out(self._arena_step(inputs))
+        if isinstance(self.network, PipelineCell) and not isinstance(self.network, GradAccumulationCell) and \
+                context.get_auto_parallel_context("pipeline_stages") > 1:
+            return self._pipeline_step(inputs)
         loss = self.network(*inputs)
         sens = torch.full_like(loss, self.sens) if isinstance(loss, torch.Tensor) else self.sens
         grads = self.grad(self.network, self.weights)(*inputs, sens)
