@@ -19,6 +19,10 @@ from .train.callback import (Callback, CheckpointConfig, LossMonitor, ModelCheck
 from .train.serialization import (export, load, load_checkpoint, load_param_into_net, save_checkpoint)
 from . import train as _train
 from .train import amp
+from .parallel import (build_searched_strategy, load_distributed_checkpoint, merge_pipeline_strategys,
+                       merge_sliced_parameter, rank_list_for_transform, restore_group_info_list,
+                       sync_pipeline_shared_parameters, transform_checkpoint_by_rank, transform_checkpoints)
+from .train.serialization import async_ckpt_thread_status, load_segmented_checkpoints
 
 mstype = dtype
 __version__ = "0.1.0"
