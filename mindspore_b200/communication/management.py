@@ -118,11 +118,18 @@ def init(backend_name=None):
     GlobalComm.BACKEND = backend_name
     GlobalComm.WORLD_COMM_GROUP = world_name
     GlobalComm.INITED = True
+    if sim is None:
+        from . import cluster
+        cluster.worker_from_env()      # registers with the scheduler and starts heartbeats when launched by msrun
     os.environ["RANK_ID"] = str(_state.rank)
     os.environ["RANK_SIZE"] = str(_state.world)
 
 
 def release():
+    from . import cluster
+    if cluster._worker is not None:
+        cluster._worker.unregister()
+        cluster._worker = None
     if GlobalComm.INITED and not _state.simulation and dist.is_initialized():
         dist.destroy_process_group()
     _state.groups.clear()
