@@ -96,7 +96,10 @@ class DistributedGradReducer(Cell):
             self.degree = degree
         self.params = list(parameters)
         from ..parallel.comm_fusion import plan_allreduce_buckets
-        self.buckets = plan_allreduce_buckets(self.params)
+        # parameters that differ on every rank by design (the experts of an expert-parallel MoE) are not reduced
+        self.local_only = {i for i, p in enumerate(self.params) if getattr(p, "dp_local", False)}
+        self.buckets = [[i for i in b if i not in self.local_only] for b in plan_allreduce_buckets(self.params)]
+        self.buckets = [b for b in self.buckets if b]
 
     def construct(self, grads):
         from ..communication import comm_func as CF
@@ -118,6 +121,9 @@ class DistributedGradReducer(Cell):
                 n = t.numel()
                 out[i] = _wrap_out(flat[off:off + n].view(t.shape).to(t.dtype))
                 off += n
+        if self.mean:
+            for i in self.local_only:      # their gradient already sums the contributions of every rank's tokens
+                out[i] = _wrap_out(grads[i] / self.degree)
         return tuple(out)
 
 

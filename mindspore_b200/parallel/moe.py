@@ -1,0 +1,423 @@
+"""Mixture of experts with expert parallelism.
+
+Routing follows the reference's ``TopkRouter`` exactly (python/mindspore/parallel/_transformer/moe.py:604-693:
+softmax, k rounds of arg-max with the kept choices masked, capacity ``ceil(k * tokens * factor / experts)``,
+position by token order, load-balance loss per round, weights normalised over the rounds), but tokens are moved as
+rows, not multiplied by one-hot dispatch / combine tensors:
+
+* the router is one kernel per round (``csrc/cuda/moe.cu``) plus a backward kernel;
+* dispatch stores each kept row straight into the owner rank's expert input buffer and combine pulls the expert
+  outputs back and applies the weights - over NVLink peer memory when the expert-parallel group has a symmetric-
+  memory context, which replaces the AlltoAll pair of the reference; the NCCL ``all_to_all`` form is the selectable
+  baseline (and the gloo path on CPU);
+* the expert FFN is a batched tcgen05 GEMM over ``[local experts, sources * capacity, hidden]``.
+
+``MoE``, ``MoEConfig`` and ``calculate_expert_capacity`` keep the reference's names and arguments
+(moe.py:42, :137, :143)."""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from .. import _native
+from ..common.initializer import initializer
+from ..common.parameter import Parameter
+from ..nn.cell import Cell
+from ..ops import fused
+from ..ops.kernels import _count, _p, _stream
+
+_P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_U64P = ctypes.POINTER(ctypes.c_ulonglong)
+_native.register_cuda_signature("msb_moe_router_step", _I, [_P] * 10 + [_I] * 5 + [_P])
+_native.register_cuda_signature("msb_moe_router_weights", _I, [_P, _P, _I, _I, _P])
+_native.register_cuda_signature("msb_moe_router_bwd", _I, [_P] * 8 + [_I, _I, _I, _P])
+_native.register_cuda_signature("msb_moe_scatter_rows", _I, [_P, _P, _P, _P, _U64P] + [_I] * 7 + [_P])
+_native.register_cuda_signature("msb_moe_gather_rows", _I, [_U64P, _P, _P, _P, _P, _P, _P] + [_I] * 7 + [_P])
+
+
+class MoEConfig:
+    def __init__(self, expert_num=1, capacity_factor=1.1, aux_loss_factor=0.05, num_experts_chosen=1,
+                 expert_group_size=None, group_wise_a2a=False, comp_comm_parallel=False, comp_comm_parallel_degree=2):
+        for name, v in (("expert_num", expert_num), ("num_experts_chosen", num_experts_chosen),
+                        ("comp_comm_parallel_degree", comp_comm_parallel_degree)):
+            if not isinstance(v, int) or isinstance(v, bool) or v <= 0:
+                raise TypeError("'%s' must be a positive int, but got %r" % (name, v))
+        if capacity_factor < 1.0:
+            raise ValueError("'capacity_factor' must be equal to or greater than 1.0, but got %s." % capacity_factor)
+        if aux_loss_factor >= 1.0:
+            raise ValueError("'aux_loss_factor' must be less than 1.0, but got %s." % aux_loss_factor)
+        if num_experts_chosen > expert_num:
+            raise ValueError("'num_experts_chosen' must not be larger than 'expert_num', but got %d."
+                             % num_experts_chosen)
+        self.expert_num, self.capacity_factor, self.aux_loss_factor = expert_num, capacity_factor, aux_loss_factor
+        self.num_experts_chosen, self.expert_group_size = num_experts_chosen, expert_group_size
+        self.group_wise_a2a, self.comp_comm_parallel = group_wise_a2a, comp_comm_parallel
+        self.comp_comm_parallel_degree = comp_comm_parallel_degree
+
+
+default_moe_config = MoEConfig()
+
+
+def calculate_expert_capacity(k, tokens_per_group, capacity_factor, expert_dim):
+    res = k * tokens_per_group * capacity_factor / expert_dim
+    res_int = int(res)
+    return res_int if res < 0 or res == res_int else res_int + 1
+
+
+# ------------------------------------------------------------------------------------------------ router
+def router_reference(logits, k, capacity):
+    """The routing arithmetic in plain torch (differentiable): returns expert [T,k] int32, slot [T,k] int32
+    (-1 = dropped), weight [T,k] fp32, load-balance loss (scalar)."""
+    T, E = logits.shape
+    prob = torch.softmax(logits.float(), dim=-1)
+    accum_mask = torch.zeros_like(prob)
+    fill = torch.zeros(E, dtype=torch.long, device=logits.device)
+    loss = prob.new_zeros(())
+    experts, slots, gates = [], [], []
+    for _ in range(k):
+        prob = prob * (1 - accum_mask)
+        gate, idx = prob.max(dim=-1)
+        mask = torch.nn.functional.one_hot(idx, E).to(prob.dtype)
+        prob_normal = prob / (prob.sum(-1, keepdim=True) + 1e-9)
+        loss = loss + (mask.mean(0) * prob_normal.mean(0)).mean() * E * E
+        position = (torch.cumsum(mask, 0) - mask).long() + fill       # exclusive count in token order
+        pos = position.gather(1, idx[:, None])[:, 0]
+        keep = pos < capacity
+        kept_mask = mask * keep[:, None].to(mask.dtype)
+        accum_mask = accum_mask + kept_mask
+        fill = fill + kept_mask.sum(0).long()
+        experts.append(idx)
+        slots.append(torch.where(keep, pos, torch.full_like(pos, -1)))
+        gates.append(gate * keep.to(gate.dtype))
+    gate = torch.stack(gates, 1)
+    weight = gate / (gate.sum(-1, keepdim=True) + 1e-9) if k > 1 else gate
+    return torch.stack(experts, 1).int(), torch.stack(slots, 1).int(), weight, loss
+
+
+class _RouterFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, k, capacity):
+        T, E = logits.shape
+        dev = logits.device
+        logits = logits.float().contiguous()
+        expert = torch.empty((T, k), dtype=torch.int32, device=dev)
+        slot = torch.empty((T, k), dtype=torch.int32, device=dev)
+        gate = torch.empty((T, k), dtype=torch.float32, device=dev)
+        weight = torch.empty((T, k), dtype=torch.float32, device=dev)
+        fill = torch.zeros(E, dtype=torch.int32, device=dev)
+        proxy = torch.zeros(E, dtype=torch.float32, device=dev)
+        density = torch.empty((k, E), dtype=torch.float32, device=dev)
+        loss = torch.zeros((), dtype=torch.float32, device=dev)
+        blocks = (T + 255) // 256
+        scan = torch.empty(blocks * E, dtype=torch.int64, device=dev)
+        ticket = torch.empty(1, dtype=torch.int32, device=dev)
+        lib = _native.cuda()
+        for step in range(k):
+            rc = lib.msb_moe_router_step(_p(logits), _p(expert), _p(slot), _p(gate), _p(fill), _p(proxy), _p(density),
+                                         _p(loss), _p(scan), _p(ticket), T, E, k, step, capacity, _stream())
+            _native.check(rc, "moe_router_step")
+            _count(2)
+        _native.check(lib.msb_moe_router_weights(_p(gate), _p(weight), T, k, _stream()), "moe_router_weights")
+        _count()
+        ctx.save_for_backward(logits, expert, slot, gate, density)
+        ctx.mark_non_differentiable(expert, slot)
+        return expert, slot, weight, loss
+
+    @staticmethod
+    def backward(ctx, _de, _ds, dweight, dloss):
+        logits, expert, slot, gate, density = ctx.saved_tensors
+        T, E = logits.shape
+        k = expert.shape[1]
+        dlogits = torch.empty_like(logits)
+        dweight = dweight.float().contiguous() if dweight is not None else torch.zeros_like(gate)
+        dloss = dloss.float().contiguous() if dloss is not None else None
+        rc = _native.cuda().msb_moe_router_bwd(_p(logits), _p(expert), _p(slot), _p(gate), _p(dweight), _p(dloss),
+                                               _p(density), _p(dlogits), T, E, k, _stream())
+        _native.check(rc, "moe_router_bwd")
+        _count()
+        return dlogits, None, None
+
+
+def route(logits, k, capacity):
+    """expert, slot, weight, loss for router logits [T, E] (kernel on CUDA, torch elsewhere)."""
+    if logits.is_cuda and _native.cuda() is not None and logits.shape[1] <= 256 and k <= 4:
+        return _RouterFn.apply(logits, k, capacity)
+    return router_reference(logits, k, capacity)
+
+
+# ------------------------------------------------------------------------------------------------ token movement
+def _ptr_array(ptrs):
+    arr = (ctypes.c_ulonglong * 8)()
+    for i, p in enumerate(ptrs):
+        arr[i] = int(p)
+    return arr
+
+
+class _TorchTransport:
+    """Rows moved with torch indexing; across ranks with ``all_to_all_single`` (NCCL or gloo).  The un-fused
+    baseline of the kernel transport and the CPU path."""
+
+    def __init__(self, experts, capacity, group=None):
+        self.group = group                                   # communication.management._Group or None
+        self.ep = group.size if group is not None else 1
+        self.me = group.ranks.index(torch.distributed.get_rank()) if group is not None else 0
+        self.E, self.EL, self.C = experts, experts // self.ep, capacity
+
+    def _flat_index(self, expert, slot):
+        """Row index into the send layout [ep_dst, EL, C] (kept choices only) + mask."""
+        keep = slot >= 0
+        idx = (expert.long() * self.C + slot.long().clamp(min=0))      # expert = dst_rank * EL + e_local
+        return idx, keep
+
+    def _exchange(self, buf):
+        """[ep_dst, EL, C, H] on every rank -> [EL, ep_src, C, H]."""
+        if self.ep == 1:
+            return buf.permute(1, 0, 2, 3).contiguous()
+        out = torch.empty_like(buf)
+        torch.distributed.all_to_all_single(out, buf.contiguous(), group=self.group.pg)
+        return out.permute(1, 0, 2, 3).contiguous()
+
+    def _exchange_back(self, buf):
+        """[EL, ep_src, C, H] -> [ep_owner, EL, C, H] back on the source ranks."""
+        send = buf.permute(1, 0, 2, 3).contiguous()
+        if self.ep == 1:
+            return send
+        out = torch.empty_like(send)
+        torch.distributed.all_to_all_single(out, send, group=self.group.pg)
+        return out
+
+    def scatter(self, src, scale, expert, slot):
+        T, H = src.shape
+        idx, keep = self._flat_index(expert, slot)
+        rows = src[:, None, :].expand(T, expert.shape[1], H)
+        if scale is not None:
+            rows = rows * scale[:, :, None].to(src.dtype)
+        send = src.new_zeros((self.ep * self.EL * self.C, H))
+        send.index_put_((idx[keep],), rows[keep].to(src.dtype))
+        return self._exchange(send.view(self.ep, self.EL, self.C, H))
+
+    def gather(self, buf, scale, expert, slot, g=None, want_out=True):
+        H = buf.shape[-1]
+        back = self._exchange_back(buf).reshape(-1, H)
+        idx, keep = self._flat_index(expert, slot)
+        rows = back[idx] * keep[:, :, None].to(back.dtype)                # [T, K, H]
+        out = None
+        if want_out:
+            w = scale if scale is not None else keep.to(torch.float32)
+            out = (rows.float() * w[:, :, None]).sum(1).to(buf.dtype)
+        dots = (rows.float() * g[:, None, :].float()).sum(-1) if g is not None else None
+        return out, dots
+
+
+class _KernelTransport:
+    """Rows moved by the scatter / gather kernels: peer stores into, and peer loads from, the owners' buffers in
+    symmetric memory (or plain device memory when the group is a single rank)."""
+
+    def __init__(self, experts, capacity, group=None, symm=None):
+        self.symm = symm                                     # fused_comm.SymmContext or None (single rank)
+        self.ep = symm.world if symm is not None else 1
+        self.me = symm.rank if symm is not None else 0
+        self.E, self.EL, self.C = experts, experts // self.ep, capacity
+
+    def _buffer(self, tag, H, dtype, device):
+        n = self.EL * self.ep * self.C * H
+        if self.symm is None:
+            buf = torch.empty(n, dtype=dtype, device=device)
+            return buf, [buf.data_ptr()]
+        raw, ptrs = self.symm.buffer(self.symm._next("moe_" + tag), n * 2)
+        return raw[:n * 2].view(dtype), ptrs
+
+    def _barrier(self):
+        if self.symm is not None:
+            self.symm.barrier(1)
+
+    def scatter(self, src, scale, expert, slot):
+        T, H = src.shape
+        buf, ptrs = self._buffer("in", H, src.dtype, src.device)
+        buf.zero_()
+        self._barrier()                                      # every owner's buffer is clear
+        rc = _native.cuda().msb_moe_scatter_rows(_p(src), _p(scale), _p(expert), _p(slot), _ptr_array(ptrs), T,
+                                                 expert.shape[1], H, self.EL, self.ep, self.me, self.C, _stream())
+        _native.check(rc, "moe_scatter_rows")
+        _count()
+        self._barrier()                                      # every source has stored its rows
+        return buf.view(self.EL, self.ep, self.C, H)
+
+    def gather(self, buf, scale, expert, slot, g=None, want_out=True):
+        T, K = expert.shape
+        H = buf.shape[-1]
+        if self.symm is not None:
+            stage, ptrs = self._buffer("out", H, buf.dtype, buf.device)
+            stage.view(buf.shape).copy_(buf)
+            self._barrier()                                  # every owner has published its rows
+        else:
+            buf = buf.contiguous()
+            ptrs = [buf.data_ptr()]
+        out = torch.empty((T, H), dtype=buf.dtype, device=buf.device) if want_out else None
+        dots = torch.empty((T, K), dtype=torch.float32, device=buf.device) if g is not None else None
+        rc = _native.cuda().msb_moe_gather_rows(_ptr_array(ptrs), _p(scale), _p(expert), _p(slot), _p(g), _p(out),
+                                                _p(dots), T, K, H, self.EL, self.ep, self.me, self.C, _stream())
+        _native.check(rc, "moe_gather_rows")
+        _count()
+        return out, dots
+
+
+class _DispatchFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, expert, slot, transport):
+        ctx.transport = transport
+        ctx.save_for_backward(expert, slot)
+        return transport.scatter(x.contiguous(), None, expert, slot)
+
+    @staticmethod
+    def backward(ctx, dbuf):
+        expert, slot = ctx.saved_tensors
+        dx, _ = ctx.transport.gather(dbuf.contiguous(), None, expert, slot)
+        return dx, None, None, None
+
+
+class _CombineFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ybuf, weight, expert, slot, transport):
+        ctx.transport = transport
+        ctx.save_for_backward(ybuf, weight, expert, slot)
+        out, _ = transport.gather(ybuf.contiguous(), weight.float().contiguous(), expert, slot)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        ybuf, weight, expert, slot = ctx.saved_tensors
+        dout = dout.contiguous()
+        _, dweight = ctx.transport.gather(ybuf.contiguous(), None, expert, slot, g=dout, want_out=False)
+        dybuf = ctx.transport.scatter(dout, weight.float().contiguous(), expert, slot)
+        return dybuf, dweight.to(weight.dtype), None, None, None
+
+
+# ------------------------------------------------------------------------------------------------ the layer
+def _pick_transport(experts, capacity, group, device, fused=True):
+    """Kernel transport on CUDA (over symmetric memory when the group has several ranks), torch otherwise."""
+    if device.type == "cuda" and _native.cuda() is not None and fused:
+        if group is None or group.size == 1:
+            return _KernelTransport(experts, capacity)
+        from . import fused_comm
+        symm = fused_comm.get_context(group)
+        if symm is not None:
+            return _KernelTransport(experts, capacity, group, symm)
+    return _TorchTransport(experts, capacity, group if group is not None and group.size > 1 else None)
+
+
+class MoE(Cell):
+    """Mixture-of-experts feed-forward layer.
+
+    Args follow the reference (``hidden_size, ffn_hidden_size, dropout_rate, hidden_act, param_init_type,
+    moe_config, parallel_config``); ``expert_parallel_group`` names the communication group whose ranks share the
+    experts (each holds ``expert_num / group size`` of them and routes its own tokens).  ``construct(x)`` takes
+    ``[batch, seq, hidden]`` or ``[tokens, hidden]`` and returns ``(output, aux_loss)`` with
+    ``aux_loss = aux_loss_factor * load-balance loss``."""
+
+    def __init__(self, hidden_size, ffn_hidden_size, dropout_rate=0.0, hidden_act="gelu",
+                 param_init_type=torch.float32, moe_config=default_moe_config, parallel_config=None,
+                 expert_parallel_group=None, has_bias=True, fused_transport=True):
+        super().__init__()
+        from ..communication import management as M
+        self.hidden_size, self.ffn_hidden_size = hidden_size, ffn_hidden_size
+        self.cfg = moe_config
+        self.E, self.k = moe_config.expert_num, moe_config.num_experts_chosen
+        self.act = hidden_act
+        self.fused_transport = fused_transport
+        self.group = M._group(expert_parallel_group) if expert_parallel_group is not None and M.GlobalComm.INITED \
+            else None
+        ep = self.group.size if self.group is not None else 1
+        if self.E % ep:
+            raise ValueError("When using MoE, 'expert_num' (%d) must be a multiple of the expert-parallel group "
+                             "size (%d)." % (self.E, ep))
+        self.ep, self.EL = ep, self.E // ep
+        self.ep_rank = self.group.ranks.index(M.get_rank()) if self.group is not None else 0
+        up = ffn_hidden_size * (2 if hidden_act == "swiglu" else 1)
+        mk = lambda shape, name, init="normal": Parameter(initializer(init, shape, param_init_type), name=name)
+        self.router_weight = Parameter(initializer("normal", (self.E, hidden_size), torch.float32),
+                                       name="router.dense.weight")
+        self.w1 = mk((self.EL, hidden_size, up), "ffn.mapping.weight")
+        self.w2 = mk((self.EL, ffn_hidden_size, hidden_size), "ffn.projection.weight")
+        self.b1 = mk((self.EL, 1, up), "ffn.mapping.bias", "zeros") if has_bias else None
+        self.b2 = mk((self.EL, 1, hidden_size), "ffn.projection.bias", "zeros") if has_bias else None
+        for p in (self.w1, self.w2, self.b1, self.b2):
+            if p is not None:
+                p.dp_local = ep > 1            # every rank owns different experts: never all-reduced over the group
+                p.expert_shard = (ep, self.ep_rank)
+        self.dropout_rate = dropout_rate
+        self._transports = {}
+
+    def _transport(self, capacity, device):
+        key = (capacity, device)
+        if key not in self._transports:
+            self._transports[key] = _pick_transport(self.E, capacity, self.group, device, self.fused_transport)
+        return self._transports[key]
+
+    def _activation(self, h):
+        if self.act == "swiglu":
+            return fused.swiglu(h.reshape(-1, h.shape[-1])).reshape(*h.shape[:-1], h.shape[-1] // 2)
+        if self.act == "gelu":
+            return torch.nn.functional.gelu(h, approximate="tanh")
+        if self.act == "relu":
+            return torch.relu(h)
+        if self.act in ("silu", "swish"):
+            return torch.nn.functional.silu(h)
+        raise ValueError("unsupported hidden_act %r" % (self.act,))
+
+    def construct(self, x):
+        shape = x.shape
+        tokens = x.reshape(-1, shape[-1]).as_subclass(torch.Tensor)
+        T = tokens.shape[0]
+        logits = torch.nn.functional.linear(tokens.float(), self.router_weight.as_subclass(torch.Tensor))
+        capacity = calculate_expert_capacity(self.k, T, self.cfg.capacity_factor, self.E)
+        if tokens.is_cuda:
+            capacity = (capacity + 7) // 8 * 8         # rows per expert stay a multiple of the GEMM granule
+        expert, slot, weight, aux = route(logits, self.k, capacity)
+        tr = self._transport(capacity, tokens.device)
+        buf = _DispatchFn.apply(tokens, expert, slot, tr)                     # [EL, ep, C, H]
+        h = buf.reshape(self.EL, self.ep * capacity, shape[-1])
+        h = fused.matmul(h, self.w1.as_subclass(torch.Tensor))
+        if self.b1 is not None:
+            h = h + self.b1.as_subclass(torch.Tensor)
+        h = self._activation(h)
+        if self.dropout_rate > 0 and self.training:
+            h = torch.nn.functional.dropout(h, self.dropout_rate)
+        y = fused.matmul(h, self.w2.as_subclass(torch.Tensor))
+        if self.b2 is not None:
+            y = y + self.b2.as_subclass(torch.Tensor)
+        y = y.reshape(self.EL, self.ep, capacity, shape[-1])
+        out = _CombineFn.apply(y, weight, expert, slot, tr)
+        from ..common.tensor import as_tensor
+        return as_tensor(out.reshape(shape)), as_tensor(aux * self.cfg.aux_loss_factor)
+
+
+def moe_reference_forward(x, router_weight, w1, w2, b1, b2, k, capacity_factor, act="gelu"):
+    """Dense GShard formulation on one device with all experts (one-hot dispatch and combine tensors, as the
+    reference builds them): the oracle for tests."""
+    T, H = x.shape
+    E = router_weight.shape[0]
+    capacity = calculate_expert_capacity(k, T, capacity_factor, E)
+    logits = x.float() @ router_weight.float().t()
+    expert, slot, weight, aux = router_reference(logits, k, capacity)
+    combine = x.new_zeros((T, E, capacity), dtype=torch.float32)
+    for j in range(k):
+        keep = slot[:, j] >= 0
+        ti = torch.nonzero(keep)[:, 0]
+        combine[ti, expert[ti, j].long(), slot[ti, j].long()] = weight[ti, j]
+    dispatch = (combine != 0).float()
+    xin = torch.einsum("tec,th->ech", dispatch, x.float())
+    h = torch.einsum("ech,ehf->ecf", xin, w1.float())
+    if b1 is not None:
+        h = h + b1.float()
+    if act == "swiglu":
+        f = h.shape[-1] // 2
+        h = torch.nn.functional.silu(h[..., :f]) * h[..., f:]
+    else:
+        h = torch.nn.functional.gelu(h, approximate="tanh")
+    y = torch.einsum("ecf,efh->ech", h, w2.float())
+    if b2 is not None:
+        y = y + b2.float()
+    return torch.einsum("tec,ech->th", combine, y), aux
