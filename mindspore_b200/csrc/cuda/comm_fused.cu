@@ -175,6 +175,64 @@ __global__ void reduce_scatter_adamw_kernel(PeerPtrs grads, PeerPtrs weights, fl
   }
 }
 
+// First half of the sharded optimizer step with gradient clipping: rank r replaces elements [base, base+n) of its
+// own gradient buffer by scale * (sum over all ranks' buffers of the same elements).  Peers only ever read the
+// slices they own, so the in-place write does not race with their loads.
+__global__ void reduce_scatter_symm_kernel(PeerPtrs grads, int rank, int world, long long base, long long n,
+                                           float scale) {
+  for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4; i < n;
+       i += (long long)gridDim.x * blockDim.x * 4) {
+    float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r) {
+      if (r < world) {
+        const float4 t = *reinterpret_cast<const float4*>(static_cast<const float*>(grads.p[r]) + base + i);
+        g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+      }
+    }
+    g.x *= scale; g.y *= scale; g.z *= scale; g.w *= scale;
+    *reinterpret_cast<float4*>(static_cast<float*>(grads.p[rank]) + base + i) = g;
+  }
+}
+
+// Second half: AdamW on n owned elements (master / m / v / grad are local, already offset) and the new bf16 weights
+// written into every rank's weight buffer at element offset `base` (the parameter AllGather).
+__global__ void adamw_allgather_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+                                       const float* __restrict__ grad, PeerPtrs weights, int world, long long base,
+                                       long long n, const float* __restrict__ hyper, const int* __restrict__ skip) {
+  if (skip && *skip) return;
+  const float lr = hyper[0], b1 = hyper[1], b2 = hyper[2], eps = hyper[3], wd = hyper[4];
+  const float bc1 = hyper[5], bc2 = hyper[6], gs = hyper[7];
+  const float step = lr / bc1, rsq = rsqrtf(bc2);
+  for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4; i < n;
+       i += (long long)gridDim.x * blockDim.x * 4) {
+    float4 g4 = *reinterpret_cast<const float4*>(grad + i);
+    float4 p4 = *reinterpret_cast<float4*>(master + i);
+    float4 m4 = *reinterpret_cast<float4*>(m + i);
+    float4 v4 = *reinterpret_cast<float4*>(v + i);
+    float* gg = reinterpret_cast<float*>(&g4);
+    float* pp = reinterpret_cast<float*>(&p4);
+    float* mm = reinterpret_cast<float*>(&m4);
+    float* vv = reinterpret_cast<float*>(&v4);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float gj = gg[j] * gs;
+      mm[j] = b1 * mm[j] + (1.f - b1) * gj;
+      vv[j] = b2 * vv[j] + (1.f - b2) * gj * gj;
+      pp[j] = pp[j] * (1.f - lr * wd) - step * mm[j] / (sqrtf(vv[j]) * rsq + eps);
+    }
+    *reinterpret_cast<float4*>(master + i) = p4;
+    *reinterpret_cast<float4*>(m + i) = m4;
+    *reinterpret_cast<float4*>(v + i) = v4;
+    uint2 o;
+    o.x = pack_bf16x2(pp[0], pp[1]);
+    o.y = pack_bf16x2(pp[2], pp[3]);
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < world) *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(weights.p[r]) + base + i) = o;
+  }
+}
+
 static int fill_peers(PeerPtrs* out, const unsigned long long* ptrs, int world, const char* what) {
   if (world < 1 || world > kMaxRanks) {
     set_last_error("%s: group size %d is outside [1, %d]", what, world, kMaxRanks);
@@ -241,6 +299,44 @@ MSB_EXPORT int msb_reduce_scatter_adamw(const unsigned long long* grad_ptrs, con
   blocks = blocks > cap ? cap : blocks;
   reduce_scatter_adamw_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       g, w, master, m, v, rank, world, per, hyper, skip);
+  MSB_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+static unsigned ew_blocks(long long n4) {
+  long long blocks = (n4 + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count()) * 4;
+  blocks = blocks < 1 ? 1 : (blocks > cap ? cap : blocks);
+  return static_cast<unsigned>(blocks);
+}
+
+MSB_EXPORT int msb_reduce_scatter_symm(const unsigned long long* grad_ptrs, int rank, int world, long long base,
+                                       long long n, float scale, void* stream) {
+  PeerPtrs g;
+  if (int rc = fill_peers(&g, grad_ptrs, world, "reduce_scatter_symm")) return rc;
+  if ((n % 4) || (base % 4)) {
+    set_last_error("reduce_scatter_symm: base %lld and length %lld must be multiples of 4", base, n);
+    return kBadArg;
+  }
+  if (n <= 0) return kOk;
+  reduce_scatter_symm_kernel<<<ew_blocks(n / 4), 256, 0, static_cast<cudaStream_t>(stream)>>>(g, rank, world, base, n,
+                                                                                              scale);
+  MSB_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+MSB_EXPORT int msb_adamw_allgather(float* master, float* m, float* v, const float* grad,
+                                   const unsigned long long* weight_ptrs, int world, long long base, long long n,
+                                   const float* hyper, const int* skip, void* stream) {
+  PeerPtrs w;
+  if (int rc = fill_peers(&w, weight_ptrs, world, "adamw_allgather")) return rc;
+  if ((n % 4) || (base % 4)) {
+    set_last_error("adamw_allgather: base %lld and length %lld must be multiples of 4", base, n);
+    return kBadArg;
+  }
+  if (n <= 0) return kOk;
+  adamw_allgather_kernel<<<ew_blocks(n / 4), 256, 0, static_cast<cudaStream_t>(stream)>>>(master, m, v, grad, w, world,
+                                                                                          base, n, hyper, skip);
   MSB_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }

@@ -81,6 +81,15 @@ class ParamArena:
     def zero_grad(self):
         self.grads.zero_()
 
+    def rebind(self, weights, grads):
+        """Moves the arena into other buffers (at least ``total`` elements; e.g. symmetric memory): parameters and
+        their ``main_grad`` become views of the new buffers.  ``weights`` must already hold the values."""
+        self.weights, self.grads = weights, grads
+        for p, o in zip(self.params, self.offsets):
+            n = p.numel()
+            p.data = weights[o:o + n].view(p.shape)
+            p.main_grad = grads[o:o + n].view(p.shape)
+
     def segment(self, first, last):
         """[start, end) element range covering params[first:last]."""
         start = self.offsets[first]
@@ -300,6 +309,19 @@ class Optimizer(Cell):
         self._reduce_runs = [seg for seg, f in runs("tp_grad_reduce") if f]
         self._sumsq_sh = torch.zeros_like(self._sumsq)
 
+    def set_data_parallel_group(self, group_name, mean=True, shard=False, fused=True):
+        """Gradients of the arena are averaged over ``group_name`` before the update.  With ``shard`` the fp32
+        master weights and the moments are split over the group (parallel optimizer): every rank updates one slice
+        and the new weights are gathered back (``parallel.zero``)."""
+        assert self.arena is not None, "set_data_parallel_group needs the arena form"
+        from ..parallel.zero import DataParallelArena
+        self._dp = DataParallelArena(self, group_name, mean, shard, fused)
+
+    def sync_data_parallel_grads(self):
+        dp = getattr(self, "_dp", None)
+        if dp is not None and not dp.shard:
+            dp.allreduce()
+
     def sync_model_parallel_grads(self):
         group = getattr(self, "_mp_group", None)
         if group is None:
@@ -477,6 +499,9 @@ class AdamWeightDecay(Optimizer):
 
     def fused_step(self, inv_loss_scale=1.0, check_finite=False):
         """One kernel per decay group over the flat arena; clip and overflow-skip decided on the device."""
+        dp = getattr(self, "_dp", None)
+        if dp is not None and dp.shard:
+            return dp.sharded_step(inv_loss_scale, check_finite)
         arena = self.arena
         t = self._step_host + 1
         lr = self._lr_value(self.learning_rate, self._step_host)

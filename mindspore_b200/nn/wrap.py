@@ -223,6 +223,7 @@ class TrainOneStepCell(Cell):
                 loss.backward()
         _collect_stray_grads(self.weights)
         opt.sync_model_parallel_grads()
+        opt.sync_data_parallel_grads()
         if self.grad_reducer is not None:
             from ..parallel.data_parallel import allreduce_arena_grads
             allreduce_arena_grads(opt.arena, self.grad_reducer)

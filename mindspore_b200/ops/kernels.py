@@ -243,7 +243,22 @@ def ce_loss_grad(logits, labels, stats, grad_scale, vocab_start=0, ignore_index=
 
 
 # --------------------------------------------------------------------------------------- optimizers
+def _adamw_host(master, m, v, grad, param_lp, hyper, skip):
+    """Same arithmetic in torch, for arenas that live in host memory."""
+    if skip is not None and int(skip) != 0:
+        return
+    lr, b1, b2, eps, wd, bc1, bc2, gs = (float(x) for x in hyper[:8])
+    g = grad.float() * gs
+    m.mul_(b1).add_(g, alpha=1 - b1)
+    v.mul_(b2).addcmul_(g, g, value=1 - b2)
+    master.mul_(1 - lr * wd).sub_((lr / bc1) * m / (v.sqrt() / (bc2 ** 0.5) + eps))
+    if param_lp is not None:
+        param_lp.copy_(master)
+
+
 def adamw_step(master, m, v, grad, param_lp, hyper, skip=None):
+    if not master.is_cuda:
+        return _adamw_host(master, m, v, grad, param_lp, hyper, skip)
     rc = _native.cuda().msb_adamw(_p(master), _p(m), _p(v), _p(grad), int(grad.dtype == f32), _p(param_lp),
                                   master.numel(), _p(hyper), _p(skip), _stream())
     _native.check(rc, "adamw")
@@ -258,12 +273,27 @@ def momentum_step(master, accum, grad, param_lp, hyper, skip=None):
 
 
 def sumsq_finite(x, out, nonfinite):
+    if not x.is_cuda:
+        xf = x.float()
+        out += (xf * xf).sum()
+        if not bool(torch.isfinite(xf).all()):
+            nonfinite.fill_(1)
+        return
     rc = _native.cuda().msb_sumsq_finite(_p(x), int(x.dtype == f32), x.numel(), _p(out), _p(nonfinite), _stream())
     _native.check(rc, "sumsq_finite")
     _count()
 
 
 def finalize_grad_scale(sumsq, nonfinite, inv_loss_scale, max_norm, hyper_scale, skip, norm_out=None):
+    if not sumsq.is_cuda:
+        norm = float(sumsq.reshape(-1)[0]) ** 0.5 * inv_loss_scale
+        s = inv_loss_scale * (min(1.0, max_norm / (norm + 1e-6)) if max_norm > 0 else 1.0)
+        hyper_scale.fill_(s)
+        if skip is not None:
+            skip.copy_(nonfinite.reshape(skip.shape))
+        if norm_out is not None:
+            norm_out.fill_(norm)
+        return
     rc = _native.cuda().msb_finalize_grad_scale(_p(sumsq), _p(nonfinite), float(inv_loss_scale), float(max_norm),
                                                 _p(hyper_scale), _p(skip), _p(norm_out), _stream())
     _native.check(rc, "finalize_grad_scale")
