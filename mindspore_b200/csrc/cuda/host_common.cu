@@ -91,6 +91,34 @@ int encode_tmap_3d(CUtensorMap* out, const void* base, int elem_size, uint64_t d
   return kOk;
 }
 
+int encode_tmap_4d(CUtensorMap* out, const void* base, const uint64_t dims[4], const uint64_t strides_bytes[3],
+                   const uint32_t box[4]) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    set_last_error("cuTensorMapEncodeTiled is not available from the driver");
+    return kCudaError;
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (strides_bytes[0] & 15) || (strides_bytes[1] & 15) ||
+      (strides_bytes[2] & 15)) {
+    set_last_error("4-D tensor map needs a 16-byte aligned base and strides (base=%p)", base);
+    return kBadArg;
+  }
+  cuuint64_t d[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t st[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
+  cuuint32_t b[4] = {box[0], box[1], box[2], box[3]};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), d, st, b, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("cuTensorMapEncodeTiled (4-D) failed with %d (dims %llu,%llu,%llu,%llu box %u,%u,%u,%u)", (int)r,
+                   (unsigned long long)d[0], (unsigned long long)d[1], (unsigned long long)d[2],
+                   (unsigned long long)d[3], b[0], b[1], b[2], b[3]);
+    return kCudaError;
+  }
+  return kOk;
+}
+
 }  // namespace msb
 
 MSB_EXPORT const char* msb_last_error() { return msb::g_last_error; }

@@ -32,6 +32,11 @@ int encode_tmap_3d(CUtensorMap* out, const void* base, int elem_size, uint64_t d
                    uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2,
                    bool swizzle128 = true);
 
+// Rank-4 bf16 tiled tensor map with 128-byte swizzle (NHWC activations: channels, width, height, image).
+//   dims / box innermost first; strides_bytes are the byte strides of dims 1..3; box[0] must be 64 elements.
+int encode_tmap_4d(CUtensorMap* out, const void* base, const uint64_t dims[4], const uint64_t strides_bytes[3],
+                   const uint32_t box[4]);
+
 }  // namespace msb
 
 #define MSB_CUDA_CHECK(expr)                                                              \

@@ -34,8 +34,8 @@ def conv2d(x, w, stride=(1, 1), pad_mode="valid", pad=0, dilation=(1, 1), group=
     top, bottom, left, right = _pads(pad_mode, pad, x.shape[-2:], w.shape[-2:], stride, dilation)
     try:
         from . import conv_kernel
-        if conv_kernel.supports(x, w, group):
-            return conv_kernel.conv2d(x, w, stride, (top, bottom, left, right), dilation, bias)
+        if conv_kernel.supports(x, w, group, dilation):
+            return conv_kernel.conv2d(x, w, tuple(stride), (top, bottom, left, right), dilation, bias)
     except ImportError:
         pass
     if top == bottom and left == right:
@@ -47,6 +47,11 @@ def conv2d(x, w, stride=(1, 1), pad_mode="valid", pad=0, dilation=(1, 1), group=
 def batch_norm(x, scale, bias, mean, variance, training, momentum, eps):
     """Functional BN; in training mode updates ``mean``/``variance`` in place
     (moving = moving*(1-momentum) + batch*momentum, the reference's BatchNorm primitive convention)."""
+    if training and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 4 and x.shape[1] % 8 == 0 \
+            and x.shape[1] <= 2048 and mean.dtype == torch.float32:
+        from . import conv_kernel
+        if conv_kernel.available():
+            return conv_kernel.batch_norm_train(x, scale, bias, mean, variance, 1.0 - momentum, eps)
     if training:
         return F.batch_norm(x, mean, variance, scale, bias, True, momentum, eps)
     return F.batch_norm(x, mean, variance, scale, bias, False, 0.0, eps)

@@ -70,3 +70,63 @@ def test_data_parallel_arena_matches_single_process(shard, clip):
         assert sharded_state == shard
         for name, value in params.items():
             torch.testing.assert_close(value, ref[name], rtol=1e-5, atol=1e-6)
+
+
+def _gpu_worker(rank, world, fused):
+    import mindspore_b200 as ms
+    from mindspore_b200 import _native, nn
+    from mindspore_b200.communication import GlobalComm, init
+    torch.cuda.set_device(rank)
+    ms.set_context(device_target="GPU", device_id=rank)
+    init("nccl")
+
+    def build():
+        torch.manual_seed(4)
+        ms.set_seed(4)
+        net = nn.SequentialCell([nn.Dense(256, 512), nn.Tanh(), nn.Dense(512, 256)]).to_float(torch.bfloat16)
+        for p in net.get_parameters():
+            p.set_data(p.detach().to(torch.bfloat16).cuda())
+        return net
+
+    def run(net, opt, x, y, steps=3):
+        for _ in range(steps):
+            opt.zero_grad()
+            out = net(ms.Tensor(x))
+            loss = ((out.float() - y) ** 2).mean()
+            loss.backward()
+            for p in net.get_parameters():
+                if p.grad is not None:
+                    p.main_grad.add_(p.grad.float())
+                    p.grad = None
+            opt.sync_data_parallel_grads()
+            opt.fused_step()
+        return {p.name: p.detach().float().clone() for p in net.get_parameters()}
+
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(64, 256, generator=g).bfloat16().cuda()
+    y = torch.randn(64, 256, generator=g).cuda()
+    ref_net = build()
+    ref_opt = nn.AdamWeightDecay(ref_net.trainable_params(), learning_rate=1e-3, weight_decay=0.1, max_grad_norm=1.0)
+    ref = run(ref_net, ref_opt, x, y)
+    net = build()
+    opt = nn.AdamWeightDecay(net.trainable_params(), learning_rate=1e-3, weight_decay=0.1, max_grad_norm=1.0)
+    opt.set_data_parallel_group(GlobalComm.WORLD_COMM_GROUP, mean=True, shard=True, fused=fused)
+    n = x.shape[0] // world
+    got = run(net, opt, x[rank * n:(rank + 1) * n], y[rank * n:(rank + 1) * n])
+    worst = max(float((got[k] - ref[k]).abs().max() / (ref[k].abs().max() + 1e-6)) for k in ref)
+    torch.cuda.synchronize()
+    status = _native.device_status()
+    used_symm = opt._dp.symm is not None
+    torch.distributed.barrier()
+    ms.communication.release()
+    return worst, status, used_symm
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fused", [True, False])
+def test_sharded_optimizer_on_2_gpus(fused):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    for worst, status, used_symm in run_ranks(_gpu_worker, 2, fused):
+        assert status == 0 and used_symm == fused
+        assert worst < 2e-2
