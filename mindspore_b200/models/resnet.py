@@ -24,6 +24,11 @@ class ConvBnAct(nn.Cell):
         self.conv = nn.Conv2d(cin, cout, kernel, stride, pad_mode="pad", padding=kernel // 2,
                               weight_init=HeNormal(mode="fan_out", nonlinearity="relu"), dtype=dtype)
         self.bn = nn.BatchNorm2d(cout, eps=1e-5, momentum=0.9, gamma_init="zeros" if zero_gamma else "ones")
+        if dtype != torch.float32:
+            # trainable affine parameters share the weights' dtype (one flat optimizer arena with fp32 masters);
+            # the moving statistics stay fp32
+            for p in (self.bn.gamma, self.bn.beta):
+                p.set_data(p.detach().to(dtype))
 
     def construct(self, x, residual=None):
         w = self.conv.weight

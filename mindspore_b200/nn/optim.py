@@ -356,15 +356,48 @@ def _to_plain(t):
 
 
 class Momentum(Optimizer):
-    def __init__(self, params, learning_rate, momentum, weight_decay=0.0, loss_scale=1.0, use_nesterov=False):
+    def __init__(self, params, learning_rate, momentum, weight_decay=0.0, loss_scale=1.0, use_nesterov=False,
+                 use_arena=None, decay_filter=None):
         super().__init__(learning_rate, params, weight_decay, loss_scale)
         if isinstance(momentum, float) and momentum < 0.0:
             raise ValueError("For 'Momentum', the argument 'momentum' must be at least 0.0, but got %s" % momentum)
         self.momentum = float(momentum)
         self.use_nesterov = use_nesterov
-        self.moments = _clone_state(self._parameters, "moments")
+        p0 = self._parameters[0]
+        same = all(p.device == p0.device and p.dtype == p0.dtype for p in self._parameters)
+        if use_arena is None:
+            use_arena = same and p0.is_cuda and p0.dtype == torch.bfloat16
+        if use_arena:
+            # flat form: bf16 weights, fp32 master + accumulator, one kernel per weight-decay group
+            arena = self._enable_arena(decay_filter or (lambda p: p.dim() > 1))
+            self._accum = torch.zeros(arena.total, dtype=torch.float32, device=arena.weights.device)
+            self.moments = ()
+        else:
+            self.moments = _clone_state(self._parameters, "moments")
 
-    def construct(self, gradients):
+    def fused_step(self, inv_loss_scale=1.0, check_finite=False):
+        arena = self.arena
+        lr = self._lr_value(self.learning_rate, self._step_host)
+        skip = None
+        if check_finite or inv_loss_scale != 1.0:
+            self._accumulate_sumsq()
+            K.finalize_grad_scale(self._sumsq, self._nonfinite, inv_loss_scale, 0.0, self._gscale, self._skip,
+                                  self._gnorm)
+            skip = self._skip if check_finite else None
+        for gi, (first, last, wd) in enumerate(self._arena_groups):
+            s, e = arena.segment(first, last)
+            h = self._hyper[gi]
+            h[:3] = torch.tensor([lr, self.momentum, wd], dtype=torch.float32)
+            h[3:4].copy_(self._gscale)
+            h[4] = 1.0 if self.use_nesterov else 0.0
+            lp = arena.weights[s:e] if arena.master is not arena.weights else None
+            K.momentum_step(arena.master[s:e], self._accum[s:e], arena.grads[s:e], lp, h, skip)
+        self._advance()
+        return True
+
+    def construct(self, gradients=None):
+        if self.use_arena:
+            return self.fused_step()
         gradients = self._prep(gradients)
         lrs = self._lrs()
         with torch.no_grad():
