@@ -161,10 +161,16 @@ class _ConvFn(torch.autograd.Function):
             else:
                 dw = dw.to(w.dtype)
         if ctx.needs_input_grad[0]:
-            if ctx.small or cout % 64:
-                raise NotImplementedError("data gradient of a convolution with fewer than 64 channels on the kernel "
-                                          "path (only a first layer, whose input needs no gradient, is expected)")
+            if ctx.small:
+                raise NotImplementedError("data gradient of a convolution with fewer than 64 input channels on the "
+                                          "kernel path (only a first layer, whose input needs no gradient, is "
+                                          "expected)")
             wt = w.permute(1, 2, 3, 0).contiguous()                      # [Cin, R, S, Cout]
+            if cout % 64:                                                # the box loads take 64 channels at a time
+                extra = 64 - cout % 64
+                wt = torch.nn.functional.pad(wt, (0, extra))
+                dy = _nhwc(torch.nn.functional.pad(dy, (0, 0, 0, 0, 0, extra)))
+                cout += extra
             if stride == 1:
                 dx = conv_fwd_raw(dy, wt, 1, pad_h, pad_w, h, w_, None, flip=True)
             elif r == 1 and s == 1:
