@@ -24,5 +24,7 @@ from .parallel import (build_searched_strategy, load_distributed_checkpoint, mer
                        sync_pipeline_shared_parameters, transform_checkpoint_by_rank, transform_checkpoints)
 from .train.serialization import async_ckpt_thread_status, load_segmented_checkpoints
 
+from .profiler import EnvProfiler, Profiler
+
 mstype = dtype
 __version__ = "0.1.0"
