@@ -152,13 +152,25 @@ bn_apply_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ s
   }
 }
 
-// dx = gamma * rstd * (dy' - sum(dy')/count - xhat * sum(dy' xhat)/count);  dres = dy' (optional).
+// dx = gamma * rstd * (dy' - sum(dy')/count - xhat * sum(dy' xhat)/count) = A[c] * dy' + B[c] * x + D[c];
+// dres = dy' (optional).  coef = [A | B | D], each C floats.
+__global__ void bn_bwd_coeff_kernel(const float* __restrict__ gamma, const float* __restrict__ mean,
+                                    const float* __restrict__ rstd, const float* __restrict__ sums,
+                                    float* __restrict__ coef, int C, float inv_count) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const float g = gamma[c], r = rstd[c], mu = mean[c];
+  const float s1 = sums[c] * inv_count, s2 = sums[C + c] * inv_count;
+  coef[c] = g * r;
+  coef[C + c] = -g * r * r * s2;
+  coef[2 * C + c] = -g * r * s1 + g * r * r * s2 * mu;
+}
+
 __global__ void __launch_bounds__(kEwThreads)
 bn_bwd_apply_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
-                    const __nv_bfloat16* __restrict__ y, const float* __restrict__ gamma,
-                    const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ sums,
+                    const __nv_bfloat16* __restrict__ y, const float* __restrict__ coef,
                     __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ dres, long long total_vecs, int vecs,
-                    int C, float inv_count, int relu) {
+                    int C, int relu) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total_vecs;
        i += (long long)gridDim.x * blockDim.x) {
     const int c0 = (int)(i % vecs) * 8;
@@ -172,21 +184,25 @@ bn_bwd_apply_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* _
       for (int j = 0; j < 8; ++j) g[j] = yv[j] > 0.f ? g[j] : 0.f;
     }
     if (dres) reinterpret_cast<uint4*>(dres)[i] = pack8(g);
+    float ca[8], cb[8], cd[8];
+    *reinterpret_cast<float4*>(ca) = *reinterpret_cast<const float4*>(coef + c0);
+    *reinterpret_cast<float4*>(ca + 4) = *reinterpret_cast<const float4*>(coef + c0 + 4);
+    *reinterpret_cast<float4*>(cb) = *reinterpret_cast<const float4*>(coef + C + c0);
+    *reinterpret_cast<float4*>(cb + 4) = *reinterpret_cast<const float4*>(coef + C + c0 + 4);
+    *reinterpret_cast<float4*>(cd) = *reinterpret_cast<const float4*>(coef + 2 * C + c0);
+    *reinterpret_cast<float4*>(cd + 4) = *reinterpret_cast<const float4*>(coef + 2 * C + c0 + 4);
     float o[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int c = c0 + j;
-      const float xh = (xv[j] - mean[c]) * rstd[c];
-      o[j] = gamma[c] * rstd[c] * (g[j] - sums[c] * inv_count - xh * sums[C + c] * inv_count);
-    }
+    for (int j = 0; j < 8; ++j) o[j] = ca[j] * g[j] + cb[j] * xv[j] + cd[j];
     reinterpret_cast<uint4*>(dx)[i] = pack8(o);
   }
 }
 
-// 3x3 / stride 2 / pad 1 max pooling, NHWC.
+// 3x3 / stride 2 / pad 1 max pooling, NHWC.  The forward pass also records, per output element, which of the nine
+// window positions (r*3 + s, first maximum in scan order) won; the backward pass routes dy by that record.
 __global__ void __launch_bounds__(kEwThreads)
-maxpool3x3s2_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int N, int H, int W,
-                        int C, int Ho, int Wo) {
+maxpool3x3s2_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                        unsigned long long* __restrict__ idx, int N, int H, int W, int C, int Ho, int Wo) {
   const int vecs = C / 8;
   const long long total = (long long)N * Ho * Wo * vecs;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -198,6 +214,7 @@ maxpool3x3s2_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __re
     const int ho = (int)(pix % Ho);
     const int n = (int)(pix / Ho);
     float m[8];
+    unsigned long long win = 0;
 #pragma unroll
     for (int j = 0; j < 8; ++j) m[j] = -INFINITY;
     for (int r = 0; r < 3; ++r) {
@@ -208,18 +225,23 @@ maxpool3x3s2_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __re
         if (w < 0 || w >= W) continue;
         float v[8];
         unpack8(reinterpret_cast<const uint4*>(x + (((long long)n * H + h) * W + w) * C)[cv], v);
+        const unsigned long long pos = (unsigned long long)(r * 3 + s);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) m[j] = fmaxf(m[j], v[j]);
+        for (int j = 0; j < 8; ++j) {
+          if (v[j] > m[j]) {
+            m[j] = v[j];
+            win = (win & ~(0xffull << (8 * j))) | (pos << (8 * j));
+          }
+        }
       }
     }
     reinterpret_cast<uint4*>(y)[i] = pack8(m);
+    if (idx) idx[i] = win;
   }
 }
 
-// dx[n,h,w,c] = sum over the (at most 4) windows containing (h,w) of dy where x[h,w,c] is the first maximum of the
-// window (scan order r, s), recomputed from x.
 __global__ void __launch_bounds__(kEwThreads)
-maxpool3x3s2_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+maxpool3x3s2_bwd_kernel(const unsigned long long* __restrict__ idx, const __nv_bfloat16* __restrict__ dy,
                         __nv_bfloat16* __restrict__ dx, int N, int H, int W, int C, int Ho, int Wo) {
   const int vecs = C / 8;
   const long long total = (long long)N * H * W * vecs;
@@ -231,34 +253,18 @@ maxpool3x3s2_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
     pix /= W;
     const int h = (int)(pix % H);
     const int n = (int)(pix / H);
-    float me[8], acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    unpack8(reinterpret_cast<const uint4*>(x)[i], me);
-    for (int ho = (h + 1 - 2 + 1) / 2; ho <= (h + 1) / 2; ++ho) {        // windows with ho*2-1 <= h <= ho*2+1
-      if (ho < 0 || ho >= Ho) continue;
-      for (int wo = (w + 1 - 2 + 1) / 2; wo <= (w + 1) / 2; ++wo) {
-        if (wo < 0 || wo >= Wo) continue;
-        // position of (h, w) in the window's scan order, and whether an earlier element is >= / a later one is >
-        bool win[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) win[j] = true;
-        const int my_r = h - (ho * 2 - 1), my_s = w - (wo * 2 - 1);
-        for (int r = 0; r < 3; ++r) {
-          const int hh = ho * 2 - 1 + r;
-          if (hh < 0 || hh >= H) continue;
-          for (int s = 0; s < 3; ++s) {
-            const int ww = wo * 2 - 1 + s;
-            if (ww < 0 || ww >= W || (r == my_r && s == my_s)) continue;
-            float v[8];
-            unpack8(reinterpret_cast<const uint4*>(x + (((long long)n * H + hh) * W + ww) * C)[cv], v);
-            const bool earlier = (r < my_r) || (r == my_r && s < my_s);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) win[j] = win[j] && (earlier ? v[j] < me[j] : v[j] <= me[j]);
-          }
-        }
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int ho = h / 2; ho <= (h + 1) / 2; ++ho) {        // windows with ho*2-1 <= h <= ho*2+1
+      if (ho >= Ho) continue;
+      for (int wo = w / 2; wo <= (w + 1) / 2; ++wo) {
+        if (wo >= Wo) continue;
+        const unsigned long long pos = (unsigned long long)((h - (ho * 2 - 1)) * 3 + (w - (wo * 2 - 1)));
+        const long long o = (((long long)n * Ho + ho) * Wo + wo) * vecs + cv;
+        const unsigned long long win = idx[o];
         float g[8];
-        unpack8(reinterpret_cast<const uint4*>(dy + (((long long)n * Ho + ho) * Wo + wo) * C)[cv], g);
+        unpack8(reinterpret_cast<const uint4*>(dy)[o], g);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += win[j] ? g[j] : 0.f;
+        for (int j = 0; j < 8; ++j) acc[j] += (((win >> (8 * j)) & 0xffull) == pos) ? g[j] : 0.f;
       }
     }
     reinterpret_cast<uint4*>(dx)[i] = pack8(acc);
@@ -372,29 +378,35 @@ MSB_EXPORT int msb_bn_bwd_reduce(const void* dy, const void* x, const void* y, c
   return kOk;
 }
 
+// coef: fp32 [3C] scratch owned by the caller (filled here).
 MSB_EXPORT int msb_bn_bwd_apply(const void* dy, const void* x, const void* y, const float* gamma, const float* mean,
-                                const float* rstd, const float* sums, void* dx, void* dres, long long rows, int C,
-                                int relu, void* stream) {
+                                const float* rstd, const float* sums, float* coef, void* dx, void* dres,
+                                long long rows, int C, int relu, void* stream) {
   if (int rc = check_c("bn_bwd_apply", C)) return rc;
   if (rows <= 0) return kOk;
+  bn_bwd_coeff_kernel<<<(C + 127) / 128, 128, 0, (cudaStream_t)stream>>>(gamma, mean, rstd, sums, coef, C,
+                                                                         1.f / (float)rows);
   const long long tv = rows * (C / 8);
   bn_bwd_apply_kernel<<<ew_grid(tv), kEwThreads, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)y, gamma, mean, rstd, sums,
-      (__nv_bfloat16*)dx, (__nv_bfloat16*)dres, tv, C / 8, C, 1.f / (float)rows, relu);
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)y, coef, (__nv_bfloat16*)dx,
+      (__nv_bfloat16*)dres, tv, C / 8, C, relu);
   MSB_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
 
-MSB_EXPORT int msb_maxpool3x3s2(const void* x, const void* dy, void* out, int N, int H, int W, int C, int backward,
-                                void* stream) {
+// Forward: x -> out (and idx: one byte per output element, 8-byte aligned, may be null).
+// Backward: idx + dy -> out = dx.
+MSB_EXPORT int msb_maxpool3x3s2(const void* x, const void* dy, void* out, void* idx, int N, int H, int W, int C,
+                                int backward, void* stream) {
   if (int rc = check_c("maxpool", C)) return rc;
   const int Ho = (H + 2 - 3) / 2 + 1, Wo = (W + 2 - 3) / 2 + 1;
   if (!backward) {
     maxpool3x3s2_fwd_kernel<<<ew_grid((long long)N * Ho * Wo * (C / 8)), kEwThreads, 0, (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)x, (__nv_bfloat16*)out, N, H, W, C, Ho, Wo);
+        (const __nv_bfloat16*)x, (__nv_bfloat16*)out, (unsigned long long*)idx, N, H, W, C, Ho, Wo);
   } else {
+    if (!idx) { set_last_error("maxpool backward needs the index record of the forward pass"); return kBadArg; }
     maxpool3x3s2_bwd_kernel<<<ew_grid((long long)N * H * W * (C / 8)), kEwThreads, 0, (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (__nv_bfloat16*)out, N, H, W, C, Ho, Wo);
+        (const unsigned long long*)idx, (const __nv_bfloat16*)dy, (__nv_bfloat16*)out, N, H, W, C, Ho, Wo);
   }
   MSB_CUDA_CHECK(cudaGetLastError());
   return kOk;

@@ -526,22 +526,32 @@ namespace msb {
 __global__ void im2col_nhwc_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int N, int H,
                                    int W, int Cin, int R, int S, int stride, int pad_h, int pad_w, int Ho, int Wo,
                                    int Kpad) {
-  const long long total = (long long)N * Ho * Wo * Kpad;
-  const int K = R * S * Cin;
+  // One thread per (output pixel, filter row): the S*Cin input values of a filter row are contiguous in NHWC, and
+  // so is their place in the patch row.  Thread R of a pixel zero-fills the padding columns.
+  const long long total = (long long)N * Ho * Wo * (R + 1);
+  const int seg = S * Cin;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
-    const int k = (int)(i % Kpad);
-    long long pix = i / Kpad;
-    __nv_bfloat16 v = __float2bfloat16(0.f);
-    if (k < K) {
-      const int c = k % Cin, tap = k / Cin, s = tap % S, r = tap / S;
-      const int wo = (int)(pix % Wo);
-      const int ho = (int)((pix / Wo) % Ho);
-      const int n = (int)(pix / ((long long)Wo * Ho));
-      const int h = ho * stride + r - pad_h, w = wo * stride + s - pad_w;
-      if (h >= 0 && h < H && w >= 0 && w < W) v = x[(((long long)n * H + h) * W + w) * Cin + c];
+    const int r = (int)(i % (R + 1));
+    const long long pix = i / (R + 1);
+    __nv_bfloat16* dst = out + pix * Kpad + (long long)r * seg;
+    if (r == R) {
+      for (int k = R * seg; k < Kpad; ++k) out[pix * Kpad + k] = __float2bfloat16(0.f);
+      continue;
     }
-    out[i] = v;
+    const int wo = (int)(pix % Wo);
+    const int ho = (int)((pix / Wo) % Ho);
+    const int n = (int)(pix / ((long long)Wo * Ho));
+    const int h = ho * stride + r - pad_h, w0 = wo * stride - pad_w;
+    if (h < 0 || h >= H) {
+      for (int k = 0; k < seg; ++k) dst[k] = __float2bfloat16(0.f);
+      continue;
+    }
+    const __nv_bfloat16* src = x + (((long long)n * H + h) * W + w0) * Cin;
+    for (int s = 0; s < S; ++s) {
+      const bool in = (w0 + s) >= 0 && (w0 + s) < W;
+      for (int c = 0; c < Cin; ++c) dst[s * Cin + c] = in ? src[s * Cin + c] : __float2bfloat16(0.f);
+    }
   }
 }
 }  // namespace msb
@@ -552,7 +562,7 @@ MSB_EXPORT int msb_im2col_nhwc(const void* x, void* out, int N, int H, int W, in
     set_last_error("im2col: padded width %d must be a multiple of 8 and at least %d", Kpad, R * S * Cin);
     return kBadArg;
   }
-  const long long total = (long long)N * Ho * Wo * Kpad;
+  const long long total = (long long)N * Ho * Wo * (R + 1);
   if (total <= 0) return kOk;
   long long blocks = (total + 255) / 256;
   const long long cap = (long long)sm_count() * 16;

@@ -26,8 +26,8 @@ _native.register_cuda_signature("msb_channel_stats", _I, [_P, _P, _L, _I, _P])
 _native.register_cuda_signature("msb_bn_finalize", _I, [_P] * 9 + [_I, _F, _F, _F, _I, _P])
 _native.register_cuda_signature("msb_bn_apply", _I, [_P, _P, _P, _P, _P, _L, _I, _I, _P])
 _native.register_cuda_signature("msb_bn_bwd_reduce", _I, [_P, _P, _P, _P, _P, _P, _L, _I, _I, _P])
-_native.register_cuda_signature("msb_bn_bwd_apply", _I, [_P] * 9 + [_L, _I, _I, _P])
-_native.register_cuda_signature("msb_maxpool3x3s2", _I, [_P, _P, _P, _I, _I, _I, _I, _I, _P])
+_native.register_cuda_signature("msb_bn_bwd_apply", _I, [_P] * 10 + [_L, _I, _I, _P])
+_native.register_cuda_signature("msb_maxpool3x3s2", _I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P])
 _native.register_cuda_signature("msb_global_avgpool", _I, [_P, _P, _I, _I, _I, _I, _P])
 
 CL = torch.channels_last
@@ -129,6 +129,7 @@ class _ConvFn(torch.autograd.Function):
         else:
             y = conv_fwd_raw(x, wk, stride, pad_h, pad_w, ho, wo, stats)
         ctx.save_for_backward(x, w)
+        ctx.col = (col, kpad) if ctx.small else None      # the patch matrix is kept for the weight gradient
         ctx.geom = (stride, pad_h, pad_w, ho, wo)
         if want_stats:
             ctx.mark_non_differentiable(stats)
@@ -145,7 +146,7 @@ class _ConvFn(torch.autograd.Function):
         dx = dw = None
         if ctx.needs_input_grad[1]:
             if ctx.small:
-                col, kpad = _im2col(x, r, s, stride, pad_h, pad_w, ho, wo)
+                col, kpad = ctx.col
                 rows = col.shape[0]
                 b = _split_k(rows)
                 dy2 = dy.permute(0, 2, 3, 1).reshape(b, rows // b, cout)
@@ -242,9 +243,10 @@ class _BnActFn(torch.autograd.Function):
                                             int(ctx.relu), _stream()), "bn_bwd_reduce")
         dx = torch.empty_like(x, memory_format=CL)
         dres = torch.empty_like(x, memory_format=CL) if ctx.has_res else None
-        _native.check(lib.msb_bn_bwd_apply(_p(dy), _p(x), _p(y), _p(g32), _p(mean), _p(rstd), _p(sums), _p(dx),
-                                           _p(dres), rows, c, int(ctx.relu), _stream()), "bn_bwd_apply")
-        _count(2)
+        coef = torch.empty(3 * c, dtype=torch.float32, device=x.device)
+        _native.check(lib.msb_bn_bwd_apply(_p(dy), _p(x), _p(y), _p(g32), _p(mean), _p(rstd), _p(sums), _p(coef),
+                                           _p(dx), _p(dres), rows, c, int(ctx.relu), _stream()), "bn_bwd_apply")
+        _count(3)
         dgamma, dbeta = sums[c:], sums[:c]
         out_g = out_b = None
         for ref, g, slot in ((ctx.gamma_ref, dgamma, 0), (ctx.beta_ref, dbeta, 1)):
@@ -293,17 +295,20 @@ class _MaxPool3x3s2Fn(torch.autograd.Function):
         n, c, h, w = x.shape
         ho, wo = (h - 1) // 2 + 1, (w - 1) // 2 + 1
         y = _empty(n, c, ho, wo, x.device)
-        _native.check(_native.cuda().msb_maxpool3x3s2(_p(x), None, _p(y), n, h, w, c, 0, _stream()), "maxpool")
+        idx = torch.empty(n * ho * wo * c, dtype=torch.uint8, device=x.device)
+        _native.check(_native.cuda().msb_maxpool3x3s2(_p(x), None, _p(y), _p(idx), n, h, w, c, 0, _stream()),
+                      "maxpool")
         _count()
-        ctx.save_for_backward(x)
+        ctx.save_for_backward(idx)
+        ctx.shape = (n, c, h, w)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        (x,) = ctx.saved_tensors
-        n, c, h, w = x.shape
-        dx = torch.empty_like(x, memory_format=CL)
-        _native.check(_native.cuda().msb_maxpool3x3s2(_p(x), _p(_nhwc(dy)), _p(dx), n, h, w, c, 1, _stream()),
+        (idx,) = ctx.saved_tensors
+        n, c, h, w = ctx.shape
+        dx = _empty(n, c, h, w, dy.device, dy.dtype)
+        _native.check(_native.cuda().msb_maxpool3x3s2(None, _p(_nhwc(dy)), _p(dx), _p(idx), n, h, w, c, 1, _stream()),
                       "maxpool_bwd")
         _count()
         return dx
