@@ -523,35 +523,39 @@ namespace msb {
 // Patch matrix for convolutions whose input has too few channels for the 64-channel box loads (the first layer of
 // image networks): out[pix, (r*S + s)*Cin + c] = x[n, ho*stride + r - pad, wo*stride + s - pad, c], zero outside the
 // image and in the padding columns k >= R*S*Cin.
-__global__ void im2col_nhwc_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int N, int H,
-                                   int W, int Cin, int R, int S, int stride, int pad_h, int pad_w, int Ho, int Wo,
-                                   int Kpad) {
-  // One thread per (output pixel, filter row): the S*Cin input values of a filter row are contiguous in NHWC, and
-  // so is their place in the patch row.  Thread R of a pixel zero-fills the padding columns.
-  const long long total = (long long)N * Ho * Wo * (R + 1);
-  const int seg = S * Cin;
+__global__ void __launch_bounds__(256)
+im2col_nhwc_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int N, int H, int W, int Cin,
+                   int R, int S, int stride, int pad_h, int pad_w, int Ho, int Wo, int Kpad) {
+  // One thread per 16-byte chunk (8 columns) of a patch row, so stores are coalesced; where column k comes from
+  // (filter row, offset inside the contiguous S*Cin input segment) is looked up in a table built once per block.
+  extern __shared__ short tab[];          // [Kpad][2]: filter row (or -1 for padding columns), segment offset
+  const int K = R * S * Cin, seg = S * Cin;
+  for (int k = threadIdx.x; k < Kpad; k += blockDim.x) {
+    tab[2 * k] = k < K ? (short)(k / seg) : (short)-1;
+    tab[2 * k + 1] = (short)(k % seg);
+  }
+  __syncthreads();
+  const int chunks = Kpad / 8;
+  const long long total = (long long)N * Ho * Wo * chunks;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
-    const int r = (int)(i % (R + 1));
-    const long long pix = i / (R + 1);
-    __nv_bfloat16* dst = out + pix * Kpad + (long long)r * seg;
-    if (r == R) {
-      for (int k = R * seg; k < Kpad; ++k) out[pix * Kpad + k] = __float2bfloat16(0.f);
-      continue;
-    }
+    const int ch = (int)(i % chunks);
+    const long long pix = i / chunks;
     const int wo = (int)(pix % Wo);
     const int ho = (int)((pix / Wo) % Ho);
     const int n = (int)(pix / ((long long)Wo * Ho));
-    const int h = ho * stride + r - pad_h, w0 = wo * stride - pad_w;
-    if (h < 0 || h >= H) {
-      for (int k = 0; k < seg; ++k) dst[k] = __float2bfloat16(0.f);
-      continue;
+    const int h0 = ho * stride - pad_h, w0 = wo * stride - pad_w;
+    const __nv_bfloat16* img = x + (long long)n * H * W * Cin;
+    __align__(16) __nv_bfloat16 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int k = ch * 8 + j;
+      const int r = tab[2 * k], off = tab[2 * k + 1];
+      const int h = h0 + r, w = w0 + off / Cin;
+      const bool in = r >= 0 && h >= 0 && h < H && w >= 0 && w < W;
+      v[j] = in ? img[((long long)h * W + w0) * Cin + off] : __float2bfloat16(0.f);
     }
-    const __nv_bfloat16* src = x + (((long long)n * H + h) * W + w0) * Cin;
-    for (int s = 0; s < S; ++s) {
-      const bool in = (w0 + s) >= 0 && (w0 + s) < W;
-      for (int c = 0; c < Cin; ++c) dst[s * Cin + c] = in ? src[s * Cin + c] : __float2bfloat16(0.f);
-    }
+    reinterpret_cast<uint4*>(out)[i] = *reinterpret_cast<const uint4*>(v);
   }
 }
 }  // namespace msb
@@ -562,12 +566,12 @@ MSB_EXPORT int msb_im2col_nhwc(const void* x, void* out, int N, int H, int W, in
     set_last_error("im2col: padded width %d must be a multiple of 8 and at least %d", Kpad, R * S * Cin);
     return kBadArg;
   }
-  const long long total = (long long)N * Ho * Wo * (R + 1);
+  const long long total = (long long)N * Ho * Wo * (Kpad / 8);
   if (total <= 0) return kOk;
   long long blocks = (total + 255) / 256;
   const long long cap = (long long)sm_count() * 16;
   blocks = blocks > cap ? cap : blocks;
-  msb::im2col_nhwc_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+  msb::im2col_nhwc_kernel<<<(unsigned)blocks, 256, Kpad * 4, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (__nv_bfloat16*)out, N, H, W, Cin, R, S, stride, pad_h, pad_w, Ho, Wo, Kpad);
   MSB_CUDA_CHECK(cudaGetLastError());
   return kOk;

@@ -176,11 +176,11 @@ class _ConvFn(torch.autograd.Function):
                 dx = conv_fwd_raw(dy, wt, 1, pad_h, pad_w, h, w_, None, flip=True)
             elif r == 1 and s == 1:
                 sub = conv_fwd_raw(dy, wt, 1, 0, 0, ho, wo, None, flip=True)
-                dx = torch.zeros((n, cin, h, w_), dtype=dy.dtype, device=dy.device).contiguous(memory_format=CL)
+                dx = _empty(n, cin, h, w_, dy.device, dy.dtype).zero_()
                 dx[:, :, 0:2 * ho:2, 0:2 * wo:2] = sub
             else:
                 hz, wz = max(h, 2 * (ho - 1) + 1), max(w_, 2 * (wo - 1) + 1)
-                dyz = torch.zeros((n, cout, hz, wz), dtype=dy.dtype, device=dy.device).contiguous(memory_format=CL)
+                dyz = _empty(n, cout, hz, wz, dy.device, dy.dtype).zero_()
                 dyz[:, :, 0:2 * ho:2, 0:2 * wo:2] = dy
                 dx = conv_fwd_raw(dyz, wt, 1, pad_h, pad_w, h, w_, None, flip=True)
         return dx, dw, None, None, None, None
