@@ -139,6 +139,11 @@ class _Recorder(TorchFunctionMode):
         if _has_tensor(out) or prim._update_parameter or prim.name in ("Send", "Barrier"):
             node = self.record(prim, args, kwargs, out)
             node.meta["primitive"] = prim.name
+            from ..parallel import spmd as _spmd
+            if _spmd.last_dispatch is not None:
+                # the sharded primitive is one node; the communication its SPMD execution performs rides along
+                node.meta.update({k: v for k, v in _spmd.last_dispatch.items() if v})
+                _spmd.last_dispatch = None
         return out
 
     def leaf_call(self, fn, args, kwargs):
@@ -326,6 +331,17 @@ def _restore_state(snapshot):
     snap, host, rng = snapshot
     with torch.no_grad():
         for p, v in snap:
+            if tuple(p.shape) != tuple(v.shape):
+                # the trace sliced this parameter to its shard (first use under a layout): restore the shard
+                lay = getattr(p, "param_layout", None)
+                if lay is None:
+                    continue
+                from .. import context as _ctx
+                from ..parallel.layout import slice_for_rank
+                rank = _ctx.get_auto_parallel_context("global_rank")
+                per = max(1, _ctx.get_auto_parallel_context("device_num") //
+                          _ctx.get_auto_parallel_context("pipeline_stages"))
+                v = slice_for_rank(v, lay, rank % per)
             torch.Tensor.copy_(p, v)
     if host is not None:
         host[0]._step_host = host[1]

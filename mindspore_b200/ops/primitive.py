@@ -44,6 +44,7 @@ def _wrap_out(out):
 class Primitive:
     def __init__(self, name):
         self.name = name
+        self.__name__ = name        # graph nodes take their label from the target's __name__
         self.attrs = {}
         self.init_attrs = {"name": name}
         self._update_parameter = False

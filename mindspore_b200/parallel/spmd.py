@@ -98,11 +98,18 @@ def _mirror(param, layout):
     if op is None:
         op = comm_ops._MirrorOperator(gname, len(ranks), context.get_auto_parallel_context("gradients_mean"))
         _mirror_cache[key] = op
+    if _record is not None:
+        _record["mirror"] += 1
     out = op._run(_plain(param))
     return out
 
 
 _equiv_cache = {}
+
+# what the most recent ``dispatch`` inserted around its primitive; the graph tracer copies it onto the node:
+# {"forward_comm": (kind, dev dims) or None, "redistribution": [operator names], "mirror": n}
+last_dispatch = None
+_record = None
 
 
 def layouts_equivalent(a: TensorLayout, b: TensorLayout):
@@ -126,6 +133,11 @@ def _plain(t):
 def _redistribute(x, cur, need):
     if layouts_equivalent(cur, need):
         return x
+    if _record is not None:
+        try:
+            _record["redistribution"] += RD.lowered_names(RD.infer(cur, need))
+        except Exception:  # noqa: BLE001  (bookkeeping only)
+            _record["redistribution"].append("Redistribution")
     return RD.apply(_plain(x), cur, need, _rank(), _stage_base())
 
 
@@ -225,6 +237,9 @@ def dispatch(prim, args, kwargs):
         if prim.in_strategy is not None:
             raise
         return _run_replicated(prim, args, kwargs)
+    global _record, last_dispatch
+    _record = {"forward_comm": tuple(info.forward_comm[:2]) if info.forward_comm else None, "redistribution": [],
+               "mirror": 0}
     need = info.input_layouts()
     local = list(args)
     for j, pos in enumerate(tensor_pos):
@@ -250,6 +265,7 @@ def dispatch(prim, args, kwargs):
         for k, v in saved.items():
             setattr(prim, k, v)
     from ..common.tensor import as_tensor
+    last_dispatch, _record = _record, None
     out_lays = info.output_layouts()
     if isinstance(out, torch.Tensor):
         out = as_tensor(_forward_comm(out, info))
