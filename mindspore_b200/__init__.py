@@ -3,7 +3,7 @@
 PyTorch is the tensor / eager substrate; hot ops are hand-written sm_100a kernels
 (``mindspore_b200/csrc/cuda``), the planner / runtime pieces are C++ (``mindspore_b200/csrc/host``).
 """
-from . import common, communication, context, nn, ops, parallel, train
+from . import common, communication, context, dataset, nn, ops, parallel, train
 from .common import (Parameter, ParameterTuple, Tensor, dtype, get_seed, initializer, set_seed)
 from .common.dtype import *  # noqa: F401,F403
 from .common.dtype import Type, dtype_to_nptype, pytype_to_dtype

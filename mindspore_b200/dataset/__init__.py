@@ -1,0 +1,5 @@
+"""``mindspore_b200.dataset``: input pipelines (sources, ``map`` / ``batch`` / ``shuffle`` / ``repeat`` / ``shard``
+/ ``take`` / ``skip`` / ``zip``, iterators) and record files."""
+from .engine import (Dataset, GeneratorDataset, MindDataset, NumpySlicesDataset, RandomDataset, config, zip)  # noqa: A004
+from .mindrecord import FileReader, FileWriter
+from . import transforms, vision

@@ -1,0 +1,516 @@
+"""Dataset pipeline: lazily composed stages over a source, executed by Python iterators; ``batch`` collates with
+numpy, ``map`` can run its operations in a thread pool (``num_parallel_workers``), and a prefetch stage keeps
+``prefetch_size`` batches ready.  Rows are dicts {column: ndarray}; ``create_tuple_iterator`` yields tuples in
+column order and ``create_dict_iterator`` the dicts.
+
+Parity (API): python/mindspore/dataset/engine/datasets.py (Dataset.map/batch/shuffle/repeat/shard/take/skip/zip,
+create_tuple_iterator, create_dict_iterator, get_dataset_size, get_col_names), datasets_user_defined.py
+(GeneratorDataset, NumpySlicesDataset), datasets_standard_format.py (MindDataset)."""
+from __future__ import annotations
+
+import builtins
+import concurrent.futures
+import queue
+import threading
+
+import numpy as np
+
+
+class _Config:
+    def __init__(self):
+        self.seed, self.prefetch_size, self.num_parallel_workers = 5489, 2, 4
+
+    def set_seed(self, s):
+        self.seed = int(s)
+
+    def get_seed(self):
+        return self.seed
+
+    def set_prefetch_size(self, n):
+        self.prefetch_size = int(n)
+
+    def get_prefetch_size(self):
+        return self.prefetch_size
+
+    def set_num_parallel_workers(self, n):
+        self.num_parallel_workers = int(n)
+
+    def get_num_parallel_workers(self):
+        return self.num_parallel_workers
+
+
+config = _Config()
+
+
+def _to_np(v):
+    import torch
+    if isinstance(v, torch.Tensor):
+        return v.detach().cpu().numpy()
+    return np.asarray(v)
+
+
+class Dataset:
+    """Base of every pipeline stage."""
+
+    def __init__(self, parent=None, columns=None):
+        self.parent = parent
+        self._columns = list(columns) if columns is not None else (parent.get_col_names() if parent else [])
+
+    # ------------------------------------------------------------------ to override
+    def _rows(self):
+        raise NotImplementedError
+
+    def get_dataset_size(self):
+        return self.parent.get_dataset_size()
+
+    # ------------------------------------------------------------------ composition
+    def get_col_names(self):
+        return list(self._columns)
+
+    def map(self, operations, input_columns=None, output_columns=None, column_order=None, num_parallel_workers=None,
+            python_multiprocessing=False, **kw):
+        return _Map(self, operations, input_columns, output_columns, num_parallel_workers)
+
+    def batch(self, batch_size, drop_remainder=False, num_parallel_workers=None, per_batch_map=None, **kw):
+        return _Batch(self, batch_size, drop_remainder, per_batch_map)
+
+    def shuffle(self, buffer_size):
+        return _Shuffle(self, buffer_size)
+
+    def repeat(self, count=None):
+        return _Repeat(self, count)
+
+    def take(self, count=-1):
+        return _Take(self, count)
+
+    def skip(self, count):
+        return _Skip(self, count)
+
+    def shard(self, num_shards, shard_id):
+        return _Shard(self, num_shards, shard_id)
+
+    def project(self, columns):
+        return _Project(self, columns)
+
+    def rename(self, input_columns, output_columns):
+        return _Rename(self, input_columns, output_columns)
+
+    def zip(self, datasets):
+        return zip((self,) + tuple(datasets if isinstance(datasets, (tuple, list)) else (datasets,)))
+
+    def prefetch(self, size=None):
+        return _Prefetch(self, size or config.prefetch_size)
+
+    # ------------------------------------------------------------------ iteration
+    def create_dict_iterator(self, num_epochs=-1, output_numpy=False, do_copy=True):
+        import mindspore_b200 as ms
+        for row in self._rows():
+            yield row if output_numpy else {k: ms.Tensor(v) for k, v in row.items()}
+
+    def create_tuple_iterator(self, columns=None, num_epochs=-1, output_numpy=False, do_copy=True):
+        import mindspore_b200 as ms
+        cols = columns or self._columns
+        for row in self._rows():
+            yield tuple(row[c] if output_numpy else ms.Tensor(row[c]) for c in cols)
+
+    def __iter__(self):
+        return self.create_tuple_iterator()
+
+    def __len__(self):
+        return self.get_dataset_size()
+
+    def output_shapes(self):
+        row = next(iter(self._rows()))
+        return [list(row[c].shape) for c in self._columns]
+
+    def output_types(self):
+        row = next(iter(self._rows()))
+        return [row[c].dtype for c in self._columns]
+
+    def get_batch_size(self):
+        return self.parent.get_batch_size() if self.parent else 1
+
+    def get_repeat_count(self):
+        return self.parent.get_repeat_count() if self.parent else 1
+
+
+# ---------------------------------------------------------------------------------------------------- sources
+class GeneratorDataset(Dataset):
+    """Source over a generator function, an iterable, or a random-access object (``__getitem__`` + ``__len__``)."""
+
+    def __init__(self, source, column_names=None, column_types=None, schema=None, num_samples=None,
+                 num_parallel_workers=1, shuffle=None, sampler=None, num_shards=None, shard_id=None,
+                 python_multiprocessing=False, max_rowsize=None):
+        if column_names is None:
+            raise ValueError("For 'GeneratorDataset', 'column_names' must be given")
+        super().__init__(None, [column_names] if isinstance(column_names, str) else column_names)
+        self.source, self.num_samples = source, num_samples
+        self.random_access = hasattr(source, "__getitem__") and hasattr(source, "__len__")
+        self.shuffle_flag = bool(shuffle) if shuffle is not None else self.random_access
+        self.num_shards, self.shard_id = num_shards, shard_id
+        self._epoch = 0
+        if (num_shards is None) != (shard_id is None):
+            raise ValueError("num_shards and shard_id must be given together")
+
+    def _indices(self):
+        n = len(self.source)
+        idx = np.arange(n)
+        if self.shuffle_flag:
+            rng = np.random.default_rng(config.seed + self._epoch)
+            rng.shuffle(idx)
+        if self.num_shards:
+            idx = idx[self.shard_id::self.num_shards]
+        if self.num_samples is not None:
+            idx = idx[:self.num_samples]
+        return idx
+
+    def get_dataset_size(self):
+        if self.random_access:
+            return len(self._indices())
+        if self.num_samples is not None:
+            return self.num_samples
+        return sum(1 for _ in self._raw())
+
+    def _raw(self):
+        if self.random_access:
+            for i in self._indices():
+                yield self.source[int(i)]
+        else:
+            it = self.source() if callable(self.source) else iter(self.source)
+            for k, item in enumerate(it):
+                if self.num_shards and k % self.num_shards != self.shard_id:
+                    continue
+                yield item
+
+    def _rows(self):
+        self._epoch += 1
+        count = 0
+        for item in self._raw():
+            if not isinstance(item, (tuple, list)):
+                item = (item,)
+            if len(item) != len(self._columns):
+                raise RuntimeError("the source yields %d columns but column_names has %d" % (len(item),
+                                                                                             len(self._columns)))
+            yield {c: _to_np(v) for c, v in builtins.zip(self._columns, item)}
+            count += 1
+            if self.num_samples is not None and count >= self.num_samples:
+                return
+
+
+class NumpySlicesDataset(GeneratorDataset):
+    def __init__(self, data, column_names=None, num_samples=None, num_parallel_workers=1, shuffle=None, sampler=None,
+                 num_shards=None, shard_id=None):
+        if isinstance(data, dict):
+            column_names = column_names or list(data.keys())
+            cols = [np.asarray(data[k]) for k in data]
+        elif isinstance(data, tuple):
+            cols = [np.asarray(d) for d in data]
+            column_names = column_names or ["column_%d" % i for i in range(len(cols))]
+        else:
+            cols = [np.asarray(data)]
+            column_names = column_names or ["column_0"]
+        n = len(cols[0])
+        if any(len(c) != n for c in cols):
+            raise ValueError("all columns of NumpySlicesDataset must have the same length")
+
+        class _Src:
+            def __len__(self):
+                return n
+
+            def __getitem__(self, i):
+                return tuple(c[i] for c in cols)
+
+        super().__init__(_Src(), column_names, num_samples=num_samples, shuffle=shuffle, num_shards=num_shards,
+                         shard_id=shard_id)
+
+
+class RandomDataset(GeneratorDataset):
+    """Synthetic rows of given shapes / dtypes (benchmarks and tests)."""
+
+    def __init__(self, shapes, dtypes, column_names, total_rows=64, seed=0):
+        rng = np.random.default_rng(seed)
+        data = [rng.standard_normal((total_rows,) + tuple(s)).astype(d) if np.issubdtype(np.dtype(d), np.floating)
+                else rng.integers(0, 100, (total_rows,) + tuple(s)).astype(d) for s, d in builtins.zip(shapes, dtypes)]
+
+        class _Src:
+            def __len__(self):
+                return total_rows
+
+            def __getitem__(self, i):
+                return tuple(c[i] for c in data)
+
+        super().__init__(_Src(), column_names, shuffle=False)
+
+
+class MindDataset(GeneratorDataset):
+    """Rows of record files written by ``dataset.mindrecord.FileWriter``."""
+
+    def __init__(self, dataset_files, columns_list=None, num_parallel_workers=None, shuffle=None, num_shards=None,
+                 shard_id=None, sampler=None, num_samples=None, **kw):
+        from .mindrecord import FileReader
+        files = [dataset_files] if isinstance(dataset_files, str) else list(dataset_files)
+        readers = [FileReader(f, columns=columns_list) for f in files]
+        index = [(ri, k) for ri, r in enumerate(readers) for k in range(len(r))]
+        cols = columns_list or readers[0].columns
+
+        class _Src:
+            def __len__(self):
+                return len(index)
+
+            def __getitem__(self, i):
+                ri, k = index[i]
+                row = readers[ri].read(k)
+                return tuple(row[c] for c in cols)
+
+        super().__init__(_Src(), cols, num_samples=num_samples, shuffle=shuffle, num_shards=num_shards,
+                         shard_id=shard_id)
+
+
+# ---------------------------------------------------------------------------------------------------- stages
+class _Map(Dataset):
+    def __init__(self, parent, operations, input_columns, output_columns, workers):
+        ops = operations if isinstance(operations, (list, tuple)) else [operations]
+        self.ops = list(ops)
+        self.inp = [input_columns] if isinstance(input_columns, str) else (input_columns or parent.get_col_names()[:1])
+        self.out = [output_columns] if isinstance(output_columns, str) else (output_columns or self.inp)
+        cols = []
+        for c in parent.get_col_names():
+            if c in self.inp:
+                if c == self.inp[0]:
+                    cols += self.out
+            else:
+                cols.append(c)
+        super().__init__(parent, cols)
+        self.workers = workers or 1
+
+    def _apply(self, row):
+        vals = tuple(row[c] for c in self.inp)
+        for op in self.ops:
+            vals = op(*vals)
+            if not isinstance(vals, tuple):
+                vals = (vals,)
+        if len(vals) != len(self.out):
+            raise RuntimeError("map produced %d columns, expected %d (%s)" % (len(vals), len(self.out), self.out))
+        new = {c: v for c, v in row.items() if c not in self.inp}
+        new.update({c: _to_np(v) for c, v in builtins.zip(self.out, vals)})
+        return new
+
+    def _rows(self):
+        if self.workers <= 1:
+            for row in self.parent._rows():
+                yield self._apply(row)
+            return
+        with concurrent.futures.ThreadPoolExecutor(self.workers) as pool:
+            window = []
+            for row in self.parent._rows():
+                window.append(pool.submit(self._apply, row))
+                if len(window) >= 4 * self.workers:
+                    yield window.pop(0).result()
+            for f in window:
+                yield f.result()
+
+
+class _Batch(Dataset):
+    def __init__(self, parent, batch_size, drop_remainder, per_batch_map):
+        if not isinstance(batch_size, int) or batch_size <= 0:
+            raise ValueError("batch_size must be a positive int")
+        super().__init__(parent)
+        self.batch_size, self.drop, self.per_batch_map = batch_size, drop_remainder, per_batch_map
+
+    def get_dataset_size(self):
+        n = self.parent.get_dataset_size()
+        return n // self.batch_size if self.drop else (n + self.batch_size - 1) // self.batch_size
+
+    def get_batch_size(self):
+        return self.batch_size
+
+    def _collate(self, rows):
+        out = {}
+        for c in self._columns:
+            vals = [r[c] for r in rows]
+            if self.per_batch_map is None:
+                out[c] = np.stack(vals)
+            else:
+                out[c] = vals
+        if self.per_batch_map is not None:
+            res = self.per_batch_map(*[out[c] for c in self._columns], {"batch_size": len(rows)})
+            out = {c: np.stack([_to_np(x) for x in v]) for c, v in builtins.zip(self._columns, res)}
+        return out
+
+    def _rows(self):
+        buf = []
+        for row in self.parent._rows():
+            buf.append(row)
+            if len(buf) == self.batch_size:
+                yield self._collate(buf)
+                buf = []
+        if buf and not self.drop:
+            yield self._collate(buf)
+
+
+class _Shuffle(Dataset):
+    def __init__(self, parent, buffer_size):
+        if buffer_size < 1:
+            raise ValueError("buffer_size must be at least 1")
+        super().__init__(parent)
+        self.buffer_size, self._epoch = buffer_size, 0
+
+    def _rows(self):
+        rng = np.random.default_rng(config.seed + 7919 * self._epoch)
+        self._epoch += 1
+        buf = []
+        for row in self.parent._rows():
+            if len(buf) < self.buffer_size:
+                buf.append(row)
+                continue
+            i = int(rng.integers(0, self.buffer_size))
+            yield buf[i]
+            buf[i] = row
+        rng.shuffle(buf)
+        yield from buf
+
+
+class _Repeat(Dataset):
+    def __init__(self, parent, count):
+        super().__init__(parent)
+        self.count = count
+
+    def get_dataset_size(self):
+        n = self.parent.get_dataset_size()
+        return n * self.count if self.count and self.count > 0 else n
+
+    def get_repeat_count(self):
+        return self.count or -1
+
+    def _rows(self):
+        k = 0
+        while self.count is None or self.count < 0 or k < self.count:
+            yield from self.parent._rows()
+            k += 1
+
+
+class _Take(Dataset):
+    def __init__(self, parent, count):
+        super().__init__(parent)
+        self.count = count
+
+    def get_dataset_size(self):
+        n = self.parent.get_dataset_size()
+        return n if self.count < 0 else min(n, self.count)
+
+    def _rows(self):
+        for i, row in enumerate(self.parent._rows()):
+            if 0 <= self.count <= i:
+                return
+            yield row
+
+
+class _Skip(Dataset):
+    def __init__(self, parent, count):
+        super().__init__(parent)
+        self.count = count
+
+    def get_dataset_size(self):
+        return max(0, self.parent.get_dataset_size() - self.count)
+
+    def _rows(self):
+        for i, row in enumerate(self.parent._rows()):
+            if i >= self.count:
+                yield row
+
+
+class _Shard(Dataset):
+    def __init__(self, parent, num_shards, shard_id):
+        if not 0 <= shard_id < num_shards:
+            raise ValueError("shard_id must be in [0, num_shards)")
+        super().__init__(parent)
+        self.num_shards, self.shard_id = num_shards, shard_id
+
+    def get_dataset_size(self):
+        n = self.parent.get_dataset_size()
+        return (n - self.shard_id + self.num_shards - 1) // self.num_shards
+
+    def _rows(self):
+        for i, row in enumerate(self.parent._rows()):
+            if i % self.num_shards == self.shard_id:
+                yield row
+
+
+class _Project(Dataset):
+    def __init__(self, parent, columns):
+        cols = [columns] if isinstance(columns, str) else list(columns)
+        missing = [c for c in cols if c not in parent.get_col_names()]
+        if missing:
+            raise RuntimeError("project: unknown columns %s" % missing)
+        super().__init__(parent, cols)
+
+    def _rows(self):
+        for row in self.parent._rows():
+            yield {c: row[c] for c in self._columns}
+
+
+class _Rename(Dataset):
+    def __init__(self, parent, inp, out):
+        inp = [inp] if isinstance(inp, str) else list(inp)
+        out = [out] if isinstance(out, str) else list(out)
+        self.mapping = dict(builtins.zip(inp, out))
+        super().__init__(parent, [self.mapping.get(c, c) for c in parent.get_col_names()])
+
+    def _rows(self):
+        for row in self.parent._rows():
+            yield {self.mapping.get(c, c): v for c, v in row.items()}
+
+
+class _Zip(Dataset):
+    def __init__(self, parents):
+        cols = []
+        for p in parents:
+            for c in p.get_col_names():
+                if c in cols:
+                    raise RuntimeError("zip: column %r appears in more than one dataset" % c)
+                cols.append(c)
+        super().__init__(None, cols)
+        self.parents = list(parents)
+
+    def get_dataset_size(self):
+        return min(p.get_dataset_size() for p in self.parents)
+
+    def _rows(self):
+        for rows in builtins.zip(*[p._rows() for p in self.parents]):
+            out = {}
+            for r in rows:
+                out.update(r)
+            yield out
+
+
+class _Prefetch(Dataset):
+    """Runs the upstream pipeline in a background thread, ``size`` rows ahead."""
+
+    def __init__(self, parent, size):
+        super().__init__(parent)
+        self.size = max(1, size)
+
+    def _rows(self):
+        q = queue.Queue(self.size)
+        end = object()
+
+        def work():
+            try:
+                for row in self.parent._rows():
+                    q.put(row)
+                q.put(end)
+            except BaseException as e:  # noqa: BLE001  (re-raised in the consumer)
+                q.put(e)
+
+        threading.Thread(target=work, daemon=True).start()
+        while True:
+            item = q.get()
+            if item is end:
+                return
+            if isinstance(item, BaseException):
+                raise item
+            yield item
+
+
+def zip(datasets):  # noqa: A001
+    return _Zip(tuple(datasets))
