@@ -26,5 +26,9 @@ from .train.serialization import async_ckpt_thread_status, load_segmented_checkp
 
 from .profiler import EnvProfiler, Profiler
 
+from .utils.dump import set_dump
+from .train.summary import SummaryRecord
+from . import hal, mint
+
 mstype = dtype
 __version__ = "0.1.0"

@@ -1,0 +1,169 @@
+"""``mindspore_b200.hal``: streams, events, device and memory queries
+(python/mindspore/hal/{stream,event,device,memory}.py)."""
+from __future__ import annotations
+
+import torch
+
+
+def is_initialized(device_target="GPU"):
+    return torch.cuda.is_initialized() if device_target == "GPU" else True
+
+
+def is_available(device_target="GPU"):
+    return torch.cuda.is_available() if device_target == "GPU" else device_target == "CPU"
+
+
+def device_count(device_target="GPU"):
+    return torch.cuda.device_count() if device_target == "GPU" else 1
+
+
+def get_device_name(device_id=0, device_target="GPU"):
+    return torch.cuda.get_device_name(device_id) if device_target == "GPU" else "CPU"
+
+
+def get_device_capability(device_id=0, device_target="GPU"):
+    return torch.cuda.get_device_capability(device_id) if device_target == "GPU" else None
+
+
+def get_device_properties(device_id=0, device_target="GPU"):
+    return torch.cuda.get_device_properties(device_id) if device_target == "GPU" else None
+
+
+def get_arch_list(device_target="GPU"):
+    return ["sm_100a"] if device_target == "GPU" else []
+
+
+class Stream:
+    def __init__(self, priority=0, **kwargs):
+        self._s = kwargs.get("stream") or (torch.cuda.Stream(priority=priority) if torch.cuda.is_available() else None)
+
+    @property
+    def id(self):
+        return self._s.cuda_stream if self._s is not None else 0
+
+    def record_event(self, event=None):
+        event = event or Event()
+        event.record(self)
+        return event
+
+    def wait_event(self, event):
+        if self._s is not None:
+            self._s.wait_event(event._e)
+
+    def wait_stream(self, stream):
+        if self._s is not None:
+            self._s.wait_stream(stream._s)
+
+    def synchronize(self):
+        if self._s is not None:
+            self._s.synchronize()
+
+    def query(self):
+        return self._s.query() if self._s is not None else True
+
+    def __enter__(self):
+        self._ctx = torch.cuda.stream(self._s) if self._s is not None else None
+        if self._ctx:
+            self._ctx.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        if self._ctx:
+            self._ctx.__exit__(*exc)
+
+
+class StreamCtx:
+    def __init__(self, ctx_stream):
+        self.stream = ctx_stream
+
+    def __enter__(self):
+        return self.stream.__enter__()
+
+    def __exit__(self, *exc):
+        return self.stream.__exit__(*exc)
+
+
+class Event:
+    def __init__(self, enable_timing=False, blocking=False):
+        self._e = torch.cuda.Event(enable_timing=enable_timing, blocking=blocking) if torch.cuda.is_available() \
+            else None
+
+    def record(self, stream=None):
+        if self._e is not None:
+            self._e.record(stream._s if stream is not None else None)
+
+    def wait(self, stream=None):
+        if self._e is not None:
+            (stream._s if stream is not None else torch.cuda.current_stream()).wait_event(self._e)
+
+    def synchronize(self):
+        if self._e is not None:
+            self._e.synchronize()
+
+    def query(self):
+        return self._e.query() if self._e is not None else True
+
+    def elapsed_time(self, end_event):
+        return self._e.elapsed_time(end_event._e)
+
+
+def current_stream():
+    return Stream(stream=torch.cuda.current_stream()) if torch.cuda.is_available() else Stream()
+
+
+def default_stream():
+    return Stream(stream=torch.cuda.default_stream()) if torch.cuda.is_available() else Stream()
+
+
+def set_cur_stream(stream):
+    if stream._s is not None:
+        torch.cuda.set_stream(stream._s)
+
+
+def synchronize():
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+
+
+def memory_stats(device_target="GPU"):
+    if not torch.cuda.is_available():
+        return {}
+    s = torch.cuda.memory_stats()
+    return {"total_reserved_memory": s.get("reserved_bytes.all.current", 0),
+            "total_allocated_memory": s.get("allocated_bytes.all.current", 0),
+            "max_reserved_memory": s.get("reserved_bytes.all.peak", 0),
+            "max_allocated_memory": s.get("allocated_bytes.all.peak", 0)}
+
+
+def memory_reserved(device_target="GPU"):
+    return torch.cuda.memory_reserved() if torch.cuda.is_available() else 0
+
+
+def max_memory_reserved(device_target="GPU"):
+    return torch.cuda.max_memory_reserved() if torch.cuda.is_available() else 0
+
+
+def memory_allocated(device_target="GPU"):
+    return torch.cuda.memory_allocated() if torch.cuda.is_available() else 0
+
+
+def max_memory_allocated(device_target="GPU"):
+    return torch.cuda.max_memory_allocated() if torch.cuda.is_available() else 0
+
+
+def reset_peak_memory_stats(device_target="GPU"):
+    if torch.cuda.is_available():
+        torch.cuda.reset_peak_memory_stats()
+
+
+def reset_max_memory_reserved(device_target="GPU"):
+    reset_peak_memory_stats(device_target)
+
+
+def reset_max_memory_allocated(device_target="GPU"):
+    reset_peak_memory_stats(device_target)
+
+
+def empty_cache():
+    if torch.cuda.is_available():
+        torch.cuda.empty_cache()
