@@ -90,3 +90,16 @@ def test_errors(tmp_path):
         ms.load_checkpoint("x.txt")
     with pytest.raises(TypeError):
         ms.save_checkpoint(3, str(tmp_path / "x.ckpt"))
+
+
+@pytest.mark.parametrize("mode", ["AES-GCM", "AES-CBC"])
+def test_encrypted_checkpoint_roundtrip(tmp_path, mode):
+    import mindspore_b200 as ms
+    key = bytes(range(16))
+    w = torch.randn(5, 7)
+    path = str(tmp_path / "enc.ckpt")
+    ms.save_checkpoint([{"name": "w", "data": ms.Tensor(w)}], path, enc_key=key, enc_mode=mode)
+    back = ms.load_checkpoint(path, dec_key=key, dec_mode=mode)
+    torch.testing.assert_close(back["w"].as_subclass(torch.Tensor), w)
+    with pytest.raises(ValueError):
+        ms.load_checkpoint(path, dec_key=bytes(16), dec_mode=mode)
