@@ -631,12 +631,15 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
 using namespace msb;
 
-// All tensors token-major [B,S,H,128] with the given token pitches (elements).  delta: fp32 [B,H,S] scratch that
-// this call fills.  dq/dk/dv pitches: dq_pitch, dkv_pitch.
-MSB_EXPORT int msb_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
-                                  const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int H,
-                                  int Hk, int D, long long q_pitch, long long k_pitch, long long v_pitch,
-                                  long long o_pitch, long long do_pitch, int causal, float scale, void* stream_) {
+static int fa_bwd_impl(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                       float* delta, void* dq, void* dk, void* dv, int B, int S, int H, int Hk, int D,
+                       long long q_pitch, long long k_pitch, long long v_pitch, long long o_pitch, long long do_pitch,
+                       long long dq_pitch, long long dkv_pitch, int causal, float scale, void* stream_) {
+  if ((dq_pitch % 8) || (dkv_pitch % 8) || (reinterpret_cast<uintptr_t>(dq) & 15) ||
+      (reinterpret_cast<uintptr_t>(dk) & 15) || (reinterpret_cast<uintptr_t>(dv) & 15)) {
+    set_last_error("flash_attn_bwd: gradient pitches must be multiples of 8 elements and pointers 16-byte aligned");
+    return kBadArg;
+  }
   if (D != kFaD || S % 128 != 0 || S <= 0 || H != Hk || B <= 0) {
     set_last_error("flash_attn_bwd: needs head_dim 128, S a multiple of 128 and equal q/kv head counts "
                    "(got D=%d S=%d H=%d Hk=%d)", D, S, H, Hk);
@@ -677,8 +680,8 @@ MSB_EXPORT int msb_flash_attn_bwd(const void* q, const void* k, const void* v, c
   p.dk = static_cast<__nv_bfloat16*>(dk);
   p.dv = static_cast<__nv_bfloat16*>(dv);
   p.status = status;
-  p.dq_pitch = (long long)H * kFaD;
-  p.dkv_pitch = (long long)Hk * kFaD;
+  p.dq_pitch = dq_pitch;
+  p.dkv_pitch = dkv_pitch;
   p.B = B; p.H = H; p.S = S; p.causal = causal;
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
@@ -689,4 +692,26 @@ MSB_EXPORT int msb_flash_attn_bwd(const void* q, const void* k, const void* v, c
   fa_bwd_dq_kernel<<<grid, kBwdThreads, DqSmem::kBytes, stream>>>(tq128, tk, tv, tdo128, p);
   MSB_CUDA_CHECK(cudaGetLastError());
   return kOk;
+}
+
+// All tensors token-major [B,S,H,128] with the given token pitches (elements).  delta: fp32 [B,H,S] scratch that
+// this call fills.  dq / dk / dv are written densely ([B,S,H,128]).
+MSB_EXPORT int msb_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                                  const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int H,
+                                  int Hk, int D, long long q_pitch, long long k_pitch, long long v_pitch,
+                                  long long o_pitch, long long do_pitch, int causal, float scale, void* stream) {
+  return fa_bwd_impl(q, k, v, o, dout, lse, delta, dq, dk, dv, B, S, H, Hk, D, q_pitch, k_pitch, v_pitch, o_pitch,
+                     do_pitch, (long long)H * kFaD, (long long)Hk * kFaD, causal, scale, stream);
+}
+
+// Same, with the token pitches of the gradient outputs given: lets dq, dk, dv be column blocks of one packed
+// [tokens, (H + 2 Hk) * 128] gradient of a fused QKV projection.
+MSB_EXPORT int msb_flash_attn_bwd_strided(const void* q, const void* k, const void* v, const void* o,
+                                          const void* dout, const float* lse, float* delta, void* dq, void* dk,
+                                          void* dv, int B, int S, int H, int Hk, int D, long long q_pitch,
+                                          long long k_pitch, long long v_pitch, long long o_pitch, long long do_pitch,
+                                          long long dq_pitch, long long dkv_pitch, int causal, float scale,
+                                          void* stream) {
+  return fa_bwd_impl(q, k, v, o, dout, lse, delta, dq, dk, dv, B, S, H, Hk, D, q_pitch, k_pitch, v_pitch, o_pitch,
+                     do_pitch, dq_pitch, dkv_pitch, causal, scale, stream);
 }

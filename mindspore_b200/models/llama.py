@@ -100,12 +100,8 @@ class LlamaAttention(nn.Cell):
         """x: [tokens(/mp), hidden] -> [tokens(/mp), hidden]"""
         sp = self.cfg.sequence_parallel
         qkv = TP.column_parallel_linear(x, self.wqkv, self.tp, sequence_parallel=sp)      # [T, (h+2hk)*d]
-        hd, kd = self.heads * self.d, self.kv_heads * self.d
-        qk = fused.rope(qkv[:, :hd + kd].contiguous(), cos, sin, self.heads + self.kv_heads, self.d, seq)
-        q = qk[:, :hd].reshape(batch, seq, self.heads, self.d)
-        k = qk[:, hd:].reshape(batch, seq, self.kv_heads, self.d)
-        v = qkv[:, hd + kd:].reshape(batch, seq, self.kv_heads, self.d)
-        o = fused.flash_attention(q, k, v, causal=True)
+        hd = self.heads * self.d
+        o = fused.qkv_rope_attention(qkv, cos, sin, batch, seq, self.heads, self.kv_heads, self.d, causal=True)
         return TP.row_parallel_linear(o.reshape(batch * seq, hd), self.wo, self.tp, sequence_parallel=sp)
 
 

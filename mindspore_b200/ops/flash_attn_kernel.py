@@ -13,6 +13,27 @@ _native.register_cuda_signature("msb_flash_attn_bwd", _I, [_P, _P, _P, _P, _P, _
                                                             _L, _L, _L, _L, _L, _I, _F, _P])
 
 
+_native.register_cuda_signature("msb_flash_attn_bwd_strided", _I, [_P] * 10 + [_I] * 5 + [_L] * 7 + [_I, _F, _P])
+
+
+def has_strided_bwd():
+    return hasattr(_native.cuda(), "msb_flash_attn_bwd_strided")
+
+
+def bwd_into(do, q, k, v, o, lse, causal, scale, dq, dk, dv, grad_pitch):
+    """Backward with dq / dk / dv written into caller-provided column blocks (token pitch ``grad_pitch``)."""
+    B, S, H, D = q.shape
+    Hk = k.shape[2]
+    do = do.contiguous()
+    delta = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+    rc = _native.cuda().msb_flash_attn_bwd_strided(
+        _p(q), _p(k), _p(v), _p(o), _p(do), _p(lse), _p(delta), _p(dq), _p(dk), _p(dv), B, S, H, Hk, D,
+        _token_major(q), _token_major(k), _token_major(v), H * D, H * D, grad_pitch, grad_pitch, int(causal),
+        float(scale), _stream())
+    _native.check(rc, "flash_attn_bwd_strided")
+    _count(3)
+
+
 def available():
     return torch.cuda.is_available() and hasattr(_native.cuda(), "msb_flash_attn_fwd")
 

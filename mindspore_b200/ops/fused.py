@@ -317,3 +317,57 @@ def flash_attention(q, k, v, causal=True, scale=None):
     """Scaled-dot-product attention on [B, S, H, D] tensors (kv heads may divide q heads)."""
     from . import attention as _attn
     return _attn.flash_attention(q, k, v, causal=causal, scale=scale)
+
+
+# ------------------------------------------------------------------------------------------ packed QKV attention
+class _QkvRopeAttnFn(torch.autograd.Function):
+    """RoPE + causal attention straight on the packed output of a fused QKV projection.
+
+    ``qkv`` [tokens, (H + 2 Hk) * D] is rotated in place (q and k column blocks), the attention kernel reads q, k, v
+    as strided views of it, and the backward kernels write dq, dk, dv into the column blocks of one packed gradient,
+    which is then un-rotated in place: no slicing copies, no concatenation."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, batch, seq, heads, kv_heads, d, causal, scale):
+        from . import flash_attn_kernel as FK
+        hd, kd = heads * d, kv_heads * d
+        K.rope_(qkv[:, :hd + kd], cos, sin, heads + kv_heads, d, seq)
+        q = qkv[:, :hd].view(batch, seq, heads, d)
+        k = qkv[:, hd:hd + kd].view(batch, seq, kv_heads, d)
+        v = qkv[:, hd + kd:].view(batch, seq, kv_heads, d)
+        o, lse, _, _, _ = FK.fwd(q, k, v, causal, scale)
+        ctx.save_for_backward(qkv, o, lse, cos, sin)
+        ctx.meta = (batch, seq, heads, kv_heads, d, causal, scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        from . import flash_attn_kernel as FK
+        qkv, o, lse, cos, sin = ctx.saved_tensors
+        batch, seq, heads, kv_heads, d, causal, scale = ctx.meta
+        hd, kd = heads * d, kv_heads * d
+        q = qkv[:, :hd].view(batch, seq, heads, d)
+        k = qkv[:, hd:hd + kd].view(batch, seq, kv_heads, d)
+        v = qkv[:, hd + kd:].view(batch, seq, kv_heads, d)
+        dqkv = torch.empty_like(qkv)
+        FK.bwd_into(do, q, k, v, o, lse, causal, scale, dqkv[:, :hd], dqkv[:, hd:hd + kd], dqkv[:, hd + kd:],
+                    qkv.shape[1])
+        K.rope_(dqkv[:, :hd + kd], cos, sin, heads + kv_heads, d, seq, backward=True)
+        return dqkv, None, None, None, None, None, None, None, None, None
+
+
+def qkv_rope_attention(qkv, cos, sin, batch, seq, heads, kv_heads, head_dim, causal=True, scale=None):
+    """Attention output [batch, seq, heads, head_dim] from the packed projection ``qkv`` [batch*seq, (H+2Hk)*D]
+    (q heads, then k heads, then v heads).  ``qkv`` is consumed: the kernel path rotates it in place."""
+    import math
+    from . import flash_attn_kernel as FK
+    scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    hd, kd = heads * head_dim, kv_heads * head_dim
+    if (_use_kernel(qkv) and qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and head_dim == 128
+            and seq % 128 == 0 and heads == kv_heads and FK.available() and FK.has_strided_bwd()):
+        return _QkvRopeAttnFn.apply(qkv, cos, sin, batch, seq, heads, kv_heads, head_dim, bool(causal), float(scale))
+    qk = rope(qkv[:, :hd + kd].contiguous(), cos, sin, heads + kv_heads, head_dim, seq)
+    q = qk[:, :hd].reshape(batch, seq, heads, head_dim)
+    k = qk[:, hd:].reshape(batch, seq, kv_heads, head_dim)
+    v = qkv[:, hd + kd:].reshape(batch, seq, kv_heads, head_dim)
+    return flash_attention(q, k, v, causal=causal, scale=scale)
