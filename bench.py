@@ -233,8 +233,11 @@ def main():
                              % args.gpus)
         args.gpus = world
     torch.cuda.set_device(local_rank)
-    ms.set_context(mode=ms.PYNATIVE_MODE, device_target="GPU", device_id=local_rank,
-                   enable_cuda_graph=os.environ.get("MSB200_CUDA_GRAPH", "0") == "1")
+    # With model parallelism the per-rank kernels shrink while the launch count does not: from 2 ranks on the step
+    # is bound by host launch time unless the micro-batch is replayed as a CUDA graph.
+    graph_env = os.environ.get("MSB200_CUDA_GRAPH", "auto")
+    use_graph = graph_env == "1" or (graph_env == "auto" and world >= 2)
+    ms.set_context(mode=ms.PYNATIVE_MODE, device_target="GPU", device_id=local_rank, enable_cuda_graph=use_graph)
     if world > 1:
         from mindspore_b200.communication import init
         init("nccl")
@@ -344,9 +347,15 @@ def main():
             "max_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
         }
         print(json.dumps(out), flush=True)
-    step_cell.release_graphs()
     if world > 1:
         torch.distributed.barrier()
+        torch.cuda.synchronize()
+        if use_graph:
+            # a captured graph holds NCCL kernels of this communicator; tearing the two down in the wrong order
+            # blocks in the NCCL watchdog, so the process ends here without running either destructor
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
         M.release()
     return 0
 
