@@ -50,7 +50,32 @@ struct GemmParams {
   void* ag_dst;
   int* ag_flags;
   int world, rank, rows_per_rank;
+  // The epilogue stages 32 rows x 128 bytes per warp in shared memory (128-byte swizzle) and writes them with TMA
+  // stores (fp32 accumulation = TMA reduce-add): full 128-byte lines instead of 16-byte fragments per row, which is
+  // what makes stores into a peer's memory efficient.  0 = per-thread stores (unaligned C, bf16 accumulation).
+  int tma_epilogue;
 };
+
+struct CMaps {
+  CUtensorMap m[8];   // m[0]: C.  MatMul -> ReduceScatter: m[r] = staging buffer of rank r
+};
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* tmap, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* tmap, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read_n() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
 
 constexpr int kBounceBytes = 8192;   // per bounce buffer of the AllGather copy warp (two buffers)
 
@@ -60,7 +85,10 @@ struct GemmCfg {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = kStages * kStageBytes;
+  // epilogue staging: 4 warps x (32 rows x 128 B), 1024-byte aligned (after the stage ring)
+  static constexpr int kStagingOffset = kStages * kStageBytes;
+  static constexpr int kStagingBytes = 4 * 4096;
+  static constexpr int kBarOffset = kStagingOffset + kStagingBytes;
   static constexpr int kBounceOffset = kBarOffset + 256;
   static constexpr int kSmemBytes = kBarOffset + 256 + 1024;  // barriers + slack for 1024B alignment
   static constexpr int kSmemBytesAG = kBounceOffset + 2 * kBounceBytes + 1024;
@@ -70,7 +98,7 @@ struct GemmCfg {
 template <int BN, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(MODE == 2 ? kGemmThreads + 32 : kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmParams p) {
+                 const __grid_constant__ CMaps tmC, const GemmParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int kStages = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -257,6 +285,89 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         c_bf16 = static_cast<__nv_bfloat16*>(p.rs_peer[owner]);
         c_off = (static_cast<long long>(p.rank) * p.rows_per_rank + (row - owner * p.rows_per_rank)) * p.ldc;
       }
+      if (p.tma_epilogue) {
+        // ---- staged epilogue: registers -> swizzled shared memory -> TMA store / reduce
+        uint8_t* stage_base = smem + Cfg::kStagingOffset + q * 4096;
+        const int row0 = m_blk * kBM + q * 32;
+        const CUtensorMap* cmap = &tmC.m[0];
+        int store_row = row0;
+        if (MODE == 1) {
+          const int owner = (m_blk * kBM) / p.rows_per_rank;
+          cmap = &tmC.m[owner];
+          store_row = p.rank * p.rows_per_rank + (row0 - owner * p.rows_per_rank);
+        }
+        const int sw = lane & 7;
+        int nbuf = 0;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          if (n0 + c >= p.N) break;  // warp-uniform
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c, r);
+          tmem_ld_wait();
+          const int col0 = n0 + c;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+          if (p.bias) {
+            const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(p.bias);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) v[j] += __bfloat162float(bias[col0 + j]);
+          }
+          if (p.out_fp32) {
+            // one chunk = 32 fp32 = a full 128-byte row
+            uint8_t* buf = stage_base;
+            if (nbuf >= 1) tma_store_wait_read_n<0>();   // the previous store has read the buffer
+            __syncwarp();
+            uint8_t* rowp = buf + lane * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<float4*>(rowp + ((j ^ sw) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2],
+                                                                               v[4 * j + 3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (p.accumulate) tma_reduce_add_3d(cmap, buf, col0, store_row, b);
+              else tma_store_3d(cmap, buf, col0, store_row, b);
+              tma_store_commit();
+            }
+            ++nbuf;
+          } else {
+            // two chunks (64 bf16) make one 128-byte row
+            const int half = (c >> 5) & 1;
+            uint8_t* buf = stage_base;
+            if (half == 0) {
+              if (nbuf >= 1) tma_store_wait_read_n<0>();
+              __syncwarp();
+            }
+            uint8_t* rowp = buf + lane * 128;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 o;
+              o.x = pack_bf16x2(v[8 * j], v[8 * j + 1]);
+              o.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+              o.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+              o.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+              *reinterpret_cast<uint4*>(rowp + (((half * 4 + j) ^ sw) << 4)) = o;
+            }
+            const bool last = (c + 32 >= BN) || (n0 + c + 32 >= p.N);
+            if (half == 1 || last) {
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_3d(cmap, buf, col0 - half * 32, store_row, b);
+                tma_store_commit();
+              }
+              ++nbuf;
+            }
+          }
+        }
+        if (lane == 0) tma_store_wait_read_n<0>();   // staging may be rewritten by the next tile
+        __syncwarp();
+        tc_fence_before_sync();
+        mbar_arrive(&tempty_bar[acc]);
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         if (n0 + c >= p.N) break;  // warp-uniform
@@ -322,6 +433,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_before_sync();
       mbar_arrive(&tempty_bar[acc]);
+    }
+    if (p.tma_epilogue && lane == 0) {
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every staged store has been written out
+      if (MODE == 1) __threadfence_system();
     }
   }
 
@@ -408,7 +523,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 template <int BN, bool A_MN, bool B_MN, int MODE>
-static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CMaps& tmC, const GemmParams& p,
+                       cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, MODE>;
   constexpr int smem = MODE == 2 ? Cfg::kSmemBytesAG : Cfg::kSmemBytes;
@@ -419,7 +535,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   }
   const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN) * p.batch;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, MODE == 2 ? kGemmThreads + 32 : kGemmThreads, smem, stream>>>(tmA, tmB, p);
+  kern<<<grid, MODE == 2 ? kGemmThreads + 32 : kGemmThreads, smem, stream>>>(tmA, tmB, tmC, p);
   MSB_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
@@ -448,6 +564,20 @@ static int encode_operands(CUtensorMap* tmA, CUtensorMap* tmB, const void* A, co
   if (b_mn) rc = encode_tmap_3d(tmB, B, 2, N, K, batch, ldb * 2, bbs_, 64, 64, 1);
   else      rc = encode_tmap_3d(tmB, B, 2, K, N, batch, ldb * 2, bbs_, 64, bn, 1);
   return rc;
+}
+
+// Tensor map of an output matrix for the staged epilogue (128-byte rows of 32 output rows); returns 0 and leaves
+// *ok = 0 when the matrix does not meet the TMA alignment rules (the kernel then stores per thread).
+static int encode_output(CUtensorMap* map, const void* C, int M, int N, int batch, long long ldc,
+                         long long c_batch_stride, int out_fp32, int* ok) {
+  const int es = out_fp32 ? 4 : 2;
+  *ok = 0;
+  if ((reinterpret_cast<uintptr_t>(C) & 15) || ((ldc * es) & 15) || (batch > 1 && ((c_batch_stride * es) & 15)))
+    return kOk;
+  const uint64_t bs = batch > 1 ? static_cast<uint64_t>(c_batch_stride) * es : static_cast<uint64_t>(ldc) * es * M;
+  if (int rc = encode_tmap_3d(map, C, es, N, M, batch, static_cast<uint64_t>(ldc) * es, bs, 128 / es, 32, 1)) return rc;
+  *ok = 1;
+  return kOk;
 }
 
 }  // namespace msb
@@ -480,14 +610,18 @@ MSB_EXPORT int msb_gemm_bf16(const void* A, const void* B, void* C, const void* 
   p.C = C; p.bias = bias; p.status = status; p.c_batch_stride = c_batch_stride;
   p.M = M; p.N = N; p.K = K; p.batch = batch; p.ldc = static_cast<int>(ldc);
   p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
+  CMaps tmC = {};
+  if (!(accumulate && !out_fp32)) {
+    if (int rc = encode_output(&tmC.m[0], C, M, N, batch, ldc, c_batch_stride, out_fp32, &p.tma_epilogue)) return rc;
+  }
 
 #define MSB_DISPATCH(BN_)                                                          \
   if (a_mn) {                                                                      \
-    if (b_mn) return launch_gemm<BN_, true, true, 0>(tmA, tmB, p, stream);         \
-    return launch_gemm<BN_, true, false, 0>(tmA, tmB, p, stream);                  \
+    if (b_mn) return launch_gemm<BN_, true, true, 0>(tmA, tmB, tmC, p, stream);    \
+    return launch_gemm<BN_, true, false, 0>(tmA, tmB, tmC, p, stream);             \
   } else {                                                                         \
-    if (b_mn) return launch_gemm<BN_, false, true, 0>(tmA, tmB, p, stream);        \
-    return launch_gemm<BN_, false, false, 0>(tmA, tmB, p, stream);                 \
+    if (b_mn) return launch_gemm<BN_, false, true, 0>(tmA, tmB, tmC, p, stream);   \
+    return launch_gemm<BN_, false, false, 0>(tmA, tmB, tmC, p, stream);            \
   }
   if (bn == 256) { MSB_DISPATCH(256) } else { MSB_DISPATCH(128) }
 #undef MSB_DISPATCH
@@ -521,13 +655,21 @@ MSB_EXPORT int msb_gemm_rs(const void* A, const void* B, const unsigned long lon
   p.world = world; p.rank = rank; p.rows_per_rank = M / world;
   for (int i = 0; i < world; ++i) p.rs_peer[i] = reinterpret_cast<void*>(stage_ptrs[i]);
   p.C = p.rs_peer[rank];
+  CMaps tmC = {};
+  int all_ok = 1;
+  for (int i = 0; i < world; ++i) {
+    int ok = 0;
+    if (int rc = encode_output(&tmC.m[i], p.rs_peer[i], M, N, 1, N, 0, 0, &ok)) return rc;
+    all_ok &= ok;
+  }
+  p.tma_epilogue = all_ok;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (bn == 256) {
-    if (b_mn) return launch_gemm<256, false, true, 1>(tmA, tmB, p, stream);
-    return launch_gemm<256, false, false, 1>(tmA, tmB, p, stream);
+    if (b_mn) return launch_gemm<256, false, true, 1>(tmA, tmB, tmC, p, stream);
+    return launch_gemm<256, false, false, 1>(tmA, tmB, tmC, p, stream);
   }
-  if (b_mn) return launch_gemm<128, false, true, 1>(tmA, tmB, p, stream);
-  return launch_gemm<128, false, false, 1>(tmA, tmB, p, stream);
+  if (b_mn) return launch_gemm<128, false, true, 1>(tmA, tmB, tmC, p, stream);
+  return launch_gemm<128, false, false, 1>(tmA, tmB, tmC, p, stream);
 }
 
 // AllGather -> MatMul.  C[M,N] = gather(A)[M,K] x B^T (+ bias) where chunk c of the gathered operand is pulled from
@@ -552,10 +694,12 @@ MSB_EXPORT int msb_gemm_ag(const unsigned long long* src_ptrs, void* gathered, i
   p.world = world; p.rank = rank; p.rows_per_rank = M / world;
   for (int i = 0; i < world; ++i) p.ag_src[i] = reinterpret_cast<const void*>(src_ptrs[i]);
   p.ag_dst = gathered; p.ag_flags = flags;
+  CMaps tmC = {};
+  if (int rc = encode_output(&tmC.m[0], C, M, N, 1, ldc, 0, 0, &p.tma_epilogue)) return rc;
   if (bn == 256) {
-    if (b_mn) return launch_gemm<256, false, true, 2>(tmA, tmB, p, stream);
-    return launch_gemm<256, false, false, 2>(tmA, tmB, p, stream);
+    if (b_mn) return launch_gemm<256, false, true, 2>(tmA, tmB, tmC, p, stream);
+    return launch_gemm<256, false, false, 2>(tmA, tmB, tmC, p, stream);
   }
-  if (b_mn) return launch_gemm<128, false, true, 2>(tmA, tmB, p, stream);
-  return launch_gemm<128, false, false, 2>(tmA, tmB, p, stream);
+  if (b_mn) return launch_gemm<128, false, true, 2>(tmA, tmB, tmC, p, stream);
+  return launch_gemm<128, false, false, 2>(tmA, tmB, tmC, p, stream);
 }
