@@ -542,8 +542,15 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CMa
 
 static int pick_bn(int M, int N, int batch, int bn_hint) {
   if (bn_hint == 128 || bn_hint == 256) return bn_hint;
+  if (N <= 128) return 128;
+  // persistent CTAs work through the tiles in rounds of one tile per SM: take the width with the smaller
+  // (rounds x time per tile); a 128-wide tile costs a little more than half of a 256-wide one
+  const long long sms = sm_count();
   const long long t256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256) * batch;
-  return (N <= 128 || t256 < sm_count()) ? 128 : 256;
+  const long long t128 = static_cast<long long>((M + 127) / 128) * ((N + 127) / 128) * batch;
+  const double c256 = static_cast<double>((t256 + sms - 1) / sms);
+  const double c128 = static_cast<double>((t128 + sms - 1) / sms) * 0.56;
+  return c128 < c256 ? 128 : 256;
 }
 
 static int encode_operands(CUtensorMap* tmA, CUtensorMap* tmB, const void* A, const void* B, int M, int N, int K,
