@@ -39,8 +39,10 @@ def parse():
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is marked invalid)")
     ap.add_argument("--global-batch", type=int, default=32)
     ap.add_argument("--seq", type=int, default=4096)
-    ap.add_argument("--model", default="llama2-7b", choices=["llama2-7b", "resnet50"],
-                    help="llama2-7b is the headline; resnet50 is the data-parallel image config (batch 256 per GPU)")
+    ap.add_argument("--model", default="llama2-7b", choices=["llama2-7b", "resnet50", "gpt-2.6b", "moe-8x"],
+                    help="llama2-7b is the headline; resnet50: data-parallel image config (batch 256 per GPU); "
+                         "gpt-2.6b: dp x mp with sharded optimizer; moe-8x: 8-expert top-2 decoder, expert parallel")
+    ap.add_argument("--mp", type=int, default=None, help="gpt-2.6b: model-parallel size (default 4, capped by N)")
     ap.add_argument("--batch-per-gpu", type=int, default=256, help="resnet50 only")
     return ap.parse_args()
 
@@ -210,12 +212,140 @@ def run_resnet(args):
     return 0
 
 
+def run_gpt_family(args):
+    """GPT-style decoders built from ``parallel.transformer``:
+    gpt-2.6b : 32 layers, hidden 2560, 32 heads, GELU FFN 10240, vocab 40000, seq 1024, global batch 64, AdamW;
+               data parallel x model parallel (mp = 4 when N >= 4) with the sharded (ZeRO-style) optimizer.
+    moe-8x   : 24 layers, hidden 4096, 32 heads, 8 experts (SwiGLU FFN 14336) top-2, capacity factor 1.25,
+               vocab 32000, seq 2048, global batch 32; expert parallel = data parallel = N."""
+    import torch
+    import mindspore_b200 as ms
+    from mindspore_b200 import _native, nn
+    from mindspore_b200.communication import management as M
+    from mindspore_b200.models.gpt import GPTConfig, GPTForCausalLM
+    from mindspore_b200.parallel.moe import MoEConfig
+    from mindspore_b200.parallel.transformer import TransformerOpParallelConfig
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    ms.set_context(mode=ms.PYNATIVE_MODE, device_target="GPU", device_id=local_rank)
+    if world > 1:
+        from mindspore_b200.communication import init
+        init("nccl")
+        ms.set_auto_parallel_context(parallel_mode="semi_auto_parallel", device_num=world, global_rank=rank,
+                                     enable_parallel_optimizer=True)
+    ms.set_seed(1234)
+    moe = args.model == "moe-8x"
+    if moe:
+        mp, dp = 1, world
+        pc = TransformerOpParallelConfig(data_parallel=dp, model_parallel=1, expert_parallel=dp, vocab_emb_dp=True)
+        cfg = GPTConfig(seq_length=2048, vocab_size=32000, hidden_size=4096, num_layers=args.layers or 24,
+                        num_heads=32, ffn_hidden_size=14336, hidden_act="swiglu", parallel_config=pc,
+                        moe_config=MoEConfig(expert_num=8, capacity_factor=1.25, num_experts_chosen=2))
+        global_batch, seq = 32, 2048
+    else:
+        mp = args.mp or (4 if world >= 4 else world)
+        dp = world // mp
+        pc = TransformerOpParallelConfig(data_parallel=dp, model_parallel=mp, vocab_emb_dp=False)
+        cfg = GPTConfig(seq_length=1024, vocab_size=40000, hidden_size=2560, num_layers=args.layers or 32,
+                        num_heads=32, ffn_hidden_size=10240, parallel_config=pc)
+        global_batch, seq = 64, 1024
+    net = GPTForCausalLM(cfg)
+    g = pc.groups()
+    opt = nn.AdamWeightDecay(net.trainable_params(), learning_rate=1e-4, beta1=0.9, beta2=0.95, eps=1e-8,
+                             weight_decay=0.1, max_grad_norm=1.0)
+    if mp > 1:
+        opt.set_model_parallel_group(g["tp"].name)
+    if dp > 1:
+        opt.set_data_parallel_group(g["dp"], mean=True, shard=not moe)
+    per_rank = global_batch // dp
+    micro = per_rank                               # micro-batch 1 sequence
+    step_cell = nn.TrainOneStepCell(nn.GradAccumulationCell(net, micro), opt)
+    step_cell.set_train()
+    dev = torch.device("cuda", local_rank)
+    gen = torch.Generator().manual_seed(99 + rank // mp)
+
+    def host_batch():
+        return torch.randint(0, cfg.vocab_size, (per_rank, seq + 1), dtype=torch.int32, generator=gen).pin_memory()
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    tokens_per_step = global_batch * seq
+    dev_tokens = host_batch().to(dev)
+    for _ in range(args.warmup):
+        step_cell(dev_tokens)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = _native.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step_cell(dev_tokens)
+    e1.record()
+    barrier()
+    dev_ms = e0.elapsed_time(e1)
+    launches = _native.launch_count - launches0
+    batches = [host_batch() for _ in range(args.steps)]
+    h2d = batches[0].numel() * batches[0].element_size()
+    barrier()
+    t0 = time.perf_counter()
+    e0.record()
+    last = None
+    for b in batches:
+        out = step_cell(ms.Tensor(b.to(dev, non_blocking=True)))
+        last = float(out.float().cpu())
+    e1.record()
+    barrier()
+    e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1000)
+    clocks = sampler.stop()
+    if world > 1:
+        t = torch.tensor([dev_ms, e2e_ms], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        dev_ms, e2e_ms = float(t[0]), float(t[1])
+    status = _native.device_status()
+    if rank == 0:
+        ms_per_step = dev_ms / args.steps
+        value = tokens_per_step / (ms_per_step / 1000)
+        name = args.model if not args.layers else "%s-truncated-%dL-INVALID" % (args.model, args.layers)
+        print(json.dumps({
+            "metric": "%s training throughput (tokens/s, max over ranks)" % args.model,
+            "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms_per_step, 2), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"model": name, "layers": cfg.num_layers, "hidden": cfg.hidden_size, "heads": cfg.num_heads,
+                       "ffn": cfg.ffn_hidden_size, "vocab": cfg.vocab_size, "global_batch": global_batch,
+                       "micro_batch": 1, "seq_len": seq,
+                       "parallelism": ("ep%d (dp%d)" % (dp, dp)) if moe else "dp%d x mp%d + sharded optimizer" % (dp, mp),
+                       "optimizer": "AdamW fp32 master + moments, grad clip 1.0",
+                       "l2": "weights and activations of a step far exceed the 126 MB L2 (no flush needed)"},
+            "clocks": clocks,
+            "e2e": {"value": round(tokens_per_step / (e2e_ms / args.steps / 1000), 1), "unit": "tokens/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches,
+            "model_tflops_per_gpu": round(cfg.flops_per_token(seq) * value / world / 1e12, 1),
+            "final_loss": last, "device_status": status,
+            "max_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)}), flush=True)
+    if world > 1:
+        torch.distributed.barrier()
+        M.release()
+    return 0
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         return run_reference(args)
     if args.model == "resnet50":
         return run_resnet(args)
+    if args.model in ("gpt-2.6b", "moe-8x"):
+        return run_gpt_family(args)
 
     import torch
     import mindspore_b200 as ms
