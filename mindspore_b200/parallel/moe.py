@@ -337,7 +337,8 @@ class MoE(Cell):
         self.ep_rank = self.group.ranks.index(M.get_rank()) if self.group is not None else 0
         up = ffn_hidden_size * (2 if hidden_act == "swiglu" else 1)
         mk = lambda shape, name, init="normal": Parameter(initializer(init, shape, param_init_type), name=name)
-        self.router_weight = Parameter(initializer("normal", (self.E, hidden_size), torch.float32),
+        # stored in the model's dtype (one optimizer arena, fp32 master there); the logits are computed in fp32
+        self.router_weight = Parameter(initializer("normal", (self.E, hidden_size), param_init_type),
                                        name="router.dense.weight")
         self.w1 = mk((self.EL, hidden_size, up), "ffn.mapping.weight")
         self.w2 = mk((self.EL, ffn_hidden_size, hidden_size), "ffn.projection.weight")
@@ -371,7 +372,7 @@ class MoE(Cell):
         shape = x.shape
         tokens = x.reshape(-1, shape[-1]).as_subclass(torch.Tensor)
         T = tokens.shape[0]
-        logits = torch.nn.functional.linear(tokens.float(), self.router_weight.as_subclass(torch.Tensor))
+        logits = torch.nn.functional.linear(tokens.float(), self.router_weight.as_subclass(torch.Tensor).float())
         capacity = calculate_expert_capacity(self.k, T, self.cfg.capacity_factor, self.E)
         if tokens.is_cuda:
             capacity = (capacity + 7) // 8 * 8         # rows per expert stay a multiple of the GEMM granule
