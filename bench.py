@@ -230,7 +230,9 @@ def run_gpt_family(args):
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
-    ms.set_context(mode=ms.PYNATIVE_MODE, device_target="GPU", device_id=local_rank)
+    # sequences of 1-2k tokens make every kernel short: the micro-batch is replayed as a CUDA graph
+    use_graph = os.environ.get("MSB200_CUDA_GRAPH", "1") != "0"
+    ms.set_context(mode=ms.PYNATIVE_MODE, device_target="GPU", device_id=local_rank, enable_cuda_graph=use_graph)
     if world > 1:
         from mindspore_b200.communication import init
         init("nccl")
@@ -323,7 +325,7 @@ def run_gpt_family(args):
                        "ffn": cfg.ffn_hidden_size, "vocab": cfg.vocab_size, "global_batch": global_batch,
                        "micro_batch": 1, "seq_len": seq,
                        "parallelism": ("ep%d (dp%d)" % (dp, dp)) if moe else "dp%d x mp%d + sharded optimizer" % (dp, mp),
-                       "optimizer": "AdamW fp32 master + moments, grad clip 1.0",
+                       "optimizer": "AdamW fp32 master + moments, grad clip 1.0", "cuda_graph": use_graph,
                        "l2": "weights and activations of a step far exceed the 126 MB L2 (no flush needed)"},
             "clocks": clocks,
             "e2e": {"value": round(tokens_per_step / (e2e_ms / args.steps / 1000), 1), "unit": "tokens/s",
@@ -334,6 +336,11 @@ def run_gpt_family(args):
             "max_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)}), flush=True)
     if world > 1:
         torch.distributed.barrier()
+        torch.cuda.synchronize()
+        if use_graph:
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)        # graphs hold NCCL kernels: leave without running either destructor
         M.release()
     return 0
 

@@ -243,7 +243,9 @@ class _KernelTransport:
         _native.check(rc, "moe_scatter_rows")
         _count()
         self._barrier()                                      # every source has stored its rows
-        return buf.view(self.EL, self.ep, self.C, H)
+        out = buf.view(self.EL, self.ep, self.C, H)
+        # the symmetric buffer is recycled two operations later, but backward still needs these rows: hand out a copy
+        return out.clone() if self.symm is not None else out
 
     def gather(self, buf, scale, expert, slot, g=None, want_out=True):
         T, K = expert.shape
