@@ -78,7 +78,14 @@ class SymmContext:
 
     def _alloc_raw(self, nbytes):
         nbytes = (nbytes + 255) // 256 * 256
-        t = self.symm_mem.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+        dev = torch.device("cuda", torch.cuda.current_device())
+        try:
+            t = self.symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
+        except RuntimeError:
+            # symmetric memory comes straight from the driver: blocks cached by the tensor allocator but not in use
+            # (initialisation temporaries) are invisible to it - release them and try once more
+            torch.cuda.empty_cache()
+            t = self.symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
         hdl = self.symm_mem.rendezvous(t, group=self.group_name)
         ptrs = [int(p) for p in hdl.buffer_ptrs]
         return t, ptrs
