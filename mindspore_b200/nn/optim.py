@@ -337,6 +337,24 @@ class Optimizer(Cell):
         self._sumsq.zero_()
         self._nonfinite.zero_()
         group = getattr(self, "_mp_group", None)
+        dp = getattr(self, "_dp", None)
+        if group is None and dp is not None and dp.local_only and not dp.shard:
+            # parameters that differ per data-parallel rank (expert shards): their squared norms add up over the
+            # group, the replicated rest counts once - every rank ends with the same global norm
+            from ..communication import comm_func as CF
+            part = torch.zeros_like(self._sumsq)
+            pos = 0
+            for s, e in sorted(dp.local_only):
+                if s > pos:
+                    K.sumsq_finite(arena.grads[pos:s], self._sumsq, self._nonfinite)
+                K.sumsq_finite(arena.grads[s:e], part, self._nonfinite)
+                pos = e
+            if pos < arena.total:
+                K.sumsq_finite(arena.grads[pos:arena.total], self._sumsq, self._nonfinite)
+            CF._all_reduce_(part, "sum", dp.group)
+            CF._all_reduce_(self._nonfinite, "max", dp.group)
+            self._sumsq.add_(part)
+            return
         if group is None:
             K.sumsq_finite(arena.grads, self._sumsq, self._nonfinite)
             return

@@ -33,6 +33,7 @@ _native.register_cuda_signature("msb_reduce_scatter_symm", _I, [_U64P, _I, _I, _
 _native.register_cuda_signature("msb_adamw_allgather", _I, [_P, _P, _P, _P, _U64P, _I, _L, _L, _P, _P, _P])
 
 _SLICE_ALIGN = 128
+_BUCKET_ELEMS = 64 * 1024 * 1024      # 256 MB of fp32 gradients per all-reduce bucket
 
 
 def _ptr_array(ptrs):
@@ -94,20 +95,35 @@ class DataParallelArena:
 
     # ------------------------------------------------------------------ plain data parallel
     def allreduce(self):
-        """All-reduce (mean) of the whole gradient arena, leaving per-rank parameters un-reduced."""
+        """All-reduce (mean) of the gradient arena in buckets (``_BUCKET_ELEMS`` fp32 elements each, so the
+        symmetric staging buffer stays small), leaving per-rank parameters (expert shards) un-reduced: those are
+        only scaled."""
         if self.world == 1:
             return
         arena, scale = self.arena, (1.0 / self.world if self.mean else 1.0)
-        keep = [(s, e, arena.grads[s:e].clone()) for s, e in self.local_only]
+        if getattr(self, "_reduce_ranges", None) is None:
+            ranges, pos = [], 0
+            for s, e in sorted(self.local_only):
+                if s > pos:
+                    ranges.append((pos, s))
+                pos = max(pos, (e + _SLICE_ALIGN - 1) // _SLICE_ALIGN * _SLICE_ALIGN)
+            if pos < arena.total:
+                ranges.append((pos, arena.total))
+            self._reduce_ranges = [(lo, min(lo + _BUCKET_ELEMS, hi)) for s, hi in ranges
+                                   for lo in range(s, hi, _BUCKET_ELEMS)]
         from . import symm
-        if symm.fused_available(self.group):
-            symm.all_reduce_(arena.grads, self.group, scale)
-        else:
-            CF._all_reduce_(arena.grads, "sum", self.group)
-            if scale != 1.0:
-                arena.grads.mul_(scale)
-        for s, e, g in keep:
-            arena.grads[s:e].copy_(g * scale)
+        fused = symm.fused_available(self.group)
+        for lo, hi in self._reduce_ranges:
+            seg = arena.grads[lo:hi]
+            if fused:
+                symm.all_reduce_(seg, self.group, scale)
+            else:
+                CF._all_reduce_(seg, "sum", self.group)
+                if scale != 1.0:
+                    seg.mul_(scale)
+        if scale != 1.0:
+            for s, e in self.local_only:
+                arena.grads[s:e].mul_(scale)
 
     # ------------------------------------------------------------------ sharded step
     def _ranges_in_slice(self, ranges):
