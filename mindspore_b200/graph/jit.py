@@ -66,6 +66,8 @@ class _Recorder(TorchFunctionMode):
     # ---- value <-> node mapping
     def bind(self, value, node):
         if _is_tensor(value):
+            node.meta.setdefault("shape", tuple(value.shape))
+            node.meta.setdefault("dtype", value.dtype)
             self.node_of[id(value)] = node
             k = self._akey(value)
             if k is not None:
@@ -89,6 +91,8 @@ class _Recorder(TorchFunctionMode):
                 n = self.alias[k]
             else:
                 n = self.fg.const_node(a)
+            n.meta.setdefault("shape", tuple(a.shape))
+            n.meta.setdefault("dtype", a.dtype)
             self.node_of[id(a)] = n
             if k is not None and k not in self.alias:
                 self.alias[k] = n
@@ -287,7 +291,30 @@ class CompiledGraph:
         return self.executor.run(tensors)
 
 
+def _search_strategies(fn, inputs, kwargs, name, owner):
+    """auto_parallel: one trace on full shapes (parallel mode switched off), then the strategy search writes
+    ``in_strategy`` onto the primitives that the real trace will dispatch."""
+    from ..context import _AutoParallelContext
+    from ..parallel import auto_parallel
+    store = _AutoParallelContext()._v
+    mode = store["parallel_mode"]
+    snapshot = _snapshot_state(owner)
+    store["parallel_mode"] = context.ParallelMode.STAND_ALONE
+    try:
+        fg0, _ = trace_callable(lambda *a: fn(*a, **kwargs), inputs, name + "_shapes")
+    finally:
+        store["parallel_mode"] = mode
+        _restore_state(snapshot)
+    devices = store["device_num"] // max(1, store["pipeline_stages"])
+    chosen = auto_parallel.search(fg0, devices, store.get("search_mode", "sharding_propagation"))
+    if owner is not None:
+        object.__setattr__(owner, "_searched_strategies", chosen)
+    return chosen
+
+
 def _compile(fn, inputs, kwargs, name, owner=None):
+    if context.get_auto_parallel_context("parallel_mode") == context.ParallelMode.AUTO_PARALLEL:
+        _search_strategies(fn, inputs, kwargs, name, owner)
     snapshot = _snapshot_state(owner)
     fg, out = trace_callable(lambda *a: fn(*a, **kwargs), inputs, name)
     _restore_state(snapshot)   # tracing really executed one step; roll parameters / optimizer state back

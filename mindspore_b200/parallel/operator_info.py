@@ -175,8 +175,30 @@ class OperatorInfo:
           "SquaredDifference", "Xdivy", "Xlogy", "BitwiseAnd", "BitwiseOr", "BitwiseXor", "Select", "MaskedFill",
           "AddN", "Lerp", "Addcmul", "Addcdiv", "BiasAdd", "TruncateDiv", "TruncateMod", "DivNoNan", "MulNoNan",
           "Hypot", "ApproximateEqual")
+def _elementwise_strategies(shape, device_num, limit=64):
+    """Every way to split the dims of ``shape`` by divisors of ``device_num`` (product dividing ``device_num``)."""
+    out = []
+
+    def rec(i, cur, prod):
+        if len(out) >= limit:
+            return
+        if i == len(shape):
+            out.append(tuple(cur))
+            return
+        for d in _divisors(device_num):
+            if prod * d > device_num or device_num % (prod * d) or shape[i] % d:
+                continue
+            rec(i + 1, cur + [d], prod * d)
+    rec(0, [], 1)
+    return out
+
+
 class ArithmeticInfo(OperatorInfo):
-    pass
+    @classmethod
+    def generate_strategies(cls, in_shapes, device_num):
+        if in_shapes and all(tuple(s) == tuple(in_shapes[0]) for s in in_shapes):
+            return [tuple(st for _ in in_shapes) for st in _elementwise_strategies(in_shapes[0], device_num)]
+        return super().generate_strategies(in_shapes, device_num)
 
 
 @register("ReLU", "ReLU6", "Sigmoid", "Tanh", "GeLU", "FastGeLU", "SiLU", "Mish", "Softplus", "Softsign", "Abs",
@@ -187,7 +209,11 @@ class ArithmeticInfo(OperatorInfo):
           "Dropout", "Lgamma", "Digamma", "BesselI0", "BesselI0e", "BesselI1", "BesselI1e", "Sinc", "Logit",
           "_VirtualDiv", "_VirtualOutput", "_MirrorOperator", "AShardIdentity")
 class ActivationInfo(OperatorInfo):
-    pass
+    @classmethod
+    def generate_strategies(cls, in_shapes, device_num):
+        if len(in_shapes) == 1:
+            return [(st,) for st in _elementwise_strategies(in_shapes[0], device_num)]
+        return super().generate_strategies(in_shapes, device_num)
 
 
 @register("MatMul", "BatchMatMul")

@@ -32,10 +32,13 @@ def _prim(node):
 
 
 def _example_bytes(node):
-    ex = node.meta.get("example")
-    if isinstance(ex, torch.Tensor):
-        return ex.numel() * ex.element_size()
-    return 0
+    shape, dtype = node.meta.get("shape"), node.meta.get("dtype")
+    if shape is None or dtype is None:
+        return 0
+    n = 1
+    for d in shape:
+        n *= d
+    return n * torch.empty(0, dtype=dtype).element_size()
 
 
 def comm_nodes(fg):
