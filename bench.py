@@ -3,7 +3,7 @@
     python bench.py --gpus N --steps K --warmup W            (N > 1: launched by torch.distributed.run)
     python bench.py --impl reference ...                     (the reference arm)
 
-Config (BASELINE.json): Llama-2-7B-shaped decoder - 32 layers, hidden 4096, 32 heads, RMSNorm, RoPE, SwiGLU FFN
+Config: Llama-2-7B-shaped decoder - 32 layers, hidden 4096, 32 heads, RMSNorm, RoPE, SwiGLU FFN
 11008, vocab 32000, seq 4096 - semi_auto_parallel with model_parallel = N and sequence parallelism, bf16 compute
 with fp32 master weights and AdamW; micro-batch 1, global batch 32 (32 accumulated micro-batches per optimizer
 step), synthetic uniform-random token ids with shifted labels, random-init weights.  One "step" is one optimizer

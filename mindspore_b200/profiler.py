@@ -142,7 +142,7 @@ def _main(argv=None):
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--layers", type=int, default=4, help="llama: number of layers (7B shapes)")
-    ap.add_argument("--out", default="./gpurun_out/prof")
+    ap.add_argument("--out", default="./profiler_out")
     args = ap.parse_args(argv)
     import mindspore_b200 as ms
     from mindspore_b200 import nn
