@@ -52,6 +52,7 @@ _CUDA_SIGNATURES = {
     "msb_last_error": (ctypes.c_char_p, []),
     "msb_read_status": (_I, [_I]),
     "msb_gemm_bf16": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _I, _I, _F, _I, _P]),
+    "msb_gemm_bf16_pair": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _L, _I, _I, _F, _I, _P, _P]),
     "msb_rmsnorm_fwd": (_I, [_P, _P, _P, _P, _P, _P, _L, _I, _F, _P]),
     "msb_rmsnorm_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _L, _I, _P]),
     "msb_layernorm_fwd": (_I, [_P, _P, _P, _P, _P, _P, _L, _I, _F, _P]),

@@ -9,6 +9,7 @@ call these, so the set of functions in this file is the GPU op inventory.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -31,6 +32,20 @@ def _count(n=1):
 
 
 # --------------------------------------------------------------------------------------- GEMM
+_PAIR_GEMM = os.environ.get("MSB200_GEMM_PAIR", "0") == "1"
+
+
+def _pair_gemm_ok(M, N, K, batch, out, o2, accumulate, bn_hint):
+    """The CTA-pair kernel (256 x 256 tiles on two SMs) takes un-batched problems whose output meets the TMA
+    alignment rules and that fill the machine with 256-wide tiles."""
+    if not _PAIR_GEMM or batch != 1 or bn_hint not in (0, 512):
+        return False
+    es = out.element_size()
+    if out.data_ptr() % 16 or (o2.stride(0) * es) % 16 or (accumulate and out.dtype != f32):
+        return False
+    return M >= 512 and N >= 512 and ((M + 255) // 256) * ((N + 255) // 256) >= 64
+
+
 def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=bf16, accumulate=False, bias=None,
          alpha=1.0, bn_hint=0):
     """``C (+)= alpha * A @ B^T (+ bias)`` on tcgen05 tensor cores.
@@ -69,6 +84,13 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=bf16, accumulate=F
         assert not accumulate
     o2 = out[0] if batched else out
     assert o2.stride(1) == 1 and o2.shape == (M, N)
+    if _pair_gemm_ok(M, N, K, batch, out, o2, accumulate, bn_hint):
+        rc = _native.cuda().msb_gemm_bf16_pair(_p(a), _p(b), _p(out), _p(bias), M, N, K, int(a_mn), int(b_mn), lda, ldb,
+                                               o2.stride(0), int(out.dtype == f32), int(accumulate), float(alpha), 2,
+                                               None, _stream())
+        _native.check(rc, "gemm_pair")
+        _count()
+        return out
     rc = _native.cuda().msb_gemm_bf16(
         _p(a), _p(b), _p(out), _p(bias), M, N, K, batch, int(a_mn), int(b_mn), lda, ldb, o2.stride(0),
         abs_, bbs_, out.stride(0) if batched else 0, int(out.dtype == f32), int(accumulate), float(alpha),
