@@ -2,4 +2,5 @@
 / ``take`` / ``skip`` / ``zip``, iterators) and record files."""
 from .engine import (Dataset, GeneratorDataset, MindDataset, NumpySlicesDataset, RandomDataset, config, zip)  # noqa: A004
 from .mindrecord import FileReader, FileWriter
+from .native_loader import NativeBatchLoader
 from . import transforms, vision
