@@ -18,6 +18,7 @@ import torch.distributed as dist
 
 from ..common.tensor import Tensor
 from ..ops.primitive import _wrap_out
+from ..utils import recorder as _recorder
 from . import management as M
 
 _REDUCE = {"sum": dist.ReduceOp.SUM, "prod": dist.ReduceOp.PRODUCT, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}
@@ -45,9 +46,15 @@ def _single(g):
 
 
 # ------------------------------------------------------------------------------------ raw (non-differentiable)
+def _rec(name, t, g):
+    if _recorder.enabled():
+        _recorder.record("collective", "%s %s" % (name, g.name), t.numel() * t.element_size(), g.size)
+
+
 def _all_reduce_(t, op, g):
     if M.is_simulation() or _single(g):
         return t
+    _rec("AllReduce", t, g)
     dist.all_reduce(t, _op(op), group=g.pg)
     return t
 
@@ -58,6 +65,7 @@ def _all_gather(t, g):
     if M.is_simulation() or _single(g):
         out.view(n, *t.shape).copy_(t.unsqueeze(0).expand(n, *t.shape))
         return out
+    _rec("AllGather", t, g)
     dist.all_gather_into_tensor(out, t.contiguous(), group=g.pg)
     return out
 
@@ -71,6 +79,7 @@ def _reduce_scatter(t, op, g):
         r = 0 if M.is_simulation() else 0
         out.copy_(t[r * out.shape[0]:(r + 1) * out.shape[0]])
         return out
+    _rec("ReduceScatter", t, g)
     dist.reduce_scatter_tensor(out, t.contiguous(), _op(op), group=g.pg)
     return out
 
@@ -81,6 +90,7 @@ def _all_to_all(t, split_dim, concat_dim, g):
     if M.is_simulation() or _single(g):
         return torch.cat(chunks, dim=concat_dim)
     outs = [torch.empty_like(c) for c in chunks]
+    _rec("AlltoAll", t, g)
     if g.pg is not None and dist.get_backend(g.pg) == "gloo":
         # gloo has no all_to_all: emulate with all_gather of the full tensor list
         gathered = [torch.empty_like(t) for _ in range(n)]

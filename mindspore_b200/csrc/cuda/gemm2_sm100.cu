@@ -27,7 +27,10 @@ constexpr int k2BM = 128;        // rows per CTA (tile M = 256)
 constexpr int k2BN = 256;        // tile N (each CTA stages 128 of them)
 constexpr int k2BK = 64;
 constexpr int k2Threads = 192;
-constexpr int k2Stages = 6;
+#ifndef MSB_K2_STAGES
+#define MSB_K2_STAGES 6
+#endif
+constexpr int k2Stages = MSB_K2_STAGES;
 constexpr int k2ABytes = k2BM * k2BK * 2;          // 16 KB
 constexpr int k2BBytes = (k2BN / 2) * k2BK * 2;    // 16 KB
 constexpr int k2StageBytes = k2ABytes + k2BBytes;
@@ -43,6 +46,7 @@ struct Gemm2Params {
   int M, N, K;
   int out_fp32, accumulate;
   float alpha;
+  int debug_lazy;     // experiment: release the stages of a tile with one burst of commits at its end
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -72,7 +76,11 @@ __device__ __forceinline__ bool mbar_test_cluster(uint64_t* bar, uint32_t parity
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
+#ifdef MSB_K2_CTA_ACQ
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+#else
       "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+#endif
       "selp.b32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
@@ -280,9 +288,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                                           : umma_smem_desc(b_addr + kk * 32, 16, 1024);
               umma2_bf16(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0);
             }
-            umma2_commit_pair(&empty_bar[s]);
+            if (!(p.debug_lazy && num_kb == k2Stages)) umma2_commit_pair(&empty_bar[s]);
             if (++s == k2Stages) { s = 0; ph ^= 1; }
           }
+          if (ok && p.debug_lazy && num_kb == k2Stages)
+            for (int e = 0; e < k2Stages; ++e) umma2_commit_pair(&empty_bar[e]);
           if (ok) umma2_commit_pair(&tfull_bar[acc]);
         }
       } else {
@@ -433,6 +443,26 @@ static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CU
   const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
   int pairs = max_pairs;
   if (tiles < pairs) pairs = tiles;
+#ifdef MSB_K2_POLICY
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(k2Threads, 1, 1);
+    cfg.dynamicSmemBytes = k2SmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = 2;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    attrs[1].id = cudaLaunchAttributeClusterSchedulingPolicyPreference;
+    attrs[1].val.clusterSchedulingPolicyPreference = static_cast<cudaClusterSchedulingPolicy>(MSB_K2_POLICY);
+    cfg.attrs = attrs;
+    cfg.numAttrs = 2;
+    MSB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, p));
+    return kOk;
+  }
+#endif
   kern<<<2 * pairs, k2Threads, k2SmemBytes, stream>>>(tmA, tmB, tmC, p);
   MSB_CUDA_CHECK(cudaGetLastError());
   return kOk;
@@ -445,6 +475,8 @@ static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CU
 MSB_EXPORT int msb_gemm_bf16_pair(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
                                   int a_mn, int b_mn, long long lda, long long ldb, long long ldc, int out_fp32,
                                   int accumulate, float alpha, int acc_buffers, int* debug, void* stream_) {
+  const int debug_lazy = acc_buffers >= 10;
+  if (debug_lazy) acc_buffers -= 10;
   if (M <= 0 || N <= 0 || K <= 0) { set_last_error("gemm_pair: empty problem"); return kBadArg; }
   if ((lda % 8) || (ldb % 8)) { set_last_error("gemm_pair: operand pitches must be multiples of 8"); return kBadArg; }
   const int es = out_fp32 ? 4 : 2;
@@ -457,6 +489,7 @@ MSB_EXPORT int msb_gemm_bf16_pair(const void* A, const void* B, void* C, const v
   p.bias = bias; p.status = status_ptr(); p.debug = debug;
   if (!p.status) { set_last_error("gemm_pair: no status word"); return kCudaError; }
   p.M = M; p.N = N; p.K = K; p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
+  p.debug_lazy = debug_lazy;
   CUtensorMap tmA, tmB, tmC;
   int rc;
   if (a_mn) rc = encode_tmap_3d(&tmA, A, 2, M, K, 1, lda * 2, (uint64_t)lda * 2 * K, 64, 64, 1);

@@ -16,6 +16,7 @@ from ..common.parameter import Parameter, ParameterTuple
 from ..common.tensor import Tensor
 from ..ops import composite as C
 from ..ops.primitive import _wrap_out
+from ..utils import recorder as _recorder
 from .cell import Cell
 
 
@@ -231,6 +232,10 @@ class TrainOneStepCell(Cell):
         return loss.detach()
 
     def construct(self, *inputs):
+        if _recorder.enabled():
+            self._rdr_step = getattr(self, "_rdr_step", 0) + 1
+            _recorder.set_step(self._rdr_step)
+            _recorder.record("step", "begin " + type(self.network).__name__)
         if self.use_arena:
             return _wrap_out(self._arena_step(inputs))
         if isinstance(self.network, PipelineCell) and not isinstance(self.network, GradAccumulationCell) and \
