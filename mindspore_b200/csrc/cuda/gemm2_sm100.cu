@@ -9,8 +9,10 @@
 // a 128 x 256 tile, so the ring holds six stages instead of four.
 //
 // Synchronisation (every wait is bounded; a wait that runs out sets the status word and the CTA leaves):
-//   full[s]      : own TMA loads of stage s have landed (each CTA, local)
-//   peer_full[s] : in the leader; the partner's relay thread arrives when the partner's loads of stage s have landed
+//   full[s]      : in the leader; the TMA loads of BOTH CTAs count their bytes on it (.cta_group::2 loads may signal
+//                  a barrier of the partner CTA), so the MMA thread waits once per stage.  A first version had the
+//                  partner forward "my half has landed" with mbarrier.arrive.release.cluster from a relay thread;
+//                  the release fence cost ~1 us per k-block and halved the throughput (660 vs 1230 TFLOP/s at 8192^3).
 //   empty[s]     : in both CTAs; tcgen05.commit of the leader (multicast to the pair) releases the stage
 //   tfull[a]     : in both CTAs; commit after the last k-block: accumulator a is complete
 //   tempty[a]    : in the leader; 256 arrivals - the 128 epilogue threads of each CTA have drained accumulator a
@@ -27,10 +29,7 @@ constexpr int k2BM = 128;        // rows per CTA (tile M = 256)
 constexpr int k2BN = 256;        // tile N (each CTA stages 128 of them)
 constexpr int k2BK = 64;
 constexpr int k2Threads = 192;
-#ifndef MSB_K2_STAGES
-#define MSB_K2_STAGES 6
-#endif
-constexpr int k2Stages = MSB_K2_STAGES;
+constexpr int k2Stages = 6;
 constexpr int k2ABytes = k2BM * k2BK * 2;          // 16 KB
 constexpr int k2BBytes = (k2BN / 2) * k2BK * 2;    // 16 KB
 constexpr int k2StageBytes = k2ABytes + k2BBytes;
@@ -46,7 +45,6 @@ struct Gemm2Params {
   int M, N, K;
   int out_fp32, accumulate;
   float alpha;
-  int debug_lazy;     // experiment: release the stages of a tile with one burst of commits at its end
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -76,11 +74,7 @@ __device__ __forceinline__ bool mbar_test_cluster(uint64_t* bar, uint32_t parity
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-#ifdef MSB_K2_CTA_ACQ
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-#else
       "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
-#endif
       "selp.b32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
@@ -140,6 +134,17 @@ __device__ __forceinline__ void umma2_commit_pair(uint64_t* bar) {
       "h"(mask)
       : "memory");
 }
+// 3-D tiled load into this CTA's shared memory whose bytes are counted on the mbarrier at `bar_cluster_addr`, an
+// address in the cluster window: with .cta_group::2 that barrier may live in the partner CTA, so both halves of a
+// stage complete on the leader's barrier and no thread has to forward "my half has landed".
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* tmap, uint32_t bar_cluster_addr,
+                                                 int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 __device__ __forceinline__ void tma_store_3d_2(const CUtensorMap* tmap, const void* smem_src, int x, int y, int z) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
                    reinterpret_cast<uint64_t>(tmap)),
@@ -163,8 +168,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + k2Stages * k2ABytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + k2BarOffset);
-  uint64_t* peer_full_bar = full_bar + k2Stages;
-  uint64_t* empty_bar = peer_full_bar + k2Stages;
+  uint64_t* empty_bar = full_bar + k2Stages;
   uint64_t* tfull_bar = empty_bar + k2Stages;     // [2]
   uint64_t* tempty_bar = tfull_bar + 2;           // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
@@ -187,7 +191,6 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   if (threadIdx.x == 0) {
     for (int s = 0; s < k2Stages; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&peer_full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -238,21 +241,23 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int n0 = n_blk * k2BN + static_cast<int>(rank) * (k2BN / 2);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_cluster(&empty_bar[s], ph ^ 1, ab)) { ok = false; break; }
-          mbar_expect_tx(&full_bar[s], k2StageBytes);
+          // both CTAs' bytes are counted on the leader's barrier; only the leader announces them
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * k2StageBytes);
+          const uint32_t bar = map_to_rank(smem_u32(&full_bar[s]), 0);
           uint8_t* a_dst = smem_a + s * k2ABytes;
           uint8_t* b_dst = smem_b + s * k2BBytes;
           const int k0 = kb * k2BK;
           if (A_MN) {
 #pragma unroll
-            for (int j = 0; j < k2BM / 64; ++j) tma_load_3d(a_dst + j * 8192, &tmA, &full_bar[s], m0 + 64 * j, k0, 0);
+            for (int j = 0; j < k2BM / 64; ++j) tma_load_3d_pair(a_dst + j * 8192, &tmA, bar, m0 + 64 * j, k0, 0);
           } else {
-            tma_load_3d(a_dst, &tmA, &full_bar[s], k0, m0, 0);
+            tma_load_3d_pair(a_dst, &tmA, bar, k0, m0, 0);
           }
           if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < k2BN / 128; ++j) tma_load_3d(b_dst + j * 8192, &tmB, &full_bar[s], n0 + 64 * j, k0, 0);
+            for (int j = 0; j < k2BN / 128; ++j) tma_load_3d_pair(b_dst + j * 8192, &tmB, bar, n0 + 64 * j, k0, 0);
           } else {
-            tma_load_3d(b_dst, &tmB, &full_bar[s], k0, n0, 0);
+            tma_load_3d_pair(b_dst, &tmB, bar, k0, n0, 0);
           }
           if (++s == k2Stages) { s = 0; ph ^= 1; }
         }
@@ -275,8 +280,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           tc_fence_after_sync();
           const uint32_t d_tmem = tmem_base + acc * k2BN;
           for (int kb = 0; kb < num_kb; ++kb) {
-            if (!mbar_wait(&full_bar[s], ph, ab)) { ok = false; break; }
-            if (!mbar_wait_cluster(&peer_full_bar[s], ph, ab)) { ok = false; break; }
+            if (!mbar_wait(&full_bar[s], ph, ab)) { ok = false; break; }      // both CTAs' halves have landed
             tc_fence_after_sync();
             const uint32_t a_addr = smem_u32(smem_a + s * k2ABytes);
             const uint32_t b_addr = smem_u32(smem_b + s * k2BBytes);
@@ -288,24 +292,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                                           : umma_smem_desc(b_addr + kk * 32, 16, 1024);
               umma2_bf16(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0);
             }
-            if (!(p.debug_lazy && num_kb == k2Stages)) umma2_commit_pair(&empty_bar[s]);
+            umma2_commit_pair(&empty_bar[s]);
             if (++s == k2Stages) { s = 0; ph ^= 1; }
           }
-          if (ok && p.debug_lazy && num_kb == k2Stages)
-            for (int e = 0; e < k2Stages; ++e) umma2_commit_pair(&empty_bar[e]);
           if (ok) umma2_commit_pair(&tfull_bar[acc]);
-        }
-      } else {
-        // ---------------------------------------------------------------- relay (partner CTA): loads landed
-        int s = 0;
-        uint32_t ph = 0;
-        bool ok = true;
-        for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
-          for (int kb = 0; kb < num_kb; ++kb) {
-            if (!mbar_wait(&full_bar[s], ph, ab)) { ok = false; break; }
-            remote_arrive(map_to_rank(smem_u32(&peer_full_bar[s]), 0));
-            if (++s == k2Stages) { s = 0; ph ^= 1; }
-          }
         }
       }
     }
@@ -443,26 +433,6 @@ static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CU
   const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
   int pairs = max_pairs;
   if (tiles < pairs) pairs = tiles;
-#ifdef MSB_K2_POLICY
-  {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * pairs, 1, 1);
-    cfg.blockDim = dim3(k2Threads, 1, 1);
-    cfg.dynamicSmemBytes = k2SmemBytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attrs[2];
-    attrs[0].id = cudaLaunchAttributeClusterDimension;
-    attrs[0].val.clusterDim.x = 2;
-    attrs[0].val.clusterDim.y = 1;
-    attrs[0].val.clusterDim.z = 1;
-    attrs[1].id = cudaLaunchAttributeClusterSchedulingPolicyPreference;
-    attrs[1].val.clusterSchedulingPolicyPreference = static_cast<cudaClusterSchedulingPolicy>(MSB_K2_POLICY);
-    cfg.attrs = attrs;
-    cfg.numAttrs = 2;
-    MSB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, p));
-    return kOk;
-  }
-#endif
   kern<<<2 * pairs, k2Threads, k2SmemBytes, stream>>>(tmA, tmB, tmC, p);
   MSB_CUDA_CHECK(cudaGetLastError());
   return kOk;
@@ -475,8 +445,6 @@ static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CU
 MSB_EXPORT int msb_gemm_bf16_pair(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
                                   int a_mn, int b_mn, long long lda, long long ldb, long long ldc, int out_fp32,
                                   int accumulate, float alpha, int acc_buffers, int* debug, void* stream_) {
-  const int debug_lazy = acc_buffers >= 10;
-  if (debug_lazy) acc_buffers -= 10;
   if (M <= 0 || N <= 0 || K <= 0) { set_last_error("gemm_pair: empty problem"); return kBadArg; }
   if ((lda % 8) || (ldb % 8)) { set_last_error("gemm_pair: operand pitches must be multiples of 8"); return kBadArg; }
   const int es = out_fp32 ? 4 : 2;
@@ -489,7 +457,6 @@ MSB_EXPORT int msb_gemm_bf16_pair(const void* A, const void* B, void* C, const v
   p.bias = bias; p.status = status_ptr(); p.debug = debug;
   if (!p.status) { set_last_error("gemm_pair: no status word"); return kCudaError; }
   p.M = M; p.N = N; p.K = K; p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
-  p.debug_lazy = debug_lazy;
   CUtensorMap tmA, tmB, tmC;
   int rc;
   if (a_mn) rc = encode_tmap_3d(&tmA, A, 2, M, K, 1, lda * 2, (uint64_t)lda * 2 * K, 64, 64, 1);
