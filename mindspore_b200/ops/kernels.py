@@ -32,7 +32,7 @@ def _count(n=1):
 
 
 # --------------------------------------------------------------------------------------- GEMM
-_PAIR_GEMM = os.environ.get("MSB200_GEMM_PAIR", "0") == "1"
+_PAIR_GEMM = os.environ.get("MSB200_GEMM_PAIR", "1") == "1"
 
 
 def _pair_gemm_ok(M, N, K, batch, out, o2, accumulate, bn_hint):

@@ -53,6 +53,25 @@ def test_gemm_layouts(K, a_mn, b_mn, bn, shape):
     _status_ok()
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+def test_gemm_cta_pair(K, a_mn, b_mn):
+    """Problems of at least 64 tiles of 256 x 256 go to the CTA-pair kernel (tcgen05.mma.cta_group::2); ragged M / N
+    edges, a bias, fp32 accumulation into an existing output."""
+    assert K._PAIR_GEMM, "the CTA-pair GEMM is expected to be on by default"
+    M, N, Kd = 2048 + 72, 2048 + 136, 448
+    a = torch.randn((Kd, M) if a_mn else (M, Kd), device=DEV).bfloat16()
+    b = torch.randn((Kd, N) if b_mn else (N, Kd), device=DEV).bfloat16()
+    bias = torch.randn(N, device=DEV).bfloat16()
+    ref = _gemm_ref(a, b, a_mn, b_mn)
+    assert K._pair_gemm_ok(M, N, Kd, 1, torch.empty(M, N, device=DEV, dtype=torch.bfloat16),
+                           torch.empty(M, N, device=DEV, dtype=torch.bfloat16), False, 0)
+    _close(K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias), ref + bias.float())
+    out = torch.randn(M, N, device=DEV)
+    exp = out + 0.5 * ref
+    _close(K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, out_dtype=torch.float32, accumulate=True, alpha=0.5), exp)
+    _status_ok()
+
+
 def test_gemm_batched_accumulate_bias(K):
     a = torch.randn(3, 256, 192, device=DEV).bfloat16()
     b = torch.randn(3, 384, 192, device=DEV).bfloat16()
