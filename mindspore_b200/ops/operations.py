@@ -1344,3 +1344,6 @@ class TopKRouter(Primitive):
 
 
 __all__ = [n for n, v in list(globals().items()) if isinstance(v, type) and issubclass(v, Primitive)]
+
+
+from .operations_ext import *  # noqa: E402,F401,F403  (second-tier primitives)

@@ -170,11 +170,6 @@ class OperatorInfo:
         return cands
 
 
-@register("Add", "Sub", "Mul", "Div", "RealDiv", "Pow", "Maximum", "Minimum", "Equal", "NotEqual", "Greater",
-          "GreaterEqual", "Less", "LessEqual", "LogicalAnd", "LogicalOr", "FloorDiv", "FloorMod", "Mod", "Atan2",
-          "SquaredDifference", "Xdivy", "Xlogy", "BitwiseAnd", "BitwiseOr", "BitwiseXor", "Select", "MaskedFill",
-          "AddN", "Lerp", "Addcmul", "Addcdiv", "BiasAdd", "TruncateDiv", "TruncateMod", "DivNoNan", "MulNoNan",
-          "Hypot", "ApproximateEqual")
 def _elementwise_strategies(shape, device_num, limit=64):
     """Every way to split the dims of ``shape`` by divisors of ``device_num`` (product dividing ``device_num``)."""
     out = []
@@ -193,6 +188,14 @@ def _elementwise_strategies(shape, device_num, limit=64):
     return out
 
 
+@register("Add", "Sub", "Mul", "Div", "RealDiv", "Pow", "Maximum", "Minimum", "Equal", "NotEqual", "Greater",
+          "GreaterEqual", "Less", "LessEqual", "LogicalAnd", "LogicalOr", "FloorDiv", "FloorMod", "Mod", "Atan2",
+          "SquaredDifference", "Xdivy", "Xlogy", "BitwiseAnd", "BitwiseOr", "BitwiseXor", "Select", "MaskedFill",
+          "AddN", "Lerp", "Addcmul", "Addcdiv", "BiasAdd", "TruncateDiv", "TruncateMod", "DivNoNan", "MulNoNan",
+          "Hypot", "ApproximateEqual", "AddExt", "SubExt", "DivMod", "Gcd", "Igamma", "Igammac", "NextAfter",
+          "LeftShift", "RightShift", "Betainc", "Assign", "AssignAdd", "AssignSub", "DropoutDoMask", "KLDivLoss",
+          "SigmoidCrossEntropyWithLogits", "BinaryCrossEntropy", "SmoothL1Loss", "FakeQuantPerLayer",
+          "InplaceAdd", "InplaceSub", "InplaceUpdate", "Zeta")
 class ArithmeticInfo(OperatorInfo):
     @classmethod
     def generate_strategies(cls, in_shapes, device_num):
@@ -207,7 +210,10 @@ class ArithmeticInfo(OperatorInfo):
           "Trunc", "Rint", "Reciprocal", "Inv", "Invert", "LogicalNot", "IsFinite", "IsNan", "IsInf", "Cast",
           "OnesLike", "ZerosLike", "Identity", "StopGradient", "Elu", "LeakyReLU", "HSigmoid", "HSwish", "SeLU",
           "Dropout", "Lgamma", "Digamma", "BesselI0", "BesselI0e", "BesselI1", "BesselI1e", "Sinc", "Logit",
-          "_VirtualDiv", "_VirtualOutput", "_MirrorOperator", "AShardIdentity")
+          "_VirtualDiv", "_VirtualOutput", "_MirrorOperator", "AShardIdentity", "Activation", "BesselJ0", "BesselJ1",
+          "HShrink", "SoftShrink", "ClampScalar", "PopulationCount", "Quant", "QuantV2", "Dequant", "AntiQuant",
+          "L2Loss", "FillV2", "PReLU", "VirtualOutput", "SelfDefineShard", "BroadcastTo", "CumProd", "Cummax",
+          "Cummin", "LinSpace", "LinSpaceExt", "Gamma")
 class ActivationInfo(OperatorInfo):
     @classmethod
     def generate_strategies(cls, in_shapes, device_num):
@@ -624,7 +630,22 @@ class FlashAttentionInfo(OperatorInfo):
 
 @register("BatchParallel", "_VirtualDataset", "GetNext", "TopK", "Sort", "Unique", "CumSum", "ArgMaxWithValue",
           "ArgMinWithValue", "Argmax", "Argmin", "Tile", "ExpandDims", "Squeeze", "Concat", "Split", "StridedSlice",
-          "Slice", "Stack", "ApplyRotaryPosEmb", "Conv2D", "BatchNorm", "MaxPool", "AvgPool")
+          "Slice", "Stack", "ApplyRotaryPosEmb", "Conv2D", "BatchNorm", "MaxPool", "AvgPool", "VirtualDataset",
+          "AvgPool3D", "MaxPool3D", "Conv3D", "Conv2DBackpropInput", "Conv2DTranspose", "Convolution", "GroupNorm",
+          "LayerNormV3", "BatchMatMulExt", "MatMulExt", "BoundingBoxEncode", "BoundingBoxDecode", "CheckValid", "IOU",
+          "Cdist", "Cholesky", "CropAndResize", "ROIAlign", "GridSampler2D", "Custom", "DecoderKVCache",
+          "PromptKVCache", "KVCacheMgr", "KVCacheScatterUpdate", "ReshapeAndCache", "PagedAttention",
+          "PagedAttentionMask", "IncreFlashAttention", "PromptFlashAttention", "FusedInferAttentionScore",
+          "DynamicQuantExt", "FFN", "FFNExt", "FakeQuantPerChannel", "MinMaxUpdatePerChannel", "MinMaxUpdatePerLayer",
+          "GatherD", "GatherNd", "GenerateEodMask", "GroupedMatmul", "IndexSelect", "L2Normalize",
+          "MoeFinalizeRouting", "OneHotExt", "PadV3", "Pad", "QuantBatchMatmul", "WeightQuantBatchMatmul",
+          "RandomChoiceWithMask", "RepeatElements", "ScatterAdd", "ScatterDiv", "ScatterMax", "ScatterMin",
+          "ScatterMul", "ScatterSub", "ScatterUpdate", "ScatterNdAdd", "ScatterNdSub", "ScatterNdUpdate",
+          "TensorScatterAdd", "TensorScatterDiv", "TensorScatterMax", "TensorScatterMin", "TensorScatterMul",
+          "TensorScatterSub", "TensorScatterUpdate", "UnsortedSegmentMax", "UnsortedSegmentMin",
+          "UnsortedSegmentProd", "UnsortedSegmentSum", "SliceExt", "SplitTensor", "SplitWithSize", "StackExt",
+          "SumExt", "TopkExt", "TensorDot", "UniformCandidateSampler", "WKV", "ResizeBilinearV2",
+          "ResizeNearestNeighbor", "Range", "SquareSumAll", "TopKRouter", "SplitV", "Unstack", "ReverseV2", "Tril", "Triu", "UniformReal", "StandardNormal")
 class BatchParallelInfo(OperatorInfo):
     """Dim 0 of every input and output is split by the strategy's first entry; other dims stay whole."""
 
