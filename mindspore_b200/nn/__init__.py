@@ -3,6 +3,8 @@ from . import lr_schedule, optim, wrap
 from .cell import Cell, GraphCell
 from .layer import *  # noqa: F401,F403
 from .layer import get_activation
+from .layer_ext import *  # noqa: F401,F403
+from .optim_ext import *  # noqa: F401,F403
 from .loss import *  # noqa: F401,F403
 from .lr_schedule import (CosineDecayLR, ExponentialDecayLR, InverseDecayLR, LearningRateSchedule, NaturalExpDecayLR,
                           PolynomialDecayLR, WarmUpLR, cosine_decay_lr, exponential_decay_lr, inverse_decay_lr,

@@ -1,0 +1,379 @@
+"""Less common layers: 3-D and transposed convolutions, RNN cells, the ``nn.Transformer`` family, pixel shuffle,
+unfold / fold, multi-field embedding lookup, InstanceNorm1d.
+
+Parity: python/mindspore/nn/layer/{conv.py (Conv3d :700, Conv1dTranspose :1190, Conv3dTranspose :900),
+rnn_cells.py, transformer.py, channel_shuffle.py / pixel shuffle in basic.py, embedding.py
+(MultiFieldEmbeddingLookup :560), normalization.py}."""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from ..common import dtype as mstype
+from ..common.initializer import HeUniform, Uniform, initializer
+from ..common.parameter import Parameter
+from ..ops.primitive import _wrap_out
+from .cell import Cell
+from .layer import CellList, Dense, Dropout, LayerNorm, MultiheadAttention
+
+__all__ = ["Conv3d", "Conv1dTranspose", "Conv3dTranspose", "InstanceNorm1d", "InstanceNorm3d", "LSTMCell", "GRUCell",
+           "RNNCell", "TransformerEncoderLayer", "TransformerDecoderLayer", "TransformerEncoder", "TransformerDecoder",
+           "Transformer", "PixelShuffle", "PixelUnshuffle", "Unfold", "Fold", "MultiFieldEmbeddingLookup",
+           "ChannelShuffle"]
+
+
+def _tuple(v, n):
+    return (v,) * n if isinstance(v, int) else tuple(v)
+
+
+def _same_pads(size, k, s, d):
+    out = []
+    for i in range(len(size)):
+        eff = (k[i] - 1) * d[i] + 1
+        total = max((math.ceil(size[i] / s[i]) - 1) * s[i] + eff - size[i], 0)
+        out.append((total // 2, total - total // 2))
+    return out
+
+
+class Conv3d(Cell):
+    def __init__(self, in_channels, out_channels, kernel_size, stride=1, pad_mode="same", padding=0, dilation=1,
+                 group=1, has_bias=False, weight_init=None, bias_init=None, data_format="NCDHW", dtype=mstype.float32):
+        super().__init__()
+        self.kernel_size, self.stride, self.dilation = _tuple(kernel_size, 3), _tuple(stride, 3), _tuple(dilation, 3)
+        self.pad_mode, self.padding, self.group = pad_mode, padding, group
+        self.weight = Parameter(initializer(weight_init or HeUniform(math.sqrt(5)),
+                                            (out_channels, in_channels // group) + self.kernel_size, dtype), name="weight")
+        fan_in = in_channels // group * self.kernel_size[0] * self.kernel_size[1] * self.kernel_size[2]
+        self.bias = Parameter(initializer(bias_init or Uniform(1 / math.sqrt(fan_in)), (out_channels,), dtype),
+                              name="bias") if has_bias else None
+
+    def construct(self, x):
+        w = self.weight.to(x.dtype)
+        b = self.bias.to(x.dtype) if self.bias is not None else None
+        pad = 0
+        if self.pad_mode == "same":
+            pads = _same_pads(x.shape[2:], self.kernel_size, self.stride, self.dilation)
+            x = F.pad(x, [p for pr in reversed(pads) for p in pr])
+        elif self.pad_mode == "pad":
+            p = self.padding
+            if isinstance(p, int):
+                pad = p
+            else:
+                x = F.pad(x, [p[4], p[5], p[2], p[3], p[0], p[1]])
+        return _wrap_out(F.conv3d(x, w, b, self.stride, pad, self.dilation, self.group))
+
+
+class _ConvTransposeNd(Cell):
+    _nd = 2
+
+    def __init__(self, in_channels, out_channels, kernel_size, stride=1, pad_mode="same", padding=0, dilation=1,
+                 group=1, output_padding=0, has_bias=False, weight_init=None, bias_init=None, dtype=mstype.float32):
+        super().__init__()
+        n = self._nd
+        self.kernel_size, self.stride, self.dilation = _tuple(kernel_size, n), _tuple(stride, n), _tuple(dilation, n)
+        self.pad_mode, self.padding, self.group, self.output_padding = pad_mode, padding, group, output_padding
+        self.weight = Parameter(initializer(weight_init or HeUniform(math.sqrt(5)),
+                                            (in_channels, out_channels // group) + self.kernel_size, dtype), name="weight")
+        self.bias = Parameter(initializer(bias_init or "zeros", (out_channels,), dtype), name="bias") if has_bias else None
+
+    def construct(self, x):
+        fn = {1: F.conv_transpose1d, 3: F.conv_transpose3d}[self._nd]
+        w = self.weight.to(x.dtype)
+        b = self.bias.to(x.dtype) if self.bias is not None else None
+        if self.pad_mode == "pad":
+            p = self.padding if isinstance(self.padding, int) else tuple(self.padding)[::2]
+            return _wrap_out(fn(x, w, b, self.stride, p, self.output_padding, self.group, self.dilation))
+        y = fn(x, w, b, self.stride, 0, 0, self.group, self.dilation)
+        if self.pad_mode == "same":
+            for i in range(self._nd):
+                target = x.shape[2 + i] * self.stride[i]
+                off = (y.shape[2 + i] - target) // 2
+                y = y.narrow(2 + i, off, target)
+        return _wrap_out(y)
+
+
+class Conv1dTranspose(_ConvTransposeNd):
+    _nd = 1
+
+
+class Conv3dTranspose(_ConvTransposeNd):
+    _nd = 3
+
+
+class _InstanceNorm(Cell):
+    def __init__(self, num_features, eps=1e-5, momentum=0.1, affine=True, gamma_init="ones", beta_init="zeros",
+                 dtype=mstype.float32):
+        super().__init__()
+        self.eps, self.affine = eps, affine
+        self.gamma = Parameter(initializer(gamma_init, (num_features,), dtype), name="gamma", requires_grad=affine)
+        self.beta = Parameter(initializer(beta_init, (num_features,), dtype), name="beta", requires_grad=affine)
+
+    def construct(self, x):
+        return _wrap_out(F.instance_norm(x, None, None, self.gamma.to(x.dtype), self.beta.to(x.dtype), True, 0.1,
+                                         self.eps))
+
+
+class InstanceNorm1d(_InstanceNorm):
+    pass
+
+
+class InstanceNorm3d(_InstanceNorm):
+    pass
+
+
+# ------------------------------------------------------------------------------------------------ RNN cells
+class _RNNCellBase(Cell):
+    _gates = 1
+
+    def __init__(self, input_size, hidden_size, has_bias=True, dtype=mstype.float32):
+        super().__init__()
+        self.input_size, self.hidden_size, self.has_bias = input_size, hidden_size, has_bias
+        k = 1 / math.sqrt(hidden_size)
+        g = self._gates * hidden_size
+        self.weight_ih = Parameter(initializer(Uniform(k), (g, input_size), dtype), name="weight_ih")
+        self.weight_hh = Parameter(initializer(Uniform(k), (g, hidden_size), dtype), name="weight_hh")
+        self.bias_ih = Parameter(initializer(Uniform(k), (g,), dtype), name="bias_ih") if has_bias else None
+        self.bias_hh = Parameter(initializer(Uniform(k), (g,), dtype), name="bias_hh") if has_bias else None
+
+
+class RNNCell(_RNNCellBase):
+    def __init__(self, input_size, hidden_size, has_bias=True, nonlinearity="tanh", dtype=mstype.float32):
+        super().__init__(input_size, hidden_size, has_bias, dtype)
+        if nonlinearity not in ("tanh", "relu"):
+            raise ValueError("For 'RNNCell', 'nonlinearity' must be tanh or relu, got %r" % nonlinearity)
+        self.nonlinearity = nonlinearity
+
+    def construct(self, x, hx):
+        pre = F.linear(x, self.weight_ih, self.bias_ih) + F.linear(hx, self.weight_hh, self.bias_hh)
+        return _wrap_out(torch.tanh(pre) if self.nonlinearity == "tanh" else F.relu(pre))
+
+
+class LSTMCell(_RNNCellBase):
+    _gates = 4
+
+    def construct(self, x, hx):
+        h, c = hx
+        gates = F.linear(x, self.weight_ih, self.bias_ih) + F.linear(h, self.weight_hh, self.bias_hh)
+        i, f, g, o = gates.chunk(4, -1)
+        c2 = torch.sigmoid(f) * c + torch.sigmoid(i) * torch.tanh(g)
+        h2 = torch.sigmoid(o) * torch.tanh(c2)
+        return _wrap_out(h2), _wrap_out(c2)
+
+
+class GRUCell(_RNNCellBase):
+    _gates = 3
+
+    def construct(self, x, hx):
+        gi = F.linear(x, self.weight_ih, self.bias_ih)
+        gh = F.linear(hx, self.weight_hh, self.bias_hh)
+        ir, iz, in_ = gi.chunk(3, -1)
+        hr, hz, hn = gh.chunk(3, -1)
+        r, z = torch.sigmoid(ir + hr), torch.sigmoid(iz + hz)
+        n = torch.tanh(in_ + r * hn)
+        return _wrap_out((1 - z) * n + z * hx)
+
+
+# ------------------------------------------------------------------------------------------------ nn.Transformer
+def _activation(name):
+    if callable(name):
+        return name
+    return {"relu": F.relu, "gelu": F.gelu}[name]
+
+
+class TransformerEncoderLayer(Cell):
+    def __init__(self, d_model, nhead, dim_feedforward=2048, dropout=0.1, activation="relu", layer_norm_eps=1e-5,
+                 batch_first=False, norm_first=False, dtype=mstype.float32):
+        super().__init__()
+        self.self_attn = MultiheadAttention(d_model, nhead, dropout=dropout, batch_first=batch_first, dtype=dtype)
+        self.dense1, self.dense2 = Dense(d_model, dim_feedforward, dtype=dtype), Dense(dim_feedforward, d_model, dtype=dtype)
+        self.norm1, self.norm2 = LayerNorm((d_model,), epsilon=layer_norm_eps), LayerNorm((d_model,), epsilon=layer_norm_eps)
+        self.dropout, self.dropout1, self.dropout2 = Dropout(p=dropout), Dropout(p=dropout), Dropout(p=dropout)
+        self.act, self.norm_first = _activation(activation), norm_first
+
+    def _sa(self, x, mask, kpm):
+        return self.dropout1(self.self_attn(x, x, x, attn_mask=mask, key_padding_mask=kpm, need_weights=False)[0])
+
+    def _ff(self, x):
+        return self.dropout2(self.dense2(self.dropout(_wrap_out(self.act(self.dense1(x))))))
+
+    def construct(self, src, src_mask=None, src_key_padding_mask=None):
+        x = src
+        if self.norm_first:
+            x = x + self._sa(self.norm1(x), src_mask, src_key_padding_mask)
+            return x + self._ff(self.norm2(x))
+        x = self.norm1(x + self._sa(x, src_mask, src_key_padding_mask))
+        return self.norm2(x + self._ff(x))
+
+
+class TransformerDecoderLayer(Cell):
+    def __init__(self, d_model, nhead, dim_feedforward=2048, dropout=0.1, activation="relu", layer_norm_eps=1e-5,
+                 batch_first=False, norm_first=False, dtype=mstype.float32):
+        super().__init__()
+        self.self_attn = MultiheadAttention(d_model, nhead, dropout=dropout, batch_first=batch_first, dtype=dtype)
+        self.multihead_attn = MultiheadAttention(d_model, nhead, dropout=dropout, batch_first=batch_first, dtype=dtype)
+        self.dense1, self.dense2 = Dense(d_model, dim_feedforward, dtype=dtype), Dense(dim_feedforward, d_model, dtype=dtype)
+        self.norm1, self.norm2, self.norm3 = (LayerNorm((d_model,), epsilon=layer_norm_eps) for _ in range(3))
+        self.dropout, self.dropout1, self.dropout2, self.dropout3 = (Dropout(p=dropout) for _ in range(4))
+        self.act, self.norm_first = _activation(activation), norm_first
+
+    def construct(self, tgt, memory, tgt_mask=None, memory_mask=None, tgt_key_padding_mask=None,
+                  memory_key_padding_mask=None):
+        def sa(x):
+            return self.dropout1(self.self_attn(x, x, x, attn_mask=tgt_mask, key_padding_mask=tgt_key_padding_mask,
+                                                need_weights=False)[0])
+
+        def ca(x):
+            return self.dropout2(self.multihead_attn(x, memory, memory, attn_mask=memory_mask,
+                                                     key_padding_mask=memory_key_padding_mask, need_weights=False)[0])
+
+        def ff(x):
+            return self.dropout3(self.dense2(self.dropout(_wrap_out(self.act(self.dense1(x))))))
+        x = tgt
+        if self.norm_first:
+            x = x + sa(self.norm1(x))
+            x = x + ca(self.norm2(x))
+            return x + ff(self.norm3(x))
+        x = self.norm1(x + sa(x))
+        x = self.norm2(x + ca(x))
+        return self.norm3(x + ff(x))
+
+
+class TransformerEncoder(Cell):
+    def __init__(self, encoder_layer, num_layers, norm=None):
+        super().__init__()
+        import copy
+        self.layers = CellList([encoder_layer] + [copy.deepcopy(encoder_layer) for _ in range(num_layers - 1)])
+        self.norm = norm
+
+    def construct(self, src, src_mask=None, src_key_padding_mask=None):
+        x = src
+        for layer in self.layers:
+            x = layer(x, src_mask, src_key_padding_mask)
+        return self.norm(x) if self.norm is not None else x
+
+
+class TransformerDecoder(Cell):
+    def __init__(self, decoder_layer, num_layers, norm=None):
+        super().__init__()
+        import copy
+        self.layers = CellList([decoder_layer] + [copy.deepcopy(decoder_layer) for _ in range(num_layers - 1)])
+        self.norm = norm
+
+    def construct(self, tgt, memory, tgt_mask=None, memory_mask=None, tgt_key_padding_mask=None,
+                  memory_key_padding_mask=None):
+        x = tgt
+        for layer in self.layers:
+            x = layer(x, memory, tgt_mask, memory_mask, tgt_key_padding_mask, memory_key_padding_mask)
+        return self.norm(x) if self.norm is not None else x
+
+
+class Transformer(Cell):
+    def __init__(self, d_model=512, nhead=8, num_encoder_layers=6, num_decoder_layers=6, dim_feedforward=2048,
+                 dropout=0.1, activation="relu", custom_encoder=None, custom_decoder=None, layer_norm_eps=1e-5,
+                 batch_first=False, norm_first=False, dtype=mstype.float32):
+        super().__init__()
+        self.encoder = custom_encoder or TransformerEncoder(
+            TransformerEncoderLayer(d_model, nhead, dim_feedforward, dropout, activation, layer_norm_eps, batch_first,
+                                    norm_first, dtype), num_encoder_layers, LayerNorm((d_model,), epsilon=layer_norm_eps))
+        self.decoder = custom_decoder or TransformerDecoder(
+            TransformerDecoderLayer(d_model, nhead, dim_feedforward, dropout, activation, layer_norm_eps, batch_first,
+                                    norm_first, dtype), num_decoder_layers, LayerNorm((d_model,), epsilon=layer_norm_eps))
+        self.d_model, self.nhead, self.batch_first = d_model, nhead, batch_first
+
+    def construct(self, src, tgt, src_mask=None, tgt_mask=None, memory_mask=None, src_key_padding_mask=None,
+                  tgt_key_padding_mask=None, memory_key_padding_mask=None):
+        memory = self.encoder(src, src_mask, src_key_padding_mask)
+        return self.decoder(tgt, memory, tgt_mask, memory_mask, tgt_key_padding_mask, memory_key_padding_mask)
+
+
+# ------------------------------------------------------------------------------------------------ layout shuffles
+class PixelShuffle(Cell):
+    def __init__(self, upscale_factor):
+        super().__init__()
+        self.upscale_factor = upscale_factor
+
+    def construct(self, x):
+        return _wrap_out(F.pixel_shuffle(x, self.upscale_factor))
+
+
+class PixelUnshuffle(Cell):
+    def __init__(self, downscale_factor):
+        super().__init__()
+        self.downscale_factor = downscale_factor
+
+    def construct(self, x):
+        return _wrap_out(F.pixel_unshuffle(x, self.downscale_factor))
+
+
+class ChannelShuffle(Cell):
+    def __init__(self, groups):
+        super().__init__()
+        self.groups = groups
+
+    def construct(self, x):
+        return _wrap_out(F.channel_shuffle(x, self.groups))
+
+
+class Unfold(Cell):
+    """Sliding local blocks: [N, C, H, W] -> [N, C * kh * kw, L] (``ksizes`` / ``strides`` / ``rates`` given as
+    [1, h, w, 1] like the reference's ``nn.Unfold``, or plain ints / pairs)."""
+
+    def __init__(self, ksizes, strides=1, rates=1, padding="valid"):
+        super().__init__()
+        def hw(v):
+            v = list(v) if isinstance(v, (list, tuple)) else [v, v]
+            return tuple(v[1:3]) if len(v) == 4 else tuple(v)
+        self.k, self.s, self.d = hw(ksizes), hw(strides), hw(rates)
+        self.padding = padding
+
+    def construct(self, x):
+        if isinstance(self.padding, str) and self.padding.lower() == "same":
+            pads = _same_pads(x.shape[2:], self.k, self.s, self.d)
+            x = F.pad(x, [pads[1][0], pads[1][1], pads[0][0], pads[0][1]])
+            pad = 0
+        else:
+            pad = 0 if isinstance(self.padding, str) else self.padding
+        return _wrap_out(F.unfold(x, self.k, self.d, pad, self.s))
+
+
+class Fold(Cell):
+    def __init__(self, output_size, kernel_size, dilation=1, padding=0, stride=1):
+        super().__init__()
+        self.args = (output_size, kernel_size, dilation, padding, stride)
+
+    def construct(self, x):
+        return _wrap_out(F.fold(x, *self.args))
+
+
+class MultiFieldEmbeddingLookup(Cell):
+    """Embedding lookup whose ids are grouped into fields: (ids [B, L], weights [B, L], field_ids [B, L]) ->
+    [B, field_size, D], combining the embeddings of one field by SUM / MEAN / MAX."""
+
+    def __init__(self, vocab_size, embedding_size, field_size, param_init="normal", target="CPU", slice_mode="batch_slice",
+                 feature_num_list=None, max_norm=None, sparse=True, operator="SUM", dtype=mstype.float32):
+        super().__init__()
+        if operator not in ("SUM", "MEAN", "MAX"):
+            raise ValueError("For 'MultiFieldEmbeddingLookup', 'operator' must be SUM, MEAN or MAX, got %r" % operator)
+        self.field_size, self.operator, self.max_norm = field_size, operator, max_norm
+        self.embedding_table = Parameter(initializer(param_init, (vocab_size, embedding_size), dtype),
+                                         name="embedding_table")
+
+    def construct(self, input_indices, input_values, field_ids):
+        emb = F.embedding(input_indices.long(), self.embedding_table, max_norm=self.max_norm)
+        emb = emb * input_values.unsqueeze(-1).to(emb.dtype)
+        B, L, D = emb.shape
+        onehot = F.one_hot(field_ids.long().clamp_min(0), self.field_size).to(emb.dtype)        # [B, L, F]
+        valid = (field_ids >= 0).unsqueeze(-1).to(emb.dtype)
+        onehot = onehot * valid
+        if self.operator == "MAX":
+            big = emb.unsqueeze(2).expand(B, L, self.field_size, D)
+            masked = torch.where(onehot.unsqueeze(-1) > 0, big, torch.full_like(big, float("-inf")))
+            out = masked.amax(1)
+            return _wrap_out(torch.where(torch.isinf(out), torch.zeros_like(out), out))
+        out = torch.einsum("blf,bld->bfd", onehot, emb)
+        if self.operator == "MEAN":
+            cnt = torch.einsum("blf,bl->bf", onehot, input_values.to(emb.dtype)).clamp_min(1e-12)
+            out = out / cnt.unsqueeze(-1)
+        return _wrap_out(out)

@@ -839,6 +839,4 @@ class AdaFactor(Optimizer):
         return True
 
 
-class thor:  # second-order THOR needs per-layer Fisher factors; provided as a thin first-order fallback
-    def __new__(cls, net, learning_rate, damping, momentum, weight_decay=0.0, loss_scale=1.0, batch_size=32, **kw):
-        return Momentum(net.trainable_params(), learning_rate, momentum, weight_decay, loss_scale)
+from .optim_ext import *  # noqa: E402,F401,F403

@@ -1,0 +1,143 @@
+"""Extended layers and optimizers: RNN cells against torch.nn cells with the same weights, transposed / 3-D
+convolutions against torch.nn.functional, the Transformer stack end to end, LazyAdam / AdamOffload against Adam,
+THOR's preconditioner, AdaSum on two CPU ranks."""
+import numpy as np
+import torch
+
+import mindspore_b200 as ms
+from mindspore_b200 import nn
+from _mp import run_ranks
+
+
+def _t(x):
+    return ms.Tensor(x)
+
+
+def test_rnn_cells_match_torch():
+    torch.manual_seed(0)
+    x, h, c = torch.randn(3, 5), torch.randn(3, 7), torch.randn(3, 7)
+    for ours, ref in ((nn.LSTMCell(5, 7), torch.nn.LSTMCell(5, 7)), (nn.GRUCell(5, 7), torch.nn.GRUCell(5, 7)),
+                      (nn.RNNCell(5, 7), torch.nn.RNNCell(5, 7))):
+        with torch.no_grad():
+            for n in ("weight_ih", "weight_hh", "bias_ih", "bias_hh"):
+                getattr(ref, n).copy_(getattr(ours, n))
+        if isinstance(ours, nn.LSTMCell):
+            (h1, c1), (h2, c2) = ours(_t(x), (_t(h), _t(c))), ref(x, (h, c))
+            torch.testing.assert_close(torch.as_tensor(h1.detach().numpy()), h2.detach(), rtol=1e-5, atol=1e-5)
+            torch.testing.assert_close(torch.as_tensor(c1.detach().numpy()), c2.detach(), rtol=1e-5, atol=1e-5)
+        else:
+            torch.testing.assert_close(torch.as_tensor(ours(_t(x), _t(h)).detach().numpy()), ref(x, h).detach(),
+                                       rtol=1e-5, atol=1e-5)
+
+
+def test_conv_variants_match_torch():
+    torch.manual_seed(1)
+    x3 = torch.randn(2, 3, 4, 5, 6)
+    c3 = nn.Conv3d(3, 4, 3, pad_mode="pad", padding=1, has_bias=True)
+    ref = torch.nn.functional.conv3d(x3, c3.weight.detach(), c3.bias.detach(), padding=1)
+    torch.testing.assert_close(torch.as_tensor(c3(_t(x3)).detach().numpy()), torch.as_tensor(ref.numpy()), rtol=1e-4,
+                               atol=1e-4)
+    t1 = nn.Conv1dTranspose(3, 2, 4, stride=2, pad_mode="same")
+    assert tuple(t1(_t(torch.randn(2, 3, 9))).shape) == (2, 2, 18)
+    t3 = nn.Conv3dTranspose(3, 2, 3, stride=2, pad_mode="pad", padding=1, output_padding=1)
+    ref = torch.nn.functional.conv_transpose3d(x3, t3.weight.detach(), None, 2, 1, 1)
+    torch.testing.assert_close(torch.as_tensor(t3(_t(x3)).detach().numpy()), torch.as_tensor(ref.numpy()), rtol=1e-4,
+                               atol=1e-4)
+    u = nn.Unfold([1, 2, 2, 1], [1, 2, 2, 1], [1, 1, 1, 1])(_t(torch.arange(32.0).reshape(1, 2, 4, 4)))
+    f = nn.Fold((4, 4), 2, stride=2)(u)
+    assert torch.equal(torch.as_tensor(f.numpy()), torch.arange(32.0).reshape(1, 2, 4, 4))
+
+
+def test_transformer_trains():
+    ms.set_seed(3)
+    model = nn.Transformer(d_model=16, nhead=4, num_encoder_layers=1, num_decoder_layers=1, dim_feedforward=32,
+                           dropout=0.0, batch_first=True)
+    src, tgt = _t(torch.randn(4, 6, 16)), _t(torch.randn(4, 5, 16))
+    mask = _t(torch.triu(torch.ones(5, 5, dtype=torch.bool), 1))
+
+    class Net(nn.Cell):
+        def __init__(self):
+            super().__init__()
+            self.m = model
+
+        def construct(self, s, t):
+            return (self.m(s, t, tgt_mask=mask) ** 2).mean()
+    net = Net()
+    step = nn.TrainOneStepCell(net, nn.Adam(net.trainable_params(), 1e-2))
+    step.set_train()
+    first = float(step(src, tgt))
+    for _ in range(20):
+        last = float(step(src, tgt))
+    assert last < first * 0.7
+
+
+def test_multifield_embedding_sum_and_max():
+    m = nn.MultiFieldEmbeddingLookup(6, 2, 2, param_init="ones", operator="SUM")
+    out = m(_t(torch.tensor([[1, 2, 3]])), _t(torch.tensor([[1.0, 2.0, 3.0]])), _t(torch.tensor([[0, 0, 1]])))
+    assert out.tolist() == [[[3.0, 3.0], [3.0, 3.0]]]
+    m2 = nn.MultiFieldEmbeddingLookup(6, 2, 2, param_init="ones", operator="MAX")
+    out = m2(_t(torch.tensor([[1, 2, 3]])), _t(torch.tensor([[1.0, 2.0, 3.0]])), _t(torch.tensor([[0, 0, -1]])))
+    assert out.tolist() == [[[2.0, 2.0], [0.0, 0.0]]]
+
+
+def _train(opt_fn, steps=5):
+    ms.set_seed(7)
+    net = nn.WithLossCell(nn.SequentialCell([nn.Dense(6, 8), nn.Tanh(), nn.Dense(8, 1)]), nn.MSELoss())
+    g = torch.Generator().manual_seed(0)
+    x, y = _t(torch.randn(32, 6, generator=g)), _t(torch.randn(32, 1, generator=g))
+    step = nn.TrainOneStepCell(net, opt_fn(net))
+    step.set_train()
+    losses = [float(step(x, y)) for _ in range(steps)]
+    return losses, [p.detach().numpy().copy() for p in net.trainable_params()]
+
+
+def test_lazy_and_offload_adam_equal_adam_on_dense_gradients():
+    ref_l, ref_p = _train(lambda n: nn.Adam(n.trainable_params(), 1e-2))
+    for cls in (nn.LazyAdam, nn.AdamOffload):
+        l, p = _train(lambda n: cls(n.trainable_params(), 1e-2))
+        np.testing.assert_allclose(l, ref_l, rtol=1e-5)
+        for a, b in zip(p, ref_p):
+            np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-6)
+
+
+def test_lazy_adam_touches_only_rows_with_gradient():
+    emb = ms.Parameter(_t(torch.ones(16, 4)), name="emb")
+    opt = nn.LazyAdam([emb], 0.1)
+    g = torch.zeros(16, 4); g[3] = 1.0
+    opt((_t(g),))
+    w = emb.detach().numpy()
+    assert (w[3] < 1).all() and (np.delete(w, 3, 0) == 1).all()
+    assert float(opt.moment1[0].abs().sum()) == float(opt.moment1[0][3].abs().sum())
+
+
+def test_thor_preconditions_dense_layers():
+    losses, _ = _train(lambda n: nn.THOR(n, 0.05, 0.05, 0.9, frequency=2), steps=25)
+    base, _ = _train(lambda n: nn.Momentum(n.trainable_params(), 0.05, 0.9), steps=25)
+    assert losses[-1] < losses[0] * 0.7
+    assert np.isfinite(losses).all() and losses[-1] < base[-1] * 1.5
+
+
+def _adasum_rank(rank, world):
+    import torch.distributed as dist
+    import mindspore_b200 as ms
+    from mindspore_b200 import nn
+    from mindspore_b200.communication import init
+    ms.set_context(device_target="CPU")
+    init("gloo")
+    p = ms.Parameter(ms.Tensor(torch.zeros(2)), name="w")
+    opt = nn.AdaSumByGradWrapCell(nn.SGD([p], 1.0))
+    grad = torch.tensor([1.0, 0.0]) if rank == 0 else torch.tensor([0.0, 1.0])
+    opt((ms.Tensor(grad),))
+    a = p.detach().numpy().tolist()
+    p2 = ms.Parameter(ms.Tensor(torch.zeros(2)), name="w2")
+    opt2 = nn.AdaSumByDeltaWeightWrapCell(nn.SGD([p2], 1.0))
+    opt2((ms.Tensor(torch.tensor([2.0, 2.0])),))
+    dist.barrier()
+    return a, p2.detach().numpy().tolist()
+
+
+def test_adasum_two_ranks():
+    res = run_ranks(_adasum_rank, 2)
+    for a, b in res:
+        np.testing.assert_allclose(a, [-1.0, -1.0])          # orthogonal gradients add
+        np.testing.assert_allclose(b, [-2.0, -2.0])          # identical deltas average
