@@ -158,6 +158,78 @@ class NeighborExchange(_CommPrimitive):
         return CF.batch_isend_irecv(ops)
 
 
+class NeighborExchangeV2(_CommPrimitive):
+    """Halo exchange of an NCHW tensor with up to eight neighbours.  ``send_rank_ids`` / ``recv_rank_ids`` list the
+    neighbour in the order top, top-right, right, bottom-right, bottom, bottom-left, left, top-left (-1: none);
+    ``send_lens`` / ``recv_lens`` are [top, bottom, left, right] widths.  The output is the input padded with the
+    received halos (ops/operations/comm_ops.py:994 in the reference; its GPU lowering is
+    plugin/device/gpu/optimizer/neighbor_exchange_v2_fusion.cc)."""
+
+    def __init__(self, send_rank_ids, send_lens, recv_rank_ids, recv_lens, data_format="NCHW", group=None):
+        super().__init__("NeighborExchangeV2")
+        self._init_group(group)
+        self.send_rank_ids, self.recv_rank_ids = list(send_rank_ids), list(recv_rank_ids)
+        self.send_lens, self.recv_lens = list(send_lens), list(recv_lens)
+        if data_format != "NCHW":
+            raise ValueError("For 'NeighborExchangeV2', only NCHW is supported, got %r" % data_format)
+
+    @staticmethod
+    def _region(direction, lens, H, W, inner):
+        """(row slice, col slice) of the strip for ``direction``; ``inner`` selects the strip inside the tensor that
+        is sent, otherwise the halo strip of the padded output that is received."""
+        t, b, l, r = lens
+        rows = {"top": slice(0, t), "bottom": slice(H - b, H), "mid": slice(0, H)}
+        cols = {"left": slice(0, l), "right": slice(W - r, W), "mid": slice(0, W)}
+        table = [("top", "mid"), ("top", "right"), ("mid", "right"), ("bottom", "right"), ("bottom", "mid"),
+                 ("bottom", "left"), ("mid", "left"), ("top", "left")]
+        rk, ck = table[direction]
+        return rows[rk], cols[ck]
+
+    def _run(self, x):
+        N, C, H, W = x.shape
+        st, sb, sl, sr = self.send_lens
+        rt, rb, rl, rr = self.recv_lens
+        out = torch.zeros(N, C, H + rt + rb, W + rl + rr, dtype=x.dtype, device=x.device)
+        out[:, :, rt:rt + H, rl:rl + W] = x
+        ops, recvs = [], []
+        for d, peer in enumerate(self.send_rank_ids):
+            if peer < 0:
+                continue
+            rs, cs = self._region(d, self.send_lens, H, W, True)
+            ops.append(CF.P2POp("isend", x[:, :, rs, cs].contiguous(), peer, self.group))
+        Hp, Wp = H + rt + rb, W + rl + rr
+        for d, peer in enumerate(self.recv_rank_ids):
+            if peer < 0:
+                continue
+            rows = {"top": slice(0, rt), "bottom": slice(Hp - rb, Hp), "mid": slice(rt, rt + H)}
+            cols = {"left": slice(0, rl), "right": slice(Wp - rr, Wp), "mid": slice(rl, rl + W)}
+            table = [("top", "mid"), ("top", "right"), ("mid", "right"), ("bottom", "right"), ("bottom", "mid"),
+                     ("bottom", "left"), ("mid", "left"), ("top", "left")]
+            rk, ck = table[d]
+            buf = torch.empty_like(out[:, :, rows[rk], cols[ck]]).contiguous()
+            recvs.append((rows[rk], cols[ck], buf))
+            ops.append(CF.P2POp("irecv", buf, peer, self.group))
+        if ops:
+            CF.batch_isend_irecv(ops)
+        for rs, cs, buf in recvs:
+            out[:, :, rs, cs] = buf
+        return out
+
+
+class _AllSwap(_CommPrimitive):
+    """All-to-all with per-peer element counts: ``send_size[i]`` elements of the flat input go to rank i and
+    ``recv_size[i]`` elements arrive from rank i (ops/operations/comm_ops.py:741)."""
+
+    def __init__(self, group=None):
+        super().__init__("_AllSwap")
+        self._init_group(group)
+
+    def _run(self, x, send_size, recv_size):
+        send = [int(v) for v in (send_size.tolist() if isinstance(send_size, torch.Tensor) else send_size)]
+        recv = [int(v) for v in (recv_size.tolist() if isinstance(recv_size, torch.Tensor) else recv_size)]
+        return CF.all_to_all_single_with_output_shape((sum(recv),) + tuple(x.shape[1:]), x, recv, send, self.group)
+
+
 class CollectiveScatter(_CommPrimitive):
     def __init__(self, src_rank=0, group=None):
         super().__init__("CollectiveScatter")

@@ -497,21 +497,130 @@ class ClusterMonitor(Callback):
 
 
 class SummaryCollector(Callback):
-    """Scalar summaries (loss, metrics) as JSON lines under ``summary_dir`` (MindInsight protobuf events are not
-    produced)."""
+    """Collects the loss (and the learning rate when the optimizer exposes one) every ``collect_freq`` steps into
+    a summary event file under ``summary_dir`` (``train.summary.SummaryRecord``: framed, CRC-checked protobuf events,
+    the format MindInsight reads), plus one JSON line per record for quick inspection
+    (train/callback/_summary_collector.py in the reference)."""
 
     def __init__(self, summary_dir, collect_freq=10, collect_specified_data=None, keep_default_action=True,
                  custom_lineage_data=None, collect_tensor_freq=None, max_file_size=None, export_options=None):
+        from .summary import SummaryRecord
         self.dir = os.path.abspath(summary_dir)
         os.makedirs(self.dir, exist_ok=True)
-        self.freq = collect_freq
+        self.freq = max(1, int(collect_freq))
         self.path = os.path.join(self.dir, "events.summary.%d.jsonl" % os.getpid())
+        self._record = SummaryRecord(self.dir)
+        self._lineage = dict(custom_lineage_data or {})
+
+    def on_train_begin(self, run_context):
+        if self._lineage:
+            with open(os.path.join(self.dir, "lineage.json"), "w") as f:
+                json.dump(self._lineage, f)
 
     def on_train_step_end(self, run_context):
         p = run_context.original_args()
         if p.cur_step_num % self.freq == 0:
+            loss = _loss_value(p.net_outputs)
+            self._record.add_value("scalar", "loss/auto", loss)
+            opt = getattr(p, "optimizer", None)
+            if opt is not None and hasattr(opt, "get_lr"):
+                try:
+                    self._record.add_value("scalar", "learning_rate/auto", float(opt.get_lr()))
+                except (TypeError, ValueError, RuntimeError):
+                    pass
+            self._record.record(p.cur_step_num)
             with open(self.path, "a") as f:
-                f.write(json.dumps({"step": p.cur_step_num, "tag": "loss/auto", "value": _loss_value(p.net_outputs)}) + "\n")
+                f.write(json.dumps({"step": p.cur_step_num, "tag": "loss/auto", "value": loss}) + "\n")
+
+    def on_train_end(self, run_context):
+        self._record.close()
+
+
+class SummaryLandscape:
+    """Loss landscape around the end of a training run: the loss is evaluated on a ``steps x steps`` grid spanned
+    by two directions through the final weights - the two leading principal components of the checkpoints saved over
+    training (``landscape_type='pca'``) or two random directions scaled per parameter to the weight norm
+    ('random') - and written to ``<summary_dir>/landscape.json`` (train/callback/_landscape.py in the reference;
+    there the grid is farmed out to several devices)."""
+
+    def __init__(self, summary_dir):
+        self.dir = os.path.abspath(summary_dir)
+        os.makedirs(self.dir, exist_ok=True)
+
+    def clean_ckpt(self):
+        ck = os.path.join(self.dir, "ckpt_dir")
+        if os.path.isdir(ck):
+            for f in os.listdir(ck):
+                os.remove(os.path.join(ck, f))
+
+    def gen_landscapes_with_multi_process(self, callback_fn, collect_landscape=None, device_ids=None, output=None):
+        """``callback_fn()`` returns (model, network, dataset, metrics); ``collect_landscape`` may hold
+        ``landscape_size``, ``create_landscape`` ({'train': bool, 'result': bool}), ``num_samples``, ``intervals``,
+        ``checkpoints`` (list of checkpoint files for the PCA directions) and ``landscape_type``."""
+        import numpy as np
+        import torch
+        from .serialization import load_checkpoint
+        cfg = dict(collect_landscape or {})
+        steps = int(cfg.get("landscape_size", 11))
+        span = float(cfg.get("span", 1.0))
+        model, network, dataset, _ = callback_fn()
+        params = [p for p in network.trainable_params()]
+        center = [p.detach().clone() for p in params]
+        flat_c = torch.cat([c.reshape(-1).float() for c in center])
+        ckpts = cfg.get("checkpoints") or []
+        kind = cfg.get("landscape_type", "pca" if len(ckpts) >= 2 else "random")
+        if kind == "pca" and len(ckpts) >= 2:
+            rows = []
+            for path in ckpts:
+                sd = load_checkpoint(path)
+                rows.append(torch.cat([torch.as_tensor(sd[p.name].asnumpy() if hasattr(sd[p.name], "asnumpy") else
+                                                       sd[p.name]).reshape(-1).float() for p in params]) - flat_c)
+            _, _, vh = torch.linalg.svd(torch.stack(rows), full_matrices=False)
+            scale = max(float(r.norm()) for r in rows) or 1.0
+            d1, d2 = vh[0] * scale, (vh[1] if vh.shape[0] > 1 else torch.randn_like(vh[0])) * scale
+        else:
+            g = torch.Generator().manual_seed(int(cfg.get("seed", 0)))
+            dirs = []
+            for _ in range(2):
+                parts = []
+                for c in center:
+                    r = torch.randn(c.shape, generator=g)
+                    parts.append((r * (c.float().norm() / (r.norm() + 1e-12))).reshape(-1))    # filter normalisation
+                dirs.append(torch.cat(parts))
+            d1, d2 = dirs
+
+        def set_weights(vec):
+            off = 0
+            with torch.no_grad():
+                for p in params:
+                    n = p.numel()
+                    p.copy_(vec[off:off + n].reshape(p.shape).to(p.dtype))
+                    off += n
+
+        def loss_now():
+            tot, cnt = 0.0, 0
+            network.set_train(False)
+            for i, batch in enumerate(dataset.create_tuple_iterator()):
+                with torch.no_grad():
+                    tot += float(network(*batch))
+                cnt += 1
+                if cnt >= int(cfg.get("num_batches", 4)):
+                    break
+            return tot / max(cnt, 1)
+
+        axis = np.linspace(-span, span, steps)
+        grid = np.zeros((steps, steps))
+        for i, a in enumerate(axis):
+            for j, b in enumerate(axis):
+                set_weights(flat_c + float(a) * d1 + float(b) * d2)
+                grid[i, j] = loss_now()
+        set_weights(flat_c)
+        out = output or self.dir
+        os.makedirs(out, exist_ok=True)
+        path = os.path.join(out, "landscape.json")
+        with open(path, "w") as f:
+            json.dump({"type": kind, "x": axis.tolist(), "y": axis.tolist(), "loss": grid.tolist()}, f)
+        return path
 
 
 class MindIOTTPAdapter(Callback):

@@ -70,3 +70,30 @@ def test_namespaces():
     assert isinstance(a, ms.Tensor) and float(mnp.sum(a)) == 2.5
     assert mnp.concatenate([mnp.ones((2, 2)), mnp.zeros((1, 2))]).shape == (3, 2)
     assert mnp.argmax(mnp.array([1, 5, 2])).item() == 1
+
+
+def test_summary_collector_writes_event_file_and_landscape(tmp_path):
+    import json
+    import numpy as np
+    import mindspore_b200 as ms
+    import mindspore_b200.dataset as ds
+    from mindspore_b200 import nn
+    from mindspore_b200.train import Model
+    from mindspore_b200.train.callback import SummaryCollector, SummaryLandscape
+    ms.set_seed(0)
+    rng = np.random.default_rng(0)
+    x = rng.normal(size=(32, 4)).astype(np.float32)
+    y = x.sum(1, keepdims=True).astype(np.float32)
+    data = ds.NumpySlicesDataset((x, y), ["x", "y"], shuffle=False).batch(8)
+    net = nn.Dense(4, 1)
+    model = Model(net, nn.MSELoss(), nn.SGD(net.trainable_params(), 0.05))
+    model.train(2, data, callbacks=[SummaryCollector(str(tmp_path), collect_freq=2)], dataset_sink_mode=False)
+    events = [f for f in os.listdir(tmp_path) if f.startswith("events") and not f.endswith(".jsonl")]
+    assert events and os.path.getsize(os.path.join(tmp_path, events[0])) > 40
+    lines = [json.loads(l) for f in os.listdir(tmp_path) if f.endswith(".jsonl") for l in open(os.path.join(tmp_path, f))]
+    assert [l["step"] for l in lines] == [2, 4, 6, 8]
+    loss_net = nn.WithLossCell(net, nn.MSELoss())
+    path = SummaryLandscape(str(tmp_path)).gen_landscapes_with_multi_process(
+        lambda: (model, loss_net, data, None), {"landscape_size": 5, "span": 1.0})
+    grid = np.array(json.load(open(path))["loss"])
+    assert grid.shape == (5, 5) and grid[2, 2] < grid.mean() and np.isfinite(grid).all()
