@@ -445,20 +445,45 @@ def parse_print(print_file_name):
 
 
 def export(net, *inputs, file_name, file_format, **kwargs):
-    """Exports the traced graph and weights.  MINDIR: graph text (``.mindir.ir``) plus a ``.ckpt`` of weights."""
+    """Exports ``net`` traced on ``inputs``.  MINDIR: one ``<file_name>.mindir`` file holding the forward graph and the
+    weights (``graph/mindir.py`` describes the layout); ``enc_key`` / ``enc_mode`` encrypt it like a checkpoint.  ONNX
+    and AIR target other runtimes and are not produced."""
     if file_format not in ("MINDIR", "ONNX", "AIR"):
         raise ValueError("For 'export', 'file_format' must be one of AIR, ONNX, MINDIR, but got %r" % file_format)
     if file_format != "MINDIR":
         raise NotImplementedError("only MINDIR export is available in this build")
     from ..graph import jit as _jit
-    g = _jit.trace_cell(net, inputs)
-    base = file_name[:-7] if file_name.endswith(".mindir") else file_name
-    with open(base + ".mindir", "w") as f:
-        f.write(g.to_text())
-    save_checkpoint(net, base + ".weights.ckpt", integrated_save=False)
-    return base + ".mindir"
+    from ..graph import mindir
+    was_training = getattr(net, "training", False)
+    net.set_train(False)
+    try:
+        g = _jit.trace_cell(net, inputs)
+    finally:
+        net.set_train(was_training)
+    path = file_name if file_name.endswith(".mindir") else file_name + ".mindir"
+    mindir.save_mindir(g, path)
+    enc_key = kwargs.get("enc_key")
+    if enc_key is not None:
+        from . import crypto
+        with open(path, "rb") as f:
+            raw = f.read()
+        with open(path, "wb") as f:
+            f.write(crypto.encrypt(raw, enc_key, kwargs.get("enc_mode", "AES-GCM")))
+    return path
 
 
 def load(file_name, **kwargs):
-    from ..graph import jit as _jit
-    return _jit.load_graph_text(file_name)
+    """Loads a graph written by ``export`` (``dec_key`` / ``dec_mode`` for an encrypted file); wrap the result in
+    ``nn.GraphCell`` to use it as a network."""
+    from ..graph import mindir
+    dec_key = kwargs.get("dec_key")
+    if dec_key is None:
+        return mindir.load_mindir(file_name)
+    import tempfile
+    from . import crypto
+    with open(file_name, "rb") as f:
+        raw = crypto.decrypt(f.read(), dec_key, kwargs.get("dec_mode", "AES-GCM"))
+    with tempfile.NamedTemporaryFile(suffix=".mindir") as tmp:
+        tmp.write(raw)
+        tmp.flush()
+        return mindir.load_mindir(tmp.name)
