@@ -30,5 +30,13 @@ from .utils.dump import set_dump
 from .train.summary import SummaryRecord
 from . import hal, mint
 
+from .common.api import *  # noqa: E402,F401,F403
+from .ops.primitive import constexpr  # noqa: E402
+from . import boost, experimental, rewrite, scipy  # noqa: E402
+from . import numpy  # noqa: E402
+from .dataset import mindrecord  # noqa: E402
+import multiprocessing  # noqa: E402  (the reference re-exports a fork-safe wrapper of the same module)
+from .graph.mindir import load_mindir  # noqa: E402
+
 mstype = dtype
 __version__ = "0.1.0"

@@ -1,0 +1,2 @@
+"""Experimental API: torch-style optimizers and learning-rate schedulers (python/mindspore/experimental/optim)."""
+from . import optim  # noqa: F401

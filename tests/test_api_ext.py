@@ -1,0 +1,146 @@
+"""Top-level helpers: sparse containers, Symbol, mutable / recompute / vmap / hessian, scipy routines, torch-style
+optimizers and schedulers, boost."""
+import numpy as np
+import pytest
+import torch
+
+import mindspore_b200 as ms
+from mindspore_b200 import nn
+
+
+def test_sparse_containers():
+    coo = ms.COOTensor([[0, 1], [1, 2], [0, 1]], [1.0, 2.0, 3.0], (2, 3))
+    dense = coo.to_dense().numpy()
+    assert dense.tolist() == [[0, 4, 0], [0, 0, 2]]
+    csr = coo.to_csr()
+    assert csr.indptr.tolist() == [0, 1, 2] and csr.indices.tolist() == [1, 2] and csr.values.tolist() == [4.0, 2.0]
+    assert csr.to_dense().numpy().tolist() == dense.tolist()
+    assert csr.mv(torch.tensor([1.0, 2.0, 3.0])).reshape(-1).tolist() == [8.0, 6.0]
+    assert csr.mm(torch.eye(3)).numpy().tolist() == dense.tolist()
+    assert (csr * 2.0).to_coo().to_dense().numpy().tolist() == (dense * 2).tolist()
+    row = ms.RowTensor([0, 2, 0], torch.ones(3, 2), (3, 2))
+    assert row.to_dense().numpy().tolist() == [[2, 2], [0, 0], [1, 1]]
+    with pytest.raises(ValueError):
+        ms.CSRTensor([0, 1], [0], [1.0], (3, 3))
+
+
+def test_symbol_and_hints():
+    s = ms.Symbol(max=64, min=8, divisor=8)
+    assert s.admits(16) and not s.admits(12) and not s.admits(128)
+    with pytest.raises(ValueError):
+        ms.Symbol(divisor=4, remainder=4)
+    m = ms.mutable((1, 2.0))
+    assert isinstance(m[0], ms.Tensor) and float(m[1]) == 2.0
+    with pytest.raises(TypeError):
+        ms.mutable("text")
+
+    @ms.jit_class
+    class Cfg:
+        pass
+    assert Cfg.__ms_class__
+    ms.set_algo_parameters(fully_use_devices=False)
+    assert ms.get_algo_parameters("fully_use_devices") is False
+    ms.reset_algo_parameters()
+    assert ms.get_algo_parameters("fully_use_devices") is True
+    with pytest.raises(ValueError):
+        ms.set_algo_parameters(nonsense=1)
+
+
+def test_recompute_vmap_hessian():
+    net = nn.SequentialCell([nn.Dense(4, 8), nn.Tanh(), nn.Dense(8, 1)])
+    x = ms.Tensor(torch.randn(3, 4)).requires_grad_(True)
+    a = net(x).sum()
+    a.backward()
+    g_ref = [p.grad.clone() for p in net.trainable_params()]
+    for p in net.trainable_params():
+        p.grad = None
+    ms.recompute(net, x).sum().backward()
+    for p, g in zip(net.trainable_params(), g_ref):
+        torch.testing.assert_close(p.grad, g)
+    out = ms.vmap(lambda a, b: (a * b).sum(), (0, None))(ms.Tensor(torch.arange(6.0).reshape(3, 2)),
+                                                         ms.Tensor(torch.tensor([1.0, 10.0])))
+    assert out.tolist() == [10.0, 32.0, 54.0]
+    h = ms.hessian(lambda v: (v ** 3).sum())(ms.Tensor(torch.tensor([1.0, 2.0])))
+    np.testing.assert_allclose(np.asarray(h.detach().numpy()), np.diag([6.0, 12.0]), atol=1e-5)
+    g = ms.Generator().manual_seed(5)
+    assert g.initial_seed() == 5
+    st = g.get_state()
+    g.seed()
+    g.set_state(st)
+    assert g.initial_seed() == 5
+
+
+def test_scipy_namespace():
+    import mindspore_b200.scipy as sp
+    torch.manual_seed(0)
+    A = torch.randn(8, 8)
+    A = A @ A.t() + 8 * torch.eye(8)
+    b = torch.randn(8)
+    for solver in (sp.sparse.linalg.cg, sp.sparse.linalg.bicgstab, sp.sparse.linalg.gmres):
+        x, info = solver(A, b, tol=1e-6)
+        assert info == 0 and float((A @ torch.as_tensor(x) - b).norm()) < 1e-4
+    csr = ms.COOTensor(torch.nonzero(A), A[A != 0], (8, 8)).to_csr()
+    x, info = sp.sparse.linalg.cg(csr, b, tol=1e-6)
+    assert info == 0 and float((A @ torch.as_tensor(x) - b).norm()) < 1e-4
+    c = sp.linalg.cho_factor(A, lower=True)
+    assert float((A @ torch.as_tensor(sp.linalg.cho_solve(c, b)) - b).norm()) < 1e-4
+    L = torch.tril(A)
+    y = sp.linalg.solve_triangular(L, b, lower=True)
+    assert float((L @ torch.as_tensor(y) - b).norm()) < 1e-4
+    p, l, u = sp.linalg.lu(A)
+    torch.testing.assert_close(torch.as_tensor(p) @ torch.as_tensor(l) @ torch.as_tensor(u), A, rtol=1e-4, atol=1e-4)
+    assert sp.linalg.block_diag(torch.ones(2, 2), torch.ones(1, 3)).shape == (3, 5)
+
+    def rosen(v):
+        return 100 * (v[1] - v[0] ** 2) ** 2 + (1 - v[0]) ** 2
+    for method in ("BFGS", "LBFGS"):
+        r = sp.optimize.minimize(rosen, torch.tensor([-1.2, 1.0]), method=method, options={"maxiter": 300})
+        assert r.success and np.allclose(r.x.numpy(), [1, 1], atol=1e-3)
+
+
+def test_experimental_optim_and_schedulers():
+    from mindspore_b200.experimental import optim
+    ms.set_seed(0)
+    net = nn.Dense(4, 2)
+    ref = torch.nn.Linear(4, 2)
+    with torch.no_grad():
+        ref.weight.copy_(net.weight)
+        ref.bias.copy_(net.bias)
+    ours = optim.AdamW(net.trainable_params(), lr=0.1, weight_decay=0.05)
+    theirs = torch.optim.AdamW(ref.parameters(), lr=0.1, weight_decay=0.05)
+    sched = optim.lr_scheduler.MultiStepLR(ours, milestones=[2], gamma=0.1)
+    tsched = torch.optim.lr_scheduler.MultiStepLR(theirs, milestones=[2], gamma=0.1)
+    for i in range(4):
+        grads = [torch.full_like(p, 0.1 * (i + 1)) for p in ref.parameters()]
+        for p, g in zip(ref.parameters(), grads):
+            p.grad = g.clone()
+        theirs.step()
+        tsched.step()
+        ours(tuple(ms.Tensor(g) for g in grads))
+        sched.step()
+    torch.testing.assert_close(net.weight.detach().as_subclass(torch.Tensor), ref.weight.detach())
+    assert ours.lrs == [g["lr"] for g in theirs.param_groups] and abs(ours.lrs[0] - 0.01) < 1e-12
+    assert sched.get_last_lr() == tsched.get_last_lr()
+
+
+def test_boost_less_bn_and_freeze():
+    from mindspore_b200 import boost
+    net = nn.SequentialCell([nn.Conv2d(1, 2, 3), nn.BatchNorm2d(2), nn.Conv2d(2, 2, 3), nn.BatchNorm2d(2),
+                             nn.Conv2d(2, 2, 3), nn.BatchNorm2d(2), nn.Conv2d(2, 2, 3), nn.BatchNorm2d(2)])
+    wrapped = boost.LessBN(net, keep=3)
+    assert wrapped.frozen == 1
+    opt = nn.SGD(net.trainable_params(), 0.1)
+    fz = boost.FreezeOpt(opt, freeze_p=0.5, total_steps=2)
+    n = len(net.trainable_params())
+    before = [p.detach().clone() for p in net.trainable_params()]
+    grads = tuple(ms.Tensor(torch.ones_like(p)) for p in net.trainable_params())
+    fz(grads)                      # t = 0: nothing frozen
+    fz(grads)                      # t = 1: a quarter frozen
+    fz(grads)                      # t = 2: half frozen
+    moved = [float((p.detach() - b).abs().max()) for p, b in zip(net.trainable_params(), before)]
+    assert abs(moved[0] - 0.1) < 1e-6 and abs(moved[-1] - 0.3) < 1e-6
+    assert fz.frozen_count() == n // 2
+    ab = boost.AutoBoost("O1")
+    assert ab.cfg["less_bn"] and ab.cfg["grad_freeze"] and not ab.cfg["adasum"]
+    with pytest.raises(ValueError):
+        boost.AutoBoost("O9")
