@@ -44,6 +44,16 @@ def _clone_state(params, prefix, init="zeros", dtype=None):
     return ParameterTuple(out)
 
 
+_grad_listeners = []
+
+
+def notify_grad_written(param):
+    """Called by backward kernels right after they have accumulated ``param``'s gradient into its arena slice
+    (``main_grad``); listeners use it to start the gradient collective of a bucket as soon as the bucket is complete."""
+    for fn in _grad_listeners:
+        fn(param)
+
+
 class ParamArena:
     """Flat storage for a list of same-dtype parameters: low-precision weights, fp32 master copy and fp32
     gradient accumulator, each one contiguous buffer; every parameter becomes a view of the weight buffer and

@@ -216,6 +216,9 @@ class TrainOneStepCell(Cell):
                 total = li.clone() if total is None else total + li
             loss = total / k
         else:
+            dp = getattr(opt, "_dp", None)
+            if dp is not None:
+                dp.begin_step()                # buckets are all-reduced as backward completes them
             with torch.enable_grad():
                 loss = net(*inputs)
             if self.sens != 1.0:

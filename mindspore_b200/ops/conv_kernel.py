@@ -33,6 +33,11 @@ _native.register_cuda_signature("msb_global_avgpool", _I, [_P, _P, _I, _I, _I, _
 CL = torch.channels_last
 
 
+def _notify(param):
+    from ..nn.optim import notify_grad_written
+    notify_grad_written(param)
+
+
 def available():
     return torch.cuda.is_available() and _native.cuda() is not None
 
@@ -159,6 +164,7 @@ class _ConvFn(torch.autograd.Function):
             if mg is not None:
                 mg.add_(dw)
                 dw = None
+                _notify(w)
             else:
                 dw = dw.to(w.dtype)
         if ctx.needs_input_grad[0]:
@@ -253,6 +259,7 @@ class _BnActFn(torch.autograd.Function):
             mg = getattr(ref, "main_grad", None)
             if mg is not None:
                 mg.add_(g)
+                _notify(ref)
             elif slot == 0:
                 out_g = g.to(ref.dtype)
             else:

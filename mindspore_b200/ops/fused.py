@@ -52,6 +52,8 @@ class _LinearFn(torch.autograd.Function):
             if mg is not None:
                 K.linear_wgrad(dy2, x2, out=mg, accumulate=True)
                 ctx.w_ref.grad_ready = True
+                from ..nn.optim import notify_grad_written
+                notify_grad_written(ctx.w_ref)
             else:
                 dw = K.linear_wgrad(dy2, x2, out_dtype=torch.bfloat16)
         if ctx.has_bias and ctx.needs_input_grad[2]:

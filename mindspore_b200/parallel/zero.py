@@ -17,6 +17,7 @@ python/mindspore/nn/optim/optimizer.py:_use_parallel_optimizer)."""
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -33,7 +34,9 @@ _native.register_cuda_signature("msb_reduce_scatter_symm", _I, [_U64P, _I, _I, _
 _native.register_cuda_signature("msb_adamw_allgather", _I, [_P, _P, _P, _P, _U64P, _I, _L, _L, _P, _P, _P])
 
 _SLICE_ALIGN = 128
+_last_overlapped = 0                   # buckets launched from inside backward so far (for tests / logs)
 _BUCKET_ELEMS = 64 * 1024 * 1024      # 256 MB of fp32 gradients per all-reduce bucket
+_OVERLAP_BUCKET_ELEMS = 4 * 1024 * 1024   # 16 MB buckets when the all-reduce overlaps backward (env MSB200_DP_OVERLAP)
 
 
 def _ptr_array(ptrs):
@@ -50,6 +53,7 @@ class DataParallelArena:
         self.world = self.group.size
         self.rank = self.group.ranks.index(M.get_rank())
         self.mean, self.shard = mean, bool(shard) and self.world > 1
+        self.overlap = os.environ.get("MSB200_DP_OVERLAP", "0") == "1"
         arena = self.arena
         self.local_only = [(arena.offsets[i], arena.offsets[i] + p.numel()) for i, p in enumerate(arena.params)
                            if getattr(p, "dp_local", False)]
@@ -93,6 +97,100 @@ class DataParallelArena:
             torch.cuda.synchronize()
             dist.barrier(group=self.group.pg)
 
+    # ------------------------------------------------------------------ overlap with backward
+    def _bucket_ranges(self):
+        if getattr(self, "_reduce_ranges", None) is None:
+            arena = self.arena
+            ranges, pos = [], 0
+            for s, e in sorted(self.local_only):
+                if s > pos:
+                    ranges.append((pos, s))
+                pos = max(pos, (e + _SLICE_ALIGN - 1) // _SLICE_ALIGN * _SLICE_ALIGN)
+            if pos < arena.total:
+                ranges.append((pos, arena.total))
+            step = _OVERLAP_BUCKET_ELEMS if self.overlap else _BUCKET_ELEMS
+            self._reduce_ranges = [(lo, min(lo + step, hi)) for s, hi in ranges for lo in range(s, hi, step)]
+        return self._reduce_ranges
+
+    def begin_step(self):
+        """Arms the overlap for one backward pass: every bucket whose parameters have all reported their gradient
+        (``nn.optim.notify_grad_written``, or a ``.grad`` that autograd accumulated) is all-reduced at once on a side
+        stream while backward goes on; ``allreduce`` afterwards only handles what is left and joins the stream.  Use
+        it only when the step runs a single backward (no micro-batch accumulation)."""
+        if not self.overlap or self.world == 1 or self.shard:
+            return False
+        from ..nn import optim as _optim
+        arena = self.arena
+        ranges = self._bucket_ranges()
+        if getattr(self, "_bucket_of", None) is None:
+            self._bucket_of, self._bucket_size = {}, [0] * len(ranges)
+            starts = [lo for lo, _ in ranges]
+            import bisect
+            for i, p in enumerate(arena.params):
+                off = arena.offsets[i]
+                b = bisect.bisect_right(starts, off) - 1
+                if b < 0 or off >= ranges[b][1] or getattr(p, "dp_local", False):
+                    continue
+                last = bisect.bisect_right(starts, off + p.numel() - 1) - 1
+                members = range(b, last + 1)               # a parameter that straddles buckets counts in each
+                self._bucket_of[id(p)] = list(members)
+                for m in members:
+                    self._bucket_size[m] += 1
+
+                def fold(param):
+                    g = param.grad
+                    if g is not None and self._armed:
+                        param.main_grad.add_(g.to(param.main_grad.dtype))
+                        param.grad = None
+                        self._on_grad(param)
+                if p.requires_grad and hasattr(p, "register_post_accumulate_grad_hook"):
+                    p.register_post_accumulate_grad_hook(fold)
+            _optim._grad_listeners.append(self._on_grad)
+            if arena.grads.is_cuda:
+                self._comm_stream = torch.cuda.Stream()
+        self._pending = list(self._bucket_size)
+        self._seen = set()
+        self._done = [False] * len(ranges)
+        self._armed = True
+        return True
+
+    def _on_grad(self, param):
+        if not getattr(self, "_armed", False):
+            return
+        key = id(param)
+        if key in self._seen or key not in self._bucket_of:
+            return
+        self._seen.add(key)
+        for b in self._bucket_of[key]:
+            self._pending[b] -= 1
+            if self._pending[b] == 0 and not self._done[b]:
+                self._launch(b)
+
+    def _launch(self, b):
+        lo, hi = self._reduce_ranges[b]
+        scale = 1.0 / self.world if self.mean else 1.0
+        stream = getattr(self, "_comm_stream", None)
+        if stream is None:
+            self._reduce_segment(lo, hi, scale)
+        else:
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                self._reduce_segment(lo, hi, scale)
+        self._done[b] = True
+        self.overlapped_buckets = getattr(self, "overlapped_buckets", 0) + 1
+        global _last_overlapped
+        _last_overlapped = self.overlapped_buckets
+
+    def _reduce_segment(self, lo, hi, scale):
+        from . import symm
+        seg = self.arena.grads[lo:hi]
+        if symm.fused_available(self.group):
+            symm.all_reduce_(seg, self.group, scale)
+        else:
+            CF._all_reduce_(seg, "sum", self.group)
+            if scale != 1.0:
+                seg.mul_(scale)
+
     # ------------------------------------------------------------------ plain data parallel
     def allreduce(self):
         """All-reduce (mean) of the gradient arena in buckets (``_BUCKET_ELEMS`` fp32 elements each, so the
@@ -101,26 +199,14 @@ class DataParallelArena:
         if self.world == 1:
             return
         arena, scale = self.arena, (1.0 / self.world if self.mean else 1.0)
-        if getattr(self, "_reduce_ranges", None) is None:
-            ranges, pos = [], 0
-            for s, e in sorted(self.local_only):
-                if s > pos:
-                    ranges.append((pos, s))
-                pos = max(pos, (e + _SLICE_ALIGN - 1) // _SLICE_ALIGN * _SLICE_ALIGN)
-            if pos < arena.total:
-                ranges.append((pos, arena.total))
-            self._reduce_ranges = [(lo, min(lo + _BUCKET_ELEMS, hi)) for s, hi in ranges
-                                   for lo in range(s, hi, _BUCKET_ELEMS)]
-        from . import symm
-        fused = symm.fused_available(self.group)
-        for lo, hi in self._reduce_ranges:
-            seg = arena.grads[lo:hi]
-            if fused:
-                symm.all_reduce_(seg, self.group, scale)
-            else:
-                CF._all_reduce_(seg, "sum", self.group)
-                if scale != 1.0:
-                    seg.mul_(scale)
+        armed = getattr(self, "_armed", False)
+        self._armed = False
+        for b, (lo, hi) in enumerate(self._bucket_ranges()):
+            if armed and self._done[b]:
+                continue                                   # already reduced on the side stream during backward
+            self._reduce_segment(lo, hi, scale)
+        if armed and getattr(self, "_comm_stream", None) is not None:
+            torch.cuda.current_stream().wait_stream(self._comm_stream)
         if scale != 1.0:
             for s, e in self.local_only:
                 arena.grads[s:e].mul_(scale)

@@ -130,3 +130,86 @@ def test_sharded_optimizer_on_2_gpus(fused):
     for worst, status, used_symm in run_ranks(_gpu_worker, 2, fused):
         assert status == 0 and used_symm == fused
         assert worst < 2e-2
+
+
+def _overlap_worker(rank, world, clip):
+    import os
+    os.environ["MSB200_DP_OVERLAP"] = "1"
+    from mindspore_b200.parallel import zero
+    zero._OVERLAP_BUCKET_ELEMS = 512                      # several buckets even for this small net
+    params, _ = _worker(rank, world, False, clip)
+    import mindspore_b200  # noqa: F401
+    return params, zero._last_overlapped
+
+
+def test_allreduce_overlapped_with_backward_matches_single_process():
+    """Buckets are all-reduced from inside backward as soon as their gradients are complete; the result must not
+    change and at least one bucket must really have been launched early."""
+    ref = _single(0.05)
+    for params, overlapped in run_ranks(_overlap_worker, 2, 0.05):
+        assert overlapped > 0
+        for name, value in params.items():
+            torch.testing.assert_close(value, ref[name], rtol=1e-5, atol=1e-6)
+
+
+def _gpu_overlap_worker(rank, world, overlap):
+    import os
+    os.environ["MSB200_DP_OVERLAP"] = "1" if overlap else "0"
+    import mindspore_b200 as ms
+    from mindspore_b200 import _native, nn
+    from mindspore_b200.communication import GlobalComm, init
+    from mindspore_b200.parallel import zero
+    zero._OVERLAP_BUCKET_ELEMS = 16 * 1024
+    torch.cuda.set_device(rank)
+    ms.set_context(device_target="GPU", device_id=rank)
+    init("nccl")
+    torch.manual_seed(11)
+    ms.set_seed(11)
+
+    class Net(nn.Cell):
+        def __init__(self):
+            super().__init__()
+            self.c1 = nn.Conv2d(64, 64, 3, dtype=torch.bfloat16)
+            self.bn1 = nn.BatchNorm2d(64)
+            self.c2 = nn.Conv2d(64, 128, 3, stride=2, dtype=torch.bfloat16)
+            self.bn2 = nn.BatchNorm2d(128)
+            self.fc = nn.Dense(128, 16, dtype=torch.bfloat16)
+            self.loss = nn.SoftmaxCrossEntropyWithLogits(sparse=True, reduction="mean")
+
+        def construct(self, x, y):
+            h = torch.relu(self.bn1(self.c1(x)))
+            h = torch.relu(self.bn2(self.c2(h)))
+            return self.loss(self.fc(h.mean((2, 3))).float(), y)
+
+    net = Net()
+    for p in net.get_parameters():
+        p.set_data(p.detach().cuda())
+    opt = nn.Momentum(net.trainable_params(), 0.05, 0.9, weight_decay=1e-4)
+    opt.set_data_parallel_group(GlobalComm.WORLD_COMM_GROUP, mean=True)
+    step = nn.TrainOneStepCell(net, opt)
+    step.set_train()
+    g = torch.Generator().manual_seed(100 + rank)
+    x = torch.randn(8, 64, 16, 16, generator=g).bfloat16().cuda()
+    y = torch.randint(0, 16, (8,), generator=g).cuda()
+    losses = [float(step(ms.Tensor(x), ms.Tensor(y))) for _ in range(4)]
+    torch.cuda.synchronize()
+    out = {p.name: p.detach().float().cpu() for p in net.trainable_params()}
+    status = _native.device_status()
+    torch.distributed.barrier()
+    ms.communication.release()
+    return out, losses, status, zero._last_overlapped
+
+
+@pytest.mark.gpu
+def test_overlapped_allreduce_on_2_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    base = run_ranks(_gpu_overlap_worker, 2, False)
+    over = run_ranks(_gpu_overlap_worker, 2, True)
+    for (p0, l0, s0, n0), (p1, l1, s1, n1) in zip(base, over):
+        assert s0 == 0 and s1 == 0 and n0 == 0 and n1 > 0
+        assert l1[-1] < l1[0]
+        for k in p0:
+            torch.testing.assert_close(p1[k], p0[k], rtol=2e-2, atol=2e-3)
+    for k in over[0][0]:                                   # both ranks hold the same weights
+        torch.testing.assert_close(over[0][0][k], over[1][0][k], rtol=0, atol=0)
