@@ -183,8 +183,10 @@ def _gpu_overlap_worker(rank, world, overlap):
 
     net = Net()
     for p in net.get_parameters():
-        p.set_data(p.detach().cuda())
+        # trainable parameters share one dtype (flat arena); moving statistics stay fp32
+        p.set_data(p.detach().to(torch.bfloat16).cuda() if p.requires_grad else p.detach().cuda())
     opt = nn.Momentum(net.trainable_params(), 0.05, 0.9, weight_decay=1e-4)
+    assert opt.arena is not None
     opt.set_data_parallel_group(GlobalComm.WORLD_COMM_GROUP, mean=True)
     step = nn.TrainOneStepCell(net, opt)
     step.set_train()
