@@ -36,7 +36,7 @@ _native.register_cuda_signature("msb_adamw_allgather", _I, [_P, _P, _P, _P, _U64
 _SLICE_ALIGN = 128
 _last_overlapped = 0                   # buckets launched from inside backward so far (for tests / logs)
 _BUCKET_ELEMS = 64 * 1024 * 1024      # 256 MB of fp32 gradients per all-reduce bucket
-_OVERLAP_BUCKET_ELEMS = 4 * 1024 * 1024   # 16 MB buckets when the all-reduce overlaps backward (env MSB200_DP_OVERLAP)
+_OVERLAP_BUCKET_ELEMS = 4 * 1024 * 1024   # 16 MB buckets when the all-reduce overlaps backward (MSB200_DP_OVERLAP=0 turns it off)
 
 
 def _ptr_array(ptrs):
@@ -53,7 +53,7 @@ class DataParallelArena:
         self.world = self.group.size
         self.rank = self.group.ranks.index(M.get_rank())
         self.mean, self.shard = mean, bool(shard) and self.world > 1
-        self.overlap = os.environ.get("MSB200_DP_OVERLAP", "0") == "1"
+        self.overlap = os.environ.get("MSB200_DP_OVERLAP", "1") != "0"
         arena = self.arena
         self.local_only = [(arena.offsets[i], arena.offsets[i] + p.numel()) for i, p in enumerate(arena.params)
                            if getattr(p, "dp_local", False)]
@@ -108,16 +108,23 @@ class DataParallelArena:
                 pos = max(pos, (e + _SLICE_ALIGN - 1) // _SLICE_ALIGN * _SLICE_ALIGN)
             if pos < arena.total:
                 ranges.append((pos, arena.total))
-            step = _OVERLAP_BUCKET_ELEMS if self.overlap else _BUCKET_ELEMS
+            step = _OVERLAP_BUCKET_ELEMS if self._overlap_eligible() else _BUCKET_ELEMS
             self._reduce_ranges = [(lo, min(lo + step, hi)) for s, hi in ranges for lo in range(s, hi, step)]
         return self._reduce_ranges
+
+    def _overlap_eligible(self):
+        """Overlap runs the gradient all-reduce on a side stream.  It is limited to pure data parallelism: with a
+        model-parallel or expert-parallel group the backward pass issues its own collectives over the same symmetric
+        buffers and barrier flags, and two streams must not interleave on those."""
+        return (self.overlap and self.world > 1 and not self.shard and not self.local_only
+                and getattr(self.opt, "_mp_group", None) is None)
 
     def begin_step(self):
         """Arms the overlap for one backward pass: every bucket whose parameters have all reported their gradient
         (``nn.optim.notify_grad_written``, or a ``.grad`` that autograd accumulated) is all-reduced at once on a side
         stream while backward goes on; ``allreduce`` afterwards only handles what is left and joins the stream.  Use
         it only when the step runs a single backward (no micro-batch accumulation)."""
-        if not self.overlap or self.world == 1 or self.shard:
+        if not self._overlap_eligible():
             return False
         from ..nn import optim as _optim
         arena = self.arena

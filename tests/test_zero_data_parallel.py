@@ -133,8 +133,6 @@ def test_sharded_optimizer_on_2_gpus(fused):
 
 
 def _overlap_worker(rank, world, clip):
-    import os
-    os.environ["MSB200_DP_OVERLAP"] = "1"
     from mindspore_b200.parallel import zero
     zero._OVERLAP_BUCKET_ELEMS = 512                      # several buckets even for this small net
     params, _ = _worker(rank, world, False, clip)
