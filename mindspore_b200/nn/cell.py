@@ -411,7 +411,15 @@ class Cell:
         return self
 
     def place(self, role, rank_id):
+        """Pins this cell to process ``rank_id`` of ``role`` for MPMD execution (``parallel.mpmd.run_placed``)."""
+        if role not in ("MS_WORKER", "MS_SERVER", "MS_SCHED", "MS_PSERVER"):
+            raise ValueError("For 'Cell.place', 'role' must be MS_WORKER, MS_SERVER, MS_SCHED or MS_PSERVER, got %r"
+                             % (role,))
+        if not isinstance(rank_id, int) or isinstance(rank_id, bool) or rank_id < 0:
+            raise ValueError("For 'Cell.place', 'rank_id' must be a non-negative int, got %r" % (rank_id,))
         self.add_flags(ms_role=role, rank_id=rank_id)
+        object.__setattr__(self, "_placement", (role, rank_id))
+        return self
 
     # ------------------------------------------------------------------ hooks
     def register_forward_pre_hook(self, hook_fn):
