@@ -197,3 +197,122 @@ class TripletMarginLoss(LossBase):
     def construct(self, a, pos, neg):
         return _wrap_out(F.triplet_margin_loss(a, pos, neg, self.margin, self.p, self.eps, self.swap,
                                                reduction=self.reduction))
+
+
+# ------------------------------------------------------------------------------------------------ further losses
+class SoftMarginLoss(LossBase):
+    def construct(self, logits, labels):
+        return self.get_loss(torch.log1p(torch.exp(-labels.float() * logits.float())))
+
+
+class HingeEmbeddingLoss(LossBase):
+    def __init__(self, margin=1.0, reduction="mean"):
+        super().__init__(reduction)
+        self.margin = float(margin)
+
+    def construct(self, logits, labels):
+        x, y = logits.float(), labels.float()
+        return self.get_loss(torch.where(y > 0, x, (self.margin - x).clamp_min(0)))
+
+
+class PoissonNLLLoss(LossBase):
+    def __init__(self, log_input=True, full=False, eps=1e-8, reduction="mean"):
+        super().__init__(reduction)
+        self.log_input, self.full, self.eps = log_input, full, eps
+
+    def construct(self, input, target):      # noqa: A002
+        return self.get_loss(torch.nn.functional.poisson_nll_loss(input.float(), target.float(), self.log_input,
+                                                                   self.full, eps=self.eps, reduction="none"))
+
+
+class GaussianNLLLoss(LossBase):
+    def __init__(self, full=False, eps=1e-6, reduction="mean"):
+        super().__init__(reduction)
+        self.full, self.eps = full, eps
+
+    def construct(self, logits, labels, var):
+        return self.get_loss(torch.nn.functional.gaussian_nll_loss(logits.float(), labels.float(), var.float(),
+                                                                    self.full, self.eps, reduction="none"))
+
+
+class MultiLabelSoftMarginLoss(LossBase):
+    def __init__(self, weight=None, reduction="mean"):
+        super().__init__(reduction)
+        self.weight = weight
+
+    def construct(self, x, target):
+        x, t = x.float(), target.float()
+        loss = -(t * torch.nn.functional.logsigmoid(x) + (1 - t) * torch.nn.functional.logsigmoid(-x))
+        if self.weight is not None:
+            loss = loss * self.weight
+        return self.get_loss(loss.mean(-1))
+
+
+class MultilabelMarginLoss(LossBase):
+    def construct(self, x, target):
+        loss = torch.nn.functional.multilabel_margin_loss(x.float(), target.long(), reduction="none")
+        return self.get_loss(loss)
+
+
+class MultiMarginLoss(LossBase):
+    def __init__(self, p=1, margin=1.0, reduction="mean", weight=None):
+        super().__init__(reduction)
+        self.p, self.margin, self.weight = p, margin, weight
+
+    def construct(self, x, target, weight=None):
+        w = weight if weight is not None else self.weight
+        loss = torch.nn.functional.multi_margin_loss(x.float(), target.long(), self.p, self.margin,
+                                                     w.float() if w is not None else None, reduction="none")
+        return self.get_loss(loss)
+
+
+class MultiClassDiceLoss(LossBase):
+    def __init__(self, weights=None, ignore_indiex=None, activation="softmax"):
+        super().__init__("mean")
+        self.weights, self.ignore = weights, ignore_indiex
+        self.activation = {"softmax": lambda t: torch.softmax(t, 1), "sigmoid": torch.sigmoid, "relu": torch.relu,
+                           "tanh": torch.tanh, None: lambda t: t}[activation]
+        self.smooth = 1e-5
+
+    def construct(self, logits, label):
+        p, y = self.activation(logits.float()), label.float()
+        total = 0.0
+        for c in range(y.shape[1]):
+            if c == self.ignore:
+                continue
+            pc, yc = p[:, c].reshape(-1), y[:, c].reshape(-1)
+            dice = 1 - (2 * (pc * yc).sum() + self.smooth) / ((pc * pc).sum() + (yc * yc).sum() + self.smooth)
+            if self.weights is not None:
+                dice = dice * self.weights[c]
+            total = total + dice
+        return _wrap_out(total / y.shape[1])
+
+
+class SampledSoftmaxLoss(LossBase):
+    """Softmax cross entropy over the true class and ``num_sampled`` uniformly sampled negatives (with the
+    log-expected-count correction), for very large output vocabularies."""
+
+    def __init__(self, num_sampled, num_classes, num_true=1, sampled_values=None, remove_accidental_hits=True, seed=0,
+                 reduction="none"):
+        super().__init__(reduction)
+        self.num_sampled, self.num_classes, self.num_true = num_sampled, num_classes, num_true
+        self.sampled_values, self.remove_accidental_hits = sampled_values, remove_accidental_hits
+        self._gen = torch.Generator().manual_seed(seed)
+
+    def construct(self, weights, biases, labels, logits):
+        labels = labels.reshape(-1, self.num_true).long()
+        dev = logits.device
+        if self.sampled_values is not None:
+            sampled = torch.as_tensor(self.sampled_values[0]).long().to(dev)
+        else:
+            sampled = torch.randint(0, self.num_classes, (self.num_sampled,), generator=self._gen).to(dev)
+        q = self.num_sampled / self.num_classes
+        true_w, true_b = weights[labels], biases[labels]                                   # [B, T, D], [B, T]
+        true_logit = (logits.unsqueeze(1) * true_w).sum(-1) + true_b - torch.log(torch.tensor(q, device=dev))
+        samp_logit = logits @ weights[sampled].t() + biases[sampled] - torch.log(torch.tensor(q, device=dev))
+        if self.remove_accidental_hits:
+            hit = (sampled.reshape(1, 1, -1) == labels.unsqueeze(-1)).any(1)
+            samp_logit = samp_logit.masked_fill(hit, -1e9)
+        all_logits = torch.cat([true_logit, samp_logit], 1).float()
+        target = torch.cat([torch.full_like(true_logit, 1.0 / self.num_true), torch.zeros_like(samp_logit)], 1).float()
+        return self.get_loss(-(target * torch.log_softmax(all_logits, -1)).sum(-1))
