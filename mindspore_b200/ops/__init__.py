@@ -8,3 +8,5 @@ from .primitive import (Primitive, PrimitiveWithCheck, PrimitiveWithInfer, const
 from . import functional as F  # noqa: N812
 from . import operations as P  # noqa: N812
 from . import composite as C  # noqa: N812
+from .composite import (Shard, UnpackCall, ZipOperation, choice_with_mask, count_nonzero, dot, gamma, laplace,  # noqa: E402,F401
+                        poisson, repeat_elements, sequence_mask, tensor_dot, vmap)

@@ -318,3 +318,114 @@ def clip_by_global_norm(x, clip_norm=1.0, use_norm=None):
         use_norm = torch.sqrt(sum((t.float() ** 2).sum() for t in x))
     scale = clip_norm / torch.maximum(use_norm, torch.as_tensor(float(clip_norm), device=use_norm.device))
     return tuple((t * scale.to(t.dtype)) for t in x)
+
+
+# ------------------------------------------------------------------------------------------------ further composites
+def _wrap_out(o):
+    from .primitive import _wrap_out as w
+    return w(o)
+
+
+class ZipOperation:
+    """``zip`` over tuples usable inside compiled code (ops/composite/base.py ``ZipOperation``)."""
+
+    def __call__(self, *seqs):
+        return tuple(zip(*seqs))
+
+
+class UnpackCall:
+    """``fn(*args_tuple, **kwargs_dict)`` (ops/composite/base.py ``UnpackCall``)."""
+
+    def __call__(self, fn, *packs):
+        args, kwargs = [], {}
+        for p in packs:
+            if isinstance(p, dict):
+                kwargs.update(p)
+            else:
+                args += list(p)
+        return fn(*args, **kwargs)
+
+
+class Shard:
+    """Functional form of ``ms.shard``: ``Shard()(fn, in_strategy, out_strategy, ...)``."""
+
+    def __call__(self, fn, in_strategy, out_strategy=None, parameter_plan=None, device="Ascend", level=0):
+        from ..parallel.shard import shard as _shard
+        return _shard(fn, in_strategy, out_strategy, parameter_plan, device, level)
+
+
+def count_nonzero(x, axis=(), keep_dims=False, dtype=torch.int32):
+    x = _as_plain(x)
+    axis = tuple(range(x.dim())) if axis in ((), None) else axis
+    out = (x != 0).sum(axis, keepdim=keep_dims)
+    return _wrap_out(out.to(dtype))
+
+
+def _as_plain(x):
+    return x if isinstance(x, torch.Tensor) else torch.as_tensor(x)
+
+
+def tensor_dot(x1, x2, axes):
+    return _wrap_out(torch.tensordot(_as_plain(x1), _as_plain(x2), dims=axes))
+
+
+def dot(x1, x2):
+    """Dot product over the last dim of ``x1`` and the second-to-last of ``x2`` (all leading dims kept, NumPy
+    ``dot`` semantics for N-d inputs)."""
+    a, b = _as_plain(x1), _as_plain(x2)
+    if a.dim() <= 2 and b.dim() <= 2:
+        return _wrap_out(a @ b)
+    return _wrap_out(torch.tensordot(a, b, dims=([-1], [-2 if b.dim() > 1 else 0])))
+
+
+def repeat_elements(x, rep, axis=0):
+    return _wrap_out(torch.repeat_interleave(_as_plain(x), int(rep), dim=axis))
+
+
+def sequence_mask(lengths, maxlen=None):
+    lengths = _as_plain(lengths)
+    n = int(lengths.max()) if maxlen is None else int(maxlen)
+    return _wrap_out(torch.arange(n, device=lengths.device) < lengths.unsqueeze(-1))
+
+
+def _seeded(seed):
+    g = torch.Generator()
+    if seed is not None:
+        g.manual_seed(int(seed))
+    else:
+        g.seed()
+    return g
+
+
+def gamma(shape, alpha, beta, seed=None):
+    a = _as_plain(alpha).float().expand(tuple(shape)).contiguous()
+    g = _seeded(seed)
+    return _wrap_out(torch._standard_gamma(a, generator=g) / _as_plain(beta).float())
+
+
+def poisson(shape, mean, seed=None):
+    m = _as_plain(mean).float().expand(tuple(shape)).contiguous()
+    return _wrap_out(torch.poisson(m, generator=_seeded(seed)).to(torch.int32))
+
+
+def laplace(shape, mean, lambda_param, seed=None):
+    u = torch.rand(tuple(shape), generator=_seeded(seed)) - 0.5
+    return _wrap_out(_as_plain(mean).float() - _as_plain(lambda_param).float() * torch.sign(u) *
+                     torch.log1p(-2 * u.abs()))
+
+
+def choice_with_mask(input_x, count=256, seed=None):
+    x = _as_plain(input_x)
+    idx = torch.nonzero(x)
+    perm = torch.randperm(idx.shape[0], generator=_seeded(seed))[:count]
+    chosen = idx[perm]
+    out = torch.zeros((count, x.dim()), dtype=torch.int32)
+    out[:chosen.shape[0]] = chosen.to(torch.int32)
+    mask = torch.zeros(count, dtype=torch.bool)
+    mask[:chosen.shape[0]] = True
+    return _wrap_out(out), _wrap_out(mask)
+
+
+def vmap(fn, in_axes=0, out_axes=0):
+    from ..common.api import vmap as _vmap
+    return _vmap(fn, in_axes, out_axes)

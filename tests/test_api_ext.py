@@ -144,3 +144,24 @@ def test_boost_less_bn_and_freeze():
     assert ab.cfg["less_bn"] and ab.cfg["grad_freeze"] and not ab.cfg["adasum"]
     with pytest.raises(ValueError):
         boost.AutoBoost("O9")
+
+
+def test_composite_functions():
+    from mindspore_b200 import ops
+    x = ms.Tensor(torch.tensor([[0, 1, 2], [0, 0, 3]]))
+    assert ops.count_nonzero(x, axis=1).tolist() == [2, 1] and int(ops.count_nonzero(x)) == 3
+    assert ops.sequence_mask(ms.Tensor(torch.tensor([1, 3])), 4).tolist() == [[True, False, False, False],
+                                                                               [True, True, True, False]]
+    a, b = torch.randn(2, 3, 4), torch.randn(5, 4, 6)
+    np.testing.assert_allclose(ops.dot(ms.Tensor(a), ms.Tensor(b)).numpy(), np.dot(a.numpy(), b.numpy()), rtol=1e-5,
+                               atol=1e-5)
+    assert ops.repeat_elements(ms.Tensor(torch.tensor([1, 2])), 2).tolist() == [1, 1, 2, 2]
+    assert ops.ZipOperation()((1, 2), (3, 4)) == ((1, 3), (2, 4))
+    assert ops.UnpackCall()(lambda p, q, r=0: p + q + r, (1, 2), {"r": 3}) == 6
+    assert torch.equal(ops.poisson((4,), 3.0, seed=2), ops.poisson((4,), 3.0, seed=2))
+    g = ops.gamma((2000,), 3.0, 2.0, seed=0)
+    assert abs(float(g.mean()) - 1.5) < 0.1
+    lp = ops.laplace((4000,), 1.0, 2.0, seed=0)
+    assert abs(float(lp.mean()) - 1.0) < 0.2 and abs(float(lp.std()) - 2 * 2 ** 0.5) < 0.3
+    idx, mask = ops.choice_with_mask(ms.Tensor(torch.tensor([1, 0, 1, 1])), 4, seed=0)
+    assert mask.tolist() == [True, True, True, False] and sorted(idx[:3, 0].tolist()) == [0, 2, 3]
