@@ -205,7 +205,10 @@ class COOTensor:
         return len(self.shape)
 
     def _torch(self):
-        return torch.sparse_coo_tensor(self.indices.t().long(), self.values, self.shape, check_invariants=True)
+        import warnings
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)          # torch announces its invariant-check default once
+            return torch.sparse_coo_tensor(self.indices.t().long(), self.values, self.shape, check_invariants=True)
 
     def to_dense(self):
         return Tensor(self._torch().to_dense())

@@ -165,3 +165,26 @@ def test_composite_functions():
     assert abs(float(lp.mean()) - 1.0) < 0.2 and abs(float(lp.std()) - 2 * 2 ** 0.5) < 0.3
     idx, mask = ops.choice_with_mask(ms.Tensor(torch.tensor([1, 0, 1, 1])), 4, seed=0)
     assert mask.tolist() == [True, True, True, False] and sorted(idx[:3, 0].tolist()) == [0, 2, 3]
+
+
+def test_mindspore_only_tensor_methods():
+    t = ms.Tensor(torch.tensor([[1., 5., 3.], [4., 2., 6.]]))
+    assert t.ptp(1).tolist() == [4.0, 4.0] and float(t.ptp()) == 5.0
+    assert float(t.itemset((0, 1), 9.0)[0, 1]) == 9.0 and float(t[0, 1]) == 5.0
+    assert t.gather_nd(ms.Tensor(torch.tensor([[0, 1], [1, 2]]))).tolist() == [5.0, 6.0]
+    a = ms.Tensor(torch.tensor([1, 3, 5]))
+    assert a.searchsorted(ms.Tensor(torch.tensor([0, 3, 6]))).tolist() == [0, 1, 3]
+    assert a.searchsorted(ms.Tensor(torch.tensor([0, 3, 6])), side="right").tolist() == [0, 2, 3]
+    ch = [ms.Tensor(torch.tensor(v)) for v in ([1, 2, 3], [4, 5, 6], [7, 8, 9])]
+    assert ms.Tensor(torch.tensor([2, 0, 1])).choose(ch).tolist() == [7, 2, 6]
+    assert float(t.scatter_mul(ms.Tensor(torch.tensor([[0, 0]])), ms.Tensor(torch.tensor([10.0])))[0, 0]) == 10.0
+    u, idx = ms.Tensor(torch.tensor([3, 1, 3, 2])).unique_with_pad(0)
+    assert u.tolist() == [3, 1, 2, 0] and idx.tolist() == [0, 1, 0, 2]
+    assert ms.Tensor(torch.tensor([0, 2])).one_hot(3).tolist() == [[1, 0, 0], [0, 0, 1]]
+    assert t.unsorted_segment_sum(ms.Tensor(torch.tensor([0, 0])), 2).tolist() == [[5.0, 7.0, 9.0], [0.0, 0.0, 0.0]]
+    assert t.to_csr().to_dense().tolist() == t.tolist() and t.to_coo().size == 6
+    assert ms.Tensor.from_numpy(np.arange(3)).tolist() == [0, 1, 2]
+    assert len(t.get_bytes()) == 24 and t.fills(2.0).tolist() == [[2.0] * 3] * 2
+    assert ms.Tensor(torch.tensor([0.1, 2.5, 7.0])).bucketize([1.0, 3.0]).tolist() == [0, 1, 2]
+    with pytest.raises(ValueError):
+        t.move_to("TPU")
