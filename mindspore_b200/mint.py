@@ -43,12 +43,47 @@ multiply = _wrap(torch.mul)
 subtract = _wrap(torch.sub)
 negative = _wrap(torch.neg)
 absolute = _wrap(torch.abs)
+for _n in """addbmm addmm addmv clone randn randn_like randint randint_like randperm transpose swapaxes t mm mv dot
+cross diag trace kron argsort bincount cummax cummin diff count_nonzero histc kthvalue msort nansum amax amin
+aminmax allclose equal exp2 expm1 log2 log10 logaddexp hypot floor_divide true_divide ldexp lerp frac xlogy sinc
+deg2rad rad2deg asinh acosh atanh bernoulli multinomial empty empty_like arange meshgrid tensor_split hsplit vsplit
+dsplit unbind movedim squeeze unflatten triu_indices tril_indices select index_add scatter masked_fill take
+take_along_dim clamp_min clamp_max logical_xor bitwise_not floor_divide isreal signbit heaviside""".split():
+    if hasattr(torch, _n) and _n not in globals():
+        globals()[_n] = _wrap(getattr(torch, _n))
+special = types.ModuleType("mindspore_b200.mint.special")
+for _n in ("erfc", "expm1", "exp2", "round", "sinc", "log1p", "log_softmax", "digamma", "gammaln", "erfinv", "i0",
+           "i0e", "i1", "i1e", "logit", "expit", "xlogy", "zeta", "bessel_j0", "bessel_j1", "ndtr", "ndtri", "entr"):
+    if hasattr(torch.special, _n):
+        setattr(special, _n, _wrap(getattr(torch.special, _n)))
+distributed = types.ModuleType("mindspore_b200.mint.distributed")
+
+
+def _fill_distributed():
+    from .communication import comm_func as _cf
+    from .communication import management as _m
+    distributed.init_process_group = lambda backend="nccl", **kw: _m.init(backend if backend != "hccl" else None)
+    distributed.destroy_process_group = lambda group=None: _m.release()
+    distributed.get_rank = _m.get_rank
+    distributed.get_world_size = _m.get_group_size
+    distributed.new_group = lambda ranks=None, **kw: (_m.create_group(_m.stage_rank_list_name(ranks), list(ranks)),
+                                                     _m.stage_rank_list_name(ranks))[1]
+    distributed.get_backend = lambda group=None: _m.GlobalComm.BACKEND
+    for _name in ("all_reduce", "all_gather_into_tensor", "reduce_scatter_tensor", "reduce", "broadcast", "barrier",
+                  "isend", "irecv", "batch_isend_irecv", "scatter_tensor", "gather_into_tensor"):
+        if hasattr(_cf, _name):
+            setattr(distributed, _name, getattr(_cf, _name))
+    distributed.P2POp = getattr(_cf, "P2POp", None)
 
 nn = types.ModuleType("mindspore_b200.mint.nn")
 optim = types.ModuleType("mindspore_b200.mint.optim")
 linalg = types.ModuleType("mindspore_b200.mint.linalg")
 linalg.norm = _wrap(torch.linalg.norm)
 linalg.inv = _wrap(torch.linalg.inv)
+for _n in ("det", "slogdet", "qr", "svd", "eigh", "eig", "cholesky", "solve", "lstsq", "pinv", "matrix_norm",
+           "vector_norm", "matrix_rank", "cross", "matrix_power", "cond", "vander"):
+    if hasattr(torch.linalg, _n):
+        setattr(linalg, _n, _wrap(getattr(torch.linalg, _n)))
 
 
 def _fill_submodules():
@@ -72,6 +107,14 @@ def _fill_submodules():
     optim.AdamW = _nn.AdamWeightDecay
     optim.Adam = _nn.Adam
     optim.SGD = _nn.SGD
+    for name in ("Fold", "Unfold", "PixelShuffle", "Conv3d", "ConvTranspose2d", "L1Loss", "Softplus", "ELU", "PReLU",
+                 "LeakyReLU", "Hardtanh", "GLU", "AdaptiveAvgPool2d", "AdaptiveMaxPool2d", "Upsample"):
+        if hasattr(_nn, name) and not hasattr(nn, name):
+            setattr(nn, name, getattr(_nn, name))
+    if hasattr(_nn, "Conv2dTranspose"):
+        nn.ConvTranspose2d = _nn.Conv2dTranspose
+    _fill_distributed()
+    globals()["functional"] = functional
 
 
 _fill_submodules()

@@ -188,3 +188,18 @@ def test_mindspore_only_tensor_methods():
     assert ms.Tensor(torch.tensor([0.1, 2.5, 7.0])).bucketize([1.0, 3.0]).tolist() == [0, 1, 2]
     with pytest.raises(ValueError):
         t.move_to("TPU")
+
+
+def test_mint_namespace():
+    import mindspore_b200.mint as mint
+    out = mint.addmm(torch.ones(2, 2), torch.ones(2, 3), torch.ones(3, 2))
+    assert isinstance(out, ms.Tensor) and out.tolist() == [[4.0, 4.0], [4.0, 4.0]]
+    assert mint.randn(2, 3).shape == (2, 3) and mint.transpose(ms.Tensor(torch.ones(2, 3)), 0, 1).shape == (3, 2)
+    assert float(mint.special.erfc(torch.tensor(0.0))) == 1.0 and float(mint.linalg.det(torch.eye(3))) == 1.0
+    for name in ("all_reduce", "barrier", "get_rank", "get_world_size", "init_process_group", "new_group"):
+        assert hasattr(mint.distributed, name)
+    assert mint.nn.functional.relu(torch.tensor([-1.0, 1.0])).tolist() == [0.0, 1.0]
+    layer = mint.nn.Linear(3, 2)
+    assert layer(ms.Tensor(torch.ones(4, 3))).shape == (4, 2)
+    opt = mint.optim.AdamW(layer.trainable_params(), 1e-3)
+    assert opt is not None and mint.nn.Fold is not None and mint.nn.Unfold is not None
