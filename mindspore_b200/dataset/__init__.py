@@ -4,3 +4,6 @@ from .engine import (Dataset, GeneratorDataset, MindDataset, NumpySlicesDataset,
 from .mindrecord import FileReader, FileWriter
 from .native_loader import NativeBatchLoader
 from . import transforms, vision
+from . import samplers  # noqa: E402
+from .samplers import *  # noqa: E402,F401,F403
+from .sources import *  # noqa: E402,F401,F403

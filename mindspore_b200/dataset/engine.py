@@ -151,9 +151,23 @@ class GeneratorDataset(Dataset):
         self._epoch = 0
         if (num_shards is None) != (shard_id is None):
             raise ValueError("num_shards and shard_id must be given together")
+        self.sampler = sampler
+        if sampler is not None:
+            if not self.random_access:
+                raise ValueError("a sampler needs a random-access source (__getitem__ and __len__)")
+            if shuffle is not None or num_shards is not None:
+                raise ValueError("sampler cannot be combined with shuffle / num_shards / shard_id")
+            if not hasattr(sampler, "indices"):                       # a plain iterable of indices
+                from .samplers import SubsetSampler
+                self.sampler = SubsetSampler(list(sampler))
+            self.sampler.bind(len(source), getattr(source, "labels", None))
 
     def _indices(self):
         n = len(self.source)
+        if getattr(self, "sampler", None) is not None:
+            self.sampler._epoch = self._epoch
+            idx = np.asarray(self.sampler.indices())
+            return idx if self.num_samples is None else idx[:self.num_samples]
         idx = np.arange(n)
         if self.shuffle_flag:
             rng = np.random.default_rng(config.seed + self._epoch)

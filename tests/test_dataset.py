@@ -68,3 +68,65 @@ def test_model_train_consumes_dataset():
     model.train(60, data, dataset_sink_mode=False)
     pred = net(ms.Tensor(x)).detach().numpy()
     assert float(((pred - y) ** 2).mean()) < 0.1
+
+
+def _write_idx(path, arr):
+    import struct
+    with open(path, "wb") as f:
+        f.write(struct.pack(">HBB", 0, 8, arr.ndim) + struct.pack(">" + "I" * arr.ndim, *arr.shape) + arr.tobytes())
+
+
+def test_source_datasets_and_samplers(tmp_path):
+    import numpy as np
+    import mindspore_b200.dataset as ds
+    rng = np.random.default_rng(0)
+    imgs = rng.integers(0, 256, (20, 28, 28), dtype=np.uint8)
+    labs = (np.arange(20) % 4).astype(np.uint8)
+    _write_idx(str(tmp_path / "train-images-idx3-ubyte"), imgs)
+    _write_idx(str(tmp_path / "train-labels-idx1-ubyte"), labs)
+    mn = ds.MnistDataset(str(tmp_path), usage="train", shuffle=False)
+    rows = list(mn.create_dict_iterator(output_numpy=True, num_epochs=1))
+    assert len(rows) == 20 and rows[3]["image"].shape == (28, 28, 1) and int(rows[3]["label"]) == 3
+    assert np.array_equal(rows[5]["image"][..., 0], imgs[5])
+    # samplers
+    sub = ds.MnistDataset(str(tmp_path), usage="train", sampler=ds.SubsetSampler([4, 2, 9]))
+    assert [int(r["label"]) for r in sub.create_dict_iterator(output_numpy=True, num_epochs=1)] == [0, 2, 1]
+    parts = []
+    for sid in range(3):
+        d = ds.MnistDataset(str(tmp_path), usage="train", sampler=ds.DistributedSampler(3, sid, shuffle=False))
+        parts.append([int(np.where((imgs == r["image"][..., 0]).all((1, 2)))[0][0])
+                      for r in d.create_dict_iterator(output_numpy=True, num_epochs=1)])
+    assert all(len(p) == 7 for p in parts) and set(sum(parts, [])) == set(range(20))
+    pk = ds.MnistDataset(str(tmp_path), usage="train", sampler=ds.PKSampler(2))
+    assert sorted(int(r["label"]) for r in pk.create_dict_iterator(output_numpy=True, num_epochs=1)) == [0, 0, 1, 1, 2, 2, 3, 3]
+    w = ds.WeightedRandomSampler([0, 0, 1.0] + [0] * 17, num_samples=5).bind(20)
+    assert list(w) == [2] * 5
+    rs = ds.RandomSampler(num_samples=6).bind(20)
+    assert len(set(rs)) == 6
+    # cifar-10 binary
+    cdir = tmp_path / "cifar"
+    cdir.mkdir()
+    rec = np.zeros((5, 3073), np.uint8)
+    rec[:, 0] = [1, 2, 3, 4, 5]
+    rec[:, 1:] = rng.integers(0, 256, (5, 3072), dtype=np.uint8)
+    rec.tofile(str(cdir / "data_batch_1.bin"))
+    c = list(ds.Cifar10Dataset(str(cdir), usage="train", shuffle=False).create_dict_iterator(output_numpy=True, num_epochs=1))
+    assert len(c) == 5 and c[0]["image"].shape == (32, 32, 3) and int(c[4]["label"]) == 5
+    assert np.array_equal(c[0]["image"][:, :, 0].reshape(-1), rec[0, 1:1025])
+    # image folder (decoded with PIL)
+    from PIL import Image
+    for cls in ("cat", "dog"):
+        (tmp_path / "img" / cls).mkdir(parents=True)
+        for k in range(2):
+            Image.fromarray(rng.integers(0, 256, (6, 5, 3), dtype=np.uint8)).save(str(tmp_path / "img" / cls / ("%d.png" % k)))
+    f = ds.ImageFolderDataset(str(tmp_path / "img"), decode=True, shuffle=False)
+    fr = list(f.create_dict_iterator(output_numpy=True, num_epochs=1))
+    assert [int(r["label"]) for r in fr] == [0, 0, 1, 1] and fr[0]["image"].shape == (6, 5, 3)
+    assert f.get_class_indexing() == {"cat": 0, "dog": 1}
+    # text and csv
+    (tmp_path / "a.txt").write_text("hello world\n\nsecond line\n")
+    t = [str(r["text"]) for r in ds.TextFileDataset(str(tmp_path / "a.txt")).create_dict_iterator(output_numpy=True, num_epochs=1)]
+    assert t == ["hello world", "second line"]
+    (tmp_path / "a.csv").write_text("x,y,name\n1,2.5,a\n3,,b\n")
+    rows = list(ds.CSVDataset(str(tmp_path / "a.csv"), column_defaults=[0, 0.5, ""]).create_dict_iterator(output_numpy=True, num_epochs=1))
+    assert int(rows[1]["x"]) == 3 and float(rows[1]["y"]) == 0.5 and str(rows[0]["name"]) == "a"
