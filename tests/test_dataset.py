@@ -130,3 +130,43 @@ def test_source_datasets_and_samplers(tmp_path):
     (tmp_path / "a.csv").write_text("x,y,name\n1,2.5,a\n3,,b\n")
     rows = list(ds.CSVDataset(str(tmp_path / "a.csv"), column_defaults=[0, 0.5, ""]).create_dict_iterator(output_numpy=True, num_epochs=1))
     assert int(rows[1]["x"]) == 3 and float(rows[1]["y"]) == 0.5 and str(rows[0]["name"]) == "a"
+
+
+def test_vision_and_general_transforms():
+    import io
+    import numpy as np
+    from PIL import Image
+    import mindspore_b200.dataset.transforms as T
+    import mindspore_b200.dataset.vision as V
+    img = np.random.default_rng(0).integers(0, 256, (20, 30, 3), dtype=np.uint8)
+    buf = io.BytesIO()
+    Image.fromarray(img).save(buf, format="PNG")
+    assert np.array_equal(V.Decode()(np.frombuffer(buf.getvalue(), np.uint8)), img)
+    assert V.RandomResizedCrop(8)(img).shape == (8, 8, 3) and V.RandomCropDecodeResize(6)(
+        np.frombuffer(buf.getvalue(), np.uint8)).shape == (6, 6, 3)
+    t = V.ToTensor()(img)
+    assert t.shape == (3, 20, 30) and t.dtype == np.float32 and t.max() <= 1.0
+    assert V.Pad((1, 2))(img).shape == (24, 32, 3) and V.Pad(2, padding_mode=V.Border.REFLECT)(img)[0, 0, 0] == img[2, 2, 0]
+    assert V.Rotate(90, expand=True)(img).shape == (30, 20, 3)
+    assert np.array_equal(V.HorizontalFlip()(img), img[:, ::-1]) and np.array_equal(V.VerticalFlip()(img), img[::-1])
+    assert np.array_equal(V.Crop((2, 3), (4, 5))(img), img[2:6, 3:8]) and np.array_equal(V.Invert()(img), 255 - img)
+    g = V.Grayscale(3)(img)
+    assert g.shape == (20, 30, 3) and np.array_equal(g[..., 0], g[..., 2])
+    assert np.array_equal(V.AdjustBrightness(1.0)(img), img) and V.AdjustBrightness(0.0)(img).max() == 0
+    assert V.AdjustHue(0.2)(img).shape == img.shape and V.RandomColorAdjust(0.2, 0.2, 0.2, 0.1)(img).shape == img.shape
+    flat = np.full((9, 9, 1), 7, np.uint8)
+    assert np.array_equal(V.GaussianBlur(3)(flat), flat)
+    e = V.RandomErasing(prob=1.0, value=-1.0)(t)
+    assert (e == -1.0).any() and e.shape == t.shape
+    x, y = V.MixUpBatch()(np.stack([img] * 4), np.eye(4))
+    assert x.shape == (4, 20, 30, 3) and np.allclose(y.sum(1), 1)
+    x, y = V.CutMixBatch("NCHW")(np.zeros((4, 3, 8, 8)), np.eye(4))
+    assert x.shape == (4, 3, 8, 8) and np.allclose(y.sum(1), 1)
+    assert T.Mask("gt", 2)(np.array([1, 2, 3, 4])).tolist() == [False, False, True, True]
+    assert T.PadEnd([5], -1)(np.array([1, 2])).tolist() == [1, 2, -1, -1, -1]
+    u, idx, cnt = T.Unique()(np.array([3, 1, 3, 2]))
+    assert u.tolist() == [3, 1, 2] and idx.tolist() == [0, 1, 0, 2] and cnt.tolist() == [2, 1, 1]
+    assert T.Concatenate(0, prepend=[0], append=[9])(np.array([1, 2])).tolist() == [0, 1, 2, 9]
+    assert T.Slice(slice(1, 3))(np.arange(5)).tolist() == [1, 2] and T.Fill(3)(np.zeros(2)).tolist() == [3, 3]
+    assert T.RandomApply([lambda v: v + 1], prob=1.0)(np.array([1])).tolist() == [2]
+    assert T.RandomChoice([lambda v: v * 2])(np.array([2])).tolist() == [4]
