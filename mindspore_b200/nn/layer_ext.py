@@ -377,3 +377,196 @@ class MultiFieldEmbeddingLookup(Cell):
             cnt = torch.einsum("blf,bl->bf", onehot, input_values.to(emb.dtype)).clamp_min(1e-12)
             out = out / cnt.unsqueeze(-1)
         return _wrap_out(out)
+
+
+# ------------------------------------------------------------------------------------------------ simple functional layers
+def _fn_cell(name, fn, arg_names=(), defaults=(), doc=None):
+    """Cell whose constructor stores ``arg_names`` and whose construct calls ``fn(x, *stored)``."""
+    def __init__(self, *args, **kwargs):
+        Cell.__init__(self)
+        vals = dict(zip(arg_names, defaults))
+        vals.update(dict(zip(arg_names, args)))
+        for k, v in kwargs.items():
+            if k not in arg_names:
+                raise TypeError("%s got an unexpected keyword argument %r" % (name, k))
+            vals[k] = v
+        missing = [a for a in arg_names if a not in vals]
+        if missing:
+            raise TypeError("%s missing required arguments: %s" % (name, ", ".join(missing)))
+        for k, v in vals.items():
+            object.__setattr__(self, k, v)
+
+    def construct(self, x, *more):
+        return _wrap_out(fn(x, *more, *[getattr(self, a) for a in arg_names]))
+
+    cls = type(name, (Cell,), {"__init__": __init__, "construct": construct, "__doc__": doc or "%s layer." % name})
+    globals()[name] = cls
+    __all__.append(name)
+    return cls
+
+
+def _pad_cell(name, nd, mode):
+    def __init__(self, padding, value=0.0):
+        Cell.__init__(self)
+        p = (padding,) * (2 * nd) if isinstance(padding, int) else tuple(padding)
+        if len(p) != 2 * nd:
+            raise ValueError("%s needs an int or %d padding values, got %r" % (name, 2 * nd, padding))
+        self.padding, self.value = p, value
+
+    def construct(self, x):
+        if mode == "constant":
+            return _wrap_out(F.pad(x, self.padding, value=self.value))
+        return _wrap_out(F.pad(x, self.padding, mode=mode))
+
+    cls = type(name, (Cell,), {"__init__": __init__, "construct": construct,
+                               "__doc__": "%s padding of the last %d dims." % (mode, nd)})
+    globals()[name] = cls
+    __all__.append(name)
+
+
+for _nd in (1, 2, 3):
+    _pad_cell("ReflectionPad%dd" % _nd, _nd, "reflect")
+    _pad_cell("ReplicationPad%dd" % _nd, _nd, "replicate")
+    _pad_cell("ConstantPad%dd" % _nd, _nd, "constant")
+
+
+class ZeroPad2d(ConstantPad2d):      # noqa: F821
+    def __init__(self, padding):
+        super().__init__(padding, 0.0)
+
+
+__all__.append("ZeroPad2d")
+
+_fn_cell("MaxPool3d", lambda x, k, s, p, d, c: F.max_pool3d(x, k, s if s is not None else k, p, d, c),
+         ("kernel_size", "stride", "padding", "dilation", "ceil_mode"), (1, None, 0, 1, False))
+_fn_cell("AvgPool3d", lambda x, k, s, p, c, cip: F.avg_pool3d(x, k, s if s is not None else k, p, c, cip),
+         ("kernel_size", "stride", "padding", "ceil_mode", "count_include_pad"), (1, None, 0, False, True))
+_fn_cell("AdaptiveAvgPool1d", F.adaptive_avg_pool1d, ("output_size",))
+_fn_cell("AdaptiveAvgPool3d", F.adaptive_avg_pool3d, ("output_size",))
+_fn_cell("AdaptiveMaxPool1d", F.adaptive_max_pool1d, ("output_size",))
+_fn_cell("AdaptiveMaxPool3d", F.adaptive_max_pool3d, ("output_size",))
+_fn_cell("LPPool1d", lambda x, n, k, s, c: F.lp_pool1d(x, n, k, s, c), ("norm_type", "kernel_size", "stride", "ceil_mode"),
+         (2, 1, None, False))
+_fn_cell("LPPool2d", lambda x, n, k, s, c: F.lp_pool2d(x, n, k, s, c), ("norm_type", "kernel_size", "stride", "ceil_mode"),
+         (2, 1, None, False))
+_fn_cell("LRN", lambda x, r, b, a, be, nr="ACROSS_CHANNELS": F.local_response_norm(x, 2 * r + 1, a * (2 * r + 1), be, b),
+         ("depth_radius", "bias", "alpha", "beta", "norm_region"), (5, 1.0, 1.0, 0.5, "ACROSS_CHANNELS"))
+_fn_cell("Softmin", lambda x, axis: F.softmin(x, axis), ("axis",), (-1,))
+_fn_cell("Softmax2d", lambda x: F.softmax(x, -3))
+_fn_cell("Hardswish", F.hardswish)
+_fn_cell("Hardsigmoid", F.hardsigmoid)
+_fn_cell("SELU", F.selu)
+_fn_cell("CELU", lambda x, alpha: F.celu(x, alpha), ("alpha",), (1.0,))
+_fn_cell("Swish", F.silu)
+_fn_cell("HShrink", lambda x, lambd: F.hardshrink(x, lambd), ("lambd",), (0.5,))
+_fn_cell("SoftShrink", lambda x, lambd: F.softshrink(x, lambd), ("lambd",), (0.5,))
+Hardshrink, Softshrink = HShrink, SoftShrink      # noqa: F821
+__all__ += ["Hardshrink", "Softshrink"]
+_fn_cell("Roll", lambda x, shift, axis: torch.roll(x, shift, axis), ("shift", "axis"))
+_fn_cell("Tril", lambda x, k=0: torch.tril(x, k))
+_fn_cell("Triu", lambda x, k=0: torch.triu(x, k))
+_fn_cell("Unflatten", lambda x, axis, unflattened_size: torch.unflatten(x, axis, tuple(unflattened_size)),
+         ("axis", "unflattened_size"))
+_fn_cell("Norm", lambda x, axis, keep_dims: torch.linalg.vector_norm(x, 2, axis if axis != () else None, keep_dims),
+         ("axis", "keep_dims"), ((), False))
+_fn_cell("CosineSimilarity", lambda a, b, dim, eps: F.cosine_similarity(a, b, dim, eps), ("dim", "eps"), (1, 1e-8))
+_fn_cell("PairwiseDistance", lambda a, b, p, eps, keepdim: F.pairwise_distance(a, b, p, eps, keepdim),
+         ("p", "eps", "keepdim"), (2.0, 1e-6, False))
+_fn_cell("MaxUnpool2d", lambda x, idx, k, s, p: F.max_unpool2d(x, idx.long(), k, s, p), ("kernel_size", "stride", "padding"),
+         (1, None, 0))
+
+
+class RReLU(Cell):
+    def __init__(self, lower=1 / 8, upper=1 / 3):
+        super().__init__()
+        self.lower, self.upper = lower, upper
+
+    def construct(self, x):
+        return _wrap_out(F.rrelu(x, self.lower, self.upper, self.training))
+
+
+class _DropoutNd(Cell):
+    _fn = staticmethod(F.dropout2d)
+
+    def __init__(self, p=0.5):
+        super().__init__()
+        if not 0 <= p < 1:
+            raise ValueError("dropout probability must be in [0, 1), got %r" % (p,))
+        self.p = p
+
+    def construct(self, x):
+        return _wrap_out(type(self)._fn(x, self.p, self.training))
+
+
+class Dropout1d(_DropoutNd):
+    _fn = staticmethod(F.dropout1d)
+
+
+class Dropout2d(_DropoutNd):
+    _fn = staticmethod(F.dropout2d)
+
+
+class Dropout3d(_DropoutNd):
+    _fn = staticmethod(F.dropout3d)
+
+
+class ResizeBilinear(Cell):
+    def __init__(self, half_pixel_centers=False):
+        super().__init__()
+        self.half_pixel_centers = half_pixel_centers
+
+    def construct(self, x, size=None, scale_factor=None, align_corners=False):
+        return _wrap_out(F.interpolate(x, size=size, scale_factor=scale_factor, mode="bilinear",
+                                       align_corners=align_corners))
+
+
+class FractionalMaxPool2d(Cell):
+    def __init__(self, kernel_size, output_size=None, output_ratio=None, return_indices=False, _random_samples=None):
+        super().__init__()
+        self.args = (kernel_size, output_size, output_ratio, return_indices, _random_samples)
+
+    def construct(self, x):
+        k, o, r, ri, rs = self.args
+        return _wrap_out(F.fractional_max_pool2d(x, k, o, r, ri, rs))
+
+
+class ClipByNorm(Cell):
+    def __init__(self, axis=None):
+        super().__init__()
+        self.axis = axis
+
+    def construct(self, x, clip_norm):
+        n = torch.linalg.vector_norm(x.float(), 2, self.axis, keepdim=self.axis is not None)
+        c = torch.as_tensor(clip_norm, dtype=torch.float32, device=x.device)
+        return _wrap_out((x.float() * (c / torch.maximum(n, c))).to(x.dtype))
+
+
+class L1Regularizer(Cell):
+    def __init__(self, scale):
+        super().__init__()
+        if scale <= 0:
+            raise ValueError("For 'L1Regularizer', 'scale' must be positive, got %r" % (scale,))
+        self.scale = scale
+
+    def construct(self, weights):
+        return _wrap_out(self.scale * weights.abs().sum())
+
+
+class BiDense(Cell):
+    """y = x1^T W x2 + b with W [out, in1, in2]."""
+
+    def __init__(self, in1_channels, in2_channels, out_channels, weight_init=None, bias_init=None, has_bias=True,
+                 dtype=mstype.float32):
+        super().__init__()
+        k = 1 / math.sqrt(in1_channels)
+        self.weight = Parameter(initializer(weight_init or Uniform(k), (out_channels, in1_channels, in2_channels), dtype),
+                                name="weight")
+        self.bias = Parameter(initializer(bias_init or Uniform(k), (out_channels,), dtype), name="bias") if has_bias else None
+
+    def construct(self, x1, x2):
+        return _wrap_out(F.bilinear(x1, x2, self.weight, self.bias))
+
+
+Bilinear = BiDense
+__all__ += ["RReLU", "Dropout1d", "Dropout2d", "Dropout3d", "ResizeBilinear", "FractionalMaxPool2d", "ClipByNorm",
+            "L1Regularizer", "BiDense", "Bilinear"]

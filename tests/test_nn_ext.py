@@ -141,3 +141,40 @@ def test_adasum_two_ranks():
     for a, b in res:
         np.testing.assert_allclose(a, [-1.0, -1.0])          # orthogonal gradients add
         np.testing.assert_allclose(b, [-2.0, -2.0])          # identical deltas average
+
+
+def test_simple_layers_match_torch_functional():
+    import torch.nn.functional as F
+    torch.manual_seed(0)
+    x = torch.randn(2, 4, 6, 6)
+    X = _t(x)
+
+    def same(a, b):
+        torch.testing.assert_close(torch.as_tensor(a.detach().numpy()), b, rtol=1e-5, atol=1e-6)
+    same(nn.ReflectionPad2d(1)(X), F.pad(x, (1, 1, 1, 1), mode="reflect"))
+    same(nn.ReplicationPad2d((1, 0, 2, 0))(X), F.pad(x, (1, 0, 2, 0), mode="replicate"))
+    same(nn.ConstantPad2d(1, 3.0)(X), F.pad(x, (1, 1, 1, 1), value=3.0))
+    same(nn.ZeroPad2d((1, 2, 0, 0))(X), F.pad(x, (1, 2, 0, 0)))
+    x5 = torch.randn(1, 2, 4, 4, 4)
+    same(nn.MaxPool3d(2)(_t(x5)), F.max_pool3d(x5, 2))
+    same(nn.AvgPool3d(2, 2)(_t(x5)), F.avg_pool3d(x5, 2, 2))
+    same(nn.AdaptiveAvgPool1d(3)(_t(x5[0, :, 0])), F.adaptive_avg_pool1d(x5[0, :, 0], 3))
+    same(nn.Softmin()(X), F.softmin(x, -1))
+    same(nn.Hardswish()(X), F.hardswish(x))
+    same(nn.CELU(0.5)(X), F.celu(x, 0.5))
+    same(nn.HShrink(0.3)(X), F.hardshrink(x, 0.3))
+    same(nn.Roll(2, 1)(X), torch.roll(x, 2, 1))
+    same(nn.Unflatten(1, (2, 2))(X), x.unflatten(1, (2, 2)))
+    same(nn.Norm(axis=1)(X), x.norm(dim=1))
+    same(nn.CosineSimilarity()(X, _t(x * 2)), F.cosine_similarity(x, x * 2))
+    same(nn.LRN(2, 1.0, 1e-4, 0.75)(X), F.local_response_norm(x, 5, 5e-4, 0.75, 1.0))
+    a, b = torch.randn(3, 5), torch.randn(3, 7)
+    bd = nn.BiDense(5, 7, 4)
+    same(bd(_t(a), _t(b)), F.bilinear(a, b, bd.weight.detach().as_subclass(torch.Tensor),
+                                      bd.bias.detach().as_subclass(torch.Tensor)))
+    assert abs(float(nn.ClipByNorm()(_t(torch.ones(4) * 3), 1.0).norm()) - 1.0) < 1e-6
+    d = nn.Dropout2d(0.5)
+    d.set_train(False)
+    same(d(X), x)
+    y, idx = F.max_pool2d(x, 2, return_indices=True)
+    same(nn.MaxUnpool2d(2)(_t(y), _t(idx)), F.max_unpool2d(y, idx, 2))
