@@ -12,7 +12,7 @@ from ..ops.primitive import _wrap_out
 from .cell import Cell
 from .optim import Adam, Momentum, Optimizer, _to_plain
 
-__all__ = ["LazyAdam", "AdamOffload", "THOR", "thor", "AdaSumByGradWrapCell", "AdaSumByDeltaWeightWrapCell"]
+__all__ = ["ConvertNetUtils", "ConvertModelUtils", "LazyAdam", "AdamOffload", "THOR", "thor", "AdaSumByGradWrapCell", "AdaSumByDeltaWeightWrapCell"]
 
 
 class LazyAdam(Adam):
@@ -218,3 +218,22 @@ class AdaSumByGradWrapCell(_AdaSumWrap):
 class AdaSumByDeltaWeightWrapCell(_AdaSumWrap):
     """Runs the local update first and combines the resulting weight deltas with AdaSum."""
     _by_delta = True
+
+
+class ConvertNetUtils:
+    """Prepares a network for THOR.  The reference swaps Dense / Conv2d / Embedding cells for variants that record
+    the Kronecker factors; here ``THOR`` attaches hooks to the ordinary cells, so the network is returned as is."""
+
+    def convert_to_thor_net(self, net):
+        return net
+
+
+class ConvertModelUtils:
+    @staticmethod
+    def convert_to_thor_model(model, network, loss_fn=None, optimizer=None, metrics=None, amp_level="O0",
+                              loss_scale_manager=None, keep_batchnorm_fp32=False):
+        """Rebuilds ``model`` around ``network`` / ``optimizer`` (a ``THOR`` instance); other optimizers pass through."""
+        from ..train.model import Model
+        if not isinstance(optimizer, THOR):
+            return model
+        return Model(network, loss_fn, optimizer, metrics, amp_level=amp_level, loss_scale_manager=loss_scale_manager)

@@ -183,3 +183,34 @@ def _map(x, fn):
     if isinstance(x, (tuple, list)):
         return type(x)(_map(v, fn) for v in x)
     return _wrap_out(fn(x))
+
+
+def custom_mixed_precision(network, *, white_list=None, black_list=None, dtype=mstype.float16):
+    """Casts by an explicit list: with ``white_list`` only cells (or primitives' owning cells) of those types run in
+    ``dtype``; with ``black_list`` everything runs in ``dtype`` except those types.  Exactly one list must be given."""
+    if not isinstance(network, Cell):
+        raise TypeError("The network type should be Cell.")
+    if (white_list is None) == (black_list is None):
+        raise ValueError("For custom_mixed_precision, exactly one of white_list and black_list must be given")
+    if dtype not in (mstype.float16, mstype.bfloat16):
+        raise ValueError("The dtype should be one of (float16, bfloat16), but got %s" % dtype)
+    if white_list is not None:
+        kinds = tuple(t for t in white_list if isinstance(t, type))
+        for _, c in network.cells_and_names():
+            if kinds and isinstance(c, kinds):
+                c.to_float(dtype)
+    else:
+        kinds = tuple(t for t in black_list if isinstance(t, type))
+        network.to_float(dtype)
+        for _, c in network.cells_and_names():
+            if kinds and isinstance(c, kinds):
+                c.to_float(mstype.float32)
+    network._mixed_precision_type = dtype
+    return network
+
+
+def init_status():
+    """Fresh overflow-status tensor (eight zeros); the overflow check itself is ``all_finite`` on the gradients."""
+    import torch
+    from ..common.tensor import Tensor
+    return Tensor(torch.zeros(8, dtype=torch.float32))

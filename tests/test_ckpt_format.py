@@ -103,3 +103,34 @@ def test_encrypted_checkpoint_roundtrip(tmp_path, mode):
     torch.testing.assert_close(back["w"].as_subclass(torch.Tensor), w)
     with pytest.raises(ValueError):
         ms.load_checkpoint(path, dec_key=bytes(16), dec_mode=mode)
+
+
+def test_safetensors_round_trip_and_check(tmp_path):
+    import json
+    import struct
+    import numpy as np
+    import torch
+    import mindspore_b200 as ms
+    from mindspore_b200 import nn, train
+    ms.set_seed(3)
+    net = nn.SequentialCell([nn.Dense(3, 4), nn.Dense(4, 2)])
+    net[1].weight.set_data(net[1].weight.detach().to(torch.bfloat16))
+    ck = str(tmp_path / "m.ckpt")
+    ms.save_checkpoint(net, ck)
+    assert train.check_checkpoint(ck) and not train.check_checkpoint(str(tmp_path / "missing.ckpt"))
+    (tmp_path / "bad.ckpt").write_bytes(b"\x00\x01garbage")
+    assert not train.check_checkpoint(str(tmp_path / "bad.ckpt"))
+    out = train.ckpt_to_safetensors(ck)[0]
+    raw = open(out, "rb").read()
+    (n,) = struct.unpack_from("<Q", raw, 0)
+    header = json.loads(raw[8:8 + n])
+    assert header["0.weight"]["dtype"] == "F32" and header["1.weight"]["dtype"] == "BF16"
+    assert header["0.weight"]["shape"] == [4, 3]
+    st = train.load_safetensors(out)
+    assert st["1.weight"].dtype == torch.bfloat16
+    torch.testing.assert_close(st["0.weight"], net[0].weight.detach().as_subclass(torch.Tensor))
+    back = train.safetensors_to_ckpt(out, save_path=str(tmp_path / "again"))[0]
+    p = ms.load_checkpoint(back)
+    assert np.allclose(p["0.bias"].numpy(), net[0].bias.detach().numpy())
+    assert torch.equal(torch.as_tensor(p["1.weight"]).view(torch.int16),
+                       net[1].weight.detach().as_subclass(torch.Tensor).view(torch.int16))
