@@ -111,3 +111,24 @@ def test_merge_pipeline_strategies_and_sliced_parameter(tmp_path):
     strat = {"p": SC.ParamLayoutEntry.from_layout(lay).as_list()}
     out = CT.merge_sliced_parameter(parts, strat)
     torch.testing.assert_close(out.as_subclass(torch.Tensor), full)
+
+
+def test_get_ckpt_path_with_strategy_finds_a_replica(tmp_path):
+    """dev matrix (dp=2, mp=2), weight split over mp only: ranks 0 / 2 and 1 / 3 hold the same slices."""
+    from mindspore_b200 import nn, train
+    sf = SC.StrategyFile(0)
+    sf.layouts["w"] = _entry([2, 2], [0, -1])
+    spath = str(tmp_path / "strategy.ckpt")
+    sf.save(spath)
+    for r in (1, 2, 3):
+        d = tmp_path / ("rank_%d" % r)
+        d.mkdir()
+        ms.save_checkpoint(nn.Dense(2, 2), str(d / "net.ckpt"))
+    (tmp_path / "rank_0").mkdir()
+    (tmp_path / "rank_0" / "net.ckpt").write_bytes(b"damaged")
+    found = train.get_ckpt_path_with_strategy(str(tmp_path / "rank_0" / "net.ckpt"), spath)
+    assert found == str(tmp_path / "rank_2" / "net.ckpt")
+    ok = train.get_ckpt_path_with_strategy(str(tmp_path / "rank_1" / "net.ckpt"), spath)
+    assert ok == str(tmp_path / "rank_1" / "net.ckpt")
+    os.remove(str(tmp_path / "rank_2" / "net.ckpt"))
+    assert train.get_ckpt_path_with_strategy(str(tmp_path / "rank_0" / "net.ckpt"), spath) is None
