@@ -140,6 +140,15 @@ class Parameter(Tensor):
     def parallel_optimizer_comm_recompute(self, v):
         self._parallel_optimizer_comm_recompute = bool(v)
 
+    @property
+    def is_param_ps(self):
+        return getattr(self, "_is_param_ps", False)
+
+    def set_param_ps(self, init_in_server=False):
+        """Marks the parameter as living on the parameter server (``parallel.ps``)."""
+        self._is_param_ps = True
+        self._init_in_server = bool(init_in_server)
+
     def add_pipeline_stage(self, stage):
         if not isinstance(stage, int) or stage < 0:
             raise TypeError("`stage` must be a non-negative int")
