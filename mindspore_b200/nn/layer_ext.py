@@ -570,3 +570,212 @@ class BiDense(Cell):
 Bilinear = BiDense
 __all__ += ["RReLU", "Dropout1d", "Dropout2d", "Dropout3d", "ResizeBilinear", "FractionalMaxPool2d", "ClipByNorm",
             "L1Regularizer", "BiDense", "Bilinear"]
+
+
+# ------------------------------------------------------------------------------------------------ math / image / wrappers
+_fn_cell("ReduceLogSumExp", lambda x, axis, keep_dims: torch.logsumexp(x, axis, keep_dims), ("axis", "keep_dims"), (None, False))
+_fn_cell("LGamma", torch.lgamma)
+_fn_cell("DiGamma", torch.digamma)
+_fn_cell("IGamma", lambda a, x: torch.special.gammainc(a, x))
+_fn_cell("LBeta", lambda x, y: torch.lgamma(x) + torch.lgamma(y) - torch.lgamma(x + y))
+_fn_cell("MatDet", torch.linalg.det)
+_fn_cell("MatInverse", torch.linalg.inv)
+_fn_cell("MatrixDiag", torch.diag_embed)
+_fn_cell("MatrixDiagPart", lambda x: torch.diagonal(x, dim1=-2, dim2=-1))
+_fn_cell("MatrixSetDiag", lambda x, d: x - torch.diag_embed(torch.diagonal(x, dim1=-2, dim2=-1)) + torch.diag_embed(d))
+def _moments(x, axis, keep_dims):
+    t = x.float().as_subclass(torch.Tensor)
+    dims = tuple(range(t.dim())) if axis is None else axis
+    return torch.mean(t, dims, bool(keep_dims)), torch.var(t, dims, unbiased=False, keepdim=bool(keep_dims))
+
+
+_fn_cell("Moments", _moments, ("axis", "keep_dims"), (None, None))
+
+
+class MatMul(Cell):
+    def __init__(self, transpose_x1=False, transpose_x2=False):
+        super().__init__()
+        self.t1, self.t2 = transpose_x1, transpose_x2
+
+    def construct(self, x1, x2):
+        a = x1.transpose(-1, -2) if self.t1 else x1
+        b = x2.transpose(-1, -2) if self.t2 else x2
+        return _wrap_out(torch.matmul(a, b))
+
+
+class Range(Cell):
+    def __init__(self, start, limit=None, delta=1):
+        super().__init__()
+        if limit is None:
+            start, limit = 0, start
+        self.args = (start, limit, delta)
+
+    def construct(self):
+        return _wrap_out(torch.arange(*self.args))
+
+
+class CentralCrop(Cell):
+    def __init__(self, central_fraction):
+        super().__init__()
+        if not 0 < central_fraction <= 1:
+            raise ValueError("For 'CentralCrop', 'central_fraction' must be in (0, 1], got %r" % (central_fraction,))
+        self.f = central_fraction
+
+    def construct(self, image):
+        h, w = image.shape[-2:]
+        ch, cw = int(h * self.f), int(w * self.f)
+        t, l = (h - ch) // 2, (w - cw) // 2
+        return _wrap_out(image[..., t:t + ch, l:l + cw])
+
+
+class ImageGradients(Cell):
+    def construct(self, images):
+        dy = torch.zeros_like(images)
+        dx = torch.zeros_like(images)
+        dy[..., :-1, :] = images[..., 1:, :] - images[..., :-1, :]
+        dx[..., :, :-1] = images[..., :, 1:] - images[..., :, :-1]
+        return _wrap_out(dy), _wrap_out(dx)
+
+
+class PSNR(Cell):
+    def __init__(self, max_val=1.0):
+        super().__init__()
+        self.max_val = float(max_val)
+
+    def construct(self, img1, img2):
+        mse = ((img1.float() - img2.float()) ** 2).mean((-3, -2, -1))
+        return _wrap_out(10 * torch.log10(self.max_val ** 2 / mse))
+
+
+def _gauss_window(size, sigma, channels, device):
+    x = torch.arange(size, dtype=torch.float32, device=device) - (size - 1) / 2
+    g = torch.exp(-x * x / (2 * sigma * sigma))
+    g = g / g.sum()
+    return (g[:, None] * g[None]).expand(channels, 1, size, size).contiguous()
+
+
+def _ssim_terms(a, b, max_val, size, sigma, k1, k2):
+    c = a.shape[1]
+    w = _gauss_window(size, sigma, c, a.device)
+    mu_a, mu_b = F.conv2d(a, w, groups=c), F.conv2d(b, w, groups=c)
+    va = F.conv2d(a * a, w, groups=c) - mu_a ** 2
+    vb = F.conv2d(b * b, w, groups=c) - mu_b ** 2
+    cov = F.conv2d(a * b, w, groups=c) - mu_a * mu_b
+    c1, c2 = (k1 * max_val) ** 2, (k2 * max_val) ** 2
+    cs = (2 * cov + c2) / (va + vb + c2)
+    return ((2 * mu_a * mu_b + c1) / (mu_a ** 2 + mu_b ** 2 + c1)) * cs, cs
+
+
+class SSIM(Cell):
+    def __init__(self, max_val=1.0, filter_size=11, filter_sigma=1.5, k1=0.01, k2=0.03):
+        super().__init__()
+        self.args = (float(max_val), int(filter_size), float(filter_sigma), k1, k2)
+
+    def construct(self, img1, img2):
+        ssim, _ = _ssim_terms(img1.float(), img2.float(), *self.args)
+        return _wrap_out(ssim.mean((-3, -2, -1)))
+
+
+class MSSSIM(Cell):
+    def __init__(self, max_val=1.0, power_factors=(0.0448, 0.2856, 0.3001, 0.2363, 0.1333), filter_size=11,
+                 filter_sigma=1.5, k1=0.01, k2=0.03):
+        super().__init__()
+        self.weights = tuple(power_factors)
+        self.args = (float(max_val), int(filter_size), float(filter_sigma), k1, k2)
+
+    def construct(self, img1, img2):
+        a, b = img1.float(), img2.float()
+        out = 1.0
+        for i, w in enumerate(self.weights):
+            ssim, cs = _ssim_terms(a, b, *self.args)
+            last = i == len(self.weights) - 1
+            term = (ssim if last else cs).mean((-3, -2, -1)).clamp_min(0)
+            out = out * term ** w
+            if not last:
+                a, b = F.avg_pool2d(a, 2), F.avg_pool2d(b, 2)
+        return _wrap_out(out)
+
+
+class TimeDistributed(Cell):
+    """Applies ``layer`` to every slice along ``time_axis`` (folded into the batch axis for the call)."""
+
+    def __init__(self, layer, time_axis, reshape_with_axis=None):
+        super().__init__()
+        self.layer, self.time_axis, self.reshape_with_axis = layer, time_axis, reshape_with_axis
+
+    def construct(self, x):
+        t = self.time_axis % x.dim()
+        moved = x.movedim(t, 1) if t != 1 else x
+        b, steps = moved.shape[0], moved.shape[1]
+        y = self.layer(_wrap_out(moved.reshape((b * steps,) + tuple(moved.shape[2:]))))
+        y = y.reshape((b, steps) + tuple(y.shape[1:]))
+        return _wrap_out(y.movedim(1, t) if t != 1 else y)
+
+
+class ParameterUpdate(Cell):
+    """Cell whose call assigns a new value to ``param`` (e.g. to change a learning-rate parameter from outside)."""
+
+    def __init__(self, param):
+        super().__init__(auto_prefix=False)
+        if not isinstance(param, Parameter):
+            raise TypeError("For 'ParameterUpdate', 'param' must be a Parameter, got %s" % type(param).__name__)
+        self._param = param
+
+    def construct(self, x):
+        with torch.no_grad():
+            self._param.copy_(torch.as_tensor(x).to(self._param.dtype).reshape(self._param.shape))
+        return x
+
+
+class Jvp(Cell):
+    def __init__(self, fn):
+        super().__init__(auto_prefix=False)
+        self.fn = fn
+
+    def construct(self, *args):
+        from ..ops.composite import jvp
+        n = len(args) // 2
+        inputs, v = args[:n], args[n:]
+        return jvp(self.fn, inputs if n > 1 else inputs[0], v if n > 1 else v[0])
+
+
+class Vjp(Cell):
+    def __init__(self, fn):
+        super().__init__(auto_prefix=False)
+        self.fn = fn
+
+    def construct(self, *args):
+        from ..ops.composite import vjp
+        inputs, v = args[:-1], args[-1]
+        out, fn = vjp(self.fn, *inputs)
+        return out, fn(v)
+
+
+class VirtualDatasetCellTriple(Cell):
+    def __init__(self, backbone):
+        super().__init__(auto_prefix=False)
+        self._backbone = backbone
+
+    def construct(self, a, b, c):
+        return self._backbone(a, b, c)
+
+
+class SparseToDense(Cell):
+    def construct(self, coo_tensor):
+        return coo_tensor.to_dense()
+
+
+class SparseTensorDenseMatmul(Cell):
+    def __init__(self, adjoint_st=False, adjoint_dt=False):
+        super().__init__()
+        self.adj_s, self.adj_d = adjoint_st, adjoint_dt
+
+    def construct(self, indices, values, sparse_shape, dense):
+        s = torch.sparse_coo_tensor(indices.t().long(), values, tuple(int(v) for v in sparse_shape)).to_dense()
+        s = s.t() if self.adj_s else s
+        d = dense.t() if self.adj_d else dense
+        return _wrap_out(s @ d)
+
+
+__all__ += ["MatMul", "Range", "CentralCrop", "ImageGradients", "PSNR", "SSIM", "MSSSIM", "TimeDistributed",
+            "ParameterUpdate", "Jvp", "Vjp", "VirtualDatasetCellTriple", "SparseToDense", "SparseTensorDenseMatmul"]

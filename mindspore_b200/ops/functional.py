@@ -642,3 +642,79 @@ jvp = C.jvp
 jacfwd = C.jacfwd
 jacrev = C.jacrev
 partial = C.partial
+
+
+# ------------------------------------------------------------------------------------------------ further functions
+def _torch_fn(fn):
+    def f(*args, **kwargs):
+        return _wrap_out(fn(*args, **kwargs))
+    f.__name__ = getattr(fn, "__name__", "fn")
+    f.__doc__ = "Same arguments as torch.%s; returns framework tensors." % f.__name__
+    return f
+
+
+for _name in """argsort nonzero repeat_interleave scatter scatter_add cdist baddbmm outer inner kron roll rot90 meshgrid
+cumprod diff searchsorted bucketize histc bincount tensor_split hsplit vsplit dsplit narrow index_select masked_select
+take index_add index_fill bernoulli randperm rand_like randn_like randint_like polygamma mvlgamma allclose isreal
+is_complex is_floating_point numel addbmm addmm addmv addr trace det logdet slogdet inverse pinverse matrix_power
+cross dot mv mm vander tril_indices triu_indices combinations cartesian_prod block_diag atleast_1d atleast_2d
+atleast_3d column_stack row_stack hstack vstack dstack swapaxes moveaxis movedim flipud fliplr nan_to_num nansum
+nanmean nanmedian nanquantile quantile msort kthvalue mode median var_mean std_mean aminmax amax amin count_nonzero
+heaviside copysign nextafter ldexp frexp logaddexp logaddexp2 float_power fmax fmin hypot igamma igammac i0 sinc
+xlogy sgn signbit trapz trapezoid cumulative_trapezoid renorm gcd lcm deg2rad rad2deg bitwise_left_shift
+bitwise_right_shift logical_xor isneginf isposinf view_as_real view_as_complex real imag conj angle polar""".split():
+    if _name not in globals() and hasattr(torch, _name):
+        globals()[_name] = _torch_fn(getattr(torch, _name))
+
+
+def unique(input, sorted=True, return_inverse=False, return_counts=False, dim=None):    # noqa: A002
+    return _wrap_out(torch.unique(input, sorted=sorted, return_inverse=return_inverse, return_counts=return_counts,
+                                  dim=dim))
+
+
+def cummax(input, axis):          # noqa: A002
+    v, i = torch.cummax(input, axis)
+    return _wrap_out(v), _wrap_out(i)
+
+
+def cummin(input, axis):          # noqa: A002
+    v, i = torch.cummin(input, axis)
+    return _wrap_out(v), _wrap_out(i)
+
+
+def shuffle(x, seed=None):
+    g = torch.Generator()
+    g.manual_seed(int(seed)) if seed is not None else g.seed()
+    return _wrap_out(x[torch.randperm(x.shape[0], generator=g).to(x.device)])
+
+
+def inplace_update(x, v, indices):
+    out = x.clone()
+    out[torch.as_tensor(indices, device=x.device)] = v.to(x.dtype)
+    return _wrap_out(out)
+
+
+def swish(x):
+    return _wrap_out(torch.nn.functional.silu(x))
+
+
+def prelu(x, weight):
+    return _wrap_out(torch.nn.functional.prelu(x, weight))
+
+
+def batch_norm(input_x, running_mean, running_var, weight, bias, training=False, momentum=0.1, eps=1e-5):
+    return _wrap_out(torch.nn.functional.batch_norm(input_x, running_mean, running_var, weight, bias, training,
+                                                    momentum, eps))
+
+
+def grid_sample(input, grid, mode="bilinear", padding_mode="zeros", align_corners=False):      # noqa: A002
+    return _wrap_out(torch.nn.functional.grid_sample(input, grid, mode, padding_mode, align_corners))
+
+
+def unfold(input, kernel_size, dilation=1, padding=0, stride=1):      # noqa: A002
+    return _wrap_out(torch.nn.functional.unfold(input, kernel_size, dilation, padding, stride))
+
+
+def fold(input, output_size, kernel_size, dilation=1, padding=0, stride=1):      # noqa: A002
+    size = tuple(int(v) for v in (output_size.tolist() if isinstance(output_size, torch.Tensor) else output_size))
+    return _wrap_out(torch.nn.functional.fold(input, size, kernel_size, dilation, padding, stride))

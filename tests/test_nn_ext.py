@@ -178,3 +178,33 @@ def test_simple_layers_match_torch_functional():
     same(d(X), x)
     y, idx = F.max_pool2d(x, 2, return_indices=True)
     same(nn.MaxUnpool2d(2)(_t(y), _t(idx)), F.max_unpool2d(y, idx, 2))
+
+
+def test_math_image_and_wrapper_cells():
+    torch.manual_seed(0)
+    a = torch.rand(2, 3, 32, 32)
+    b = (a + 0.1 * torch.rand(2, 3, 32, 32)).clamp(0, 1)
+    s_same, s_diff = nn.SSIM()(_t(a), _t(a)), nn.SSIM()(_t(a), _t(b))
+    assert torch.allclose(s_same.as_subclass(torch.Tensor), torch.ones(2), atol=1e-6) and float(s_diff.max()) < 1.0
+    assert float(nn.MSSSIM(power_factors=(0.5, 0.5), filter_size=5)(_t(a), _t(a)).min()) > 0.9999
+    mse = ((a - b) ** 2).mean((1, 2, 3))
+    torch.testing.assert_close(nn.PSNR()(_t(a), _t(b)).as_subclass(torch.Tensor), 10 * torch.log10(1 / mse))
+    dy, dx = nn.ImageGradients()(_t(torch.arange(12.0).reshape(1, 1, 3, 4)))
+    assert dy[0, 0, 0].tolist() == [4.0] * 4 and dy[0, 0, 2].tolist() == [0.0] * 4 and dx[0, 0, 0].tolist() == [1, 1, 1, 0]
+    td = nn.TimeDistributed(nn.Dense(4, 2), 1)
+    x = torch.randn(3, 5, 4)
+    ref = torch.stack([td.layer(_t(x[:, i])).detach().as_subclass(torch.Tensor) for i in range(5)], 1)
+    torch.testing.assert_close(td(_t(x)).detach().as_subclass(torch.Tensor), ref)
+    assert nn.CentralCrop(0.5)(_t(a)).shape == (2, 3, 16, 16)
+    m, v = nn.Moments(axis=0)(_t(a))
+    torch.testing.assert_close(v.as_subclass(torch.Tensor), a.var(0, unbiased=False))
+    assert nn.MatrixSetDiag()(_t(torch.ones(2, 2)), _t(torch.tensor([5., 6.]))).tolist() == [[5, 1], [1, 6]]
+    p = ms.Parameter(_t(torch.tensor(0.1)), name="lr")
+    nn.ParameterUpdate(p)(_t(torch.tensor(0.5)))
+    assert float(p.detach()) == 0.5
+    out, g = nn.Vjp(lambda t: t ** 2)(_t(torch.tensor([1., 2.])), _t(torch.ones(2)))
+    assert out.tolist() == [1.0, 4.0] and torch.as_tensor(g[0] if isinstance(g, tuple) else g).tolist() == [2.0, 4.0]
+    from mindspore_b200 import ops
+    assert ops.argsort(_t(torch.tensor([3., 1., 2.]))).tolist() == [1, 2, 0]
+    assert ops.cummax(_t(torch.tensor([1., 3., 2.])), 0)[0].tolist() == [1, 3, 3]
+    assert sorted(ops.shuffle(_t(torch.arange(5)), seed=1).tolist()) == [0, 1, 2, 3, 4]
