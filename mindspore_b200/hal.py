@@ -167,3 +167,49 @@ def reset_max_memory_allocated(device_target="GPU"):
 def empty_cache():
     if torch.cuda.is_available():
         torch.cuda.empty_cache()
+
+
+def memory_summary(device_target="GPU"):
+    """Readable table of the allocator's counters."""
+    if not torch.cuda.is_available():
+        return "no CUDA device: the allocator keeps no statistics on CPU"
+    return torch.cuda.memory_summary()
+
+
+class contiguous_tensors_handle:      # noqa: N801  (name of the reference's module-level helper namespace)
+    """Views a list of same-dtype tensors as slices of one flat buffer (python/mindspore/hal/contiguous_tensors_handle.py):
+    ``handle[i]`` is tensor i backed by the flat storage, ``handle.buffer`` the whole buffer, ``slice_by_tensor_index``
+    / ``slice_by_padding_index`` give sub-ranges of it."""
+
+    def __init__(self, tensor_list, enable_mem_align=True):
+        if not tensor_list:
+            raise ValueError("contiguous_tensors_handle needs at least one tensor")
+        dt, dev = tensor_list[0].dtype, tensor_list[0].device
+        if any(t.dtype != dt for t in tensor_list):
+            raise TypeError("all tensors must have the same dtype")
+        align = (512 // tensor_list[0].element_size()) if enable_mem_align else 1
+        self.offsets, pos = [], 0
+        for t in tensor_list:
+            self.offsets.append((pos, pos + t.numel()))
+            pos = (pos + t.numel() + align - 1) // align * align
+        self.buffer = torch.zeros(pos, dtype=dt, device=dev)
+        self.tensors = []
+        for t, (a, b) in zip(tensor_list, self.offsets):
+            view = self.buffer[a:b].view(t.shape)
+            view.copy_(t.detach())
+            self.tensors.append(view)
+
+    def __getitem__(self, i):
+        return self.tensors[i]
+
+    def __len__(self):
+        return len(self.tensors)
+
+    def slice_by_tensor_index(self, start=None, end=None):
+        start, end = start or 0, len(self.tensors) if end is None else end
+        if not 0 <= start < end <= len(self.tensors):
+            raise ValueError("invalid tensor index range [%s, %s)" % (start, end))
+        return self.buffer[self.offsets[start][0]:self.offsets[end - 1][1]]
+
+    def slice_by_padding_index(self, start=None, end=None):
+        return self.buffer[start or 0:self.buffer.numel() if end is None else end]
