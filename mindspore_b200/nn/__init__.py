@@ -14,3 +14,4 @@ from .optim import (ASGD, FTRL, LARS, SGD, AdaFactor, Adadelta, Adagrad, Adam, A
 from .wrap import (DistributedGradReducer, DynamicLossScaleUpdateCell, FixedLossScaleUpdateCell, ForwardValueAndGrad,
                    GetNextSingleOp, GradAccumulationCell, MicroBatchInterleaved, PipelineCell, PipelineGradReducer,
                    TrainOneStepCell, TrainOneStepWithLossScaleCell, WithEvalCell, WithGradCell, WithLossCell)
+from . import probability  # noqa: E402,F401
