@@ -528,3 +528,200 @@ class _Prefetch(Dataset):
 
 def zip(datasets):  # noqa: A001
     return _Zip(tuple(datasets))
+
+
+# ------------------------------------------------------------------------------------------------ further operations
+class _Concat(Dataset):
+    def __init__(self, parents):
+        cols = parents[0].get_col_names()
+        for p in parents[1:]:
+            if p.get_col_names() != cols:
+                raise ValueError("concat: column names differ: %s vs %s" % (cols, p.get_col_names()))
+        super().__init__(parents[0], cols)
+        self.parents = list(parents)
+
+    def get_dataset_size(self):
+        return sum(p.get_dataset_size() for p in self.parents)
+
+    def _rows(self):
+        for p in self.parents:
+            yield from p._rows()
+
+
+class _Filter(Dataset):
+    def __init__(self, parent, predicate, input_columns):
+        super().__init__(parent)
+        self.predicate, self.cols = predicate, input_columns or parent.get_col_names()
+
+    def get_dataset_size(self):
+        return sum(1 for _ in self._rows())
+
+    def _rows(self):
+        for row in self.parent._rows():
+            if self.predicate(*[row[c] for c in self.cols]):
+                yield row
+
+
+class _FlatMap(Dataset):
+    def __init__(self, parent, func):
+        super().__init__(parent)
+        self.func = func
+
+    def get_dataset_size(self):
+        return sum(1 for _ in self._rows())
+
+    def _rows(self):
+        for row in self.parent._rows():
+            yield from self.func(*[row[c] for c in self.parent.get_col_names()])._rows()
+
+
+class _PaddedBatch(Dataset):
+    """Batches rows whose shapes differ: every column is padded to ``pad_info[col] = (shape, value)`` (None entries of
+    the shape, or a missing column, mean "longest in this batch")."""
+
+    def __init__(self, parent, batch_size, drop_remainder, pad_info):
+        super().__init__(parent)
+        self.batch_size, self.drop, self.pad_info = batch_size, drop_remainder, pad_info or {}
+
+    def get_dataset_size(self):
+        n = self.parent.get_dataset_size()
+        return n // self.batch_size if self.drop else -(-n // self.batch_size)
+
+    def _pad(self, col, arrays):
+        shape, value = self.pad_info.get(col, (None, 0))
+        arrays = [np.asarray(a) for a in arrays]
+        nd = arrays[0].ndim
+        target = [max(a.shape[d] for a in arrays) for d in range(nd)]
+        if shape is not None:
+            target = [t if s is None else s for t, s in builtins.zip(target, shape)]
+        out = np.full([len(arrays)] + target, value if value is not None else 0, dtype=arrays[0].dtype)
+        for i, a in enumerate(arrays):
+            sl = tuple(slice(0, min(s, t)) for s, t in builtins.zip(a.shape, target))
+            out[(i,) + sl] = a[sl]
+        return out
+
+    def _emit(self, rows):
+        return {c: self._pad(c, [r[c] for r in rows]) for c in self._columns}
+
+    def _rows(self):
+        buf = []
+        for row in self.parent._rows():
+            buf.append(row)
+            if len(buf) == self.batch_size:
+                yield self._emit(buf)
+                buf = []
+        if buf and not self.drop:
+            yield self._emit(buf)
+
+
+class _BucketBatch(_PaddedBatch):
+    def __init__(self, parent, column_names, boundaries, batch_sizes, length_fn, pad_info, pad_to_bucket_boundary,
+                 drop_remainder):
+        if len(batch_sizes) != len(boundaries) + 1:
+            raise ValueError("bucket_batch_by_length: need len(bucket_boundaries) + 1 batch sizes")
+        super().__init__(parent, 1, drop_remainder, pad_info)
+        self.cols, self.bounds, self.sizes = column_names, list(boundaries), list(batch_sizes)
+        self.length_fn = length_fn or (lambda *a: len(a[0]))
+        self.to_boundary = pad_to_bucket_boundary
+
+    def get_dataset_size(self):
+        return sum(1 for _ in self._rows())
+
+    def _rows(self):
+        import bisect
+        buckets = [[] for _ in self.sizes]
+        for row in self.parent._rows():
+            b = bisect.bisect_right(self.bounds, self.length_fn(*[row[c] for c in self.cols]))
+            buckets[b].append(row)
+            if len(buckets[b]) == self.sizes[b]:
+                yield self._emit_bucket(b, buckets[b])
+                buckets[b] = []
+        if not self.drop:
+            for b, rows in enumerate(buckets):
+                if rows:
+                    yield self._emit_bucket(b, rows)
+
+    def _emit_bucket(self, b, rows):
+        if self.to_boundary and b < len(self.bounds):
+            info = dict(self.pad_info)
+            for c in self.cols:
+                shape, value = info.get(c, (None, 0))
+                nd = np.asarray(rows[0][c]).ndim
+                shape = list(shape) if shape is not None else [None] * nd
+                shape[0] = self.bounds[b] - 1
+                info[c] = (shape, value)
+            saved, self.pad_info = self.pad_info, info
+            try:
+                return self._emit(rows)
+            finally:
+                self.pad_info = saved
+        return self._emit(rows)
+
+
+def _ds_concat(self, datasets):
+    others = list(datasets) if isinstance(datasets, (list, tuple)) else [datasets]
+    return _Concat([self] + others)
+
+
+def _ds_split(self, sizes, randomize=True):
+    """Splits into datasets of the given absolute sizes (ints) or fractions (floats summing to 1)."""
+    rows = list(self._rows())
+    n = len(rows)
+    if all(isinstance(s, float) for s in sizes):
+        if abs(sum(sizes) - 1) > 1e-6:
+            raise ValueError("split: fractions must sum to 1")
+        counts = [int(round(s * n)) for s in sizes]
+        counts[-1] = n - sum(counts[:-1])
+    else:
+        counts = [int(s) for s in sizes]
+        if sum(counts) != n:
+            raise ValueError("split: sizes %s do not add up to the dataset size %d" % (counts, n))
+    order = np.random.default_rng(config.seed).permutation(n) if randomize else np.arange(n)
+    out, pos = [], 0
+    cols = self.get_col_names()
+    for c in counts:
+        part = [rows[i] for i in order[pos:pos + c]]
+        pos += c
+        out.append(GeneratorDataset([tuple(r[k] for k in cols) for r in part] or [()], cols, shuffle=False)
+                   if part else _Take(self, 0))
+    return tuple(out)
+
+
+def _ds_save(self, file_name, num_files=1, file_type="mindrecord"):
+    if file_type != "mindrecord":
+        raise ValueError("save: only file_type 'mindrecord' is supported")
+    from .mindrecord import FileWriter
+    rows = list(self._rows())
+    if not rows:
+        raise RuntimeError("save: the dataset is empty")
+    schema = {}
+    for c, v in rows[0].items():
+        a = np.asarray(v)
+        kind = {"f": "float32" if a.dtype.itemsize <= 4 else "float64", "i": "int64" if a.dtype.itemsize > 4 else "int32",
+                "u": "int32", "b": "int32"}.get(a.dtype.kind, "string")
+        schema[c] = {"type": kind} if a.ndim == 0 else {"type": kind, "shape": [-1] if a.ndim == 1 else list(a.shape)}
+    w = FileWriter(file_name, shard_num=num_files)
+    w.add_schema(schema, "saved")
+    w.write_raw_data([{c: (np.asarray(v) if np.asarray(v).ndim else np.asarray(v).item()) for c, v in r.items()}
+                      for r in rows])
+    w.commit()
+
+
+Dataset.concat = _ds_concat
+Dataset.__add__ = lambda self, other: _Concat([self, other])
+Dataset.filter = lambda self, predicate, input_columns=None, num_parallel_workers=None: _Filter(self, predicate, input_columns)
+Dataset.flat_map = lambda self, func: _FlatMap(self, func)
+Dataset.apply = lambda self, apply_func: apply_func(self)
+Dataset.padded_batch = lambda self, batch_size, drop_remainder=False, num_parallel_workers=None, pad_info=None: \
+    _PaddedBatch(self, batch_size, drop_remainder, pad_info)
+Dataset.bucket_batch_by_length = lambda self, column_names, bucket_boundaries, bucket_batch_sizes, \
+    element_length_function=None, pad_info=None, pad_to_bucket_boundary=False, drop_remainder=False: \
+    _BucketBatch(self, column_names, bucket_boundaries, bucket_batch_sizes, element_length_function, pad_info,
+                 pad_to_bucket_boundary, drop_remainder)
+Dataset.split = _ds_split
+Dataset.save = _ds_save
+Dataset.device_que = lambda self, send_epoch_end=True, create_data_info_queue=False, queue_name="": self
+Dataset.to_device = Dataset.device_que
+Dataset.num_classes = lambda self: (len(set(int(np.asarray(r[self.get_col_names()[-1]])) for r in self._rows())))
+Dataset.reset = lambda self: None
+Dataset.close = lambda self: None

@@ -170,3 +170,36 @@ def test_vision_and_general_transforms():
     assert T.Slice(slice(1, 3))(np.arange(5)).tolist() == [1, 2] and T.Fill(3)(np.zeros(2)).tolist() == [3, 3]
     assert T.RandomApply([lambda v: v + 1], prob=1.0)(np.array([1])).tolist() == [2]
     assert T.RandomChoice([lambda v: v * 2])(np.array([2])).tolist() == [4]
+
+
+def test_concat_filter_flat_map_padded_and_bucket_batches(tmp_path):
+    import numpy as np
+    import mindspore_b200.dataset as ds
+    a = ds.NumpySlicesDataset(np.arange(5), ["x"], shuffle=False)
+    b = ds.NumpySlicesDataset(np.arange(10, 13), ["x"], shuffle=False)
+    both = a + b
+    vals = lambda d: [int(r["x"]) for r in d.create_dict_iterator(output_numpy=True, num_epochs=1)]
+    assert both.get_dataset_size() == 8 and vals(both) == [0, 1, 2, 3, 4, 10, 11, 12]
+    assert vals(a.concat([b, b]))[-3:] == [10, 11, 12]
+    assert vals(both.filter(lambda x: x % 2 == 0)) == [0, 2, 4, 10, 12]
+    fm = a.flat_map(lambda x: ds.NumpySlicesDataset(np.array([x, x]), ["x"], shuffle=False))
+    assert vals(fm) == [0, 0, 1, 1, 2, 2, 3, 3, 4, 4]
+    assert vals(a.apply(lambda d: d.take(2))) == [0, 1]
+    tr, te = a.split([3, 2], randomize=False)
+    assert vals(tr) == [0, 1, 2] and vals(te) == [3, 4]
+    p1, p2 = both.split([0.5, 0.5])
+    assert sorted(vals(p1) + vals(p2)) == sorted(vals(both))
+    seqs = [np.arange(n, dtype=np.int32) for n in (2, 5, 3, 1, 4, 6)]
+    g = ds.GeneratorDataset([(s,) for s in seqs], ["tok"], shuffle=False)
+    pb = list(g.padded_batch(3, pad_info={"tok": ([None], -1)}).create_dict_iterator(output_numpy=True, num_epochs=1))
+    assert pb[0]["tok"].shape == (3, 5) and pb[0]["tok"][0].tolist() == [0, 1, -1, -1, -1] and pb[1]["tok"].shape == (3, 6)
+    bb = list(g.bucket_batch_by_length(["tok"], [3, 5], [2, 2, 2], pad_to_bucket_boundary=True)
+              .create_dict_iterator(output_numpy=True, num_epochs=1))
+    shapes = sorted(tuple(x["tok"].shape) for x in bb)
+    assert shapes == [(2, 2), (2, 4), (2, 6)]
+    path = str(tmp_path / "saved.mindrecord")
+    ds.NumpySlicesDataset({"x": np.arange(4, dtype=np.int32), "y": np.arange(4, dtype=np.float32) * 0.5},
+                          shuffle=False).save(path)
+    back = ds.MindDataset(path, shuffle=False)
+    rows = list(back.create_dict_iterator(output_numpy=True, num_epochs=1))
+    assert [int(r["x"]) for r in rows] == [0, 1, 2, 3] and float(rows[3]["y"]) == 1.5
