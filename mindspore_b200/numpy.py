@@ -192,3 +192,100 @@ def isclose(a, b, rtol=1e-05, atol=1e-08, equal_nan=False):
 
 def allclose(a, b, rtol=1e-05, atol=1e-08):
     return bool(torch.allclose(_t(a), _t(b), rtol, atol))
+
+
+# ------------------------------------------------------------------------------------------------ wider coverage
+# Functions that torch offers under the same name and meaning are forwarded to torch (they stay on the device and
+# differentiable); the rest run through NumPy on the host and come back as tensors on the input's device.
+import numpy as _onp
+
+
+def _fwd(fn):
+    def f(*args, **kwargs):
+        kwargs = {("dim" if k == "axis" else "keepdim" if k == "keepdims" else k): v for k, v in kwargs.items()}
+        out = fn(*args, **kwargs)
+        return _w(out)
+    f.__name__ = getattr(fn, "__name__", "fn")
+    return f
+
+
+def _w(out):
+    from .ops.primitive import _wrap_out
+    if isinstance(out, (tuple, list)) and not isinstance(out, torch.Size):
+        return type(out)(_w(o) for o in out) if not hasattr(out, "_fields") else tuple(_w(o) for o in out)
+    return _wrap_out(out)
+
+
+for _n in """logspace diag diagflat trace meshgrid ravel swapaxes moveaxis vstack hstack dstack column_stack hsplit
+vsplit dsplit fliplr flipud rot90 sort argsort searchsorted nansum cumprod nanmean median quantile
+nanquantile bincount cov corrcoef vdot inner outer tensordot einsum kron cross fmod float_power exp2 logaddexp
+logaddexp2 arcsinh arccosh arctanh hypot deg2rad rad2deg fix fmax fmin isneginf isposinf signbit copysign nan_to_num
+diff gradient trapz gcd lcm heaviside bitwise_and bitwise_or bitwise_xor logical_not logical_xor count_nonzero
+nonzero argwhere tril_indices triu_indices broadcast_to atleast_1d atleast_2d atleast_3d vander sinc rand randn
+randint full_like empty_like take unique""".split():
+    if _n not in globals() and hasattr(torch, _n):
+        globals()[_n] = _fwd(getattr(torch, _n))
+
+_ALIASES = {"take_along_axis": torch.take_along_dim, "broadcast_arrays": torch.broadcast_tensors, "mod": torch.remainder,
+            "fabs": torch.abs, "invert": torch.bitwise_not, "around": torch.round, "round": torch.round,
+            "rint": torch.round, "degrees": torch.rad2deg, "radians": torch.deg2rad, "norm": torch.linalg.norm,
+            "nanmax": lambda x, dim=None, keepdim=False: torch.amax(torch.nan_to_num(x, nan=float("-inf")),
+                                                                    dim if dim is not None else tuple(range(x.dim())), keepdim),
+            "nanmin": lambda x, dim=None, keepdim=False: torch.amin(torch.nan_to_num(x, nan=float("inf")),
+                                                                    dim if dim is not None else tuple(range(x.dim())), keepdim),
+            "cbrt": lambda x: torch.sign(x) * torch.abs(x) ** (1.0 / 3), "identity": lambda n, dtype=None: torch.eye(n, dtype=dtype),
+            "flatnonzero": lambda x: torch.nonzero(x.reshape(-1)).reshape(-1),
+            "array_equal": lambda a, b: bool(a.shape == b.shape and torch.equal(torch.as_tensor(a), torch.as_tensor(b))),
+            "ptp": lambda x, dim=None, keepdim=False: (torch.amax(x, dim, keepdim) - torch.amin(x, dim, keepdim))
+            if dim is not None else x.max() - x.min(),
+            "repeat": lambda a, repeats, dim=None: torch.repeat_interleave(a, repeats, dim=dim),
+            "average": lambda a, dim=None, weights=None: (a.mean() if dim is None else a.mean(dim)) if weights is None
+            else ((a * weights).sum(dim if dim is not None else tuple(range(a.dim())))
+                  / weights.sum(dim if dim is not None else tuple(range(weights.dim())))),
+            "divmod": lambda a, b: (torch.floor_divide(a, b), torch.remainder(a, b))}
+_ALIASES["flip"] = lambda m, dim=None: torch.flip(m, tuple(range(m.dim())) if dim is None else
+                                                  ((dim,) if isinstance(dim, int) else tuple(dim)))
+_ALIASES["roll"] = lambda a, shift, dim=None: torch.roll(a, shift) if dim is None else torch.roll(a, shift, dim)
+for _n, _f in _ALIASES.items():
+    if _n not in globals():
+        globals()[_n] = _fwd(_f)
+
+
+def _host(name):
+    fn = getattr(_onp, name)
+
+    def f(*args, **kwargs):
+        dev = next((a.device for a in args if isinstance(a, torch.Tensor)), None)
+
+        def down(x):
+            if isinstance(x, torch.Tensor):
+                x = x.detach().cpu()
+                return x.float().numpy() if x.dtype == torch.bfloat16 else x.numpy()
+            if isinstance(x, (list, tuple)):
+                return type(x)(down(y) for y in x)
+            return x
+
+        def up(x):
+            if isinstance(x, _onp.ndarray):
+                if x.dtype == object or x.dtype.kind in "US":
+                    return x
+                t = torch.from_numpy(_onp.ascontiguousarray(x))
+                return _w(t.to(dev) if dev is not None else t)
+            if isinstance(x, (list, tuple)):
+                return type(x)(up(y) for y in x)
+            if isinstance(x, _onp.generic):
+                return x.item()
+            return x
+        return up(fn(*down(args), **{k: down(v) for k, v in kwargs.items()}))
+    f.__name__ = name
+    f.__doc__ = "numpy.%s evaluated on the host; tensors come back on the input's device." % name
+    return f
+
+
+for _n in """geomspace rollaxis array_split choose select piecewise nanargmax nanargmin nancumsum nanstd nanvar
+percentile histogram histogram2d histogramdd digitize correlate convolve interp ediff1d array_equiv tri diag_indices
+ix_ indices unravel_index ravel_multi_index pad apply_along_axis apply_over_axes polyadd polysub polymul polyval
+polyder polyint bartlett blackman hamming hanning kaiser""".split():
+    if _n not in globals() and hasattr(_onp, _n):
+        globals()[_n] = _host(_n)
+mgrid, ogrid = _onp.mgrid, _onp.ogrid

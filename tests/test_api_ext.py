@@ -203,3 +203,25 @@ def test_mint_namespace():
     assert layer(ms.Tensor(torch.ones(4, 3))).shape == (4, 2)
     opt = mint.optim.AdamW(layer.trainable_params(), 1e-3)
     assert opt is not None and mint.nn.Fold is not None and mint.nn.Unfold is not None
+
+
+def test_numpy_namespace_wide_coverage():
+    import mindspore_b200.numpy as mnp
+    x = ms.Tensor(torch.tensor([[1., float("nan"), 3.], [4., 5., 6.]]))
+    assert float(mnp.nanmax(x)) == 6.0 and mnp.nansum(x, axis=1).tolist() == [4.0, 15.0]
+    assert mnp.percentile(ms.Tensor(torch.arange(5.)), 50) == 2.0
+    assert mnp.interp(ms.Tensor(torch.tensor([1.5])), ms.Tensor(torch.tensor([1., 2.])),
+                      ms.Tensor(torch.tensor([10., 20.]))).tolist() == [15.0]
+    hist, edges = mnp.histogram(ms.Tensor(torch.tensor([1., 2., 2., 3.])), bins=3)
+    assert hist.tolist() == [1, 2, 1] and len(edges) == 4
+    assert mnp.polyval([1, 2, 3], ms.Tensor(torch.tensor([2.]))).tolist() == [11.0]
+    c = mnp.cbrt(ms.Tensor(torch.tensor([27., -8.])))
+    assert isinstance(c, ms.Tensor) and np.allclose(c.numpy(), [3, -2], atol=1e-5)
+    assert float(mnp.average(ms.Tensor(torch.tensor([1., 3.])), weights=ms.Tensor(torch.tensor([3., 1.])))) == 1.5
+    a = ms.Tensor(torch.arange(6.).reshape(2, 3))
+    assert mnp.flip(a, 0).tolist() == [[3, 4, 5], [0, 1, 2]] and mnp.vstack([a, a]).shape == (4, 3)
+    assert mnp.take_along_axis(a, ms.Tensor(torch.tensor([[2], [0]])), 1).tolist() == [[2.0], [3.0]]
+    q, r = mnp.divmod(ms.Tensor(torch.tensor([7, -7])), ms.Tensor(torch.tensor([2, 2])))
+    assert q.tolist() == [3, -4] and r.tolist() == [1, 1]
+    assert mnp.unravel_index(5, (2, 3)) == (1, 2) and np.allclose(mnp.hanning(4).numpy(), np.hanning(4))
+    assert mnp.array_equal(a, a) and not mnp.array_equal(a, a + 1)
