@@ -431,7 +431,138 @@ class Cell:
     def register_backward_hook(self, hook_fn):
         return _HookHandle(self._backward_hook, hook_fn)
 
+    def register_backward_pre_hook(self, hook_fn):
+        """``hook_fn(cell, grad_output)`` runs before the cell's backward; it may return a replacement gradient."""
+        return _HookHandle(self._backward_hook, lambda cell, gin, gout: hook_fn(cell, gout))
+
+    def register_state_dict_post_hook(self, hook_fn):
+        hooks = self.__dict__.setdefault("_state_dict_hooks", OrderedDict())
+        return _HookHandle(hooks, hook_fn)
+
+    def register_load_state_dict_post_hook(self, hook_fn):
+        hooks = self.__dict__.setdefault("_load_state_dict_hooks", OrderedDict())
+        return _HookHandle(hooks, hook_fn)
+
+    # ------------------------------------------------------------------ torch-style state access (mint / experimental)
+    def state_dict(self):
+        out = OrderedDict((p.name, p) for p in self.get_parameters())
+        for h in self.__dict__.get("_state_dict_hooks", {}).values():
+            r = h(self, out)
+            out = r if r is not None else out
+        return out
+
+    def load_state_dict(self, state_dict, strict=True):
+        own = {p.name: p for p in self.get_parameters()}
+        missing = [k for k in own if k not in state_dict]
+        unexpected = [k for k in state_dict if k not in own]
+        if strict and (missing or unexpected):
+            raise RuntimeError("load_state_dict: missing keys %s, unexpected keys %s" % (missing, unexpected))
+        import torch as _torch
+        with _torch.no_grad():
+            for k, p in own.items():
+                if k in state_dict:
+                    p.copy_(_torch.as_tensor(state_dict[k]).to(p.dtype).reshape(p.shape))
+        for h in self.__dict__.get("_load_state_dict_hooks", {}).values():
+            h(self, (missing, unexpected))
+        return missing, unexpected
+
+    def named_parameters(self, name_prefix="", recurse=True):
+        return self.parameters_and_names(name_prefix)
+
+    def parameters(self, recurse=True):
+        return self.get_parameters()
+
+    def train(self, mode=True):
+        return self.set_train(mode)
+
+    def eval(self):
+        return self.set_train(False)
+
     # ------------------------------------------------------------------ misc
+    @property
+    def param_prefix(self):
+        return getattr(self, "_param_prefix", "")
+
+    @property
+    def bprop_debug(self):
+        return getattr(self, "_bprop_debug", False)
+
+    @bprop_debug.setter
+    def bprop_debug(self, value):
+        object.__setattr__(self, "_bprop_debug", bool(value))
+
+    @property
+    def cell_init_args(self):
+        return getattr(self, "_cell_init_args", type(self).__name__)
+
+    def get_scope(self):
+        return getattr(self, "_scope", None)
+
+    def generate_scope(self):
+        """Scope names (``Default/<attr>-<Class>``) for this cell's children, used in graph dumps."""
+        base = self.get_scope() or "Default"
+        for name, cell in self._cells.items():
+            if cell is not None:
+                object.__setattr__(cell, "_scope", "%s/%s-%s" % (base, name, type(cell).__name__))
+                cell.generate_scope()
+
+    def update_cell_prefix(self):
+        for name, cell in self.cells_and_names():
+            object.__setattr__(cell, "_param_prefix", name)
+
+    def update_cell_type(self, cell_type):
+        object.__setattr__(self, "cell_type", cell_type)
+
+    def check_names(self):
+        seen = set()
+        for _, p in self.parameters_and_names():
+            if p.name in seen:
+                raise ValueError("The value of %s is duplicated in this cell: parameter names must be unique" % p.name)
+            seen.add(p.name)
+
+    def cast_inputs(self, inputs, dst_type):
+        import torch as _torch
+        return tuple(x.to(dst_type) if isinstance(x, _torch.Tensor) and x.is_floating_point() else x for x in inputs)
+
+    def auto_cast_inputs(self, inputs):
+        dt = getattr(self, "_mixed_precision_type", None)
+        return self.cast_inputs(inputs, dt) if dt is not None else tuple(inputs)
+
+    def run_construct(self, cast_inputs, kwargs):
+        return self._run_construct(tuple(cast_inputs), kwargs or {})
+
+    def infer_param_pipeline_stage(self):
+        """Parameters that belong to this process's pipeline stage."""
+        from .. import context as _ctx
+        stages = _ctx.get_auto_parallel_context("pipeline_stages")
+        if stages <= 1:
+            return list(self.get_parameters())
+        per = max(1, _ctx.get_auto_parallel_context("device_num") // stages)
+        mine = _ctx.get_auto_parallel_context("global_rank") // per
+        out = []
+        for _, cell in self.cells_and_names():
+            st = getattr(cell, "_pipeline_stage", None)
+            if st is None or st == mine:
+                out += [p for p in cell._params.values() if p is not None]
+        return out
+
+    def remove_redundant_parameters(self):
+        """Drops parameters of cells that belong to other pipeline stages (their memory is freed)."""
+        keep = {id(p) for p in self.infer_param_pipeline_stage()}
+        for _, cell in self.cells_and_names():
+            for name in [n for n, p in cell._params.items() if p is not None and id(p) not in keep]:
+                del cell._params[name]
+
+    def set_param_ps(self, recurse=True, init_in_server=False):
+        for p in (self.get_parameters() if recurse else self._params.values()):
+            if p is not None:
+                p.set_param_ps(init_in_server)
+
+    def get_func_graph_proto(self):
+        """Text of the compiled graph of this cell (empty before the first graph-mode call)."""
+        cg = getattr(self, "_compiled_graph", None)
+        return cg.fg.to_text() if cg is not None and hasattr(cg, "fg") else ""
+
     def cast_param(self, param):
         return param
 

@@ -208,3 +208,31 @@ def test_math_image_and_wrapper_cells():
     assert ops.argsort(_t(torch.tensor([3., 1., 2.]))).tolist() == [1, 2, 0]
     assert ops.cummax(_t(torch.tensor([1., 3., 2.])), 0)[0].tolist() == [1, 3, 3]
     assert sorted(ops.shuffle(_t(torch.arange(5)), seed=1).tolist()) == [0, 1, 2, 3, 4]
+
+
+def test_cell_state_dict_scopes_and_hooks():
+    ms.set_seed(0)
+    net = nn.SequentialCell([nn.Dense(2, 3), nn.ReLU(), nn.Dense(3, 1)])
+    other = nn.SequentialCell([nn.Dense(2, 3), nn.ReLU(), nn.Dense(3, 1)])
+    sd = net.state_dict()
+    assert list(sd) == ["0.weight", "0.bias", "2.weight", "2.bias"]
+    assert other.load_state_dict({k: v.detach().clone() for k, v in sd.items()}) == ([], [])
+    x = _t(torch.ones(1, 2))
+    assert torch.equal(net(x), other(x))
+    import pytest
+    with pytest.raises(RuntimeError):
+        other.load_state_dict({"0.weight": sd["0.weight"]})
+    assert other.load_state_dict({"0.weight": sd["0.weight"]}, strict=False)[0] == ["0.bias", "2.weight", "2.bias"]
+    net.generate_scope()
+    assert net[0].get_scope() == "Default/0-Dense" and net[2].get_scope() == "Default/2-Dense"
+    net.check_names()
+    net.eval()
+    assert not net.training and len(list(net.parameters())) == 4 and dict(net.named_parameters()).keys() == sd.keys()
+    seen = []
+    net[2].register_backward_pre_hook(lambda c, g: seen.append(tuple(g.shape)))
+    net.train()
+    net(x).sum().backward()
+    assert seen == [(1, 1)]
+    assert net.cast_inputs((x, 3), torch.bfloat16)[0].dtype == torch.bfloat16
+    net.set_param_ps()
+    assert all(p.is_param_ps for p in net.get_parameters())
