@@ -10,9 +10,9 @@ A ``.ckpt`` file is a *concatenation of serialized ``Checkpoint`` protobuf messa
                           required bytes tensor_content = 3; }
 
 Tensors above 512 MB are written as several consecutive values with the same tag; an optional trailer
-``crc_num`` + 10-digit CRC32 follows when ``crc_check`` is on; AES-GCM/CBC encryption wraps each block.
-The wire format is produced by the native codec (``csrc/host/ckpt_codec.cpp``: streaming writer that never
-holds more than one slice in host memory) with a pure-Python fallback that is byte-identical.
+``crc_num`` + the CRC32 as 10 big-endian bytes follows when ``crc_check`` is on; AES-GCM/CBC encryption wraps
+each block.  The bytes are produced here in Python; ``csrc/host/ckpt_codec.cpp`` is a native encoder / decoder of
+the same wire format (``_native.host().msb_ckpt_*``) that ``tests/test_ckpt_format.py`` checks against this one.
 
 Parity: mindspore/python/mindspore/train/serialization.py:255-375 (_exec_save), :436-583
 (save_checkpoint), :1076-1128 (_load_into_param_dict), :1139-1252 (load_checkpoint), :1406-1438
@@ -77,8 +77,53 @@ def encode_value(tag, dims, type_name, content):
     return _ld(1, value)
 
 
-def decode_stream(buf):
-    """Yields (tag, dims, type_name, content_memoryview) for every Value in a concatenated stream."""
+def _decode_native(buf):
+    """Indexes the stream with the C++ scanner (csrc/host/ckpt_codec.cpp) -> list of records, or None when the host
+    library is not loadable or the image needs the Python decoder's error reporting."""
+    import ctypes
+    try:
+        from .. import _native
+        lib = _native.host()
+        scan = lib.msb_ckpt_scan
+    except Exception:  # noqa: BLE001
+        return None
+    scan.restype = ctypes.c_int
+    n = len(buf)
+    raw = (ctypes.c_ubyte * n).from_buffer_copy(buf) if not isinstance(buf, bytearray) else \
+        (ctypes.c_ubyte * n).from_buffer(buf)
+    cap, dcap = 4096, 16384
+    while True:
+        rec = (ctypes.c_int64 * (4 * cap))()
+        dims = (ctypes.c_int64 * dcap)()
+        didx = (ctypes.c_int32 * (2 * cap))()
+        types = ctypes.create_string_buffer(16 * cap)
+        r = scan(raw, ctypes.c_uint64(n), cap, rec, dims, dcap, didx, types)
+        if r == -1:
+            cap, dcap = cap * 4, dcap * 4
+            continue
+        if r < 0:
+            return None
+        break
+    view = memoryview(raw).cast("B")
+    out = []
+    for i in range(r):
+        to, tl, co, cl = rec[4 * i:4 * i + 4]
+        d0, dn = didx[2 * i], didx[2 * i + 1]
+        dd = [d - (1 << 64) if d >= (1 << 63) else d for d in dims[d0:d0 + dn]]
+        out.append((bytes(view[to:to + tl]).decode(), dd, types.raw[16 * i:16 * i + 16].rstrip(b"\0").decode(),
+                    view[co:co + cl]))
+    return out
+
+
+def decode_stream(buf, native=True):
+    """Yields (tag, dims, type_name, content_memoryview) for every Value in a concatenated stream.  The index is
+    built by the native scanner when the host library is available; the Python decoder below is the fallback and
+    the one that reports where a corrupt image breaks."""
+    if native and len(buf) > 0:
+        recs = _decode_native(buf)
+        if recs is not None:
+            yield from recs
+            return
     view = memoryview(buf)
     pos, n = 0, len(buf)
     while pos < n:
@@ -132,7 +177,12 @@ def _tensor_bytes(t):
 def _bytes_tensor(content, dims, type_name):
     if type_name == "str":
         return bytes(content).decode()
-    dt = mstype.ckpt_type_from_name(type_name)
+    if type_name == "random_op":        # raw generator state (reference serialization.py:312-321)
+        return torch.from_numpy(np.frombuffer(content, dtype=np.uint8).copy())
+    try:
+        dt = mstype.ckpt_type_from_name(type_name)
+    except KeyError:
+        raise ValueError("unknown tensor_type %r in checkpoint" % type_name)
     shape = () if list(dims) == [0] else tuple(dims)
     if dt == torch.bfloat16:
         arr = np.frombuffer(content, dtype=np.int16).copy()
@@ -194,8 +244,14 @@ def _to_records(items, append_dict):
         if isinstance(v, str):
             recs.append((name, [0], "str", v.encode()))
             continue
+        if name == "random_op" and isinstance(v, (bytes, bytearray)):
+            recs.append((name, [0], "random_op", bytes(v)))
+            continue
         if not isinstance(v, torch.Tensor):
             v = Tensor(v)
+        if name == "random_op":
+            recs.append((name, [0], "random_op", _tensor_bytes(v.to(torch.uint8))))
+            continue
         dims = list(v.shape) if v.dim() > 0 else [0]
         recs.append((name, dims, mstype.ckpt_type_name(v.dtype), v))
     if append_dict:
@@ -239,7 +295,7 @@ def _write(path, recs, enc_key, enc_mode, crc_check):
                         crc = binascii.crc32(block, crc)
                     f.write(block)
             if crc_check:
-                f.write(_CRC_TAG + ("%010d" % crc).encode())
+                f.write(_CRC_TAG + crc.to_bytes(10, "big"))          # reference serialization.py:302
         os.replace(tmp, path)
         os.chmod(path, stat.S_IRUSR | stat.S_IWUSR)
 
@@ -280,11 +336,13 @@ def wait_async_save():
 def _read_file(path, dec_key, dec_mode, crc_check):
     with open(path, "rb") as f:
         data = f.read()
-    crc_pos = data.rfind(_CRC_TAG, max(0, len(data) - 32))
-    has_crc = crc_pos >= 0 and len(data) - crc_pos == len(_CRC_TAG) + 10 and data[crc_pos + 7:].isdigit()
+    # trailer = b"crc_num" + 10 big-endian bytes (reference serialization.py:1417-1425); files written by older
+    # versions of this module carried 10 ASCII digits instead and are still accepted
+    has_crc = len(data) >= 17 and data[-17:-10] == _CRC_TAG
     if has_crc:
-        expect = int(data[crc_pos + len(_CRC_TAG):])
-        data = data[:crc_pos]
+        tail = data[-10:]
+        expect = int(tail) if tail.isdigit() and tail[:1] != b"\x00" else int.from_bytes(tail, "big")
+        data = data[:-17]
         if crc_check and binascii.crc32(data) != expect:
             raise ValueError("For 'load_checkpoint', the crc check has failed. Please check whether the ckpt file "
                              "is damaged.")

@@ -134,3 +134,76 @@ def test_safetensors_round_trip_and_check(tmp_path):
     assert np.allclose(p["0.bias"].numpy(), net[0].bias.detach().numpy())
     assert torch.equal(torch.as_tensor(p["1.weight"]).view(torch.int16),
                        net[1].weight.detach().as_subclass(torch.Tensor).view(torch.int16))
+
+
+def _reference_style_file(path, values, crc=True):
+    """Builds a checkpoint the way the reference writes one: google.protobuf ``SerializeToString`` of one
+    ``Checkpoint`` message per value, then ``b'crc_num' + crc.to_bytes(10, 'big')``
+    (mindspore/python/mindspore/train/serialization.py:255-302)."""
+    import binascii
+    from google.protobuf import descriptor_pb2, descriptor_pool, message_factory
+    fd = descriptor_pb2.FileDescriptorProto(name="ckpt_ref.proto", syntax="proto2")
+    tp = fd.message_type.add(name="TensorProto")
+    tp.field.add(name="dims", number=1, type=3, label=3)
+    tp.field.add(name="tensor_type", number=2, type=9, label=2)
+    tp.field.add(name="tensor_content", number=3, type=12, label=2)
+    ck = fd.message_type.add(name="Checkpoint")
+    val = ck.nested_type.add(name="Value")
+    val.field.add(name="tag", number=1, type=9, label=2)
+    val.field.add(name="tensor", number=2, type=11, label=1, type_name=".TensorProto")
+    ck.field.add(name="value", number=1, type=11, label=3, type_name=".Checkpoint.Value")
+    pool = descriptor_pool.DescriptorPool()
+    pool.Add(fd)
+    cls = message_factory.GetMessageClass(pool.FindMessageTypeByName("Checkpoint"))
+    blob, c = b"", 0
+    for tag, dims, tname, content in values:
+        m = cls()
+        v = m.value.add()
+        v.tag = tag
+        v.tensor.dims.extend(dims)
+        v.tensor.tensor_type = tname
+        v.tensor.tensor_content = content
+        b = m.SerializeToString()
+        c = binascii.crc32(b, c)
+        blob += b
+    if crc:
+        blob += b"crc_num" + c.to_bytes(10, byteorder="big")
+    open(path, "wb").write(blob)
+    return blob
+
+
+def test_reads_reference_style_file_with_binary_crc_and_random_op(tmp_path):
+    pytest.importorskip("google.protobuf")
+    w = np.random.randn(3, 4).astype(np.float32)
+    seed_state = bytes(range(40))
+    path = str(tmp_path / "ref.ckpt")
+    _reference_style_file(path, [("fc.weight", [3, 4], "Float32", w.tobytes()),
+                                 ("random_op", [0], "random_op", seed_state)])
+    for check in (True, False):
+        d = ms.load_checkpoint(path, crc_check=check)
+        np.testing.assert_array_equal(d["fc.weight"].asnumpy(), w)
+        assert bytes(d["random_op"].numpy().tobytes()) == seed_state
+    raw = bytearray(open(path, "rb").read())
+    raw[30] ^= 0x55
+    (tmp_path / "bad.ckpt").write_bytes(bytes(raw))
+    with pytest.raises(ValueError, match="crc check"):
+        ms.load_checkpoint(str(tmp_path / "bad.ckpt"), crc_check=True)
+
+
+def test_written_trailer_is_the_reference_one(tmp_path):
+    import binascii
+    path = ms.save_checkpoint({"a": ms.Tensor(np.arange(5, dtype=np.float32))}, str(tmp_path / "c.ckpt"),
+                              crc_check=True)
+    raw = open(path, "rb").read()
+    assert raw[-17:-10] == b"crc_num"
+    assert int.from_bytes(raw[-10:], "big") == binascii.crc32(raw[:-17], 0)
+
+
+def test_native_scanner_matches_python_decoder(tmp_path):
+    path = ms.save_checkpoint({"a": ms.Tensor(np.arange(12, dtype=np.float32).reshape(3, 4)),
+                               "s": ms.Tensor(np.int32(7))}, str(tmp_path / "n.ckpt"), append_dict={"note": "hi"})
+    raw = open(path, "rb").read()
+    a = [(t, d, n, bytes(c)) for t, d, n, c in S.decode_stream(raw, native=True)]
+    b = [(t, d, n, bytes(c)) for t, d, n, c in S.decode_stream(raw, native=False)]
+    assert a == b and [r[0] for r in a] == ["a", "s", "note"]
+    assert S._decode_native(raw) is not None, "the host library's scanner was not used"
