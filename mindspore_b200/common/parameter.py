@@ -21,6 +21,17 @@ from .tensor import Tensor, _to_torch
 _uid = itertools.count()
 
 
+def sync_master(param, value=None):
+    """A parameter packed into an optimizer arena has an fp32 master copy (whole, or one slice per rank under the
+    sharded optimizer) from which every update rewrites the low-precision weights: whoever overwrites the
+    parameter's value calls this so that the master follows."""
+    arena = getattr(param, "arena", None)
+    owner = getattr(arena, "owner", None) if arena is not None else None
+    opt = owner() if owner is not None else None
+    if opt is not None:
+        opt.write_master(param, param if value is None else value)
+
+
 class Parameter(Tensor):
     @staticmethod
     def __new__(cls, default_input, name=None, requires_grad=True, layerwise_parallel=False,
@@ -173,6 +184,7 @@ class Parameter(Tensor):
         with torch.no_grad():
             if tuple(new.shape) == tuple(self.shape) and new.dtype == self.dtype:
                 torch.Tensor.copy_(self, new)
+                sync_master(self, new)
             else:
                 _swap_storage(self, new)
         return self

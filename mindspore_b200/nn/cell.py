@@ -81,8 +81,7 @@ class Cell:
                 value.update_parameters_name(name + ".")
             cells[name] = value
         elif isinstance(value, ParameterTuple):
-            for p in value:
-                self._params_list.setdefault(name, value)
+            self._params_list[name] = value
             object.__setattr__(self, name, value)
         elif params is not None and name in params:
             if value is None:
@@ -461,7 +460,10 @@ class Cell:
         with _torch.no_grad():
             for k, p in own.items():
                 if k in state_dict:
-                    p.copy_(_torch.as_tensor(state_dict[k]).to(p.dtype).reshape(p.shape))
+                    src = _torch.as_tensor(state_dict[k]).reshape(p.shape)
+                    p.copy_(src.to(p.dtype))
+                    from ..common.parameter import sync_master
+                    sync_master(p, src)
         for h in self.__dict__.get("_load_state_dict_hooks", {}).values():
             h(self, (missing, unexpected))
         return missing, unexpected

@@ -47,9 +47,23 @@ def _clone_state(params, prefix, init="zeros", dtype=None):
 _grad_listeners = []
 
 
+def note_grad_producer(param):
+    """Called in forward (with gradients enabled) by every op whose backward will accumulate into
+    ``param.main_grad``.  A parameter used several times in one step (tied embedding / LM head, shared layers) has
+    several producers; its gradient is complete only after the last of them has written."""
+    if getattr(param, "main_grad", None) is not None and torch.is_grad_enabled():
+        param._grad_writers = getattr(param, "_grad_writers", 0) + 1
+
+
 def notify_grad_written(param):
     """Called by backward kernels right after they have accumulated ``param``'s gradient into its arena slice
-    (``main_grad``); listeners use it to start the gradient collective of a bucket as soon as the bucket is complete."""
+    (``main_grad``).  Listeners are told once the last registered producer of this step has written; they use it to
+    start the gradient collective of a bucket as soon as the bucket is complete."""
+    n = getattr(param, "_grad_writers", 0)
+    if n > 1:
+        param._grad_writers = n - 1
+        return
+    param._grad_writers = 0
     for fn in _grad_listeners:
         fn(param)
 
@@ -273,6 +287,8 @@ class Optimizer(Cell):
         self._arena_order = order
         ordered = [params[i] for i in order]
         self.arena = ParamArena(ordered)
+        import weakref
+        self.arena.owner = weakref.ref(self)
         # contiguous runs of equal weight decay -> one kernel launch each
         self._arena_groups = []
         start = 0
@@ -293,6 +309,74 @@ class Optimizer(Cell):
     def zero_grad(self):
         if self.arena is not None:
             self.arena.zero_grad()
+
+    # ------------------------------------------------------------------ arena state <-> checkpoints
+    def _state_views(self, buf, prefix):
+        """Per-parameter Parameters ``<prefix>.<name>`` that alias slices of the flat state buffer ``buf``: they are
+        saved and loaded like the reference's cloned optimizer states (``adam_m.*``, ``adam_v.*``, ``moments.*``;
+        nn/optim/adam.py:866, momentum.py:50) while the fused kernels keep working on the flat buffer."""
+        out = []
+        for prm, off in zip(self.arena.params, self.arena.offsets):
+            s = Parameter(torch.empty(0, dtype=buf.dtype), name=prefix + "." + prm.name, requires_grad=False,
+                          device=buf.device)
+            s.data = buf[off:off + prm.numel()].view(prm.shape)
+            s.param_layout = prm.param_layout
+            s.cloned_from = prm
+            out.append(s)
+        return ParameterTuple(out)
+
+    def _flat_state(self, buf, name):
+        s = Parameter(torch.empty(0, dtype=buf.dtype), name=name, requires_grad=False, device=buf.device)
+        s.data = buf
+        return ParameterTuple([s])
+
+    def _expose_arena_state(self):
+        """(Re)builds the checkpoint view of the arena state.  Full arena: per-parameter views of the moments and of
+        the fp32 master copy.  Sharded over a data-parallel group: this rank's slice of master / moments as three
+        flat tensors (``*.opt_shard``), saved per rank like the reference's sliced optimizer states."""
+        arena = self.arena
+        if arena is None:
+            return
+        dp = getattr(self, "_dp", None)
+        names = self._arena_state_names()
+        if dp is not None and dp.shard:
+            for (attr, prefix), buf in zip(names, dp.state_buffers()):
+                setattr(self, attr, self._flat_state(buf, prefix + ".opt_shard"))
+            self.fp32_master = self._flat_state(dp.master, "fp32_master.opt_shard")
+            return
+        for (attr, prefix), buf in zip(names, self._arena_state_buffers()):
+            setattr(self, attr, self._state_views(buf, prefix))
+        if arena.master is not None and arena.master is not arena.weights:
+            self.fp32_master = self._state_views(arena.master, "fp32_master")
+
+    def _arena_state_names(self):
+        return ()
+
+    def _arena_state_buffers(self):
+        return ()
+
+    def sync_step_from_checkpoint(self):
+        """After ``global_step`` was loaded from a checkpoint: the host-side step (learning-rate schedule, bias
+        correction) follows it."""
+        self._step_host = int(self.global_step.detach().reshape(-1)[0])
+
+    def write_master(self, param, value):
+        """Copies ``value`` (what was just written into ``param``) into the fp32 master copy of ``param`` (full
+        arena, or the owned part of a sharded one), so that the next update does not bring the old weights back from
+        the master."""
+        arena = self.arena
+        if arena is None or getattr(param, "arena", None) is not arena:
+            return
+        new = value.detach().as_subclass(torch.Tensor).to(param.device)
+        o, n = param.arena_offset, param.numel()
+        flat = new.reshape(-1).float()
+        dp = getattr(self, "_dp", None)
+        if dp is not None and dp.shard:
+            lo, hi = max(o, dp.lo), min(o + n, dp.hi)
+            if lo < hi:
+                dp.master[lo - dp.lo:hi - dp.lo].copy_(flat[lo - o:hi - o])
+        elif arena.master is not None and arena.master is not arena.weights:
+            arena.master[o:o + n].copy_(flat)
 
     # ------------------------------------------------------------------ model-parallel awareness (arena form)
     def set_model_parallel_group(self, group_name):
@@ -326,6 +410,7 @@ class Optimizer(Cell):
         assert self.arena is not None, "set_data_parallel_group needs the arena form"
         from ..parallel.zero import DataParallelArena
         self._dp = DataParallelArena(self, group_name, mean, shard, fused)
+        self._expose_arena_state()
 
     def sync_data_parallel_grads(self):
         dp = getattr(self, "_dp", None)
@@ -399,11 +484,17 @@ class Momentum(Optimizer):
             # flat form: bf16 weights, fp32 master + accumulator, one kernel per weight-decay group
             arena = self._enable_arena(decay_filter or (lambda p: p.dim() > 1))
             self._accum = torch.zeros(arena.total, dtype=torch.float32, device=arena.weights.device)
-            self.moments = ()
+            self._expose_arena_state()
         else:
             self.moments = _clone_state(self._parameters, "moments")
 
-    def fused_step(self, inv_loss_scale=1.0, check_finite=False):
+    def _arena_state_names(self):
+        return (("moments", "moments"),)
+
+    def _arena_state_buffers(self):
+        return (self._accum,)
+
+    def fused_step(self, inv_loss_scale=1.0, check_finite=False, advance=True):
         arena = self.arena
         lr = self._lr_value(self.learning_rate, self._step_host)
         skip = None
@@ -420,7 +511,8 @@ class Momentum(Optimizer):
             h[4] = 1.0 if self.use_nesterov else 0.0
             lp = arena.weights[s:e] if arena.master is not arena.weights else None
             K.momentum_step(arena.master[s:e], self._accum[s:e], arena.grads[s:e], lp, h, skip)
-        self._advance()
+        if advance:
+            self._advance()
         return True
 
     def construct(self, gradients=None):
@@ -528,13 +620,19 @@ class AdamWeightDecay(Optimizer):
             arena = self._enable_arena(self.decay_filter)
             self._m = torch.zeros(arena.total, dtype=torch.float32, device=arena.weights.device)
             self._v = torch.zeros(arena.total, dtype=torch.float32, device=arena.weights.device)
-            self.moment1 = self.moment2 = ()
+            self._expose_arena_state()
         else:
             self.moment1 = _clone_state(self._parameters, "adam_m")
             self.moment2 = _clone_state(self._parameters, "adam_v")
 
     def _decay_flag(self, p):
         return self.decay_filter(p)
+
+    def _arena_state_names(self):
+        return (("moment1", "adam_m"), ("moment2", "adam_v"))
+
+    def _arena_state_buffers(self):
+        return (self._m, self._v)
 
     def decay_weight(self, gradients):
         return gradients  # decoupled decay is applied in the update itself
@@ -558,11 +656,12 @@ class AdamWeightDecay(Optimizer):
         self._advance()
         return True
 
-    def fused_step(self, inv_loss_scale=1.0, check_finite=False):
-        """One kernel per decay group over the flat arena; clip and overflow-skip decided on the device."""
+    def fused_step(self, inv_loss_scale=1.0, check_finite=False, advance=True):
+        """One kernel per decay group over the flat arena; clip and overflow-skip decided on the device.  With
+        ``advance=False`` the caller advances the step counter itself (after it has read the skip flag)."""
         dp = getattr(self, "_dp", None)
         if dp is not None and dp.shard:
-            return dp.sharded_step(inv_loss_scale, check_finite)
+            return dp.sharded_step(inv_loss_scale, check_finite, advance)
         arena = self.arena
         t = self._step_host + 1
         lr = self._lr_value(self.learning_rate, self._step_host)
@@ -581,7 +680,8 @@ class AdamWeightDecay(Optimizer):
             h[7:8].copy_(self._gscale)
             lp = arena.weights[s:e] if arena.master is not arena.weights else None
             K.adamw_step(arena.master[s:e], self._m[s:e], self._v[s:e], arena.grads[s:e], lp, h, skip)
-        self._advance()
+        if advance:
+            self._advance()
         return True
 
 

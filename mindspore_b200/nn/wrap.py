@@ -168,9 +168,9 @@ class TrainOneStepCell(Cell):
         thousands of kernel launches per micro-batch become one, which removes the host launch bound."""
         runner = getattr(self, "_runner", None)
         if runner is None or runner.network is not network:
-            runner = _MicroBatchRunner(network, scale)
+            runner = _MicroBatchRunner(network, None)
             self._runner = runner
-        runner.scale = scale
+        runner._set_scale(scale)
         return runner
 
     def release_graphs(self):
@@ -197,20 +197,24 @@ class TrainOneStepCell(Cell):
         self.optimizer(grads)
         return _wrap_out(loss)
 
-    def _arena_step(self, inputs):
-        """Arena optimizers: gradients flow straight into the flat fp32 accumulator inside backward."""
+    def _arena_backward(self, inputs, scale):
+        """Forward + backward of one step for arena optimizers, up to (not including) the update: gradients flow
+        straight into the flat fp32 accumulator inside backward, micro-batches and pipeline stages are scheduled
+        here, and the gradient collectives of the model-parallel group, the data-parallel group and the legacy
+        reducer run before returning.  ``scale`` multiplies the loss before backward: a float (``sens``) or the
+        device-resident loss scale."""
         opt = self.optimizer
         opt.zero_grad()
         net = self.network
         if isinstance(net, PipelineCell) and not isinstance(net, GradAccumulationCell) and \
                 context.get_auto_parallel_context("pipeline_stages") > 1:
             from ..parallel.pipeline import run_pipeline_step
-            loss = run_pipeline_step(net, inputs, self.sens / net.micro_size)
+            loss = run_pipeline_step(net, inputs, scale / net.micro_size)
         elif isinstance(net, GradAccumulationCell):
             # micro-batches run back to back; each backward accumulates into the flat fp32 gradient arena
             total = None
             k = net.micro_size
-            runner = self._micro_runner(net.network, self.sens / k)
+            runner = self._micro_runner(net.network, scale / k)
             for i in range(k):
                 li = runner(net.micro_inputs(i, *inputs))
                 total = li.clone() if total is None else total + li
@@ -221,8 +225,10 @@ class TrainOneStepCell(Cell):
                 dp.begin_step()                # buckets are all-reduced as backward completes them
             with torch.enable_grad():
                 loss = net(*inputs)
-            if self.sens != 1.0:
-                (loss * self.sens).backward()
+            if isinstance(scale, torch.Tensor):
+                (loss * scale.to(loss.dtype)).backward()
+            elif scale != 1.0:
+                (loss * scale).backward()
             else:
                 loss.backward()
         _collect_stray_grads(self.weights)
@@ -231,8 +237,12 @@ class TrainOneStepCell(Cell):
         if self.grad_reducer is not None:
             from ..parallel.data_parallel import allreduce_arena_grads
             allreduce_arena_grads(opt.arena, self.grad_reducer)
-        opt.fused_step(inv_loss_scale=1.0 / self.sens if self.sens != 1.0 else 1.0)
         return loss.detach()
+
+    def _arena_step(self, inputs):
+        loss = self._arena_backward(inputs, self.sens)
+        self.optimizer.fused_step(inv_loss_scale=1.0 / self.sens if self.sens != 1.0 else 1.0)
+        return loss
 
     def construct(self, *inputs):
         if _recorder.enabled():
@@ -272,12 +282,24 @@ class _MicroBatchRunner:
         self.static_loss = None
         self.launches_per_replay = 0
 
+    def _set_scale(self, scale):
+        """A float scale is baked into the (captured) backward; a tensor scale (dynamic loss scale) is kept in a
+        buffer of this runner that a captured graph re-reads at every replay."""
+        if isinstance(scale, torch.Tensor):
+            if not isinstance(self.scale, torch.Tensor):
+                self.scale = scale.detach().clone().float().reshape(())
+            else:
+                self.scale.copy_(scale.detach().reshape(()))
+        else:
+            self.scale = scale
+
     def _eager(self, inputs):
         from ..parallel import fused_comm
         fused_comm.step_fence()
         with torch.enable_grad():
             loss = self.network(*inputs)
-        (loss * self.scale).backward()
+        sc = self.scale.to(loss.dtype) if isinstance(self.scale, torch.Tensor) else self.scale
+        (loss * sc).backward()
         return loss.detach()
 
     def __call__(self, inputs):
@@ -406,19 +428,18 @@ class TrainOneStepWithLossScaleCell(TrainOneStepCell):
     def construct(self, *inputs):
         scale = self.scale_sense
         if self.use_arena:
+            # same backward + gradient synchronisation as TrainOneStepCell (micro-batches, pipeline, model- and
+            # data-parallel groups), with the loss scale as the initial gradient; the update kernels read the skip
+            # flag on the device, and the step counter only advances when the update was applied (the reference
+            # skips the optimizer on overflow: nn/wrap/loss_scale.py:404-422)
             opt = self.optimizer
-            opt.zero_grad()
-            with torch.enable_grad():
-                loss = self.network(*inputs)
-            (loss * scale.to(loss.dtype)).backward()
-            _collect_stray_grads(self.weights)
-            if self.grad_reducer is not None:
-                from ..parallel.data_parallel import allreduce_arena_grads
-                allreduce_arena_grads(opt.arena, self.grad_reducer)
-            opt.fused_step(inv_loss_scale=1.0 / float(scale), check_finite=True)
-            overflow = opt._skip.bool().reshape(())
-            overflow = self.process_loss_scale(overflow)
-            return _wrap_out(loss.detach()), _wrap_out(torch.as_tensor(overflow)), scale
+            loss = self._arena_backward(inputs, scale.detach().as_subclass(torch.Tensor))
+            opt.fused_step(inv_loss_scale=1.0 / float(scale), check_finite=True, advance=False)
+            overflow = bool(opt._skip.reshape(()))
+            if not overflow:
+                opt._advance()
+            overflow = self.process_loss_scale(torch.as_tensor(overflow))
+            return _wrap_out(loss), _wrap_out(torch.as_tensor(overflow)), scale
         loss = self.network(*inputs)
         sens = torch.full_like(loss, 1.0) * scale.to(loss.dtype)
         grads = self.grad(self.network, self.weights)(*inputs, sens)

@@ -38,6 +38,13 @@ def _notify(param):
     notify_grad_written(param)
 
 
+def _producer(*params):
+    from ..nn.optim import note_grad_producer
+    for p in params:
+        if p is not None:
+            note_grad_producer(p)
+
+
 def available():
     return torch.cuda.is_available() and _native.cuda() is not None
 
@@ -199,6 +206,7 @@ def conv2d(x, w, stride, pads, dilation=(1, 1), bias=None):
     if sh != sw or sh not in (1, 2) or top != bottom or left != right:
         x = torch.nn.functional.pad(x, (left, right, top, bottom))
         return torch.nn.functional.conv2d(x, w, bias, stride, 0, dilation)
+    _producer(w)
     y, _ = _ConvFn.apply(x, w.to(torch.bfloat16) if w.dtype != torch.bfloat16 else w, sh, top, left, False)
     if bias is not None:
         y = y + bias.view(1, -1, 1, 1)
@@ -272,6 +280,7 @@ def conv_bn_act(x, w, gamma, beta, moving_mean, moving_var, stride=1, pad=0, rel
     """Training-mode Conv2d -> BatchNorm2d -> (+ residual) -> ReLU on the kernel path.  ``momentum`` is the weight
     of the old moving statistics (nn.BatchNorm2d convention)."""
     wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+    _producer(wb, gamma, beta)
     y, stats = _ConvFn.apply(x, wb, stride, pad, pad, True)
     return _BnActFn.apply(y, stats, gamma, beta, residual, relu, eps, (moving_mean, moving_var, momentum))
 
@@ -360,4 +369,5 @@ def batch_norm_train(x, gamma, beta, moving_mean, moving_var, keep, eps, relu=Fa
     _count()
     mm = moving_mean.detach().as_subclass(torch.Tensor)
     mv = moving_var.detach().as_subclass(torch.Tensor)
+    _producer(gamma, beta)
     return _BnActFn.apply(x, stats, gamma, beta, residual, relu, eps, (mm, mv, keep))

@@ -24,6 +24,16 @@ def _plain(t):
     return t.as_subclass(torch.Tensor) if t is not None and type(t) is not torch.Tensor else t
 
 
+def _producer(param):
+    from ..nn.optim import note_grad_producer
+    note_grad_producer(param)
+
+
+def _written(param):
+    from ..nn.optim import notify_grad_written
+    notify_grad_written(param)
+
+
 # ------------------------------------------------------------------------------------------ Linear
 class _LinearFn(torch.autograd.Function):
     @staticmethod
@@ -64,6 +74,7 @@ class _LinearFn(torch.autograd.Function):
 def linear(x, w, bias=None):
     """y = x @ w^T + bias with w stored [out, in]."""
     if _use_kernel(x, w, bias) and x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0:
+        _producer(w)
         return _LinearFn.apply(x, w, bias)
     return F.linear(x, w, bias)
 
@@ -128,6 +139,7 @@ class _RmsNormFn(torch.autograd.Function):
         dx, dw = K.rmsnorm_bwd(dy.contiguous(), xsum, w, rstd, dresidual=dres, dw_out=mg, accumulate=mg is not None)
         if mg is not None:
             dw = None
+            _written(ctx.w_ref)
         if ctx.has_res:
             return dx, dw, None, dx
         return dx, dw, None, None
@@ -136,6 +148,7 @@ class _RmsNormFn(torch.autograd.Function):
 def rms_norm(x, w, eps=1e-6, residual=None):
     """Returns (y, stream) where stream = x + residual (or x).  y = stream * rsqrt(mean(stream^2)+eps) * w."""
     if _use_kernel(x, w, residual) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384:
+        _producer(w)
         y, stream = _RmsNormFn.apply(x, w, eps, residual)
         return y, (stream if residual is not None else x)
     stream = x if residual is None else x + residual
@@ -160,6 +173,9 @@ class _LayerNormFn(torch.autograd.Function):
         if mgw is not None and (ctx.b_ref is None or mgb is not None):
             dx, _, _ = K.layernorm_bwd(dy.contiguous(), x.contiguous(), w, mean, rstd, dw_out=mgw, db_out=mgb,
                                        accumulate=True)
+            _written(ctx.w_ref)
+            if ctx.b_ref is not None:
+                _written(ctx.b_ref)
             return dx, None, None, None
         dx, dw, db = K.layernorm_bwd(dy.contiguous(), x.contiguous(), w, mean, rstd, has_bias=ctx.b_ref is not None)
         return dx, dw, db, None
@@ -167,6 +183,9 @@ class _LayerNormFn(torch.autograd.Function):
 
 def layer_norm(x, w, b, eps=1e-5):
     if _use_kernel(x, w, b) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384:
+        _producer(w)
+        if b is not None:
+            _producer(b)
         return _LayerNormFn.apply(x, w, b, eps)
     return F.layer_norm(x, (x.shape[-1],), w, b, eps)
 
@@ -300,6 +319,7 @@ class _EmbeddingFn(torch.autograd.Function):
         mg = getattr(t, "main_grad", None)
         if mg is not None:
             K.embedding_bwd(dout.contiguous(), ids32, mg.view(t.shape), ctx.vocab_start)
+            _written(t)
             return None, None, None
         acc = torch.zeros(t.shape, dtype=torch.float32, device=t.device)
         K.embedding_bwd(dout.contiguous(), ids32, acc, ctx.vocab_start)
@@ -308,6 +328,7 @@ class _EmbeddingFn(torch.autograd.Function):
 
 def embedding(table, ids, vocab_start=0):
     if _use_kernel(table) and table.shape[1] % 8 == 0:
+        _producer(table)
         return _EmbeddingFn.apply(table, ids, vocab_start)
     idx = ids.long() - vocab_start
     mask = (idx >= 0) & (idx < table.shape[0])

@@ -210,6 +210,11 @@ def _gemm_ag(ctx, a_shard, b, b_mn, bias=None):
     return c, gathered
 
 
+def _optim():
+    from ..nn import optim
+    return optim
+
+
 def _shapes_ok(rows_total, world, *dims):
     return rows_total % world == 0 and (rows_total // world) % 128 == 0 and all(d % 8 == 0 for d in dims)
 
@@ -232,6 +237,7 @@ class _MatmulReduceScatter(torch.autograd.Function):
         if mg is not None:
             K.linear_wgrad(dy_full, x, out=mg, accumulate=True)
             dw = None
+            _optim().notify_grad_written(ctx.w_ref)
         else:
             dw = K.linear_wgrad(dy_full, x, out_dtype=torch.bfloat16)
         return dx, dw, None
@@ -256,6 +262,7 @@ class _AllgatherMatmul(torch.autograd.Function):
         if mg is not None:
             K.linear_wgrad(dy, gathered, out=mg, accumulate=True)
             dw = None
+            _optim().notify_grad_written(ctx.w_ref)
         else:
             dw = K.linear_wgrad(dy, gathered, out_dtype=torch.bfloat16)
         db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias else None
@@ -268,6 +275,7 @@ def matmul_reduce_scatter(x, w_shard, tp):
         from . import tp as _tp
         from ..ops import fused
         return _tp.scatter_tokens_reduce(fused.linear(x, w_shard), tp)
+    _optim().note_grad_producer(w_shard)
     return _MatmulReduceScatter.apply(x, w_shard, tp.name)
 
 
@@ -277,6 +285,7 @@ def allgather_matmul(x_shard, w_shard, tp, bias=None):
         from . import tp as _tp
         from ..ops import fused
         return fused.linear(_tp.gather_tokens(x_shard, tp), w_shard, bias)
+    _optim().note_grad_producer(w_shard)
     return _AllgatherMatmul.apply(x_shard, w_shard, bias, tp.name)
 
 

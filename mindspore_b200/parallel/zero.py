@@ -97,6 +97,10 @@ class DataParallelArena:
             torch.cuda.synchronize()
             dist.barrier(group=self.group.pg)
 
+    def state_buffers(self):
+        """The sharded moments (this rank's slice), in the order of ``Optimizer._arena_state_names``."""
+        return (self.m, self.v)
+
     # ------------------------------------------------------------------ overlap with backward
     def _bucket_ranges(self):
         if getattr(self, "_reduce_ranges", None) is None:
@@ -155,6 +159,8 @@ class DataParallelArena:
             _optim._grad_listeners.append(self._on_grad)
             if arena.grads.is_cuda:
                 self._comm_stream = torch.cuda.Stream()
+        for p in arena.params:
+            p._grad_writers = 0                # producers register again in this step's forward
         self._pending = list(self._bucket_size)
         self._seen = set()
         self._done = [False] * len(ranges)
@@ -226,7 +232,7 @@ class DataParallelArena:
             if lo < hi:
                 yield lo - self.lo, hi - lo, tag
 
-    def sharded_step(self, inv_loss_scale=1.0, check_finite=False):
+    def sharded_step(self, inv_loss_scale=1.0, check_finite=False, advance=True):
         opt, arena = self.opt, self.arena
         scale = 1.0 / self.world if self.mean else 1.0
         own = arena.grads[self.lo:self.hi]
@@ -294,5 +300,6 @@ class DataParallelArena:
             gathered = torch.empty_like(arena.weights)
             dist.all_gather_into_tensor(gathered, lp_slice.contiguous(), group=self.group.pg)
             arena.weights.copy_(gathered)
-        opt._advance()
+        if advance:
+            opt._advance()
         return True

@@ -454,9 +454,10 @@ def load_param_into_net(net, parameter_dict, strict_load=False, remove_redundanc
             new = new.to(p.dtype)
         with torch.no_grad():
             torch.Tensor.copy_(p, new.to(p.device))
-        if getattr(p, "arena", None) is not None and p.arena.master is not None and p.arena.master is not p.arena.weights:
-            o = p.arena_offset
-            p.arena.master[o:o + p.numel()].copy_(new.reshape(-1).float().to(p.device))
+        if ("fp32_master." + name) not in parameter_dict and "fp32_master.opt_shard" not in parameter_dict:
+            # no exact master in the checkpoint: the master (whole, or this rank's slice) follows the loaded weights
+            from ..common.parameter import sync_master
+            sync_master(p, new)
 
     for _, p in params:
         if p.name in parameter_dict and isinstance(parameter_dict[p.name], torch.Tensor):
@@ -480,6 +481,12 @@ def load_param_into_net(net, parameter_dict, strict_load=False, remove_redundanc
         not_loaded = still
     ckpt_not_loaded = [k for k in parameter_dict if k not in loaded and k != "random_op"
                        and isinstance(parameter_dict[k], torch.Tensor)]
+    if "global_step" in loaded:
+        # the host-side step drives the learning-rate schedule and Adam's bias correction
+        for _, cell in net.cells_and_names():
+            if hasattr(cell, "sync_step_from_checkpoint") and \
+                    any(q is getattr(cell, "global_step", None) for _, q in params):
+                cell.sync_step_from_checkpoint()
     if not_loaded:
         logger.warning("For 'load_param_into_net', %d parameters in the 'net' are not loaded: %s", len(not_loaded),
                        not_loaded[:8])

@@ -213,3 +213,115 @@ def test_overlapped_allreduce_on_2_gpus():
             torch.testing.assert_close(p1[k], p0[k], rtol=2e-2, atol=2e-3)
     for k in over[0][0]:                                   # both ranks hold the same weights
         torch.testing.assert_close(over[0][0][k], over[1][0][k], rtol=0, atol=0)
+
+
+class _KernelStyleLinear(torch.autograd.Function):
+    """Stands in for the GPU kernel path on CPU ranks: backward accumulates the weight gradient straight into
+    ``main_grad`` and reports it, like ops/fused.py::_LinearFn and _EmbeddingFn do."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w.detach())
+        ctx.w_ref = w
+        return x @ w.detach().t()
+
+    @staticmethod
+    def backward(ctx, dy):
+        from mindspore_b200.nn.optim import notify_grad_written
+        x, w = ctx.saved_tensors
+        ctx.w_ref.main_grad.add_(dy.t() @ x)
+        notify_grad_written(ctx.w_ref)
+        return dy @ w, None
+
+
+def _tied_worker(rank, world, overlap):
+    """A weight used twice in one step (tied table): its bucket may only be reduced after the second write."""
+    import os
+    os.environ["MSB200_DP_OVERLAP"] = "1" if overlap else "0"
+    import mindspore_b200 as ms
+    from mindspore_b200 import nn
+    from mindspore_b200.communication import GlobalComm, init
+    from mindspore_b200.common.parameter import Parameter
+    from mindspore_b200.nn.optim import note_grad_producer
+    from mindspore_b200.parallel import zero
+    ms.set_context(device_target="CPU")
+    init("mccl")
+    torch.manual_seed(5)
+
+    class Tied(nn.Cell):
+        def __init__(self):
+            super().__init__()
+            self.table = Parameter(torch.randn(12, 12) * 0.3, name="table")
+            self.mid = nn.Dense(12, 12)
+
+        def construct(self, x):
+            note_grad_producer(self.table)
+            h = _KernelStyleLinear.apply(x, self.table)            # first use (its backward runs last)
+            h = torch.tanh(self.mid(h))
+            note_grad_producer(self.table)
+            return _KernelStyleLinear.apply(h, self.table).pow(2).mean()   # second use (backward runs first)
+
+    net = Tied()
+    opt = nn.AdamWeightDecay(net.trainable_params(), learning_rate=1e-2, use_arena=True)
+    opt.set_data_parallel_group(GlobalComm.WORLD_COMM_GROUP, mean=True, shard=False)
+    step = nn.TrainOneStepCell(net, opt)
+    g = torch.Generator().manual_seed(40 + rank)
+    for _ in range(2):
+        step(ms.Tensor(torch.randn(6, 12, generator=g)))
+    torch.distributed.barrier()
+    return {p.name: p.detach().clone() for p in net.get_parameters()}, zero._last_overlapped
+
+
+def test_overlap_waits_for_the_last_write_of_a_shared_parameter():
+    on = run_ranks(_tied_worker, 2, True)
+    off = run_ranks(_tied_worker, 2, False)
+    assert on[0][1] > 0, "the overlap path did not run"
+    for (p_on, _), (p_off, _) in zip(on, off):
+        for name in p_on:
+            torch.testing.assert_close(p_on[name], p_off[name], rtol=0, atol=0)
+    for name in on[0][0]:                       # replicas stay identical
+        torch.testing.assert_close(on[0][0][name], on[1][0][name], rtol=0, atol=0)
+
+
+def _loss_scale_worker(rank, world):
+    import mindspore_b200 as ms
+    from mindspore_b200 import nn
+    from mindspore_b200.communication import GlobalComm, init
+    ms.set_context(device_target="CPU")
+    init("mccl")
+    net = _net(ms, nn)
+    opt = _opt(nn, net, 0.0)
+    opt.set_data_parallel_group(GlobalComm.WORLD_COMM_GROUP, mean=True, shard=False)
+    step = nn.TrainOneStepWithLossScaleCell(net, opt, nn.DynamicLossScaleUpdateCell(1024.0, 2.0, 1000))
+    x, y = _data()
+    n = x.shape[0] // world
+    for _ in range(3):
+        step(ms.Tensor(x[rank * n:(rank + 1) * n]), ms.Tensor(y[rank * n:(rank + 1) * n]))
+    torch.distributed.barrier()
+    return {p.name: p.detach().clone() for p in net.get_parameters()}
+
+
+def test_loss_scale_cell_synchronises_gradients_over_the_data_parallel_group():
+    ref = _single(0.0)
+    for params in run_ranks(_loss_scale_worker, 2):
+        for name, value in params.items():
+            torch.testing.assert_close(value, ref[name], rtol=1e-4, atol=1e-5)
+
+
+def test_overflow_step_does_not_advance_the_optimizer_step():
+    import mindspore_b200 as ms
+    from mindspore_b200 import nn
+    net = _net(ms, nn)
+    opt = _opt(nn, net, 0.0)
+    step = nn.TrainOneStepWithLossScaleCell(net, opt, nn.DynamicLossScaleUpdateCell(1024.0, 2.0, 1000))
+    x, y = _data()
+    before = {p.name: p.detach().clone() for p in net.get_parameters()}
+    bad = x.clone()
+    bad[0, 0] = float("inf")
+    _, overflow, scale = step(ms.Tensor(bad), ms.Tensor(y))
+    assert bool(overflow) and opt._step_host == 0 and int(opt.global_step) == 0
+    assert float(step.scale_sense) == 512.0
+    for p in net.get_parameters():
+        torch.testing.assert_close(p.detach(), before[p.name], rtol=0, atol=0)
+    _, overflow, _ = step(ms.Tensor(x), ms.Tensor(y))
+    assert not bool(overflow) and opt._step_host == 1 and int(opt.global_step) == 1
