@@ -35,7 +35,11 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "tp", "library"],
+                    help="ours: strategy-driven model on the fused sm_100a kernels (default); reference: the "
+                         "unmodified reference framework (unavailable offline); tp: the hand-placed tensor-parallel "
+                         "formulation on the same kernels; library: the same model on torch ops (cuBLAS / SDPA / "
+                         "fused Adam) with un-fused NCCL collectives")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is marked invalid)")
     ap.add_argument("--global-batch", type=int, default=32)
     ap.add_argument("--seq", type=int, default=4096)
@@ -349,6 +353,13 @@ def main():
     args = parse()
     if args.impl == "reference":
         return run_reference(args)
+    if args.impl == "library":
+        import bench_library
+        if args.model == "resnet50":
+            return bench_library.run_resnet(args, ClockSampler)
+        if args.model == "llama2-7b":
+            return bench_library.run_llama(args, ClockSampler)
+        raise SystemExit("--impl library covers llama2-7b and resnet50")
     if args.model == "resnet50":
         return run_resnet(args)
     if args.model in ("gpt-2.6b", "moe-8x"):
@@ -359,7 +370,6 @@ def main():
     from mindspore_b200 import _native, nn
     from mindspore_b200.communication import management as M
     from mindspore_b200.models.llama import LlamaConfig, LlamaForCausalLM
-    from mindspore_b200.parallel import tp as TP
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -380,17 +390,24 @@ def main():
         init("nccl")
         ms.set_auto_parallel_context(parallel_mode="semi_auto_parallel", device_num=world, global_rank=rank,
                                      full_batch=True, enable_parallel_optimizer=False)
-    tp = TP.TPGroup() if world > 1 else TP.TPGroup(name=None, size=1, rank=0)
     ms.set_seed(1234)
 
+    # The network is primitives + shard strategies only (models/llama.py); under semi_auto_parallel the dispatcher
+    # slices the parameters, inserts AllGather / ReduceScatter where the layouts ask for them and runs each
+    # (collective, MatMul) pair as one fused NVLink kernel.  --impl tp selects the hand-placed formulation.
     cfg = LlamaConfig(model_parallel=world, seq_length=args.seq)
     if args.layers:
         cfg.num_layers = args.layers
-    net = LlamaForCausalLM(cfg, tp)
+    if args.impl == "tp":
+        from mindspore_b200.models import llama_tp
+        from mindspore_b200.parallel import tp as TP
+        net = llama_tp.LlamaForCausalLM(cfg, TP.TPGroup() if world > 1 else TP.TPGroup(name=None, size=1, rank=0))
+    else:
+        net = LlamaForCausalLM(cfg)
     opt = nn.AdamWeightDecay(net.trainable_params(), learning_rate=1e-4, beta1=0.9, beta2=0.95, eps=1e-8,
                              weight_decay=0.1, max_grad_norm=1.0)
     if world > 1:
-        opt.set_model_parallel_group(tp.name)
+        opt.set_model_parallel_group(M.GlobalComm.WORLD_COMM_GROUP)
     micro = args.global_batch          # micro-batch size 1 -> one micro-batch per sequence
     step_cell = nn.TrainOneStepCell(nn.GradAccumulationCell(net, micro), opt)
     step_cell.set_train()
@@ -469,6 +486,8 @@ def main():
                        "ffn": cfg.ffn_hidden_size, "vocab": cfg.vocab_size, "global_batch": args.global_batch,
                        "micro_batch": 1, "seq_len": args.seq,
                        "parallelism": "mp%d+sp" % world if world > 1 else "single",
+                       "formulation": "shard strategies (semi_auto_parallel dispatcher)" if args.impl == "ours"
+                       else "hand-placed tensor parallel",
                        "optimizer": "AdamW fp32 master + moments, grad clip 1.0",
                        "cuda_graph": bool(ms.get_context("enable_cuda_graph")),
                        "fused_comm": bool(world > 1 and os.environ.get("MSB200_FUSED_COMM", "1") != "0"),

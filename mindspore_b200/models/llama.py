@@ -1,15 +1,25 @@
-"""Llama-2 style decoder (RMSNorm, RoPE, SwiGLU, optional grouped kv heads) with tensor + sequence parallelism.
+"""Llama-2 style decoder (RMSNorm, RoPE, SwiGLU, optional grouped kv heads), written with primitives and shard
+strategies only.
 
-The network is written against the framework's own cells and fused ops; with ``parallel_config.model_parallel =
-mp`` every Dense becomes column- or row-parallel (weights are created already sharded, so a 7B model never
-materialises in full on one GPU), activations between the parallel regions are token-sharded, the embedding and
-the LM head are vocabulary-parallel and the loss is the vocab-parallel cross entropy.
+Every operator of a block is an ``ops`` primitive; model parallelism is nothing but the strategies set on them
+(``cfg.model_parallel = mp``, reference notation):
 
-Shard strategies equivalent to what this model does, in the reference's notation (mp = model_parallel):
-  wqkv / w_gate_up : MatMul.shard(((1, 1), (mp, 1)))                      column parallel
-  wo / w_down      : MatMul.shard(((1, mp), (1, mp)), out_strategy=((mp, 1),))   row parallel + ReduceScatter
-  RMSNorm, residual: shard(((mp, 1),)) on the token dim                    sequence parallel
-  FlashAttention   : shard over heads (mp)
+  wqkv / w_gate_up / lm_head : MatMul(transpose_b).shard(((1, 1), (mp, 1)))                  column parallel
+  wo / w_down                : MatMul(transpose_b).shard(((1, mp), (1, mp)), out_strategy=((mp, 1),))
+                                                                                row parallel -> ReduceScatter
+  (Add)RmsNorm, residual     : shard(((mp, 1), ..., (1,)))         token (sequence) parallel, gamma mirrored
+  RotaryFlashAttention       : shard(((1, mp), (1, 1), (1, 1)))    heads over mp
+  SwiGLU                     : shard(((1, mp),))
+  embedding                  : Gather.shard(((mp, 1), (1,)), out_strategy=((mp, 1),))   vocabulary parallel
+  loss                       : SparseSoftmaxCrossEntropyWithLogits.shard(((1, mp), (1,)))  vocabulary parallel
+
+Under ``semi_auto_parallel`` the dispatcher (``parallel/spmd.py``) derives layouts from these strategies, slices
+the parameters, inserts the redistribution (the AllGather in front of a column-parallel MatMul) and the forward
+communication (the ReduceScatter behind a row-parallel one) - and runs each (collective, MatMul) pair as one fused
+NVLink kernel.  With ``sequence_parallel=False`` the row-parallel MatMuls all-reduce and the norms run replicated.
+In stand-alone mode the same code runs the kernels directly.  ``models/llama_tp.py`` is the hand-placed
+tensor-parallel formulation of the same network, kept as the baseline the strategy-driven one is tested against.
+
 Parity: the reference's Llama system test model (tests/st/networks/llama/parallel_llama.py:66-112, mindformers
 Llama) and parallel/_transformer/transformer.py building blocks.
 """
@@ -20,13 +30,12 @@ from dataclasses import dataclass
 
 import torch
 
-from .. import nn
+from .. import nn, ops
 from ..common import dtype as mstype
 from ..common.initializer import Normal, initializer
 from ..common.parameter import Parameter
 from ..ops import fused
-from ..ops.primitive import _wrap_out
-from ..parallel import tp as TP
+from ..parallel import spmd
 
 
 @dataclass
@@ -69,90 +78,114 @@ class LlamaConfig:
 LLAMA2_7B = LlamaConfig()
 
 
-def _param(shape, std, dtype, name):
+def _mp(cfg):
+    """Model-parallel width the strategies use: ``cfg.model_parallel`` when the dispatcher is active, else 1."""
+    return cfg.model_parallel if (cfg.model_parallel > 1 and spmd.active()) else 1
+
+
+def _sharded(prim, *strategy, out=None):
+    """``prim.shard`` when there is something to shard (keeps stand-alone runs free of strategy warnings)."""
+    if any(s != 1 for st in strategy for s in st):
+        prim.shard(tuple(strategy), out)
+    return prim
+
+
+def _weight(shape, std, dtype, name, prim):
+    """Full-shape parameter, sliced at once to what input 1 of ``prim`` (a MatMul) needs."""
     p = Parameter(initializer(Normal(std), shape, dtype), name=name)
-    p.tp_sharded = True          # every matrix of this model is sharded over the model-parallel group
-    return p
-
-
-def _norm_weight(cfg, tp, name):
-    p = Parameter(torch.ones(cfg.hidden_size, dtype=cfg.dtype), name=name)
-    # replicated over the model-parallel group but fed by token-sharded activations: gradients are partial sums
-    p.tp_grad_reduce = tp.active and cfg.sequence_parallel
-    return p
+    return spmd.shard_parameter(p, prim, 1)
 
 
 class LlamaAttention(nn.Cell):
-    def __init__(self, cfg: LlamaConfig, tp: TP.TPGroup):
+    def __init__(self, cfg: LlamaConfig):
         super().__init__()
-        mp = tp.size
-        if cfg.num_heads % mp or cfg.num_kv_heads % mp:
+        mp = _mp(cfg)
+        if cfg.num_heads % cfg.model_parallel or cfg.num_kv_heads % cfg.model_parallel:
             raise ValueError("heads (%d, kv %d) must be divisible by model_parallel %d"
-                             % (cfg.num_heads, cfg.num_kv_heads, mp))
-        self.cfg, self.tp = cfg, tp
-        self.heads, self.kv_heads, self.d = cfg.num_heads // mp, cfg.num_kv_heads // mp, cfg.head_dim
-        qkv_out = (self.heads + 2 * self.kv_heads) * self.d
-        self.wqkv = _param((qkv_out, cfg.hidden_size), cfg.init_std, cfg.dtype, "wqkv")
-        self.wo = _param((cfg.hidden_size, self.heads * self.d), cfg.init_std / math.sqrt(2 * cfg.num_layers),
-                         cfg.dtype, "wo")
+                             % (cfg.num_heads, cfg.num_kv_heads, cfg.model_parallel))
+        sp = cfg.sequence_parallel
+        d = cfg.head_dim
+        self.qkv_proj = _sharded(ops.MatMul(transpose_b=True), (1, 1), (mp, 1))
+        self.attention = _sharded(ops.RotaryFlashAttention(cfg.num_heads, cfg.num_kv_heads, d,
+                                                           groups=cfg.model_parallel, causal=True),
+                                  (1, mp), (1, 1), (1, 1))
+        self.out_proj = _sharded(ops.MatMul(transpose_b=True), (1, mp), (1, mp),
+                                 out=((mp, 1),) if (sp and mp > 1) else None)
+        qkv_out = (cfg.num_heads + 2 * cfg.num_kv_heads) * d
+        self.wqkv = _weight((qkv_out, cfg.hidden_size), cfg.init_std, cfg.dtype, "wqkv", self.qkv_proj)
+        self.wo = _weight((cfg.hidden_size, cfg.num_heads * d), cfg.init_std / math.sqrt(2 * cfg.num_layers),
+                          cfg.dtype, "wo", self.out_proj)
 
-    def construct(self, x, cos, sin, batch, seq):
+    def construct(self, x, cos, sin):
         """x: [tokens(/mp), hidden] -> [tokens(/mp), hidden]"""
-        sp = self.cfg.sequence_parallel
-        qkv = TP.column_parallel_linear(x, self.wqkv, self.tp, sequence_parallel=sp)      # [T, (h+2hk)*d]
-        hd = self.heads * self.d
-        o = fused.qkv_rope_attention(qkv, cos, sin, batch, seq, self.heads, self.kv_heads, self.d, causal=True)
-        return TP.row_parallel_linear(o.reshape(batch * seq, hd), self.wo, self.tp, sequence_parallel=sp)
+        qkv = self.qkv_proj(x, self.wqkv)                 # [T, (h + 2 hk) d], heads split over mp
+        o = self.attention(qkv, cos, sin)                 # [T, h d]
+        return self.out_proj(o, self.wo)
 
 
 class LlamaMLP(nn.Cell):
-    def __init__(self, cfg: LlamaConfig, tp: TP.TPGroup):
+    def __init__(self, cfg: LlamaConfig):
         super().__init__()
-        if cfg.ffn_hidden_size % tp.size:
+        if cfg.ffn_hidden_size % cfg.model_parallel:
             raise ValueError("ffn_hidden_size must be divisible by model_parallel")
-        self.cfg, self.tp = cfg, tp
-        f = cfg.ffn_hidden_size // tp.size
-        self.w_gate_up = _param((2 * f, cfg.hidden_size), cfg.init_std, cfg.dtype, "w_gate_up")
-        self.w_down = _param((cfg.hidden_size, f), cfg.init_std / math.sqrt(2 * cfg.num_layers), cfg.dtype, "w_down")
+        mp = _mp(cfg)
+        sp = cfg.sequence_parallel
+        self.gate_up_proj = _sharded(ops.MatMul(transpose_b=True), (1, 1), (mp, 1))
+        self.act = _sharded(ops.SwiGLU(groups=cfg.model_parallel), (1, mp))
+        self.down_proj = _sharded(ops.MatMul(transpose_b=True), (1, mp), (1, mp),
+                                  out=((mp, 1),) if (sp and mp > 1) else None)
+        f = cfg.ffn_hidden_size
+        self.w_gate_up = _weight((2 * f, cfg.hidden_size), cfg.init_std, cfg.dtype, "w_gate_up", self.gate_up_proj)
+        self.w_down = _weight((cfg.hidden_size, f), cfg.init_std / math.sqrt(2 * cfg.num_layers), cfg.dtype,
+                              "w_down", self.down_proj)
 
     def construct(self, x):
-        sp = self.cfg.sequence_parallel
-        gu = TP.column_parallel_linear(x, self.w_gate_up, self.tp, sequence_parallel=sp)
-        return TP.row_parallel_linear(fused.swiglu(gu), self.w_down, self.tp, sequence_parallel=sp)
+        return self.down_proj(self.act(self.gate_up_proj(x, self.w_gate_up)), self.w_down)
+
+
+def _norm_prims(cfg):
+    mp = _mp(cfg) if cfg.sequence_parallel else 1
+    return (_sharded(ops.RmsNorm(cfg.rms_norm_eps), (mp, 1), (1,)),
+            _sharded(ops.AddRmsNorm(cfg.rms_norm_eps), (mp, 1), (mp, 1), (1,)))
 
 
 class LlamaDecoderLayer(nn.Cell):
-    def __init__(self, cfg: LlamaConfig, tp: TP.TPGroup):
+    def __init__(self, cfg: LlamaConfig):
         super().__init__()
         self.cfg = cfg
-        self.attention_norm = _norm_weight(cfg, tp, "attention_norm")
-        self.ffn_norm = _norm_weight(cfg, tp, "ffn_norm")
-        self.attention = LlamaAttention(cfg, tp)
-        self.feed_forward = LlamaMLP(cfg, tp)
+        self.attention_norm = Parameter(torch.ones(cfg.hidden_size, dtype=cfg.dtype), name="attention_norm")
+        self.ffn_norm = Parameter(torch.ones(cfg.hidden_size, dtype=cfg.dtype), name="ffn_norm")
+        self.norm, self.add_norm = _norm_prims(cfg)
+        self.attention = LlamaAttention(cfg)
+        self.feed_forward = LlamaMLP(cfg)
 
-    def construct(self, x, delta, cos, sin, batch, seq):
-        """Residual stream is carried as (x, delta): the add is fused into the next RMSNorm kernel."""
-        eps = self.cfg.rms_norm_eps
-        h, x = fused.rms_norm(x, self.attention_norm, eps, delta)
-        a = self.attention(h, cos, sin, batch, seq)
-        h, x = fused.rms_norm(x, self.ffn_norm, eps, a)
+    def construct(self, x, delta, cos, sin):
+        """The residual stream is carried as (x, delta): the add is part of the next norm kernel."""
+        if delta is None:
+            h = self.norm(x, self.attention_norm)[0]
+        else:
+            h, x = self.add_norm(x, delta, self.attention_norm)
+        a = self.attention(h, cos, sin)
+        h, x = self.add_norm(x, a, self.ffn_norm)
         return x, self.feed_forward(h)
 
 
 class LlamaModel(nn.Cell):
-    def __init__(self, cfg: LlamaConfig, tp: TP.TPGroup = None):
+    def __init__(self, cfg: LlamaConfig):
         super().__init__()
         self.cfg = cfg
-        self.tp = tp or TP.TPGroup(size=1, rank=0, name=None)
-        if cfg.model_parallel != self.tp.size:
-            raise ValueError("config.model_parallel (%d) does not match the model-parallel group size (%d)"
-                             % (cfg.model_parallel, self.tp.size))
-        if cfg.vocab_size % self.tp.size:
+        if cfg.vocab_size % cfg.model_parallel:
             raise ValueError("vocab_size must be divisible by model_parallel")
-        self.tok_embeddings = _param((cfg.vocab_size // self.tp.size, cfg.hidden_size), cfg.init_std, cfg.dtype,
-                                     "tok_embeddings")
-        self.layers = nn.CellList([LlamaDecoderLayer(cfg, self.tp) for _ in range(cfg.num_layers)])
-        self.norm_out = _norm_weight(cfg, self.tp, "norm_out")
+        mp = _mp(cfg)
+        sp = cfg.sequence_parallel and mp > 1
+        self.embedding = _sharded(ops.Gather(), (mp, 1), (1,), out=((mp, 1),) if sp else None)
+        self.tok_embeddings = Parameter(initializer(Normal(cfg.init_std), (cfg.vocab_size, cfg.hidden_size),
+                                                    cfg.dtype), name="tok_embeddings")
+        spmd.shard_parameter(self.tok_embeddings, self.embedding, 0,
+                             shapes=[(cfg.vocab_size, cfg.hidden_size), (cfg.model_parallel * 128,)], axis=0)
+        self.layers = nn.CellList([LlamaDecoderLayer(cfg) for _ in range(cfg.num_layers)])
+        self.norm_out = Parameter(torch.ones(cfg.hidden_size, dtype=cfg.dtype), name="norm_out")
+        self.norm, self.add_norm = _norm_prims(cfg)
         self._rope = {}
         if cfg.recompute:
             for layer in self.layers:
@@ -168,41 +201,41 @@ class LlamaModel(nn.Cell):
         """tokens [B, S] int -> hidden states [B*S(/mp), hidden]"""
         batch, seq = tokens.shape
         cos, sin = self.rope(seq, tokens.device)
-        ids = tokens.reshape(-1)
-        x = TP.vocab_parallel_embedding(self.tok_embeddings, ids, self.tp, self.cfg.sequence_parallel)
+        x = self.embedding(self.tok_embeddings, tokens.reshape(-1), 0)
         delta = None
         for layer in self.layers:
-            x, delta = layer(x, delta, cos, sin, batch, seq)
-        h, _ = fused.rms_norm(x, self.norm_out, self.cfg.rms_norm_eps, delta)
-        return h
+            x, delta = layer(x, delta, cos, sin)
+        if delta is None:
+            return self.norm(x, self.norm_out)[0]
+        return self.add_norm(x, delta, self.norm_out)[0]
 
 
 class LlamaForCausalLM(nn.Cell):
     """tokens [B, S+1] (or (inputs, labels)) -> mean next-token cross entropy."""
 
-    def __init__(self, cfg: LlamaConfig, tp: TP.TPGroup = None):
+    def __init__(self, cfg: LlamaConfig):
         super().__init__()
         self.cfg = cfg
-        self.model = LlamaModel(cfg, tp)
-        self.tp = self.model.tp
-        self.lm_head = _param((cfg.vocab_size // self.tp.size, cfg.hidden_size), cfg.init_std, cfg.dtype, "lm_head")
+        mp = _mp(cfg)
+        self.model = LlamaModel(cfg)
+        self.head_proj = _sharded(ops.MatMul(transpose_b=True), (1, 1), (mp, 1))
+        self.loss = _sharded(ops.SparseSoftmaxCrossEntropyWithLogits(), (1, mp), (1,))
+        self.lm_head = _weight((cfg.vocab_size, cfg.hidden_size), cfg.init_std, cfg.dtype, "lm_head", self.head_proj)
 
     def logits(self, tokens):
-        h = self.model(tokens)
-        return TP.column_parallel_linear(h, self.lm_head, self.tp, sequence_parallel=self.cfg.sequence_parallel)
+        return self.head_proj(self.model(tokens), self.lm_head)
 
     def construct(self, tokens, labels=None):
         if labels is None:
             tokens, labels = tokens[:, :-1], tokens[:, 1:]
-        logits = self.logits(tokens)
-        loss = TP.vocab_parallel_cross_entropy(logits, labels.reshape(-1), self.tp)
-        return _wrap_out(loss)
+        return self.loss(self.logits(tokens), labels.reshape(-1))
 
 
-def shard_full_weights(full, cfg: LlamaConfig, mp: int, rank: int):
-    """Slices a dict {name: full tensor} of the mp=1 model into the shard held by ``rank`` of an mp-way model:
-    q/k/v heads and gate/up columns are split per rank inside the fused matrices, wo / w_down by input columns,
-    embedding and LM head by vocabulary rows; norm weights are replicated."""
+def pack_full_weights(full, cfg: LlamaConfig, groups: int):
+    """Re-orders the fused matrices of a {name: full tensor} dict from the plain layout (all q heads, then k, then
+    v; all gate rows, then up) to the one packed in ``groups`` blocks that ``RotaryFlashAttention`` /
+    ``SwiGLU(groups=...)`` read: block i = [q_i, k_i, v_i] (resp. [gate_i, up_i]) of the i-th 1/groups of the heads
+    (resp. FFN rows).  With groups = 1 nothing moves."""
     d = cfg.head_dim
     hq, hk = cfg.num_heads * d, cfg.num_kv_heads * d
     f = cfg.ffn_hidden_size
@@ -210,15 +243,13 @@ def shard_full_weights(full, cfg: LlamaConfig, mp: int, rank: int):
     for name, w in full.items():
         if name.endswith("wqkv"):
             q, k, v = w[:hq], w[hq:hq + hk], w[hq + hk:]
-            out[name] = torch.cat([torch.chunk(q, mp, 0)[rank], torch.chunk(k, mp, 0)[rank],
-                                   torch.chunk(v, mp, 0)[rank]], 0)
+            out[name] = torch.cat([t for i in range(groups) for t in (torch.chunk(q, groups, 0)[i],
+                                                                       torch.chunk(k, groups, 0)[i],
+                                                                       torch.chunk(v, groups, 0)[i])], 0)
         elif name.endswith("w_gate_up"):
             g, u = w[:f], w[f:]
-            out[name] = torch.cat([torch.chunk(g, mp, 0)[rank], torch.chunk(u, mp, 0)[rank]], 0)
-        elif name.endswith("wo") or name.endswith("w_down"):
-            out[name] = torch.chunk(w, mp, 1)[rank]
-        elif name.endswith("tok_embeddings") or name.endswith("lm_head"):
-            out[name] = torch.chunk(w, mp, 0)[rank]
+            out[name] = torch.cat([t for i in range(groups) for t in (torch.chunk(g, groups, 0)[i],
+                                                                       torch.chunk(u, groups, 0)[i])], 0)
         else:
             out[name] = w
     return {k: v.contiguous() for k, v in out.items()}

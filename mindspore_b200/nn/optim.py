@@ -383,15 +383,23 @@ class Optimizer(Cell):
         """Tells the optimizer that parameters flagged ``tp_sharded`` hold different shards on every rank of
         ``group_name`` while the others are replicated there.  The global gradient norm then sums the sharded
         part across the group, and gradients of parameters flagged ``tp_grad_reduce`` (replicated parameters fed
-        by token-sharded activations) are all-reduced over the group before the update."""
+        by token-sharded activations) are all-reduced before the update - over their ``mirror_group`` when the
+        parallel dispatcher recorded one, else over ``group_name``.  The flags are read at the first step, so
+        they may be set by the first forward pass."""
         assert self.arena is not None, "set_model_parallel_group needs the arena form"
         self._mp_group = group_name
+        self._mp_runs_ready = False
+        self._sumsq_sh = torch.zeros_like(self._sumsq)
+
+    def _ensure_mp_runs(self):
+        if getattr(self, "_mp_runs_ready", True):
+            return
         arena = self.arena
 
-        def runs(flag):
+        def runs(key):
             out, start, cur = [], 0, None
             for i, p in enumerate(arena.params):
-                f = bool(getattr(p, flag, False))
+                f = key(p)
                 if cur is None:
                     cur, start = f, i
                 elif f != cur:
@@ -399,9 +407,11 @@ class Optimizer(Cell):
                     cur, start = f, i
             out.append((arena.segment(start, len(arena.params)), cur))
             return out
-        self._norm_runs = runs("tp_sharded")
-        self._reduce_runs = [seg for seg, f in runs("tp_grad_reduce") if f]
-        self._sumsq_sh = torch.zeros_like(self._sumsq)
+        self._norm_runs = runs(lambda p: bool(getattr(p, "tp_sharded", False)))
+        self._reduce_runs = [(seg, g) for seg, g in runs(
+            lambda p: (getattr(p, "mirror_group", None) or self._mp_group)
+            if getattr(p, "tp_grad_reduce", False) else None) if g is not None]
+        self._mp_runs_ready = True
 
     def set_data_parallel_group(self, group_name, mean=True, shard=False, fused=True):
         """Gradients of the arena are averaged over ``group_name`` before the update.  With ``shard`` the fp32
@@ -423,9 +433,9 @@ class Optimizer(Cell):
             return
         from ..communication import comm_func as CF
         from ..communication import management as M
-        g = M._group(group)
-        for s, e in self._reduce_runs:
-            CF._all_reduce_(self.arena.grads[s:e], "sum", g)
+        self._ensure_mp_runs()
+        for (s, e), gname in self._reduce_runs:
+            CF._all_reduce_(self.arena.grads[s:e], "sum", M._group(gname))
 
     def _accumulate_sumsq(self):
         arena = self.arena
@@ -455,6 +465,7 @@ class Optimizer(Cell):
             return
         from ..communication import comm_func as CF
         from ..communication import management as M
+        self._ensure_mp_runs()
         self._sumsq_sh.zero_()
         for (s, e), sharded in self._norm_runs:
             K.sumsq_finite(arena.grads[s:e], self._sumsq_sh if sharded else self._sumsq, self._nonfinite)

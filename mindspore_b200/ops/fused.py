@@ -125,14 +125,16 @@ class _RmsNormFn(torch.autograd.Function):
         ctx.save_for_backward(xsum, w, rstd)
         ctx.w_ref = w
         ctx.has_res = residual is not None
+        rstd_out = rstd.view_as(rstd)
+        ctx.mark_non_differentiable(rstd_out)
         if residual is not None:
-            return y, xsum
+            return y, xsum, rstd_out
         dummy = x.new_empty(0)
         ctx.mark_non_differentiable(dummy)
-        return y, dummy
+        return y, dummy, rstd_out
 
     @staticmethod
-    def backward(ctx, dy, dxsum):
+    def backward(ctx, dy, dxsum, _drstd):
         xsum, w, rstd = ctx.saved_tensors
         mg = getattr(ctx.w_ref, "main_grad", None)
         dres = dxsum.contiguous() if (ctx.has_res and dxsum is not None) else None
@@ -145,16 +147,19 @@ class _RmsNormFn(torch.autograd.Function):
         return dx, dw, None, None
 
 
-def rms_norm(x, w, eps=1e-6, residual=None):
-    """Returns (y, stream) where stream = x + residual (or x).  y = stream * rsqrt(mean(stream^2)+eps) * w."""
+def rms_norm(x, w, eps=1e-6, residual=None, with_rstd=False):
+    """Returns (y, stream) where stream = x + residual (or x).  y = stream * rsqrt(mean(stream^2)+eps) * w.
+    ``with_rstd`` appends the per-row reciprocal RMS (fp32, shape [..., 1])."""
     if _use_kernel(x, w, residual) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384:
         _producer(w)
-        y, stream = _RmsNormFn.apply(x, w, eps, residual)
-        return y, (stream if residual is not None else x)
+        y, stream, rstd = _RmsNormFn.apply(x, w, eps, residual)
+        stream = stream if residual is not None else x
+        return (y, stream, rstd.reshape(*x.shape[:-1], 1)) if with_rstd else (y, stream)
     stream = x if residual is None else x + residual
     xf = stream.float()
-    y = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
-    return y, stream
+    rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    y = (xf * rstd).to(x.dtype) * w
+    return (y, stream, rstd) if with_rstd else (y, stream)
 
 
 class _LayerNormFn(torch.autograd.Function):

@@ -989,8 +989,7 @@ class RmsNorm(Primitive):
         pass
 
     def _run(self, x, gamma):
-        y, _ = fused.rms_norm(x, gamma, self.epsilon)
-        rstd = torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + self.epsilon)
+        y, _, rstd = fused.rms_norm(x, gamma, self.epsilon, with_rstd=True)
         return y, rstd
 
 
@@ -1347,3 +1346,7 @@ __all__ = [n for n, v in list(globals().items()) if isinstance(v, type) and issu
 
 
 from .operations_ext import *  # noqa: E402,F401,F403  (second-tier primitives)
+from .llm_ops import *  # noqa: E402,F401,F403  (fused decoder primitives)
+from . import llm_ops as _llm_ops  # noqa: E402
+
+__all__ = __all__ + list(_llm_ops.__all__)

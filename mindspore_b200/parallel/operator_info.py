@@ -386,6 +386,103 @@ class NormInfo(_AxisOpInfo):
         return outs
 
 
+@register("AddRmsNorm")
+class AddRmsNormInfo(OperatorInfo):
+    """(x, residual, gamma) -> (y, x + residual): x and the residual share one strategy whose normalised (last) dim
+    is whole; gamma is replicated, so under sequence parallelism its gradient is a partial sum per rank (mirror)."""
+
+    def check_strategy(self):
+        OperatorInfo.check_strategy(self)
+        if self.in_strategy[0] != self.in_strategy[1]:
+            raise StrategyError("AddRmsNorm: x and the residual must be split alike, got %s / %s"
+                                % (self.in_strategy[0], self.in_strategy[1]))
+        if self.in_strategy[0][-1] != 1 or any(s != 1 for s in self.in_strategy[2]):
+            raise StrategyError("AddRmsNorm: the normalised dim and gamma can not be split")
+
+    def used_devices(self):
+        return int(np.prod(self.in_strategy[0]))
+
+    def base_dev_matrix(self):
+        return list(self.in_strategy[0])
+
+    def infer_inputs_tensor_map(self):
+        m = [self._k(i) if s > 1 else -1 for i, s in enumerate(self.in_strategy[0])]
+        return [m, list(m), [-1] * len(self.in_shapes[2])]
+
+    def out_shapes(self):
+        return [self.in_shapes[0], self.in_shapes[0]]
+
+    def infer_outputs_tensor_map(self):
+        m = list(self.inputs_tensor_map[0])
+        return [m, list(m)]
+
+
+class _PackedLastDimInfo(OperatorInfo):
+    """Ops on a last dim packed in ``groups`` blocks (``ops/llm_ops.py``): that dim may be split by a divisor of
+    ``groups``; each rank then runs the op with ``groups / split`` blocks."""
+
+    def _groups(self):
+        return int(self.attrs.get("groups", 1))
+
+    def check_strategy(self):
+        OperatorInfo.check_strategy(self)
+        s = self.in_strategy[0][-1]
+        if self._groups() % s:
+            raise StrategyError("%s: the packed dim holds %d groups and can not be split %d ways"
+                                % (self.prim_name, self._groups(), s))
+        for st in self.in_strategy[1:]:
+            if any(x != 1 for x in st):
+                raise StrategyError("%s: only the first input can be split" % self.prim_name)
+
+    def used_devices(self):
+        return int(np.prod(self.in_strategy[0]))
+
+    def base_dev_matrix(self):
+        return list(self.in_strategy[0])
+
+    def infer_inputs_tensor_map(self):
+        maps = [[self._k(i) if s > 1 else -1 for i, s in enumerate(self.in_strategy[0])]]
+        for sh in self.in_shapes[1:]:
+            maps.append([-1] * len(sh))
+        return maps
+
+    def infer_outputs_tensor_map(self):
+        return [list(self.inputs_tensor_map[0])]
+
+    def local_attrs(self):
+        return {"groups": self._groups() // self.in_strategy[0][-1]}
+
+
+@register("SwiGLU")
+class SwiGLUInfo(_PackedLastDimInfo):
+    def out_shapes(self):
+        x = self.in_shapes[0]
+        return [tuple(x[:-1]) + (x[-1] // 2,)]
+
+
+@register("RotaryFlashAttention")
+class RotaryFlashAttentionInfo(_PackedLastDimInfo):
+    """qkv [tokens, (H + 2 Hk) * D] split (t, g): heads over ``g`` ranks (g divides ``groups``); a split token dim
+    must keep whole sequences on a rank (batch split), i.e. tokens / t is a multiple of ``seq_length``."""
+
+    def check_strategy(self):
+        super().check_strategy()
+        t = self.in_strategy[0][0]
+        seq = int(self.in_shapes[1][0]) if len(self.in_shapes) > 1 else 1
+        if t > 1 and (self.in_shapes[0][0] // t) % seq:
+            raise StrategyError("RotaryFlashAttention: a token split of %d would cut sequences of %d tokens" % (t, seq))
+
+    def out_shapes(self):
+        a = self.attrs
+        return [(self.in_shapes[0][0], int(a["head_num"]) * int(a["head_dim"]))]
+
+    def local_attrs(self):
+        g = self.in_strategy[0][-1]
+        a = self.attrs
+        return {"groups": self._groups() // g, "head_num": int(a["head_num"]) // g,
+                "kv_head_num": int(a["kv_head_num"]) // g}
+
+
 @register("ReduceSum", "ReduceMean", "ReduceMax", "ReduceMin", "ReduceAll", "ReduceAny", "ReduceProd")
 class ReduceInfo(_AxisOpInfo):
     def __init__(self, prim, in_shapes, in_strategy, out_strategy=None, stage_devices=1, attrs=None, axis=()):
@@ -515,15 +612,31 @@ class GatherInfo(OperatorInfo):
         p, i = self.in_shapes
         return [tuple(i) + tuple(p[1:])]
 
+    def _reduce_scatter(self):
+        """out_strategy whose dim 0 is split by the vocabulary split: the partial lookups are reduce-scattered over
+        the index rows instead of all-reduced (sequence parallelism starts at the embedding)."""
+        p, i = self.in_strategy
+        if p[0] == 1 or not self.out_strategy or len(i) != 1 or i[0] != 1:
+            return False
+        os_ = tuple(self.out_strategy[0])
+        return os_[0] == p[0] and all(x == 1 for x in os_[1:]) and self.in_shapes[1][0] % p[0] == 0
+
     def infer_outputs_tensor_map(self):
         p, i = self.in_strategy
         ni = len(i)
+        if self._reduce_scatter():
+            return [[self._k(ni)] + [-1] * (len(p) - 1)]
         return [[self._k(t) if s > 1 else -1 for t, s in enumerate(i)] +
                 [self._k(ni + 1 + t) if s > 1 else -1 for t, s in enumerate(p[1:])]]
 
     def infer_forward_comm(self):
         p, i = self.in_strategy
-        self.forward_comm = ("AllReduce", [self._k(len(i))]) if p[0] > 1 else None
+        if p[0] == 1:
+            self.forward_comm = None
+        elif self._reduce_scatter():
+            self.forward_comm = ("ReduceScatter", [self._k(len(i))], 0)
+        else:
+            self.forward_comm = ("AllReduce", [self._k(len(i))])
 
     def vocab_split(self):
         return self.in_strategy[0][0]
@@ -553,25 +666,34 @@ class OneHotInfo(OperatorInfo):
 
 @register("SoftmaxCrossEntropyWithLogits", "SparseSoftmaxCrossEntropyWithLogits")
 class LossInfo(OperatorInfo):
-    """logits [B, C] split (b, 1): batch-parallel loss; the class dim can not be split here (use the
-    vocab-parallel loss for that)."""
+    """logits [B, C] split (b, c).  b > 1: batch-parallel loss, the mean is all-reduced.  c > 1 (sparse variant
+    only): vocabulary-parallel loss - every rank reduces its class shard to (max, sum-exp, target logit), the three
+    numbers per row are combined over the class group and each rank writes the gradient of its own shard; the
+    scalar result is identical on the ranks of that group and its backward does not all-reduce, so those ranks do
+    not count as repeats for the loss divisor."""
 
     def check_strategy(self):
         st = self.in_strategy[0]
-        if st[-1] != 1:
+        if st[-1] != 1 and not self.prim_name.startswith("Sparse"):
             raise StrategyError("%s: the class dim can not be split" % self.prim_name)
-        if self.in_shapes[0][0] % st[0]:
-            raise StrategyError("%s: batch not divisible" % self.prim_name)
+        if self.in_shapes[0][0] % st[0] or self.in_shapes[0][-1] % st[-1]:
+            raise StrategyError("%s: logits %s are not divisible by %s" % (self.prim_name, self.in_shapes[0], st))
+        if st[0] * st[-1] > self.stage_devices or self.stage_devices % (st[0] * st[-1]):
+            raise StrategyError("%s: strategy %s does not fit %d devices" % (self.prim_name, st, self.stage_devices))
+
+    def class_split(self):
+        return int(self.in_strategy[0][-1])
 
     def used_devices(self):
-        return int(self.in_strategy[0][0])
+        return int(self.in_strategy[0][0]) * self.class_split()
 
     def base_dev_matrix(self):
-        return [self.in_strategy[0][0]]
+        return [self.in_strategy[0][0], self.class_split()]
 
     def infer_inputs_tensor_map(self):
         b = self._k(0) if self.in_strategy[0][0] > 1 else -1
-        maps = [[b, -1]]
+        c = self._k(1) if self.class_split() > 1 else -1
+        maps = [[b, c]]
         for sh in self.in_shapes[1:]:
             maps.append([b] + [-1] * (len(sh) - 1))
         return maps
@@ -590,6 +712,9 @@ class LossInfo(OperatorInfo):
     def infer_forward_comm(self):
         if self.prim_name.startswith("Sparse") and self.in_strategy[0][0] > 1:
             self.forward_comm = ("AllReduceMean", [self._k(0)])
+
+    def as_loss_divisor(self):
+        return max(1, self.output_layouts()[0].repeat_num() // self.class_split())
 
 
 @register("FlashAttentionScore")

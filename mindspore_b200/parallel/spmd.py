@@ -87,12 +87,24 @@ def _group_for(dev_matrix, dev_dims):
 
 
 def _mirror(param, layout):
-    """Replicated parameter -> identity whose backward all-reduces the gradient over the replica group."""
+    """Replicated parameter -> identity whose backward all-reduces the gradient over the replica group.
+
+    A parameter whose gradient accumulates in an optimizer arena (``main_grad``) is not wrapped: it is flagged
+    (``tp_grad_reduce`` + ``mirror_group``) and the optimizer all-reduces its accumulated gradient once per step,
+    after the last micro-batch - what the reference's ``_MirrorMicroStepOperator`` does under gradient accumulation
+    (ops/operations/comm_ops.py:1722, frontend/parallel/step_parallel.cc:1234-1322)."""
     from ..ops import comm_ops
     dims = layout.unused_dev_dims()
     if not dims or not param._ms_requires_grad:
         return param
     gname, ranks = _group_for(layout.device_matrix, dims)
+    if getattr(param, "main_grad", None) is not None:
+        if getattr(param, "mirror_group", None) != gname:
+            param.tp_grad_reduce = True
+            param.mirror_group = gname
+        if _record is not None:
+            _record["mirror"] += 1
+        return param
     key = (gname, len(ranks))
     op = _mirror_cache.get(key)
     if op is None:
@@ -130,9 +142,56 @@ def _plain(t):
     return t.as_subclass(torch.Tensor) if type(t) is not torch.Tensor else t
 
 
+_rebase_cache = {}
+
+
+def rebase(cur: TensorLayout, device_matrix):
+    """``cur`` rewritten over ``device_matrix`` (same slices on every rank), or None when that matrix has no axis
+    that walks the ranks the way a split of ``cur`` does.  Producer and consumer operators each derive their own
+    device matrix from their strategy (e.g. [mp, 1] for a token-split norm, [1, 1, mp] for the column-parallel
+    MatMul behind it); bringing both layouts over one matrix lets redistribution inference find the single
+    AllGather / StridedSlice / AlltoAll between them instead of falling back to gather-everything-then-slice."""
+    dm = tuple(int(d) for d in device_matrix)
+    if tuple(cur.device_matrix) == dm:
+        return cur
+    key = (cur, dm)
+    if key in _rebase_cache:
+        return _rebase_cache[key]
+    out = None
+    n = int(np.prod(dm)) if dm else 1
+    if n == cur.num_devices() and not any(isinstance(m, tuple) for m in cur.tensor_map):
+        probe = TensorLayout(dm, [-1] * len(cur.shape), cur.shape)
+        coords = [probe.coord(r) for r in range(n)]
+        idx = [cur.slice_index(r) for r in range(n)]
+        new_map, used, ok = [], set(), True
+        for i in range(len(cur.shape)):
+            c = cur.split_count(i)
+            if c == 1:
+                new_map.append(-1)
+                continue
+            found = None
+            for k in range(len(dm)):
+                a = len(dm) - 1 - k
+                if k in used or dm[a] != c:
+                    continue
+                if all(coords[r][a] == idx[r][i] for r in range(n)):
+                    found = k
+                    break
+            if found is None:
+                ok = False
+                break
+            used.add(found)
+            new_map.append(found)
+        if ok:
+            out = TensorLayout(dm, new_map, cur.shape, cur.opt_shard_size, cur.opt_shard_step)
+    _rebase_cache[key] = out
+    return out
+
+
 def _redistribute(x, cur, need):
     if layouts_equivalent(cur, need):
         return x
+    cur = rebase(cur, need.device_matrix) or cur
     if _record is not None:
         try:
             _record["redistribution"] += RD.lowered_names(RD.infer(cur, need))
@@ -147,6 +206,8 @@ def _prepare_input(x, need: TensorLayout):
             x.init_data(need, set_sliced=True)
             parameter_layouts[x.name] = need
             set_layout(x, need)
+            if any(m != -1 for m in need.tensor_map):
+                x.tp_sharded = True          # ranks hold different slices: its squared norm adds up over the group
         cur = x.param_layout
         y = _redistribute(_mirror(x, cur), cur, need)
         return set_layout(y, need)
@@ -181,6 +242,97 @@ def _forward_comm(y, info, out_index=0):
             return CF.reduce_scatter_autograd(y.contiguous(), "sum", gname)
         return CF.reduce_scatter_autograd(y.movedim(dim, 0).contiguous(), "sum", gname).movedim(0, dim).contiguous()
     raise NotImplementedError(kind)
+
+
+def shard_parameter(param, prim, index, shapes=None, **extra):
+    """Slices ``param`` now according to what input ``index`` of ``prim`` (a primitive with a shard strategy) needs.
+    ``shapes``: full shapes of all tensor inputs of ``prim`` (default: only the parameter's own is known and the
+    other inputs are taken from the strategy as one row / column per split).  Models call it from ``__init__`` so
+    that full weights never stay resident and an optimizer built afterwards packs the slices."""
+    if not active() or prim.in_strategy is None or param.param_layout is not None:
+        return param
+    strategy = prim.in_strategy
+    if shapes is None:
+        shapes = [tuple(s) for s in strategy]
+        shapes[index] = tuple(param.shape)
+        if prim.name in ("MatMul", "BatchMatMul") and len(strategy) == 2:
+            ta, tb = bool(getattr(prim, "transpose_a", False)), bool(getattr(prim, "transpose_b", False))
+            if index == 1:
+                kdim = param.shape[-1] if tb else param.shape[-2]
+                m = strategy[0][-1] if ta else strategy[0][-2]
+                shapes[0] = (kdim, m) if ta else (m, kdim)
+    info = OI.make_info(prim, shapes, strategy, prim.out_strategy, stage_devices(), **extra)
+    need = info.input_layouts()[index]
+    param.init_data(need, set_sliced=True)
+    parameter_layouts[param.name] = need
+    set_layout(param, need)
+    if any(m != -1 for m in need.tensor_map):
+        param.tp_sharded = True
+    return param
+
+
+def _tp_group(gname):
+    from . import tp as TP
+    return TP.TPGroup(name=gname)
+
+
+def _fused_matmul(prim, info, x, w, need):
+    """Row-parallel MatMul whose forward communication is a ReduceScatter over the token rows, and column-parallel
+    MatMul whose first input only needs an AllGather of its token rows, run as ONE kernel each over NVLink
+    (``fused_comm``): the GEMM epilogue pushes / reduces its tiles into the owning rank, the GEMM loader pulls the
+    peers' shards.  Returns the local output or NotImplemented (then redistribution + MatMul + collective run as
+    separate operators).  Reference: forward ops of ops_info/matmul_info.cc:361-403 and the AllGather that
+    tensor_layout/redistribution_operator_infer.cc:98-231 emits in front of the MatMul."""
+    from . import fused_comm as FC
+    if getattr(prim, "transpose_a", False) or not getattr(prim, "transpose_b", False):
+        return NotImplemented
+    if x.dim() != 2 or w.dim() != 2 or not isinstance(w, Parameter):
+        return NotImplemented
+    fc = info.forward_comm
+    if fc is not None and fc[0] == "ReduceScatter" and fc[2] == 0:
+        gname, ranks = _group_for(info.dev_matrix, fc[1])
+        if not FC.available(M._group(gname)):
+            return NotImplemented
+        xl = _plain(_prepare_input(x, need[0]))
+        wl = _prepare_input(w, need[1])
+        if _record is not None:
+            _record["fused"] = "MatMulReduceScatter"
+        return FC.matmul_reduce_scatter(xl, wl, _tp_group(gname))
+    if fc is None:
+        cur = get_layout(x)
+        if cur is None or layouts_equivalent(cur, need[0]):
+            return NotImplemented
+        cur = rebase(cur, need[0].device_matrix) or cur
+        try:
+            ops = RD.infer(cur, need[0])
+        except Exception:  # noqa: BLE001
+            return NotImplemented
+        if ops is None or len(ops) != 1 or ops[0].type != RD.CONCAT or ops[0].dim != 0:
+            return NotImplemented
+        gname, ranks = _group_for(cur.device_matrix, [ops[0].dev_dim])
+        if not FC.available(M._group(gname)):
+            return NotImplemented
+        wl = _prepare_input(w, need[1])
+        if _record is not None:
+            _record["fused"] = "AllGatherMatMul"
+            _record["redistribution"].append("AllGather")
+        return FC.allgather_matmul(_plain(x), wl, _tp_group(gname))
+    return NotImplemented
+
+
+def _vocab_parallel_loss(info, logits, labels, need):
+    """SparseSoftmaxCrossEntropyWithLogits with a split class dim: per-shard (max, sum-exp, target) statistics
+    from one pass over the local logits, combined over the class group; the gradient of the local shard is written
+    in one pass too (``parallel.tp._VocabParallelCE``)."""
+    from . import tp as TP
+    k = info.inputs_tensor_map[0][1]
+    gname, ranks = _group_for(info.dev_matrix, [k])
+    pos = RD._coord_along(info.dev_matrix, _rank() - _stage_base(), k)
+    ll = _plain(_prepare_input(logits, need[0])).contiguous()
+    lb = _plain(_prepare_input(labels, need[1]))
+    if _record is not None:
+        _record["fused"] = "VocabParallelCrossEntropy"
+    return TP._VocabParallelCE.apply(ll, lb, gname, pos, -100)
 
 
 def _follow_strategy(prim, tensors):
@@ -239,8 +391,19 @@ def dispatch(prim, args, kwargs):
         return _run_replicated(prim, args, kwargs)
     global _record, last_dispatch
     _record = {"forward_comm": tuple(info.forward_comm[:2]) if info.forward_comm else None, "redistribution": [],
-               "mirror": 0}
+               "mirror": 0, "fused": None}
     need = info.input_layouts()
+    from ..common.tensor import as_tensor
+    fused_out = NotImplemented
+    if name == "MatMul" and len(tensor_pos) == 2:
+        fused_out = _fused_matmul(prim, info, args[tensor_pos[0]], args[tensor_pos[1]], need)
+    elif name == "SparseSoftmaxCrossEntropyWithLogits" and info.class_split() > 1 and len(tensor_pos) == 2:
+        fused_out = _vocab_parallel_loss(info, args[tensor_pos[0]], args[tensor_pos[1]], need)
+        if fused_out is not NotImplemented:
+            fused_out = _forward_comm(fused_out, info)
+    if fused_out is not NotImplemented:
+        last_dispatch, _record = _record, None
+        return set_layout(as_tensor(fused_out), info.output_layouts()[0])
     local = list(args)
     for j, pos in enumerate(tensor_pos):
         if j < len(need):
@@ -264,7 +427,6 @@ def dispatch(prim, args, kwargs):
     finally:
         for k, v in saved.items():
             setattr(prim, k, v)
-    from ..common.tensor import as_tensor
     last_dispatch, _record = _record, None
     out_lays = info.output_layouts()
     if isinstance(out, torch.Tensor):

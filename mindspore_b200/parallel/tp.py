@@ -52,10 +52,23 @@ def scatter_tokens_reduce(x, tp):
     return CF.reduce_scatter_autograd(x.contiguous(), "sum", tp.name)
 
 
+class _ReduceFromTP(torch.autograd.Function):
+    """AllReduce forward, identity backward: the partner of ``_CopyToTP`` (whose backward all-reduces).  Between
+    the two, replicated activations carry the complete gradient on every rank."""
+
+    @staticmethod
+    def forward(ctx, x, gname):
+        return CF._all_reduce_(x.clone(), "sum", M._group(gname))
+
+    @staticmethod
+    def backward(ctx, dy):
+        return dy, None
+
+
 def reduce_partial(x, tp):
     if not tp.active:
         return x
-    return CF.all_reduce_autograd(x, "sum", tp.name)
+    return _ReduceFromTP.apply(x, tp.name)
 
 
 class _CopyToTP(torch.autograd.Function):

@@ -255,6 +255,7 @@ class DataParallelArena:
             if mp_group is None:
                 K.sumsq_finite(own, opt._sumsq, opt._nonfinite)
             else:
+                opt._ensure_mp_runs()
                 opt._sumsq_sh.zero_()
                 runs = [(s, e, sh) for (s, e), sh in opt._norm_runs]
                 for off, n, sharded in self._ranges_in_slice(runs):

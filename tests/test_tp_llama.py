@@ -17,7 +17,7 @@ def _worker(rank, world, port, device, q):
                       LOCAL_RANK=str(rank))
     import mindspore_b200 as ms
     from mindspore_b200.communication import init
-    from mindspore_b200.models.llama import LlamaConfig, LlamaForCausalLM, shard_full_weights
+    from mindspore_b200.models.llama_tp import LlamaConfig, LlamaForCausalLM, shard_full_weights
     from mindspore_b200.parallel import tp as TP
     ms.set_context(device_target="GPU" if device == "cuda" else "CPU", device_id=rank if device == "cuda" else 0)
     init("nccl" if device == "cuda" else "mccl")
