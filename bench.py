@@ -104,6 +104,18 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def _teardown(step_cell, M):
+    """Orderly end of a multi-rank run: captured CUDA graphs hold NCCL kernels of the communicators, so they are
+    destroyed first (``release_graphs``), then the groups."""
+    import torch
+    torch.distributed.barrier()
+    torch.cuda.synchronize()
+    step_cell.release_graphs()
+    torch.cuda.synchronize()
+    torch.distributed.barrier()
+    M.release()
+
+
 def run_reference(args):
     print(json.dumps({
         "impl": "reference",
@@ -339,13 +351,7 @@ def run_gpt_family(args):
             "final_loss": last, "device_status": status,
             "max_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)}), flush=True)
     if world > 1:
-        torch.distributed.barrier()
-        torch.cuda.synchronize()
-        if use_graph:
-            sys.stdout.flush()
-            sys.stderr.flush()
-            os._exit(0)        # graphs hold NCCL kernels: leave without running either destructor
-        M.release()
+        _teardown(step_cell, M)
     return 0
 
 
@@ -504,15 +510,7 @@ def main():
         }
         print(json.dumps(out), flush=True)
     if world > 1:
-        torch.distributed.barrier()
-        torch.cuda.synchronize()
-        if use_graph:
-            # a captured graph holds NCCL kernels of this communicator; tearing the two down in the wrong order
-            # blocks in the NCCL watchdog, so the process ends here without running either destructor
-            sys.stdout.flush()
-            sys.stderr.flush()
-            os._exit(0)
-        M.release()
+        _teardown(step_cell, M)
     return 0
 
 

@@ -79,8 +79,8 @@ class _VocabParallelCE(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dloss):
         p, loc, inr = ctx.saved_tensors
-        rows = torch.arange(p.shape[0], device=p.device)[inr]
-        p[rows, loc[inr]] -= 1
+        # softmax - onehot, without data-dependent shapes (the micro-batch is captured into a CUDA graph)
+        p = p.scatter_add(1, loc.clamp(0, p.shape[1] - 1)[:, None], -inr.to(p.dtype)[:, None])
         return (p * (dloss / p.shape[0])).to(torch.bfloat16), None, None, None
 
 

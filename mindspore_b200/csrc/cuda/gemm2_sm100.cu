@@ -45,6 +45,10 @@ struct Gemm2Params {
   int M, N, K;
   int out_fp32, accumulate;
   float alpha;
+  // split-K: every output tile is ksplit work items, item j covering k-blocks [j, j+1) * num_kb / ksplit; each item
+  // adds its partial product into C with the TMA reduce epilogue (fp32 accumulate only).  It shortens the last,
+  // partly filled round of tiles when the tile count is a poor multiple of the number of CTA pairs.
+  int ksplit;
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -183,7 +187,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
   const int tiles_m = (p.M + 2 * k2BM - 1) / (2 * k2BM);
   const int tiles_n = (p.N + k2BN - 1) / k2BN;
-  const int total_tiles = tiles_m * tiles_n;
+  const int ksplit = p.ksplit;
+  const int total_tiles = tiles_m * tiles_n * ksplit;      // work items
   const int num_kb = (p.K + k2BK - 1) / k2BK;
   const int pairs = gridDim.x / 2;
   const int pair = blockIdx.x / 2;
@@ -218,7 +223,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     p.debug[rank * 2 + 1] = static_cast<int>(tmem_base);
   }
 
-  auto tile_coords = [&](int tile, int& m_blk, int& n_blk) {
+  // k-block range [kb0, kb1) of a work item
+  auto k_range = [&](int item, int& kb0, int& kb1) {
+    const int ks = item % ksplit;
+    kb0 = static_cast<int>(static_cast<long long>(ks) * num_kb / ksplit);
+    kb1 = static_cast<int>(static_cast<long long>(ks + 1) * num_kb / ksplit);
+  };
+  auto tile_coords = [&](int item, int& m_blk, int& n_blk) {
+    const int tile = item / ksplit;
     const int group_sz = 4 * tiles_n;            // groups of 4 m-tiles share B tiles in L2
     const int g = tile / group_sz;
     const int first_m = g * 4;
@@ -239,7 +251,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         tile_coords(tile, m_blk, n_blk);
         const int m0 = m_blk * 2 * k2BM + static_cast<int>(rank) * k2BM;
         const int n0 = n_blk * k2BN + static_cast<int>(rank) * (k2BN / 2);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int kb0, kb1;
+        k_range(tile, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait_cluster(&empty_bar[s], ph ^ 1, ab)) { ok = false; break; }
           // both CTAs' bytes are counted on the leader's barrier; only the leader announces them
           if (leader) mbar_expect_tx(&full_bar[s], 2 * k2StageBytes);
@@ -279,7 +293,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (!mbar_wait_cluster(&tempty_bar[acc], acc_ph ^ 1, ab)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t d_tmem = tmem_base + acc * k2BN;
-          for (int kb = 0; kb < num_kb; ++kb) {
+          int kb0, kb1;
+          k_range(tile, kb0, kb1);
+          for (int kb = kb0; kb < kb1; ++kb) {
             if (!mbar_wait(&full_bar[s], ph, ab)) { ok = false; break; }      // both CTAs' halves have landed
             tc_fence_after_sync();
             const uint32_t a_addr = smem_u32(smem_a + s * k2ABytes);
@@ -290,7 +306,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                                           : umma_smem_desc(a_addr + kk * 32, 16, 1024);
               const uint64_t bdesc = B_MN ? umma_smem_desc(b_addr + kk * 2048, 8192, 1024)
                                           : umma_smem_desc(b_addr + kk * 32, 16, 1024);
-              umma2_bf16(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0);
+              umma2_bf16(d_tmem, adesc, bdesc, idesc, ((kb - kb0) | kk) != 0);
             }
             umma2_commit_pair(&empty_bar[s]);
             if (++s == k2Stages) { s = 0; ph ^= 1; }
@@ -401,6 +417,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
 using namespace msb;
 
+static int g_pair_splitk_auto = 1;
+
+// 1 (default): accumulating fp32 GEMMs choose a split-K factor by themselves; 0: never split.
+MSB_EXPORT void msb_gemm_pair_set_splitk(int enabled) { g_pair_splitk_auto = enabled ? 1 : 0; }
+
 template <bool A_MN, bool B_MN, int ACC>
 static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const Gemm2Params& p,
                         cudaStream_t stream) {
@@ -431,9 +452,30 @@ static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CU
     max_pairs = n;
   }
   const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
+  Gemm2Params q = p;
+  q.ksplit = 1;
+  if (p.ksplit == 0 && p.accumulate && p.out_fp32 && !p.bias && g_pair_splitk_auto) {
+    // pick the split with the fewest (rounds x length): rounds = ceil(tiles * s / pairs), each 1/s long, plus a
+    // per-item cost of about two k-blocks for the pipeline fill and the read-modify-write epilogue
+    const int num_kb = (p.K + k2BK - 1) / k2BK;
+    double best = 1e30;
+    for (int s = 1; s <= 4; ++s) {
+      if (num_kb / s < 8) break;
+      const int rounds = (tiles * s + max_pairs - 1) / max_pairs;
+      const double cost = rounds * (static_cast<double>(num_kb) / s + 2.0);
+      if (cost < best * 0.97) { best = cost; q.ksplit = s; }
+    }
+  } else if (p.ksplit > 1) {
+    if (!(p.accumulate && p.out_fp32)) {
+      set_last_error("gemm_pair: split-K needs an fp32 output that is accumulated into");
+      return kBadArg;
+    }
+    q.ksplit = p.ksplit;
+  }
+  const int items = tiles * q.ksplit;
   int pairs = max_pairs;
-  if (tiles < pairs) pairs = tiles;
-  kern<<<2 * pairs, k2Threads, k2SmemBytes, stream>>>(tmA, tmB, tmC, p);
+  if (items < pairs) pairs = items;
+  kern<<<2 * pairs, k2Threads, k2SmemBytes, stream>>>(tmA, tmB, tmC, q);
   MSB_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }

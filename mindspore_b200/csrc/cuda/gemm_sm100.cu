@@ -49,6 +49,9 @@ struct GemmParams {
   const void* ag_src[8];
   void* ag_dst;
   int* ag_flags;
+  // ag_in_kernel = 0: the chunks are brought in by the copy engines instead (peer -> local copies on side streams,
+  // each followed by a copy of 1 into ag_flags[c]); warp 6 idles and a chunk is ready when its flag is >= 1.
+  int ag_in_kernel, ag_flag_target;
   int world, rank, rows_per_rank;
   // The epilogue stages 32 rows x 128 bytes per warp in shared memory (128-byte swizzle) and writes them with TMA
   // stores (fp32 accumulation = TMA reduce-add): full 128-byte lines instead of 16-byte fragments per row, which is
@@ -183,7 +186,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int chunk = m0 / p.rows_per_rank;
           const volatile int* flag = p.ag_flags + chunk;
           const unsigned long long t0 = globaltimer_ns();
-          while (*flag < static_cast<int>(gridDim.x)) {
+          while (*flag < p.ag_flag_target) {
             if (*cta_abort) { ok = false; break; }
             if (globaltimer_ns() - t0 > kWaitLimitNs) {
               *cta_abort = 1;
@@ -440,7 +443,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   }
 
-  if (MODE == 2 && warp == 6) {
+  if (MODE == 2 && warp == 6 && p.ag_in_kernel) {
     // ------------------------------------------------------------------ AllGather copy warp
     // One lane moves this CTA's share of every chunk peer -> shared bounce buffer -> local gathered operand
     // with bulk copies (two buffers in flight), own chunk first, then ranks rank+1, rank+2, ...
@@ -635,6 +638,42 @@ MSB_EXPORT int msb_gemm_bf16(const void* A, const void* B, void* C, const void* 
 #undef MSB_DISPATCH
 }
 
+namespace msb {
+
+static __device__ int g_ag_ones[8] = {1, 1, 1, 1, 1, 1, 1, 1};
+
+// Per-device side streams / events for the copy-engine all-gather of msb_gemm_ag.  Created on the first call of a
+// device (outside any stream capture: the callers run eagerly before they capture).
+struct AgDma {
+  cudaStream_t side[2];
+  cudaEvent_t fork, join[2];
+  int* ones;
+  bool ready;
+};
+
+static int ag_dma_state(AgDma** out) {
+  static AgDma state[64] = {};
+  int dev = 0;
+  MSB_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) { set_last_error("gemm_ag: device ordinal %d out of range", dev); return kBadArg; }
+  AgDma* st = &state[dev];
+  if (!st->ready) {
+    for (int i = 0; i < 2; ++i) {
+      MSB_CUDA_CHECK(cudaStreamCreateWithFlags(&st->side[i], cudaStreamNonBlocking));
+      MSB_CUDA_CHECK(cudaEventCreateWithFlags(&st->join[i], cudaEventDisableTiming));
+    }
+    MSB_CUDA_CHECK(cudaEventCreateWithFlags(&st->fork, cudaEventDisableTiming));
+    void* p = nullptr;
+    MSB_CUDA_CHECK(cudaGetSymbolAddress(&p, g_ag_ones));
+    st->ones = static_cast<int*>(p);
+    st->ready = true;
+  }
+  *out = st;
+  return kOk;
+}
+
+}  // namespace msb
+
 static int check_chunks(const char* what, int M, int world, int rank) {
   using namespace msb;
   if (world < 2 || world > 8 || rank < 0 || rank >= world || M % world || (M / world) % kBM) {
@@ -681,11 +720,15 @@ MSB_EXPORT int msb_gemm_rs(const void* A, const void* B, const unsigned long lon
 }
 
 // AllGather -> MatMul.  C[M,N] = gather(A)[M,K] x B^T (+ bias) where chunk c of the gathered operand is pulled from
-// src_ptrs[c] (rank c's [M/world][K] shard in symmetric memory) into `gathered` ([M][K], local) by the kernel
-// itself while tiles of chunks that have already arrived are being multiplied.  flags: int[world], zeroed here.
+// src_ptrs[c] (rank c's [M/world][K] shard in symmetric memory) into `gathered` ([M][K], local) while tiles of
+// chunks that have already arrived are being multiplied.  flags: int[world], zeroed here.
+//   use_dma = 0: a copy warp of every CTA pulls the chunks with bulk copies through shared memory;
+//   use_dma = 1: the copy engines pull them - peer -> local cudaMemcpyAsync on two side streams in ring order
+//                (rank+1, rank+2, ...), each followed by a 4-byte copy that raises the chunk's flag; the SMs only
+//                multiply.  The side streams fork from and join `stream`, so the call also captures into a graph.
 MSB_EXPORT int msb_gemm_ag(const unsigned long long* src_ptrs, void* gathered, int* flags, const void* B, void* C,
                            const void* bias, int M, int N, int K, int b_mn, long long ldb, long long ldc, int world,
-                           int rank, int bn_hint, void* stream_) {
+                           int rank, int bn_hint, int use_dma, void* stream_) {
   using namespace msb;
   if (int rc = check_chunks("gemm_ag", M, world, rank)) return rc;
   if (K % 8) { set_last_error("gemm_ag: K=%d must be a multiple of 8", K); return kBadArg; }
@@ -702,12 +745,44 @@ MSB_EXPORT int msb_gemm_ag(const unsigned long long* src_ptrs, void* gathered, i
   p.world = world; p.rank = rank; p.rows_per_rank = M / world;
   for (int i = 0; i < world; ++i) p.ag_src[i] = reinterpret_cast<const void*>(src_ptrs[i]);
   p.ag_dst = gathered; p.ag_flags = flags;
+  p.ag_in_kernel = use_dma ? 0 : 1;
   CMaps tmC = {};
   if (int rc = encode_output(&tmC.m[0], C, M, N, 1, ldc, 0, 0, &p.tma_epilogue)) return rc;
-  if (bn == 256) {
-    if (b_mn) return launch_gemm<256, false, true, 2>(tmA, tmB, tmC, p, stream);
-    return launch_gemm<256, false, false, 2>(tmA, tmB, tmC, p, stream);
+  const int tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
+  p.ag_flag_target = use_dma ? 1 : (tiles < sm_count() ? tiles : sm_count());
+  AgDma* dma = nullptr;
+  if (use_dma) {
+    if (int rc = ag_dma_state(&dma)) return rc;
+    const size_t chunk_bytes = static_cast<size_t>(p.rows_per_rank) * K * 2;
+    char* dst = static_cast<char*>(gathered);
+    MSB_CUDA_CHECK(cudaEventRecord(dma->fork, stream));
+    for (int i = 0; i < 2; ++i) MSB_CUDA_CHECK(cudaStreamWaitEvent(dma->side[i], dma->fork, 0));
+    for (int sidx = 1; sidx < world; ++sidx) {
+      const int c = (rank + sidx) % world;
+      cudaStream_t q = dma->side[(sidx - 1) & 1];
+      MSB_CUDA_CHECK(cudaMemcpyAsync(dst + c * chunk_bytes, reinterpret_cast<const void*>(src_ptrs[c]), chunk_bytes,
+                                     cudaMemcpyDeviceToDevice, q));
+      MSB_CUDA_CHECK(cudaMemcpyAsync(flags + c, dma->ones, sizeof(int), cudaMemcpyDeviceToDevice, q));
+    }
+    // own shard: on the launching stream, so it is in place before the kernel starts
+    MSB_CUDA_CHECK(cudaMemcpyAsync(dst + rank * chunk_bytes, reinterpret_cast<const void*>(src_ptrs[rank]),
+                                   chunk_bytes, cudaMemcpyDeviceToDevice, stream));
+    MSB_CUDA_CHECK(cudaMemcpyAsync(flags + rank, dma->ones, sizeof(int), cudaMemcpyDeviceToDevice, stream));
   }
-  if (b_mn) return launch_gemm<128, false, true, 2>(tmA, tmB, tmC, p, stream);
-  return launch_gemm<128, false, false, 2>(tmA, tmB, tmC, p, stream);
+  int rc;
+  if (bn == 256) {
+    rc = b_mn ? launch_gemm<256, false, true, 2>(tmA, tmB, tmC, p, stream)
+              : launch_gemm<256, false, false, 2>(tmA, tmB, tmC, p, stream);
+  } else {
+    rc = b_mn ? launch_gemm<128, false, true, 2>(tmA, tmB, tmC, p, stream)
+              : launch_gemm<128, false, false, 2>(tmA, tmB, tmC, p, stream);
+  }
+  if (use_dma) {
+    // join even when the launch failed: a forked side stream must come back before a capture can end
+    for (int i = 0; i < 2; ++i) {
+      MSB_CUDA_CHECK(cudaEventRecord(dma->join[i], dma->side[i]));
+      MSB_CUDA_CHECK(cudaStreamWaitEvent(stream, dma->join[i], 0));
+    }
+  }
+  return rc;
 }

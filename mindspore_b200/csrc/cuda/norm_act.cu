@@ -97,9 +97,12 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
-// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres_in) ; dw_acc[H] += sum_rows dy * xhat.
-// Persistent over rows; per-CTA partial dw kept in registers, one atomicAdd per element at the end.
-template <int ITER>
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres_in) ; dw = sum_rows dy * xhat.
+// Persistent over rows; per-CTA partial dw kept in registers.  Two-stage reduction (ATOMIC = false): CTA b stores
+// its partial as row b of dw_acc[gridDim.x][H] and reduce_partials_kernel sums the rows in a fixed order
+// (deterministic).  ATOMIC = true adds into a single dw_acc[H] instead (the allocation-free entry point, whose
+// scratch is one row).
+template <int ITER, bool ATOMIC>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
@@ -155,9 +158,38 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   for (int it = 0; it < ITER; ++it) {
     const int c = (it * kNormThreads + threadIdx.x) * 8;
     if (c < H) {
+      if (ATOMIC) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) atomicAdd(dw_acc + c + j, dwreg[it][j]);
+        for (int j = 0; j < 8; ++j) atomicAdd(dw_acc + c + j, dwreg[it][j]);
+      } else {
+        float* dst = dw_acc + static_cast<long long>(blockIdx.x) * H + c;
+        *reinterpret_cast<float4*>(dst) = make_float4(dwreg[it][0], dwreg[it][1], dwreg[it][2], dwreg[it][3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(dwreg[it][4], dwreg[it][5], dwreg[it][6], dwreg[it][7]);
+      }
     }
+  }
+}
+
+// Second stage of the weight-gradient reduction: out[c] (+)= sum_b partial[b][c] for b = 0..parts-1, rows visited
+// in a fixed order.  Block = 32 columns x 8 row lanes; lane r sums rows r, r+8, ... and the 8 lanes are combined
+// through shared memory, always in the same order.
+__global__ void __launch_bounds__(256)
+reduce_partials_kernel(const float* __restrict__ partial, int parts, int H, __nv_bfloat16* __restrict__ out_bf16,
+                       float* __restrict__ out_f32, int accumulate) {
+  __shared__ float sm[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
+  float s = 0.f;
+  if (c < H)
+    for (int b = ry; b < parts; b += 8) s += partial[static_cast<long long>(b) * H + c];
+  sm[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && c < H) {
+    float v = sm[0][cx];
+#pragma unroll
+    for (int r = 1; r < 8; ++r) v += sm[r][cx];
+    if (out_f32) out_f32[c] = accumulate ? out_f32[c] + v : v;
+    if (out_bf16) out_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(out_bf16[c]) + v : v);
   }
 }
 
@@ -261,14 +293,18 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
       }
     }
   }
+  // two-stage reduction: this CTA's partial sums are row blockIdx.x of dw_acc / db_acc ([gridDim.x][H] each)
 #pragma unroll
   for (int it = 0; it < ITER; ++it) {
     const int c = (it * kNormThreads + threadIdx.x) * 8;
     if (c < H) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        atomicAdd(dw_acc + c + j, dwreg[it][j]);
-        if (db_acc) atomicAdd(db_acc + c + j, dbreg[it][j]);
+      float* dw = dw_acc + static_cast<long long>(blockIdx.x) * H + c;
+      *reinterpret_cast<float4*>(dw) = make_float4(dwreg[it][0], dwreg[it][1], dwreg[it][2], dwreg[it][3]);
+      *reinterpret_cast<float4*>(dw + 4) = make_float4(dwreg[it][4], dwreg[it][5], dwreg[it][6], dwreg[it][7]);
+      if (db_acc) {
+        float* db = db_acc + static_cast<long long>(blockIdx.x) * H + c;
+        *reinterpret_cast<float4*>(db) = make_float4(dbreg[it][0], dbreg[it][1], dbreg[it][2], dbreg[it][3]);
+        *reinterpret_cast<float4*>(db + 4) = make_float4(dbreg[it][4], dbreg[it][5], dbreg[it][6], dbreg[it][7]);
       }
     }
   }
@@ -437,24 +473,30 @@ MSB_EXPORT int msb_rmsnorm_fwd(const void* x, const void* res, const void* w, vo
 
 // dw_acc: fp32 [H] scratch that this call zeroes, accumulates into and leaves holding sum_rows dy*xhat.
 // dw_out (bf16 or fp32 by dw_fp32) receives (accumulate ? dw_out + dw_acc : dw_acc).
+// Floats of scratch the norm backward launchers need for hidden size H: one partial row per CTA.
+MSB_EXPORT long long msb_norm_bwd_scratch_elems(int H, int with_bias) {
+  return 2LL * sm_count() * H * (with_bias ? 2 : 1);
+}
+
+// dw_acc: fp32 scratch of msb_norm_bwd_scratch_elems(H, 0) floats (per-CTA partial rows; nothing needs clearing).
 MSB_EXPORT int msb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
                                void* dx, float* dw_acc, void* dw_out, int dw_fp32, int accumulate, long long rows,
                                int H, void* stream_) {
   if (int rc = check_h("rmsnorm_bwd", H)) return rc;
   cudaStream_t stream = (cudaStream_t)stream_;
-  MSB_CUDA_CHECK(cudaMemsetAsync(dw_acc, 0, sizeof(float) * H, stream));
+  int grid = 0;
   if (rows > 0) {
-    const int grid = (int)(rows < 2LL * sm_count() ? rows : 2LL * sm_count());
+    grid = (int)(rows < 2LL * sm_count() ? rows : 2LL * sm_count());
 #define CALL(I)                                                                                      \
-  rmsnorm_bwd_kernel<I><<<grid, kNormThreads, 0, stream>>>(                                          \
+  rmsnorm_bwd_kernel<I, false><<<grid, kNormThreads, 0, stream>>>(                                   \
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,              \
       (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, dw_acc, (int)rows, H)
     MSB_ITER_DISPATCH(H, CALL);
 #undef CALL
   }
   if (dw_out) {
-    finalize_acc_kernel<<<(H + 255) / 256, 256, 0, stream>>>(dw_acc, dw_fp32 ? nullptr : (__nv_bfloat16*)dw_out,
-                                                             dw_fp32 ? (float*)dw_out : nullptr, H, accumulate);
+    reduce_partials_kernel<<<(H + 31) / 32, 256, 0, stream>>>(dw_acc, grid, H, dw_fp32 ? nullptr : (__nv_bfloat16*)dw_out,
+                                                             dw_fp32 ? (float*)dw_out : nullptr, accumulate);
   }
   MSB_CUDA_CHECK(cudaGetLastError());
   return kOk;
@@ -474,28 +516,30 @@ MSB_EXPORT int msb_layernorm_fwd(const void* x, const void* w, const void* b, vo
   return kOk;
 }
 
-// acc: fp32 [2*H] scratch (dw then db), zeroed here.
+// acc: fp32 scratch of msb_norm_bwd_scratch_elems(H, 1) floats: per-CTA partial rows of dw, then those of db.
 MSB_EXPORT int msb_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
                                  void* dx, float* acc, void* dw_out, void* db_out, int out_fp32, int accumulate,
                                  long long rows, int H, void* stream_) {
   if (int rc = check_h("layernorm_bwd", H)) return rc;
   cudaStream_t stream = (cudaStream_t)stream_;
-  MSB_CUDA_CHECK(cudaMemsetAsync(acc, 0, sizeof(float) * 2 * H, stream));
+  int grid = 0;
+  float* db_part = acc + 2LL * sm_count() * H;
   if (rows > 0) {
-    const int grid = (int)(rows < 2LL * sm_count() ? rows : 2LL * sm_count());
+    grid = (int)(rows < 2LL * sm_count() ? rows : 2LL * sm_count());
 #define CALL(I)                                                                                   \
   layernorm_bwd_kernel<I><<<grid, kNormThreads, 0, stream>>>(                                     \
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, mean, rstd,     \
-      (__nv_bfloat16*)dx, acc, db_out ? acc + H : nullptr, (int)rows, H)
+      (__nv_bfloat16*)dx, acc, db_out ? db_part : nullptr, (int)rows, H)
     MSB_ITER_DISPATCH(H, CALL);
 #undef CALL
   }
   if (dw_out)
-    finalize_acc_kernel<<<(H + 255) / 256, 256, 0, stream>>>(acc, out_fp32 ? nullptr : (__nv_bfloat16*)dw_out,
-                                                             out_fp32 ? (float*)dw_out : nullptr, H, accumulate);
+    reduce_partials_kernel<<<(H + 31) / 32, 256, 0, stream>>>(acc, grid, H, out_fp32 ? nullptr : (__nv_bfloat16*)dw_out,
+                                                             out_fp32 ? (float*)dw_out : nullptr, accumulate);
   if (db_out)
-    finalize_acc_kernel<<<(H + 255) / 256, 256, 0, stream>>>(acc + H, out_fp32 ? nullptr : (__nv_bfloat16*)db_out,
-                                                             out_fp32 ? (float*)db_out : nullptr, H, accumulate);
+    reduce_partials_kernel<<<(H + 31) / 32, 256, 0, stream>>>(db_part, grid, H,
+                                                             out_fp32 ? nullptr : (__nv_bfloat16*)db_out,
+                                                             out_fp32 ? (float*)db_out : nullptr, accumulate);
   MSB_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
@@ -592,7 +636,7 @@ MSB_EXPORT int msb_rmsnorm_bwd_static(const void* dy, const void* x, const void*
   if (rows > 0) {
     const int grid = (int)(rows < 2LL * sm_count() ? rows : 2LL * sm_count());
 #define CALL(I)                                                                                      \
-  rmsnorm_bwd_kernel<I><<<grid, kNormThreads, 0, stream>>>(                                          \
+  rmsnorm_bwd_kernel<I, true><<<grid, kNormThreads, 0, stream>>>(                                    \
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,              \
       (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, acc, (int)rows, H)
     MSB_ITER_DISPATCH(H, CALL);

@@ -43,7 +43,10 @@ def _pair_gemm_ok(M, N, K, batch, out, o2, accumulate, bn_hint):
     es = out.element_size()
     if out.data_ptr() % 16 or (o2.stride(0) * es) % 16 or (accumulate and out.dtype != f32):
         return False
-    return M >= 512 and N >= 512 and ((M + 255) // 256) * ((N + 255) // 256) >= 64
+    tiles = ((M + 255) // 256) * ((N + 255) // 256)
+    if accumulate and K >= 2048:
+        return M >= 512 and N >= 512 and tiles >= 16      # split-K fills the machine with fewer output tiles
+    return M >= 512 and N >= 512 and tiles >= 64
 
 
 def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=bf16, accumulate=False, bias=None,
@@ -119,11 +122,16 @@ def linear_wgrad(dy, x, out=None, accumulate=False, out_dtype=f32):
 _scratch = {}
 
 
-def _acc_scratch(device, n):
+def _acc_scratch(device, H, with_bias=False):
+    """Scratch for the two-stage weight-gradient reduction of the norm backward kernels: one fp32 partial row of H
+    per CTA (the size comes from the library, which knows its grid)."""
+    lib = _native.cuda()
+    lib.msb_norm_bwd_scratch_elems.restype = ctypes.c_longlong
+    n = int(lib.msb_norm_bwd_scratch_elems(int(H), int(with_bias)))
     key = (device, "acc")
     buf = _scratch.get(key)
     if buf is None or buf.numel() < n:
-        buf = torch.empty(max(n, 65536), dtype=f32, device=device)
+        buf = torch.empty(n, dtype=f32, device=device)
         _scratch[key] = buf
     return buf
 
@@ -154,7 +162,7 @@ def rmsnorm_bwd(dy, x, w, rstd, dresidual=None, dw_out=None, accumulate=False):
     rc = _native.cuda().msb_rmsnorm_bwd(_p(dy), _p(x), _p(w), _p(rstd), _p(dresidual), _p(dx), _p(acc), _p(dw_out),
                                         int(dw_out.dtype == f32), int(accumulate), rows, H, _stream())
     _native.check(rc, "rmsnorm_bwd")
-    _count(3)
+    _count(2)
     return dx, dw_out
 
 
@@ -175,7 +183,7 @@ def layernorm_bwd(dy, x, w, mean, rstd, dw_out=None, db_out=None, accumulate=Fal
     H = x.shape[-1]
     rows = x.numel() // H
     dx = torch.empty_like(x)
-    acc = _acc_scratch(x.device, 2 * H)
+    acc = _acc_scratch(x.device, H, with_bias=True)
     if dw_out is None:
         dw_out = torch.empty(H, dtype=w.dtype, device=x.device)
         db_out = torch.empty(H, dtype=w.dtype, device=x.device) if has_bias else None
@@ -183,7 +191,7 @@ def layernorm_bwd(dy, x, w, mean, rstd, dw_out=None, db_out=None, accumulate=Fal
     rc = _native.cuda().msb_layernorm_bwd(_p(dy), _p(x), _p(w), _p(mean), _p(rstd), _p(dx), _p(acc), _p(dw_out),
                                           _p(db_out), int(dw_out.dtype == f32), int(accumulate), rows, H, _stream())
     _native.check(rc, "layernorm_bwd")
-    _count(4)
+    _count(3)
     return dx, dw_out, db_out
 
 

@@ -39,10 +39,12 @@ _native.register_cuda_signature("msb_allreduce_symm", _I, [_U64P, _I, _I, _L, _F
 _native.register_cuda_signature("msb_reduce_slots", _I, [_P, _P, _I, _L, _P])
 _native.register_cuda_signature("msb_reduce_scatter_adamw", _I, [_U64P, _U64P, _P, _P, _P, _I, _I, _L, _P, _P, _P])
 _native.register_cuda_signature("msb_gemm_rs", _I, [_P, _P, _U64P, _I, _I, _I, _I, _L, _L, _I, _I, _I, _P])
-_native.register_cuda_signature("msb_gemm_ag", _I, [_U64P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _I, _I, _I, _P])
+_native.register_cuda_signature("msb_gemm_ag", _I, [_U64P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _I, _I, _I, _I, _P])
 
 _contexts = {}
 _disabled = set()
+# AllGather -> MatMul: 1 = the copy engines pull the peers' shards (SMs only multiply), 0 = a copy warp per CTA does
+_AG_DMA = int(os.environ.get("MSB200_AG_DMA", "1") != "0")
 
 
 def _ptr_array(ptrs):
@@ -204,7 +206,7 @@ def _gemm_ag(ctx, a_shard, b, b_mn, bias=None):
     flags = torch.empty(ctx.world, dtype=torch.int32, device=a_shard.device)
     c = torch.empty((M_, N_), dtype=torch.bfloat16, device=a_shard.device)
     rc = _native.cuda().msb_gemm_ag(_ptr_array(ptrs), _p(gathered), _p(flags), _p(b), _p(c), _p(bias), M_, N_, K_,
-                                    int(b_mn), b.stride(0), N_, ctx.world, ctx.rank, 0, _stream())
+                                    int(b_mn), b.stride(0), N_, ctx.world, ctx.rank, 0, _AG_DMA, _stream())
     _native.check(rc, "gemm_ag")
     _count()
     return c, gathered

@@ -149,8 +149,19 @@ class OperatorInfo:
     def input_layouts(self):
         return [TensorLayout(self.dev_matrix, m, s) for m, s in zip(self.inputs_tensor_map, self.in_shapes)]
 
-    def output_layouts(self):
-        return [TensorLayout(self.dev_matrix, m, s) for m, s in zip(self.outputs_tensor_map, self.out_shapes())]
+    def output_layouts(self, local_shapes=None):
+        """Layouts of the outputs.  An operator that can not tell an output's extents from its attributes returns
+        None for that shape; the layout is then rebuilt from the shape of the local result (``local_shapes``)."""
+        lays = []
+        for i, (m, s) in enumerate(zip(self.outputs_tensor_map, self.out_shapes())):
+            if s is None:
+                if local_shapes is None or i >= len(local_shapes):
+                    raise StrategyError("%s: the output shape is only known after running the local operator"
+                                        % self.prim_name)
+                dm = self.dev_matrix
+                s = tuple(int(d) * (dm[len(dm) - 1 - k] if k != -1 else 1) for d, k in zip(local_shapes[i], m))
+            lays.append(TensorLayout(self.dev_matrix, m, s))
+        return lays
 
     def as_loss_divisor(self):
         """Number of ranks holding the same output slice: the loss gradient is divided by it (_VirtualDiv)."""
@@ -159,6 +170,10 @@ class OperatorInfo:
     def local_attrs(self):
         """Attribute / argument adjustments needed when the op runs on slices (e.g. Reshape target shape)."""
         return {}
+
+    def localize_args(self, others):
+        """Non-tensor call arguments as the local operator must see them (slice ends, tile multiples ...)."""
+        return list(others)
 
     # ---- search
     @classmethod
@@ -191,7 +206,7 @@ def _elementwise_strategies(shape, device_num, limit=64):
 @register("Add", "Sub", "Mul", "Div", "RealDiv", "Pow", "Maximum", "Minimum", "Equal", "NotEqual", "Greater",
           "GreaterEqual", "Less", "LessEqual", "LogicalAnd", "LogicalOr", "FloorDiv", "FloorMod", "Mod", "Atan2",
           "SquaredDifference", "Xdivy", "Xlogy", "BitwiseAnd", "BitwiseOr", "BitwiseXor", "Select", "MaskedFill",
-          "AddN", "Lerp", "Addcmul", "Addcdiv", "BiasAdd", "TruncateDiv", "TruncateMod", "DivNoNan", "MulNoNan",
+          "AddN", "Lerp", "Addcmul", "Addcdiv", "TruncateDiv", "TruncateMod", "DivNoNan", "MulNoNan",
           "Hypot", "ApproximateEqual", "AddExt", "SubExt", "DivMod", "Gcd", "Igamma", "Igammac", "NextAfter",
           "LeftShift", "RightShift", "Betainc", "Assign", "AssignAdd", "AssignSub", "DropoutDoMask", "KLDivLoss",
           "SigmoidCrossEntropyWithLogits", "BinaryCrossEntropy", "SmoothL1Loss", "FakeQuantPerLayer",
@@ -212,8 +227,7 @@ class ArithmeticInfo(OperatorInfo):
           "Dropout", "Lgamma", "Digamma", "BesselI0", "BesselI0e", "BesselI1", "BesselI1e", "Sinc", "Logit",
           "_VirtualDiv", "_VirtualOutput", "_MirrorOperator", "AShardIdentity", "Activation", "BesselJ0", "BesselJ1",
           "HShrink", "SoftShrink", "ClampScalar", "PopulationCount", "Quant", "QuantV2", "Dequant", "AntiQuant",
-          "L2Loss", "FillV2", "PReLU", "VirtualOutput", "SelfDefineShard", "BroadcastTo", "CumProd", "Cummax",
-          "Cummin", "LinSpace", "LinSpaceExt", "Gamma")
+          "L2Loss", "FillV2", "VirtualOutput", "SelfDefineShard", "LinSpace", "LinSpaceExt", "Gamma")
 class ActivationInfo(OperatorInfo):
     @classmethod
     def generate_strategies(cls, in_shapes, device_num):
@@ -753,24 +767,19 @@ class FlashAttentionInfo(OperatorInfo):
         return {"head_num": self.attrs.get("head_num", 1) // self.in_strategy[0][-1]}
 
 
-@register("BatchParallel", "_VirtualDataset", "GetNext", "TopK", "Sort", "Unique", "CumSum", "ArgMaxWithValue",
-          "ArgMinWithValue", "Argmax", "Argmin", "Tile", "ExpandDims", "Squeeze", "Concat", "Split", "StridedSlice",
-          "Slice", "Stack", "ApplyRotaryPosEmb", "Conv2D", "BatchNorm", "MaxPool", "AvgPool", "VirtualDataset",
-          "AvgPool3D", "MaxPool3D", "Conv3D", "Conv2DBackpropInput", "Conv2DTranspose", "Convolution", "GroupNorm",
+@register("BatchParallel", "_VirtualDataset", "GetNext", "Unique", "ApplyRotaryPosEmb", "VirtualDataset",
+          "Conv3D", "Conv2DBackpropInput", "Conv2DTranspose", "GroupNorm",
           "LayerNormV3", "BatchMatMulExt", "MatMulExt", "BoundingBoxEncode", "BoundingBoxDecode", "CheckValid", "IOU",
-          "Cdist", "Cholesky", "CropAndResize", "ROIAlign", "GridSampler2D", "Custom", "DecoderKVCache",
+          "Cdist", "Cholesky", "Custom", "DecoderKVCache",
           "PromptKVCache", "KVCacheMgr", "KVCacheScatterUpdate", "ReshapeAndCache", "PagedAttention",
           "PagedAttentionMask", "IncreFlashAttention", "PromptFlashAttention", "FusedInferAttentionScore",
           "DynamicQuantExt", "FFN", "FFNExt", "FakeQuantPerChannel", "MinMaxUpdatePerChannel", "MinMaxUpdatePerLayer",
-          "GatherD", "GatherNd", "GenerateEodMask", "GroupedMatmul", "IndexSelect", "L2Normalize",
-          "MoeFinalizeRouting", "OneHotExt", "PadV3", "Pad", "QuantBatchMatmul", "WeightQuantBatchMatmul",
+          "GatherNd", "GenerateEodMask", "GroupedMatmul", "IndexSelect", "MoeFinalizeRouting", "OneHotExt", "QuantBatchMatmul", "WeightQuantBatchMatmul",
           "RandomChoiceWithMask", "RepeatElements", "ScatterAdd", "ScatterDiv", "ScatterMax", "ScatterMin",
           "ScatterMul", "ScatterSub", "ScatterUpdate", "ScatterNdAdd", "ScatterNdSub", "ScatterNdUpdate",
           "TensorScatterAdd", "TensorScatterDiv", "TensorScatterMax", "TensorScatterMin", "TensorScatterMul",
           "TensorScatterSub", "TensorScatterUpdate", "UnsortedSegmentMax", "UnsortedSegmentMin",
-          "UnsortedSegmentProd", "UnsortedSegmentSum", "SliceExt", "SplitTensor", "SplitWithSize", "StackExt",
-          "SumExt", "TopkExt", "TensorDot", "UniformCandidateSampler", "WKV", "ResizeBilinearV2",
-          "ResizeNearestNeighbor", "Range", "SquareSumAll", "TopKRouter", "SplitV", "Unstack", "ReverseV2", "Tril", "Triu", "UniformReal", "StandardNormal")
+          "SumExt", "TensorDot", "UniformCandidateSampler", "WKV", "Range", "SquareSumAll", "TopKRouter", "Tril", "Triu", "UniformReal", "StandardNormal")
 class BatchParallelInfo(OperatorInfo):
     """Dim 0 of every input and output is split by the strategy's first entry; other dims stay whole."""
 
@@ -827,3 +836,6 @@ def make_info(prim, in_shapes, in_strategy, out_strategy=None, stage_devices=1, 
             raise StrategyError("primitive %s has no distributed OperatorInfo and its strategy %s is not batch-parallel"
                                 % (prim if isinstance(prim, str) else prim.name, in_strategy))
     return cls(prim, in_shapes, in_strategy, out_strategy, stage_devices, **extra)
+
+
+from . import operator_info_ext  # noqa: E402,F401  (array / convolution / selection operators register themselves)

@@ -355,84 +355,172 @@ def _follow_strategy(prim, tensors):
     return tuple(strat)
 
 
-def dispatch(prim, args, kwargs):
-    """Runs ``prim`` under its shard strategy.  Returns NotImplemented when the primitive takes no tensor."""
-    tensor_pos = [i for i, a in enumerate(args) if isinstance(a, torch.Tensor)]
-    if not tensor_pos:
-        return NotImplemented
-    tensors = [args[i] for i in tensor_pos]
-    strategy = prim.in_strategy
+# Non-tensor call arguments that the OperatorInfo of a primitive needs by name (position among the non-tensor
+# arguments of the call).
+_EXTRA_ARGS = {
+    "Transpose": ("perm",), "Reshape": ("shape",), "Gather": ("axis",), "SparseGatherV2": ("axis",),
+    "OneHot": ("depth",), "StridedSlice": ("begin", "end", "strides"), "Slice": ("begin", "size"),
+    "SliceExt": ("begin", "size"), "Tile": ("multiples",), "ExpandDims": ("axis",), "CumSum": ("axis",),
+    "CumProd": ("axis",), "Cummax": ("axis",), "Cummin": ("axis",), "TopK": ("k",), "TopkExt": ("k",),
+    "GatherD": ("dim",), "UnsortedSegmentSum": ("num_segments",), "UnsortedSegmentProd": ("num_segments",),
+    "ReverseV2": ("axis",), "PadV3": ("paddings",),
+}
+_REDUCE = ("ReduceSum", "ReduceMean", "ReduceMax", "ReduceMin", "ReduceAll", "ReduceAny", "ReduceProd")
+
+
+def _flatten_args(args):
+    """Tensor arguments of a call in order; a tuple / list of tensors (Concat, Stack, AddN) contributes its members.
+    Returns (tensors, slots) with slots[i] = (position, index inside the sequence or None)."""
+    tensors, slots = [], []
+    for i, a in enumerate(args):
+        if isinstance(a, torch.Tensor):
+            tensors.append(a)
+            slots.append((i, None))
+        elif isinstance(a, (tuple, list)) and a and all(isinstance(x, torch.Tensor) for x in a):
+            for j, x in enumerate(a):
+                tensors.append(x)
+                slots.append((i, j))
+    return tensors, slots
+
+
+def build_info(prim, tensors, others, strategy=None):
+    """OperatorInfo of ``prim`` for these tensor inputs (full shapes are taken from their layouts) and non-tensor
+    arguments; ``strategy`` defaults to the primitive's own, else to following the sharded inputs.  Returns None
+    when the call carries nothing to shard."""
+    strategy = prim.in_strategy if strategy is None else strategy
     if strategy is None:
         strategy = _follow_strategy(prim, tensors)
         if strategy is None:
-            return NotImplemented
-    if len(strategy) < len(tensors):
+            return None
+    if len(strategy) < len(tensors) and not (len(strategy) == 1 and prim.name in ("Concat", "Stack", "AddN")):
         strategy = tuple(strategy) + tuple(tuple(1 for _ in full_shape(t)) for t in tensors[len(strategy):])
     shapes = [full_shape(t) for t in tensors]
     extra = {}
     name = prim.name
-    others = [a for i, a in enumerate(args) if i not in tensor_pos]
-    if name in ("ReduceSum", "ReduceMean", "ReduceMax", "ReduceMin", "ReduceAll", "ReduceAny", "ReduceProd"):
+    if name in _REDUCE:
         extra["axis"] = others[0] if others else ()
-    elif name == "Transpose":
-        extra["perm"] = others[0]
-    elif name == "Reshape":
-        extra["shape"] = others[0]
-    elif name in ("Gather", "SparseGatherV2"):
-        extra["axis"] = others[0] if others else 0
-    elif name == "OneHot":
-        extra["depth"] = others[0]
+    else:
+        for key, val in zip(_EXTRA_ARGS.get(name, ()), others):
+            extra[key] = val
+        if name in ("Gather", "SparseGatherV2"):
+            extra.setdefault("axis", 0)
+    n = len(shapes) if len(strategy) == 1 and len(shapes) > 1 else len(strategy)
+    return OI.make_info(prim, shapes[:n], strategy[:len(shapes)], prim.out_strategy, stage_devices(), **extra)
+
+
+def _sync_batch_norm(prim, info, x, scale, bias, mean, var):
+    """Training-mode BatchNorm on a batch (or spatially) split input: per-channel sums are all-reduced over the
+    device dims that spread a channel's samples, then every rank normalises its slice with the global statistics and
+    applies the same moving-average update (reference: the forward AllReduce of ops_info/batchnorm_info.cc)."""
+    from ..communication import comm_func as CF
+    gname, ranks = _group_for(info.dev_matrix, info.stat_dev_dims())
+    c = x.shape[1]
+    dims = [0] + list(range(2, x.dim()))
+    xf = x.float()
+    local = torch.cat([xf.sum(dims), (xf * xf).sum(dims), xf.new_full((1,), float(x.numel() // c))])
+    tot = CF.all_reduce_autograd(local, "sum", gname)
+    n = tot[-1]
+    m = tot[:c] / n
+    v = (tot[c:2 * c] / n - m * m).clamp_min(0)
+    shp = [1, c] + [1] * (x.dim() - 2)
+    y = ((xf - m.view(shp)) * torch.rsqrt(v.view(shp) + prim.epsilon) * scale.float().view(shp)
+         + bias.float().view(shp)).to(x.dtype)
+    with torch.no_grad():
+        mom = float(prim.momentum)
+        unbiased = v * (n / (n - 1).clamp_min(1))
+        torch.Tensor.mul_(mean, 1 - mom).add_(m.to(mean.dtype) * mom)
+        torch.Tensor.mul_(var, 1 - mom).add_(unbiased.to(var.dtype) * mom)
+    return y, mean, var, mean, var
+
+
+def run_local(prim, info, local, other_pos, others, tensor_pos, kwargs, rank_in_stage, sync_bn=None):
+    """The primitive on one rank's slices: ``local`` is the argument list with tensors already replaced by their
+    slices; shape-like arguments and attributes are rewritten the way ``info`` says the slice must see them."""
+    name = prim.name
+    la = info.local_attrs()
+    if name == "Reshape" and "shape" in la:
+        local[other_pos[0]] = la["shape"]
+    else:
+        for pos, v in zip(other_pos, info.localize_args(others)):
+            local[pos] = v
+    saved = {}
+    for k, v in la.items():
+        if (k != "shape" or name != "Reshape") and hasattr(prim, k):
+            saved[k] = getattr(prim, k)
+            setattr(prim, k, v)
     try:
-        info = OI.make_info(prim, shapes[:len(strategy)], strategy[:len(shapes)], prim.out_strategy,
-                            stage_devices(), **extra)
+        if name in ("Gather", "EmbeddingLookup", "SparseGatherV2") and info.vocab_split() > 1:
+            from ..ops import fused
+            k = info.inputs_tensor_map[0][0]
+            pos = RD._coord_along(info.dev_matrix, rank_in_stage, k)
+            return fused.embedding(local[tensor_pos[0]], local[tensor_pos[1]], pos * local[tensor_pos[0]].shape[0])
+        if name == "BatchNorm" and info.needs_sync_stats():
+            fn = sync_bn or _sync_batch_norm
+            return fn(prim, info, *[local[i] for i in tensor_pos][:5])
+        return prim._run(*local, **kwargs)
+    finally:
+        for k, v in saved.items():
+            setattr(prim, k, v)
+
+
+def dispatch(prim, args, kwargs):
+    """Runs ``prim`` under its shard strategy.  Returns NotImplemented when the primitive takes no tensor."""
+    tensors, slots = _flatten_args(args)
+    if not tensors:
+        return NotImplemented
+    tensor_positions = {i for i, _ in slots}
+    other_pos = [i for i in range(len(args)) if i not in tensor_positions]
+    others = [args[i] for i in other_pos]
+    name = prim.name
+    try:
+        info = build_info(prim, tensors, others)
     except OI.StrategyError:
         if prim.in_strategy is not None:
             raise
         return _run_replicated(prim, args, kwargs)
+    if info is None:
+        return NotImplemented
     global _record, last_dispatch
     _record = {"forward_comm": tuple(info.forward_comm[:2]) if info.forward_comm else None, "redistribution": [],
                "mirror": 0, "fused": None}
     need = info.input_layouts()
     from ..common.tensor import as_tensor
     fused_out = NotImplemented
-    if name == "MatMul" and len(tensor_pos) == 2:
-        fused_out = _fused_matmul(prim, info, args[tensor_pos[0]], args[tensor_pos[1]], need)
-    elif name == "SparseSoftmaxCrossEntropyWithLogits" and info.class_split() > 1 and len(tensor_pos) == 2:
-        fused_out = _vocab_parallel_loss(info, args[tensor_pos[0]], args[tensor_pos[1]], need)
+    if name == "MatMul" and len(tensors) == 2:
+        fused_out = _fused_matmul(prim, info, tensors[0], tensors[1], need)
+    elif name == "SparseSoftmaxCrossEntropyWithLogits" and info.class_split() > 1 and len(tensors) == 2:
+        fused_out = _vocab_parallel_loss(info, tensors[0], tensors[1], need)
         if fused_out is not NotImplemented:
             fused_out = _forward_comm(fused_out, info)
     if fused_out is not NotImplemented:
         last_dispatch, _record = _record, None
         return set_layout(as_tensor(fused_out), info.output_layouts()[0])
-    local = list(args)
-    for j, pos in enumerate(tensor_pos):
+    # inputs -> required layouts (redistribution, parameter slicing, mirrors)
+    prepared = []
+    for j, t in enumerate(tensors):
         if j < len(need):
-            v = _prepare_input(args[pos], need[j])
-            local[pos] = v if isinstance(v, Parameter) else _plain(v)
-    # localise shape-like arguments
-    la = info.local_attrs()
-    if name == "Reshape" and "shape" in la:
-        idx = [i for i in range(len(args)) if i not in tensor_pos][0]
-        local[idx] = la["shape"]
-    saved = {}
-    for k, v in la.items():
-        if k != "shape" and hasattr(prim, k):
-            saved[k] = getattr(prim, k)
-            setattr(prim, k, v)
-    try:
-        if name in ("Gather", "EmbeddingLookup", "SparseGatherV2") and info.vocab_split() > 1:
-            out = _sharded_gather(local, info)
+            v = _prepare_input(t, need[j])
+            prepared.append(v if isinstance(v, Parameter) else _plain(v))
         else:
-            out = prim._run(*local, **kwargs)
-    finally:
-        for k, v in saved.items():
-            setattr(prim, k, v)
+            prepared.append(t)
+    local = list(args)
+    seqs = {}
+    for (pos, sub), v in zip(slots, prepared):
+        if sub is None:
+            local[pos] = v
+        else:
+            seqs.setdefault(pos, list(args[pos]))[sub] = v
+    for pos, seq in seqs.items():
+        local[pos] = type(args[pos])(seq)
+    out = run_local(prim, info, local, other_pos, others, sorted(tensor_positions), kwargs,
+                    _rank() - _stage_base())
     last_dispatch, _record = _record, None
-    out_lays = info.output_layouts()
     if isinstance(out, torch.Tensor):
+        out_lays = info.output_layouts([tuple(out.shape)])
         out = as_tensor(_forward_comm(out, info))
         return set_layout(out, out_lays[0])
     if isinstance(out, (tuple, list)):
+        out_lays = info.output_layouts([tuple(o.shape) if isinstance(o, torch.Tensor) else () for o in out])
         res = []
         for i, o in enumerate(out):
             if isinstance(o, torch.Tensor) and i < len(out_lays):
@@ -441,15 +529,6 @@ def dispatch(prim, args, kwargs):
                 res.append(o)
         return type(out)(res)
     return out
-
-
-def _sharded_gather(local, info):
-    from ..ops import fused
-    table, ids = local[0], local[1]
-    n = info.vocab_split()
-    k = info.inputs_tensor_map[0][0]
-    pos = RD._coord_along(info.dev_matrix, _rank() - _stage_base(), k)
-    return fused.embedding(table, ids, pos * table.shape[0])
 
 
 def _run_replicated(prim, args, kwargs):
