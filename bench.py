@@ -48,6 +48,10 @@ def parse():
                          "gpt-2.6b: dp x mp with sharded optimizer; moe-8x: 8-expert top-2 decoder, expert parallel")
     ap.add_argument("--mp", type=int, default=None, help="gpt-2.6b: model-parallel size (default 4, capped by N)")
     ap.add_argument("--batch-per-gpu", type=int, default=256, help="resnet50 only")
+    ap.add_argument("--pp", type=int, default=1,
+                    help="llama2-7b: pipeline stages (model parallel = N / pp inside a stage; 1F1B over "
+                         "--micro-batches micro-batches, activations sent with NCCL point-to-point)")
+    ap.add_argument("--micro-batches", type=int, default=8, help="llama2-7b with --pp > 1")
     return ap.parse_args()
 
 
@@ -394,14 +398,18 @@ def main():
     if world > 1:
         from mindspore_b200.communication import init
         init("nccl")
+        if world % args.pp:
+            raise SystemExit("--pp %d does not divide %d ranks" % (args.pp, world))
         ms.set_auto_parallel_context(parallel_mode="semi_auto_parallel", device_num=world, global_rank=rank,
-                                     full_batch=True, enable_parallel_optimizer=False)
+                                     full_batch=True, enable_parallel_optimizer=False, pipeline_stages=args.pp)
+    pp = args.pp if world > 1 else 1
+    mp = world // pp
     ms.set_seed(1234)
 
     # The network is primitives + shard strategies only (models/llama.py); under semi_auto_parallel the dispatcher
     # slices the parameters, inserts AllGather / ReduceScatter where the layouts ask for them and runs each
     # (collective, MatMul) pair as one fused NVLink kernel.  --impl tp selects the hand-placed formulation.
-    cfg = LlamaConfig(model_parallel=world, seq_length=args.seq)
+    cfg = LlamaConfig(model_parallel=mp, seq_length=args.seq)
     if args.layers:
         cfg.num_layers = args.layers
     if args.impl == "tp":
@@ -412,10 +420,15 @@ def main():
         net = LlamaForCausalLM(cfg)
     opt = nn.AdamWeightDecay(net.trainable_params(), learning_rate=1e-4, beta1=0.9, beta2=0.95, eps=1e-8,
                              weight_decay=0.1, max_grad_norm=1.0)
-    if world > 1:
-        opt.set_model_parallel_group(M.GlobalComm.WORLD_COMM_GROUP)
-    micro = args.global_batch          # micro-batch size 1 -> one micro-batch per sequence
-    step_cell = nn.TrainOneStepCell(nn.GradAccumulationCell(net, micro), opt)
+    if mp > 1:
+        base = (rank // mp) * mp
+        opt.set_model_parallel_group(M.group_for_ranks(list(range(base, base + mp))))
+    if pp > 1:
+        opt.set_pipeline_parallel_group(M.group_for_ranks([rank % mp + s * mp for s in range(pp)]))
+        step_cell = nn.TrainOneStepCell(nn.PipelineCell(net, args.micro_batches), opt)
+    else:
+        micro = args.global_batch          # micro-batch size 1 -> one micro-batch per sequence
+        step_cell = nn.TrainOneStepCell(nn.GradAccumulationCell(net, micro), opt)
     step_cell.set_train()
 
     dev = torch.device("cuda", local_rank)
@@ -461,6 +474,10 @@ def main():
         last = float(out.float().cpu())
     e1.record()
     barrier()
+    if pp > 1:                       # the loss lives on the last stage
+        lt = torch.tensor([last], device=dev)
+        torch.distributed.all_reduce(lt, op=torch.distributed.ReduceOp.MAX)
+        last = float(lt)
     e2e_ms = e0.elapsed_time(e1)
     wall_ms = (time.perf_counter() - t0) * 1000
     e2e_ms = max(e2e_ms, wall_ms)
@@ -490,13 +507,14 @@ def main():
             "config": {"model": "llama2-7b" if not args.layers else "llama2-7b-truncated-%dL-INVALID" % args.layers,
                        "layers": cfg.num_layers, "hidden": cfg.hidden_size, "heads": cfg.num_heads,
                        "ffn": cfg.ffn_hidden_size, "vocab": cfg.vocab_size, "global_batch": args.global_batch,
-                       "micro_batch": 1, "seq_len": args.seq,
-                       "parallelism": "mp%d+sp" % world if world > 1 else "single",
+                       "micro_batch": 1 if pp == 1 else args.global_batch // args.micro_batches, "seq_len": args.seq,
+                       "parallelism": ("pp%d x mp%d+sp, 1F1B, %d micro-batches" % (pp, mp, args.micro_batches)
+                                       if pp > 1 else "mp%d+sp" % world) if world > 1 else "single",
                        "formulation": "shard strategies (semi_auto_parallel dispatcher)" if args.impl == "ours"
                        else "hand-placed tensor parallel",
                        "optimizer": "AdamW fp32 master + moments, grad clip 1.0",
                        "cuda_graph": bool(ms.get_context("enable_cuda_graph")),
-                       "fused_comm": bool(world > 1 and os.environ.get("MSB200_FUSED_COMM", "1") != "0"),
+                       "fused_comm": bool(mp > 1 and os.environ.get("MSB200_FUSED_COMM", "1") != "0"),
                        "l2": "working set >100 GB per step, far larger than the 126 MB L2 (no flush needed)"},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,

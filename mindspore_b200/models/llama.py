@@ -83,6 +83,11 @@ def _mp(cfg):
     return cfg.model_parallel if (cfg.model_parallel > 1 and spmd.active()) else 1
 
 
+def _pipeline_stages():
+    from .. import context
+    return int(context.get_auto_parallel_context("pipeline_stages")) if spmd.active() else 1
+
+
 def _sharded(prim, *strategy, out=None):
     """``prim.shard`` when there is something to shard (keeps stand-alone runs free of strategy warnings)."""
     if any(s != 1 for st in strategy for s in st):
@@ -158,6 +163,7 @@ class LlamaDecoderLayer(nn.Cell):
         self.norm, self.add_norm = _norm_prims(cfg)
         self.attention = LlamaAttention(cfg)
         self.feed_forward = LlamaMLP(cfg)
+        self.pipeline_outputs = 2          # (residual stream, pending delta): what a later pipeline stage skips over
 
     def construct(self, x, delta, cos, sin):
         """The residual stream is carried as (x, delta): the add is part of the next norm kernel."""
@@ -190,6 +196,17 @@ class LlamaModel(nn.Cell):
         if cfg.recompute:
             for layer in self.layers:
                 layer.recompute()
+        # pipeline parallelism: consecutive blocks of layers per stage.  The embedding runs in front of the first
+        # tagged cell (so on the first stage it feeds layer 0; later stages skip to their first own layer and take
+        # the residual stream from the previous stage); the final norm, the LM head and the loss follow the last
+        # tagged cell, i.e. they run on the last stage only.
+        stages = _pipeline_stages()
+        if stages > 1:
+            if cfg.num_layers % stages:
+                raise ValueError("num_layers %d must be divisible by pipeline_stages %d" % (cfg.num_layers, stages))
+            per = cfg.num_layers // stages
+            for i, layer in enumerate(self.layers):
+                layer.pipeline_stage = i // per
 
     def rope(self, seq, device):
         key = (seq, str(device))

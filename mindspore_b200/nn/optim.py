@@ -391,6 +391,12 @@ class Optimizer(Cell):
         self._mp_runs_ready = False
         self._sumsq_sh = torch.zeros_like(self._sumsq)
 
+    def set_pipeline_parallel_group(self, group_name):
+        """Ranks of ``group_name`` hold the same parameter slices but train different pipeline stages: a parameter
+        has a non-zero gradient on its own stage only, so the squared gradient norm (and the overflow flag) is
+        summed over the group to give every stage the global norm."""
+        self._pp_group = group_name
+
     def _ensure_mp_runs(self):
         if getattr(self, "_mp_runs_ready", True):
             return
@@ -473,6 +479,10 @@ class Optimizer(Cell):
         CF._all_reduce_(self._sumsq_sh, "sum", g)
         CF._all_reduce_(self._nonfinite, "max", g)
         self._sumsq.add_(self._sumsq_sh)
+        pp = getattr(self, "_pp_group", None)
+        if pp is not None:
+            CF._all_reduce_(self._sumsq, "sum", M._group(pp))
+            CF._all_reduce_(self._nonfinite, "max", M._group(pp))
 
 
 def _to_plain(t):

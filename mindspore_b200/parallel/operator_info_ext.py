@@ -523,9 +523,6 @@ class SpatialOpInfo(_SingleInputInfo):
     def out_shapes(self):
         return [None]          # spatial extents follow the op's attributes; only the map matters here
 
-    def output_layouts(self):
-        raise NotImplementedError
-
     def infer_outputs_tensor_map(self):
         return [list(self.inputs_tensor_map[0])]
 

@@ -6,7 +6,7 @@ pipeline_scheduler.cc: GPipe, 1F1B, interleaved 1F1B).  Here the split happens w
 executes ``construct`` of the whole network, and a hook on tagged cells decides per cell
 
 * stage of the cell < stage of this rank : the cell is skipped and yields a placeholder that absorbs every
-  operation applied to it;
+  operation applied to it (a cell that returns a tuple declares its length as ``cell.pipeline_outputs``);
 * same stage                             : placeholders among its inputs are replaced by tensors received from the
   previous stage (first own cell only), then the cell runs;
 * later stage                            : the activations this cell would consume are sent to the next stage and
@@ -28,7 +28,7 @@ from . import planner
 
 _DTYPES = [torch.float32, torch.float16, torch.bfloat16, torch.float64, torch.int32, torch.int64, torch.int8,
            torch.uint8, torch.bool, torch.int16]
-_META_LEN = 80
+_META_LEN = 192
 _MAX_DIMS = 8
 
 
@@ -76,11 +76,18 @@ def _comm_device(like=None):
 
 
 def _encode_meta(tensors):
+    """dtype, requires_grad, shape and - for a tensor that carries a parallel layout - device matrix, tensor map and
+    full shape of every tensor of a hand-over, as one int64 vector.  The layout travels with the activation because
+    the receiving stage continues the sharded computation where the sender stopped."""
+    from . import spmd
     meta = torch.zeros(_META_LEN, dtype=torch.int64)
     meta[0] = len(tensors)
     pos = 1
     for t in tensors:
-        if t.dim() > _MAX_DIMS or pos + 3 + t.dim() > _META_LEN:
+        lay = spmd.get_layout(t)
+        flat_map = lay is not None and not any(isinstance(m, tuple) for m in lay.tensor_map)
+        need = 4 + t.dim() + ((1 + len(lay.device_matrix) + 2 * t.dim()) if flat_map else 0)
+        if t.dim() > _MAX_DIMS or pos + need > _META_LEN:
             raise ValueError("pipeline border: too many / too high-rank tensors for one hand-over")
         meta[pos] = _DTYPES.index(t.dtype)
         meta[pos + 1] = int(t.requires_grad)
@@ -88,16 +95,34 @@ def _encode_meta(tensors):
         for k, d in enumerate(t.shape):
             meta[pos + 3 + k] = d
         pos += 3 + t.dim()
+        meta[pos] = len(lay.device_matrix) if flat_map else -1
+        pos += 1
+        if flat_map:
+            for v in list(lay.device_matrix) + list(lay.tensor_map) + list(lay.shape):
+                meta[pos] = v
+                pos += 1
     return meta
 
 
 def _decode_meta(meta):
+    """-> [(dtype, requires_grad, shape, layout or None)]"""
+    from .layout import TensorLayout
     meta = meta.tolist()
     out, pos = [], 1
     for _ in range(meta[0]):
         nd = meta[pos + 2]
-        out.append((_DTYPES[meta[pos]], bool(meta[pos + 1]), tuple(meta[pos + 3:pos + 3 + nd])))
+        dtype, rg, shape = _DTYPES[meta[pos]], bool(meta[pos + 1]), tuple(meta[pos + 3:pos + 3 + nd])
         pos += 3 + nd
+        ndm = meta[pos]
+        pos += 1
+        lay = None
+        if ndm >= 0:
+            dm = meta[pos:pos + ndm]
+            tmap = meta[pos + ndm:pos + ndm + nd]
+            full = meta[pos + ndm + nd:pos + ndm + 2 * nd]
+            pos += ndm + 2 * nd
+            lay = TensorLayout(dm, tmap, full)
+        out.append((dtype, rg, shape, lay))
     return out
 
 
@@ -138,7 +163,7 @@ class PipelineRuntime:
         if key not in self._meta_cache:
             meta = _encode_meta(tensors).to(dev)
             self._pending.append((dist.isend(meta, dst, group=group), meta))
-            self._meta_cache[key] = [(t.dtype, t.requires_grad, tuple(t.shape)) for t in tensors]
+            self._meta_cache[key] = True
         for t in tensors:
             buf = t.detach().contiguous()
             if buf.device != dev:
@@ -152,12 +177,13 @@ class PipelineRuntime:
             dist.recv(meta, src, group=group)
             self._meta_cache[key] = _decode_meta(meta.cpu())
         out = []
-        for dtype, needs_grad, shape in self._meta_cache[key]:
+        from . import spmd
+        for dtype, needs_grad, shape, lay in self._meta_cache[key]:
             buf = torch.empty(shape, dtype=dtype, device=dev)
             dist.recv(buf, src, group=group)
             if buf.device != like_device:
                 buf = buf.to(like_device)
-            out.append((buf, needs_grad))
+            out.append((buf, needs_grad, lay))
         return out
 
     def _drain(self):
@@ -171,7 +197,10 @@ class PipelineRuntime:
             return cell._call_impl(inputs, kwargs)
         t, s = cell._pipeline_stage, self.stage
         if t < s:
-            return Skipped.make()
+            # a cell of an earlier stage: placeholders stand for its results (``pipeline_outputs`` on the cell says
+            # how many when it returns a tuple that the caller unpacks)
+            n = int(getattr(cell, "pipeline_outputs", 1) or 1)
+            return Skipped.make() if n == 1 else tuple(Skipped.make() for _ in range(n))
         fwd, _ = _direction_groups()
         if t == s:
             n_skipped = sum(1 for a in inputs if _is_skipped(a))
@@ -187,9 +216,12 @@ class PipelineRuntime:
                 new_inputs = []
                 for a in inputs:
                     if _is_skipped(a):
-                        buf, needs_grad = next(it)
+                        buf, needs_grad, lay = next(it)
                         from ..common.tensor import as_tensor
+                        from . import spmd
                         buf = as_tensor(buf)
+                        if lay is not None:
+                            spmd.set_layout(buf, lay)
                         if self._train and needs_grad and buf.is_floating_point():
                             buf.requires_grad_(True)
                         self._rec["x_in"].append(buf)

@@ -1,4 +1,5 @@
-"""Ring attention and Ulysses (all-to-all) attention over gloo ranks against single-device attention."""
+"""Ring attention and Ulysses (all-to-all) attention against single-device attention: over gloo ranks on CPU, and on
+2 / 4 GPUs (NCCL point-to-point / all-to-all, per-block work on the tcgen05 FlashAttention kernels)."""
 import pytest
 import torch
 
@@ -34,3 +35,45 @@ def _worker(rank, world, scheme, causal):
 def test_context_parallel_attention(scheme, causal, world):
     for errs in run_ranks(_worker, world, scheme, causal):
         assert max(errs) < 1e-4, errs
+
+
+def _gpu_worker(rank, world, scheme, causal):
+    import mindspore_b200 as ms
+    from mindspore_b200 import _native
+    from mindspore_b200.communication import GlobalComm, init
+    from mindspore_b200.ops.attention import reference_attention
+    from mindspore_b200.parallel import context_parallel as CP
+    torch.cuda.set_device(rank)
+    ms.set_context(device_target="GPU", device_id=rank)
+    init("nccl")
+    B, S, H, D = 1, 256 * world, 4, 128
+    g = torch.Generator().manual_seed(0)
+    q, k, v, do = (torch.randn(B, S, H, D, generator=g).cuda().bfloat16() for _ in range(4))
+    qf, kf, vf = (t.float().clone().requires_grad_(True) for t in (q, k, v))
+    ref = reference_attention(qf, kf, vf, causal)
+    ref.backward(do.float())
+    sl = slice(rank * S // world, (rank + 1) * S // world)
+    ql, kl, vl = (t[:, sl].clone().requires_grad_(True) for t in (q, k, v))
+    fn = CP.ring_attention if scheme == "ring" else CP.ulysses_attention
+    out = fn(ql, kl, vl, GlobalComm.WORLD_COMM_GROUP, causal=causal)
+    out.backward(do[:, sl].contiguous())
+    torch.cuda.synchronize()
+
+    def rel(a, b):
+        return float((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6))
+    errs = [rel(out, ref[:, sl]), rel(ql.grad, qf.grad[:, sl]), rel(kl.grad, kf.grad[:, sl]),
+            rel(vl.grad, vf.grad[:, sl])]
+    status = _native.device_status()
+    torch.distributed.barrier()
+    return errs, status
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("scheme,causal,world", [("ring", True, 2), ("ulysses", True, 2), ("ring", True, 4),
+                                                  ("ulysses", False, 4)])
+def test_context_parallel_attention_gpu(scheme, causal, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    for errs, status in run_ranks(_gpu_worker, world, scheme, causal):
+        assert status == 0
+        assert max(errs) < 4e-2, errs
