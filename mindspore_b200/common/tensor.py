@@ -150,6 +150,10 @@ class Tensor(torch.Tensor):
         return id(self)
 
     def __bool__(self):
+        from ..graph import tracer
+        session = tracer.current()
+        if session is not None:
+            session.note_host_branch(self)
         return bool(torch.Tensor.__bool__(self.as_subclass(torch.Tensor)))
 
     # ------------------------------------------------------------------ attributes

@@ -51,7 +51,41 @@ def _rec(name, t, g):
         _recorder.record("collective", "%s %s" % (name, g.name), t.numel() * t.element_size(), g.size)
 
 
-def _all_reduce_(t, op, g):
+def _traced(fn, *args):
+    """While a graph is being traced a raw collective is recorded as one node (target = the function below taking
+    the group by *name*), so that a replay performs it; eagerly it just runs."""
+    from ..graph import tracer
+    if not tracer.is_tracing():
+        return None
+    from ..graph import jit
+    return jit.leaf_call(fn, args, {})
+
+
+def all_reduce_node(t, op, gname):
+    return _all_reduce_(t, op, M._group(gname), _node=True)
+
+
+def all_gather_node(t, gname):
+    return _all_gather(t, M._group(gname), _node=True)
+
+
+def reduce_scatter_node(t, op, gname):
+    return _reduce_scatter(t, op, M._group(gname), _node=True)
+
+
+def all_to_all_node(t, split_dim, concat_dim, gname):
+    return _all_to_all(t, split_dim, concat_dim, M._group(gname), _node=True)
+
+
+for _f in (all_reduce_node, all_gather_node, reduce_scatter_node, all_to_all_node):
+    _f.is_collective = True
+
+
+def _all_reduce_(t, op, g, _node=False):
+    if not _node and isinstance(t, torch.Tensor) and not _single(g):
+        out = _traced(all_reduce_node, t, op, g.name)
+        if out is not None:
+            return out
     if M.is_simulation() or _single(g):
         return t
     _rec("AllReduce", t, g)
@@ -59,7 +93,11 @@ def _all_reduce_(t, op, g):
     return t
 
 
-def _all_gather(t, g):
+def _all_gather(t, g, _node=False):
+    if not _node and not _single(g):
+        out = _traced(all_gather_node, t, g.name)
+        if out is not None:
+            return out
     n = g.size
     out = torch.empty((n * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
     if M.is_simulation() or _single(g):
@@ -70,7 +108,11 @@ def _all_gather(t, g):
     return out
 
 
-def _reduce_scatter(t, op, g):
+def _reduce_scatter(t, op, g, _node=False):
+    if not _node and not _single(g):
+        out = _traced(reduce_scatter_node, t, op, g.name)
+        if out is not None:
+            return out
     n = g.size
     if t.shape[0] % n:
         raise ValueError("ReduceScatter needs dim 0 (%d) divisible by the group size (%d)" % (t.shape[0], n))
@@ -84,7 +126,11 @@ def _reduce_scatter(t, op, g):
     return out
 
 
-def _all_to_all(t, split_dim, concat_dim, g):
+def _all_to_all(t, split_dim, concat_dim, g, _node=False):
+    if not _node and not _single(g):
+        out = _traced(all_to_all_node, t, split_dim, concat_dim, g.name)
+        if out is not None:
+            return out
     n = g.size
     chunks = [c.contiguous() for c in torch.chunk(t, n, dim=split_dim)]
     if M.is_simulation() or _single(g):

@@ -36,10 +36,50 @@ class GraphExecutor:
             for a in n.all_input_nodes:
                 self.last_use[a] = i
         self.vjp_needed = {n.args[0] for n in self.nodes if n.op == "call_function" and n.target is autodiff.vjp}
+        self.memory_plan = self._plan_memory()
+        self._comm_stream = None
         self._cuda_graph = None
         self._static_inputs = None
         self._static_outputs = None
         self._runs = 0
+
+    def _plan_memory(self):
+        """Static memory plan of the graph's intermediate values (the reference's SOMAS role,
+        backend/common/somas/somas.cc): every node output with a known shape is a tensor living from its node to its
+        last user; the native best-fit planner (``msb_memory_plan``) packs them into one arena.  The plan gives
+        the peak activation footprint of a replay before anything runs - ``jit`` reports it with ``save_graphs``
+        and warns when it exceeds ``max_device_memory`` - and each node's planned offset (``meta['mem_offset']``).
+        Execution itself takes its buffers from the caching allocator, which frees at the same last-use points."""
+        sizes, starts, ends, owners = [], [], [], []
+        for i, n in enumerate(self.nodes):
+            shp, dt = n.meta.get("shape"), n.meta.get("dtype")
+            if n.op != "call_function" or shp is None or dt is None:
+                continue
+            numel = 1
+            for d in shp:
+                numel *= int(d)
+            if numel == 0:
+                continue
+            nbytes = numel * torch.empty((), dtype=dt).element_size()
+            end = self.last_use.get(n, i)
+            if n.meta.get("requires_vjp") and n.name in self.vjp_needed:
+                # kept for its vjp node: alive until that node has run
+                end = max(end, next((j for j, m in enumerate(self.nodes) if m.op == "call_function"
+                                     and m.target is autodiff.vjp and m.args[0] == n.name), end))
+            sizes.append(nbytes)
+            starts.append(i)
+            ends.append(max(end, i))
+            owners.append(n)
+        if not sizes:
+            return {"arena_bytes": 0, "sum_bytes": 0, "tensors": 0}
+        try:
+            from ..parallel import planner
+            offsets, total = planner.memory_plan(sizes, starts, ends)
+        except Exception:  # noqa: BLE001  (host library unavailable: keep running without a plan)
+            return {"arena_bytes": None, "sum_bytes": sum(sizes), "tensors": len(sizes)}
+        for n, off in zip(owners, offsets):
+            n.meta["mem_offset"] = int(off)
+        return {"arena_bytes": int(total), "sum_bytes": int(sum(sizes)), "tensors": len(sizes)}
 
     def run(self, inputs):
         use_cg = context.get_context("enable_cuda_graph") and inputs and all(
@@ -65,7 +105,14 @@ class GraphExecutor:
         saved = {}
         it = iter(inputs)
         result = None
+        pending = {}       # node -> event: its value is being produced on the communication stream
+        on_cuda = any(isinstance(t, torch.Tensor) and t.is_cuda for t in inputs)
         for i, n in enumerate(self.nodes):
+            if pending:
+                for a in n.all_input_nodes:
+                    ev = pending.pop(a, None)
+                    if ev is not None:
+                        torch.cuda.current_stream().wait_event(ev)
             if n.op == "placeholder":
                 env[n] = next(it)
             elif n.op == "get_attr":
@@ -78,6 +125,22 @@ class GraphExecutor:
                     kwargs = fx.node.map_arg(n.kwargs, lambda a: env[a])
                     if n.meta.get("requires_vjp") and n.name in self.vjp_needed:
                         env[n] = self._run_recorded(n, args, kwargs, saved)
+                    elif on_cuda and n.meta.get("comm_stream"):
+                        # a collective whose result is needed later: issue it on the communication stream, the
+                        # nodes up to its first user overlap it (optimize_gradients_allreduce_overlap.cc's role)
+                        if self._comm_stream is None:
+                            self._comm_stream = torch.cuda.Stream()
+                        cur = torch.cuda.current_stream()
+                        self._comm_stream.wait_stream(cur)
+                        with torch.cuda.stream(self._comm_stream):
+                            out = n.target(*args, **kwargs)
+                        ev = torch.cuda.Event()
+                        ev.record(self._comm_stream)
+                        for o in (out if isinstance(out, (tuple, list)) else (out,)):
+                            if isinstance(o, torch.Tensor):
+                                o.record_stream(cur)
+                        pending[n] = ev
+                        env[n] = out
                     else:
                         env[n] = n.target(*args, **kwargs)
             elif n.op == "output":
@@ -85,6 +148,8 @@ class GraphExecutor:
             for a in n.all_input_nodes:
                 if self.last_use.get(a) == i and a.op != "get_attr":
                     env.pop(a, None)
+        for ev in pending.values():                       # results nobody consumed: still join the stream
+            torch.cuda.current_stream().wait_event(ev)
         return _wrap(result)
 
     @staticmethod

@@ -45,9 +45,11 @@ def _is_tensor(x):
 class _Recorder(TorchFunctionMode):
     """Records executed torch-level calls into an fx.Graph while really executing them."""
 
-    def __init__(self, fg):
+    def __init__(self, fg, parent=None):
         super().__init__()
         self.fg = fg
+        self.parent = parent        # enclosing recorder when this one traces a branch of a Switch
+        self.captured = []          # values of the enclosing trace this sub-graph reads: [(tensor, placeholder)]
         self.depth = 0
         self.node_of = {}   # id(tensor) -> fx.Node
         self.alias = {}     # (data_ptr, shape, stride, dtype) -> fx.Node, for untracked aliases (as_subclass ...)
@@ -89,6 +91,12 @@ class _Recorder(TorchFunctionMode):
                 n = self.fg.param_node(a)
             elif k is not None and k in self.alias:
                 n = self.alias[k]
+            elif self.parent is not None and self.parent.knows(a):
+                # a value computed by the enclosing trace: it becomes an extra input of this sub-graph
+                with self.fg.graph.inserting_before(next(iter(self.fg.graph.nodes), None)):
+                    n = self.fg.graph.placeholder("cap%d" % len(self.captured))
+                n.meta["example"] = (tuple(a.shape), a.dtype)
+                self.captured.append((a, n))
             else:
                 n = self.fg.const_node(a)
             n.meta.setdefault("shape", tuple(a.shape))
@@ -107,6 +115,14 @@ class _Recorder(TorchFunctionMode):
         if isinstance(a, slice):
             return slice(self.arg(a.start), self.arg(a.stop), self.arg(a.step))
         return a
+
+    def knows(self, t):
+        if id(t) in self.node_of:
+            return True
+        k = self._akey(t)
+        if k is not None and k in self.alias:
+            return True
+        return self.parent is not None and self.parent.knows(t)
 
     def record(self, target, args, kwargs, out):
         node = self.fg.graph.call_function(target, self.arg(tuple(args)), self.arg(dict(kwargs or {})))
@@ -224,9 +240,33 @@ def _flat_tensors(x):
     return []
 
 
+_warned_branches = set()
+
+
 class _TraceSession:
     def __init__(self, rec):
         self.rec = rec
+
+    def note_host_branch(self, t):
+        """``bool(tensor)`` during a trace: if the tensor was computed by the graph (it is not a constant of the
+        trace), the Python branch taken now is frozen into the graph.  Said once per call site."""
+        rec = self.rec
+        if rec.depth > 0:
+            return
+        n = rec.node_of.get(id(t))
+        if n is None or n.op == "get_attr":
+            return
+        import traceback
+        frame = next((f for f in reversed(traceback.extract_stack(limit=8)[:-2])
+                      if "mindspore_b200/common/tensor.py" not in f.filename), None)
+        key = (frame.filename, frame.lineno) if frame else None
+        if key in _warned_branches:
+            return
+        _warned_branches.add(key)
+        from ..utils.log import logger
+        logger.warning("graph mode: a Python branch on a tensor value (%s:%s) is decided at trace time and stays "
+                       "fixed in the compiled graph; use ops.cond(pred, true_fn, false_fn, ...) or ops.select to "
+                       "keep it data dependent", *(key or ("?", "?")))
 
     def trace_grad(self, *a, **k):
         return self.rec.trace_grad(*a, **k)
@@ -256,6 +296,47 @@ def trace_callable(fn, example_inputs, name="graph"):
     fg.set_output(rec.arg(out) if _has_tensor(out) else out, out)
     fg.example_outputs = out
     return fg, out
+
+
+def trace_branch(fn, operands, outer, name):
+    """Traces one branch of a ``cond`` into its own FuncGraph while the enclosing trace is suspended.  Returns
+    (graph, example outputs, captured outer tensors).  ``graph.operand_positions`` lists which operands are tensor
+    inputs; the captured values follow them in the sub-graph's input order."""
+    fg = FuncGraph(name)
+    rec = _Recorder(fg, parent=outer)
+    positions = []
+    for i, x in enumerate(operands):
+        if _is_tensor(x):
+            n = fg.graph.placeholder("arg%d" % i)
+            n.meta["example"] = (tuple(x.shape), x.dtype)
+            rec.bind(x, n)
+            positions.append(i)
+    prev_hook, prev_cur = _prim_mod._trace_hook, _trace_state.current()
+    _prim_mod._set_trace_hook(rec.primitive_hook)
+    _trace_state._set_current(_TraceSession(rec))
+    outer.depth += 1               # the enclosing recorder must not record what the branch executes
+    try:
+        with rec:
+            out = fn(*operands)
+    finally:
+        outer.depth -= 1
+        _prim_mod._set_trace_hook(prev_hook)
+        _trace_state._set_current(prev_cur)
+    fg.set_output(rec.arg(out) if _has_tensor(out) else out, out)
+    fg.example_outputs = out
+    # placeholders were created as: operand args (in order), captured ones inserted at the front later; the
+    # executor feeds inputs in node order, so move the captured placeholders behind the operand placeholders
+    fg.operand_positions = positions
+    ordered = [n for n in fg.graph.nodes if n.op == "placeholder" and n.name.startswith("arg")]
+    caps = [n for _, n in rec.captured]
+    last = ordered[-1] if ordered else None
+    for c in caps:
+        if last is not None:
+            last.append(c)
+        last = c
+    fg.input_positions = list(range(len(ordered) + len(caps)))
+    run_default_passes(fg, name, 0, ".")
+    return fg, out, [t for t, _ in rec.captured]
 
 
 def leaf_call(fn, args, kwargs):
@@ -289,6 +370,10 @@ class CompiledGraph:
     def __call__(self, *inputs):
         tensors = [inputs[i] for i in self.fg.input_positions]
         return self.executor.run(tensors)
+
+    def memory_report(self):
+        """{'arena_bytes': planned peak of intermediate values, 'sum_bytes': without reuse, 'tensors': count}."""
+        return dict(self.executor.memory_plan)
 
 
 def _search_strategies(fn, inputs, kwargs, name, owner):
@@ -329,7 +414,23 @@ def _compile(fn, inputs, kwargs, name, owner=None):
         annotate_graph(fg, owner)
         if level:
             dump_graph(fg, os.path.join(path, "%s_step_parallel_end.ir" % name))
-    return CompiledGraph(fg, out)
+    cg = CompiledGraph(fg, out)
+    plan = cg.executor.memory_plan
+    if level:
+        with open(os.path.join(path, "%s_memory_plan.txt" % name), "w") as f:
+            f.write("intermediate tensors %d\nwithout reuse %d bytes\nplanned arena %s bytes\n"
+                    % (plan["tensors"], plan["sum_bytes"], plan["arena_bytes"]))
+    limit = context.get_context("max_device_memory")
+    if plan.get("arena_bytes") and isinstance(limit, str) and limit.upper().endswith("GB"):
+        try:
+            cap = float(limit[:-2]) * 2 ** 30
+            if plan["arena_bytes"] > cap:
+                from ..utils.log import logger
+                logger.warning("graph %s: the planned activation arena (%.2f GB) exceeds max_device_memory (%s)",
+                               name, plan["arena_bytes"] / 2 ** 30, limit)
+        except ValueError:
+            pass
+    return cg
 
 
 def _snapshot_state(owner):

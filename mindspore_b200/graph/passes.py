@@ -28,6 +28,8 @@ def is_impure(node):
     t = node.target
     if t is autodiff.vjp:
         return True
+    if getattr(t, "is_collective", False) or type(t).__name__ == "Switch":
+        return True
     if _is_primitive(t):
         if t._update_parameter:
             return True
@@ -113,10 +115,25 @@ class PassManager:
 
 
 def run_default_passes(fg, tag, save_level=0, path="."):
+    """opt_a: simplification to a fixed point; opt_b: communication passes (merge, bucket fusion, hoisting, stream
+    marking) with the effect chains they respect.  Pass order follows pipeline/jit/ps/pass.cc:424-527 in spirit:
+    simplify first so that the communication passes see the final producers."""
+    from . import opt_passes as O
     pm = PassManager("opt_a")
+    pm.add("cast_eliminate", O.cast_eliminate)
+    pm.add("arithmetic_simplify", O.arithmetic_simplify)
     pm.add("cse", common_subexpression_elimination)
     pm.add("dce", dead_code_elimination)
-    pm.run(fg, tag, save_level, path)
+    for _ in range(4):
+        if not pm.run(fg, tag, save_level, path):
+            break
+    pb = PassManager("opt_b")
+    pb.add("merge_comm", O.merge_comm)
+    pb.add("allreduce_fusion", O.allreduce_fusion)
+    pb.add("comm_reorder", O.comm_reorder)
+    pb.add("mark_comm_stream", O.mark_comm_stream)
+    pb.run(fg, tag + "_comm", save_level, path)
+    O.effect_chains(fg)
     if save_level:
         dump_graph(fg, os.path.join(path, "%s_validate.ir" % tag))
     return fg

@@ -18,7 +18,11 @@ class LearningRateSchedule(Cell):
 
 
 def _f(step):
-    return float(step.item()) if isinstance(step, torch.Tensor) else float(step)
+    """The step as an fp32 0-d tensor: every schedule below is tensor arithmetic, so a schedule evaluated while a
+    graph is traced becomes graph nodes fed by ``global_step`` instead of a constant."""
+    if isinstance(step, torch.Tensor):
+        return step.detach().as_subclass(torch.Tensor).reshape(()).to(torch.float32)
+    return torch.tensor(float(step), dtype=torch.float32)
 
 
 def _check(lr, rate, steps, name):
@@ -39,24 +43,24 @@ class ExponentialDecayLR(LearningRateSchedule):
     def construct(self, global_step):
         p = _f(global_step) / self.steps
         if self.stair:
-            p = math.floor(p)
-        return _wrap_out(torch.tensor(self.lr * self.rate ** p))
+            p = torch.floor(p)
+        return _wrap_out(self.lr * torch.pow(torch.tensor(self.rate, dtype=torch.float32), p))
 
 
 class NaturalExpDecayLR(ExponentialDecayLR):
     def construct(self, global_step):
         p = _f(global_step)
         if self.stair:
-            p = math.floor(p / self.steps) * self.steps
-        return _wrap_out(torch.tensor(self.lr * math.exp(-self.rate * p)))
+            p = torch.floor(p / self.steps) * self.steps
+        return _wrap_out(self.lr * torch.exp(-self.rate * p))
 
 
 class InverseDecayLR(ExponentialDecayLR):
     def construct(self, global_step):
         p = _f(global_step) / self.steps
         if self.stair:
-            p = math.floor(p)
-        return _wrap_out(torch.tensor(self.lr / (1 + self.rate * p)))
+            p = torch.floor(p)
+        return _wrap_out(self.lr / (1 + self.rate * p))
 
 
 class CosineDecayLR(LearningRateSchedule):
@@ -69,8 +73,8 @@ class CosineDecayLR(LearningRateSchedule):
         self.min_lr, self.max_lr, self.steps = min_lr, max_lr, decay_steps
 
     def construct(self, global_step):
-        p = min(_f(global_step), self.steps)
-        return _wrap_out(torch.tensor(self.min_lr + 0.5 * (self.max_lr - self.min_lr) * (1 + math.cos(math.pi * p / self.steps))))
+        p = torch.clamp(_f(global_step), max=float(self.steps))
+        return _wrap_out(self.min_lr + 0.5 * (self.max_lr - self.min_lr) * (1 + torch.cos(math.pi * p / self.steps)))
 
 
 class PolynomialDecayLR(LearningRateSchedule):
@@ -80,11 +84,11 @@ class PolynomialDecayLR(LearningRateSchedule):
 
     def construct(self, global_step):
         s = _f(global_step)
-        steps = self.steps
+        steps = torch.tensor(float(self.steps))
         if self.update:
-            steps = steps * max(1, math.ceil(s / steps))
-        s = min(s, steps)
-        return _wrap_out(torch.tensor((self.lr - self.end) * (1 - s / steps) ** self.power + self.end))
+            steps = steps * torch.clamp(torch.ceil(s / steps), min=1.0)
+        s = torch.minimum(s, steps)
+        return _wrap_out((self.lr - self.end) * torch.pow(1 - s / steps, self.power) + self.end)
 
 
 class WarmUpLR(LearningRateSchedule):
@@ -95,7 +99,7 @@ class WarmUpLR(LearningRateSchedule):
         self.lr, self.warm = learning_rate, warmup_steps
 
     def construct(self, global_step):
-        return _wrap_out(torch.tensor(self.lr * min(_f(global_step), self.warm) / self.warm))
+        return _wrap_out(self.lr * torch.clamp(_f(global_step), max=float(self.warm)) / self.warm)
 
 
 # ---- list builders (nn/dynamic_lr.py)

@@ -188,7 +188,25 @@ class Optimizer(Cell):
         self.arena = None
 
     # ------------------------------------------------------------------ lr / decay helpers
+    def _step(self):
+        """The step the update is computed for.  Eagerly a host int.  While a graph is being traced it is the
+        ``global_step`` tensor, so that the learning-rate schedule and Adam's bias correction are computed by graph
+        nodes at every replay instead of being frozen at their trace-time value."""
+        from ..graph import tracer
+        if tracer.is_tracing():
+            return self.global_step.reshape(()).to(torch.float32)
+        return self._step_host
+
     def _lr_value(self, spec, step):
+        if isinstance(step, torch.Tensor):
+            if isinstance(spec, LearningRateSchedule):
+                return spec(step).to(torch.float32)
+            if isinstance(spec, (list, tuple)) or (isinstance(spec, torch.Tensor) and spec.dim() == 1):
+                table = torch.as_tensor(spec, dtype=torch.float32, device=step.device)
+                return table[step.long().clamp(max=table.numel() - 1)]
+            if isinstance(spec, torch.Tensor):
+                return float(spec)
+            return float(spec)
         if isinstance(spec, LearningRateSchedule):
             v = spec(torch.tensor(step))
             return float(v)
@@ -211,7 +229,7 @@ class Optimizer(Cell):
         return _wrap_out(torch.tensor(self._lr_value(self.learning_rate, step)))
 
     def _lrs(self):
-        step = self._step_host
+        step = self._step()
         if self.is_group_lr:
             return [self._lr_value(s, step) for s in self.group_lr]
         v = self._lr_value(self.learning_rate, step)
@@ -264,6 +282,27 @@ class Optimizer(Cell):
 
     def broadcast_params(self, optim_result):
         return optim_result
+
+    def predicated(self, gradients, skip):
+        """The update, applied unless the 0-d bool tensor ``skip`` is set - without reading ``skip`` on the host,
+        so the whole step stays one graph (and one CUDA graph).  Every tensor the update writes (parameters, the
+        optimizer's states and its step counter) is put back where ``skip`` holds.  Arena optimizers do the same
+        inside their kernels (``fused_step(check_finite=True)``)."""
+        if self.use_arena:
+            raise RuntimeError("arena optimizers skip an update inside their kernels: use fused_step(check_finite=True)")
+        touched, seen = [], set()
+        for p in list(self._parameters) + list(self.get_parameters()):
+            if id(p) not in seen:
+                seen.add(id(p))
+                touched.append(p)
+        old = [p.detach().as_subclass(torch.Tensor).clone() for p in touched]
+        out = self(gradients)
+        keep = skip.reshape(()).to(torch.bool)
+        with torch.no_grad():
+            for p, o in zip(touched, old):
+                cur = p.detach().as_subclass(torch.Tensor)      # in-place on the detached alias replays in any grad mode
+                cur.copy_(torch.where(keep, o, cur))
+        return out
 
     @property
     def unique(self):
@@ -489,6 +528,19 @@ def _to_plain(t):
     return t.detach().as_subclass(torch.Tensor) if isinstance(t, torch.Tensor) else t
 
 
+def _fill_hyper(h, start, values):
+    """Writes scalars (host numbers, or 0-d tensors when the step is traced) into the device hyper-parameter
+    vector: one host-to-device copy when all are numbers."""
+    if not any(isinstance(v, torch.Tensor) for v in values):
+        h[start:start + len(values)] = torch.tensor(values, dtype=torch.float32)
+        return
+    for i, v in enumerate(values):
+        if isinstance(v, torch.Tensor):
+            h[start + i:start + i + 1].copy_(v.reshape(1).to(h.dtype))
+        else:
+            h[start + i] = float(v)
+
+
 class Momentum(Optimizer):
     def __init__(self, params, learning_rate, momentum, weight_decay=0.0, loss_scale=1.0, use_nesterov=False,
                  use_arena=None, decay_filter=None):
@@ -517,7 +569,7 @@ class Momentum(Optimizer):
 
     def fused_step(self, inv_loss_scale=1.0, check_finite=False, advance=True):
         arena = self.arena
-        lr = self._lr_value(self.learning_rate, self._step_host)
+        lr = self._lr_value(self.learning_rate, self._step())
         skip = None
         if check_finite or inv_loss_scale != 1.0:
             self._accumulate_sumsq()
@@ -527,7 +579,7 @@ class Momentum(Optimizer):
         for gi, (first, last, wd) in enumerate(self._arena_groups):
             s, e = arena.segment(first, last)
             h = self._hyper[gi]
-            h[:3] = torch.tensor([lr, self.momentum, wd], dtype=torch.float32)
+            _fill_hyper(h, 0, [lr, self.momentum, wd])
             h[3:4].copy_(self._gscale)
             h[4] = 1.0 if self.use_nesterov else 0.0
             lp = arena.weights[s:e] if arena.master is not arena.weights else None
@@ -549,7 +601,7 @@ class Momentum(Optimizer):
                 if pt.dtype != mt.dtype:
                     pt.copy_((pt.to(mt.dtype) - lr * upd).to(pt.dtype))
                 else:
-                    pt.sub_(upd, alpha=lr)
+                    pt.sub_(upd * lr)
         self._advance()
         return True
 
@@ -571,7 +623,11 @@ class SGD(Optimizer):
             for p, g, a, lr in zip(self._parameters, gradients, self.accum, lrs):
                 pt, at, gt = _to_plain(p), _to_plain(a), _to_plain(g).to(a.dtype)
                 if self.momentum != 0:
-                    if self._first:
+                    step = self._step()
+                    if isinstance(step, torch.Tensor):
+                        # traced: "first step" is decided by the step counter at every replay
+                        at.copy_(torch.where(step == 0, gt, at * self.momentum + gt * (1 - self.dampening)))
+                    elif self._first:
                         at.copy_(gt)
                     else:
                         at.mul_(self.momentum).add_(gt, alpha=1 - self.dampening)
@@ -598,7 +654,7 @@ class Adam(Optimizer):
     def construct(self, gradients):
         gradients = self._prep(gradients)
         lrs = self._lrs()
-        t = self._step_host + 1
+        t = self._step() + 1
         bc1, bc2 = 1 - self.beta1 ** t, 1 - self.beta2 ** t
         with torch.no_grad():
             for i, (p, g, m, v, lr) in enumerate(zip(self._parameters, gradients, self.moment1, self.moment2, lrs)):
@@ -610,7 +666,7 @@ class Adam(Optimizer):
                     vh = _to_plain(self.vhat[i])
                     torch.maximum(vh, vt, out=vh)
                     vv = vh
-                lr_t = lr * math.sqrt(bc2) / bc1
+                lr_t = lr * bc2 ** 0.5 / bc1
                 num = (self.beta1 * mt + (1 - self.beta1) * gt) if self.use_nesterov else mt
                 upd = lr_t * num / (vv.sqrt() + self.eps)
                 pt.copy_((pt.to(upd.dtype) - upd).to(pt.dtype))
@@ -663,7 +719,7 @@ class AdamWeightDecay(Optimizer):
             return self.fused_step()
         gradients = self._prep(gradients)
         lrs = self._lrs()
-        t = self._step_host + 1
+        t = self._step() + 1
         bc1 = 1 - self.beta1 ** t if self.bias_correction else 1.0
         bc2 = 1 - self.beta2 ** t if self.bias_correction else 1.0
         with torch.no_grad():
@@ -684,8 +740,8 @@ class AdamWeightDecay(Optimizer):
         if dp is not None and dp.shard:
             return dp.sharded_step(inv_loss_scale, check_finite, advance)
         arena = self.arena
-        t = self._step_host + 1
-        lr = self._lr_value(self.learning_rate, self._step_host)
+        t = self._step() + 1
+        lr = self._lr_value(self.learning_rate, self._step())
         bc1 = 1 - self.beta1 ** t if self.bias_correction else 1.0
         bc2 = 1 - self.beta2 ** t if self.bias_correction else 1.0
         skip = None
@@ -697,7 +753,7 @@ class AdamWeightDecay(Optimizer):
         for gi, (first, last, wd) in enumerate(self._arena_groups):
             s, e = arena.segment(first, last)
             h = self._hyper[gi]
-            h[:7] = torch.tensor([lr, self.beta1, self.beta2, self.eps, wd, bc1, bc2], dtype=torch.float32)
+            _fill_hyper(h, 0, [lr, self.beta1, self.beta2, self.eps, wd, bc1, bc2])
             h[7:8].copy_(self._gscale)
             lp = arena.weights[s:e] if arena.master is not arena.weights else None
             K.adamw_step(arena.master[s:e], self._m[s:e], self._v[s:e], arena.grads[s:e], lp, h, skip)
@@ -722,7 +778,7 @@ class Lamb(Optimizer):
     def construct(self, gradients):
         gradients = self._prep(gradients)
         lrs = self._lrs()
-        t = self._step_host + 1
+        t = self._step() + 1
         with torch.no_grad():
             for i, (p, g, m, v, lr) in enumerate(zip(self._parameters, gradients, self.moment1, self.moment2, lrs)):
                 pt, mt, vt, gt = _to_plain(p), _to_plain(m), _to_plain(v), _to_plain(g).to(m.dtype)
@@ -813,7 +869,7 @@ class AdaMax(Optimizer):
 
     def construct(self, gradients):
         gradients = self._prep(gradients)
-        t = self._step_host + 1
+        t = self._step() + 1
         with torch.no_grad():
             for p, g, m, v, lr in zip(self._parameters, gradients, self.moment1, self.moment2, self._lrs()):
                 pt, mt, vt, gt = _to_plain(p), _to_plain(m), _to_plain(v), _to_plain(g).to(m.dtype)
@@ -833,7 +889,7 @@ class ASGD(Optimizer):
 
     def construct(self, gradients):
         gradients = self._prep(gradients)
-        step = self._step_host + 1
+        step = self._step() + 1
         with torch.no_grad():
             for p, g, ax, lr in zip(self._parameters, gradients, self.ax, self._lrs()):
                 eta = lr / ((1 + self.lambd * lr * step) ** self.alpha)
@@ -955,7 +1011,7 @@ class AdaFactor(Optimizer):
 
     def construct(self, gradients):
         gradients = self._prep(gradients)
-        t = self._step_host + 1
+        t = self._step() + 1
         rho = 1 - t ** (-self._kw["decay"])
         e1, e2 = self._kw["eps2"]
         with torch.no_grad():

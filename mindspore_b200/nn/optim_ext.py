@@ -22,7 +22,7 @@ class LazyAdam(Adam):
     def construct(self, gradients):
         gradients = self._prep(gradients)
         lrs = self._lrs()
-        t = self._step_host + 1
+        t = self._step() + 1
         lr_scale = math.sqrt(1 - self.beta2 ** t) / (1 - self.beta1 ** t)
         with torch.no_grad():
             for p, g, m, v, lr in zip(self._parameters, gradients, self.moment1, self.moment2, lrs):
@@ -61,7 +61,7 @@ class AdamOffload(Adam):
     def construct(self, gradients):
         gradients = self._prep(gradients)
         lrs = self._lrs()
-        t = self._step_host + 1
+        t = self._step() + 1
         lr_scale = math.sqrt(1 - self.beta2 ** t) / (1 - self.beta1 ** t)
         with torch.no_grad():
             for p, g, m, v, lr in zip(self._parameters, gradients, self._host_m, self._host_v, lrs):

@@ -354,6 +354,22 @@ class DynamicLossScaleUpdateCell(Cell):
         return self.loss_scale_value
 
     def construct(self, loss_scale, overflow):
+        from ..graph import tracer
+        if tracer.is_tracing():
+            # tensor form: nothing is read on the host, so the update is part of the graph and follows the
+            # overflow flag of every replay (reference: DynamicLossScaleUpdateCell.construct, loss_scale.py:135-168)
+            with torch.no_grad():
+                ov = overflow.reshape(()).to(torch.bool)
+                scale = loss_scale.detach().as_subclass(torch.Tensor)
+                cur = self.cur_iter.detach().as_subclass(torch.Tensor)
+                last = self.last_overflow_iter.detach().as_subclass(torch.Tensor)
+                grow = (~ov) & ((cur - last) >= self.scale_window)
+                new_scale = torch.where(ov, torch.clamp(scale / self.scale_factor, min=1.0),
+                                        torch.where(grow, scale * self.scale_factor, scale))
+                torch.Tensor.copy_(loss_scale, new_scale)
+                torch.Tensor.copy_(self.last_overflow_iter, torch.where(ov | grow, cur, last))
+                torch.Tensor.add_(self.cur_iter, 1)
+            return overflow
         overflow = bool(overflow)
         cur, last = int(self.cur_iter), int(self.last_overflow_iter)
         with torch.no_grad():
@@ -377,7 +393,8 @@ class FixedLossScaleUpdateCell(Cell):
         return self.loss_scale_value
 
     def construct(self, _, overflow):
-        return bool(overflow)
+        from ..graph import tracer
+        return overflow if tracer.is_tracing() else bool(overflow)
 
 
 class TrainOneStepWithLossScaleCell(TrainOneStepCell):
@@ -397,7 +414,8 @@ class TrainOneStepWithLossScaleCell(TrainOneStepCell):
         else:
             raise TypeError("For 'TrainOneStepWithLossScaleCell', 'scale_sense' must be Cell or Tensor, got %s"
                             % type(scale_sense))
-        self._use_graph = False  # the overflow branch reads a device flag
+        # the arena path reads the overflow flag on the host (step counter); the per-parameter path is traceable
+        self._use_graph = False if self.use_arena else None
 
     def set_sense_scale(self, sens):
         if self.scale_sense is not None and isinstance(sens, torch.Tensor):
@@ -423,7 +441,8 @@ class TrainOneStepWithLossScaleCell(TrainOneStepCell):
     def process_loss_scale(self, overflow):
         if self.loss_scaling_manager is not None:
             return self.loss_scaling_manager(self.scale_sense, overflow)
-        return bool(overflow)
+        from ..graph import tracer
+        return overflow if tracer.is_tracing() else bool(overflow)
 
     def construct(self, *inputs):
         scale = self.scale_sense
@@ -448,6 +467,12 @@ class TrainOneStepWithLossScaleCell(TrainOneStepCell):
             grads = self.grad_reducer(grads)
         cond = self.get_overflow_status(None, grads)
         overflow = self.process_loss_scale(cond)
+        from ..graph import tracer
+        if tracer.is_tracing():
+            # the reference's ``if not overflow: optimizer(grads)`` (nn/wrap/loss_scale.py:404-422) as a predicated
+            # update: the branch is taken on the device at every replay, not frozen at its trace-time outcome
+            self.optimizer.predicated(grads, overflow)
+            return loss, _wrap_out(overflow), scale
         if not overflow:
             self.optimizer(grads)
         return loss, _wrap_out(torch.as_tensor(overflow)), scale

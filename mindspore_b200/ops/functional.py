@@ -315,6 +315,13 @@ def one_hot(indices, depth, on_value=1, off_value=0, axis=-1):
     return _prim(P.OneHot, axis)(indices, depth, on_value, off_value)
 
 
+def cond(pred, true_fn, false_fn, *operands):
+    """Traceable conditional: ``true_fn(*operands) if pred else false_fn(*operands)``.  In graph mode both branches
+    become sub-graphs behind one Switch node and the branch is chosen at every run (``graph/control_flow.py``)."""
+    from ..graph.control_flow import cond as _cond
+    return _cond(pred, true_fn, false_fn, *operands)
+
+
 def select(cond, x, y):
     return _prim(P.Select)(cond, x, y)
 

@@ -270,8 +270,8 @@ class DataParallelArena:
             K.finalize_grad_scale(opt._sumsq, opt._nonfinite, inv_loss_scale, opt.max_grad_norm, opt._gscale,
                                   opt._skip, opt._gnorm)
             skip = opt._skip if check_finite else None
-        t = opt._step_host + 1
-        lr = opt._lr_value(opt.learning_rate, opt._step_host)
+        t = opt._step() + 1
+        lr = opt._lr_value(opt.learning_rate, opt._step())
         bc1 = 1 - opt.beta1 ** t if opt.bias_correction else 1.0
         bc2 = 1 - opt.beta2 ** t if opt.bias_correction else 1.0
         groups = []
@@ -284,7 +284,8 @@ class DataParallelArena:
             lp_slice = arena.weights[self.lo:self.hi]
         for off, n, gi in self._ranges_in_slice(groups):
             h = opt._hyper[gi]
-            h[:7] = torch.tensor([lr, opt.beta1, opt.beta2, opt.eps, wds[gi], bc1, bc2], dtype=torch.float32)
+            from ..nn.optim import _fill_hyper
+            _fill_hyper(h, 0, [lr, opt.beta1, opt.beta2, opt.eps, wds[gi], bc1, bc2])
             h[7:8].copy_(opt._gscale)
             if self.symm is not None:
                 rc = _native.cuda().msb_adamw_allgather(_p(self.master[off:]), _p(self.m[off:]), _p(self.v[off:]),
