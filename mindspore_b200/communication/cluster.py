@@ -47,6 +47,12 @@ def _lib():
         lib.msb_store_get.argtypes = [c_str, c_int, c_str, ctypes.c_char_p, c_int, c_dbl]
         lib.msb_store_delete.restype = c_int
         lib.msb_store_delete.argtypes = [c_str, c_int, c_str, c_dbl]
+        lib.msb_store_add.restype = ctypes.c_longlong
+        lib.msb_store_add.argtypes = [c_str, c_int, c_str, ctypes.c_longlong, c_dbl]
+        lib.msb_sched_snapshot.restype = c_int
+        lib.msb_sched_snapshot.argtypes = [ctypes.c_char_p, c_int]
+        lib.msb_sched_restore.restype = c_int
+        lib.msb_sched_restore.argtypes = [ctypes.c_char_p, c_int]
         _sig_done = True
     return lib
 
@@ -54,11 +60,48 @@ def _lib():
 class Scheduler:
     """The metadata server of one job (one per process).  ``port=0`` picks a free port."""
 
-    def __init__(self, port=0, expected_workers=1, node_timeout_s=30.0):
+    def __init__(self, port=0, expected_workers=1, node_timeout_s=30.0, persist_path=None, persist_interval_s=1.0):
+        """``persist_path``: file the scheduler's state (node -> rank table and the metadata store) is written to
+        every ``persist_interval_s`` seconds and on ``stop``; a scheduler started with an existing file continues
+        from it, so a restarted scheduler hands every node its old rank and still knows the job's metadata
+        (reference: cluster/topology/meta_server_node.cc:561-635, MS_ENABLE_RECOVERY / MS_RECOVERY_PATH)."""
         self.port = _lib().msb_sched_start(int(port), int(expected_workers), float(node_timeout_s))
         if self.port <= 0:
             raise ClusterError("scheduler could not listen on port %s (already running in this process?)" % port)
         self.expected = expected_workers
+        self.persist_path = persist_path
+        self._persist_stop = threading.Event()
+        self._persist_thread = None
+        if persist_path:
+            if os.path.isfile(persist_path):
+                with open(persist_path, "rb") as f:
+                    data = f.read()
+                self.restored = _lib().msb_sched_restore(data, len(data))
+            else:
+                self.restored = 0
+
+            def loop():
+                while not self._persist_stop.wait(persist_interval_s):
+                    self.persist()
+            self._persist_thread = threading.Thread(target=loop, name="msb-sched-persist", daemon=True)
+            self._persist_thread.start()
+
+    def snapshot(self):
+        cap = 1 << 16
+        while True:
+            buf = ctypes.create_string_buffer(cap)
+            n = _lib().msb_sched_snapshot(buf, cap)
+            if n >= 0:
+                return buf.raw[:n]
+            cap = -n + 1024
+
+    def persist(self):
+        if not self.persist_path:
+            return
+        tmp = self.persist_path + ".tmp"
+        with open(tmp, "wb") as f:
+            f.write(self.snapshot())
+        os.replace(tmp, self.persist_path)
 
     def registered(self):
         return _lib().msb_sched_registered()
@@ -75,6 +118,11 @@ class Scheduler:
         return False
 
     def stop(self):
+        self._persist_stop.set()
+        if self._persist_thread is not None:
+            self._persist_thread.join(5)
+            self._persist_thread = None
+        self.persist()
         _lib().msb_sched_stop()
 
     def __enter__(self):
@@ -180,6 +228,13 @@ class WorkerClient:
 
     def delete(self, key):
         _lib().msb_store_delete(self.host, self.port, key.encode(), self.timeout_s)
+
+    def add(self, key, delta=0):
+        """Atomic counter in the metadata store: adds ``delta`` and returns the new value (``delta=0`` reads)."""
+        v = _lib().msb_store_add(self.host, self.port, key.encode(), int(delta), self.timeout_s)
+        if v < 0:
+            raise ClusterError("store add(%s) failed" % key)
+        return int(v)
 
 
 _worker = None

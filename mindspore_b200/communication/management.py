@@ -112,7 +112,12 @@ def init(backend_name=None):
             kw = {}
             if torch_backend == "nccl":
                 kw["device_id"] = torch.device("cuda", torch.cuda.current_device())
-            dist.init_process_group(torch_backend, rank=rank, world_size=world, timeout=timeout, **kw)
+            # the rendezvous runs under a watchdog: ranks that never arrive end this call with an error after
+            # MS_CLUSTER_TIMEOUT instead of leaving the process blocked (collective_manager.cc:80-118)
+            from .elastic import run_with_watchdog
+            run_with_watchdog(lambda: dist.init_process_group(torch_backend, rank=rank, world_size=world,
+                                                              timeout=timeout, **kw),
+                              timeout.total_seconds() + 30, "init_process_group(%s)" % torch_backend)
         _state.rank, _state.world, _state.local_rank = dist.get_rank(), dist.get_world_size(), local_rank
         _state.groups[world_name] = _Group(world_name, range(_state.world), dist.group.WORLD)
     GlobalComm.BACKEND = backend_name

@@ -8,6 +8,7 @@
 //   "GET <key>\n"          -> "OK <len>\n<bytes>" | "NONE\n"
 //   "DEL <key>\n"          -> "OK\n"
 //   "UNREG <node_id>\n"    -> "OK\n"
+//   "ADD <key> <delta>\n"  -> "OK <value>\n"               (atomic counter in the store; delta 0 reads it)
 // The scheduler's monitor marks a node abnormal when no heartbeat arrived within the timeout; workers learn
 // the abnormal count from every heartbeat reply and can abort their next collective.
 #include <arpa/inet.h>
@@ -143,6 +144,14 @@ void handle(Scheduler* s, int fd) {
     std::lock_guard<std::mutex> lk(s->mu);
     s->kv.erase(a);
     reply = "OK\n";
+  } else if (nf >= 3 && c == "ADD") {
+    std::lock_guard<std::mutex> lk(s->mu);
+    long cur = 0;
+    auto it = s->kv.find(a);
+    if (it != s->kv.end()) cur = std::strtol(it->second.c_str(), nullptr, 10);
+    cur += len;
+    s->kv[a] = std::to_string(cur);
+    reply = "OK " + std::to_string(cur) + "\n";
   } else if (nf >= 2 && c == "UNREG") {
     std::lock_guard<std::mutex> lk(s->mu);
     s->alive.erase(a);
@@ -235,6 +244,80 @@ MSB_API int msb_sched_registered() {
   if (!g_sched) return -1;
   std::lock_guard<std::mutex> lk(g_sched->mu);
   return static_cast<int>(g_sched->rank_of.size());
+}
+
+// Scheduler state as text, for persistence across a scheduler restart (the reference keeps the same in a
+// configuration file: cluster/topology/meta_server_node.cc:561-635):
+//   "NODE <rank> <node_id>\n" per registered node, "KV <key> <hex of value>\n" per store entry.
+// Returns the length, or -(needed length) when `capacity` is too small.
+MSB_API int msb_sched_snapshot(char* buf, int capacity) {
+  if (!g_sched) return 0;
+  std::string out;
+  {
+    std::lock_guard<std::mutex> lk(g_sched->mu);
+    for (auto& kvp : g_sched->rank_of) out += "NODE " + std::to_string(kvp.second) + " " + kvp.first + "\n";
+    static const char* hex = "0123456789abcdef";
+    for (auto& kvp : g_sched->kv) {
+      out += "KV " + kvp.first + " ";
+      for (unsigned char ch : kvp.second) { out.push_back(hex[ch >> 4]); out.push_back(hex[ch & 15]); }
+      out += "\n";
+    }
+  }
+  if (static_cast<int>(out.size()) > capacity) return -static_cast<int>(out.size());
+  std::memcpy(buf, out.data(), out.size());
+  return static_cast<int>(out.size());
+}
+
+// Loads a snapshot into the running scheduler: nodes get their old ranks back (and a fresh heartbeat deadline, so
+// that workers that kept running have one timeout period to show up again), the store gets its entries back.
+MSB_API int msb_sched_restore(const char* text, int len) {
+  if (!g_sched) return -1;
+  std::lock_guard<std::mutex> lk(g_sched->mu);
+  std::string all(text, static_cast<size_t>(len));
+  size_t pos = 0;
+  int n = 0;
+  while (pos < all.size()) {
+    size_t e = all.find('\n', pos);
+    if (e == std::string::npos) e = all.size();
+    const std::string line = all.substr(pos, e - pos);
+    pos = e + 1;
+    if (line.compare(0, 5, "NODE ") == 0) {
+      const size_t sp = line.find(' ', 5);
+      if (sp == std::string::npos) continue;
+      const int rank = std::atoi(line.substr(5, sp - 5).c_str());
+      const std::string id = line.substr(sp + 1);
+      g_sched->rank_of[id] = rank;
+      g_sched->last_seen[id] = Clock::now();
+      g_sched->alive[id] = true;
+      ++n;
+    } else if (line.compare(0, 3, "KV ") == 0) {
+      const size_t sp = line.find(' ', 3);
+      if (sp == std::string::npos) continue;
+      const std::string key = line.substr(3, sp - 3), hx = line.substr(sp + 1);
+      std::string val;
+      for (size_t i = 0; i + 1 < hx.size(); i += 2) {
+        auto d = [](char ch) { return ch <= '9' ? ch - '0' : ch - 'a' + 10; };
+        val.push_back(static_cast<char>((d(hx[i]) << 4) | d(hx[i + 1])));
+      }
+      g_sched->kv[key] = val;
+      ++n;
+    }
+  }
+  return n;
+}
+
+// Atomic counter in the store: adds `delta` (0 = read) and returns the new value, or -1 on IO failure.
+MSB_API long long msb_store_add(const char* host, int port, const char* key, long long delta, double timeout_s) {
+  const int fd = connect_to(host, port, timeout_s);
+  if (fd < 0) return -1;
+  const std::string req = std::string("ADD ") + key + " " + std::to_string(delta) + "\n";
+  std::string line;
+  long long v = -1;
+  if (write_all(fd, req.data(), req.size()) && read_line(fd, &line)) {
+    if (std::sscanf(line.c_str(), "OK %lld", &v) != 1) v = -1;
+  }
+  ::close(fd);
+  return v;
 }
 
 // Worker side.  Each call opens one connection.  Return: >=0 on success, -1 connect/IO failure, -2 rejected.

@@ -61,7 +61,13 @@ class ProcessManager:
         if self.args.node_rank != 0 or self.args.sim_level >= 0:
             return
         from .communication.cluster import Scheduler
-        self.scheduler = Scheduler(0, self.args.worker_num, self.args.heartbeat_timeout)
+        # with MS_ENABLE_RECOVERY the scheduler keeps its node table and metadata store in MS_RECOVERY_PATH, so a
+        # restarted launcher hands every node its old rank (cluster/topology/meta_server_node.cc:561-635)
+        persist = None
+        if os.environ.get("MS_ENABLE_RECOVERY", "0") == "1" and os.environ.get("MS_RECOVERY_PATH"):
+            os.makedirs(os.environ["MS_RECOVERY_PATH"], exist_ok=True)
+            persist = os.path.join(os.environ["MS_RECOVERY_PATH"], "scheduler.state")
+        self.scheduler = Scheduler(0, self.args.worker_num, self.args.heartbeat_timeout, persist_path=persist)
         self.cluster_port = self.scheduler.port
 
     def _env(self, rank, local_rank):

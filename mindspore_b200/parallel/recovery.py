@@ -33,6 +33,40 @@ class RecoveryContext:
             json.dump({"epoch": epoch, "step": step, "path": ckpt_path}, f)
         os.replace(tmp, os.path.join(self.rank_dir(rank), "latest.json"))
 
+    def record_all(self, rank, epoch, step, ckpt_path, keep=8):
+        """Appends to this rank's history (``history.json``, newest last, ``keep`` entries) besides ``latest.json``:
+        after a failure the ranks agree on the newest point that all of them still have."""
+        self.record(rank, epoch, step, ckpt_path)
+        hp = os.path.join(self.rank_dir(rank), "history.json")
+        hist = []
+        if os.path.exists(hp):
+            with open(hp) as f:
+                hist = json.load(f)
+        hist = [h for h in hist if (h["epoch"], h["step"]) != (epoch, step)] + \
+            [{"epoch": epoch, "step": step, "path": ckpt_path}]
+        hist = hist[-keep:]
+        with open(hp + ".tmp", "w") as f:
+            json.dump(hist, f)
+        os.replace(hp + ".tmp", hp)
+
+    def local_history(self, rank):
+        hp = os.path.join(self.path, "rank_%d" % rank, "history.json")
+        if not os.path.exists(hp):
+            one = self.local_latest(rank)
+            return [one] if one else []
+        with open(hp) as f:
+            return [h for h in json.load(f) if os.path.exists(h["path"])]
+
+    def agree(self, rank):
+        """The newest checkpoint every rank has, found by an all-gather over the current communicator (each rank
+        reads only its own directory).  Returns this rank's record for it, or None."""
+        from ..communication.elastic import agree_on_checkpoint
+        hist = self.local_history(rank)
+        point = agree_on_checkpoint([(h["epoch"], h["step"]) for h in hist])
+        if point is None:
+            return None
+        return next(h for h in hist if (h["epoch"], h["step"]) == point)
+
     def local_latest(self, rank):
         p = os.path.join(self.path, "rank_%d" % rank, "latest.json")
         if not os.path.exists(p):
@@ -41,7 +75,8 @@ class RecoveryContext:
             return json.load(f)
 
     def latest_common_checkpoint(self, rank=None, world=None):
-        """(epoch, step) = min over ranks; returns this rank's file for that point, or None."""
+        """(epoch, step) = min over ranks, read from every rank's directory: only for jobs whose ranks share
+        ``MS_RECOVERY_PATH`` (one node).  ``agree`` is the general form.  Returns this rank's file or None."""
         from ..communication import management as M
         if rank is None:
             rank = M._state.rank if M.GlobalComm.INITED else 0
