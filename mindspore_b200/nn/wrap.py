@@ -250,7 +250,9 @@ class TrainOneStepCell(Cell):
             _recorder.set_step(self._rdr_step)
             _recorder.record("step", "begin " + type(self.network).__name__)
         if self.use_arena:
-            return _wrap_out(self._arena_step(inputs))
+            from ..profiler import step_range
+            with step_range():
+                return _wrap_out(self._arena_step(inputs))
         if isinstance(self.network, PipelineCell) and not isinstance(self.network, GradAccumulationCell) and \
                 context.get_auto_parallel_context("pipeline_stages") > 1:
             return self._pipeline_step(inputs)

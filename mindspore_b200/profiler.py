@@ -47,6 +47,7 @@ class Profiler:
         self._prof = torch.profiler.profile(activities=acts, profile_memory=self.profile_memory,
                                             with_stack=self.with_stack, record_shapes=False)
         self._prof.__enter__()
+        _active[0] += 1
         self._t0 = time.time()
 
     def stop(self):
@@ -55,6 +56,7 @@ class Profiler:
         if torch.cuda.is_available():
             torch.cuda.synchronize()
         self._prof.__exit__(None, None, None)
+        _active[0] = max(0, _active[0] - 1)
         self._t1 = time.time()
 
     # ------------------------------------------------------------------ analysis
@@ -99,6 +101,12 @@ class Profiler:
             for k, v in sorted(host.items(), key=lambda kv: -kv[1][1]):
                 w.writerow([k, v[0], round(v[1], 1)])
         self._prof.export_chrome_trace(os.path.join(self.output_path, "timeline_%d.json" % self.rank))
+        trace = self.step_trace()
+        if trace:
+            with open(os.path.join(self.output_path, "step_trace_%d.csv" % self.rank), "w", newline="") as f:
+                w = csv.DictWriter(f, fieldnames=list(trace[0]))
+                w.writeheader()
+                w.writerows(trace)
         if self.profile_memory:
             with open(os.path.join(self.output_path, "memory_%d.csv" % self.rank), "w", newline="") as f:
                 w = csv.writer(f)
@@ -106,6 +114,84 @@ class Profiler:
                 for e in self._prof.key_averages():
                     w.writerow([e.key, getattr(e, "self_device_memory_usage", 0), e.self_cpu_memory_usage])
         return kernels
+
+    # ------------------------------------------------------------------ step trace
+    COMM = ("nccl", "symm_barrier", "allreduce_symm", "reduce_slots", "reduce_scatter_symm", "all_gather", "Memcpy PtoP",
+            "moe_dispatch", "moe_combine")
+    OPT = ("adamw", "momentum_kernel", "sumsq_finite", "finalize_grad_scale", "multi_tensor", "FusedAdam", "fused_sgd")
+    BWD = ("bwd", "dgrad", "wgrad", "_grad", "Backward", "backward")
+
+    @classmethod
+    def classify(cls, name):
+        """forward / backward / optimizer / comm for a device kernel name.  The GEMM's role follows its operand
+        layouts (template flags of ``gemm_bf16_kernel<BN, A_MN, B_MN, MODE>`` / ``gemm2_bf16_kernel<A_MN, B_MN, ..>``):
+        B stored [K, N] is a dgrad, both operands MN-major a wgrad; MODE 1 / 2 carry their collective inside."""
+        low = name
+        if any(k in low for k in cls.COMM):
+            return "comm"
+        if any(k in low for k in cls.OPT):
+            return "optimizer"
+        if "gemm_bf16_kernel<" in low or "gemm2_bf16_kernel<" in low:
+            flags = low.split("<", 1)[1].split(">")[0].replace(" ", "").split(",")
+            bools = [f for f in flags if f in ("true", "false")]
+            if len(bools) >= 2 and bools[1] == "true":
+                return "backward"
+            return "forward"
+        if any(k in low for k in cls.BWD):
+            return "backward"
+        return "forward"
+
+    def step_trace(self):
+        """Per training step (``msb::step`` ranges recorded by the train-step cells; the whole capture when there are
+        none): device time by phase, the part of communication not hidden behind compute, and idle gaps - the
+        split of the reference's step trace (profiler/parser/step_trace_parser.py: iteration interval, fp_and_bp,
+        tail; gpu_profiling.cc:459-547 for the kernel / op correlation)."""
+        evs = list(self._events())
+        kernels = sorted(((e.time_range.start, e.time_range.end, e.name) for e in evs
+                          if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda k: k[0])
+        steps = sorted((e.time_range.start, e.time_range.end) for e in evs
+                       if e.device_type == torch.autograd.DeviceType.CPU and e.name == "msb::step")
+        if not kernels:
+            return []
+        if not steps:
+            windows = [(kernels[0][0], max(k[1] for k in kernels))]
+        else:
+            # a step's kernels run after its CPU range starts and before the next step's first kernel
+            windows = []
+            for i, (s0, s1) in enumerate(steps):
+                nxt = steps[i + 1][0] if i + 1 < len(steps) else float("inf")
+                ks = [k for k in kernels if s0 <= k[0] < nxt]
+                if ks:
+                    windows.append((ks[0][0], max(k[1] for k in ks)))
+        rows = []
+        for i, (w0, w1) in enumerate(windows):
+            ks = [k for k in kernels if w0 <= k[0] <= w1]
+            by = {"forward": 0.0, "backward": 0.0, "optimizer": 0.0, "comm": 0.0}
+            marks = []
+            for a, b, name in ks:
+                c = self.classify(name)
+                by[c] += b - a
+                marks.append((a, 1, c == "comm"))
+                marks.append((b, -1, c == "comm"))
+            marks.sort(key=lambda m: (m[0], m[1]))
+            busy = exposed = 0.0
+            n_all = n_comm = 0
+            prev = None
+            for t, d, is_comm in marks:
+                if prev is not None and n_all > 0:
+                    busy += t - prev
+                    if n_comm == n_all:
+                        exposed += t - prev
+                n_all += d
+                if is_comm:
+                    n_comm += d
+                prev = t
+            total = w1 - w0
+            rows.append({"step": i, "total_ms": round(total / 1e3, 3), "fp_ms": round(by["forward"] / 1e3, 3),
+                         "bp_ms": round(by["backward"] / 1e3, 3), "optimizer_ms": round(by["optimizer"] / 1e3, 3),
+                         "comm_ms": round(by["comm"] / 1e3, 3), "comm_exposed_ms": round(exposed / 1e3, 3),
+                         "gap_ms": round((total - busy) / 1e3, 3), "kernels": len(ks)})
+        return rows
 
     def summary(self, top=30):
         rows = self.op_analyse()
@@ -115,6 +201,17 @@ class Profiler:
             lines.append("%10.3f ms %6.2f%% n=%5d  %s" % (r["total_us"] / 1000, 100 * r["share"], r["calls"],
                                                          r["name"][:110]))
         return "\n".join(lines)
+
+
+_active = [0]
+
+
+def step_range():
+    """Context manager the train-step cells wrap one step in: a ``msb::step`` range when a profiler is running."""
+    if _active[0] > 0:
+        return torch.profiler.record_function("msb::step")
+    import contextlib
+    return contextlib.nullcontext()
 
 
 class EnvProfiler:
@@ -172,6 +269,9 @@ def _main(argv=None):
     prof.stop()
     prof.analyse()
     print(prof.summary(40))
+    for row in prof.step_trace():
+        print("step %(step)d: %(total_ms).2f ms = fp %(fp_ms).2f + bp %(bp_ms).2f + optimizer %(optimizer_ms).2f + "
+              "comm %(comm_ms).2f (exposed %(comm_exposed_ms).2f) + gaps %(gap_ms).2f" % row)
     return 0
 
 

@@ -1,9 +1,13 @@
 """Micro-benchmarks of the sm_100a kernels: ``python -m mindspore_b200.utils.kernel_bench <what> [options]``.
 
-Each benchmark warms up, then times ``--iters`` launches with CUDA events on the launching stream.  Between timed
-launches the operands rotate through enough distinct buffers to exceed the L2 capacity (``--l2-mb``), so every launch
-reads its inputs from HBM.  One JSON line per case goes to stdout.  With ``--once`` a case is launched a few times
-without timing (the form to run under a profiler on a small problem)."""
+Each benchmark warms up, then times at least ``--iters`` launches - and at least ``--min-ms`` of device time, so that
+the 200 ms clock sampler sees the region - with CUDA events on the launching stream.  Between timed launches the
+operands rotate through enough distinct buffers to exceed the L2 capacity (``--l2-mb``), so every launch reads its
+inputs from HBM.  One JSON line per case goes to stdout; every row carries the SM clock sampled during its timed
+region (``sm_mhz``: median under load, ``sm_max_mhz``, throttle ``reasons``) and ``ms_x_mhz`` (time x clock, the
+quantity to compare between runs that saw different clocks).  A row whose reasons include a hardware or thermal
+slowdown is not a valid performance number.  With ``--once`` a case is launched a few times without timing (the form
+to run under a profiler on a small problem)."""
 from __future__ import annotations
 
 import argparse
@@ -14,17 +18,49 @@ import sys
 import torch
 
 
+_sampler = None
+_min_ms = 1500.0
+_last_clocks = {}
+
+
 def _time(fn, sets, iters, warmup=3):
+    """Mean milliseconds per launch; the clocks seen during the timed region are left in ``_last_clocks``."""
+    import time
     for i in range(warmup):
         fn(*sets[i % len(sets)])
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record()
+    for i in range(3):
+        fn(*sets[i % len(sets)])
+    e1.record()
+    torch.cuda.synchronize()
+    est = max(e0.elapsed_time(e1) / 3, 1e-3)
+    iters = max(iters, int(math.ceil(_min_ms / est)))
+    t0 = time.time()
+    e0.record()
     for i in range(iters):
         fn(*sets[i % len(sets)])
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / iters
+    t1 = time.time()
+    ms = e0.elapsed_time(e1) / iters
+    _last_clocks.clear()
+    if _sampler is not None:
+        time.sleep(0.25)                      # let the sample that covers the end of the region arrive
+        _last_clocks.update(_sampler.window(t0, t1))
+        _last_clocks["iters"] = iters
+    return ms
+
+
+def _clk(ms, prefix=""):
+    c = dict(_last_clocks)
+    out = {prefix + "sm_mhz": c.get("sm_mhz"), prefix + "reasons": c.get("reasons")}
+    if not prefix:
+        out["sm_max_mhz"] = c.get("sm_max_mhz")
+    if c.get("sm_mhz"):
+        out[prefix + "ms_x_mhz"] = round(ms * c["sm_mhz"], 2)
+    return out
 
 
 def _nsets(bytes_per_set, l2_mb):
@@ -53,11 +89,14 @@ def bench_gemm(args):
                 torch.cuda.synchronize()
                 continue
             lib = lambda a, b, c: torch.matmul(a.t() if a_mn else a, b if b_mn else b.t(), out=c)
-            ms, ms_lib = _time(ours, sets, args.iters), _time(lib, sets, args.iters)
+            ms = _time(ours, sets, args.iters)
+            c_ours = _clk(ms)
+            ms_lib = _time(lib, sets, args.iters)
+            c_lib = _clk(ms_lib, "cublas_")
             fl = 2.0 * M * N * Kd
             _emit(kernel="gemm_bf16", M=M, N=N, K=Kd, a_mn=a_mn, b_mn=b_mn, ms=round(ms, 4),
                   tflops=round(fl / ms / 1e9, 1), cublas_ms=round(ms_lib, 4), cublas_tflops=round(fl / ms_lib / 1e9, 1),
-                  buffers=n)
+                  buffers=n, **c_ours, **c_lib)
 
 
 def bench_attention(args):
@@ -79,7 +118,10 @@ def bench_attention(args):
             outs = [fwd(*s) for s in sets]
             bwd_sets = [(s[3], o[2], o[3], o[4], o[0], o[1]) for s, o in zip(sets, outs)]
             bwd = lambda do, q, k, v, o, lse: FK.bwd(do, q, k, v, o, lse, causal, sc)
-            ms_f, ms_b = _time(fwd, sets, args.iters), _time(bwd, bwd_sets, args.iters)
+            ms_f = _time(fwd, sets, args.iters)
+            c_f = _clk(ms_f, "fwd_")
+            ms_b = _time(bwd, bwd_sets, args.iters)
+            c_b = _clk(ms_b, "bwd_")
             lib_sets = [tuple(t.permute(0, 2, 1, 3).detach().requires_grad_(True) for t in s[:3]) + (s[3].permute(0, 2, 1, 3),)
                         for s in sets]
             sdpa = torch.nn.functional.scaled_dot_product_attention
@@ -87,12 +129,15 @@ def bench_attention(args):
             lib_outs = [lib_f(*s) for s in lib_sets]
             lib_b_sets = [(o, s) for o, s in zip(lib_outs, lib_sets)]
             lib_b = lambda o, s: torch.autograd.grad(o, s[:3], s[3], retain_graph=True)
-            ms_lf, ms_lb = _time(lib_f, lib_sets, args.iters), _time(lib_b, lib_b_sets, args.iters)
+            ms_lf = _time(lib_f, lib_sets, args.iters)
+            c_lf = _clk(ms_lf, "sdpa_fwd_")
+            ms_lb = _time(lib_b, lib_b_sets, args.iters)
+            c_lb = _clk(ms_lb, "sdpa_bwd_")
             f = 4.0 * B * H * S * S * D * (0.5 if causal else 1.0)
             _emit(kernel="flash_attention", B=B, S=S, H=H, D=D, causal=causal, fwd_ms=round(ms_f, 4),
                   fwd_tflops=round(f / ms_f / 1e9, 1), bwd_ms=round(ms_b, 4), bwd_tflops=round(2.5 * f / ms_b / 1e9, 1),
                   sdpa_fwd_ms=round(ms_lf, 4), sdpa_fwd_tflops=round(f / ms_lf / 1e9, 1), sdpa_bwd_ms=round(ms_lb, 4),
-                  sdpa_bwd_tflops=round(2.5 * f / ms_lb / 1e9, 1), buffers=n)
+                  sdpa_bwd_tflops=round(2.5 * f / ms_lb / 1e9, 1), buffers=n, **c_f, **c_b, **c_lf, **c_lb)
 
 
 def bench_elementwise(args):
@@ -104,22 +149,22 @@ def bench_elementwise(args):
     w = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16()
     sets = [(mk(rows, H), mk(rows, H)) for _ in range(n)]
     ms = _time(lambda x, r: K.rmsnorm_fwd(x, w, 1e-5, residual=r), sets, args.iters)
-    _emit(kernel="rmsnorm_fwd+residual", rows=rows, H=H, ms=round(ms, 4), gbs=round(rows * H * 2 * 4 / ms / 1e6, 1))
+    _emit(kernel="rmsnorm_fwd+residual", rows=rows, H=H, ms=round(ms, 4), gbs=round(rows * H * 2 * 4 / ms / 1e6, 1), **_clk(ms))
     y, rstd, xs = K.rmsnorm_fwd(sets[0][0], w, 1e-5, residual=sets[0][1])
     ms = _time(lambda x, r: K.rmsnorm_bwd(x, r, w, rstd, dresidual=x), sets, args.iters)
-    _emit(kernel="rmsnorm_bwd+dresidual", rows=rows, H=H, ms=round(ms, 4), gbs=round(rows * H * 2 * 4 / ms / 1e6, 1))
+    _emit(kernel="rmsnorm_bwd+dresidual", rows=rows, H=H, ms=round(ms, 4), gbs=round(rows * H * 2 * 4 / ms / 1e6, 1), **_clk(ms))
     n2 = _nsets(rows * F * 2 * 3, args.l2_mb)
     gsets = [(mk(rows, 2 * F), mk(rows, F)) for _ in range(n2)]
     ms = _time(lambda gu, do: K.swiglu_fwd(gu), gsets, args.iters)
-    _emit(kernel="swiglu_fwd", rows=rows, F=F, ms=round(ms, 4), gbs=round(rows * F * 2 * 3 / ms / 1e6, 1))
+    _emit(kernel="swiglu_fwd", rows=rows, F=F, ms=round(ms, 4), gbs=round(rows * F * 2 * 3 / ms / 1e6, 1), **_clk(ms))
     ms = _time(lambda gu, do: K.swiglu_bwd(gu, do), gsets, args.iters)
-    _emit(kernel="swiglu_bwd", rows=rows, F=F, ms=round(ms, 4), gbs=round(rows * F * 2 * 5 / ms / 1e6, 1))
+    _emit(kernel="swiglu_bwd", rows=rows, F=F, ms=round(ms, 4), gbs=round(rows * F * 2 * 5 / ms / 1e6, 1), **_clk(ms))
     nel = 1 << 28
     p, m, v, g = (torch.randn(nel, device="cuda") for _ in range(4))
     lp = torch.empty(nel, device="cuda", dtype=torch.bfloat16)
     hy = torch.tensor([1e-4, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05, 1.0], device="cuda")
     ms = _time(lambda: K.adamw_step(p, m, v, g, lp, hy), [()], args.iters)
-    _emit(kernel="adamw", n=nel, ms=round(ms, 4), gbs=round(nel * (4 * 7 + 2) / ms / 1e6, 1))
+    _emit(kernel="adamw", n=nel, ms=round(ms, 4), gbs=round(nel * (4 * 7 + 2) / ms / 1e6, 1), **_clk(ms))
 
 
 def main(argv=None):
@@ -135,11 +180,21 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--l2-mb", type=int, default=128)
     ap.add_argument("--once", action="store_true")
+    ap.add_argument("--min-ms", type=float, default=1500.0, help="shortest timed region per case (clock sampling)")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("kernel_bench needs a CUDA device", file=sys.stderr)
         return 1
-    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise}[args.what](args)
+    global _sampler, _min_ms
+    _min_ms = args.min_ms
+    if not args.once:
+        from .clocks import ClockSampler
+        _sampler = ClockSampler(torch.cuda.current_device()).start()
+    try:
+        {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise}[args.what](args)
+    finally:
+        if _sampler is not None:
+            _sampler.stop()
     from .. import _native
     torch.cuda.synchronize()
     _emit(device_status=_native.device_status())

@@ -97,3 +97,32 @@ def test_summary_collector_writes_event_file_and_landscape(tmp_path):
         lambda: (model, loss_net, data, None), {"landscape_size": 5, "span": 1.0})
     grid = np.array(json.load(open(path))["loss"])
     assert grid.shape == (5, 5) and grid[2, 2] < grid.mean() and np.isfinite(grid).all()
+
+
+def test_step_trace_splits_phases_exposed_communication_and_gaps():
+    """Synthetic timeline: two steps; forward, backward (by name and by GEMM operand layout), optimizer, a
+    collective half hidden behind a GEMM, and an idle gap."""
+    import types
+    import torch
+    from mindspore_b200.profiler import Profiler
+
+    def ev(name, start, end, cuda=True):
+        return types.SimpleNamespace(name=name, time_range=types.SimpleNamespace(start=start, end=end),
+                                     device_type=torch.autograd.DeviceType.CUDA if cuda else torch.autograd.DeviceType.CPU)
+
+    def step(t):
+        return [ev("msb::step", t, t + 50, cuda=False),
+                ev("msb::rmsnorm_fwd_kernel<2>", t + 100, t + 200),
+                ev("void msb::gemm_bf16_kernel<256, false, false, 0>(...)", t + 200, t + 500),
+                ev("ncclDevKernel_AllGather_RING_LL", t + 400, t + 700),        # 100 us hidden, 200 us exposed
+                ev("void msb::gemm_bf16_kernel<256, false, true, 0>(...)", t + 800, t + 1000),    # dgrad
+                ev("msb::fa_bwd_dq_kernel", t + 1000, t + 1100),
+                ev("void msb::adamw_kernel<float>(...)", t + 1100, t + 1300)]
+
+    prof = Profiler.__new__(Profiler)
+    prof._events = lambda: step(0) + step(10000)
+    rows = prof.step_trace()
+    assert len(rows) == 2
+    for r in rows:
+        assert r["fp_ms"] == 0.4 and r["bp_ms"] == 0.3 and r["optimizer_ms"] == 0.2 and r["comm_ms"] == 0.3
+        assert r["comm_exposed_ms"] == 0.2 and r["gap_ms"] == 0.1 and r["total_ms"] == 1.2 and r["kernels"] == 6
