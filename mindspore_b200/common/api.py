@@ -19,7 +19,7 @@ from .tensor import Tensor
 __all__ = ["mutable", "lazy_inline", "no_inline", "jit_class", "recompute", "Symbol", "Generator", "default_generator",
            "manual_seed", "initial_seed", "get_rng_state", "set_rng_state", "COOTensor", "CSRTensor", "RowTensor",
            "SparseTensor", "vmap", "hessian", "get_grad", "data_sink", "ms_memory_recycle", "run_check",
-           "set_algo_parameters", "get_algo_parameters", "reset_algo_parameters"]
+           "set_algo_parameters", "get_algo_parameters", "reset_algo_parameters", "set_cost_model_context", "get_cost_model_context", "reset_cost_model_context"]
 
 
 # ------------------------------------------------------------------------------------------------ compile hints
@@ -450,6 +450,10 @@ def get_algo_parameters(attr_key):
     if attr_key not in _algo:
         raise ValueError("Get context keyword %s is not recognized!" % attr_key)
     return _algo[attr_key]
+
+
+from ..parallel.cost_model import (get_cost_model_context, reset_cost_model_context,  # noqa: E402,F401
+                                   set_cost_model_context)
 
 
 def reset_algo_parameters():

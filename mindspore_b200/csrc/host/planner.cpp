@@ -249,3 +249,136 @@ MSB_API int msb_propagate_strategies(int n, const int32_t* n_cand, const int32_t
     if (choice_out[i] < 0) choice_out[i] = 0;
   return assigned;
 }
+
+// ------------------------------------------------------------------------------------------------ elimination search
+// Exact minimum of   sum_i op_cost[i][c_i] + sum_e edge_cost[e][c_src][c_dst]   over all assignments, by eliminating
+// the nodes one after the other (min-degree order): removing node v folds its own cost and every cost table that
+// mentions v into one table over v's remaining neighbours, remembering the best candidate of v for each of their
+// assignments.  Eliminating a node of degree 1 / 2 / 3 is what the reference calls operator, edge / merge /
+// contract, and triangle / star elimination (auto_parallel/graph_costmodel.cc:866-1776, dp_algo_costmodel.cc); the
+// general form handles any graph whose neighbourhoods stay small.  fixed[i] >= 0 pins node i.
+// Returns the optimal cost, or -1 when a table would exceed `max_table` entries (caller falls back).
+namespace {
+struct Factor {
+  std::vector<int> vars;
+  std::vector<double> tab;   // row-major over vars, last var fastest
+};
+}  // namespace
+
+MSB_API double msb_elimination_search(int n, const int32_t* n_cand, const double* op_cost, int n_edges,
+                                      const int32_t* src, const int32_t* dst, const int64_t* cost_off,
+                                      const double* edge_cost, const int32_t* fixed, long long max_table,
+                                      int32_t* choice_out) {
+  const double INF = std::numeric_limits<double>::infinity();
+  if (n <= 0) return 0.0;
+  std::vector<int> op_off(n + 1, 0);
+  for (int i = 0; i < n; ++i) op_off[i + 1] = op_off[i] + n_cand[i];
+  std::vector<Factor> factors;
+  for (int i = 0; i < n; ++i) {
+    Factor f;
+    f.vars = {i};
+    f.tab.assign(op_cost + op_off[i], op_cost + op_off[i + 1]);
+    if (fixed && fixed[i] >= 0)
+      for (int c = 0; c < n_cand[i]; ++c)
+        if (c != fixed[i]) f.tab[c] = INF;
+    factors.push_back(std::move(f));
+  }
+  for (int e = 0; e < n_edges; ++e) {
+    if (src[e] < 0 || src[e] >= n || dst[e] < 0 || dst[e] >= n || src[e] == dst[e]) return -1;
+    Factor f;
+    f.vars = {src[e], dst[e]};
+    f.tab.assign(edge_cost + cost_off[e], edge_cost + cost_off[e] + static_cast<long long>(n_cand[src[e]]) * n_cand[dst[e]]);
+    factors.push_back(std::move(f));
+  }
+  std::vector<bool> alive_f(factors.size(), true), gone(n, false);
+  struct Decision {
+    int var;
+    std::vector<int> scope;
+    std::vector<int32_t> arg;
+  };
+  std::vector<Decision> decisions;
+  double constant = 0.0;
+  for (int step = 0; step < n; ++step) {
+    // interaction-graph degree of every remaining node
+    int best_v = -1;
+    size_t best_deg = static_cast<size_t>(-1);
+    for (int v = 0; v < n; ++v) {
+      if (gone[v]) continue;
+      std::vector<int> nb;
+      for (size_t fi = 0; fi < factors.size(); ++fi) {
+        if (!alive_f[fi]) continue;
+        const auto& vs = factors[fi].vars;
+        if (std::find(vs.begin(), vs.end(), v) == vs.end()) continue;
+        for (int u : vs)
+          if (u != v && std::find(nb.begin(), nb.end(), u) == nb.end()) nb.push_back(u);
+      }
+      if (nb.size() < best_deg) { best_deg = nb.size(); best_v = v; }
+    }
+    const int v = best_v;
+    std::vector<size_t> mine;
+    std::vector<int> scope;
+    for (size_t fi = 0; fi < factors.size(); ++fi) {
+      if (!alive_f[fi]) continue;
+      const auto& vs = factors[fi].vars;
+      if (std::find(vs.begin(), vs.end(), v) == vs.end()) continue;
+      mine.push_back(fi);
+      for (int u : vs)
+        if (u != v && std::find(scope.begin(), scope.end(), u) == scope.end()) scope.push_back(u);
+    }
+    std::sort(scope.begin(), scope.end());
+    long long size = 1;
+    for (int u : scope) {
+      size *= n_cand[u];
+      if (size > max_table) return -1;
+    }
+    Factor nf;
+    nf.vars = scope;
+    nf.tab.assign(static_cast<size_t>(size), INF);
+    Decision d;
+    d.var = v;
+    d.scope = scope;
+    d.arg.assign(static_cast<size_t>(size), 0);
+    std::vector<int> assign(n, 0);
+    for (long long idx = 0; idx < size; ++idx) {
+      long long rem = idx;
+      for (int k = static_cast<int>(scope.size()) - 1; k >= 0; --k) {
+        assign[scope[k]] = static_cast<int>(rem % n_cand[scope[k]]);
+        rem /= n_cand[scope[k]];
+      }
+      double best = INF;
+      int best_c = 0;
+      for (int c = 0; c < n_cand[v]; ++c) {
+        assign[v] = c;
+        double sum = 0.0;
+        for (size_t fi : mine) {
+          const Factor& f = factors[fi];
+          long long off = 0;
+          for (int u : f.vars) off = off * n_cand[u] + assign[u];
+          sum += f.tab[static_cast<size_t>(off)];
+          if (sum == INF) break;
+        }
+        if (sum < best) { best = sum; best_c = c; }
+      }
+      nf.tab[static_cast<size_t>(idx)] = best;
+      d.arg[static_cast<size_t>(idx)] = best_c;
+    }
+    for (size_t fi : mine) alive_f[fi] = false;
+    gone[v] = true;
+    if (scope.empty()) {
+      constant += nf.tab[0];
+    } else {
+      factors.push_back(std::move(nf));
+      alive_f.push_back(true);
+    }
+    decisions.push_back(std::move(d));
+  }
+  std::vector<int> assign(n, 0);
+  for (int k = static_cast<int>(decisions.size()) - 1; k >= 0; --k) {
+    const Decision& d = decisions[k];
+    long long off = 0;
+    for (int u : d.scope) off = off * n_cand[u] + assign[u];
+    assign[d.var] = d.arg[static_cast<size_t>(off)];
+  }
+  for (int i = 0; i < n; ++i) choice_out[i] = assign[i];
+  return constant;
+}

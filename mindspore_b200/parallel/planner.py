@@ -107,3 +107,26 @@ def propagate_strategies(n_cand, fixed, edges, edge_costs):
     if rc < 0:
         raise ValueError("invalid propagation request")
     return [choice[i] for i in range(n)]
+
+
+def elimination_search(n_cand, op_costs, edges, edge_costs, fixed=None, max_table=4_000_000):
+    """Exact minimum-cost strategy assignment on a general operator graph by node elimination (native).  Returns
+    (choices, cost) or (None, None) when an intermediate table would exceed ``max_table`` entries."""
+    n = len(n_cand)
+    offs, flat = [], []
+    for m in edge_costs:
+        offs.append(len(flat))
+        for row in m:
+            flat += [float(v) for v in row]
+    flat_op = [float(v) for c in op_costs for v in c]
+    choice = (ctypes.c_int32 * max(n, 1))()
+    lib = _host()
+    lib.msb_elimination_search.restype = ctypes.c_double
+    cost = lib.msb_elimination_search(
+        n, _arr(ctypes.c_int32, n_cand), _arr(ctypes.c_double, flat_op), len(edges),
+        _arr(ctypes.c_int32, [e[0] for e in edges]), _arr(ctypes.c_int32, [e[1] for e in edges]),
+        _arr(ctypes.c_int64, offs), _arr(ctypes.c_double, flat),
+        _arr(ctypes.c_int32, fixed if fixed is not None else [-1] * n), ctypes.c_longlong(max_table), choice)
+    if cost < 0:
+        return None, None
+    return [choice[i] for i in range(n)], cost
