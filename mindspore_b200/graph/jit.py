@@ -116,6 +116,20 @@ class _Recorder(TorchFunctionMode):
             return slice(self.arg(a.start), self.arg(a.stop), self.arg(a.step))
         return a
 
+    def _remap(self, replaced):
+        """Nodes that a rewrite replaced: tensors recorded against them now belong to the replacement."""
+        if not replaced:
+            return
+
+        def final(n):
+            while n in replaced:
+                n = replaced[n]
+            return n
+        for table in (self.node_of, self.alias):
+            for k, n in list(table.items()):
+                if n in replaced:
+                    table[k] = final(n)
+
     def knows(self, t):
         if id(t) in self.node_of:
             return True
@@ -181,9 +195,17 @@ class _Recorder(TorchFunctionMode):
     # ---- GradOperation under trace
     def trace_grad(self, fn, inputs, weights, sens, want_inputs, input_positions, has_aux, return_value):
         fg = self.fg
-        start = len(list(fg.graph.nodes))
+        before = list(fg.graph.nodes)
+        anchor = before[-1] if before else None
         out = fn(*inputs)  # forward recorded inline (second copy of the forward; CSE merges it with the first)
-        fwd_nodes = list(fg.graph.nodes)[start:]
+        # operator chains that have one fused kernel are rewritten now, before reverse mode is built on them; the
+        # pass runs over the whole graph so that an earlier copy of the same forward is fused identically
+        from .fusion import fuse_patterns
+        self._remap(fuse_patterns(fg))
+        nodes = list(fg.graph.nodes)
+        if anchor is not None and anchor not in nodes:          # the anchor itself was fused away
+            anchor = next((n for n in reversed(before) if n in set(nodes)), None)
+        fwd_nodes = nodes[nodes.index(anchor) + 1:] if anchor is not None else nodes
         primary = out[0] if has_aux else out
         out_nodes = [self.node_of[id(o)] for o in _flat_tensors(primary) if id(o) in self.node_of]
         in_targets = [x for i, x in enumerate(inputs) if want_inputs and (input_positions is None or i in input_positions)

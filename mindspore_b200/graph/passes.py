@@ -84,6 +84,10 @@ def common_subexpression_elimination(fg):
             seen[key] = n
             continue
         if n.meta.get("requires_vjp"):
+            if prev.meta.get("requires_vjp") and any(
+                    m.op == "call_function" and m.target is autodiff.vjp and m.args[0] == prev.name
+                    for m in fg.graph.nodes):
+                continue          # both copies are differentiated: each vjp node consumes its own saved forward
             prev.meta["requires_vjp"] = True
             # the vjp node refers to the forward node by name: redirect it
             for m in fg.graph.nodes:
@@ -119,11 +123,13 @@ def run_default_passes(fg, tag, save_level=0, path="."):
     marking) with the effect chains they respect.  Pass order follows pipeline/jit/ps/pass.cc:424-527 in spirit:
     simplify first so that the communication passes see the final producers."""
     from . import opt_passes as O
+    from .fusion import fuse_patterns
     pm = PassManager("opt_a")
     pm.add("cast_eliminate", O.cast_eliminate)
     pm.add("arithmetic_simplify", O.arithmetic_simplify)
     pm.add("cse", common_subexpression_elimination)
     pm.add("dce", dead_code_elimination)
+    pm.add("fuse_patterns", lambda g: len(fuse_patterns(g)))
     for _ in range(4):
         if not pm.run(fg, tag, save_level, path):
             break

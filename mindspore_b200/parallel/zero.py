@@ -112,9 +112,23 @@ class DataParallelArena:
                 pos = max(pos, (e + _SLICE_ALIGN - 1) // _SLICE_ALIGN * _SLICE_ALIGN)
             if pos < arena.total:
                 ranges.append((pos, arena.total))
-            step = _OVERLAP_BUCKET_ELEMS if self._overlap_eligible() else _BUCKET_ELEMS
+            step = self._overlap_bucket_elems() if self._overlap_eligible() else _BUCKET_ELEMS
             self._reduce_ranges = [(lo, min(lo + step, hi)) for s, hi in ranges for lo in range(s, hi, step)]
         return self._reduce_ranges
+
+    @staticmethod
+    def _overlap_bucket_elems():
+        """fp32 gradient elements per overlapped all-reduce bucket: the ``comm_fusion`` all-reduce size threshold of
+        the auto-parallel context when one is configured (``{"allreduce": {"mode": "size", "config": MB}}``), else
+        16 MB."""
+        from .comm_fusion import _policy
+        from .. import context
+        cf = context.get_auto_parallel_context("comm_fusion") or {}
+        if "allreduce" in cf:
+            mode, cfg = _policy("allreduce")
+            if mode == "size" and cfg:
+                return max(_SLICE_ALIGN, int(float(cfg) * 1024 * 1024 / 4) // _SLICE_ALIGN * _SLICE_ALIGN)
+        return _OVERLAP_BUCKET_ELEMS
 
     def _overlap_eligible(self):
         """Overlap runs the gradient all-reduce on a side stream.  It is limited to pure data parallelism: with a

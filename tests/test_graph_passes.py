@@ -182,3 +182,54 @@ def test_graph_mode_data_parallel_all_reduces_on_every_replay():
             torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
     for a, b in zip(graph[0][0], graph[1][0]):               # replicas stay identical
         torch.testing.assert_close(a, b, rtol=0, atol=0)
+
+
+def test_pattern_fusion_keeps_training_results():
+    """Reference-style small operators (Add + RmsNorm, Split + SiLU * up, MatMul + BiasAdd + GeLU) train to the same
+    parameters in graph mode, where they are rewritten to the fused primitives, as eagerly."""
+    def run(mode):
+        ms.set_context(mode=mode, device_target="CPU")
+        ms.set_seed(4)
+
+        class Block(nn.Cell):
+            def __init__(self):
+                super().__init__()
+                g = torch.Generator().manual_seed(2)
+                self.gamma = ms.Parameter(ms.Tensor(torch.rand(16, generator=g) + 0.5), name="gamma")
+                self.w_gu = ms.Parameter(ms.Tensor(torch.randn(64, 16, generator=g) * 0.2), name="w_gu")
+                self.w_d = ms.Parameter(ms.Tensor(torch.randn(16, 32, generator=g) * 0.2), name="w_d")
+                self.b_d = ms.Parameter(ms.Tensor(torch.randn(16, generator=g) * 0.1), name="b_d")
+                self.b_gu = ms.Parameter(ms.Tensor(torch.randn(64, generator=g) * 0.1), name="b_gu")
+                self.bias_gu = ops.BiasAdd()
+                self.add, self.norm = ops.Add(), ops.RmsNorm(1e-5)
+                self.mm1, self.mm2 = ops.MatMul(transpose_b=True), ops.MatMul(transpose_b=True)
+                self.split, self.silu, self.mul = ops.Split(axis=-1, output_num=2), ops.SiLU(), ops.Mul()
+                self.bias, self.gelu, self.sum = ops.BiasAdd(), ops.GeLU(), ops.ReduceSum()
+
+            def construct(self, x, r):
+                s = self.add(x, r)
+                h = self.norm(s, self.gamma)[0]
+                gate, up = self.split(self.bias_gu(self.mm1(h, self.w_gu), self.b_gu))
+                y = self.gelu(self.bias(self.mm2(self.mul(self.silu(gate), up), self.w_d), self.b_d))
+                return self.sum((y + s) * (y + s), ())
+
+        net = Block()
+        opt = nn.Momentum(net.trainable_params(), learning_rate=0.01, momentum=0.9)
+        step = nn.TrainOneStepCell(net, opt)
+        step.set_train()
+        g = torch.Generator().manual_seed(7)
+        losses = [float(step(ms.Tensor(torch.randn(8, 16, generator=g)), ms.Tensor(torch.randn(8, 16, generator=g))))
+                  for _ in range(4)]
+        names = []
+        if mode == ms.GRAPH_MODE:
+            (cg,) = step._compiled.values()
+            names = _names(cg.fg)
+        return losses, [p.detach().clone() for p in net.get_parameters()], names
+    ref_l, ref_p, _ = run(ms.PYNATIVE_MODE)
+    l, p, names = run(ms.GRAPH_MODE)
+    ms.set_context(mode=ms.PYNATIVE_MODE)
+    assert "AddRmsNorm" in names and "SwiGLU" in names and "RmsNorm" not in names and "SiLU" not in names, names
+    assert "gelu_tanh" in names and "linear" in names and "BiasAdd" not in names, names
+    assert l == pytest.approx(ref_l, rel=1e-5)
+    for a, b in zip(p, ref_p):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
