@@ -75,12 +75,20 @@ _CUDA_SIGNATURES = {
 }
 
 
+def _apply_signature(lib, name, restype, argtypes):
+    """Sets the ctypes signature of ``name`` and of its fp16 build (``name_fp16``, or ``..._fp16`` for a name that
+    spells ``bf16``), which takes the same arguments."""
+    for n in {name, name + "_fp16", name.replace("bf16", "fp16")}:
+        if hasattr(lib, n):
+            fn = getattr(lib, n)
+            fn.restype, fn.argtypes = restype, argtypes
+
+
 def register_cuda_signature(name, restype, argtypes):
     """Lets later modules (attention, conv, fused collectives) declare their entry points."""
     _CUDA_SIGNATURES[name] = (restype, argtypes)
-    if _cuda is not None and hasattr(_cuda, name):
-        fn = getattr(_cuda, name)
-        fn.restype, fn.argtypes = restype, argtypes
+    if _cuda is not None:
+        _apply_signature(_cuda, name, restype, argtypes)
 
 
 def cuda():
@@ -91,9 +99,7 @@ def cuda():
             if _cuda is None:
                 lib = _load(_build.CUDA_LIB, _build.build_cuda)
                 for name, (res, args) in _CUDA_SIGNATURES.items():
-                    if hasattr(lib, name):
-                        fn = getattr(lib, name)
-                        fn.restype, fn.argtypes = res, args
+                    _apply_signature(lib, name, res, args)
                 _cuda = lib
     return _cuda
 

@@ -2,9 +2,10 @@
 // [batch][token][head][128] tensors, the tensor-map encoder for them, and exp2.
 #pragma once
 #include "host_common.h"
-#include "ptx.cuh"
+#include "elem.cuh"
 
 namespace msb {
+namespace MSB_ELEM_NS {
 
 constexpr int kFaD = 128;  // head dim served by these kernels
 
@@ -70,12 +71,13 @@ static inline int fa_encode_map(CUtensorMap* m, const void* base, int B, int S, 
 // 64-column halves are `half_stride` bytes apart.
 __device__ __forceinline__ void fa_store_chunk(uint8_t* tile, int row, int ch, int half_stride, const float* v) {
   uint4 o;
-  o.x = pack_bf16x2(v[0], v[1]);
-  o.y = pack_bf16x2(v[2], v[3]);
-  o.z = pack_bf16x2(v[4], v[5]);
-  o.w = pack_bf16x2(v[6], v[7]);
+  o.x = pack_e2(v[0], v[1]);
+  o.y = pack_e2(v[2], v[3]);
+  o.z = pack_e2(v[4], v[5]);
+  o.w = pack_e2(v[6], v[7]);
   const int half = ch >> 3, cc = ch & 7;
   *reinterpret_cast<uint4*>(tile + half * half_stride + row * 128 + ((cc ^ (row & 7)) << 4)) = o;
 }
 
+}  // namespace MSB_ELEM_NS
 }  // namespace msb

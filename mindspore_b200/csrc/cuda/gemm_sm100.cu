@@ -36,7 +36,8 @@ struct GemmParams {
   long long c_batch_stride;  // elements
   int M, N, K, batch;
   int ldc;            // elements
-  int out_fp32;       // C is fp32 (else bf16)
+  int out_fp32;       // C is fp32 (else the operands' 16-bit type)
+  int fp16;           // operands, bias and a 16-bit C are fp16 (else bf16)
   int accumulate;     // C += result (read-modify-write)
   float alpha;        // result scale applied before bias/accumulate
   // --- MatMul -> ReduceScatter (MODE 1): the epilogue stores each bf16 output tile straight into the staging
@@ -229,7 +230,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     if (lane == 0) {
       // ------------------------------------------------------------------ MMA issuer
-      constexpr uint32_t idesc = umma_idesc_bf16(kBM, BN, A_MN, B_MN);
+      const uint32_t idesc = p.fp16 ? umma_idesc_f16(kBM, BN, A_MN, B_MN) : umma_idesc_bf16(kBM, BN, A_MN, B_MN);
       int s = 0;
       uint32_t ph = 0;
       int it = 0;
@@ -281,6 +282,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int n0 = n_blk * BN;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       const bool row_ok = row < p.M;
+      const bool f16 = p.fp16 != 0;
       long long c_off = static_cast<long long>(b) * p.c_batch_stride + static_cast<long long>(row) * p.ldc;
       __nv_bfloat16* c_bf16 = static_cast<__nv_bfloat16*>(p.C);
       if (MODE == 1 && row_ok_pre(row, p.M)) {
@@ -312,10 +314,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
           if (p.bias) {
-            const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(p.bias);
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) v[j] += __bfloat162float(bias[col0 + j]);
+              if (col0 + j < p.N) v[j] += load_16(p.bias, col0 + j, f16);
           }
           if (p.out_fp32) {
             // one chunk = 32 fp32 = a full 128-byte row
@@ -347,10 +348,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4 o;
-              o.x = pack_bf16x2(v[8 * j], v[8 * j + 1]);
-              o.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
-              o.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
-              o.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+              o.x = pack_16x2(v[8 * j], v[8 * j + 1], f16);
+              o.y = pack_16x2(v[8 * j + 2], v[8 * j + 3], f16);
+              o.z = pack_16x2(v[8 * j + 4], v[8 * j + 5], f16);
+              o.w = pack_16x2(v[8 * j + 6], v[8 * j + 7], f16);
               *reinterpret_cast<uint4*>(rowp + (((half * 4 + j) ^ sw) << 4)) = o;
             }
             const bool last = (c + 32 >= BN) || (n0 + c + 32 >= p.N);
@@ -383,10 +384,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
         if (p.bias) {
-          const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(p.bias);
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) v[j] += __bfloat162float(bias[col0 + j]);
+            if (col0 + j < p.N) v[j] += load_16(p.bias, col0 + j, f16);
         }
         const bool full = (col0 + 32 <= p.N);
         if (p.out_fp32) {
@@ -412,25 +412,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int j = 0; j < 32; j += 8) {
               if (p.accumulate) {
                 const uint4 old = *reinterpret_cast<const uint4*>(dst + j);
-                const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
+                const uint32_t* ob = reinterpret_cast<const uint32_t*>(&old);
 #pragma unroll
                 for (int t = 0; t < 4; ++t) {
-                  const float2 f = __bfloat1622float2(ob[t]);
+                  const float2 f = unpack_16x2(ob[t], f16);
                   v[j + 2 * t] += f.x;
                   v[j + 2 * t + 1] += f.y;
                 }
               }
               uint4 o;
-              o.x = pack_bf16x2(v[j], v[j + 1]);
-              o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-              o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-              o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+              o.x = pack_16x2(v[j], v[j + 1], f16);
+              o.y = pack_16x2(v[j + 2], v[j + 3], f16);
+              o.z = pack_16x2(v[j + 4], v[j + 5], f16);
+              o.w = pack_16x2(v[j + 6], v[j + 7], f16);
               *reinterpret_cast<uint4*>(dst + j) = o;
             }
           } else {
             for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N)
-                dst[j] = __float2bfloat16(p.accumulate ? __bfloat162float(dst[j]) + v[j] : v[j]);
+              if (col0 + j < p.N) store_16(dst, j, p.accumulate ? load_16(dst, j, f16) + v[j] : v[j], f16);
           }
         }
       }
@@ -597,10 +596,10 @@ static int encode_output(CUtensorMap* map, const void* C, int M, int N, int batc
 // (a_mn=1, row pitch lda); B is [N,K] (b_mn=0) or stored [K,N] (b_mn=1).  Pitches and batch
 // strides are in elements and must be multiples of 8; base pointers 16-byte aligned.
 // bn_hint: 0 = choose, else 128 or 256.
-MSB_EXPORT int msb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int batch,
-                             int a_mn, int b_mn, long long lda, long long ldb, long long ldc,
-                             long long a_batch_stride, long long b_batch_stride, long long c_batch_stride,
-                             int out_fp32, int accumulate, float alpha, int bn_hint, void* stream_) {
+static int gemm_16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int batch,
+                   int a_mn, int b_mn, long long lda, long long ldb, long long ldc, long long a_batch_stride,
+                   long long b_batch_stride, long long c_batch_stride, int out_fp32, int accumulate, float alpha,
+                   int bn_hint, int fp16, void* stream_) {
   using namespace msb;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) {
     set_last_error("gemm: empty problem M=%d N=%d K=%d batch=%d", M, N, K, batch);
@@ -620,7 +619,7 @@ MSB_EXPORT int msb_gemm_bf16(const void* A, const void* B, void* C, const void* 
   GemmParams p = {};
   p.C = C; p.bias = bias; p.status = status; p.c_batch_stride = c_batch_stride;
   p.M = M; p.N = N; p.K = K; p.batch = batch; p.ldc = static_cast<int>(ldc);
-  p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
+  p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha; p.fp16 = fp16;
   CMaps tmC = {};
   if (!(accumulate && !out_fp32)) {
     if (int rc = encode_output(&tmC.m[0], C, M, N, batch, ldc, c_batch_stride, out_fp32, &p.tma_epilogue)) return rc;
@@ -636,6 +635,24 @@ MSB_EXPORT int msb_gemm_bf16(const void* A, const void* B, void* C, const void* 
   }
   if (bn == 256) { MSB_DISPATCH(256) } else { MSB_DISPATCH(128) }
 #undef MSB_DISPATCH
+}
+
+MSB_EXPORT int msb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int batch,
+                             int a_mn, int b_mn, long long lda, long long ldb, long long ldc,
+                             long long a_batch_stride, long long b_batch_stride, long long c_batch_stride,
+                             int out_fp32, int accumulate, float alpha, int bn_hint, void* stream_) {
+  return gemm_16(A, B, C, bias, M, N, K, batch, a_mn, b_mn, lda, ldb, ldc, a_batch_stride, b_batch_stride,
+                 c_batch_stride, out_fp32, accumulate, alpha, bn_hint, 0, stream_);
+}
+
+// The same GEMM on fp16 operands (fp16 bias; C fp16 or fp32): the tensor-core instruction takes the operand format
+// from its descriptor, so this is the bf16 kernel with another descriptor and another 16-bit pack in the epilogue.
+MSB_EXPORT int msb_gemm_fp16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int batch,
+                             int a_mn, int b_mn, long long lda, long long ldb, long long ldc,
+                             long long a_batch_stride, long long b_batch_stride, long long c_batch_stride,
+                             int out_fp32, int accumulate, float alpha, int bn_hint, void* stream_) {
+  return gemm_16(A, B, C, bias, M, N, K, batch, a_mn, b_mn, lda, ldb, ldc, a_batch_stride, b_batch_stride,
+                 c_batch_stride, out_fp32, accumulate, alpha, bn_hint, 1, stream_);
 }
 
 namespace msb {

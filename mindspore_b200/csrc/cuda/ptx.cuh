@@ -7,6 +7,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 
 namespace msb {
@@ -205,10 +206,35 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, bool a_mn_m
          (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// The same for fp16 operands: the A / B format fields (bits 7-9, 10-12) are 0 for fp16 and 1 for bf16.
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n, bool a_mn_major, bool b_mn_major) {
+  return umma_idesc_bf16(m, n, a_mn_major, b_mn_major) & ~((7u << 7) | (7u << 10));
+}
+
 // ----------------------------------------------------------------------------- misc
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+// Two fp32 values as one 32-bit pair of 16-bit floats: fp16 when `fp16`, else bf16.
+__device__ __forceinline__ uint32_t pack_16x2(float lo, float hi, bool fp16) {
+  if (fp16) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  return pack_bf16x2(lo, hi);
+}
+__device__ __forceinline__ float2 unpack_16x2(uint32_t u, bool fp16) {
+  if (fp16) return __half22float2(*reinterpret_cast<const __half2*>(&u));
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u));
+}
+__device__ __forceinline__ float load_16(const void* base, long long i, bool fp16) {
+  return fp16 ? __half2float(static_cast<const __half*>(base)[i])
+              : __bfloat162float(static_cast<const __nv_bfloat16*>(base)[i]);
+}
+__device__ __forceinline__ void store_16(void* base, long long i, float v, bool fp16) {
+  if (fp16) static_cast<__half*>(base)[i] = __float2half_rn(v);
+  else static_cast<__nv_bfloat16*>(base)[i] = __float2bfloat16(v);
 }
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

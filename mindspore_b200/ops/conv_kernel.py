@@ -50,7 +50,7 @@ def available():
 
 
 def supports(x, w, group=1, dilation=(1, 1)):
-    return (available() and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 4 and group == 1
+    return (available() and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and x.dim() == 4 and group == 1
             and tuple(dilation) == (1, 1) and w.shape[0] % 8 == 0 and w.shape[2] * w.shape[3] <= 49)
 
 
@@ -77,8 +77,8 @@ def conv_fwd_raw(x, w_krsc, stride, pad_h, pad_w, ho, wo, stats=None, flip=False
     """x NHWC-memory [N, Cin, H, W]; w_krsc [Cout, R, S, Cin] -> y [N, Cout, ho, wo] (channels-last)."""
     n, cin, h, w_ = x.shape
     cout, r, s, _ = w_krsc.shape
-    y = _empty(n, cout, ho, wo, x.device)
-    rc = _native.cuda().msb_conv_fwd(_p(x), _p(w_krsc), _p(y), _p(stats), n, h, w_, cin, cout, r, s, stride, pad_h,
+    y = _empty(n, cout, ho, wo, x.device, x.dtype)
+    rc = K._fn("msb_conv_fwd", x)(_p(x), _p(w_krsc), _p(y), _p(stats), n, h, w_, cin, cout, r, s, stride, pad_h,
                                      pad_w, int(flip), ho, wo, cin, cout, 0, _stream())
     _native.check(rc, "conv_fwd")
     _count()
@@ -90,7 +90,7 @@ def conv_wgrad_raw(x, dy, r, s, stride, pad_h, pad_w):
     n, cin, h, w_ = x.shape
     _, cout, ho, wo = dy.shape
     dw = torch.empty((cout, r, s, cin), dtype=torch.float32, device=x.device)
-    rc = _native.cuda().msb_conv_wgrad(_p(x), _p(dy), _p(dw), n, h, w_, cin, cout, r, s, stride, pad_h, pad_w, ho, wo,
+    rc = K._fn("msb_conv_wgrad", x)(_p(x), _p(dy), _p(dw), n, h, w_, cin, cout, r, s, stride, pad_h, pad_w, ho, wo,
                                        cin, cout, 0, _stream())
     _native.check(rc, "conv_wgrad")
     _count(2)
@@ -100,8 +100,8 @@ def conv_wgrad_raw(x, dy, r, s, stride, pad_h, pad_w):
 def _im2col(x, r, s, stride, pad_h, pad_w, ho, wo):
     n, cin, h, w_ = x.shape
     kpad = (r * s * cin + 63) // 64 * 64
-    col = torch.empty((n * ho * wo, kpad), dtype=torch.bfloat16, device=x.device)
-    rc = _native.cuda().msb_im2col_nhwc(_p(x), _p(col), n, h, w_, cin, r, s, stride, pad_h, pad_w, ho, wo, kpad,
+    col = torch.empty((n * ho * wo, kpad), dtype=x.dtype, device=x.device)
+    rc = K._fn("msb_im2col_nhwc", x)(_p(x), _p(col), n, h, w_, cin, r, s, stride, pad_h, pad_w, ho, wo, kpad,
                                         _stream())
     _native.check(rc, "im2col")
     _count()
@@ -130,12 +130,12 @@ class _ConvFn(torch.autograd.Function):
         ctx.small = cin % 64 != 0
         if ctx.small:
             col, kpad = _im2col(x, r, s, stride, pad_h, pad_w, ho, wo)
-            wmat = torch.zeros((cout, kpad), dtype=torch.bfloat16, device=x.device)
+            wmat = torch.zeros((cout, kpad), dtype=x.dtype, device=x.device)
             wmat[:, :r * s * cin] = wk.reshape(cout, -1)
             y2 = K.gemm(col, wmat)                                       # [pixels, Cout]
             y = y2.view(n, ho, wo, cout).permute(0, 3, 1, 2)
             if want_stats:
-                _native.check(_native.cuda().msb_channel_stats(_p(y2), _p(stats), y2.shape[0], cout, _stream()),
+                _native.check(K._fn("msb_channel_stats", y2)(_p(y2), _p(stats), y2.shape[0], cout, _stream()),
                               "channel_stats")
                 _count()
         else:
@@ -207,7 +207,7 @@ def conv2d(x, w, stride, pads, dilation=(1, 1), bias=None):
         x = torch.nn.functional.pad(x, (left, right, top, bottom))
         return torch.nn.functional.conv2d(x, w, bias, stride, 0, dilation)
     _producer(w)
-    y, _ = _ConvFn.apply(x, w.to(torch.bfloat16) if w.dtype != torch.bfloat16 else w, sh, top, left, False)
+    y, _ = _ConvFn.apply(x, w.to(x.dtype) if w.dtype != x.dtype else w, sh, top, left, False)
     if bias is not None:
         y = y + bias.view(1, -1, 1, 1)
     return y
@@ -237,7 +237,7 @@ class _BnActFn(torch.autograd.Function):
                       "bn_finalize")
         y = torch.empty_like(x, memory_format=CL)
         res = _nhwc(residual) if residual is not None else None
-        _native.check(lib.msb_bn_apply(_p(x), _p(scale), _p(shift), _p(res), _p(y), rows, c, int(relu), _stream()),
+        _native.check(K._fn("msb_bn_apply", x)(_p(x), _p(scale), _p(shift), _p(res), _p(y), rows, c, int(relu), _stream()),
                       "bn_apply")
         _count(2)
         ctx.save_for_backward(x, y, g32, mean, rstd)
@@ -253,12 +253,12 @@ class _BnActFn(torch.autograd.Function):
         dy = _nhwc(dy)
         sums = torch.zeros(2 * c, dtype=torch.float32, device=x.device)
         lib = _native.cuda()
-        _native.check(lib.msb_bn_bwd_reduce(_p(dy), _p(x), _p(y), _p(mean), _p(rstd), _p(sums), rows, c,
+        _native.check(K._fn("msb_bn_bwd_reduce", x)(_p(dy), _p(x), _p(y), _p(mean), _p(rstd), _p(sums), rows, c,
                                             int(ctx.relu), _stream()), "bn_bwd_reduce")
         dx = torch.empty_like(x, memory_format=CL)
         dres = torch.empty_like(x, memory_format=CL) if ctx.has_res else None
         coef = torch.empty(3 * c, dtype=torch.float32, device=x.device)
-        _native.check(lib.msb_bn_bwd_apply(_p(dy), _p(x), _p(y), _p(g32), _p(mean), _p(rstd), _p(sums), _p(coef),
+        _native.check(K._fn("msb_bn_bwd_apply", x)(_p(dy), _p(x), _p(y), _p(g32), _p(mean), _p(rstd), _p(sums), _p(coef),
                                            _p(dx), _p(dres), rows, c, int(ctx.relu), _stream()), "bn_bwd_apply")
         _count(3)
         dgamma, dbeta = sums[c:], sums[:c]
@@ -279,7 +279,7 @@ def conv_bn_act(x, w, gamma, beta, moving_mean, moving_var, stride=1, pad=0, rel
                 momentum=0.9):
     """Training-mode Conv2d -> BatchNorm2d -> (+ residual) -> ReLU on the kernel path.  ``momentum`` is the weight
     of the old moving statistics (nn.BatchNorm2d convention)."""
-    wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+    wb = w if w.dtype == x.dtype else w.to(x.dtype)
     _producer(wb, gamma, beta)
     y, stats = _ConvFn.apply(x, wb, stride, pad, pad, True)
     return _BnActFn.apply(y, stats, gamma, beta, residual, relu, eps, (moving_mean, moving_var, momentum))
@@ -297,7 +297,7 @@ def bn_act_inference(x, gamma, beta, moving_mean, moving_var, relu=True, residua
                                       float(eps), 0, _stream()), "bn_finalize")
     y = torch.empty_like(x, memory_format=CL)
     res = _nhwc(residual) if residual is not None else None
-    _native.check(lib.msb_bn_apply(_p(x), _p(scale), _p(shift), _p(res), _p(y), n * h * w, c, int(relu), _stream()),
+    _native.check(K._fn("msb_bn_apply", x)(_p(x), _p(scale), _p(shift), _p(res), _p(y), n * h * w, c, int(relu), _stream()),
                   "bn_apply")
     _count(2)
     return y
@@ -312,7 +312,7 @@ class _MaxPool3x3s2Fn(torch.autograd.Function):
         ho, wo = (h - 1) // 2 + 1, (w - 1) // 2 + 1
         y = _empty(n, c, ho, wo, x.device)
         idx = torch.empty(n * ho * wo * c, dtype=torch.uint8, device=x.device)
-        _native.check(_native.cuda().msb_maxpool3x3s2(_p(x), None, _p(y), _p(idx), n, h, w, c, 0, _stream()),
+        _native.check(K._fn("msb_maxpool3x3s2", x)(_p(x), None, _p(y), _p(idx), n, h, w, c, 0, _stream()),
                       "maxpool")
         _count()
         ctx.save_for_backward(idx)
@@ -324,7 +324,7 @@ class _MaxPool3x3s2Fn(torch.autograd.Function):
         (idx,) = ctx.saved_tensors
         n, c, h, w = ctx.shape
         dx = _empty(n, c, h, w, dy.device, dy.dtype)
-        _native.check(_native.cuda().msb_maxpool3x3s2(None, _p(_nhwc(dy)), _p(dx), _p(idx), n, h, w, c, 1, _stream()),
+        _native.check(K._fn("msb_maxpool3x3s2", dy)(None, _p(_nhwc(dy)), _p(dx), _p(idx), n, h, w, c, 1, _stream()),
                       "maxpool_bwd")
         _count()
         return dx
@@ -336,7 +336,7 @@ class _GlobalAvgPoolFn(torch.autograd.Function):
         x = _nhwc(x)
         n, c, h, w = x.shape
         y = torch.empty((n, c), dtype=x.dtype, device=x.device)
-        _native.check(_native.cuda().msb_global_avgpool(_p(x), _p(y), n, h * w, c, 0, _stream()), "avgpool")
+        _native.check(K._fn("msb_global_avgpool", x)(_p(x), _p(y), n, h * w, c, 0, _stream()), "avgpool")
         _count()
         ctx.shape = (n, c, h, w)
         return y
@@ -345,7 +345,7 @@ class _GlobalAvgPoolFn(torch.autograd.Function):
     def backward(ctx, dy):
         n, c, h, w = ctx.shape
         dx = _empty(n, c, h, w, dy.device, dy.dtype)
-        _native.check(_native.cuda().msb_global_avgpool(_p(dy.contiguous()), _p(dx), n, h * w, c, 1, _stream()),
+        _native.check(K._fn("msb_global_avgpool", dy)(_p(dy.contiguous()), _p(dx), n, h * w, c, 1, _stream()),
                       "avgpool_bwd")
         _count()
         return dx
@@ -365,7 +365,7 @@ def batch_norm_train(x, gamma, beta, moving_mean, moving_var, keep, eps, relu=Fa
     x = _nhwc(x)
     n, c, h, w = x.shape
     stats = torch.zeros(2 * c, dtype=torch.float32, device=x.device)
-    _native.check(_native.cuda().msb_channel_stats(_p(x), _p(stats), n * h * w, c, _stream()), "channel_stats")
+    _native.check(K._fn("msb_channel_stats", x)(_p(x), _p(stats), n * h * w, c, _stream()), "channel_stats")
     _count()
     mm = moving_mean.detach().as_subclass(torch.Tensor)
     mv = moving_var.detach().as_subclass(torch.Tensor)

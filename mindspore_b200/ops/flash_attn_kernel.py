@@ -5,6 +5,7 @@ import math
 import torch
 
 from .. import _native
+from . import kernels as K
 from .kernels import _count, _p, _stream
 
 _P, _I, _L, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
@@ -26,7 +27,7 @@ def bwd_into(do, q, k, v, o, lse, causal, scale, dq, dk, dv, grad_pitch):
     Hk = k.shape[2]
     do = do.contiguous()
     delta = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
-    rc = _native.cuda().msb_flash_attn_bwd_strided(
+    rc = K._fn("msb_flash_attn_bwd_strided", q)(
         _p(q), _p(k), _p(v), _p(o), _p(do), _p(lse), _p(delta), _p(dq), _p(dk), _p(dv), B, S, H, Hk, D,
         _token_major(q), _token_major(k), _token_major(v), H * D, H * D, grad_pitch, grad_pitch, int(causal),
         float(scale), _stream())
@@ -52,7 +53,7 @@ def _token_major(t):
 
 
 def supports(q, k, v):
-    if not (q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == q.dtype and v.dtype == q.dtype):
+    if not (q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and k.dtype == q.dtype and v.dtype == q.dtype):
         return False
     B, S, H, D = q.shape
     return D == 128 and S % 128 == 0 and k.shape[1] == S and H % k.shape[2] == 0 and k.shape[3] == 128
@@ -73,7 +74,7 @@ def fwd(q, k, v, causal, scale):
         vp = Hk * D
     o = torch.empty((B, S, H, D), dtype=q.dtype, device=q.device)
     lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
-    rc = _native.cuda().msb_flash_attn_fwd(_p(q), _p(k), _p(v), _p(o), _p(lse), B, S, H, Hk, D, qp, kp, vp, H * D,
+    rc = K._fn("msb_flash_attn_fwd", q)(_p(q), _p(k), _p(v), _p(o), _p(lse), B, S, H, Hk, D, qp, kp, vp, H * D,
                                            int(causal), float(scale), _stream())
     _native.check(rc, "flash_attn_fwd")
     _count()
@@ -92,7 +93,7 @@ def bwd(do, q, k, v, o, lse, causal, scale):
     dk = torch.empty((B, S, Hk, D), dtype=q.dtype, device=q.device)
     dv = torch.empty((B, S, Hk, D), dtype=q.dtype, device=q.device)
     delta = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
-    rc = lib.msb_flash_attn_bwd(_p(q), _p(k), _p(v), _p(o), _p(do), _p(lse), _p(delta), _p(dq), _p(dk), _p(dv), B, S, H,
+    rc = K._fn("msb_flash_attn_bwd", q)(_p(q), _p(k), _p(v), _p(o), _p(do), _p(lse), _p(delta), _p(dq), _p(dk), _p(dv), B, S, H,
                                 Hk, D, qp, kp, _token_major(v), H * D, H * D, int(causal), float(scale), _stream())
     _native.check(rc, "flash_attn_bwd")
     _count(3)

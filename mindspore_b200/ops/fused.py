@@ -1,5 +1,5 @@
-"""Autograd-aware hot ops backed by the sm_100a kernels (CUDA bf16) with a PyTorch reference path
-for CPU tensors and other dtypes, so the same model code runs in CPU tests and on the GPU.
+"""Autograd-aware hot ops backed by the sm_100a kernels (CUDA bf16, and fp16 for the GEMM, norm, activation, RoPE and
+attention kernels) with a PyTorch reference path for CPU tensors and other dtypes, so the same model code runs in CPU tests and on the GPU.
 
 Each op is a ``torch.autograd.Function`` whose forward and backward call ``ops.kernels``; weight
 gradients are accumulated straight into ``param.main_grad`` (fp32 arena view) when a parameter
@@ -15,9 +15,16 @@ import torch.nn.functional as F
 from . import kernels as K
 
 
-def _use_kernel(*tensors):
-    return all(t is None or (t.is_cuda and t.dtype == torch.bfloat16) for t in tensors) and \
-        any(t is not None for t in tensors)
+def _use_kernel(*tensors, fp16_ok=False):
+    """All tensors on a GPU and of one 16-bit type the kernels take: bf16 everywhere, fp16 where the op has an fp16
+    build (GEMM, norms, RoPE, SwiGLU, GELU)."""
+    ts = [t for t in tensors if t is not None]
+    if not ts or not all(t.is_cuda for t in ts):
+        return False
+    dt = ts[0].dtype
+    if dt != torch.bfloat16 and not (fp16_ok and dt == torch.float16):
+        return False
+    return all(t.dtype == dt for t in ts)
 
 
 def _plain(t):
@@ -65,7 +72,7 @@ class _LinearFn(torch.autograd.Function):
                 from ..nn.optim import notify_grad_written
                 notify_grad_written(ctx.w_ref)
             else:
-                dw = K.linear_wgrad(dy2, x2, out_dtype=torch.bfloat16)
+                dw = K.linear_wgrad(dy2, x2, out_dtype=dy2.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(dy2.dtype)
         return dx, dw, db
@@ -73,7 +80,7 @@ class _LinearFn(torch.autograd.Function):
 
 def linear(x, w, bias=None):
     """y = x @ w^T + bias with w stored [out, in]."""
-    if _use_kernel(x, w, bias) and x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0:
+    if _use_kernel(x, w, bias, fp16_ok=True) and x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0:
         _producer(w)
         return _LinearFn.apply(x, w, bias)
     return F.linear(x, w, bias)
@@ -109,7 +116,7 @@ class _MatMulFn(torch.autograd.Function):
 
 
 def matmul(a, b, transpose_a=False, transpose_b=False):
-    if _use_kernel(a, b) and a.dim() == b.dim() and a.dim() in (2, 3) and a.is_contiguous() and b.is_contiguous() \
+    if _use_kernel(a, b, fp16_ok=True) and a.dim() == b.dim() and a.dim() in (2, 3) and a.is_contiguous() and b.is_contiguous() \
             and all(s % 8 == 0 for s in a.shape[-2:]) and all(s % 8 == 0 for s in b.shape[-2:]):
         return _MatMulFn.apply(a, b, bool(transpose_a), bool(transpose_b))
     aa = a.transpose(-1, -2) if transpose_a else a
@@ -150,7 +157,7 @@ class _RmsNormFn(torch.autograd.Function):
 def rms_norm(x, w, eps=1e-6, residual=None, with_rstd=False):
     """Returns (y, stream) where stream = x + residual (or x).  y = stream * rsqrt(mean(stream^2)+eps) * w.
     ``with_rstd`` appends the per-row reciprocal RMS (fp32, shape [..., 1])."""
-    if _use_kernel(x, w, residual) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384:
+    if _use_kernel(x, w, residual, fp16_ok=True) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384:
         _producer(w)
         y, stream, rstd = _RmsNormFn.apply(x, w, eps, residual)
         stream = stream if residual is not None else x
@@ -187,7 +194,7 @@ class _LayerNormFn(torch.autograd.Function):
 
 
 def layer_norm(x, w, b, eps=1e-5):
-    if _use_kernel(x, w, b) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384:
+    if _use_kernel(x, w, b, fp16_ok=True) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384:
         _producer(w)
         if b is not None:
             _producer(b)
@@ -210,7 +217,7 @@ class _SwiGLUFn(torch.autograd.Function):
 
 def swiglu(gu):
     """silu(gu[..., :F]) * gu[..., F:]"""
-    if _use_kernel(gu) and gu.is_contiguous() and (gu.shape[-1] // 2) % 8 == 0:
+    if _use_kernel(gu, fp16_ok=True) and gu.is_contiguous() and (gu.shape[-1] // 2) % 8 == 0:
         return _SwiGLUFn.apply(gu)
     f = gu.shape[-1] // 2
     return F.silu(gu[..., :f]) * gu[..., f:]
@@ -234,7 +241,7 @@ class _GeluFn(torch.autograd.Function):
 
 
 def gelu_tanh(x, bias=None):
-    if _use_kernel(x, bias) and x.is_contiguous() and x.shape[-1] % 8 == 0:
+    if _use_kernel(x, bias, fp16_ok=True) and x.is_contiguous() and x.shape[-1] % 8 == 0:
         return _GeluFn.apply(x, bias)
     return F.gelu(x if bias is None else x + bias, approximate="tanh")
 
@@ -266,7 +273,7 @@ def rope_tables(seq, head_dim, theta=10000.0, device="cpu"):
 
 def rope(x, cos, sin, heads, head_dim, seq):
     """Rotate-half RoPE on x[..., seq, heads*head_dim] (token-major); cos/sin fp32 [seq, head_dim/2]."""
-    if _use_kernel(x) and x.is_contiguous() and head_dim % 16 == 0:
+    if _use_kernel(x, fp16_ok=True) and x.is_contiguous() and head_dim % 16 == 0:
         return _RopeFn.apply(x, cos, sin, heads, head_dim, seq)
     shp = x.shape
     xv = x.reshape(-1, seq, heads, head_dim).float()
@@ -391,7 +398,7 @@ def qkv_rope_attention(qkv, cos, sin, batch, seq, heads, kv_heads, head_dim, cau
     from . import flash_attn_kernel as FK
     scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
     hd, kd = heads * head_dim, kv_heads * head_dim
-    if (_use_kernel(qkv) and qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and head_dim == 128
+    if (_use_kernel(qkv, fp16_ok=True) and qkv.is_contiguous() and head_dim == 128
             and seq % 128 == 0 and heads == kv_heads and FK.available() and FK.has_strided_bwd()):
         return _QkvRopeAttnFn.apply(qkv, cos, sin, batch, seq, heads, kv_heads, head_dim, bool(causal), float(scale))
     qk = rope(qkv[:, :hd + kd].contiguous(), cos, sin, heads + kv_heads, head_dim, seq)

@@ -16,7 +16,13 @@ import torch
 from .. import _native
 
 bf16 = torch.bfloat16
+f16 = torch.float16
 f32 = torch.float32
+
+
+def _fn(name, t):
+    """The entry point for t's element type: the fp16 builds of the 16-bit kernels carry the suffix _fp16."""
+    return getattr(_native.cuda(), name + "_fp16" if t.dtype == f16 else name)
 
 
 def _stream():
@@ -35,10 +41,10 @@ def _count(n=1):
 _PAIR_GEMM = os.environ.get("MSB200_GEMM_PAIR", "1") == "1"
 
 
-def _pair_gemm_ok(M, N, K, batch, out, o2, accumulate, bn_hint):
+def _pair_gemm_ok(M, N, K, batch, out, o2, accumulate, bn_hint, dtype=bf16):
     """The CTA-pair kernel (256 x 256 tiles on two SMs) takes un-batched problems whose output meets the TMA
     alignment rules and that fill the machine with 256-wide tiles."""
-    if not _PAIR_GEMM or batch != 1 or bn_hint not in (0, 512):
+    if not _PAIR_GEMM or batch != 1 or bn_hint not in (0, 512) or dtype != bf16:
         return False
     es = out.element_size()
     if out.data_ptr() % 16 or (o2.stride(0) * es) % 16 or (accumulate and out.dtype != f32):
@@ -49,7 +55,7 @@ def _pair_gemm_ok(M, N, K, batch, out, o2, accumulate, bn_hint):
     return M >= 512 and N >= 512 and tiles >= 64
 
 
-def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=bf16, accumulate=False, bias=None,
+def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, accumulate=False, bias=None,
          alpha=1.0, bn_hint=0):
     """``C (+)= alpha * A @ B^T (+ bias)`` on tcgen05 tensor cores.
 
@@ -58,7 +64,10 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=bf16, accumulate=F
     holds logical ``[.., N, K]`` stored ``[.., N, K]`` or ``[.., K, N]``.  Rows must be
     contiguous; row pitch may exceed the row length (views of wider buffers are fine).
     """
-    assert a.dtype == bf16 and b.dtype == bf16, "gemm operands must be bf16"
+    assert a.dtype == b.dtype and a.dtype in (bf16, f16), "gemm operands must both be bf16 or both fp16"
+    assert bias is None or bias.dtype == a.dtype
+    if out_dtype is None:
+        out_dtype = a.dtype
     assert a.dim() == b.dim() and a.dim() in (2, 3)
     batched = a.dim() == 3
     if batched:
@@ -86,15 +95,15 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=bf16, accumulate=F
         out = torch.empty(shape, dtype=out_dtype, device=a.device)
         assert not accumulate
     o2 = out[0] if batched else out
-    assert o2.stride(1) == 1 and o2.shape == (M, N)
-    if _pair_gemm_ok(M, N, K, batch, out, o2, accumulate, bn_hint):
+    assert o2.stride(1) == 1 and o2.shape == (M, N) and out.dtype in (a.dtype, f32)
+    if _pair_gemm_ok(M, N, K, batch, out, o2, accumulate, bn_hint, a.dtype):
         rc = _native.cuda().msb_gemm_bf16_pair(_p(a), _p(b), _p(out), _p(bias), M, N, K, int(a_mn), int(b_mn), lda, ldb,
                                                o2.stride(0), int(out.dtype == f32), int(accumulate), float(alpha), 2,
                                                None, _stream())
         _native.check(rc, "gemm_pair")
         _count()
         return out
-    rc = _native.cuda().msb_gemm_bf16(
+    rc = (_native.cuda().msb_gemm_fp16 if a.dtype == f16 else _native.cuda().msb_gemm_bf16)(
         _p(a), _p(b), _p(out), _p(bias), M, N, K, batch, int(a_mn), int(b_mn), lda, ldb, o2.stride(0),
         abs_, bbs_, out.stride(0) if batched else 0, int(out.dtype == f32), int(accumulate), float(alpha),
         int(bn_hint), _stream())
@@ -143,7 +152,7 @@ def rmsnorm_fwd(x, w, eps, residual=None):
     y = torch.empty_like(x)
     rstd = torch.empty(rows, dtype=f32, device=x.device)
     xsum = torch.empty_like(x) if residual is not None else None
-    rc = _native.cuda().msb_rmsnorm_fwd(_p(x), _p(residual), _p(w), _p(y), _p(xsum), _p(rstd), rows, H, float(eps),
+    rc = _fn("msb_rmsnorm_fwd", x)(_p(x), _p(residual), _p(w), _p(y), _p(xsum), _p(rstd), rows, H, float(eps),
                                         _stream())
     _native.check(rc, "rmsnorm_fwd")
     _count()
@@ -159,7 +168,7 @@ def rmsnorm_bwd(dy, x, w, rstd, dresidual=None, dw_out=None, accumulate=False):
     if dw_out is None:
         dw_out = torch.empty(H, dtype=w.dtype, device=x.device)
         accumulate = False
-    rc = _native.cuda().msb_rmsnorm_bwd(_p(dy), _p(x), _p(w), _p(rstd), _p(dresidual), _p(dx), _p(acc), _p(dw_out),
+    rc = _fn("msb_rmsnorm_bwd", x)(_p(dy), _p(x), _p(w), _p(rstd), _p(dresidual), _p(dx), _p(acc), _p(dw_out),
                                         int(dw_out.dtype == f32), int(accumulate), rows, H, _stream())
     _native.check(rc, "rmsnorm_bwd")
     _count(2)
@@ -172,7 +181,7 @@ def layernorm_fwd(x, w, b, eps):
     y = torch.empty_like(x)
     mean = torch.empty(rows, dtype=f32, device=x.device)
     rstd = torch.empty(rows, dtype=f32, device=x.device)
-    rc = _native.cuda().msb_layernorm_fwd(_p(x), _p(w), _p(b), _p(y), _p(mean), _p(rstd), rows, H, float(eps),
+    rc = _fn("msb_layernorm_fwd", x)(_p(x), _p(w), _p(b), _p(y), _p(mean), _p(rstd), rows, H, float(eps),
                                           _stream())
     _native.check(rc, "layernorm_fwd")
     _count()
@@ -188,7 +197,7 @@ def layernorm_bwd(dy, x, w, mean, rstd, dw_out=None, db_out=None, accumulate=Fal
         dw_out = torch.empty(H, dtype=w.dtype, device=x.device)
         db_out = torch.empty(H, dtype=w.dtype, device=x.device) if has_bias else None
         accumulate = False
-    rc = _native.cuda().msb_layernorm_bwd(_p(dy), _p(x), _p(w), _p(mean), _p(rstd), _p(dx), _p(acc), _p(dw_out),
+    rc = _fn("msb_layernorm_bwd", x)(_p(dy), _p(x), _p(w), _p(mean), _p(rstd), _p(dx), _p(acc), _p(dw_out),
                                           _p(db_out), int(dw_out.dtype == f32), int(accumulate), rows, H, _stream())
     _native.check(rc, "layernorm_bwd")
     _count(3)
@@ -201,7 +210,7 @@ def rope_(x, cos, sin, heads, head_dim, seq, positions=None, backward=False):
     x2 = x.reshape(-1, x.shape[-1]) if x.is_contiguous() else x
     assert x2.dim() == 2 and x2.stride(1) == 1
     tokens = x2.shape[0]
-    rc = _native.cuda().msb_rope(_p(x2), _p(cos), _p(sin), _p(positions), tokens, heads, head_dim, x2.stride(0), seq,
+    rc = _fn("msb_rope", x2)(_p(x2), _p(cos), _p(sin), _p(positions), tokens, heads, head_dim, x2.stride(0), seq,
                                  int(backward), _stream())
     _native.check(rc, "rope")
     _count()
@@ -212,7 +221,7 @@ def swiglu_fwd(gu):
     F = gu.shape[-1] // 2
     rows = gu.numel() // (2 * F)
     out = torch.empty(gu.shape[:-1] + (F,), dtype=gu.dtype, device=gu.device)
-    _native.check(_native.cuda().msb_swiglu_fwd(_p(gu), _p(out), rows, F, _stream()), "swiglu_fwd")
+    _native.check(_fn("msb_swiglu_fwd", gu)(_p(gu), _p(out), rows, F, _stream()), "swiglu_fwd")
     _count()
     return out
 
@@ -221,7 +230,7 @@ def swiglu_bwd(gu, dout):
     F = gu.shape[-1] // 2
     rows = gu.numel() // (2 * F)
     dgu = torch.empty_like(gu)
-    _native.check(_native.cuda().msb_swiglu_bwd(_p(gu), _p(dout), _p(dgu), rows, F, _stream()), "swiglu_bwd")
+    _native.check(_fn("msb_swiglu_bwd", gu)(_p(gu), _p(dout), _p(dgu), rows, F, _stream()), "swiglu_bwd")
     _count()
     return dgu
 
@@ -229,7 +238,7 @@ def swiglu_bwd(gu, dout):
 def gelu_fwd(x, bias=None):
     N = x.shape[-1]
     y = torch.empty_like(x)
-    _native.check(_native.cuda().msb_gelu(_p(x), _p(bias), None, _p(y), x.numel() // N, N, 0, _stream()), "gelu")
+    _native.check(_fn("msb_gelu", x)(_p(x), _p(bias), None, _p(y), x.numel() // N, N, 0, _stream()), "gelu")
     _count()
     return y
 
@@ -237,7 +246,7 @@ def gelu_fwd(x, bias=None):
 def gelu_bwd(x, dy, bias=None):
     N = x.shape[-1]
     dx = torch.empty_like(x)
-    _native.check(_native.cuda().msb_gelu(_p(x), _p(bias), _p(dy), _p(dx), x.numel() // N, N, 1, _stream()), "gelu")
+    _native.check(_fn("msb_gelu", x)(_p(x), _p(bias), _p(dy), _p(dx), x.numel() // N, N, 1, _stream()), "gelu")
     _count()
     return dx
 
