@@ -203,7 +203,8 @@ class _MasterAdamW:
             for m, p in zip(masters, grp):
                 m.grad = p.grad.float() * scale
             opt.step()
-            torch._foreach_copy_(grp, masters)
+            with torch.no_grad():
+                torch._foreach_copy_(grp, masters)
             for m, p in zip(masters, grp):
                 m.grad = None
                 p.grad.zero_()

@@ -477,8 +477,7 @@ MSB_EXPORT int MSB_FN(msb_rmsnorm_fwd)(const void* x, const void* res, const voi
   return kOk;
 }
 
-// dw_acc: fp32 [H] scratch that this call zeroes, accumulates into and leaves holding sum_rows dy*xhat.
-// dw_out (bf16 or fp32 by dw_fp32) receives (accumulate ? dw_out + dw_acc : dw_acc).
+// dw_out (bf16 or fp32 by dw_fp32) receives (accumulate ? dw_out + dw : dw), dw = sum_rows dy * xhat.
 // Floats of scratch the norm backward launchers need for hidden size H: one partial row per CTA.
 #ifndef MSB_ELEM_FP16
 MSB_EXPORT long long msb_norm_bwd_scratch_elems(int H, int with_bias) {

@@ -1,0 +1,690 @@
+"""MindIR in the reference's protobuf wire format (``mind_ir.proto``: ModelProto / GraphProto / NodeProto /
+PrimitiveProto / AttributeProto / TensorProto), so that graph files travel between the two frameworks.
+
+Writer: ``save_model_proto(fg, path)`` stores a traced forward graph the way the reference's exporter lays one out
+(ccsrc/common/debug/mindir_exporter.cc):
+
+* weights are ``GraphProto.parameter`` tensors (name, dims, data_type, raw little-endian bytes), network inputs are
+  ``GraphProto.input`` value infos;
+* every primitive call is a ``NodeProto`` whose ``op_type`` is ``REF::<Prim>:<id>`` and names an entry of
+  ``ModelProto.primitives`` carrying the primitive's attributes; node outputs are named ``<graph>:<n>``;
+* values that are not nodes (scalars, tuples, dtypes, small tensors) become ``Constant`` nodes with one attribute
+  ``value``; tuple indexing is the primitive ``TupleGetItem``, a tuple result ``MakeTuple``;
+* attribute values carry their ``AttributeType``: INT64 / BOOL in ``i``, FLOAT in ``f``, DOUBLE in ``d``, STRING in
+  ``s``, TUPLE / LIST in ``values``, a tensor or a dtype as one ``tensors`` entry (TENSORS), None as NONE.
+
+Reader: ``load_model_proto(bytes)`` accepts that layout and the older one in which a node's ``op_type`` is the
+primitive name itself and the attributes sit on the node (core/load_mindir/load_model.cc:1770-1780 distinguishes the
+two by the ``REF::`` prefix).  Primitives are looked up by name in ``mindspore_b200.ops``; an operator this build does
+not define is reported by name.  Sub-graphs (``functions``), closures and monads are outside this reader.
+
+The message classes are built at import time from a description of the schema (field names, numbers and types are
+the file format), so no generated ``_pb2`` module and no ``protoc`` are needed."""
+from __future__ import annotations
+
+import inspect
+import operator
+
+import numpy as np
+import torch
+
+from .ir import FuncGraph
+from .mindir import LoadedGraph, MindIRError
+
+# ---------------------------------------------------------------------------------------------------- schema
+_OPT, _REP, _REQ = 1, 3, 2
+_T = {"string": 9, "bytes": 12, "int64": 3, "int32": 5, "uint64": 4, "float": 2, "double": 1, "bool": 8, "msg": 11,
+      "enum": 5}        # enums travel as int32 here: unknown values of a newer writer must not fail the parse
+
+_SCHEMA = {
+    "AttributeProto": [
+        ("name", 1, "string"), ("f", 2, "float"), ("i", 3, "int64"), ("d", 4, "double"), ("s", 5, "bytes"),
+        ("t", 6, "TensorProto"), ("g", 7, "GraphProto"), ("floats", 8, "float*"), ("doubles", 9, "double*"),
+        ("ints", 10, "int64*"), ("strings", 11, "bytes*"), ("tensors", 12, "TensorProto*"),
+        ("graphs", 13, "GraphProto*"), ("doc_string", 14, "string"), ("ref_attr_name", 15, "string"),
+        ("type", 16, "enum"), ("values", 17, "AttributeProto*")],
+    "ValueInfoProto": [
+        ("name", 1, "string"), ("tensor", 2, "TensorProto*"), ("doc_string", 3, "string"),
+        ("denotation", 4, "string"), ("attr_info", 5, "AttributeProto")],
+    "NodeProto": [
+        ("input", 1, "string*"), ("output", 2, "string*"), ("name", 3, "string"), ("op_type", 4, "string"),
+        ("attribute", 5, "AttributeProto*"), ("doc_string", 6, "string"), ("domain", 7, "string"),
+        ("node_attr", 8, "AttributeProto*"), ("primal_attr", 9, "AttributeProto*")],
+    "ModelProto": [
+        ("ir_version", 1, "string"), ("producer_name", 2, "string"), ("producer_version", 3, "string"),
+        ("domain", 4, "string"), ("model_version", 5, "string"), ("doc_string", 6, "string"),
+        ("graph", 7, "GraphProto"), ("functions", 8, "GraphProto*"), ("little_endian", 10, "bool"),
+        ("parallel", 11, "ParallelProto"), ("primitives", 12, "PrimitiveProto*"), ("mind_ir_version", 13, "int64")],
+    "GraphProto": [
+        ("node", 1, "NodeProto*"), ("name", 2, "string"), ("parameter", 3, "TensorProto*"),
+        ("doc_string", 4, "string"), ("input", 5, "ValueInfoProto*"), ("output", 6, "ValueInfoProto*"),
+        ("bprop_hash", 7, "string"), ("attribute", 8, "AttributeProto*"), ("bprop_filepath", 9, "string")],
+    "TensorProto": [
+        ("dims", 1, "int64*"), ("data_type", 2, "int32"), ("float_data", 3, "float*"), ("int32_data", 4, "int32*"),
+        ("string_data", 5, "bytes*"), ("int64_data", 6, "int64*"), ("name", 7, "string"), ("doc_string", 8, "string"),
+        ("raw_data", 9, "bytes"), ("double_data", 10, "double*"), ("uint64_data", 11, "uint64*"),
+        ("ref_key", 13, "string"), ("min_dims", 14, "int64*"), ("max_dims", 15, "int64*"),
+        ("compression_type", 16, "enum")],
+    "ParallelProto": [("layout", 1, "LayoutProto*")],
+    "LayoutProto": [
+        ("name", 1, "string"), ("device_arrangement_int", 2, "int64*"), ("tensor_map_int", 3, "int64*"),
+        ("slice_shape_int", 4, "int64*"), ("field_size", 5, "int64"), ("uniform_split", 6, "bool"),
+        ("opt_shard_group", 7, "string")],
+    "PrimitiveProto": [
+        ("name", 1, "string"), ("op_type", 2, "string"), ("attribute", 3, "AttributeProto*"),
+        ("instance_name", 4, "string"), ("prim_type", 5, "enum")],
+}
+
+_messages = None
+
+
+def messages():
+    """{message name: class} built from ``_SCHEMA`` (package ``mind_ir``)."""
+    global _messages
+    if _messages is not None:
+        return _messages
+    from google.protobuf import descriptor_pb2, descriptor_pool, message_factory
+    fdp = descriptor_pb2.FileDescriptorProto()
+    fdp.name = "mindspore_b200/mind_ir.proto"
+    fdp.package = "mind_ir"
+    fdp.syntax = "proto2"
+    for mname, fields in _SCHEMA.items():
+        m = fdp.message_type.add()
+        m.name = mname
+        for fname, number, kind in fields:
+            f = m.field.add()
+            f.name, f.number = fname, number
+            rep = kind.endswith("*")
+            kind = kind.rstrip("*")
+            f.label = _REP if rep else _OPT
+            if kind in _T:
+                f.type = _T[kind]
+            else:
+                f.type = _T["msg"]
+                f.type_name = ".mind_ir." + kind
+    pool = descriptor_pool.DescriptorPool()
+    fd = pool.Add(fdp) if hasattr(pool, "Add") and not hasattr(pool, "AddSerializedFile") else \
+        pool.AddSerializedFile(fdp.SerializeToString())
+    get = getattr(message_factory, "GetMessageClass", None)
+    out = {}
+    for mname in _SCHEMA:
+        desc = pool.FindMessageTypeByName("mind_ir." + mname)
+        out[mname] = get(desc) if get else message_factory.MessageFactory(pool).GetPrototype(desc)
+    _messages = out
+    return out
+
+
+# AttributeProto.AttributeType / TensorProto.DataType values used here
+A_FLOAT, A_INT8, A_INT16, A_INT32, A_INT64, A_STRING, A_BOOL, A_DOUBLE = 1, 3, 5, 6, 7, 8, 9, 11
+A_UINT8, A_UINT16, A_UINT32, A_UINT64 = 2, 4, 12, 13
+A_TENSOR, A_TENSORS, A_TUPLE, A_LIST, A_DICT, A_UMONAD, A_IOMONAD, A_NONE = 17, 19, 20, 21, 22, 23, 24, 25
+_INT_ATTR = (A_INT8, A_INT16, A_INT32, A_INT64, A_UINT8, A_UINT16, A_UINT32, A_UINT64)
+
+_DT = {torch.float32: 1, torch.uint8: 2, torch.int8: 3, torch.int16: 5, torch.int32: 6, torch.int64: 7, torch.bool: 9,
+       torch.float16: 10, torch.float64: 11, torch.complex64: 14, torch.complex128: 15, torch.bfloat16: 16}
+_DT_REV = {v: k for k, v in _DT.items()}
+_DT_REV[17] = torch.float64          # FLOAT64 is a second code for double
+_DT_REV[4] = torch.int32             # uint16 / uint32 / uint64 have no torch counterpart everywhere: widened on load
+_DT_REV[12] = torch.int64
+_DT_REV[13] = torch.int64
+_DT_NP = {4: np.uint16, 12: np.uint32, 13: np.uint64}
+
+_BUILTIN_PRIMS = {operator.add: "Add", operator.sub: "Sub", operator.mul: "Mul", operator.truediv: "RealDiv",
+                  operator.neg: "Neg", operator.matmul: "MatMul", operator.pow: "Pow"}
+
+
+# ---------------------------------------------------------------------------------------------------- tensors
+def _fill_tensor(tp, t, name=None):
+    plain = t.detach().to("cpu").contiguous()
+    if plain.dtype not in _DT:
+        raise MindIRError("tensors of type %s have no MindIR data type" % plain.dtype)
+    if name is not None:
+        tp.name = name
+    tp.data_type = _DT[plain.dtype]
+    tp.dims.extend(int(d) for d in plain.shape)
+    tp.raw_data = plain.view(torch.uint8).numpy().tobytes() if plain.dtype == torch.bfloat16 \
+        else plain.numpy().tobytes()
+
+
+def _read_tensor(tp):
+    code = tp.data_type
+    if code not in _DT_REV:
+        raise MindIRError("tensor %r has MindIR data type %d, which is not supported" % (tp.name, code))
+    dt = _DT_REV[code]
+    shape = [int(d) for d in tp.dims]
+    n = int(np.prod(shape)) if shape else 1
+    if tp.raw_data:
+        raw = bytearray(tp.raw_data)
+        if code in _DT_NP:
+            return torch.from_numpy(np.frombuffer(raw, dtype=_DT_NP[code]).astype(np.int64)).to(dt).reshape(shape)
+        if dt == torch.bfloat16:
+            return torch.frombuffer(raw, dtype=torch.uint8).view(torch.bfloat16).reshape(shape).clone()
+        return torch.frombuffer(raw, dtype=dt).reshape(shape).clone()
+    for field in ("float_data", "int32_data", "int64_data", "double_data", "uint64_data"):
+        vals = list(getattr(tp, field))
+        if vals:
+            return torch.tensor(vals).to(dt).reshape(shape)
+    if n == 0:
+        return torch.empty(shape, dtype=dt)
+    return None                                   # a type-only tensor (no data): the caller decides what it means
+
+
+# ---------------------------------------------------------------------------------------------------- attributes
+def _fill_attr(ap, v):
+    """Python value -> AttributeProto (type tag + payload)."""
+    if v is None:
+        ap.type = A_NONE
+    elif isinstance(v, (bool, np.bool_)):
+        ap.type, ap.i = A_BOOL, int(bool(v))
+    elif isinstance(v, (int, np.integer)):
+        ap.type, ap.i = A_INT64, int(v)
+    elif isinstance(v, (float, np.floating)):
+        f32 = float(np.float32(v))
+        if f32 == float(v) or v != v:
+            ap.type, ap.f = A_FLOAT, float(v)
+        else:
+            ap.type, ap.d = A_DOUBLE, float(v)
+    elif isinstance(v, str):
+        ap.type, ap.s = A_STRING, v.encode()
+    elif isinstance(v, (tuple, list, torch.Size)):
+        ap.type = A_LIST if isinstance(v, list) else A_TUPLE
+        for item in v:
+            _fill_attr(ap.values.add(), item)
+    elif isinstance(v, dict):
+        ap.type = A_DICT
+        for k, item in v.items():
+            sub = ap.values.add()
+            sub.name = str(k)
+            _fill_attr(sub, item)
+    elif isinstance(v, torch.dtype):
+        ap.type = A_TENSORS                       # a type value: one tensor entry that carries only a data type
+        tp = ap.tensors.add()
+        tp.name = "value0"
+        if v not in _DT:
+            raise MindIRError("dtype %s has no MindIR data type" % v)
+        tp.data_type = _DT[v]
+    elif isinstance(v, torch.Tensor):
+        ap.type = A_TENSORS
+        _fill_tensor(ap.tensors.add(), v, "value0")
+    elif isinstance(v, np.ndarray):
+        ap.type = A_TENSORS
+        _fill_tensor(ap.tensors.add(), torch.from_numpy(np.ascontiguousarray(v)), "value0")
+    else:
+        raise MindIRError("value of type %s cannot be stored as a MindIR attribute" % type(v).__name__)
+
+
+def _read_attr(ap):
+    t = ap.type
+    if t == A_NONE:
+        return None
+    if t == A_BOOL:
+        return bool(ap.i)
+    if t in _INT_ATTR:
+        return int(ap.i)
+    if t == A_FLOAT:
+        return float(ap.f)
+    if t == A_DOUBLE:
+        return float(ap.d)
+    if t == A_STRING:
+        return ap.s.decode()
+    if t in (A_TUPLE, A_LIST):
+        vals = [_read_attr(x) for x in ap.values]
+        return vals if t == A_LIST else tuple(vals)
+    if t == A_DICT:
+        return {x.name: _read_attr(x) for x in ap.values}
+    if t in (A_TENSORS, A_TENSOR):
+        tps = list(ap.tensors) if t == A_TENSORS else [ap.t]
+        out = []
+        for tp in tps:
+            ten = _read_tensor(tp)
+            out.append(ten if ten is not None else _DT_REV[tp.data_type])
+        return out[0] if len(out) == 1 else tuple(out)
+    if t in (A_UMONAD, A_IOMONAD):
+        return _MONAD
+    if t == 0:                                    # older writers: untyped, the payload field says what it is
+        if ap.ints:
+            return tuple(int(x) for x in ap.ints)
+        if ap.floats:
+            return tuple(float(x) for x in ap.floats)
+        if ap.strings:
+            return tuple(s.decode() for s in ap.strings)
+        if ap.tensors:
+            tens = [_read_tensor(tp) for tp in ap.tensors]
+            return tens[0] if len(tens) == 1 else tuple(tens)
+        for field, conv in (("s", lambda s: s.decode()), ("i", int), ("f", float), ("d", float)):
+            if ap.HasField(field):
+                return conv(getattr(ap, field))
+        return None
+    raise MindIRError("attribute %r has type %d, which this reader does not handle" % (ap.name, t))
+
+
+class _Monad:
+    def __repr__(self):
+        return "U"
+
+
+_MONAD = _Monad()
+
+
+# ---------------------------------------------------------------------------------------------------- lowering
+def _pair(v):
+    return (int(v), int(v)) if isinstance(v, int) else tuple(int(x) for x in v)
+
+
+def _lowerings():
+    """{torch function: rule}.  A rule receives (emit, args, kwargs, node) and returns the name of its result;
+    ``emit(primitive name, attributes, inputs)`` writes one primitive node.  Layers of ``nn`` call these torch
+    functions directly, so a traced network is a mix of primitives and of them; the rules restate each call with the
+    primitives a MindIR consumer knows."""
+    import torch.nn.functional as F
+
+    def arg(args, kwargs, i, name, default=None):
+        if len(args) > i:
+            return args[i]
+        return kwargs.get(name, default)
+
+    def conv2d(emit, a, k, n):
+        x, w, b = a[0], a[1], arg(a, k, 2, "bias")
+        stride, pad = _pair(arg(a, k, 3, "stride", 1)), arg(a, k, 4, "padding", 0)
+        dil, groups = _pair(arg(a, k, 5, "dilation", 1)), int(arg(a, k, 6, "groups", 1))
+        wshape = tuple(w.meta["shape"])
+        if isinstance(pad, str):
+            raise MindIRError("string padding of conv2d is not lowered")
+        ph, pw = _pair(pad)
+        attrs = {"out_channel": int(wshape[0]), "kernel_size": (int(wshape[2]), int(wshape[3])), "mode": 1,
+                 "pad_mode": "pad" if (ph or pw) else "valid", "pad": (ph, ph, pw, pw),
+                 "stride": (1, 1) + stride, "dilation": (1, 1) + dil, "group": groups, "format": "NCHW"}
+        y = emit("Conv2D", attrs, [x, w])
+        return emit("BiasAdd", {"format": "NCHW"}, [_Ref(y), b]) if b is not None else y
+
+    def linear(emit, a, k, n):
+        x, w, b = a[0], a[1], arg(a, k, 2, "bias")
+        rank = len(x.meta.get("shape", (0, 0)))
+        if rank != 2:
+            shp = tuple(int(d) for d in x.meta["shape"])
+            x2 = emit("Reshape", {}, [x, (-1, shp[-1])])
+            y = emit("MatMul", {"transpose_a": False, "transpose_b": True}, [_Ref(x2), w])
+            if b is not None:
+                y = emit("BiasAdd", {"format": "NCHW"}, [_Ref(y), b])
+            return emit("Reshape", {}, [_Ref(y), shp[:-1] + (int(w.meta["shape"][0]),)])
+        y = emit("MatMul", {"transpose_a": False, "transpose_b": True}, [x, w])
+        return emit("BiasAdd", {"format": "NCHW"}, [_Ref(y), b]) if b is not None else y
+
+    def pool(name):
+        def rule(emit, a, k, n):
+            ks = _pair(arg(a, k, 1, "kernel_size"))
+            st = arg(a, k, 2, "stride")
+            st = ks if st in (None, ()) else _pair(st)
+            if _pair(arg(a, k, 3, "padding", 0)) != (0, 0) or arg(a, k, 5 if name == "MaxPool" else 4, "ceil_mode", False):
+                raise MindIRError("padded / ceil-mode pooling is not lowered")
+            return emit(name, {"kernel_size": (1, 1) + ks, "strides": (1, 1) + st, "pad_mode": "VALID",
+                               "format": "NCHW"}, [a[0]])
+        return rule
+
+    def unary(name, **attrs):
+        return lambda emit, a, k, n: emit(name, dict(attrs), [a[0]])
+
+    def binary(name):
+        def rule(emit, a, k, n):
+            if k.get("alpha", 1) != 1:
+                raise MindIRError("alpha of torch.add / torch.sub is not lowered")
+            return emit(name, {}, [a[0], a[1]])
+        return rule
+
+    def softmax(name):
+        def rule(emit, a, k, n):
+            return emit(name, {"axis": int(arg(a, k, 1, "dim", -1))}, [a[0]])
+        return rule
+
+    def flatten(emit, a, k, n):
+        start, end = int(arg(a, k, 1, "start_dim", 0)), int(arg(a, k, 2, "end_dim", -1))
+        shp = tuple(int(d) for d in a[0].meta["shape"])
+        if start == 1 and end in (-1, len(shp) - 1):
+            return emit("Flatten", {}, [a[0]])
+        end = end % len(shp)
+        mid = 1
+        for d in shp[start:end + 1]:
+            mid *= d
+        return emit("Reshape", {}, [a[0], shp[:start] + (mid,) + shp[end + 1:]])
+
+    def layer_norm(emit, a, k, n):
+        x, nshape = a[0], tuple(arg(a, k, 1, "normalized_shape"))
+        w, b, eps = arg(a, k, 2, "weight"), arg(a, k, 3, "bias"), float(arg(a, k, 4, "eps", 1e-5))
+        if w is None or b is None:
+            raise MindIRError("layer_norm without affine parameters is not lowered")
+        axis = len(x.meta["shape"]) - len(nshape)
+        y = emit("LayerNorm", {"begin_norm_axis": axis, "begin_params_axis": axis, "epsilon": eps}, [x, w, b])
+        return emit("TupleGetItem", {}, [_Ref(y), 0])
+
+    def batch_norm(emit, a, k, n):
+        x, mean, var = a[0], arg(a, k, 1, "running_mean"), arg(a, k, 2, "running_var")
+        w, b = arg(a, k, 3, "weight"), arg(a, k, 4, "bias")
+        if arg(a, k, 5, "training", False) or mean is None or w is None:
+            raise MindIRError("only inference-mode batch_norm with affine parameters is lowered")
+        y = emit("BatchNorm", {"is_training": False, "epsilon": float(arg(a, k, 7, "eps", 1e-5)), "momentum": 0.1,
+                               "format": "NCHW"}, [x, w, b, mean, var])
+        return emit("TupleGetItem", {}, [_Ref(y), 0])
+
+    def reshape(emit, a, k, n):
+        shape = a[1] if len(a) == 2 and isinstance(a[1], (tuple, list, torch.Size)) else tuple(a[1:])
+        return emit("Reshape", {}, [a[0], tuple(int(d) for d in shape)])
+
+    def permute(emit, a, k, n):
+        perm = a[1] if len(a) == 2 and isinstance(a[1], (tuple, list)) else tuple(a[1:])
+        return emit("Transpose", {}, [a[0], tuple(int(d) for d in perm)])
+
+    def transpose(emit, a, k, n):
+        rank = len(a[0].meta["shape"])
+        perm = list(range(rank))
+        d0, d1 = int(a[1]) % rank, int(a[2]) % rank
+        perm[d0], perm[d1] = perm[d1], perm[d0]
+        return emit("Transpose", {}, [a[0], tuple(perm)])
+
+    def matmul(emit, a, k, n):
+        rank = len(a[0].meta.get("shape", (0, 0)))
+        return emit("MatMul" if rank == 2 else "BatchMatMul", {"transpose_a": False, "transpose_b": False},
+                    [a[0], a[1]])
+
+    def dropout(emit, a, k, n):
+        if arg(a, k, 2, "training", True):
+            raise MindIRError("training-mode dropout is not lowered")
+        return emit("Identity", {}, [a[0]])
+
+    def gelu(emit, a, k, n):
+        return emit("GeLU", {}, [a[0]])
+
+    def cat(emit, a, k, n):
+        xs = list(a[0])
+        t = emit("MakeTuple", {}, xs)
+        return emit("Concat", {"axis": int(arg(a, k, 1, "dim", 0))}, [_Ref(t)])
+
+    def reduce(name):
+        def rule(emit, a, k, n):
+            dim = arg(a, k, 1, "dim", ())
+            dim = (int(dim),) if isinstance(dim, int) else tuple(int(d) for d in (dim or ()))
+            return emit(name, {"keep_dims": bool(arg(a, k, 2, "keepdim", False))}, [a[0], dim])
+        return rule
+
+    def embedding(emit, a, k, n):
+        return emit("Gather", {"batch_dims": 0}, [a[1], a[0], 0])
+
+    T = torch.Tensor
+    table = {
+        torch.conv2d: conv2d, F.conv2d: conv2d, F.linear: linear, torch._C._nn.linear: linear,
+        F.max_pool2d: pool("MaxPool"), F.avg_pool2d: pool("AvgPool"), torch._C._nn.avg_pool2d: pool("AvgPool"),
+        torch.relu: unary("ReLU"), F.relu: unary("ReLU"), T.relu: unary("ReLU"),
+        torch.sigmoid: unary("Sigmoid"), T.sigmoid: unary("Sigmoid"), torch.tanh: unary("Tanh"), T.tanh: unary("Tanh"),
+        F.silu: unary("SiLU"), F.gelu: gelu, torch.exp: unary("Exp"), torch.sqrt: unary("Sqrt"),
+        torch.neg: unary("Neg"), T.neg: unary("Neg"),
+        torch.add: binary("Add"), T.add: binary("Add"), torch.sub: binary("Sub"), T.sub: binary("Sub"),
+        torch.mul: binary("Mul"), T.mul: binary("Mul"), torch.div: binary("RealDiv"), T.div: binary("RealDiv"),
+        torch.true_divide: binary("RealDiv"), torch.pow: binary("Pow"), T.pow: binary("Pow"),
+        T.__add__: binary("Add"), T.__sub__: binary("Sub"), T.__mul__: binary("Mul"), T.__truediv__: binary("RealDiv"),
+        T.__radd__: binary("Add"), T.__rmul__: binary("Mul"),
+        torch.softmax: softmax("Softmax"), F.softmax: softmax("Softmax"), T.softmax: softmax("Softmax"),
+        torch.log_softmax: softmax("LogSoftmax"), F.log_softmax: softmax("LogSoftmax"),
+        torch.flatten: flatten, T.flatten: flatten, F.layer_norm: layer_norm, torch.layer_norm: layer_norm,
+        F.batch_norm: batch_norm, torch.batch_norm: batch_norm,
+        torch.reshape: reshape, T.reshape: reshape, T.view: reshape, torch.permute: permute, T.permute: permute,
+        torch.transpose: transpose, T.transpose: transpose, torch.matmul: matmul, T.matmul: matmul,
+        torch.bmm: matmul, torch.mm: matmul, F.dropout: dropout, torch.dropout: dropout, torch.cat: cat,
+        torch.mean: reduce("ReduceMean"), T.mean: reduce("ReduceMean"), torch.sum: reduce("ReduceSum"),
+        T.sum: reduce("ReduceSum"), F.embedding: embedding, torch.embedding: embedding,
+    }
+    return table
+
+
+class _Ref:
+    """The result of a node that this export has just written (by its MindIR name)."""
+
+    def __init__(self, name):
+        self.name = name
+
+
+_LOWER = None
+
+
+# ---------------------------------------------------------------------------------------------------- writer
+def build_model_proto(fg, producer_version="2.4.0"):
+    import torch.fx as fx
+    from . import autodiff
+    M = messages()
+    model = M["ModelProto"]()
+    model.ir_version = "0.1.1"
+    model.producer_name = "MindSpore"
+    model.producer_version = producer_version
+    model.model_version = "1"
+    model.little_endian = True
+    model.mind_ir_version = 2
+    gp = model.graph
+    gname = fg.name or "graph"
+    gp.name = gname
+    counter = [0]
+    names = {}
+
+    def fresh():
+        counter[0] += 1
+        return "%s:%d" % (gname, counter[0])
+
+    def constant(value):
+        node = gp.node.add()
+        node.name = fresh()
+        node.output.append(node.name)
+        node.op_type = "Constant"
+        ap = node.attribute.add()
+        ap.name = "value"
+        _fill_attr(ap, value)
+        return node.name
+
+    def operand(a):
+        if isinstance(a, fx.Node):
+            return names[a]
+        if isinstance(a, _Ref):
+            return a.name
+        return constant(a)
+
+    def call(prim_name, attrs, inputs, scope=""):
+        pp = model.primitives.add()
+        pp.name = "%s:%d" % (prim_name, len(model.primitives))
+        pp.op_type = prim_name
+        pp.prim_type = 1
+        for k, v in attrs.items():
+            ap = pp.attribute.add()
+            ap.name = k
+            try:
+                _fill_attr(ap, v)
+            except MindIRError:
+                del pp.attribute[-1]              # callables and the like are not part of a primitive's record
+        ins = [operand(a) for a in inputs]        # constants are written before the node that reads them
+        node = gp.node.add()
+        node.name = fresh()
+        node.output.append(node.name)
+        node.op_type = "REF::" + pp.name
+        node.domain = scope
+        node.input.extend(ins)
+        return node.name
+
+    for n in fg.graph.nodes:
+        if n.op == "placeholder":
+            vi = gp.input.add()
+            vi.name = n.name
+            names[n] = n.name
+            if "shape" in n.meta and "dtype" in n.meta and n.meta["dtype"] in _DT:
+                tp = vi.tensor.add()
+                tp.dims.extend(int(d) for d in n.meta["shape"])
+                tp.data_type = _DT[n.meta["dtype"]]
+        elif n.op == "get_attr":
+            if "param" in n.meta:
+                pname = n.target.split("::", 1)[1]
+                _fill_tensor(gp.parameter.add(), n.meta["param"], pname)
+                names[n] = pname
+            else:
+                names[n] = constant(n.meta["const"])
+        elif n.op == "call_function":
+            if n.target is autodiff.vjp:
+                raise MindIRError("only forward graphs can be exported (found a gradient node)")
+            is_prim = hasattr(n.target, "name") and hasattr(n.target, "attrs")
+            if n.kwargs and (is_prim or n.target in _BUILTIN_PRIMS or n.target is operator.getitem):
+                raise MindIRError("node %s passes keyword arguments, which MindIR nodes cannot carry" % n.name)
+            if n.target is operator.getitem:
+                if not isinstance(n.args[1], int):
+                    raise MindIRError("node %s slices a tensor; only tuple indexing is stored" % n.name)
+                names[n] = call("TupleGetItem", {}, [n.args[0], int(n.args[1])])
+            elif n.target in _BUILTIN_PRIMS:
+                names[n] = call(_BUILTIN_PRIMS[n.target], {}, list(n.args))
+            elif hasattr(n.target, "name") and hasattr(n.target, "attrs"):
+                attrs = dict(n.target.attrs)
+                if getattr(n.target, "in_strategy", None) is not None:
+                    attrs["in_strategy"] = n.target.in_strategy
+                if getattr(n.target, "out_strategy", None) is not None:
+                    attrs["out_strategy"] = n.target.out_strategy
+                names[n] = call(n.target.name, attrs, list(n.args), str(n.meta.get("scope", "")))
+            else:
+                global _LOWER
+                if _LOWER is None:
+                    _LOWER = _lowerings()
+                rule = _LOWER.get(n.target)
+                if rule is None:
+                    raise MindIRError("node %s calls %r, which is neither a primitive nor a function with a "
+                                      "lowering to primitives" % (n.name, n.target))
+                names[n] = rule(call, tuple(n.args), dict(n.kwargs), n)
+        elif n.op == "output":
+            res = n.args[0]
+            if isinstance(res, (tuple, list)):
+                out_name = call("MakeTuple", {}, list(res))
+            else:
+                out_name = operand(res)
+            gp.output.add().name = out_name
+        else:
+            raise MindIRError("node kind %s is not supported in graph files" % n.op)
+    return model
+
+
+def save_model_proto(fg, path):
+    data = build_model_proto(fg).SerializeToString()
+    with open(path, "wb") as f:
+        f.write(data)
+    return path
+
+
+# ---------------------------------------------------------------------------------------------------- reader
+def looks_like_model_proto(data):
+    """A ModelProto starts with field 1 (ir_version, a short string): tag 0x0A."""
+    return len(data) > 2 and data[0] == 0x0A and data[1] < 32
+
+
+def _make_primitive(op_type, attrs):
+    from .. import ops
+    cls = getattr(ops, op_type, None)
+    if cls is None or not inspect.isclass(cls):
+        raise MindIRError("the graph uses operator %s, which this build does not define" % op_type)
+    init = getattr(cls.__init__, "decorated_func", cls.__init__)
+    params = [p for p in list(inspect.signature(init).parameters.values())[1:]
+              if p.kind in (p.POSITIONAL_OR_KEYWORD, p.KEYWORD_ONLY)]
+    kwargs = {p.name: attrs[p.name] for p in params if p.name in attrs}
+    prim = cls(**kwargs)
+    for k, v in attrs.items():
+        if k in ("in_strategy", "out_strategy") or k in kwargs:
+            continue
+        if hasattr(prim, "add_prim_attr"):
+            try:
+                prim.add_prim_attr(k, v)
+            except Exception:  # noqa: BLE001  (bookkeeping attributes of the writer: not needed to run)
+                pass
+    if attrs.get("in_strategy") is not None and hasattr(prim, "shard"):
+        prim.shard(attrs["in_strategy"], attrs.get("out_strategy"))
+    return prim
+
+
+def _make_tuple(*items):
+    return tuple(items)
+
+
+def load_model_proto(data):
+    from ..common.parameter import Parameter
+    from ..common.tensor import Tensor
+    M = messages()
+    model = M["ModelProto"]()
+    try:
+        model.ParseFromString(bytes(data))
+    except Exception as e:  # noqa: BLE001
+        raise MindIRError("not a MindIR protobuf file: %s" % e)
+    if model.functions:
+        raise MindIRError("the file holds %d sub-graphs (control flow / closures); this reader takes single-graph "
+                          "models" % len(model.functions))
+    gp = model.graph
+    prims = {p.name: p for p in model.primitives}
+    fg = FuncGraph(gp.name or "graph")
+    g = fg.graph
+    env = {}
+    param_names = {tp.name for tp in gp.parameter}
+    n_in = 0
+    for vi in gp.input:
+        if vi.name in param_names:
+            continue                              # older writers list the weights among the inputs too
+        node = g.placeholder("x%d" % n_in if not vi.name.isidentifier() else vi.name)
+        if vi.tensor:
+            node.meta["shape"] = tuple(int(d) for d in vi.tensor[0].dims)
+            if vi.tensor[0].data_type in _DT_REV:
+                node.meta["dtype"] = _DT_REV[vi.tensor[0].data_type]
+        env[vi.name] = node
+        n_in += 1
+    for tp in gp.parameter:
+        ten = _read_tensor(tp)
+        if ten is None:
+            raise MindIRError("parameter %r has no data (stored outside the file?)" % tp.name)
+        p = Parameter(Tensor(ten), name=tp.name, requires_grad=ten.is_floating_point())
+        node = g.create_node("get_attr", "param::" + tp.name)
+        node.meta["param"] = p
+        fg.params[tp.name] = p
+        env[tp.name] = node
+
+    def value_of(name):
+        if name not in env:
+            raise MindIRError("node input %r is not defined before its use" % name)
+        return env[name]
+
+    for nd in gp.node:
+        out_name = nd.output[0] if nd.output else nd.name
+        if nd.op_type == "Constant":
+            val = _read_attr(nd.attribute[0]) if nd.attribute else None
+            if isinstance(val, torch.Tensor):
+                cn = g.create_node("get_attr", "const::%d" % len(env))
+                cn.meta["const"] = val
+                val = cn
+            env[out_name] = val
+            continue
+        if nd.op_type.startswith("REF::"):
+            key = nd.op_type[5:]
+            if key not in prims:
+                raise MindIRError("node %s refers to %s, which is not a primitive of the model (a sub-graph or a "
+                                  "closure?)" % (nd.name, key))
+            op_type = prims[key].op_type
+            attrs = {a.name: _read_attr(a) for a in prims[key].attribute}
+        else:
+            op_type = nd.op_type
+            attrs = {a.name: _read_attr(a) for a in nd.attribute}
+        args = [value_of(i) for i in nd.input]
+        args = [a for a in args if a is not _MONAD]          # side-effect tokens order nodes: the list order does
+        if op_type == "TupleGetItem":
+            node = g.create_node("call_function", operator.getitem, (args[0], int(args[1])), {})
+        elif op_type == "MakeTuple":
+            node = g.create_node("call_function", _make_tuple, tuple(args), {})
+        elif op_type in ("Depend", "UpdateState", "Load"):
+            env[out_name] = args[0] if args else _MONAD
+            continue
+        elif op_type == "Return":
+            env[out_name] = args[0]
+            continue
+        else:
+            node = g.create_node("call_function", _make_primitive(op_type, attrs), tuple(args), {})
+            node.meta["primitive"] = op_type
+        if nd.domain:
+            node.meta["scope"] = nd.domain
+        env[out_name] = node
+    if not gp.output:
+        raise MindIRError("the graph has no output")
+    outs = [value_of(o.name) for o in gp.output]
+    fg.output_node = g.output(outs[0] if len(outs) == 1 else tuple(outs))
+    fg.input_positions = list(range(n_in))
+    return LoadedGraph(fg)

@@ -175,6 +175,20 @@ def all_reduce_(tensor, group, scale=1.0, nonfinite=None):
     return tensor
 
 
+def all_reduce_symm_(ctx, ptrs, offset, n, scale=1.0, nonfinite=None):
+    """In-place sum (x scale) of elements [offset, offset + n) of an fp32 buffer that already lives in symmetric
+    memory (``ptrs`` = its address on every rank): no staging copies.  Rank r sums slice r of the range over peer
+    loads and stores the result into every rank's buffer; the barriers on both sides order it against the producers
+    of the range and against whoever reads it next."""
+    assert (offset * 4) % 16 == 0
+    ctx.barrier(0)
+    rc = _native.cuda().msb_allreduce_symm(_ptr_array([p + offset * 4 for p in ptrs]), ctx.rank, ctx.world, n,
+                                           float(scale), _p(nonfinite), _stream())
+    _native.check(rc, "allreduce_symm")
+    _count()
+    ctx.barrier(0)
+
+
 # --------------------------------------------------------------------------------------------- GEMM + collectives
 def _gemm_rs(ctx, a, b, b_mn):
     """partial = a @ op(b) reduced over the group and scattered by token rows -> [M/world, N]."""

@@ -58,7 +58,21 @@ class DataParallelArena:
         self.local_only = [(arena.offsets[i], arena.offsets[i] + p.numel()) for i, p in enumerate(arena.params)
                            if getattr(p, "dp_local", False)]
         self.symm = None
+        self._symm_grads = None
         if not self.shard:
+            if fused and self.world > 1 and arena.grads.is_cuda and os.environ.get("MSB200_SYMM_GRADS", "1") != "0":
+                from . import fused_comm
+                if fused_comm.available(self.group):
+                    # the gradient arena itself lives in symmetric memory: bucket all-reduces run in place on it
+                    # (peer loads / peer stores) instead of through a staging buffer
+                    ctx = fused_comm.get_context(self.group)
+                    graw, ptrs = ctx._alloc_raw(arena.grads.numel() * 4)
+                    grads = graw[:arena.grads.numel() * 4].view(torch.float32)
+                    grads.copy_(arena.grads)
+                    arena.rebind(arena.weights, grads)
+                    self._symm_grads = (ctx, ptrs, graw)
+                    torch.cuda.synchronize()
+                    dist.barrier(group=self.group.pg)
             return
         if self.local_only:
             raise ValueError("optimizer-state sharding over the data-parallel group cannot hold parameters that "
@@ -211,7 +225,11 @@ class DataParallelArena:
     def _reduce_segment(self, lo, hi, scale):
         from . import symm
         seg = self.arena.grads[lo:hi]
-        if symm.fused_available(self.group):
+        if self._symm_grads is not None:
+            from . import fused_comm
+            ctx, ptrs, _ = self._symm_grads
+            fused_comm.all_reduce_symm_(ctx, ptrs, lo, hi - lo, scale)
+        elif symm.fused_available(self.group):
             symm.all_reduce_(seg, self.group, scale)
         else:
             CF._all_reduce_(seg, "sum", self.group)

@@ -511,8 +511,10 @@ def parse_print(print_file_name):
 
 def export(net, *inputs, file_name, file_format, **kwargs):
     """Exports ``net`` traced on ``inputs``.  MINDIR: one ``<file_name>.mindir`` file holding the forward graph and the
-    weights (``graph/mindir.py`` describes the layout); ``enc_key`` / ``enc_mode`` encrypt it like a checkpoint.  ONNX
-    and AIR target other runtimes and are not produced."""
+    weights, in the reference's protobuf layout (``graph/mindir_proto.py``) when every node is a primitive, else in
+    this framework's own container (``graph/mindir.py``; ``container="native"`` forces it, ``container="proto"``
+    insists on protobuf); ``enc_key`` / ``enc_mode`` encrypt it like a checkpoint.  ONNX and AIR target other
+    runtimes and are not produced."""
     if file_format not in ("MINDIR", "ONNX", "AIR"):
         raise ValueError("For 'export', 'file_format' must be one of AIR, ONNX, MINDIR, but got %r" % file_format)
     if file_format != "MINDIR":
@@ -526,7 +528,20 @@ def export(net, *inputs, file_name, file_format, **kwargs):
     finally:
         net.set_train(was_training)
     path = file_name if file_name.endswith(".mindir") else file_name + ".mindir"
-    mindir.save_mindir(g, path)
+    container = kwargs.get("container", "auto")
+    if container not in ("auto", "proto", "native"):
+        raise ValueError("For 'export', 'container' must be auto, proto or native, but got %r" % container)
+    written = False
+    if container in ("auto", "proto"):
+        from ..graph import mindir_proto
+        try:
+            mindir_proto.save_model_proto(g, path)
+            written = True
+        except mindir.MindIRError:
+            if container == "proto":
+                raise
+    if not written:
+        mindir.save_mindir(g, path)
     enc_key = kwargs.get("enc_key")
     if enc_key is not None:
         from . import crypto
@@ -540,14 +555,18 @@ def export(net, *inputs, file_name, file_format, **kwargs):
 def load(file_name, **kwargs):
     """Loads a graph written by ``export`` (``dec_key`` / ``dec_mode`` for an encrypted file); wrap the result in
     ``nn.GraphCell`` to use it as a network."""
-    from ..graph import mindir
+    from ..graph import mindir, mindir_proto
     dec_key = kwargs.get("dec_key")
+    with open(file_name, "rb") as f:
+        raw = f.read()
+    if dec_key is not None:
+        from . import crypto
+        raw = crypto.decrypt(raw, dec_key, kwargs.get("dec_mode", "AES-GCM"))
+    if raw[:8] != mindir.MAGIC and mindir_proto.looks_like_model_proto(raw):
+        return mindir_proto.load_model_proto(raw)          # the reference's protobuf layout
     if dec_key is None:
         return mindir.load_mindir(file_name)
     import tempfile
-    from . import crypto
-    with open(file_name, "rb") as f:
-        raw = crypto.decrypt(f.read(), dec_key, kwargs.get("dec_mode", "AES-GCM"))
     with tempfile.NamedTemporaryFile(suffix=".mindir") as tmp:
         tmp.write(raw)
         tmp.flush()

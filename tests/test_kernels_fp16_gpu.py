@@ -136,7 +136,8 @@ def test_flash_attention_fp16(K, B, S, H, causal):
     _status_ok()
 
 
-def test_conv_bn_relu_fp16(K):
+@pytest.mark.parametrize("relu", [False, True])
+def test_conv_bn_relu_fp16(K, relu):
     from mindspore_b200.ops import conv_kernel as CK
     n, cin, cout, h = 8, 64, 128, 28
     x = torch.randn(n, cin, h, h, device=DEV).half().contiguous(memory_format=torch.channels_last)
@@ -147,20 +148,25 @@ def test_conv_bn_relu_fp16(K):
     gg, bg = gamma.clone().requires_grad_(True), beta.clone().requires_grad_(True)
     assert CK.supports(xg, wg)
     before = K._native.launch_count
-    y = CK.conv_bn_act(xg, wg, gg, bg, mm, mv, stride=1, pad=1, relu=True)
+    y = CK.conv_bn_act(xg, wg, gg, bg, mm, mv, stride=1, pad=1, relu=relu)
     assert y.dtype == H16 and K._native.launch_count > before
     dy = torch.randn_like(y)
     y.backward(dy)
     xr, wr = x.float().clone().requires_grad_(True), w.float().clone().requires_grad_(True)
     gr, br = gamma.clone().requires_grad_(True), beta.clone().requires_grad_(True)
-    yr = torch.relu(torch.nn.functional.batch_norm(torch.nn.functional.conv2d(xr, wr, None, 1, 1), None, None, gr, br,
-                                                   True, 0.1, 1e-5))
+    yr = torch.nn.functional.batch_norm(torch.nn.functional.conv2d(xr, wr, None, 1, 1), None, None, gr, br, True, 0.1,
+                                        1e-5)
+    if relu:
+        yr = torch.relu(yr)
     yr.backward(dy.float())
     _close(y, yr, 1e-2)
-    _close(xg.grad, xr.grad, 2e-2)
-    _close(wg.grad, wr.grad, 2e-2)
-    _close(gg.grad, gr.grad, 2e-2)
-    _close(bg.grad, br.grad, 2e-2)
+    # with the ReLU, outputs next to zero fall on the other side of the mask in fp16 than in the fp32 reference:
+    # single gradient elements then differ by a whole term, whatever the precision of the rest
+    tol = 6e-2 if relu else 2e-2
+    _close(xg.grad, xr.grad, tol)
+    _close(wg.grad, wr.grad, tol)
+    _close(gg.grad, gr.grad, tol)
+    _close(bg.grad, br.grad, tol)
     _status_ok()
 
 

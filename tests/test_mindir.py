@@ -62,3 +62,120 @@ def test_bad_files_are_rejected(tmp_path):
         ms.load(str(p))
     with pytest.raises(ValueError):
         ms.export(Small(), ms.Tensor(torch.randn(1, 6)), file_name=str(tmp_path / "x"), file_format="TFLITE")
+
+
+def test_export_uses_the_reference_protobuf_layout(tmp_path):
+    """LeNet exports as a ModelProto (mind_ir.proto field numbers): weights in graph.parameter, every call a
+    REF::<Prim>:<id> node with its primitive record, and loads back to the same numbers."""
+    from mindspore_b200.graph import mindir_proto as MP
+    ms.set_seed(3)
+    net = LeNet5()
+    x = ms.Tensor(torch.randn(2, 1, 32, 32))
+    path = ms.export(net, x, file_name=str(tmp_path / "lenet_pb"), file_format="MINDIR", container="proto")
+    raw = open(path, "rb").read()
+    model = MP.messages()["ModelProto"]()
+    model.ParseFromString(raw)
+    assert model.producer_name == "MindSpore" and model.ir_version
+    assert {t.name for t in model.graph.parameter} == {p.name for p in net.get_parameters()}
+    conv = next(p for p in model.primitives if p.op_type == "Conv2D")
+    attrs = {a.name: a for a in conv.attribute}
+    assert attrs["out_channel"].type == MP.A_INT64 and attrs["out_channel"].i == 6
+    assert attrs["kernel_size"].type == MP.A_TUPLE and [v.i for v in attrs["kernel_size"].values] == [5, 5]
+    assert attrs["pad_mode"].type == MP.A_STRING and attrs["pad_mode"].s == b"valid"
+    assert all(n.op_type.startswith("REF::") or n.op_type == "Constant" for n in model.graph.node)
+    w = next(t for t in model.graph.parameter if t.name == "conv1.weight")
+    assert list(w.dims) == [6, 1, 5, 5] and w.data_type == 1 and len(w.raw_data) == 6 * 25 * 4
+    cell = nn.GraphCell(ms.load(path))
+    np.testing.assert_allclose(cell(x).numpy(), net(x).detach().numpy(), rtol=1e-5, atol=1e-6)
+
+
+def test_load_a_file_laid_out_by_an_older_writer(tmp_path):
+    """Plain op_type nodes with attributes on the node, weights repeated among the inputs, side-effect plumbing
+    (Load / UpdateState / Depend with monads), a Return node: y = relu(x @ w^T + b) * 2 read from such a file."""
+    from mindspore_b200.graph import mindir_proto as MP
+    M = MP.messages()
+    model = M["ModelProto"]()
+    model.ir_version = "0.1.0"
+    model.producer_name = "MindSpore"
+    g = model.graph
+    g.name = "net"
+    w = torch.randn(4, 6)
+    b = torch.randn(4)
+    for name, t in (("fc.weight", w), ("fc.bias", b)):
+        tp = g.parameter.add()
+        tp.name, tp.data_type = name, 1
+        tp.dims.extend(t.shape)
+        tp.raw_data = t.numpy().tobytes()
+    vi = g.input.add()
+    vi.name = "x"
+    tin = vi.tensor.add()
+    tin.dims.extend([3, 6])
+    tin.data_type = 1
+    g.input.add().name = "fc.weight"                     # older writers list parameters as inputs too
+
+    def node(op, ins, out, **attrs):
+        n = g.node.add()
+        n.op_type, n.name = op, out
+        n.output.append(out)
+        n.input.extend(ins)
+        for k, v in attrs.items():
+            a = n.attribute.add()
+            a.name = k
+            MP._fill_attr(a, v)
+        return n
+
+    u = g.node.add()
+    u.op_type, u.name = "Constant", "net:u"
+    u.output.append("net:u")
+    ua = u.attribute.add()
+    ua.name, ua.type = "value", MP.A_UMONAD
+    node("Load", ["fc.weight", "net:u"], "net:1")
+    node("MatMul", ["x", "net:1"], "net:2", transpose_a=False, transpose_b=True)
+    node("BiasAdd", ["net:2", "fc.bias"], "net:3", format="NCHW")
+    node("ReLU", ["net:3"], "net:4")
+    two = g.node.add()
+    two.op_type, two.name = "Constant", "net:5"
+    two.output.append("net:5")
+    ta = two.attribute.add()
+    ta.name = "value"
+    MP._fill_attr(ta, torch.tensor(2.0))
+    node("Mul", ["net:4", "net:5"], "net:6")
+    node("UpdateState", ["net:u", "net:6"], "net:7")
+    node("Depend", ["net:6", "net:7"], "net:8")
+    node("Return", ["net:8"], "net:9")
+    g.output.add().name = "net:9"
+    p = tmp_path / "old.mindir"
+    p.write_bytes(model.SerializeToString())
+    graph = ms.load(str(p))
+    x = torch.randn(3, 6)
+    out = nn.GraphCell(graph)(ms.Tensor(x))
+    np.testing.assert_allclose(out.numpy(), (torch.relu(x @ w.t() + b) * 2).numpy(), rtol=1e-6, atol=1e-6)
+    assert set(graph.params) == {"fc.weight", "fc.bias"}
+    # an operator this build does not know is named in the error
+    node("NoSuchOperator", ["x"], "net:10")
+    del g.output[:]
+    g.output.add().name = "net:10"
+    p.write_bytes(model.SerializeToString())
+    from mindspore_b200.graph.mindir import MindIRError
+    with pytest.raises(MindIRError, match="NoSuchOperator"):
+        ms.load(str(p))
+
+
+def test_attribute_values_round_trip():
+    from mindspore_b200.graph import mindir_proto as MP
+    A = MP.messages()["AttributeProto"]
+    for v in (3, -7, True, False, 0.5, 1e-7, 3.141592653589793, "same", None, (1, 2, 3), [1.5, "a", (2, False)],
+              {"k": 1, "z": (2, 3)}, torch.float16):
+        a = A()
+        MP._fill_attr(a, v)
+        b = A()
+        b.ParseFromString(a.SerializeToString())
+        got = MP._read_attr(b)
+        if isinstance(v, float):
+            assert got == pytest.approx(v, rel=1e-7)
+        else:
+            assert got == v, (v, got)
+    t = torch.arange(6, dtype=torch.bfloat16).reshape(2, 3)
+    a = A()
+    MP._fill_attr(a, t)
+    assert torch.equal(MP._read_attr(a), t)

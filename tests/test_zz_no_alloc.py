@@ -40,6 +40,8 @@ def _case(rows, H, seed):
 
 def test_static_scratch_matches_regular_entry_point_twice():
     fn, ref, err = _lib()
+    from mindspore_b200 import _native
+    lib_scratch = _native.cuda().msb_norm_bwd_scratch_elems
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     # two calls in a row, the second with a smaller H so that stale scratch beyond H and within H both matter
     for rows, H, seed, fp32, acc in ((777, 4096, 1, 1, 1), (300, 1024, 2, 0, 0)):
@@ -49,7 +51,9 @@ def test_static_scratch_matches_regular_entry_point_twice():
         dw_b = dw_a.clone()
         dx_a = torch.empty_like(x)
         dx_b = torch.empty_like(x)
-        scratch = torch.empty(H, device="cuda", dtype=torch.float32)
+        # the ordinary entry point reduces in two stages: its scratch is one partial row of H floats per CTA
+        lib_scratch.restype = _L
+        scratch = torch.empty(int(lib_scratch(H, 0)), device="cuda", dtype=torch.float32)
         rc = ref(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dres.data_ptr(), dx_a.data_ptr(),
                  scratch.data_ptr(), dw_a.data_ptr(), fp32, acc, rows, H, stream)
         assert rc == 0, err()
