@@ -40,6 +40,9 @@ def parse():
                          "unmodified reference framework (unavailable offline); tp: the hand-placed tensor-parallel "
                          "formulation on the same kernels; library: the same model on torch ops (cuBLAS / SDPA / "
                          "fused Adam) with un-fused NCCL collectives")
+    ap.add_argument("--mode", default="pynative", choices=["pynative", "graph"],
+                    help="llama2-7b: graph = GRAPH_MODE, the micro-batch forward + backward is traced, optimised by the "
+                         "pass pipeline and run by the graph executor")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is marked invalid)")
     ap.add_argument("--global-batch", type=int, default=32)
     ap.add_argument("--seq", type=int, default=4096)
@@ -404,7 +407,8 @@ def main():
     # is bound by host launch time unless the micro-batch is replayed as a CUDA graph.
     graph_env = os.environ.get("MSB200_CUDA_GRAPH", "auto")
     use_graph = graph_env == "1" or (graph_env == "auto" and world >= 2)
-    ms.set_context(mode=ms.PYNATIVE_MODE, device_target="GPU", device_id=local_rank, enable_cuda_graph=use_graph)
+    ms.set_context(mode=ms.GRAPH_MODE if args.mode == "graph" else ms.PYNATIVE_MODE, device_target="GPU",
+                   device_id=local_rank, enable_cuda_graph=use_graph)
     if world > 1:
         from mindspore_b200.communication import init
         init("nccl")
@@ -524,6 +528,7 @@ def main():
                        else "hand-placed tensor parallel",
                        "optimizer": "AdamW fp32 master + moments, grad clip 1.0",
                        "cuda_graph": bool(ms.get_context("enable_cuda_graph")),
+                       "mode": "GRAPH_MODE" if args.mode == "graph" else "PYNATIVE_MODE",
                        "fused_comm": bool(mp > 1 and os.environ.get("MSB200_FUSED_COMM", "1") != "0"),
                        "l2": "working set >100 GB per step, far larger than the 126 MB L2 (no flush needed)"},
             "clocks": clocks,

@@ -266,13 +266,16 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         float pv[64];
         if (!mbar_wait(&s_full[st], ph, ab)) { ok = false; break; }
         tc_fence_after_sync();
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tm_s + st * 64 + lane_sel + c * 32, r);
+        {
+          // both loads are issued before the one wait: a single TMEM round trip per tile
+          uint32_t r[2][32];
+          tmem_ld_32x32(tm_s + st * 64 + lane_sel, r[0]);
+          tmem_ld_32x32(tm_s + st * 64 + lane_sel + 32, r[1]);
           tmem_ld_wait();
 #pragma unroll
-          for (int t = 0; t < 32; ++t) pv[c * 32 + t] = __uint_as_float(r[t]);
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int t = 0; t < 32; ++t) pv[c * 32 + t] = __uint_as_float(r[c][t]);
         }
         tc_fence_before_sync();
         mbar_arrive(&s_empty[st]);
@@ -299,19 +302,22 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         // ---- dS^T
         if (!mbar_wait(&dp_full[st], ph, ab)) { ok = false; break; }
         tc_fence_after_sync();
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tm_dp + st * 64 + lane_sel + c * 32, r);
+        {
+          uint32_t r[2][32];
+          tmem_ld_32x32(tm_dp + st * 64 + lane_sel, r[0]);
+          tmem_ld_32x32(tm_dp + st * 64 + lane_sel + 32, r[1]);
           tmem_ld_wait();
 #pragma unroll
-          for (int t4 = 0; t4 < 8; ++t4) {
-            const float4 d4 = *reinterpret_cast<const float4*>(delta_row + q0 + c * 32 + t4 * 4);
-            const float dv4[4] = {d4.x, d4.y, d4.z, d4.w};
+          for (int c = 0; c < 2; ++c) {
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              const int cc = c * 32 + t4 * 4 + t;
-              pv[cc] = pv[cc] * (__uint_as_float(r[t4 * 4 + t]) - dv4[t]) * p.scale;
+            for (int t4 = 0; t4 < 8; ++t4) {
+              const float4 d4 = *reinterpret_cast<const float4*>(delta_row + q0 + c * 32 + t4 * 4);
+              const float dv4[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                const int cc = c * 32 + t4 * 4 + t;
+                pv[cc] = pv[cc] * (__uint_as_float(r[c][t4 * 4 + t]) - dv4[t]) * p.scale;
+              }
             }
           }
         }
@@ -559,12 +565,17 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (!mbar_wait(&s_full[st], ph, ab)) { ok = false; break; }
         tc_fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tm_s + st * 128 + lane_sel + c * 32, r);
+        for (int c2 = 0; c2 < 2; ++c2) {
+          // two loads per wait (64 registers in flight beside the 128 of the row)
+          uint32_t r[2][32];
+          tmem_ld_32x32(tm_s + st * 128 + lane_sel + c2 * 64, r[0]);
+          tmem_ld_32x32(tm_s + st * 128 + lane_sel + c2 * 64 + 32, r[1]);
           tmem_ld_wait();
 #pragma unroll
-          for (int t = 0; t < 32; ++t) pv[c * 32 + t] = ex2(__uint_as_float(r[t]) * p.scale_log2 - lse2);
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int t = 0; t < 32; ++t)
+              pv[c2 * 64 + c * 32 + t] = ex2(__uint_as_float(r[c][t]) * p.scale_log2 - lse2);
         }
         tc_fence_before_sync();
         mbar_arrive(&s_empty[st]);
@@ -576,12 +587,18 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (!mbar_wait(dp_full, kvc & 1, ab)) { ok = false; break; }
         tc_fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tm_dp + lane_sel + c * 32, r);
+        for (int c2 = 0; c2 < 2; ++c2) {
+          uint32_t r[2][32];
+          tmem_ld_32x32(tm_dp + lane_sel + c2 * 64, r[0]);
+          tmem_ld_32x32(tm_dp + lane_sel + c2 * 64 + 32, r[1]);
           tmem_ld_wait();
 #pragma unroll
-          for (int t = 0; t < 32; ++t) pv[c * 32 + t] = pv[c * 32 + t] * (__uint_as_float(r[t]) - dl) * p.scale;
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int t = 0; t < 32; ++t) {
+              const int cc = c2 * 64 + c * 32 + t;
+              pv[cc] = pv[cc] * (__uint_as_float(r[c][t]) - dl) * p.scale;
+            }
         }
         tc_fence_before_sync();
         mbar_arrive(dp_empty);

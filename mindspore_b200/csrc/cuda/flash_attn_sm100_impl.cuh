@@ -220,14 +220,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int sb = sc & 1;
         if (!mbar_wait(&s_full[sb], (sc >> 1) & 1, ab)) { ok = false; break; }
         tc_fence_after_sync();
+        // raw scores; the softmax scale is folded into the exponent below (one FFMA per element) and every
+        // reduction runs on four independent accumulators: with one warp per scheduler a serial chain of 128
+        // dependent max / add instructions would cost its full latency 128 times
         float s[128];
+        {
+          // the four loads are issued back to back and waited for once: one TMEM round trip instead of four
+          uint32_t r[4][32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_base + sb * 128 + lane_sel + c * 32, r);
+          for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_base + sb * 128 + lane_sel + c * 32, r[c]);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]) * p.scale_log2;
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[c][i]);
         }
         tc_fence_before_sync();
         mbar_arrive(&s_empty[sb]);
@@ -236,9 +242,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           for (int i = 0; i < 128; ++i)
             if (i > row) s[i] = -INFINITY;
         }
-        float mx = s[0];
+        float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-        for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+        for (int i = 4; i < 128; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;   // scale > 0
         // rescale only when some row of this warp grew its max by more than 8 (in log2 units)
         const bool grow = mx > m_used + 8.f;
         const bool warp_grow = __any_sync(0xffffffffu, grow);
@@ -248,13 +255,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           alpha = (m_used == -INFINITY) ? 0.f : ex2(m_used - m_new);
           m_used = m_new;
         }
-        float rs = 0.f;
+        const float neg_m = -m_used;
+        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < 128; ++i) {
-          s[i] = ex2(s[i] - m_used);
-          rs += s[i];
+          s[i] = ex2(fmaf(s[i], p.scale_log2, neg_m));
+          rs4[i & 3] += s[i];
         }
-        l = l * alpha + rs;
+        l = l * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
         if (j > 0) {
           // previous PV must have retired before O is rescaled or P is overwritten
           if (!mbar_wait(o_done, oc & 1, ab)) { ok = false; break; }
@@ -336,385 +344,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }
 
 
-// ---------------------------------------------------------------------------------------------------------------
-// Two-stream forward.  The 128 query rows of an item are served by TWO independent online-softmax streams: stream 0
-// takes the even key blocks, stream 1 the odd ones, each with its own S and O accumulators in TMEM, its own K / V / P
-// shared-memory tiles, its own running (max, sum) and its own softmax warpgroup.  The MMA warp interleaves the two
-// streams, so the tensor pipe works on one stream while the other does its exponentials, and two warps per scheduler
-// hide each other's TMEM-load and MUFU latencies.  The epilogue merges the two partial results
-// (O = (w0 O0 + w1 O1) / (w0 l0 + w1 l1), w = 2^(m - max(m0, m1))), each warpgroup writing one half of the head dim.
-//
-// 320 threads: warp 0 TMA, warp 1 MMA, warps 2-5 softmax of stream 0, warps 6-9 softmax of stream 1.  With 320
-// threads a thread has 168 registers, too few for a row of 128 scores, so the softmax reads its S row from TMEM twice:
-// once for the row maximum, once (32 columns at a time) for the exponentials, which go straight to shared memory.
-// TMEM: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512).
-// shared memory: Q | K0 | K1 | V0 | V1 | P0 | P1 (32 KB each) | barriers.
-constexpr int kFa2Threads = 320;
-
-struct Fa2Smem {
-  static constexpr int kQ = 0;
-  static constexpr int kK = kTileBytes;
-  static constexpr int kV = 3 * kTileBytes;
-  static constexpr int kP = 5 * kTileBytes;
-  static constexpr int kBar = 7 * kTileBytes;
-  static constexpr int kBytes = kBar + 256 + 1024;
-};
-
-__global__ void __launch_bounds__(kFa2Threads, 1)
-flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                  const __grid_constant__ CUtensorMap tmV, const FaParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Fa2Smem::kBar);
-  uint64_t* q_full = bars + 0;
-  uint64_t* q_empty = bars + 1;
-  uint64_t* k_full = bars + 2;    // [2], one per stream
-  uint64_t* k_empty = bars + 4;
-  uint64_t* v_full = bars + 6;
-  uint64_t* v_empty = bars + 8;
-  uint64_t* s_full = bars + 10;
-  uint64_t* s_empty = bars + 12;
-  uint64_t* p_ready = bars + 14;
-  uint64_t* o_done = bars + 16;
-  uint64_t* epi = bars + 18;      // [2]: (max, sum) published / both accumulators read
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
-  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const AbortCtx ab{cta_abort, p.status};
-  const int nq = p.S / kFaBM;
-  const int total = p.B * p.H * nq;
-  const int group = p.H / p.Hk;
-
-  if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
-      mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
-      mbar_init(&p_ready[i], 128);
-      mbar_init(&o_done[i], 1);
-      mbar_init(&epi[i], 256);
-    }
-    *cta_abort = 0;
-    fence_mbar_init();
-    tma_prefetch_desc(&tmQ);
-    tma_prefetch_desc(&tmK);
-    tma_prefetch_desc(&tmV);
-  }
-  if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 256;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      // ------------------------------------------------------------------ TMA producer
-      // K tiles run one key block ahead of V tiles (K0 K1 V0 K2 V1 ...): a K buffer is free as soon as its QK product
-      // has retired, long before the V buffer of the same stream, whose PV product waits for the softmax
-      uint32_t items = 0, ck[2] = {0, 0}, cv[2] = {0, 0};   // per stream: K / V tiles loaded so far
-      bool ok = true;
-      for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++items) {
-        int b, h, qb;
-        fa_item(w, p, nq, b, h, qb);
-        const int hk = h / group;
-        const int nblk = p.causal ? qb + 1 : p.S / kFaBN;
-        if (!mbar_wait(q_empty, (items & 1) ^ 1, ab)) { ok = false; break; }
-        mbar_expect_tx(q_full, kTileBytes);
-        tma_load_4d(smem + Fa2Smem::kQ, &tmQ, q_full, 0, h, qb * kFaBM, b);
-        tma_load_4d(smem + Fa2Smem::kQ + 16384, &tmQ, q_full, 64, h, qb * kFaBM, b);
-        auto load_k = [&](int j) -> bool {
-          const int st = j & 1;
-          if (!mbar_wait(&k_empty[st], (ck[st] & 1) ^ 1, ab)) return false;
-          mbar_expect_tx(&k_full[st], kTileBytes);
-          uint8_t* kd = smem + Fa2Smem::kK + st * kTileBytes;
-          tma_load_4d(kd, &tmK, &k_full[st], 0, hk, j * kFaBN, b);
-          tma_load_4d(kd + 16384, &tmK, &k_full[st], 64, hk, j * kFaBN, b);
-          ++ck[st];
-          return true;
-        };
-        auto load_v = [&](int j) -> bool {
-          const int st = j & 1;
-          if (!mbar_wait(&v_empty[st], (cv[st] & 1) ^ 1, ab)) return false;
-          mbar_expect_tx(&v_full[st], kTileBytes);
-          uint8_t* vd = smem + Fa2Smem::kV + st * kTileBytes;
-          tma_load_4d(vd, &tmV, &v_full[st], 0, hk, j * kFaBN, b);
-          tma_load_4d(vd + 16384, &tmV, &v_full[st], 64, hk, j * kFaBN, b);
-          ++cv[st];
-          return true;
-        };
-        if (!load_k(0)) { ok = false; break; }
-        for (int j = 0; j < nblk; ++j) {
-          if (j + 1 < nblk && !load_k(j + 1)) { ok = false; break; }
-          if (!load_v(j)) { ok = false; break; }
-        }
-      }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    if (lane == 0) {
-      // ------------------------------------------------------------------ MMA issuer
-      constexpr uint32_t idesc_qk = umma_idesc_elem(128, 128, false, false);
-      constexpr uint32_t idesc_pv = umma_idesc_elem(128, 128, false, true);   // V is MN-major (d contiguous)
-      const uint32_t q_addr = smem_u32(smem + Fa2Smem::kQ);
-      uint32_t items = 0;
-      uint32_t kc[2] = {0, 0}, vc[2] = {0, 0};   // per stream: QK / PV products issued so far
-      bool ok = true;
-      auto issue_qk = [&](int st) -> bool {
-        if (!mbar_wait(&k_full[st], kc[st] & 1, ab)) return false;
-        if (!mbar_wait(&s_empty[st], (kc[st] & 1) ^ 1, ab)) return false;
-        tc_fence_after_sync();
-        const uint32_t k_addr = smem_u32(smem + Fa2Smem::kK + st * kTileBytes);
-#pragma unroll
-        for (int kk = 0; kk < kFaD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tmem_base + st * 128, umma_smem_desc(q_addr + off, 16, 1024),
-                    umma_smem_desc(k_addr + off, 16, 1024), idesc_qk, kk != 0);
-        }
-        umma_commit(&s_full[st]);
-        umma_commit(&k_empty[st]);
-        ++kc[st];
-        return true;
-      };
-      auto issue_pv = [&](int st, bool first) -> bool {
-        if (!mbar_wait(&p_ready[st], vc[st] & 1, ab)) return false;
-        if (!mbar_wait(&v_full[st], vc[st] & 1, ab)) return false;
-        tc_fence_after_sync();
-        const uint32_t p_addr = smem_u32(smem + Fa2Smem::kP + st * kTileBytes);
-        const uint32_t v_addr = smem_u32(smem + Fa2Smem::kV + st * kTileBytes);
-#pragma unroll
-        for (int kk = 0; kk < kFaBN / 16; ++kk) {
-          const uint64_t adesc = umma_smem_desc(p_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
-          const uint64_t bdesc = umma_smem_desc(v_addr + kk * 2048, 16384, 1024);
-          umma_bf16(tmem_o + st * 128, adesc, bdesc, idesc_pv, !first || kk != 0);
-        }
-        umma_commit(&v_empty[st]);
-        umma_commit(&o_done[st]);
-        ++vc[st];
-        return true;
-      };
-      for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++items) {
-        int b, h, qb;
-        fa_item(w, p, nq, b, h, qb);
-        const int nblk = p.causal ? qb + 1 : p.S / kFaBN;
-        if (!mbar_wait(q_full, items & 1, ab)) { ok = false; break; }
-        if (!issue_qk(0)) { ok = false; break; }
-        if (nblk > 1 && !issue_qk(1)) { ok = false; break; }
-        if (nblk <= 2) umma_commit(q_empty);   // every QK of this item is in flight: Q may be reloaded when they retire
-        for (int j = 0; j < nblk; ++j) {
-          if (j + 2 < nblk) {
-            if (!issue_qk(j & 1)) { ok = false; break; }
-            if (j + 3 == nblk) umma_commit(q_empty);
-          }
-          if (!issue_pv(j & 1, j < 2)) { ok = false; break; }
-        }
-      }
-    }
-    __syncwarp();
-  } else {
-    // -------------------------------------------------------------------- softmax of one stream / merge / epilogue
-    const int g = (warp - 2) >> 2;                 // stream of this warpgroup
-    const int q = warp & 3;                        // TMEM lane quarter this warp may access
-    const int row = q * 32 + lane;                 // row inside the 128-row tile == TMEM lane
-    const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
-    const uint32_t tmem_s = tmem_base + g * 128 + lane_sel;
-    const uint32_t tmem_my_o = tmem_o + g * 128 + lane_sel;
-    uint8_t* p_smem = smem + Fa2Smem::kP + g * kTileBytes;
-    float* ml_mine = reinterpret_cast<float*>(p_smem);                                   // reused after the last PV
-    const float* ml_other = reinterpret_cast<const float*>(smem + Fa2Smem::kP + (g ^ 1) * kTileBytes);
-    uint32_t sc = 0, oc = 0, items = 0;
-    bool ok = true;
-    for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++items) {
-      int b, h, qb;
-      fa_item(w, p, nq, b, h, qb);
-      const int nblk = p.causal ? qb + 1 : p.S / kFaBN;
-      const int mine = (nblk - g + 1) >> 1;        // key blocks g, g + 2, ...
-      float m_used = -INFINITY;   // max the stored probabilities are relative to (log2 domain)
-      float l = 0.f;
-      for (int jj = 0; jj < mine; ++jj, ++sc) {
-        const int j = 2 * jj + g;
-        if (!mbar_wait(&s_full[g], sc & 1, ab)) { ok = false; break; }
-        tc_fence_after_sync();
-        const bool diag = p.causal && j == qb;
-        // ---- pass 1: row maximum
-        float mx = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_s + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float v = __uint_as_float(r[i]);
-            mx = (diag && c * 32 + i > row) ? mx : fmaxf(mx, v);
-          }
-        }
-        mx *= p.scale_log2;                        // the scale is positive: max(scale * s) = scale * max(s)
-        // rescale only when some row of this warp grew its max by more than 8 (in log2 units)
-        const bool grow = mx > m_used + 8.f;
-        const bool warp_grow = __any_sync(0xffffffffu, grow);
-        float alpha = 1.f;
-        if (warp_grow) {
-          const float m_new = fmaxf(m_used, mx);
-          alpha = (m_used == -INFINITY) ? 0.f : ex2(m_used - m_new);
-          m_used = m_new;
-        }
-        if (jj > 0) {
-          // the previous PV of this stream must have retired before O is rescaled or P is overwritten
-          if (!mbar_wait(&o_done[g], oc & 1, ab)) { ok = false; break; }
-          ++oc;
-          tc_fence_after_sync();
-          if (warp_grow) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              uint32_t r[32];
-              tmem_ld_32x32(tmem_my_o + c * 32, r);
-              tmem_ld_wait();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-              tmem_st_32x32(tmem_my_o + c * 32, r);
-            }
-            tmem_st_wait();
-          }
-        }
-        // ---- pass 2: exponentials, 32 columns at a time; P row -> shared memory, K-major 128B swizzle: 16-byte
-        // chunk ch of row r lands at chunk (ch ^ (r & 7))
-        float rs = 0.f;
-        const float neg_m = -m_used;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_s + c * 32, r);
-          tmem_ld_wait();
-          if (c == 3) {
-            tc_fence_before_sync();
-            mbar_arrive(&s_empty[g]);              // the S row is in registers: the next QK of this stream may start
-          }
-          float e[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float v = ex2(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
-            e[i] = (diag && c * 32 + i > row) ? 0.f : v;
-            rs += e[i];
-          }
-#pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) {
-            uint4 v;
-            v.x = pack_e2(e[k4 * 8 + 0], e[k4 * 8 + 1]);
-            v.y = pack_e2(e[k4 * 8 + 2], e[k4 * 8 + 3]);
-            v.z = pack_e2(e[k4 * 8 + 4], e[k4 * 8 + 5]);
-            v.w = pack_e2(e[k4 * 8 + 6], e[k4 * 8 + 7]);
-            const int ch = c * 4 + k4;
-            const int half = ch >> 3, cc = ch & 7;
-            *reinterpret_cast<uint4*>(p_smem + half * 16384 + row * 128 + ((cc ^ (row & 7)) << 4)) = v;
-          }
-        }
-        l = l * alpha + rs;
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        mbar_arrive(&p_ready[g]);
-      }
-      if (!ok) break;
-      // ---- merge the two streams: this stream's last PV has retired, so its P tile is free to carry (max, sum)
-      if (mine > 0) {
-        if (!mbar_wait(&o_done[g], oc & 1, ab)) { ok = false; break; }
-        ++oc;
-      }
-      ml_mine[2 * row] = m_used;
-      ml_mine[2 * row + 1] = l;
-      tc_fence_before_sync();
-      mbar_arrive(&epi[0]);
-      if (!mbar_wait(&epi[0], items & 1, ab)) { ok = false; break; }
-      tc_fence_after_sync();
-      const float m_o = ml_other[2 * row], l_o = ml_other[2 * row + 1];
-      const float m_all = fmaxf(m_used, m_o);
-      const bool have_me = mine > 0, have_ot = ((nblk - (g ^ 1) + 1) >> 1) > 0;   // uniform over the CTA
-      const float w_me = have_me ? ex2(m_used - m_all) : 0.f;
-      const float w_ot = have_ot ? ex2(m_o - m_all) : 0.f;
-      const float l_all = l * w_me + l_o * w_ot;
-      const float inv_l = 1.f / l_all;
-      const float f_me = w_me * inv_l, f_ot = w_ot * inv_l;
-      const uint32_t tmem_ot_o = tmem_o + (g ^ 1) * 128 + lane_sel;
-      const long long tok = static_cast<long long>(b) * p.S + qb * kFaBM + row;
-      elem_t* orow = p.o + tok * p.o_pitch + static_cast<long long>(h) * kFaD;
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = 2 * g + cc;                  // this warpgroup writes head-dim columns [64 g, 64 g + 64)
-        uint32_t r[32], t[32];
-        float acc[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-        if (have_me) {                             // a stream without key blocks never wrote its accumulator
-          tmem_ld_32x32(tmem_my_o + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[i] = __uint_as_float(r[i]) * f_me;
-        }
-        if (have_ot) {
-          tmem_ld_32x32(tmem_ot_o + c * 32, t);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[i] += __uint_as_float(t[i]) * f_ot;
-        }
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          uint4 v;
-          v.x = pack_e2(acc[i + 0], acc[i + 1]);
-          v.y = pack_e2(acc[i + 2], acc[i + 3]);
-          v.z = pack_e2(acc[i + 4], acc[i + 5]);
-          v.w = pack_e2(acc[i + 6], acc[i + 7]);
-          *reinterpret_cast<uint4*>(orow + c * 32 + i) = v;
-        }
-      }
-      if (g == 0 && p.lse) {
-        p.lse[(static_cast<long long>(b) * p.H + h) * p.S + qb * kFaBM + row] =
-            (m_all + log2f(l_all)) * 0.6931471805599453f;
-      }
-      // both accumulators and both (max, sum) scratch rows have been read: the next item may overwrite them
-      tc_fence_before_sync();
-      mbar_arrive(&epi[1]);
-      if (!mbar_wait(&epi[1], items & 1, ab)) { ok = false; break; }
-    }
-  }
-
-  tc_fence_before_sync();
-  __syncthreads();
-  if (*cta_abort && threadIdx.x == 0) {
-    // a wait was abandoned: give bulk copies that may still be in flight a bounded time to land
-    const unsigned long long t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 100000000ull) {
-      if (mbar_try_wait(q_full, 0) && mbar_try_wait(q_full, 1)) break;
-    }
-  }
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 512);
-  }
-}
-
 }  // namespace MSB_ELEM_NS
 }  // namespace msb
 
 using namespace msb;
 using namespace msb::MSB_ELEM_NS;
-
-// 2 = the two-stream kernel (default), 1 = the single-stream kernel.
-static int g_fa_fwd_variant = 2;
-MSB_EXPORT int MSB_FN(msb_flash_attn_fwd_variant)(int v) {
-  const int old = g_fa_fwd_variant;
-  if (v == 1 || v == 2) g_fa_fwd_variant = v;
-  return old;
-}
 
 // q [B,S,H,128], k/v [B,S,Hk,128] with token pitches (elements) q_pitch / k_pitch / v_pitch; o [B,S,H,128] with o_pitch.
 // S must be a multiple of 128.  lse (fp32 [B,H,S]) may be null.
@@ -742,8 +376,6 @@ MSB_EXPORT int MSB_FN(msb_flash_attn_fwd)(const void* q, const void* k, const vo
   if (!configured) {
     MSB_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         FaSmem::kBytes));
-    MSB_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        Fa2Smem::kBytes));
     configured = true;
   }
   FaParams p;
@@ -757,10 +389,7 @@ MSB_EXPORT int MSB_FN(msb_flash_attn_fwd)(const void* q, const void* k, const vo
   p.scale_log2 = scale * 1.4426950408889634f;
   const int total = B * H * (S / 128);
   const int grid = total < sm_count() ? total : sm_count();
-  if (g_fa_fwd_variant == 2)
-    flash_fwd2_kernel<<<grid, kFa2Threads, Fa2Smem::kBytes, static_cast<cudaStream_t>(stream_)>>>(tq, tk, tv, p);
-  else
-    flash_fwd_kernel<<<grid, kFaThreads, FaSmem::kBytes, static_cast<cudaStream_t>(stream_)>>>(tq, tk, tv, p);
+  flash_fwd_kernel<<<grid, kFaThreads, FaSmem::kBytes, static_cast<cudaStream_t>(stream_)>>>(tq, tk, tv, p);
   MSB_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }

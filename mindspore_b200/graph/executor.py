@@ -39,6 +39,7 @@ class GraphExecutor:
         self.memory_plan = self._plan_memory()
         self._comm_stream = None
         self._cuda_graph = None
+        self.allow_cuda_graph = True      # a caller that captures the run itself (the micro-batch runner) clears it
         self._static_inputs = None
         self._static_outputs = None
         self._runs = 0
@@ -82,7 +83,7 @@ class GraphExecutor:
         return {"arena_bytes": int(total), "sum_bytes": int(sum(sizes)), "tensors": len(sizes)}
 
     def run(self, inputs):
-        use_cg = context.get_context("enable_cuda_graph") and inputs and all(
+        use_cg = self.allow_cuda_graph and context.get_context("enable_cuda_graph") and inputs and all(
             isinstance(t, torch.Tensor) and t.is_cuda for t in inputs)
         if not use_cg:
             return self._run_nodes(inputs)

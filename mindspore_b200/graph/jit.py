@@ -233,7 +233,13 @@ class _Recorder(TorchFunctionMode):
                 self.depth -= 1
         vals = []
         for g, t, n in zip(gs, in_targets + w_targets, grad_nodes):
+            in_accumulator = g is None and getattr(t, "main_grad", None) is not None
+            if in_accumulator:
+                # the operator's backward added this gradient into the parameter's fp32 accumulator: no graph value
+                g = torch.zeros((), dtype=t.dtype, device=t.device).expand(t.shape)
             v = (torch.zeros_like(t.detach()) if g is None else g).detach().as_subclass(Tensor)
+            if in_accumulator:
+                v.in_accumulator = True
             self.node_of[id(v)] = n
             self.keep.append(v)
             vals.append(v)

@@ -160,7 +160,9 @@ class TrainOneStepCell(Cell):
         if self.reducer_flag:
             self.grad_reducer = DistributedGradReducer(self.weights)
         self.use_arena = getattr(optimizer, "use_arena", False)
-        self._use_graph = None
+        # an arena step is driven from the host (micro-batch schedule, bucket overlap, fused optimizer launch); in
+        # GRAPH_MODE its compiled unit is the micro-batch forward + backward (``_MicroBatchRunner``), not this cell
+        self._use_graph = False if self.use_arena else None
 
     def _micro_runner(self, network, scale):
         """Callable running forward + backward of one micro-batch.  With the context option ``enable_cuda_graph``
@@ -223,6 +225,15 @@ class TrainOneStepCell(Cell):
             dp = getattr(opt, "_dp", None)
             if dp is not None:
                 dp.begin_step()                # buckets are all-reduced as backward completes them
+            if context.get_context("mode") == context.GRAPH_MODE and getattr(net, "_use_graph", None) is not False:
+                loss = self._micro_runner(net, scale)(inputs)
+                _collect_stray_grads(self.weights)
+                opt.sync_model_parallel_grads()
+                opt.sync_data_parallel_grads()
+                if self.grad_reducer is not None:
+                    from ..parallel.data_parallel import allreduce_arena_grads
+                    allreduce_arena_grads(opt.arena, self.grad_reducer)
+                return loss.detach()
             with torch.enable_grad():
                 loss = net(*inputs)
             if isinstance(scale, torch.Tensor):
@@ -280,6 +291,7 @@ class _MicroBatchRunner:
         self.network, self.scale = network, scale
         self.calls = 0
         self.graph = None
+        self._compiled = None
         self.static_inputs = None
         self.static_loss = None
         self.launches_per_replay = 0
@@ -295,9 +307,48 @@ class _MicroBatchRunner:
         else:
             self.scale = scale
 
+    def _compiled_graph(self, inputs):
+        """GRAPH_MODE: forward + backward of the micro-batch traced once into one graph - primitives, the collectives
+        that the shard strategies insert and the reverse-mode nodes - which goes through the pass pipeline (pattern
+        fusion, simplification, communication passes; ``save_graphs`` dumps each) and then runs on the graph executor.
+        The weight gradients never appear as graph values: the reverse-mode nodes of the parameter-owning operators
+        accumulate into the flat fp32 gradient arena, exactly as their eager backward does.  The call that traces is
+        also the first real execution (nothing is rolled back)."""
+        if self._compiled is None:
+            from ..common.parameter import ParameterTuple
+            from ..graph import jit as _jit
+            from ..ops.composite import GradOperation
+            net = self.network
+            weights = ParameterTuple(net.trainable_params())
+            grad = GradOperation(get_by_list=True, sens_param=True)
+            runner = self
+
+            def forward_backward(*xs):
+                loss = net(*xs)
+                sc = runner.scale
+                sens = torch.ones_like(loss) * (sc.to(loss.dtype) if isinstance(sc, torch.Tensor) else sc)
+                grads = grad(net, weights)(*xs, sens)
+                for w, g in zip(weights, grads):
+                    # operators without an accumulator-aware backward hand their weight gradient back as a value
+                    if not getattr(g, "in_accumulator", False) and getattr(w, "main_grad", None) is not None:
+                        w.main_grad.add_(g.to(w.main_grad.dtype))
+                return loss
+            self._compiled = _jit._compile(forward_backward, tuple(inputs), {}, type(net).__name__ + "_microbatch", None)
+            self._compiled.executor.allow_cuda_graph = False      # this runner captures (``__call__``), not the executor
+            self._compiled_scale = self.scale
+            first = self._compiled.first_outputs
+            return first.detach() if isinstance(first, torch.Tensor) else first
+        if not isinstance(self.scale, torch.Tensor) and self.scale != self._compiled_scale:
+            raise RuntimeError("the loss scale baked into the compiled micro-batch changed (%r -> %r); pass it as a "
+                               "tensor to change it between steps" % (self._compiled_scale, self.scale))
+        out = self._compiled(*inputs)
+        return out.detach() if isinstance(out, torch.Tensor) else out
+
     def _eager(self, inputs):
         from ..parallel import fused_comm
         fused_comm.step_fence()
+        if context.get_context("mode") == context.GRAPH_MODE and getattr(self.network, "_use_graph", None) is not False:
+            return self._compiled_graph(inputs)
         with torch.enable_grad():
             loss = self.network(*inputs)
         sc = self.scale.to(loss.dtype) if isinstance(self.scale, torch.Tensor) else self.scale
