@@ -344,6 +344,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }
 
 
+
 }  // namespace MSB_ELEM_NS
 }  // namespace msb
 

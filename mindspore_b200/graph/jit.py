@@ -42,6 +42,23 @@ def _is_tensor(x):
     return isinstance(x, torch.Tensor)
 
 
+_SYMBOLIC_GRADS = False
+
+
+class symbolic_gradients:
+    """Within this context a trace builds its reverse-mode nodes without computing concrete gradients: the values
+    that ``GradOperation`` hands back during the trace are zero placeholders.  For callers that only want the graph
+    and run it afterwards (the arena micro-batch, whose first real execution is the compiled graph itself)."""
+
+    def __enter__(self):
+        global _SYMBOLIC_GRADS
+        self._old, _SYMBOLIC_GRADS = _SYMBOLIC_GRADS, True
+
+    def __exit__(self, *exc):
+        global _SYMBOLIC_GRADS
+        _SYMBOLIC_GRADS = self._old
+
+
 class _Recorder(TorchFunctionMode):
     """Records executed torch-level calls into an fx.Graph while really executing them."""
 
@@ -54,6 +71,7 @@ class _Recorder(TorchFunctionMode):
         self.node_of = {}   # id(tensor) -> fx.Node
         self.alias = {}     # (data_ptr, shape, stride, dtype) -> fx.Node, for untracked aliases (as_subclass ...)
         self.keep = []      # keep recorded tensors alive so ids and data pointers stay unique
+        self.symbolic_grads = _SYMBOLIC_GRADS   # trace_grad builds the reverse-mode nodes without running a tape
 
     @staticmethod
     def _akey(t):
@@ -216,26 +234,33 @@ class _Recorder(TorchFunctionMode):
         if sens is not None:
             seeds = [self.arg(s) if _is_tensor(s) else s for s in (_flat_tensors(sens) or [sens])]
         grad_nodes = build_backward(fg, fwd_nodes, out_nodes, target_nodes, seeds)
-        # concrete values for the rest of the trace: compute with the tape
-        with torch.enable_grad():
-            work = [x.detach().requires_grad_(True) if _is_tensor(x) and x.is_floating_point() else x for x in inputs]
-            self.depth += 1
-            try:
-                o2 = fn(*work)
-                p2 = o2[0] if has_aux else o2
-                outs = [o for o in _flat_tensors(p2) if o.requires_grad]
-                tg = [w for w, x in zip(work, inputs) if any(x is t for t in in_targets)] + w_targets
-                sd = [torch.ones_like(o) for o in outs] if sens is None else \
-                    [(s if _is_tensor(s) else torch.full_like(o, float(s))).to(o.dtype).expand_as(o)
-                     for s, o in zip(_flat_tensors(sens) or [sens] * len(outs), outs)]
-                gs = torch.autograd.grad(outs, tg, sd, allow_unused=True) if outs and tg else [None] * len(tg)
-            finally:
-                self.depth -= 1
+        if self.symbolic_grads:
+            # the caller wants the graph only (it runs the compiled graph afterwards for the real values): no second
+            # forward and no tape, so tracing a large network holds one forward's activations, not three
+            gs = [None] * (len(in_targets) + len(w_targets))
+        else:
+            # concrete values for the rest of the trace: compute with the tape
+            with torch.enable_grad():
+                work = [x.detach().requires_grad_(True) if _is_tensor(x) and x.is_floating_point() else x
+                        for x in inputs]
+                self.depth += 1
+                try:
+                    o2 = fn(*work)
+                    p2 = o2[0] if has_aux else o2
+                    outs = [o for o in _flat_tensors(p2) if o.requires_grad]
+                    tg = [w for w, x in zip(work, inputs) if any(x is t for t in in_targets)] + w_targets
+                    sd = [torch.ones_like(o) for o in outs] if sens is None else \
+                        [(s if _is_tensor(s) else torch.full_like(o, float(s))).to(o.dtype).expand_as(o)
+                         for s, o in zip(_flat_tensors(sens) or [sens] * len(outs), outs)]
+                    gs = torch.autograd.grad(outs, tg, sd, allow_unused=True) if outs and tg else [None] * len(tg)
+                finally:
+                    self.depth -= 1
         vals = []
         for g, t, n in zip(gs, in_targets + w_targets, grad_nodes):
-            in_accumulator = g is None and getattr(t, "main_grad", None) is not None
-            if in_accumulator:
-                # the operator's backward added this gradient into the parameter's fp32 accumulator: no graph value
+            in_accumulator = g is None and getattr(t, "main_grad", None) is not None and not self.symbolic_grads
+            if in_accumulator or (g is None and self.symbolic_grads):
+                # no graph value: the operator's backward added this gradient into the parameter's fp32 accumulator
+                # (or no concrete gradients are computed at all in this trace)
                 g = torch.zeros((), dtype=t.dtype, device=t.device).expand(t.shape)
             v = (torch.zeros_like(t.detach()) if g is None else g).detach().as_subclass(Tensor)
             if in_accumulator:

@@ -278,6 +278,15 @@ class TrainOneStepCell(Cell):
         return loss
 
 
+def fold_grad_(main_grad, grad):
+    """Graph node of a compiled micro-batch: adds a weight gradient that came back as a value into the fp32
+    accumulator.  Operators with an accumulator-aware backward add theirs inside the reverse-mode node and hand back
+    nothing (``None``)."""
+    if grad is not None:
+        main_grad.add_(grad.to(main_grad.dtype))
+    return main_grad
+
+
 class _MicroBatchRunner:
     """Forward + backward of one micro-batch, eagerly or as a replayed CUDA graph.
 
@@ -317,27 +326,28 @@ class _MicroBatchRunner:
         if self._compiled is None:
             from ..common.parameter import ParameterTuple
             from ..graph import jit as _jit
-            from ..ops.composite import GradOperation
+            from ..ops.composite import _run_grad
             net = self.network
-            weights = ParameterTuple(net.trainable_params())
-            grad = GradOperation(get_by_list=True, sens_param=True)
+            weights = list(ParameterTuple(net.trainable_params()))
             runner = self
 
             def forward_backward(*xs):
-                loss = net(*xs)
                 sc = runner.scale
-                sens = torch.ones_like(loss) * (sc.to(loss.dtype) if isinstance(sc, torch.Tensor) else sc)
-                grads = grad(net, weights)(*xs, sens)
+                example = xs[0]
+                sens = torch.ones((), device=example.device) * (sc if isinstance(sc, torch.Tensor) else float(sc))
+                loss, _, grads = _run_grad(net, xs, weights, sens, False, None, False, True)
                 for w, g in zip(weights, grads):
-                    # operators without an accumulator-aware backward hand their weight gradient back as a value
-                    if not getattr(g, "in_accumulator", False) and getattr(w, "main_grad", None) is not None:
-                        w.main_grad.add_(g.to(w.main_grad.dtype))
+                    if getattr(w, "main_grad", None) is not None:
+                        _jit.leaf_call(fold_grad_, (w.main_grad, g), {})
                 return loss
-            self._compiled = _jit._compile(forward_backward, tuple(inputs), {}, type(net).__name__ + "_microbatch", None)
+            # The trace runs one forward (to record it) and builds the reverse-mode nodes symbolically: nothing is
+            # accumulated by it (the gradients it sees are zero placeholders), and the first real execution of this
+            # micro-batch is the run of the compiled graph below.
+            with _jit.symbolic_gradients():
+                self._compiled = _jit._compile(forward_backward, tuple(inputs), {}, type(net).__name__ + "_microbatch",
+                                               None)
             self._compiled.executor.allow_cuda_graph = False      # this runner captures (``__call__``), not the executor
             self._compiled_scale = self.scale
-            first = self._compiled.first_outputs
-            return first.detach() if isinstance(first, torch.Tensor) else first
         if not isinstance(self.scale, torch.Tensor) and self.scale != self._compiled_scale:
             raise RuntimeError("the loss scale baked into the compiled micro-batch changed (%r -> %r); pass it as a "
                                "tensor to change it between steps" % (self._compiled_scale, self.scale))

@@ -286,3 +286,24 @@ def test_llama_kernel_path_matches_fp32_reference():
     for p in ref_net.get_parameters():
         _close(got[p.name], p.grad, 6e-2, 1e-4)
     _status_ok()
+
+
+
+@pytest.mark.parametrize("B,S,H,causal", [(1, 128, 1, True), (1, 256, 2, False), (2, 512, 4, True), (1, 1024, 4, True)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_flash_attention_forward_lse(K, B, S, H, causal, dtype):
+    """Forward output and log-sum-exp against the fp32 reference, both element types."""
+    from mindspore_b200.ops import flash_attn_kernel as FK
+    from mindspore_b200.ops.attention import reference_attention
+    D = 128
+    q, k, v = (torch.randn(B, S, H, D, device=DEV).to(dtype) for _ in range(3))
+    sc = 1 / math.sqrt(D)
+    qf, kf, vf = q.float(), k.float(), v.float()
+    ref = reference_attention(qf, kf, vf, causal)
+    scores = torch.einsum("bqhd,bkhd->bhqk", qf, kf) * sc
+    if causal:
+        scores = scores.masked_fill(torch.ones(S, S, device=DEV, dtype=torch.bool).triu(1), float("-inf"))
+    o, lse, *_ = FK.fwd(q, k, v, causal, sc)
+    _close(o, ref, 2e-2)
+    _close(lse, torch.logsumexp(scores, -1), 1e-3, 1e-3)
+    _status_ok()
