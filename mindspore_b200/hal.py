@@ -54,9 +54,15 @@ class Stream:
         if self._s is not None:
             self._s.wait_stream(stream._s)
 
-    def synchronize(self):
-        if self._s is not None:
+    def synchronize(self, timeout=None):
+        if self._s is None:
+            return
+        if timeout is None:
             self._s.synchronize()
+            return
+        ev = torch.cuda.Event()
+        ev.record(self._s)
+        wait_event(ev.query, timeout, "the stream")
 
     def query(self):
         return self._s.query() if self._s is not None else True
@@ -120,9 +126,45 @@ def set_cur_stream(stream):
         torch.cuda.set_stream(stream._s)
 
 
-def synchronize():
-    if torch.cuda.is_available():
+class StreamSyncTimeout(RuntimeError):
+    """The device did not finish the work queued before ``synchronize(timeout=...)`` within the limit (a hung
+    collective after a peer was lost, typically): the caller can tear the communicator down and recover instead of
+    blocking for ever in the driver."""
+
+
+def wait_event(query, timeout, what="the device", poll_s=0.001, clock=None, sleep=None):
+    """Polls ``query()`` (true when done) until it holds or ``timeout`` seconds pass; raises StreamSyncTimeout."""
+    import time
+    clock = clock or time.monotonic
+    sleep = sleep or time.sleep
+    deadline = clock() + float(timeout)
+    while not query():
+        if clock() >= deadline:
+            raise StreamSyncTimeout("%s did not finish within %.1f s" % (what, float(timeout)))
+        sleep(poll_s)
+        poll_s = min(poll_s * 2, 0.05)
+
+
+def synchronize(timeout=None):
+    """Waits for all queued device work.  With ``timeout`` (seconds; default from ``MS_STREAM_SYNC_TIMEOUT`` when
+    set) the wait polls an event instead of blocking in the driver and raises ``StreamSyncTimeout`` when it runs out;
+    afterwards the per-device status word of the kernels' own bounded waits is checked as well
+    (runtime/device/stream_synchronizer.cc:33-63 waits with a time limit when recovery is enabled)."""
+    import os
+    if not torch.cuda.is_available():
+        return
+    if timeout is None and os.environ.get("MS_STREAM_SYNC_TIMEOUT"):
+        timeout = float(os.environ["MS_STREAM_SYNC_TIMEOUT"])
+    if timeout is None:
         torch.cuda.synchronize()
+        return
+    ev = torch.cuda.Event()
+    ev.record()
+    wait_event(ev.query, timeout, "device %d" % torch.cuda.current_device())
+    from . import _native
+    status = _native.device_status(clear=False) if _native._cuda is not None else 0
+    if status:
+        raise StreamSyncTimeout("a kernel gave up a bounded wait (device status word %d)" % status)
 
 
 def memory_stats(device_target="GPU"):

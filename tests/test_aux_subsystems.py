@@ -3,6 +3,7 @@ import json
 import os
 
 import numpy as np
+import pytest
 import torch
 
 import mindspore_b200 as ms
@@ -126,3 +127,25 @@ def test_step_trace_splits_phases_exposed_communication_and_gaps():
     for r in rows:
         assert r["fp_ms"] == 0.4 and r["bp_ms"] == 0.3 and r["optimizer_ms"] == 0.2 and r["comm_ms"] == 0.3
         assert r["comm_exposed_ms"] == 0.2 and r["gap_ms"] == 0.1 and r["total_ms"] == 1.2 and r["kernels"] == 6
+
+
+def test_timed_synchronize_polls_and_gives_up():
+    """hal.wait_event (the core of synchronize(timeout=...)): returns once the query holds, raises after the limit;
+    driven by a fake clock, no device involved."""
+    from mindspore_b200 import hal
+    now = [0.0]
+    polls = []
+
+    def sleep(dt):
+        polls.append(dt)
+        now[0] += dt
+    state = {"n": 0}
+
+    def done_after_three():
+        state["n"] += 1
+        return state["n"] > 3
+    hal.wait_event(done_after_three, 5.0, clock=lambda: now[0], sleep=sleep)
+    assert state["n"] == 4 and len(polls) == 3 and polls[1] > polls[0]
+    with pytest.raises(hal.StreamSyncTimeout, match="did not finish within 2.0 s"):
+        hal.wait_event(lambda: False, 2.0, what="device 0", clock=lambda: now[0], sleep=sleep)
+    hal.synchronize(timeout=1.0)          # no GPU here: returns at once
