@@ -103,7 +103,8 @@ def _build_lib(srcs, hdrs, compiler_cmd, flags, lib, link_cmd, verbose):
 def build_cuda(verbose=True) -> str:
     srcs = sorted(os.path.join(CSRC_CUDA, f) for f in os.listdir(CSRC_CUDA) if f.endswith(".cu"))
     nvcc = _nvcc()
-    return _build_lib(srcs, _headers(CSRC_CUDA), [nvcc], NVCC_FLAGS, CUDA_LIB,
+    shared = [h for h in _headers(CSRC_HOST) if h.endswith(".hpp")]      # headers the device code includes too
+    return _build_lib(srcs, _headers(CSRC_CUDA) + shared, [nvcc], NVCC_FLAGS, CUDA_LIB,
                       [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a"], verbose)
 
 
