@@ -203,7 +203,11 @@ def get_process_group_ranks(group=None):
 
 
 def create_group(group, rank_ids):
-    """Registers a named group.  Every rank of the job must call it with the same arguments."""
+    """Registers a named group.  Its members must call it with the same arguments; ranks outside it may call it too
+    or not at all (groups are often made lazily by the ranks that need them: the model-parallel group of one pipeline
+    stage, a ring of one data-parallel slice).  That is why the process group is created with local synchronisation:
+    torch then derives the group's rendezvous prefix from its ranks, so two disjoint groups made at the same moment
+    by different ranks do not meet under one counter-based name."""
     _check_inited()
     if not isinstance(group, str):
         raise TypeError("For 'create_group', the argument 'group' must be type of string")
@@ -222,7 +226,12 @@ def create_group(group, rank_ids):
             return
         pg = None
         if not _state.simulation:
-            pg = dist.new_group(rank_ids) if len(rank_ids) < _state.world else dist.group.WORLD
+            if len(rank_ids) == _state.world:
+                pg = dist.group.WORLD
+            elif _state.rank in rank_ids:
+                pg = dist.new_group(rank_ids, use_local_synchronization=True)
+            else:
+                pg = None                      # not a member: nothing to create, the name is only recorded
         _state.groups[group] = _Group(group, rank_ids, pg)
 
 

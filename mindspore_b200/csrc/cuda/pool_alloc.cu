@@ -8,6 +8,8 @@
 
 #include "../host/mem_pool.hpp"
 
+#include <new>
+
 namespace {
 
 constexpr int kMaxDev = 64;
@@ -43,7 +45,7 @@ MSB_EXPORT void msb_cuda_pool_configure(unsigned long long block_size, unsigned 
 
 MSB_EXPORT void* msb_cuda_pool_malloc(long long size, int device, void* stream) {
   msb::BestFitPool* pool = pool_for(device);
-  if (pool == nullptr) return nullptr;
+  if (pool == nullptr) throw std::bad_alloc();
   int prev = 0;
   cudaGetDevice(&prev);
   if (prev != device) cudaSetDevice(device);
@@ -56,6 +58,12 @@ MSB_EXPORT void* msb_cuda_pool_malloc(long long size, int device, void* stream) 
     p = pool->allocate(static_cast<size_t>(size), reinterpret_cast<uint64_t>(stream));
   }
   if (prev != device) cudaSetDevice(prev);
+  if (p == nullptr) {
+    // the hook has no error return and torch does not test the pointer: an exception is the only way to refuse
+    // (it travels through torch's C++ frames and surfaces in Python as MemoryError)
+    msb::set_last_error("device pool: cannot serve %lld bytes on device %d (limit %zu bytes)", size, device, g_max_size);
+    throw std::bad_alloc();
+  }
   return p;
 }
 

@@ -38,6 +38,13 @@ def zeros_like_if_none(g, ref):
     return torch.zeros_like(ref.detach()) if g is None else g
 
 
+def grad_or_none(g, ref):
+    """The gradient as it came out of reverse mode, ``None`` included (an operator that adds its weight gradient
+    into the parameter's accumulator hands back nothing): for callers that fold gradients themselves and must not
+    pay a zero tensor of every weight's size per run."""
+    return g
+
+
 def seed_like(sens, ref):
     if isinstance(sens, torch.Tensor):
         s = sens.to(ref.dtype)
@@ -65,7 +72,7 @@ def _tensor_arg_nodes(node):
     return out
 
 
-def build_backward(fg, fwd_nodes, out_nodes, target_nodes, seeds=None):
+def build_backward(fg, fwd_nodes, out_nodes, target_nodes, seeds=None, none_as_zero=True):
     g = fg.graph
     fwd_set = set(fwd_nodes)
     for n in fwd_nodes:
@@ -117,5 +124,5 @@ def build_backward(fg, fwd_nodes, out_nodes, target_nodes, seeds=None):
     grads = []
     for t in target_nodes:
         gn = total(t)
-        grads.append(g.call_function(zeros_like_if_none, (gn, t)))
+        grads.append(g.call_function(zeros_like_if_none if none_as_zero else grad_or_none, (gn, t)))
     return grads

@@ -233,7 +233,8 @@ class _Recorder(TorchFunctionMode):
         seeds = None
         if sens is not None:
             seeds = [self.arg(s) if _is_tensor(s) else s for s in (_flat_tensors(sens) or [sens])]
-        grad_nodes = build_backward(fg, fwd_nodes, out_nodes, target_nodes, seeds)
+        grad_nodes = build_backward(fg, fwd_nodes, out_nodes, target_nodes, seeds,
+                                    none_as_zero=not self.symbolic_grads)
         if self.symbolic_grads:
             # the caller wants the graph only (it runs the compiled graph afterwards for the real values): no second
             # forward and no tape, so tracing a large network holds one forward's activations, not three

@@ -87,13 +87,17 @@ def linear(x, w, bias=None):
 
 
 class _MatMulFn(torch.autograd.Function):
-    """General 2-D/3-D bf16 matmul with transpose flags (MatMul / BatchMatMul primitives)."""
+    """General 2-D/3-D 16-bit matmul with transpose flags (MatMul / BatchMatMul primitives).  A 2-D second operand
+    that owns an fp32 gradient accumulator (``main_grad``, a parameter of an arena optimizer) gets its gradient added
+    there by the wgrad GEMM's epilogue, like ``linear``: no 16-bit ``.grad`` tensor, no separate accumulation pass per
+    micro-batch."""
 
     @staticmethod
     def forward(ctx, a, b, ta, tb):
         # logical C = op(a) @ op(b); kernel wants A=[M,K] (or stored [K,M]) and B as [N,K] (or stored [K,N])
         ctx.save_for_backward(a, b)
         ctx.ta, ctx.tb = ta, tb
+        ctx.b_ref = b
         return K.gemm(a, b, a_mn=ta, b_mn=not tb)
 
     @staticmethod
@@ -108,16 +112,25 @@ class _MatMulFn(torch.autograd.Function):
             else:        # a stored [K,M]: da[K,M] = op(b) @ dc^T -> A' logical [K_out, N_red], B' = dc [M, N_red]
                 da = K.gemm(b, dc, a_mn=tb)
         if ctx.needs_input_grad[1]:
+            mg = getattr(ctx.b_ref, "main_grad", None)
+            acc = mg is not None and b.dim() == 2 and tuple(mg.shape) == tuple(b.shape)
+            kw = dict(out=mg, accumulate=True) if acc else {}
             if not tb:   # b stored [K,N]: db[K,N] = op(a)^T @ dc -> A logical [K, M(red)], B logical [N, M(red)]
-                db = K.gemm(a, dc, a_mn=not ta, b_mn=True)
+                db = K.gemm(a, dc, a_mn=not ta, b_mn=True, **kw)
             else:        # b stored [N,K]: db[N,K] = dc^T @ op(a) -> A logical [N, M(red)], B logical [K, M(red)]
-                db = K.gemm(dc, a, a_mn=True, b_mn=not ta)
+                db = K.gemm(dc, a, a_mn=True, b_mn=not ta, **kw)
+            if acc:
+                db = None
+                ctx.b_ref.grad_ready = True
+                _written(ctx.b_ref)
         return da, db, None, None
 
 
 def matmul(a, b, transpose_a=False, transpose_b=False):
     if _use_kernel(a, b, fp16_ok=True) and a.dim() == b.dim() and a.dim() in (2, 3) and a.is_contiguous() and b.is_contiguous() \
             and all(s % 8 == 0 for s in a.shape[-2:]) and all(s % 8 == 0 for s in b.shape[-2:]):
+        if b.dim() == 2 and getattr(b, "main_grad", None) is not None:
+            _producer(b)
         return _MatMulFn.apply(a, b, bool(transpose_a), bool(transpose_b))
     aa = a.transpose(-1, -2) if transpose_a else a
     bb = b.transpose(-1, -2) if transpose_b else b

@@ -307,3 +307,24 @@ def test_flash_attention_forward_lse(K, B, S, H, causal, dtype):
     _close(o, ref, 2e-2)
     _close(lse, torch.logsumexp(scores, -1), 1e-3, 1e-3)
     _status_ok()
+
+
+@pytest.mark.parametrize("tb", [True, False])
+def test_matmul_primitive_accumulates_into_main_grad(K, tb):
+    """MatMul whose weight owns an fp32 accumulator: two backward passes leave 2 x the weight gradient there (added
+    by the wgrad GEMM epilogue) and no ``.grad``; the input gradient is returned as usual."""
+    from mindspore_b200.ops import fused
+    M, N, Kd = 512, 384, 256
+    a = torch.randn(M, Kd, device=DEV).bfloat16().requires_grad_(True)
+    w = torch.randn((N, Kd) if tb else (Kd, N), device=DEV).bfloat16().requires_grad_(True)
+    w.main_grad = torch.zeros(w.shape, dtype=torch.float32, device=DEV)
+    dy = torch.randn(M, N, device=DEV).bfloat16()
+    for _ in range(2):
+        fused.matmul(a, w, False, tb).backward(dy)
+    assert w.grad is None
+    wf = w.detach().float()
+    ref_w = dy.float().t() @ a.detach().float() if tb else a.detach().float().t() @ dy.float()
+    ref_a = dy.float() @ wf if tb else dy.float() @ wf.t()
+    _close(w.main_grad, 2 * ref_w, 1e-2)
+    _close(a.grad, 2 * ref_a, 2e-2)
+    _status_ok()

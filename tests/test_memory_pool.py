@@ -88,22 +88,20 @@ ms.set_context(device_target="GPU", mempool_block_size="256MB", max_device_memor
 MP.enable_device_pool()
 x = torch.randn(4096, 4096, device="cuda")
 y = x @ x
-z = torch.empty(64 << 20, dtype=torch.uint8, device="cuda")
+z = torch.empty(1 << 30, dtype=torch.uint8, device="cuda")      # larger than a block: gets a block of its own
 st = MP.device_pool_stats()
-assert st["used"] >= 2 * 64 * 2 ** 20 + (64 << 20) and st["reserved"] >= st["used"] and st["blocks"] >= 1, st
+assert st["used"] >= 2 * 64 * 2 ** 20 + (1 << 30) and st["reserved"] >= st["used"] and st["blocks"] >= 2, st
 ref = float((x.cpu() @ x.cpu())[0, 0])
 assert abs(float(y[0, 0]) - ref) <= 1e-2 * max(1.0, abs(ref))
 del x, y, z
 st2 = MP.device_pool_stats()
 assert st2["used"] < st["used"], (st, st2)
-freed = MP.device_pool_release_idle()
-assert freed > 0 and MP.device_pool_stats()["reserved"] < st["reserved"]
+freed = MP.device_pool_release_idle()      # the block of z has no live buffer left (library workspaces live elsewhere)
+assert freed >= 1 << 30 and MP.device_pool_stats()["reserved"] <= st["reserved"] - (1 << 30), (freed, st)
 try:
     torch.empty(9 << 30, dtype=torch.uint8, device="cuda")
-except torch.OutOfMemoryError:
-    print("limit ok")
-except RuntimeError as e:
-    print("limit ok", str(e)[:60])
+except (MemoryError, RuntimeError) as e:
+    print("limit ok", type(e).__name__, str(e)[:60])
 else:
     raise SystemExit("the 8 GB limit was not enforced")
 print("pool ok", st)
