@@ -40,6 +40,7 @@ class GraphExecutor:
         self._comm_stream = None
         self._cuda_graph = None
         self.allow_cuda_graph = True      # a caller that captures the run itself (the micro-batch runner) clears it
+        self.use_comm_stream = True       # ... and this: inside its capture every node runs on the capturing stream
         self._static_inputs = None
         self._static_outputs = None
         self._runs = 0
@@ -126,7 +127,7 @@ class GraphExecutor:
                     kwargs = fx.node.map_arg(n.kwargs, lambda a: env[a])
                     if n.meta.get("requires_vjp") and n.name in self.vjp_needed:
                         env[n] = self._run_recorded(n, args, kwargs, saved)
-                    elif on_cuda and n.meta.get("comm_stream"):
+                    elif on_cuda and n.meta.get("comm_stream") and self.use_comm_stream:
                         # a collective whose result is needed later: issue it on the communication stream, the
                         # nodes up to its first user overlap it (optimize_gradients_allreduce_overlap.cc's role)
                         if self._comm_stream is None:

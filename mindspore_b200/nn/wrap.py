@@ -347,6 +347,7 @@ class _MicroBatchRunner:
                 self._compiled = _jit._compile(forward_backward, tuple(inputs), {}, type(net).__name__ + "_microbatch",
                                                None)
             self._compiled.executor.allow_cuda_graph = False      # this runner captures (``__call__``), not the executor
+            self._compiled.executor.use_comm_stream = not context.get_context("enable_cuda_graph")
             self._compiled_scale = self.scale
         if not isinstance(self.scale, torch.Tensor) and self.scale != self._compiled_scale:
             raise RuntimeError("the loss scale baked into the compiled micro-batch changed (%r -> %r); pass it as a "

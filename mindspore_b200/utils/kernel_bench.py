@@ -13,6 +13,7 @@ from __future__ import annotations
 import argparse
 import json
 import math
+import os
 import sys
 
 import torch
@@ -167,9 +168,109 @@ def bench_elementwise(args):
     _emit(kernel="adamw", n=nel, ms=round(ms, 4), gbs=round(nel * (4 * 7 + 2) / ms / 1e6, 1), **_clk(ms))
 
 
+def bench_fused_comm(args):
+    """The four model-parallel collective GEMMs of a Llama-2-7B layer (one micro-batch of 4096 tokens, mp = world
+    size): fused NVLink kernel vs the same GEMM followed / preceded by the NCCL collective vs the GEMM alone.  Run
+    under torchrun, one rank per GPU; every number is device time of calls replayed from one CUDA graph (no host
+    launch time), max over ranks.  Also prints the roofline of each op: the slower of its FLOPs at the measured GEMM
+    rate and its NVLink bytes at the measured per-direction peer bandwidth."""
+    import json
+    import torch.distributed as dist
+    import mindspore_b200 as ms
+    from ..communication import comm_func as CF
+    from ..communication import init
+    from ..communication import management as M
+    from ..ops import fused
+    from ..parallel import fused_comm as FC
+    from ..parallel import tp as TP
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    if world < 2:
+        print("fused_comm needs torchrun with at least 2 ranks", file=sys.stderr)
+        return
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    ms.set_context(device_target="GPU", device_id=local)
+    init("nccl")
+    ms.set_auto_parallel_context(parallel_mode="semi_auto_parallel", device_num=world, global_rank=rank,
+                                 full_batch=True)
+    tp, g = TP.TPGroup(), M._group(None)
+
+    def timed(fn, iters=10, reps=5):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(iters):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / (iters * reps)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        del graph
+        return t.item() * 1000.0                                     # microseconds
+
+    peaks = {}
+    try:
+        root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except (OSError, ValueError):
+        pass
+    tflops = float(peaks.get("bf16_tflops", 1590.0))
+    link_gbs = 770.0                                                 # measured peer copy, per direction per GPU
+    T, H, F = 4096, 4096, 11008
+    bf = dict(device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        xs = torch.randn(T // world, H, **bf)
+        wqkv, wgu = torch.randn(3 * H // world, H, **bf), torch.randn(2 * F // world, H, **bf)
+        xo, wo = torch.randn(T, H // world, **bf), torch.randn(H, H // world, **bf)
+        xd, wd = torch.randn(T, F // world, **bf), torch.randn(H, F // world, **bf)
+        xf = torch.randn(T, H, **bf)
+        cases = (
+            ("allgather+qkv", (T, 3 * H // world, H), T * H * 2 * (world - 1) / world,
+             lambda: FC.allgather_matmul(xs, wqkv, tp), lambda: fused.linear(CF._all_gather(xs, g), wqkv),
+             lambda: fused.linear(xf, wqkv)),
+            ("allgather+gate_up", (T, 2 * F // world, H), T * H * 2 * (world - 1) / world,
+             lambda: FC.allgather_matmul(xs, wgu, tp), lambda: fused.linear(CF._all_gather(xs, g), wgu),
+             lambda: fused.linear(xf, wgu)),
+            ("wo+reducescatter", (T, H, H // world), T * H * 2 * (world - 1) / world,
+             lambda: FC.matmul_reduce_scatter(xo, wo, tp), lambda: CF._reduce_scatter(fused.linear(xo, wo), "sum", g),
+             lambda: fused.linear(xo, wo)),
+            ("down+reducescatter", (T, H, F // world), T * H * 2 * (world - 1) / world,
+             lambda: FC.matmul_reduce_scatter(xd, wd, tp), lambda: CF._reduce_scatter(fused.linear(xd, wd), "sum", g),
+             lambda: fused.linear(xd, wd)))
+        for name, (m, n, k), link_bytes, f_fused, f_nccl, f_gemm in cases:
+            t_fused, t_nccl, t_gemm = timed(f_fused), timed(f_nccl), timed(f_gemm)
+            t_math = 2.0 * m * n * k / (tflops * 1e12) * 1e6
+            t_link = link_bytes / (link_gbs * 1e9) * 1e6
+            roof = max(t_math, t_link)
+            if rank == 0:
+                _emit(kernel=name, world=world, m=m, n=n, k=k, fused_us=round(t_fused, 1),
+                      gemm_plus_nccl_us=round(t_nccl, 1), gemm_alone_us=round(t_gemm, 1),
+                      roofline_us=round(roof, 1), bound="link" if t_link > t_math else "math",
+                      fused_of_roofline=round(roof / t_fused, 3))
+    from .. import _native
+    torch.cuda.synchronize()
+    st = torch.tensor([_native.device_status()], device="cuda")
+    dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        _emit(device_status=int(st.item()))
+    dist.barrier()
+    M.release()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="kernel_bench")
-    ap.add_argument("what", choices=["gemm", "attention", "elementwise"])
+    ap.add_argument("what", choices=["gemm", "attention", "elementwise", "fused_comm"])
     ap.add_argument("--shapes", nargs="*", help="gemm: MxNxK ...")
     ap.add_argument("--layout", help="gemm: 00 (fwd), 01 (dgrad) or 11 (wgrad)")
     ap.add_argument("--bn", type=int, default=0)
@@ -185,6 +286,9 @@ def main(argv=None):
     if not torch.cuda.is_available():
         print("kernel_bench needs a CUDA device", file=sys.stderr)
         return 1
+    if args.what == "fused_comm":
+        bench_fused_comm(args)
+        return 0
     global _sampler, _min_ms
     _min_ms = args.min_ms
     if not args.once:
