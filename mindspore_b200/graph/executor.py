@@ -162,10 +162,15 @@ class GraphExecutor:
             if isinstance(a, torch.Tensor):
                 if a.is_floating_point() or a.is_complex():
                     d = a.detach()
-                    if type(a) is not type(d) and hasattr(a, "main_grad"):
-                        d = a  # keep Parameter identity (main_grad accumulation, in-place updates)
-                    else:
-                        d.requires_grad_(True)
+                    if type(a) is not type(d) and getattr(a, "main_grad", None) is not None:
+                        # A parameter of an arena optimizer: the operator adds its gradient into ``main_grad`` and
+                        # hands back nothing.  It sees a fresh alias, not the parameter object: the parameter's
+                        # gradient accumulator node lives on the stream it was first used on, and differentiating
+                        # with respect to it inside a stream capture would tie the capture to that stream.
+                        d = d.as_subclass(type(a))
+                        d.__dict__.update(a.__dict__)        # name, layouts, main_grad, flags of the dispatcher
+                        d._param_ref = a
+                    d.requires_grad_(True)
                     leaves.append(d)
                     return d
                 leaves.append(None)

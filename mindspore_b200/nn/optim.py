@@ -51,6 +51,7 @@ def note_grad_producer(param):
     """Called in forward (with gradients enabled) by every op whose backward will accumulate into
     ``param.main_grad``.  A parameter used several times in one step (tied embedding / LM head, shared layers) has
     several producers; its gradient is complete only after the last of them has written."""
+    param = getattr(param, "_param_ref", param)     # the graph executor hands operators a fresh alias of the parameter
     if getattr(param, "main_grad", None) is not None and torch.is_grad_enabled():
         param._grad_writers = getattr(param, "_grad_writers", 0) + 1
 
@@ -59,6 +60,7 @@ def notify_grad_written(param):
     """Called by backward kernels right after they have accumulated ``param``'s gradient into its arena slice
     (``main_grad``).  Listeners are told once the last registered producer of this step has written; they use it to
     start the gradient collective of a bucket as soon as the bucket is complete."""
+    param = getattr(param, "_param_ref", param)
     n = getattr(param, "_grad_writers", 0)
     if n > 1:
         param._grad_writers = n - 1
