@@ -354,15 +354,7 @@ class _MicroBatchRunner:
         if not isinstance(self.scale, torch.Tensor) and self.scale != self._compiled_scale:
             raise RuntimeError("the loss scale baked into the compiled micro-batch changed (%r -> %r); pass it as a "
                                "tensor to change it between steps" % (self._compiled_scale, self.scale))
-        if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing() and \
-                os.environ.get("MSB200_GRAPH_BWD_INLINE", "1") == "1":
-            # The executor differentiates node by node (one autograd call per reverse-mode node).  Inside a stream
-            # capture those calls run on this thread: autograd's device worker thread has its own current stream,
-            # which is not part of the capture.
-            with torch.autograd.set_multithreading_enabled(False):
-                out = self._compiled(*inputs)
-        else:
-            out = self._compiled(*inputs)
+        out = self._compiled(*inputs)
         return out.detach() if isinstance(out, torch.Tensor) else out
 
     def _eager(self, inputs):
