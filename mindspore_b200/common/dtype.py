@@ -22,6 +22,50 @@ uint8 = ubyte = torch.uint8
 uint16 = getattr(torch, "uint16", torch.int16)
 uint32 = getattr(torch, "uint32", torch.int32)
 uint64 = getattr(torch, "uint64", torch.int64)
+ushort, uintc, uintp, uint = uint16, uint32, uint64, uint64          # C-style aliases (common/dtype.py:69-73)
+qint4x2 = torch.int8                                                  # two 4-bit values per byte: stored as bytes
+
+
+class TensorType:
+    """``TensorType(element_type)``: the type of a tensor whose elements have ``element_type``."""
+
+    def __init__(self, element_type=None):
+        self._element_type = element_type
+
+    def element_type(self):
+        return self._element_type
+
+    def __eq__(self, other):
+        return isinstance(other, TensorType) and other._element_type == self._element_type
+
+    def __hash__(self):
+        return hash(("TensorType", self._element_type))
+
+    def __repr__(self):
+        return "Tensor[%s]" % (dtype_to_pytype(self._element_type).__name__ if False else self._element_type)
+
+
+tensor_type = TensorType
+
+
+class Int:
+    """Integer type descriptor with a bit width, e.g. ``Int(32)``; compares equal to the matching dtype."""
+
+    _BY_BITS = {}
+
+    def __init__(self, nbits=64):
+        self.nbits = int(nbits)
+
+    def __eq__(self, other):
+        if isinstance(other, Int):
+            return other.nbits == self.nbits
+        return other is Int._BY_BITS.get(self.nbits)
+
+    def __hash__(self):
+        return hash(("Int", self.nbits))
+
+    def __repr__(self):
+        return "Int%d" % self.nbits
 bool_ = torch.bool
 complex64 = torch.complex64
 complex128 = torch.complex128
@@ -134,3 +178,5 @@ def type_size_in_bytes(t) -> int:
 
 def is_floating(t) -> bool:
     return t in float_type
+
+Int._BY_BITS.update({8: int8, 16: int16, 32: int32, 64: int64})

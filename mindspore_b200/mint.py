@@ -118,3 +118,6 @@ def _fill_submodules():
 
 
 _fill_submodules()
+
+arctan2 = _wrap(torch.arctan2)
+inverse = _wrap(torch.linalg.inv)

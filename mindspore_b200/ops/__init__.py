@@ -10,3 +10,36 @@ from . import operations as P  # noqa: N812
 from . import composite as C  # noqa: N812
 from .composite import (Shard, UnpackCall, ZipOperation, choice_with_mask, count_nonzero, dot, gamma, laplace,  # noqa: E402,F401
                         poisson, repeat_elements, sequence_mask, tensor_dot, vmap)
+
+from .op_info_register import (AiCPURegOp, AkgAscendRegOp, AkgGpuRegOp, CpuRegOp, CustomRegOp, DataType,  # noqa: E402,F401
+                               TBERegOp, custom_info_register, get_vm_impl_fn, op_info_register, vm_impl_registry)
+
+
+def reshard(tensor, layout):
+    """Redistributes ``tensor`` to ``layout`` (a ``parallel.Layout`` with its tensor map applied): the dispatcher's
+    redistribution - all-gather / slice / all-to-all as the two layouts require - inserted by hand at this point of
+    the network (python/mindspore/ops/function/reshard_func.py).  Outside semi-auto / auto parallel mode, or for a
+    tensor whose layout the dispatcher does not know, the tensor is taken as replicated."""
+    from .. import context
+    from ..parallel import spmd
+    from ..parallel.layout import Layout, TensorLayout
+    if not isinstance(layout, Layout):
+        raise TypeError("Reshard only support type mindspore.Layout, but got %s" % type(layout))
+    d = layout.to_dict()
+    if len(d["tensor_map"]) != tensor.dim():
+        raise ValueError("reshard: the layout has %d dims, the tensor %d" % (len(d["tensor_map"]), tensor.dim()))
+    mode = context.get_auto_parallel_context("parallel_mode")
+    if mode not in (context.ParallelMode.SEMI_AUTO_PARALLEL, context.ParallelMode.AUTO_PARALLEL):
+        return tensor
+    cur = spmd.get_layout(tensor)
+    full = cur.shape if cur is not None else tuple(tensor.shape)
+    need = TensorLayout(d["device_matrix"], d["tensor_map"], full)
+    if cur is None:
+        cur = TensorLayout(d["device_matrix"], (-1,) * tensor.dim(), full)
+    out = spmd._redistribute(tensor, cur, need)
+    return spmd.set_layout(_wrap_reshard(out), need)
+
+
+def _wrap_reshard(t):
+    from .primitive import _wrap_out
+    return _wrap_out(t)

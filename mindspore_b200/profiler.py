@@ -25,6 +25,14 @@ import time
 import torch
 
 
+class ProfilerLevel:
+    """How much the profiler collects (python/mindspore/profiler/common/constant.py): Level0 - step and collective
+    ranges only, Level1 - plus kernel tables, Level2 - plus memory and call stacks."""
+    Level0 = "Level0"
+    Level1 = "Level1"
+    Level2 = "Level2"
+
+
 class Profiler:
     def __init__(self, output_path="./data", profile_communication=False, profile_memory=False, op_time=True,
                  data_process=False, timeline_limit=500, start_profile=True, l2_cache=False, with_stack=False, **kw):

@@ -5,8 +5,10 @@ from .callback import (BackupAndRestore, Callback, CheckpointConfig, ClusterMoni
 from .dataset_helper import DatasetHelper, connect_network_with_dataset
 from .loss_scale_manager import DynamicLossScaleManager, FixedLossScaleManager, LossScaleManager
 from .model import Model
-from .serialization import (async_ckpt_thread_status, export, load, load_checkpoint, load_param_into_net,
-                            load_segmented_checkpoints, save_checkpoint)
+from .serialization import (async_ckpt_thread_status, export, export_split_mindir, load, load_checkpoint,
+                            load_checkpoint_async, load_param_into_net, load_segmented_checkpoints, parse_print,
+                            save_checkpoint)
+from .amp import build_train_network
 from .safetensors_io import (check_checkpoint, ckpt_to_safetensors, get_ckpt_path_with_strategy,  # noqa: E402,F401
                              load_safetensors, safetensors_to_ckpt, save_safetensors)
 from .metrics import Metric  # noqa: E402,F401
@@ -19,6 +21,9 @@ def __getattr__(name):
                 "transform_checkpoint_by_rank", "transform_checkpoints", "sync_pipeline_shared_parameters"):
         from .. import parallel
         return getattr(parallel, name)
+    if name == "data_sink":
+        from ..common.api import data_sink
+        return data_sink
     if name in ("convert_model", "obfuscate_model"):
         def unavailable(*a, **k):
             raise NotImplementedError("%s targets other runtimes (ONNX conversion / model obfuscation) and is not "

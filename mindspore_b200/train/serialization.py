@@ -506,7 +506,51 @@ def load_segmented_checkpoints(ckpt_file_dir, net=None, strict_load=False, filte
 
 
 def parse_print(print_file_name):
-    raise NotImplementedError("print files are plain text in this runtime: read them directly")
+    """Reads a file written by the ``Print`` operator (``context.set_context(print_file_path=...)``): one record per
+    printed value, returned as a list of strings (scalars / text) and numpy arrays (tensors), in print order.  The
+    file is this framework's checkpoint container (a list of named values), so the reader is the checkpoint reader."""
+    import os
+    if not os.path.isfile(print_file_name):
+        raise ValueError("The print_file_name %r does not exist" % (print_file_name,))
+    with open(print_file_name, "rb") as f:
+        data = f.read()
+    if not data:
+        return []
+    try:
+        records = decode_stream(data)
+    except Exception:  # noqa: BLE001  (a plain-text print file: one value per line)
+        return data.decode(errors="replace").splitlines()
+    out = []
+    for rec in records:
+        value = rec[1] if isinstance(rec, (tuple, list)) and len(rec) > 1 else rec
+        out.append(value.numpy() if hasattr(value, "numpy") else value)
+    return out
+
+
+def load_checkpoint_async(ckpt_file_name, net=None, strict_load=False, filter_prefix=None, dec_key=None,
+                          dec_mode="AES-GCM", specify_prefix=None, choice_func=None):
+    """Starts ``load_checkpoint`` on a worker thread and returns a future-like object: ``result()`` waits and returns
+    the parameter dict (the reference overlaps the file read with graph compilation the same way)."""
+    from concurrent.futures import ThreadPoolExecutor
+    pool = ThreadPoolExecutor(max_workers=1, thread_name_prefix="ckpt-load")
+    fut = pool.submit(load_checkpoint, ckpt_file_name, net, strict_load, filter_prefix, dec_key, dec_mode,
+                      specify_prefix, choice_func)
+    fut.add_done_callback(lambda _f: pool.shutdown(wait=False))
+    return fut
+
+
+def export_split_mindir(net, *inputs, file_name, devices_num=8, **kwargs):
+    """Exports the graph once per device of a model-parallel job (``<file_name>_rank_<r>.mindir``): every file holds
+    this rank's slices of the sharded parameters.  Runs on each rank for its own file; ``devices_num`` is checked
+    against the parallel context."""
+    from .. import context
+    n = context.get_auto_parallel_context("device_num")
+    if devices_num != n:
+        raise ValueError("export_split_mindir: devices_num %d differs from the parallel context's device_num %d"
+                         % (devices_num, n))
+    rank = context.get_auto_parallel_context("global_rank")
+    base = file_name[:-7] if file_name.endswith(".mindir") else file_name
+    return export(net, *inputs, file_name="%s_rank_%d" % (base, rank), file_format="MINDIR", **kwargs)
 
 
 def export(net, *inputs, file_name, file_format, **kwargs):

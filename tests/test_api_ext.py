@@ -225,3 +225,43 @@ def test_numpy_namespace_wide_coverage():
     assert q.tolist() == [3, -4] and r.tolist() == [1, 1]
     assert mnp.unravel_index(5, (2, 3)) == (1, 2) and np.allclose(mnp.hanning(4).numpy(), np.hanning(4))
     assert mnp.array_equal(a, a) and not mnp.array_equal(a, a + 1)
+
+
+def test_map_parameter_custom_registration_and_reshard():
+    import numpy as np
+    import torch
+    import mindspore_b200 as ms
+    from mindspore_b200 import ops
+    from mindspore_b200.experimental import MapParameter
+    from mindspore_b200.parallel import Layout
+    m = MapParameter(key_dtype=ms.int32, value_dtype=ms.float32, value_shape=(3,), default_value="zeros")
+    m.put(ms.Tensor(torch.tensor([5, 9])), ms.Tensor(torch.tensor([[1., 2., 3.], [4., 5., 6.]])))
+    got = m.get(ms.Tensor(torch.tensor([9, 7, 5])))
+    assert got.tolist() == [[4., 5., 6.], [0., 0., 0.], [1., 2., 3.]] and len(m) == 3      # 7 was inserted
+    m.scatter_update(ms.Tensor(torch.tensor([5, 5])), ms.Tensor(torch.ones(2, 3)), lr=0.5)
+    assert m[ms.Tensor(torch.tensor([5]))].tolist() == [[0., 1., 2.]]
+    m.erase(ms.Tensor(torch.tensor([7])))
+    keys, values, status = m.export_data()
+    assert keys.tolist() == [5, 9] and values.shape == (2, 3) and status.shape == (2,)
+    m2 = MapParameter(value_shape=(3,)).import_data((keys, values))
+    assert np.allclose(m2.get_values().numpy(), values)
+    # registration records of a custom operator
+    info = (ops.CustomRegOp("axpy").input(0, "x").input(1, "y").output(0, "z").attr("alpha", "required", "float")
+            .dtype_format(ops.DataType.F32_Default, ops.DataType.F32_Default, ops.DataType.F32_Default)
+            .target("GPU").get_op_info())
+    assert info["op_name"] == "axpy" and len(info["inputs"]) == 2 and info["dtype_format"][0][0] == ("float32", "DefaultFormat")
+
+    @ops.custom_info_register(info)
+    def axpy(x, y):
+        return x + y
+    assert axpy.reg_info[0]["target"] == "GPU" and float(axpy(1.0, 2.0)) == 3.0
+    assert ops.get_vm_impl_fn(ops.ReLU()) is not None
+    # reshard outside a parallel mode is the identity; the layout is still checked against the tensor
+    lay = Layout((2, 2), ("dp", "mp"))
+    x = ms.Tensor(torch.randn(4, 6))
+    assert ops.reshard(x, lay("dp", "None")) is x
+    import pytest
+    with pytest.raises(ValueError):
+        ops.reshard(x, lay("dp", "None", "mp"))
+    with pytest.raises(TypeError):
+        ops.reshard(x, "dp")
