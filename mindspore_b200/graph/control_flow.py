@@ -87,7 +87,8 @@ def cond(pred, true_fn, false_fn, *operands):
         raise TypeError("For 'cond', both branches must return the same structure, got %s and %s"
                         % (_structure(t_out), _structure(f_out)))
     sw = Switch(tg, fg, len(operands), len(t_caps), len(f_caps))
-    out = t_out if bool(pred) else f_out
+    # (read through the plain tensor type: this Python branch only picks the example values of the trace)
+    out = t_out if pred.detach().as_subclass(torch.Tensor).item() else f_out
     args = (pred,) + tuple(operands) + tuple(t_caps) + tuple(f_caps)
     node = outer.record(sw, args, {}, out)
     node.meta["primitive"] = "Switch"

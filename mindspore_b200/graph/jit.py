@@ -585,7 +585,8 @@ def jit(fn=None, mode="PSJit", input_signature=None, hash_args=None, jit_config=
             try:
                 if cg is None:
                     owner = args[0] if args and isinstance(args[0], Cell) else None
-                    cg = _compile(f, args, kwargs, getattr(f, "__name__", "jit_fn"), owner=owner)
+                    from .ast_transform import convert_function
+                    cg = _compile(convert_function(f), args, kwargs, getattr(f, "__name__", "jit_fn"), owner=owner)
                     cache[key] = cg
                 return cg(*args)
             finally:

@@ -148,7 +148,11 @@ class Cell:
             from torch.utils.checkpoint import checkpoint
             out = checkpoint(lambda *a: self.construct(*a, **kwargs), *inputs, use_reentrant=False)
         else:
-            out = self.construct(*inputs, **kwargs)
+            construct = self.construct
+            if Cell._graph_depth > 0:
+                from ..graph.ast_transform import converted_construct
+                construct = converted_construct(self)          # data-dependent ifs become Switch nodes
+            out = construct(*inputs, **kwargs)
         for hook in self._forward_hook.values():
             res = hook(self, inputs, out)
             if res is not None:

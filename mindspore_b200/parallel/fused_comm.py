@@ -44,7 +44,12 @@ _native.register_cuda_signature("msb_gemm_ag", _I, [_U64P, _P, _P, _P, _P, _P, _
 _contexts = {}
 _disabled = set()
 # AllGather -> MatMul: 1 = the copy engines pull the peers' shards (SMs only multiply), 0 = a copy warp per CTA does
-_AG_DMA = int(os.environ.get("MSB200_AG_DMA", "1") != "0")
+# AllGather -> MatMul: who moves the peer shards.  1 = the copy engines (peer copies on two side streams, one flag per
+# chunk), 0 = the GEMM kernel's own copy warp.  Measured per op (utils/kernel_bench.py fused_comm): the copy engines
+# win at 2 and 4 ranks (186 vs 196 us at 2 ranks for the QKV projection), the copy warp at 8 ranks, where seven small
+# peer copies per call cost more in launch and event traffic than they save (118 vs 135 us).  "auto" follows that.
+_AG_DMA_ENV = os.environ.get("MSB200_AG_DMA", "auto")
+_AG_DMA = None if _AG_DMA_ENV == "auto" else int(_AG_DMA_ENV != "0")
 
 
 def _ptr_array(ptrs):
@@ -220,7 +225,8 @@ def _gemm_ag(ctx, a_shard, b, b_mn, bias=None):
     flags = torch.empty(ctx.world, dtype=torch.int32, device=a_shard.device)
     c = torch.empty((M_, N_), dtype=torch.bfloat16, device=a_shard.device)
     rc = _native.cuda().msb_gemm_ag(_ptr_array(ptrs), _p(gathered), _p(flags), _p(b), _p(c), _p(bias), M_, N_, K_,
-                                    int(b_mn), b.stride(0), N_, ctx.world, ctx.rank, 0, _AG_DMA, _stream())
+                                    int(b_mn), b.stride(0), N_, ctx.world, ctx.rank, 0,
+                                    int(ctx.world <= 4) if _AG_DMA is None else _AG_DMA, _stream())
     _native.check(rc, "gemm_ag")
     _count()
     return c, gathered
