@@ -4,10 +4,10 @@ The tracer runs ``construct`` once and records what ran, so a plain Python ``if`
 at trace time.  This module rewrites the function's syntax tree before it is traced: every ``if`` / ``elif`` / ``else``
 whose branches only bind local names becomes two local functions and one call of ``run_if``,
 
-    if cond_expr:                       def __ms_true_0(a=a):            # names bound before are passed in
+    if cond_expr:                       def __ms_true_0(a=<a, if bound>):  # names bound before are passed in
         a = f(a)                            a = f(a); b = g(a)
         b = g(a)              ==>           return (a, b)
-    else:                               def __ms_false_0(a=a):
+    else:                               def __ms_false_0(a=<a, if bound>):
         b = h(a)                            b = h(a)
                                             return (a, b)
                                         (a, b) = __ms_run_if(cond_expr, __ms_true_0, __ms_false_0)
@@ -43,6 +43,14 @@ def run_if(test, true_fn, false_fn):
             from .control_flow import cond
             return cond(test.reshape(()) if test.dim() else test, true_fn, false_fn)
     return true_fn() if test else false_fn()
+
+
+def value_of(thunk):
+    """Current value of a local name that may not be bound yet on this path (``thunk`` = ``lambda: name``)."""
+    try:
+        return thunk()
+    except NameError:                      # UnboundLocalError and the free-variable form are both NameErrors
+        return _UNDEFINED
 
 
 class _Unsupported(Exception):
@@ -172,7 +180,10 @@ class _IfRewriter:
                       for n in names], ctx=ast.Load()))
             args = ast.arguments(posonlyargs=[], args=[ast.arg(arg=n) for n in passed], vararg=None, kwonlyargs=[],
                                  kw_defaults=[], kwarg=None,
-                                 defaults=[ast.Name(id=n, ctx=ast.Load()) for n in passed])
+                                 defaults=[ast.Call(func=ast.Name(id="__ms_value_of", ctx=ast.Load()), args=[
+                                     ast.Lambda(args=ast.arguments(posonlyargs=[], args=[], vararg=None, kwonlyargs=[],
+                                                                   kw_defaults=[], kwarg=None, defaults=[]),
+                                                body=ast.Name(id=n, ctx=ast.Load()))], keywords=[]) for n in passed])
             return ast.FunctionDef(name=name, args=args, body=body + [ret], decorator_list=[], returns=None,
                                    type_comment=None, type_params=[])
 
@@ -238,6 +249,7 @@ def _convert(fn):
     glb = fn.__globals__                                      # the function keeps its module's live globals
     glb.setdefault("__ms_run_if", run_if)
     glb.setdefault("__ms_undefined", _UNDEFINED)
+    glb.setdefault("__ms_value_of", value_of)
     ns = {}
     try:
         exec(code, glb, ns)                                   # noqa: S102  (our own rewritten source of fn)
