@@ -93,3 +93,122 @@ def cond(pred, true_fn, false_fn, *operands):
     node = outer.record(sw, args, {}, out)
     node.meta["primitive"] = "Switch"
     return out
+
+
+
+# ---------------------------------------------------------------------------------------------------- loops
+class While:
+    """Target of a While node: the traced condition and body of ``while_loop``.  Each run evaluates the condition
+    sub-graph on the current state, reads it on the host and runs the body sub-graph until it is false (the
+    reference lowers ``while`` to a recursive Switch between the body-and-call-again graph and the exit graph:
+    ccsrc/pipeline/jit/ps/parse/parse.cc ParseWhile; ops WhileLoop in ops/operations/_scalar_ops.py).  Reverse mode
+    goes through the iterations that ran, like ``Switch``."""
+
+    def __init__(self, cond_graph, body_graph, n_state, n_cond_caps, n_body_caps, max_iterations=None):
+        from .executor import GraphExecutor
+        self.graphs = (cond_graph, body_graph)
+        self.executors = (GraphExecutor(cond_graph), GraphExecutor(body_graph))
+        self.n_state, self.n_cond_caps, self.n_body_caps = n_state, n_cond_caps, n_body_caps
+        self.max_iterations = max_iterations
+        self.__name__ = "While"
+        self.last_iterations = None
+
+    def __call__(self, *vals):
+        state = list(vals[:self.n_state])
+        c_caps = list(vals[self.n_state:self.n_state + self.n_cond_caps])
+        b_caps = list(vals[self.n_state + self.n_cond_caps:])
+        cg, bg = self.graphs
+        if any(isinstance(v, torch.Tensor) and v.is_cuda for v in state) and torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("a While node can not be captured into a CUDA graph: its trip count is read on the host")
+        n = 0
+        while True:
+            pred = self.executors[0].run([state[i] for i in cg.operand_positions] + c_caps)
+            if not bool(pred.detach().as_subclass(torch.Tensor).reshape(-1)[0].item()):
+                break
+            out = self.executors[1].run([state[i] for i in bg.operand_positions] + b_caps)
+            state = list(out) if isinstance(out, (tuple, list)) else [out]
+            n += 1
+            if self.max_iterations is not None and n >= self.max_iterations:
+                break
+        self.last_iterations = n
+        return tuple(state)
+
+
+def while_loop(cond_fn, body_fn, init_val, max_iterations=None):
+    """``state = init_val; while cond_fn(*state): state = body_fn(*state); return state`` with ``state`` a tuple of
+    tensors (a single tensor is taken as a one-element state and returned as a tensor).  In graph mode the condition
+    and the body become sub-graphs behind ONE While node whose trip count is decided at every run."""
+    single = isinstance(init_val, torch.Tensor)
+    state = (init_val,) if single else tuple(init_val)
+
+    def plain():
+        cur, n = state, 0
+        while bool(cond_fn(*cur)):
+            nxt = body_fn(*cur)
+            cur = (nxt,) if isinstance(nxt, torch.Tensor) else tuple(nxt)
+            n += 1
+            if max_iterations is not None and n >= max_iterations:
+                break
+        return cur
+
+    session = _trace_state.current()
+    if session is None or session.rec.depth > 0 or not all(isinstance(v, torch.Tensor) for v in state):
+        out = plain()
+        return out[0] if single else out
+    from . import jit as _jit
+    outer = session.rec
+    cg, c_out, c_caps = _jit.trace_branch(cond_fn, state, outer, "while_cond")
+    bg, b_out, b_caps = _jit.trace_branch(body_fn, state, outer, "while_body")
+    b_tuple = (b_out,) if isinstance(b_out, torch.Tensor) else tuple(b_out)
+    if _structure(tuple(b_tuple)) != _structure(tuple(state)):
+        raise TypeError("For 'while_loop', the body must return the structure of the loop state, got %s for %s"
+                        % (_structure(tuple(b_tuple)), _structure(tuple(state))))
+    if not isinstance(c_out, torch.Tensor) or c_out.numel() != 1:
+        raise TypeError("For 'while_loop', the condition must return a one-element tensor")
+    outer.depth += 1                                   # the example run of the trace itself is not recorded
+    try:
+        out = plain()
+    finally:
+        outer.depth -= 1
+    node_target = While(cg, bg, len(state), len(c_caps), len(b_caps), max_iterations)
+    args = tuple(state) + tuple(c_caps) + tuple(b_caps)
+    node = outer.record(node_target, args, {}, tuple(out))
+    node.meta["primitive"] = "While"
+    return out[0] if single else tuple(out)
+
+
+def fori_loop(lower, upper, body_fn, init_val, unroll=True):
+    """``val = init_val; for i in range(lower, upper): val = body_fn(i, val)``.  Integer bounds unroll into the
+    trace; tensor bounds run as a ``while_loop`` over (i, val)."""
+    if isinstance(lower, int) and isinstance(upper, int):
+        val = init_val
+        for i in range(lower, upper):
+            val = body_fn(i, val)
+        return val
+    lo = torch.as_tensor(lower)
+    hi = torch.as_tensor(upper)
+    single = isinstance(init_val, torch.Tensor)
+    vals = (init_val,) if single else tuple(init_val)
+
+    def c(i, *v):
+        return i < hi
+
+    def b(i, *v):
+        out = body_fn(i, v[0] if single else tuple(v))
+        out = (out,) if isinstance(out, torch.Tensor) else tuple(out)
+        return (i + 1,) + out
+    res = while_loop(c, b, (lo.clone(),) + vals)
+    return res[1] if single else tuple(res[1:])
+
+
+def scan(f, init, xs, length=None):
+    """``carry, ys = init, []; for x in xs: carry, y = f(carry, x); ys.append(y)``; returns (carry, stacked ys).
+    The steps unroll into the trace (the leading dimension is static)."""
+    n = length if xs is None else (len(xs) if not isinstance(xs, torch.Tensor) else xs.shape[0])
+    carry, ys = init, []
+    for k in range(n):
+        carry, y = f(carry, None if xs is None else xs[k])
+        ys.append(y)
+    if ys and isinstance(ys[0], torch.Tensor):
+        return carry, torch.stack(ys)
+    return carry, ys

@@ -28,7 +28,7 @@ def is_impure(node):
     t = node.target
     if t is autodiff.vjp:
         return True
-    if getattr(t, "is_collective", False) or type(t).__name__ == "Switch":
+    if getattr(t, "is_collective", False) or type(t).__name__ in ("Switch", "While"):
         return True
     if _is_primitive(t):
         if t._update_parameter:

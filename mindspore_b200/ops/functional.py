@@ -322,6 +322,22 @@ def cond(pred, true_fn, false_fn, *operands):
     return _cond(pred, true_fn, false_fn, *operands)
 
 
+def while_loop(cond_fn, body_fn, init_val, max_iterations=None):
+    """Traceable loop: see ``graph/control_flow.py::while_loop``."""
+    from ..graph.control_flow import while_loop as _w
+    return _w(cond_fn, body_fn, init_val, max_iterations)
+
+
+def fori_loop(lower, upper, body_fn, init_val, unroll=True):
+    from ..graph.control_flow import fori_loop as _f
+    return _f(lower, upper, body_fn, init_val, unroll)
+
+
+def scan(f, init, xs, length=None):
+    from ..graph.control_flow import scan as _s
+    return _s(f, init, xs, length)
+
+
 def select(cond, x, y):
     return _prim(P.Select)(cond, x, y)
 
