@@ -19,7 +19,12 @@ tensor computed by the graph being traced.  This is the role of the reference's 
 
 Left as they are (and therefore decided at trace time, with the tracer's warning): branches that ``return``,
 ``break``, ``continue``, ``raise``, ``yield``, ``del`` or assign to attributes / subscripts, and functions whose source
-is not available.  ``while`` loops on tensor conditions are not rewritten."""
+is not available.
+
+``while`` loops whose bodies only rebind local names that exist before the loop are rewritten the same way into a
+condition function, a body function over the loop-carried names and one call of ``run_while``, which records a single
+While node when the condition is a tensor of the graph (ParseWhile in the reference) and runs the plain Python loop
+otherwise."""
 from __future__ import annotations
 
 import ast
@@ -43,6 +48,28 @@ def run_if(test, true_fn, false_fn):
             from .control_flow import cond
             return cond(test.reshape(()) if test.dim() else test, true_fn, false_fn)
     return true_fn() if test else false_fn()
+
+
+def run_while(cond_fn, body_fn, state):
+    """Runtime of a rewritten ``while``: a condition that is a tensor computed by the graph being traced makes the
+    loop one While node (``graph.control_flow.while_loop``); anything else runs as the plain Python loop."""
+    from . import tracer as _trace_state
+    if _trace_state.is_tracing() and all(isinstance(v, torch.Tensor) for v in state):
+        session = _trace_state.current()
+        rec = getattr(session, "rec", None)
+        if rec is not None and rec.depth == 0:
+            rec.depth += 1                              # probe the condition without recording it
+            try:
+                first = cond_fn(*state)
+            finally:
+                rec.depth -= 1
+            if isinstance(first, torch.Tensor) and first.numel() == 1 and \
+                    any(rec.knows(v) for v in state):
+                from .control_flow import while_loop
+                return tuple(while_loop(cond_fn, body_fn, tuple(state)))
+    while cond_fn(*state):
+        state = body_fn(*state)
+    return tuple(state)
 
 
 def value_of(thunk):
@@ -143,6 +170,8 @@ class _IfRewriter:
         for st in stmts:
             if isinstance(st, ast.If):
                 out.extend(self.convert_if(st, bound))
+            elif isinstance(st, ast.While) and not st.orelse and self.convertible_while(st, bound):
+                out.extend(self.convert_while(st, bound))
             else:
                 for field in ("body", "orelse", "finalbody"):
                     sub = getattr(st, field, None)
@@ -158,6 +187,42 @@ class _IfRewriter:
                     h.body = self.block(h.body, set(bound) | ({h.name} if h.name else set()))
                 out.append(st)
             bound |= _all_stores(st)
+        return out
+
+    def convertible_while(self, node, bound):
+        try:
+            names = _stored_names(node.body)
+        except _Unsupported:
+            return False
+        # every loop-carried name must be bound before the loop (it is passed in as state)
+        return bool(names) and all(n in bound for n in names)
+
+    def convert_while(self, node, bound):
+        names = _stored_names(node.body)
+        inner = set(bound) | set(names)
+        node.body = self.block(node.body, inner)
+        k = self.counter
+        self.counter += 1
+        self.changed = True
+
+        def fn(name, body):
+            args = ast.arguments(posonlyargs=[], args=[ast.arg(arg=n) for n in names], vararg=None, kwonlyargs=[],
+                                 kw_defaults=[], kwarg=None, defaults=[])
+            return ast.FunctionDef(name=name, args=args, body=body, decorator_list=[], returns=None,
+                                   type_comment=None, type_params=[])
+
+        state = ast.Tuple(elts=[ast.Name(id=n, ctx=ast.Load()) for n in names], ctx=ast.Load())
+        c_name, b_name = "__ms_wcond_%d" % k, "__ms_wbody_%d" % k
+        cond_def = fn(c_name, [ast.Return(value=node.test)])
+        body_def = fn(b_name, list(node.body) + [ast.Return(value=state)])
+        call = ast.Call(func=ast.Name(id="__ms_run_while", ctx=ast.Load()),
+                        args=[ast.Name(id=c_name, ctx=ast.Load()), ast.Name(id=b_name, ctx=ast.Load()), state],
+                        keywords=[])
+        assign = ast.Assign(targets=[ast.Tuple(elts=[ast.Name(id=n, ctx=ast.Store()) for n in names],
+                                               ctx=ast.Store())], value=call)
+        out = [cond_def, body_def, assign]
+        for n in out:
+            ast.copy_location(n, node)
         return out
 
     def convert_if(self, node, bound):
@@ -222,7 +287,7 @@ def _convert(fn):
     except (OSError, TypeError, SyntaxError, IndentationError):
         return None
     funcs = [n for n in tree.body if isinstance(n, (ast.FunctionDef,))]
-    if len(funcs) != 1 or not any(isinstance(n, ast.If) for n in ast.walk(funcs[0])):
+    if len(funcs) != 1 or not any(isinstance(n, (ast.If, ast.While)) for n in ast.walk(funcs[0])):
         return None
     func = funcs[0]
     if any(isinstance(n, ast.Nonlocal) for n in ast.walk(func)):
@@ -250,6 +315,7 @@ def _convert(fn):
     glb.setdefault("__ms_run_if", run_if)
     glb.setdefault("__ms_undefined", _UNDEFINED)
     glb.setdefault("__ms_value_of", value_of)
+    glb.setdefault("__ms_run_while", run_while)
     ns = {}
     try:
         exec(code, glb, ns)                                   # noqa: S102  (our own rewritten source of fn)

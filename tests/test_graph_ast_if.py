@@ -126,3 +126,46 @@ def test_zero_argument_super_still_works_after_the_rewrite(graph_mode):
     assert net(ms.Tensor(torch.tensor([1.0]))).tolist() == [6.0]
     assert net(ms.Tensor(torch.tensor([-5.0]))).tolist() == [-4.0]
     assert len(net._compiled) == 1
+
+
+def test_while_on_a_tensor_condition_is_one_node_with_a_dynamic_trip_count(graph_mode):
+    class Halve(nn.Cell):
+        def __init__(self):
+            super().__init__()
+            self.w = ms.Parameter(ms.Tensor(torch.tensor(1.5)), name="w")
+
+        def construct(self, x, limit):
+            n = x * 0
+            y = x * self.w
+            while y.sum() > limit:
+                y = y * 0.5
+                n = n + 1
+            return y, n
+
+    net = Halve()
+    lim = ms.Tensor(torch.tensor(1.0))
+    for vals, trips in (([8.0, 8.0], 5), ([0.25, 0.25], 0), ([1.0, 1.0], 2)):
+        y, n = net(ms.Tensor(torch.tensor(vals)), lim)
+        assert n.tolist() == [float(trips)] * 2, (vals, n.tolist())
+        torch.testing.assert_close(y.as_subclass(torch.Tensor), torch.tensor(vals) * 1.5 * 0.5 ** trips)
+    assert len(net._compiled) == 1
+    (cg,) = net._compiled.values()
+    names = [getattr(n.target, "__name__", "") for n in cg.fg.graph.nodes if n.op == "call_function"]
+    assert names.count("While") == 1
+    # reverse mode goes through the iterations that ran: d(sum y)/dw = sum(x) * 0.5^trips
+    grad = ops.GradOperation(get_by_list=True)(lambda x, l: net(x, l)[0], ms.ParameterTuple([net.w]))
+    (g,) = grad(ms.Tensor(torch.tensor([8.0, 8.0])), lim)
+    assert float(g) == pytest.approx(16.0 * 0.5 ** 5)
+
+
+def test_loop_functions():
+    ms.set_context(mode=ms.PYNATIVE_MODE, device_target="CPU")
+    s = ops.while_loop(lambda i, acc: i < 5, lambda i, acc: (i + 1, acc + i), (ms.Tensor(torch.tensor(0)),
+                                                                                ms.Tensor(torch.tensor(0))))
+    assert [int(v) for v in s] == [5, 10]
+    assert float(ops.fori_loop(0, 4, lambda i, v: v * 2, ms.Tensor(torch.tensor(1.0)))) == 16.0
+    out = ops.fori_loop(ms.Tensor(torch.tensor(2)), ms.Tensor(torch.tensor(5)), lambda i, v: v + i,
+                        ms.Tensor(torch.tensor(0)))
+    assert int(out) == 2 + 3 + 4
+    carry, ys = ops.scan(lambda c, x: (c + x, c * x), ms.Tensor(torch.tensor(0.0)), ms.Tensor(torch.arange(4.0)))
+    assert float(carry) == 6.0 and ys.tolist() == [0.0, 0.0, 2.0, 9.0]
