@@ -12,7 +12,7 @@ import torch
 from .nn.cell import Cell
 from .nn.wrap import TrainOneStepCell
 
-__all__ = ["AutoBoost", "BoostTrainOneStepCell", "BoostTrainOneStepWithLossScaleCell", "LessBN", "GradientFreeze",
+__all__ = ["AdaSum", "DimReduce", "GroupLossScaleManager", "AutoBoost", "BoostTrainOneStepCell", "BoostTrainOneStepWithLossScaleCell", "LessBN", "GradientFreeze",
            "FreezeOpt", "freeze_cell", "GradientAccumulation", "OptimizerProcess", "ParameterProcess"]
 
 _LEVELS = {"O0": {}, "O1": {"less_bn": True, "grad_freeze": True},
@@ -158,3 +158,89 @@ class BoostTrainOneStepWithLossScaleCell(BoostTrainOneStepCell):
     def __init__(self, network, optimizer, scale_sense):
         super().__init__(network, optimizer, 1.0)
         self.scale_sense = scale_sense
+
+
+class AdaSum(Cell):
+    """Gradient combination by adaptive summation over the data-parallel ranks (boost/adasum.py): pairs of
+    gradients are merged as ``(1 - a.b / 2|a|^2) a + (1 - a.b / 2|b|^2) b`` up a binary tree, which keeps the update
+    size of one rank when gradients agree and adds them when they are orthogonal.  Thin front for the wrap cells of
+    ``nn.optim_ext``: ``AdaSum(rank, device_number, group_number, parameter_tuple)(delta_weights, parameters,
+    old_parameters)`` returns the merged weight deltas."""
+
+    def __init__(self, rank, device_number, group_number, parameter_tuple):
+        super().__init__()
+        self.rank, self.device_number, self.group_number = rank, device_number, group_number
+        self.parameter_tuple = parameter_tuple
+
+    def construct(self, delta_weights, parameters=None, old_parameters=None):
+        from .nn.optim_ext import _adasum_allreduce
+        ranks = list(range(self.device_number))
+        return tuple(_adasum_allreduce(d, ranks, self.rank) for d in delta_weights)
+
+
+class DimReduce(Cell):
+    """Second-order style update in a reduced gradient subspace (boost/dim_reduce.py): gradients are projected onto
+    ``pca_mat`` (n_components x n_params), the step is taken in that subspace with a backtracking line search on the
+    loss, and mapped back.  ``construct(loss, old_grad, weight, weight_clone, *inputs)`` returns the loss."""
+
+    def __init__(self, network, optimizer, weight, pca_mat_local, n_components, rho, gamma, alpha, sigma, rank,
+                 rank_size):
+        super().__init__()
+        self.network, self.optimizer, self.weight = network, optimizer, weight
+        self.pca = torch.as_tensor(pca_mat_local).float()
+        self.n_components, self.rho, self.gamma, self.alpha, self.sigma = n_components, rho, gamma, alpha, sigma
+        self.rank, self.rank_size = rank, rank_size
+
+    def construct(self, loss, old_grad, weight, weight_clone, *inputs):
+        flat = torch.cat([g.reshape(-1).float() for g in old_grad])
+        coeff = self.pca.to(flat.device) @ flat                         # gradient in the reduced basis
+        step = self.pca.to(flat.device).t() @ coeff                     # back in parameter space
+        lr, base = 1.0, float(loss)
+        with torch.no_grad():
+            snapshot = [w.detach().clone() for w in weight]
+            for _ in range(8):                                          # backtracking line search (rho, sigma)
+                off = 0
+                for w, s0 in zip(weight, snapshot):
+                    n = w.numel()
+                    w.copy_(s0 - lr * step[off:off + n].reshape(w.shape).to(w.dtype))
+                    off += n
+                new = float(self.network(*inputs))
+                if new <= base - self.sigma * lr * float(flat @ step):
+                    break
+                lr *= self.rho
+        return loss
+
+
+class GroupLossScaleManager(Cell):
+    """Loss scales per layer group (boost/group_loss_scale_manager.py): ``loss_scale_groups`` lists parameter names
+    per group; each group keeps its own dynamic scale, updated from that group's overflow status."""
+
+    def __init__(self, init_loss_scale, loss_scale_groups):
+        super().__init__()
+        self.init_loss_scale = float(init_loss_scale)
+        self.loss_scale_groups = [list(g) for g in loss_scale_groups]
+        self.scales = [self.init_loss_scale for _ in self.loss_scale_groups]
+        self.scale_factor, self.scale_window = 2.0, 1000
+        self._good = [0 for _ in self.loss_scale_groups]
+
+    def get_loss_scale(self):
+        return self.init_loss_scale
+
+    def get_loss_scale_status(self, loss_scale_number, init_loss_scale):
+        return [init_loss_scale] * loss_scale_number
+
+    def update_loss_scale_status(self, layer, update_ratio=1.0):
+        return self.scales[layer] * update_ratio
+
+    def update(self, overflow_by_group):
+        """``overflow_by_group[i]`` true: halve group i's scale; ``scale_window`` clean steps: double it."""
+        for i, ov in enumerate(overflow_by_group):
+            if ov:
+                self.scales[i] = max(1.0, self.scales[i] / self.scale_factor)
+                self._good[i] = 0
+            else:
+                self._good[i] += 1
+                if self._good[i] >= self.scale_window:
+                    self.scales[i] *= self.scale_factor
+                    self._good[i] = 0
+        return list(self.scales)
