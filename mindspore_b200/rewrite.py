@@ -434,3 +434,119 @@ class SymbolTree:
         net = cls(self._origin, self._added)
         net._rewrite_source = code
         return net
+
+
+# ------------------------------------------------------------------------------------------------ pattern engine
+class PatternNode:
+    """One node of a pattern: matches a tree node whose instance is of ``instance_type`` (None matches any), with
+    ``inputs`` matched against the producers of that node's arguments (python/mindspore/rewrite/api/pattern_engine.py).
+    """
+
+    def __init__(self, pattern_node_name, instance_type=None, inputs=None):
+        self._name = pattern_node_name
+        self._type = instance_type
+        self._inputs = list(inputs or [])
+
+    @staticmethod
+    def from_node(node):
+        return PatternNode(node.get_name(), node.get_instance_type(),
+                           [PatternNode.from_node(i) for i in node.get_inputs()])
+
+    @staticmethod
+    def create_pattern_from_list(type_list):
+        """A chain: type_list[0] feeds type_list[1] feeds ...; returns the last (root) pattern node."""
+        cur = None
+        for i, t in enumerate(type_list):
+            cur = PatternNode("pattern_%d" % i, t, [cur] if cur is not None else [])
+        return cur
+
+    def add_input(self, node):
+        self._inputs.append(node)
+
+    def set_inputs(self, inputs):
+        self._inputs = list(inputs)
+
+    def get_inputs(self):
+        return list(self._inputs)
+
+    def name(self):
+        return self._name
+
+    def type(self):
+        return self._type
+
+    def match(self, node):
+        return self._type is None or (node.get_instance_type() is not None and
+                                      issubclass(node.get_instance_type(), self._type))
+
+
+class VarNode(PatternNode):
+    """Matches any node (a wildcard input of a pattern)."""
+
+    def __init__(self):
+        super().__init__("placeholder", None, [])
+
+
+class Replacement:
+    """``build(pattern, is_chain_pattern, matched) -> [Node]``: the nodes that take the place of a match; the last
+    one provides the value the matched root provided."""
+
+    def build(self, pattern, is_chain_pattern, matched):
+        raise NotImplementedError
+
+
+class PatternEngine:
+    """Finds every match of ``pattern`` (a PatternNode tree, or a list of types for a chain) in a SymbolTree and
+    replaces it by what ``replacement.build`` returns.  Interior nodes of a match must have no users outside it."""
+
+    def __init__(self, pattern, replacement=None):
+        if isinstance(pattern, (list, tuple)):
+            self._is_chain = True
+            self._pattern = PatternNode.create_pattern_from_list(list(pattern))
+        else:
+            self._is_chain = False
+            self._pattern = pattern
+        self._replacement = replacement
+
+    def pattern(self):
+        return self._pattern
+
+    def _match(self, pat, node, matched):
+        if isinstance(pat, VarNode):
+            return True
+        if not pat.match(node):
+            return False
+        matched[pat.name()] = node
+        inputs = node.get_inputs()
+        pins = pat.get_inputs()
+        if not pins:
+            return True
+        if len(pins) > len(inputs):
+            return False
+        return all(self._match(p, n, matched) for p, n in zip(pins, inputs))
+
+    def apply(self, stree):
+        """Returns True if anything was replaced."""
+        changed = False
+        for node in list(stree.nodes()):
+            if node.get_symbol_tree() is None:
+                continue
+            matched = {}
+            if not self._match(self._pattern, node, matched):
+                continue
+            inside = set(id(n) for n in matched.values())
+            interior_ok = all(all(id(u) in inside for u in n.get_users()) for n in matched.values() if n is not node)
+            if not interior_ok or self._replacement is None:
+                continue
+            new_nodes = self._replacement.build(self._pattern, self._is_chain, matched)
+            if not new_nodes:
+                continue
+            stree.replace(node, list(new_nodes))
+            for n in reversed([m for m in stree.nodes() if id(m) in inside]):
+                if not n.get_users():
+                    stree.erase(n)
+            changed = True
+        return changed
+
+
+__all__ += ["PatternEngine", "PatternNode", "Replacement", "VarNode"]

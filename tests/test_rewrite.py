@@ -96,3 +96,37 @@ def test_set_arg_rewires_a_node():
     ref = net.fc2(net.fc1(x)) * 2.0
     np.testing.assert_allclose(st.get_network()(x).detach().numpy(), ref.detach().numpy(), rtol=1e-6)
     assert ScopedValue.create_naming_value("h").code() == "h"
+
+
+def test_pattern_engine_replaces_a_chain():
+    from mindspore_b200.rewrite import PatternEngine, PatternNode, Replacement, VarNode
+
+    class DenseRelu(nn.Cell):
+        def __init__(self, dense):
+            super().__init__()
+            self.dense = dense
+
+        def construct(self, x):
+            return ops.relu(self.dense(x))
+
+    class Fuse(Replacement):
+        def build(self, pattern, is_chain_pattern, matched):
+            assert is_chain_pattern
+            dense, relu = matched["pattern_0"], matched["pattern_1"]
+            return [Node.create_call_cell(DenseRelu(dense.get_instance()), targets=relu.get_targets(),
+                                          args=dense.get_args(), name="dense_relu")]
+
+    ms.set_seed(3)
+    net = Net()
+    st = SymbolTree.create(net)
+    assert PatternEngine([nn.Dense, nn.ReLU], Fuse()).apply(st)
+    names = [n.get_name() for n in st.nodes()]
+    assert "dense_relu" in names and "fc1" not in names and "act" not in names and "fc2" in names
+    new = st.get_network()
+    x = ms.Tensor(torch.randn(5, 4))
+    np.testing.assert_allclose(new(x).detach().numpy(), net(x).detach().numpy(), rtol=1e-6)
+    # a pattern that is not there changes nothing; a tree pattern with a wildcard input matches the first Dense
+    assert not PatternEngine([nn.Tanh, nn.Dense], Fuse()).apply(SymbolTree.create(net))
+    pat = PatternNode("d", nn.Dense, [VarNode()])
+    m = {}
+    assert PatternEngine(pat)._match(pat, SymbolTree.create(net).get_node("fc1"), m) and list(m) == ["d"]
