@@ -50,6 +50,8 @@ def parse():
                     help="llama2-7b is the headline; resnet50: data-parallel image config (batch 256 per GPU); "
                          "gpt-2.6b: dp x mp with sharded optimizer; moe-8x: 8-expert top-2 decoder, expert parallel")
     ap.add_argument("--mp", type=int, default=None, help="gpt-2.6b: model-parallel size (default 4, capped by N)")
+    ap.add_argument("--micro-size", type=int, default=None,
+                    help="gpt-2.6b / moe-8x: sequences per micro-batch (default 4 for gpt-2.6b, 1 for moe-8x)")
     ap.add_argument("--batch-per-gpu", type=int, default=256, help="resnet50 only")
     ap.add_argument("--pp", type=int, default=None,
                     help="llama2-7b: pipeline stages (model parallel = N / pp inside a stage; 1F1B over "
@@ -299,7 +301,10 @@ def run_gpt_family(args):
     if dp > 1:
         opt.set_data_parallel_group(g["dp"], mean=True, shard=not moe)
     per_rank = global_batch // dp
-    micro = per_rank                               # micro-batch 1 sequence
+    micro_size = args.micro_size or 1
+    if per_rank % micro_size:
+        raise SystemExit("--micro-size %d does not divide the %d sequences of a rank" % (micro_size, per_rank))
+    micro = per_rank // micro_size                 # number of micro-batches
     step_cell = nn.TrainOneStepCell(nn.GradAccumulationCell(net, micro), opt)
     step_cell.set_train()
     dev = torch.device("cuda", local_rank)
@@ -359,7 +364,7 @@ def run_gpt_family(args):
             "dtype": "bf16", "data": "synthetic",
             "config": {"model": name, "layers": cfg.num_layers, "hidden": cfg.hidden_size, "heads": cfg.num_heads,
                        "ffn": cfg.ffn_hidden_size, "vocab": cfg.vocab_size, "global_batch": global_batch,
-                       "micro_batch": 1, "seq_len": seq,
+                       "micro_batch": micro_size, "seq_len": seq,
                        "parallelism": ("ep%d (dp%d)" % (dp, dp)) if moe else "dp%d x mp%d + sharded optimizer" % (dp, mp),
                        "optimizer": "AdamW fp32 master + moments, grad clip 1.0", "cuda_graph": use_graph,
                        "l2": "weights and activations of a step far exceed the 126 MB L2 (no flush needed)"},

@@ -54,6 +54,7 @@ struct GemmParams {
   // each followed by a copy of 1 into ag_flags[c]); warp 6 idles and a chunk is ready when its flag is >= 1.
   int ag_in_kernel, ag_flag_target;
   int world, rank, rows_per_rank;
+  int rs_slot;        // MODE 1: which [rows_per_rank][N] slot of the owner's buffer this rank's rows go to
   // The epilogue stages 32 rows x 128 bytes per warp in shared memory (128-byte swizzle) and writes them with TMA
   // stores (fp32 accumulation = TMA reduce-add): full 128-byte lines instead of 16-byte fragments per row, which is
   // what makes stores into a peer's memory efficient.  0 = per-thread stores (unaligned C, bf16 accumulation).
@@ -288,7 +289,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (MODE == 1 && row_ok_pre(row, p.M)) {
         const int owner = row / p.rows_per_rank;
         c_bf16 = static_cast<__nv_bfloat16*>(p.rs_peer[owner]);
-        c_off = (static_cast<long long>(p.rank) * p.rows_per_rank + (row - owner * p.rows_per_rank)) * p.ldc;
+        c_off = (static_cast<long long>(p.rs_slot) * p.rows_per_rank + (row - owner * p.rows_per_rank)) * p.ldc;
       }
       if (p.tma_epilogue) {
         // ---- staged epilogue: registers -> swizzled shared memory -> TMA store / reduce
@@ -299,7 +300,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (MODE == 1) {
           const int owner = (m_blk * kBM) / p.rows_per_rank;
           cmap = &tmC.m[owner];
-          store_row = p.rank * p.rows_per_rank + (row0 - owner * p.rows_per_rank);
+          store_row = p.rs_slot * p.rows_per_rank + (row0 - owner * p.rows_per_rank);
         }
         const int sw = lane & 7;
         int nbuf = 0;
@@ -704,26 +705,28 @@ static int check_chunks(const char* what, int M, int world, int rank) {
 // MatMul -> ReduceScatter.  partial[M,N] = A[M,K] x B^T is never materialised locally: tile rows owned by rank o
 // are stored into stage_ptrs[o] + (rank*rows_per_rank + local_row)*N  (bf16 staging of shape [world][M/world][N]
 // on every rank).  After a group barrier each rank sums its `world` slots (msb_reduce_slots).
-MSB_EXPORT int msb_gemm_rs(const void* A, const void* B, const unsigned long long* stage_ptrs, int M, int N, int K,
-                           int b_mn, long long lda, long long ldb, int world, int rank, int bn_hint, void* stream_) {
+static int gemm_push(const char* what, const void* A, const void* B, const void* bias,
+                     const unsigned long long* stage_ptrs, int M, int N, int K, int b_mn, long long lda,
+                     long long ldb, int world, int rank, int slot, int slots, int bn_hint, void* stream_) {
   using namespace msb;
-  if (int rc = check_chunks("gemm_rs", M, world, rank)) return rc;
-  if (N % 8) { set_last_error("gemm_rs: N=%d must be a multiple of 8", N); return kBadArg; }
+  if (int rc = check_chunks(what, M, world, rank)) return rc;
+  if (N % 8) { set_last_error("%s: N=%d must be a multiple of 8", what, N); return kBadArg; }
+  if (slot < 0 || slot >= slots) { set_last_error("%s: slot %d outside [0, %d)", what, slot, slots); return kBadArg; }
   int* status = status_ptr();
-  if (!status) { set_last_error("gemm_rs: no status word"); return kCudaError; }
+  if (!status) { set_last_error("%s: no status word", what); return kCudaError; }
   const int bn = pick_bn(M, N, 1, bn_hint);
   CUtensorMap tmA, tmB;
   if (int rc = encode_operands(&tmA, &tmB, A, B, M, N, K, 1, 0, b_mn, lda, ldb, 0, 0, bn)) return rc;
   GemmParams p = {};
-  p.status = status; p.M = M; p.N = N; p.K = K; p.batch = 1; p.ldc = N; p.alpha = 1.f;
-  p.world = world; p.rank = rank; p.rows_per_rank = M / world;
+  p.status = status; p.M = M; p.N = N; p.K = K; p.batch = 1; p.ldc = N; p.alpha = 1.f; p.bias = bias;
+  p.world = world; p.rank = rank; p.rows_per_rank = M / world; p.rs_slot = slot;
   for (int i = 0; i < world; ++i) p.rs_peer[i] = reinterpret_cast<void*>(stage_ptrs[i]);
   p.C = p.rs_peer[rank];
   CMaps tmC = {};
   int all_ok = 1;
   for (int i = 0; i < world; ++i) {
     int ok = 0;
-    if (int rc = encode_output(&tmC.m[i], p.rs_peer[i], M, N, 1, N, 0, 0, &ok)) return rc;
+    if (int rc = encode_output(&tmC.m[i], p.rs_peer[i], slots * p.rows_per_rank, N, 1, N, 0, 0, &ok)) return rc;
     all_ok &= ok;
   }
   p.tma_epilogue = all_ok;
@@ -734,6 +737,22 @@ MSB_EXPORT int msb_gemm_rs(const void* A, const void* B, const unsigned long lon
   }
   if (b_mn) return launch_gemm<128, false, true, 1>(tmA, tmB, tmC, p, stream);
   return launch_gemm<128, false, false, 1>(tmA, tmB, tmC, p, stream);
+}
+
+MSB_EXPORT int msb_gemm_rs(const void* A, const void* B, const unsigned long long* stage_ptrs, int M, int N, int K,
+                           int b_mn, long long lda, long long ldb, int world, int rank, int bn_hint, void* stream_) {
+  return gemm_push("gemm_rs", A, B, nullptr, stage_ptrs, M, N, K, b_mn, lda, ldb, world, rank, rank, world, bn_hint,
+                   stream_);
+}
+
+// MatMul -> row exchange (an expert's GEMM whose rows go back to the ranks their tokens came from).  Rows
+// [o*M/world, (o+1)*M/world) of  A x op(B) + bias  are stored into slot `slot` of rank o's buffer dst_ptrs[o], bf16
+// [slots][M/world][N]; nothing is summed, the receiver reads the slots after a group barrier.
+MSB_EXPORT int msb_gemm_push_rows(const void* A, const void* B, const void* bias, const unsigned long long* dst_ptrs,
+                                  int M, int N, int K, int b_mn, long long lda, long long ldb, int world, int rank,
+                                  int slot, int slots, int bn_hint, void* stream_) {
+  return gemm_push("gemm_push_rows", A, B, bias, dst_ptrs, M, N, K, b_mn, lda, ldb, world, rank, slot, slots, bn_hint,
+                   stream_);
 }
 
 // AllGather -> MatMul.  C[M,N] = gather(A)[M,K] x B^T (+ bias) where chunk c of the gathered operand is pulled from

@@ -39,6 +39,7 @@ _native.register_cuda_signature("msb_allreduce_symm", _I, [_U64P, _I, _I, _L, _F
 _native.register_cuda_signature("msb_reduce_slots", _I, [_P, _P, _I, _L, _P])
 _native.register_cuda_signature("msb_reduce_scatter_adamw", _I, [_U64P, _U64P, _P, _P, _P, _I, _I, _L, _P, _P, _P])
 _native.register_cuda_signature("msb_gemm_rs", _I, [_P, _P, _U64P, _I, _I, _I, _I, _L, _L, _I, _I, _I, _P])
+_native.register_cuda_signature("msb_gemm_push_rows", _I, [_P, _P, _P, _U64P, _I, _I, _I, _I, _L, _L, _I, _I, _I, _I, _I, _P])
 _native.register_cuda_signature("msb_gemm_ag", _I, [_U64P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _I, _I, _I, _I, _P])
 
 _contexts = {}
@@ -230,6 +231,40 @@ def _gemm_ag(ctx, a_shard, b, b_mn, bias=None):
     _native.check(rc, "gemm_ag")
     _count()
     return c, gathered
+
+
+def gemm_gather_rows(ctx, src_ptrs, rows, b, b_mn, bias=None, out=None, gathered=None):
+    """c = gather(chunks) @ op(b) (+ bias) -> ([world * rows, N], the gathered operand [world * rows, K]) where chunk c
+    is ``rows`` x K bf16 at ``src_ptrs[c]`` in rank c's symmetric memory (already published: the caller has passed a
+    barrier after writing it).  Tiles of chunks that have arrived are multiplied while the others are in flight.
+    ``out`` / ``gathered``: contiguous bf16 destinations of those shapes (allocated here if None)."""
+    K_ = b.shape[0] if b_mn else b.shape[1]
+    N_ = b.shape[1] if b_mn else b.shape[0]
+    M_ = rows * ctx.world
+    if gathered is None:
+        gathered = torch.empty((M_, K_), dtype=torch.bfloat16, device=b.device)
+    if out is None:
+        out = torch.empty((M_, N_), dtype=torch.bfloat16, device=b.device)
+    assert out.is_contiguous() and gathered.is_contiguous() and out.shape == (M_, N_) and gathered.shape == (M_, K_)
+    flags = torch.empty(ctx.world, dtype=torch.int32, device=b.device)
+    rc = _native.cuda().msb_gemm_ag(_ptr_array(src_ptrs), _p(gathered), _p(flags), _p(b), _p(out), _p(bias), M_, N_,
+                                    K_, int(b_mn), b.stride(0), N_, ctx.world, ctx.rank, 0,
+                                    int(ctx.world <= 4) if _AG_DMA is None else _AG_DMA, _stream())
+    _native.check(rc, "gemm_ag")
+    _count()
+    return out, gathered
+
+
+def gemm_push_rows(ctx, a, b, b_mn, dst_ptrs, slot, slots, bias=None):
+    """Rows [o * M / world, (o + 1) * M / world) of  a @ op(b) (+ bias)  are stored from the GEMM's epilogue into
+    slot ``slot`` of rank o's buffer ``dst_ptrs[o]`` (bf16 [slots][M / world][N]); the product is never written
+    locally.  The receivers read their slots after the next group barrier."""
+    M_, K_ = a.shape
+    N_ = b.shape[1] if b_mn else b.shape[0]
+    rc = _native.cuda().msb_gemm_push_rows(_p(a), _p(b), _p(bias), _ptr_array(dst_ptrs), M_, N_, K_, int(b_mn),
+                                           a.stride(0), b.stride(0), ctx.world, ctx.rank, slot, slots, 0, _stream())
+    _native.check(rc, "gemm_push_rows")
+    _count()
 
 
 def _optim():

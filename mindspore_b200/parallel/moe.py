@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 
@@ -297,6 +298,134 @@ class _CombineFn(torch.autograd.Function):
         return dybuf, dweight.to(weight.dtype), None, None, None
 
 
+# ------------------------------------------------------------------------------------------------ GEMMs fused with the exchange
+class _FusedExchange:
+    """The expert GEMMs as the consumers / producers of the row exchange over symmetric memory.
+
+    * gather form (dispatch -> first GEMM, and the backward of the second): every rank scatters its rows locally
+      into an [experts][capacity][H] send buffer in symmetric memory; the owner of expert e multiplies
+      ``gather_r(send_r[e]) @ W`` with the AllGather -> MatMul kernel, which pulls rank r's block while it multiplies
+      the blocks that have arrived.
+    * push form (second GEMM -> combine, and the backward of the first): the MatMul epilogue stores row block r of
+      the expert's product straight into slot e of rank r's [experts][capacity][H] receive buffer; after a barrier
+      every rank combines its own rows locally.
+
+    Needs capacity % 128 == 0 (a row block is a whole number of GEMM tiles) and bf16."""
+
+    def __init__(self, tr):
+        self.tr, self.ctx = tr, tr.symm
+        self.E, self.EL, self.C, self.ep, self.me = tr.E, tr.EL, tr.C, tr.ep, tr.me
+
+    def _buf(self, tag, H, device):
+        n = self.E * self.C * H
+        raw, ptrs = self.ctx.buffer(self.ctx._next("moe_" + tag), n * 2)
+        return raw[:n * 2].view(torch.bfloat16), ptrs
+
+    def _local(self, fn_name, *args):
+        rc = getattr(_native.cuda(), fn_name)(*args)
+        _native.check(rc, fn_name[4:])
+        _count()
+
+    def publish(self, src, scale, expert, slot):
+        """Local scatter of this rank's rows into a zeroed send buffer; returns the buffer's addresses on every rank
+        after the barrier that makes it readable."""
+        T, H = src.shape
+        buf, ptrs = self._buf("send", H, src.device)
+        buf.zero_()
+        self._local("msb_moe_scatter_rows", _p(src), _p(scale), _p(expert), _p(slot), _ptr_array([buf.data_ptr()]), T,
+                    expert.shape[1], H, self.E, 1, 0, self.C, _stream())
+        self.ctx.barrier(1)
+        return ptrs
+
+    def gather_gemm(self, ptrs, H, w, b_mn, bias):
+        """[EL, ep * C, N] = gathered rows of each local expert times its weight; also returns the gathered rows."""
+        from . import fused_comm
+        K_ = w.shape[1] if b_mn else w.shape[2]
+        N_ = w.shape[2] if b_mn else w.shape[1]
+        M_ = self.ep * self.C
+        assert K_ == H
+        out = torch.empty((self.EL, M_, N_), dtype=torch.bfloat16, device=w.device)
+        rows = torch.empty((self.EL, M_, H), dtype=torch.bfloat16, device=w.device)
+        for le in range(self.EL):
+            off = (self.me * self.EL + le) * self.C * H * 2
+            fused_comm.gemm_gather_rows(self.ctx, [p + off for p in ptrs], self.C, w[le], b_mn,
+                                        bias[le].reshape(-1) if bias is not None else None, out[le], rows[le])
+        return out, rows
+
+    def push_gemm(self, a, w, b_mn, bias, N):
+        """Each local expert's product goes to the ranks its rows came from; returns this rank's received
+        [E, C, N] rows (a view of the receive buffer: copy what must outlive the next two exchanges)."""
+        from . import fused_comm
+        buf, ptrs = self._buf("recv", N, a.device)
+        for le in range(self.EL):
+            fused_comm.gemm_push_rows(self.ctx, a[le], w[le], b_mn, ptrs, self.me * self.EL + le, self.E,
+                                      bias[le].reshape(-1) if bias is not None else None)
+        self.ctx.barrier(1)
+        return buf.view(self.E, self.C, N)
+
+    def combine(self, ybuf, scale, expert, slot, g=None, want_out=True):
+        T, K = expert.shape
+        H = ybuf.shape[-1]
+        out = torch.empty((T, H), dtype=ybuf.dtype, device=ybuf.device) if want_out else None
+        dots = torch.empty((T, K), dtype=torch.float32, device=ybuf.device) if g is not None else None
+        self._local("msb_moe_gather_rows", _ptr_array([ybuf.data_ptr()]), _p(scale), _p(expert), _p(slot), _p(g),
+                    _p(out), _p(dots), T, K, H, self.E, 1, 0, self.C, _stream())
+        return out, dots
+
+
+class _DispatchGemmFn(torch.autograd.Function):
+    """h[le] = dispatch(x)[le] @ w1[le] + b1[le]: the row exchange runs inside the GEMM (gather form)."""
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, expert, slot, fx):
+        x = x.contiguous()
+        ptrs = fx.publish(x, None, expert, slot)
+        h, rows = fx.gather_gemm(ptrs, x.shape[1], w1, True, b1)
+        ctx.fx, ctx.has_bias = fx, b1 is not None
+        ctx.save_for_backward(rows, w1, expert, slot)
+        return h
+
+    @staticmethod
+    def backward(ctx, dh):
+        rows, w1, expert, slot = ctx.saved_tensors
+        fx = ctx.fx
+        dh = dh.contiguous()
+        dw1 = fused.matmul(rows, dh, transpose_a=True) if ctx.needs_input_grad[1] else None
+        db1 = dh.sum(1, keepdim=True) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        dx = None
+        if ctx.needs_input_grad[0]:
+            recv = fx.push_gemm(dh, w1, False, None, w1.shape[1])          # dh @ w1^T, rows back to their sources
+            dx, _ = fx.combine(recv, None, expert, slot)
+        return dx, dw1, db1, None, None, None
+
+
+class _GemmCombineFn(torch.autograd.Function):
+    """out = combine(h[le] @ w2[le] + b2[le]): the GEMM's epilogue delivers the rows (push form)."""
+
+    @staticmethod
+    def forward(ctx, h, w2, b2, weight, expert, slot, fx):
+        h = h.contiguous()
+        ctx.weight_dtype = weight.dtype
+        weight = weight.float().contiguous()
+        ybuf = fx.push_gemm(h, w2, True, b2, w2.shape[2]).clone()
+        out, _ = fx.combine(ybuf, weight, expert, slot)
+        ctx.fx, ctx.has_bias = fx, b2 is not None
+        ctx.save_for_backward(h, w2, ybuf, weight, expert, slot)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        h, w2, ybuf, weight, expert, slot = ctx.saved_tensors
+        fx = ctx.fx
+        dout = dout.contiguous()
+        _, dweight = fx.combine(ybuf, None, expert, slot, g=dout, want_out=False)
+        ptrs = fx.publish(dout, weight, expert, slot)
+        dh, dy = fx.gather_gemm(ptrs, dout.shape[1], w2, False, None)      # gather(weight * dout) @ w2^T
+        dw2 = fused.matmul(h, dy, transpose_a=True) if ctx.needs_input_grad[1] else None
+        db2 = dy.sum(1, keepdim=True) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        return dh, dw2, db2, dweight.to(ctx.weight_dtype), None, None, None
+
+
 # ------------------------------------------------------------------------------------------------ the layer
 def _pick_transport(experts, capacity, group, device, fused=True):
     """Kernel transport on CUDA (over symmetric memory when the group has several ranks), torch otherwise."""
@@ -352,6 +481,9 @@ class MoE(Cell):
                 p.expert_shard = (ep, self.ep_rank)
         self.dropout_rate = dropout_rate
         self._transports = {}
+        self._exchanges = {}
+        # MSB200_MOE_FUSED_GEMM=0: expert GEMMs as separate launches around the scatter / gather kernels
+        self.fused_gemm = os.environ.get("MSB200_MOE_FUSED_GEMM", "1") != "0"
 
     def _transport(self, capacity, device):
         key = (capacity, device)
@@ -376,23 +508,40 @@ class MoE(Cell):
         T = tokens.shape[0]
         logits = torch.nn.functional.linear(tokens.float(), self.router_weight.as_subclass(torch.Tensor).float())
         capacity = calculate_expert_capacity(self.k, T, self.cfg.capacity_factor, self.E)
+        plain = lambda p: p.as_subclass(torch.Tensor) if p is not None else None
+        w1, w2, b1, b2 = plain(self.w1), plain(self.w2), plain(self.b1), plain(self.b2)
+        # expert GEMMs that run the row exchange themselves need whole GEMM tiles per (source rank, expert) block
+        fuse_gemm = (self.ep > 1 and tokens.is_cuda and self.fused_transport and self.fused_gemm
+                     and all(t is None or t.dtype == torch.bfloat16 for t in (tokens, w1, w2, b1, b2))
+                     and all(d % 8 == 0 for d in (shape[-1], w1.shape[-1], w2.shape[-2])))
         if tokens.is_cuda:
-            capacity = (capacity + 7) // 8 * 8         # rows per expert stay a multiple of the GEMM granule
+            g = 128 if fuse_gemm else 8                # rows per expert stay a multiple of the GEMM granule
+            capacity = (capacity + g - 1) // g * g
         expert, slot, weight, aux = route(logits, self.k, capacity)
         tr = self._transport(capacity, tokens.device)
-        buf = _DispatchFn.apply(tokens, expert, slot, tr)                     # [EL, ep, C, H]
-        h = buf.reshape(self.EL, self.ep * capacity, shape[-1])
-        h = fused.matmul(h, self.w1.as_subclass(torch.Tensor))
-        if self.b1 is not None:
-            h = h + self.b1.as_subclass(torch.Tensor)
+        fuse_gemm = fuse_gemm and isinstance(tr, _KernelTransport) and tr.symm is not None
+        if fuse_gemm:
+            fx = self._exchanges.get(id(tr))
+            if fx is None:
+                fx = self._exchanges[id(tr)] = _FusedExchange(tr)
+            h = _DispatchGemmFn.apply(tokens, w1, b1, expert, slot, fx)        # [EL, ep * C, up]
+        else:
+            buf = _DispatchFn.apply(tokens, expert, slot, tr)                 # [EL, ep, C, H]
+            h = buf.reshape(self.EL, self.ep * capacity, shape[-1])
+            h = fused.matmul(h, w1)
+            if b1 is not None:
+                h = h + b1
         h = self._activation(h)
         if self.dropout_rate > 0 and self.training:
             h = torch.nn.functional.dropout(h, self.dropout_rate)
-        y = fused.matmul(h, self.w2.as_subclass(torch.Tensor))
-        if self.b2 is not None:
-            y = y + self.b2.as_subclass(torch.Tensor)
-        y = y.reshape(self.EL, self.ep, capacity, shape[-1])
-        out = _CombineFn.apply(y, weight, expert, slot, tr)
+        if fuse_gemm:
+            out = _GemmCombineFn.apply(h, w2, b2, weight, expert, slot, fx)
+        else:
+            y = fused.matmul(h, w2)
+            if b2 is not None:
+                y = y + b2
+            y = y.reshape(self.EL, self.ep, capacity, shape[-1])
+            out = _CombineFn.apply(y, weight, expert, slot, tr)
         from ..common.tensor import as_tensor
         return as_tensor(out.reshape(shape)), as_tensor(aux * self.cfg.aux_loss_factor)
 

@@ -77,10 +77,12 @@ def _worker(rank, world, device, stages, micro):
     return stage, float(loss), loss_ref, worst, checked
 
 
-def test_pp2_mp2_llama_matches_single_cpu():
-    res = run_ranks(_worker, 4, "cpu", 2, 2, timeout=420)
+@pytest.mark.parametrize("world,stages", [(4, 2), (2, 2), (4, 4)])
+def test_pipeline_llama_matches_single_cpu(world, stages):
+    """pp2 x mp2, and pure pipelines (one rank per stage) of 2 and 4 stages."""
+    res = run_ranks(_worker, world, "cpu", stages, 2, timeout=420)
     for stage, loss, ref, worst, checked in res:
-        if stage == 1:
+        if stage == stages - 1:
             assert abs(loss - ref) < 1e-4, (loss, ref)
         assert worst < 1e-3 and checked > 0, (stage, worst, checked)
 

@@ -72,6 +72,8 @@ def _ep_worker(rank, world):
     net = _layer(E, k, H, F, cf=2.0, group=ms.communication.GlobalComm.WORLD_COMM_GROUP)
     el = E // world
     with torch.no_grad():
+        full.b1.copy_(torch.randn(full.b1.shape, generator=torch.Generator().manual_seed(5)) * 0.2)
+        full.b2.copy_(torch.randn(full.b2.shape, generator=torch.Generator().manual_seed(6)) * 0.2)
         net.router_weight.copy_(full.router_weight)
         for a, b in ((net.w1, full.w1), (net.w2, full.w2), (net.b1, full.b1), (net.b2, full.b2)):
             a.copy_(b[rank * el:(rank + 1) * el])
@@ -158,18 +160,23 @@ def test_moe_layer_kernels_match_dense_formulation(k, act):
     assert _native.device_status() == 0
 
 
-def _ep_gpu_worker(rank, world, fused):
+def _ep_gpu_worker(rank, world, fused, drops=False):
     from mindspore_b200 import _native
     from mindspore_b200.communication import init
     torch.cuda.set_device(rank)
     ms.set_context(device_target="GPU", device_id=rank)
     init("nccl")
     E, H, F, T, k = 8, 256, 512, 512, 2
-    full = _layer(E, k, H, F, cf=2.0, dtype=torch.bfloat16)
-    net = _layer(E, k, H, F, cf=2.0, group=ms.communication.GlobalComm.WORLD_COMM_GROUP, dtype=torch.bfloat16)
+    cf = 2.0
+    if drops:                                   # capacity 256 for 2048 choices over 8 experts: tokens are dropped
+        H, F, T, cf = 512, 1024, 1024, 1.0
+    full = _layer(E, k, H, F, cf=cf, dtype=torch.bfloat16)
+    net = _layer(E, k, H, F, cf=cf, group=ms.communication.GlobalComm.WORLD_COMM_GROUP, dtype=torch.bfloat16)
     net.fused_transport = fused
     el = E // world
     with torch.no_grad():
+        full.b1.copy_(torch.randn(full.b1.shape, generator=torch.Generator().manual_seed(5)) * 0.2)
+        full.b2.copy_(torch.randn(full.b2.shape, generator=torch.Generator().manual_seed(6)) * 0.2)
         net.router_weight.copy_(full.router_weight)
         for a, b in ((net.w1, full.w1), (net.w2, full.w2), (net.b1, full.b1), (net.b2, full.b2)):
             a.copy_(b[rank * el:(rank + 1) * el])
@@ -184,20 +191,30 @@ def _ep_gpu_worker(rank, world, fused):
     scale = float(ref.float().abs().max())
     err_out = float((out.float() - ref.float()).abs().max()) / scale
     err_dx = float((x.grad.float() - xr.grad.float()).abs().max()) / float(xr.grad.float().abs().max())
+    # expert weights see the tokens of every rank: the full layer's gradients summed over the ranks, sliced
+    err_dw = 0.0
+    for a, b in ((net.w1, full.w1), (net.w2, full.w2), (net.b1, full.b1), (net.b2, full.b2)):
+        gf = (b.grad if b.grad is not None else b.main_grad).float().clone()
+        torch.distributed.all_reduce(gf)
+        ga = (a.grad if a.grad is not None else a.main_grad).float()
+        ref_slice = gf[rank * el:(rank + 1) * el]
+        err_dw = max(err_dw, float((ga - ref_slice).abs().max()) / (float(ref_slice.abs().max()) + 1e-6))
     torch.cuda.synchronize()
     status = _native.device_status()
     torch.distributed.barrier()
     ms.communication.release()
-    return kind, err_out, err_dx, float(aux), float(aux_ref), status
+    return kind, err_out, err_dx, err_dw, float(aux), float(aux_ref), status
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("fused", [True, False])
-def test_expert_parallel_on_2_gpus(fused):
+@pytest.mark.parametrize("fused,drops", [(True, False), (False, False), (True, True)])
+def test_expert_parallel_on_2_gpus(fused, drops):
+    """fused: the expert GEMMs run the row exchange themselves (gather form in front of the first, push form behind
+    the second, and the mirrored forms in backward); otherwise torch all_to_all around batched GEMMs."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    for kind, err_out, err_dx, aux, aux_ref, status in run_ranks(_ep_gpu_worker, 2, fused):
+    for kind, err_out, err_dx, err_dw, aux, aux_ref, status in run_ranks(_ep_gpu_worker, 2, fused, drops):
         assert kind == ("_KernelTransport" if fused else "_TorchTransport")
         assert status == 0
-        assert err_out < 3e-2 and err_dx < 5e-2
+        assert err_out < 3e-2 and err_dx < 5e-2 and err_dw < 5e-2, (err_out, err_dx, err_dw)
         assert aux == pytest.approx(aux_ref, rel=1e-3)
