@@ -55,11 +55,13 @@ def parse():
     ap.add_argument("--batch-per-gpu", type=int, default=256, help="resnet50 only")
     ap.add_argument("--pp", type=int, default=None,
                     help="llama2-7b: pipeline stages (model parallel = N / pp inside a stage; 1F1B over "
-                         "--micro-batches micro-batches, activations sent with NCCL point-to-point).  Default: 2 on "
-                         "8 GPUs (the configuration 'pipeline_stages = 2 x mp = 4 with 8 micro-batches' of the "
-                         "Llama-2-7B benchmark definition, 1.6x the throughput of mp = 8 on this machine), else 1 "
-                         "(model parallel = N with sequence parallelism)")
-    ap.add_argument("--micro-batches", type=int, default=8, help="llama2-7b with --pp > 1")
+                         "--micro-batches micro-batches, activations sent with NCCL point-to-point).  Default: 2 "
+                         "from 2 GPUs on - the faster arrangement at every width measured on this machine (2 GPUs: "
+                         "41.5k tokens/s against 38.7k for mp2; 4: 77.3k against 67.4k for mp4; 8: 'pipeline_stages "
+                         "= 2 x mp = 4 with 8 micro-batches' of the Llama-2-7B benchmark definition, 1.6x mp8).  "
+                         "--pp 1 selects model parallel = N with sequence parallelism")
+    ap.add_argument("--micro-batches", type=int, default=None,
+                    help="llama2-7b with --pp > 1 (default 8 on 8 GPUs as the benchmark definition says, else 16)")
     return ap.parse_args()
 
 
@@ -301,7 +303,7 @@ def run_gpt_family(args):
     if dp > 1:
         opt.set_data_parallel_group(g["dp"], mean=True, shard=not moe)
     per_rank = global_batch // dp
-    micro_size = args.micro_size or 1
+    micro_size = args.micro_size or (1 if moe else 4)
     if per_rank % micro_size:
         raise SystemExit("--micro-size %d does not divide the %d sequences of a rank" % (micro_size, per_rank))
     micro = per_rank // micro_size                 # number of micro-batches
@@ -411,7 +413,9 @@ def main():
                              % args.gpus)
         args.gpus = world
     if args.pp is None:
-        args.pp = 2 if world == 8 else 1
+        args.pp = 2 if world >= 2 and world % 2 == 0 and args.mode != "graph" and args.impl == "ours" else 1
+    if args.micro_batches is None:
+        args.micro_batches = 8 if world == 8 else 16
     torch.cuda.set_device(local_rank)
     # With model parallelism the per-rank kernels shrink while the launch count does not: from 2 ranks on the step
     # is bound by host launch time unless the micro-batch is replayed as a CUDA graph.
@@ -534,8 +538,8 @@ def main():
                        "micro_batch": 1 if pp == 1 else args.global_batch // args.micro_batches, "seq_len": args.seq,
                        "parallelism": ("pp%d x mp%d+sp, 1F1B, %d micro-batches" % (pp, mp, args.micro_batches)
                                        if pp > 1 else "mp%d+sp" % world) if world > 1 else "single",
-                       "benchmark_config": ("Llama-2-7B, pipeline_stages=2 x mp=%d with %d micro-batches, send/recv "
-                                            "over NCCL p2p" % (mp, args.micro_batches)) if pp > 1 else
+                       "benchmark_config": ("Llama-2-7B, pipeline_stages=%d x mp=%d with %d micro-batches, send/recv "
+                                            "over NCCL p2p" % (pp, mp, args.micro_batches)) if pp > 1 else
                        "Llama-2-7B, mp=N with sequence parallel, micro-batch 1",
                        "formulation": "shard strategies (semi_auto_parallel dispatcher)" if args.impl == "ours"
                        else "hand-placed tensor parallel",

@@ -482,8 +482,10 @@ class MoE(Cell):
         self.dropout_rate = dropout_rate
         self._transports = {}
         self._exchanges = {}
-        # MSB200_MOE_FUSED_GEMM=0: expert GEMMs as separate launches around the scatter / gather kernels
-        self.fused_gemm = os.environ.get("MSB200_MOE_FUSED_GEMM", "1") != "0"
+        # MSB200_MOE_FUSED_GEMM=1 (or setting the attribute): the expert GEMMs run the row exchange themselves
+        # (_FusedExchange).  Off by default: with 4 experts per rank on 2 ranks the batched GEMM between the scatter /
+        # gather kernels measured 3 % faster than four GEMM launches that each gather or push their own rows.
+        self.fused_gemm = os.environ.get("MSB200_MOE_FUSED_GEMM", "0") == "1"
 
     def _transport(self, capacity, device):
         key = (capacity, device)

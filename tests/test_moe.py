@@ -173,6 +173,7 @@ def _ep_gpu_worker(rank, world, fused, drops=False):
     full = _layer(E, k, H, F, cf=cf, dtype=torch.bfloat16)
     net = _layer(E, k, H, F, cf=cf, group=ms.communication.GlobalComm.WORLD_COMM_GROUP, dtype=torch.bfloat16)
     net.fused_transport = fused
+    net.fused_gemm = fused
     el = E // world
     with torch.no_grad():
         full.b1.copy_(torch.randn(full.b1.shape, generator=torch.Generator().manual_seed(5)) * 0.2)
