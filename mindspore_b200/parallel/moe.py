@@ -298,6 +298,61 @@ class _CombineFn(torch.autograd.Function):
         return dybuf, dweight.to(weight.dtype), None, None, None
 
 
+class TopkRouter(Cell):
+    """Maps router logits to the dense dispatch / combine tensors of the GShard formulation.
+
+    ``construct(router_logits [..., T, E])`` returns ``(dispatch [..., T, E, C], combine [..., T, E, C], loss)``:
+    ``dispatch[t, e, c] = 1`` when token t sits in slot c of expert e, ``combine`` carries the normalised gate there,
+    ``loss`` is the load-balance loss (not yet multiplied by ``aux_loss_factor``), averaged over the leading groups.
+    Every leading index is one routing group with its own capacity, as in the reference
+    (python/mindspore/parallel/_transformer/moe.py:476).  ``MoE`` uses the index form (``route``) directly and never
+    builds these tensors."""
+
+    def __init__(self, d_model, moe_config, training=True, parallel_config=None):
+        super().__init__()
+        self.d_model = d_model
+        self.expert_dim = moe_config.expert_num
+        self.capacity_factor = moe_config.capacity_factor
+        self.num_experts_chosen = moe_config.num_experts_chosen
+        self.training = training
+
+    def construct(self, router_logits):
+        logits = router_logits.as_subclass(torch.Tensor)
+        lead, (T, E) = logits.shape[:-2], logits.shape[-2:]
+        k = self.num_experts_chosen
+        capacity = calculate_expert_capacity(k, T, self.capacity_factor, E)
+        groups = logits.reshape(-1, T, E)
+        dispatch, combine, losses = [], [], []
+        for g in groups:
+            expert, slot, weight, loss = route(g, k, capacity)
+            kept = slot >= 0
+            flat = (expert.long() * capacity + slot.clamp(min=0).long())          # [T, k] position in E * C
+            onehot = torch.nn.functional.one_hot(flat, E * capacity).to(weight.dtype) * kept[..., None]
+            dispatch.append(onehot.sum(1).reshape(T, E, capacity))
+            combine.append((onehot * weight[..., None]).sum(1).reshape(T, E, capacity))
+            losses.append(loss)
+        from ..common.tensor import as_tensor
+        shape = tuple(lead) + (T, E, capacity)
+        return (as_tensor(torch.stack(dispatch).reshape(shape)), as_tensor(torch.stack(combine).reshape(shape)),
+                as_tensor(torch.stack(losses).mean()))
+
+
+class Router(Cell):
+    """Router backbone: a bias-free Dense producing one logit per expert (computed in fp32), followed by the
+    routing policy (``TopkRouter`` unless ``routing_policy`` is given).  Parity: moe.py:412."""
+
+    def __init__(self, d_model, moe_config, routing_policy=None, training=True, parallel_config=None):
+        super().__init__()
+        self.d_model, self.expert_dim = d_model, moe_config.expert_num
+        self.weight = Parameter(initializer("normal", (self.expert_dim, d_model), torch.float32), name="dense.weight")
+        self.router = routing_policy if routing_policy is not None else \
+            TopkRouter(d_model, moe_config, training, parallel_config)
+
+    def construct(self, input_tensor):
+        x = input_tensor.as_subclass(torch.Tensor).float()
+        return self.router(torch.nn.functional.linear(x, self.weight.as_subclass(torch.Tensor).float()))
+
+
 # ------------------------------------------------------------------------------------------------ GEMMs fused with the exchange
 class _FusedExchange:
     """The expert GEMMs as the consumers / producers of the row exchange over symmetric memory.
