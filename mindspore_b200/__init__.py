@@ -38,5 +38,33 @@ from .dataset import mindrecord  # noqa: E402
 import multiprocessing  # noqa: E402  (the reference re-exports a fork-safe wrapper of the same module)
 from .graph.mindir import load_mindir  # noqa: E402
 
+from .common.dtype import QuantDtype  # noqa: E402
+from .common.jit_config import JitConfig  # noqa: E402
+from .common.api import jit_class as ms_class  # noqa: E402
+from .graph.flops import flops_collection  # noqa: E402
+from .dataset.mindrecord import *  # noqa: E402,F401,F403
+from .train.dataset_helper import DatasetHelper, connect_network_with_dataset  # noqa: E402
+from .train.amp import build_train_network  # noqa: E402
+from .train.loss_scale_manager import (DynamicLossScaleManager, FixedLossScaleManager,  # noqa: E402
+                                       LossScaleManager)
+from .train.serialization import (check_checkpoint, ckpt_to_safetensors, convert_model,  # noqa: E402
+                                  export_split_mindir, get_ckpt_path_with_strategy, load_checkpoint_async,
+                                  parse_print, safetensors_to_ckpt, save_mindir)
+from .train.callback import *  # noqa: E402,F401,F403
+from .utils.log import get_level, get_log_config  # noqa: E402
+from .ops import reshard  # noqa: E402
+from .rewrite import Node, NodeType, ScopedValue, SymbolTree  # noqa: E402
+from .safeguard import load_obf_params_into_net, obfuscate_ckpt, obfuscate_model  # noqa: E402
+from .context import get_ps_context, reset_ps_context, set_ps_context, set_offload_context  # noqa: E402
+from .nn.cell import GraphCell  # noqa: E402
+from . import _aliases  # noqa: E402
+
+_aliases.install()
+
+
+def __getattr__(name):
+    return _aliases.lazy_attribute(name)
+
+
 mstype = dtype
 __version__ = "0.1.0"

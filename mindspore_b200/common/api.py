@@ -459,3 +459,16 @@ from ..parallel.cost_model import (get_cost_model_context, reset_cost_model_cont
 def reset_algo_parameters():
     _algo.clear()
     _algo.update(_ALGO_DEFAULTS)
+
+
+def __getattr__(name):
+    # the reference keeps jit / ms_function / ms_class / flops_collection in common.api; they live in graph.jit here
+    if name in ("jit", "ms_function"):
+        from ..graph import jit as _jit
+        return getattr(_jit, name)
+    if name == "ms_class":
+        return jit_class
+    if name == "flops_collection":
+        from ..graph.flops import flops_collection
+        return flops_collection
+    raise AttributeError("module %r has no attribute %r" % (__name__, name))

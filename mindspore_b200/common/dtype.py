@@ -180,3 +180,32 @@ def is_floating(t) -> bool:
     return t in float_type
 
 Int._BY_BITS.update({8: int8, 16: int16, 32: int32, 64: int64})
+
+
+import enum as _enum
+
+
+class QuantDtype(_enum.Enum):
+    """Integer widths for quantisation: INT1 .. INT16 (values 0 .. 15) and UINT1 .. UINT16 (100 .. 115).
+    Parity: python/mindspore/common/dtype.py:353."""
+    locals().update({"INT%d" % b: b - 1 for b in range(1, 17)})
+    locals().update({"UINT%d" % b: 99 + b for b in range(1, 17)})
+
+    def __str__(self):
+        return self.name
+
+    @staticmethod
+    def is_signed(dtype):
+        return dtype.value < 100
+
+    @staticmethod
+    def switch_signed(dtype):
+        return QuantDtype(dtype.value + 100) if dtype.value < 100 else QuantDtype(dtype.value - 100)
+
+    @property
+    def num_bits(self):
+        return self.value % 100 + 1
+
+    def value_range(self):
+        b = self.num_bits
+        return (-(1 << (b - 1)), (1 << (b - 1)) - 1) if self.value < 100 else (0, (1 << b) - 1)

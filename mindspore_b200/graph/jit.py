@@ -469,6 +469,8 @@ def _compile(fn, inputs, kwargs, name, owner=None):
         if level:
             dump_graph(fg, os.path.join(path, "%s_step_parallel_end.ir" % name))
     cg = CompiledGraph(fg, out)
+    from .flops import note_compiled
+    note_compiled("train" if (owner is None or getattr(owner, "training", True)) else "predict", fg)
     plan = cg.executor.memory_plan
     if level:
         with open(os.path.join(path, "%s_memory_plan.txt" % name), "w") as f:

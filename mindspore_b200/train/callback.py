@@ -450,7 +450,9 @@ class OnRequestExit(Callback):
 
 
 class FlopsUtilizationCollector(Callback):
-    """Per-step model-FLOPs utilisation from a caller-supplied FLOPs-per-step figure."""
+    """Per-step model-FLOPs utilisation.  FLOPs per step: ``flops_per_step`` if given, else what
+    ``flops_collection('train')`` reports for the compiled training graph (GRAPH_MODE), looked up after the first
+    step.  ``peak_flops`` (per device, FLOP/s) turns the rate into a utilisation."""
 
     def __init__(self, data_size=None, computility=1, full_flops=True, enable_ma_collector=False,
                  flops_per_step=None, peak_flops=None):
@@ -468,6 +470,12 @@ class FlopsUtilizationCollector(Callback):
             torch.cuda.synchronize()
         dt = time.time() - self._t
         rec = {"step_time_s": dt}
+        if not self.flops_per_step:
+            try:
+                from ..graph.flops import flops_collection
+                self.flops_per_step = flops_collection("train")[2] or None
+            except RuntimeError:
+                pass
         if self.flops_per_step:
             rec["tflops"] = self.flops_per_step / dt / 1e12
             if self.peak:

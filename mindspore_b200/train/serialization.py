@@ -615,3 +615,44 @@ def load(file_name, **kwargs):
         tmp.write(raw)
         tmp.flush()
         return mindir.load_mindir(tmp.name)
+
+
+def save_mindir(model, file_name):
+    """Writes a loaded graph back to ``file_name`` (``.mindir`` appended when missing): a protobuf model message as
+    its serialized bytes, a ``FuncGraph`` in the native container.  Parity: serialization.py (save_mindir)."""
+    if not isinstance(file_name, str):
+        raise TypeError("For 'save_mindir', 'file_name' must be string, but got %s" % type(file_name))
+    if not file_name.endswith(".mindir"):
+        file_name += ".mindir"
+    folder = os.path.dirname(os.path.abspath(file_name))
+    os.makedirs(folder, exist_ok=True)
+    if hasattr(model, "SerializeToString"):
+        with open(file_name, "wb") as f:
+            f.write(model.SerializeToString())
+        return
+    from ..graph.ir import FuncGraph
+    from ..graph.mindir import save_mindir as _save_native
+    fg = model if isinstance(model, FuncGraph) else getattr(model, "fg", getattr(model, "graph", None))
+    if not isinstance(fg, FuncGraph):
+        raise TypeError("For 'save_mindir', 'model' must be a model protobuf message or a loaded graph, but got %s"
+                        % type(model))
+    _save_native(fg, file_name)
+
+
+def convert_model(mindir_file, convert_file, file_format):
+    """Converts a MindIR file to another format.  Only ``file_format='MINDIR'`` (a verified copy: the file is loaded
+    and written again) is available; ONNX export needs a converter that this build does not ship."""
+    if file_format == "ONNX":
+        raise NotImplementedError("convert_model: ONNX output is not available in this build")
+    if file_format != "MINDIR":
+        raise ValueError("For 'convert_model', 'file_format' must be 'ONNX' or 'MINDIR', but got %r" % (file_format,))
+    graph = load(mindir_file)
+    with open(mindir_file, "rb") as src:
+        data = src.read()
+    del graph                                   # parsed only to reject files that are not loadable graphs
+    with open(convert_file, "wb") as dst:
+        dst.write(data)
+
+
+from .safetensors_io import (check_checkpoint, ckpt_to_safetensors, get_ckpt_path_with_strategy,  # noqa: E402,F401
+                             safetensors_to_ckpt)

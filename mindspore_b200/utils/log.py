@@ -31,6 +31,19 @@ def get_level():
     return str({v: k for k, v in _LEVELS.items()}[logger.level])
 
 
+def get_log_config():
+    """The logging environment in effect, under the reference's variable names."""
+    cfg = {"GLOG_v": get_level()}
+    to_stderr = os.environ.get("GLOG_logtostderr", "1")
+    cfg["GLOG_logtostderr"] = to_stderr
+    if to_stderr == "0" and os.environ.get("GLOG_log_dir"):
+        cfg["GLOG_log_dir"] = os.environ["GLOG_log_dir"]
+    for k in ("GLOG_stderrthreshold", "MS_SUBMODULE_LOG_v", "logger_maxBytes", "logger_backupCount"):
+        if os.environ.get(k) is not None:
+            cfg[k] = os.environ[k]
+    return cfg
+
+
 def debug(msg, *a, **k): logger.debug(msg, *a, **k)
 def info(msg, *a, **k): logger.info(msg, *a, **k)
 def warning(msg, *a, **k): logger.warning(msg, *a, **k)

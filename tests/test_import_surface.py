@@ -1,0 +1,130 @@
+"""The reference's import paths and top-level names, FLOPs collection of a compiled graph, checkpoint weight
+obfuscation, QuantDtype, save_mindir / convert_model."""
+import importlib
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import mindspore_b200 as ms
+from mindspore_b200 import nn, ops
+
+
+@pytest.mark.parametrize("path,attr", [
+    ("amp", "DynamicLossScaler"), ("log", "get_log_config"), ("mindrecord", "FileWriter"),
+    ("nn.learning_rate_schedule", "CosineDecayLR"), ("nn.dynamic_lr", "piecewise_constant_lr"),
+    ("nn.transformer", "TransformerOpParallelConfig"), ("parallel._transformer.moe", "MoE"),
+    ("parallel.cluster.run", "main"), ("ops.operations.comm_ops", "AllReduce"), ("ops.function", "relu"),
+    ("common.api", "jit"), ("common.lazy_inline", "lazy_inline"), ("common.mutable", "mutable"),
+    ("common.dump", "set_dump"), ("train.summary.summary_record", "SummaryRecord"),
+    ("nn.wrap.loss_scale", "DynamicLossScaleUpdateCell"), ("nn.wrap.cell_wrapper", "PipelineCell"),
+    ("parallel.algo_parameter_config", "set_algo_parameters"), ("parallel._cost_model_context", "set_cost_model_context"),
+    ("communication.comm_func", "all_reduce"), ("profiler.profiling", "Profiler"), ("safeguard", "obfuscate_ckpt"),
+    ("dataset.engine.datasets", "GeneratorDataset"), ("train.callback", "ModelCheckpoint"),
+])
+def test_reference_import_paths_resolve(path, attr):
+    mod = importlib.import_module("mindspore_b200." + path)
+    assert hasattr(mod, attr), (path, attr)
+
+
+def test_top_level_names_and_aliases_are_the_real_modules():
+    for n in ["QuantDtype", "ms_class", "JitConfig", "flops_collection", "save_mindir", "FileWriter", "MindPage",
+              "DatasetHelper", "connect_network_with_dataset", "build_train_network", "FixedLossScaleManager",
+              "check_checkpoint", "export_split_mindir", "parse_print", "convert_model", "load_checkpoint_async",
+              "get_log_config", "reshard", "SymbolTree", "obfuscate_ckpt", "load_obf_params_into_net",
+              "SummaryCollector", "EarlyStopping", "ckpt_to_safetensors", "get_ckpt_path_with_strategy"]:
+        assert hasattr(ms, n), n
+    import mindspore_b200.amp as amp
+    import mindspore_b200.train.amp as real
+    assert amp is real and ms.amp is real and real.__spec__.name == "mindspore_b200.train.amp"
+    with pytest.raises(AttributeError):
+        ms.no_such_name
+    with pytest.raises(ImportError):
+        importlib.import_module("mindspore_b200.no_such_module")
+    q = ms.QuantDtype
+    assert q.INT8.value == 7 and q.UINT8.value == 107 and q.UINT4.num_bits == 4 and str(q.INT4) == "INT4"
+    assert q.switch_signed(q.INT8) is q.UINT8 and q.INT4.value_range() == (-8, 7) and not q.is_signed(q.UINT2)
+
+
+class _Mlp(nn.Cell):
+    def __init__(self):
+        super().__init__()
+        self.fc1 = nn.Dense(32, 64)
+        self.fc2 = nn.Dense(64, 8)
+
+    def construct(self, x):
+        return self.fc2(ops.relu(self.fc1(x)))
+
+
+def test_flops_collection_counts_the_compiled_training_graph():
+    from mindspore_b200.graph.flops import graph_flops
+    from mindspore_b200.graph.jit import trace_cell
+    ms.set_seed(0)
+    net = _Mlp()
+    x = ms.Tensor(torch.randn(16, 32))
+    fwd = graph_flops(trace_cell(net, (x,)))
+    mm = 2 * 16 * 32 * 64 + 2 * 16 * 64 * 8
+    assert mm <= fwd["model"] <= mm + 16 * (64 * 3 + 8 * 2)           # contractions + a few element-wise passes
+    ms.set_context(mode=ms.GRAPH_MODE)
+    try:
+        loss_net = nn.WithLossCell(net, nn.MSELoss())
+        step = nn.TrainOneStepCell(loss_net, nn.SGD(net.trainable_params(), learning_rate=0.1))
+        step.set_train()
+        step(x, ms.Tensor(torch.randn(16, 8)))
+        full, hw, shard, shard_hw, dynamic = ms.flops_collection("train")
+        assert 3 * mm <= full <= 3 * mm + 40 * 16 * 64 and hw == full and shard == full and dynamic is False
+    finally:
+        ms.set_context(mode=ms.PYNATIVE_MODE)
+    with pytest.raises(RuntimeError):
+        from mindspore_b200.graph import flops
+        flops._last.clear()
+        ms.flops_collection("train")
+
+
+def test_obfuscated_checkpoint_needs_the_ratios(tmp_path):
+    ms.set_seed(1)
+    net = _Mlp()
+    x = ms.Tensor(torch.randn(4, 32))
+    want = net(x).detach().numpy()
+    src, dst = tmp_path / "plain", tmp_path / "obf"
+    src.mkdir()
+    dst.mkdir()
+    ms.save_checkpoint(net, str(src / "net.ckpt"))
+    ratios = ms.obfuscate_ckpt(net, str(src), target_modules=["", "fc1|fc2"], saved_path=str(dst), obfuscate_scale=50)
+    assert len(ratios) == 2 and all(1 / 50 <= r <= 50 for r in ratios)
+    assert os.listdir(dst) == ["net_obf.ckpt"]
+    scaled = ms.load_checkpoint(str(dst / "net_obf.ckpt"))
+    np.testing.assert_allclose(scaled["fc1.weight"].detach().numpy(),
+                               net.fc1.weight.detach().numpy() * ratios[0], rtol=1e-5)
+    np.testing.assert_allclose(scaled["fc1.bias"].detach().numpy(), net.fc1.bias.detach().numpy())
+    ms.set_seed(2)
+    other = _Mlp()
+    ms.load_param_into_net(other, scaled)
+    assert not np.allclose(other(x).detach().numpy(), want, atol=1e-3)        # scaled weights alone are wrong
+    ms.load_obf_params_into_net(other, ["", "fc1|fc2"], ratios)
+    np.testing.assert_allclose(other(x).detach().numpy(), want, rtol=1e-4, atol=1e-5)
+    with pytest.raises(ValueError):
+        ms.obfuscate_ckpt(net, str(src), target_modules=["", "nope"], saved_path=str(dst))
+    with pytest.raises(ValueError):
+        ms.obfuscate_ckpt(net, str(src), target_modules=["a b", "fc1"], saved_path=str(dst))
+    with pytest.raises(ValueError):
+        ms.load_obf_params_into_net(_Mlp(), ["", "fc1|fc2"], [1.0])
+    with pytest.raises(NotImplementedError):
+        ms.obfuscate_model({})
+
+
+def test_save_mindir_and_convert_model(tmp_path):
+    ms.set_seed(3)
+    net = _Mlp()
+    x = ms.Tensor(torch.randn(2, 32))
+    ms.export(net, x, file_name=str(tmp_path / "m"), file_format="MINDIR")
+    ms.convert_model(str(tmp_path / "m.mindir"), str(tmp_path / "copy.mindir"), "MINDIR")
+    g = ms.load(str(tmp_path / "copy.mindir"))
+    np.testing.assert_allclose(nn.GraphCell(g)(x).detach().numpy(), net(x).detach().numpy(), rtol=1e-5, atol=1e-6)
+    with pytest.raises(NotImplementedError):
+        ms.convert_model(str(tmp_path / "m.mindir"), str(tmp_path / "m.onnx"), "ONNX")
+    with pytest.raises(ValueError):
+        ms.convert_model(str(tmp_path / "m.mindir"), str(tmp_path / "m.x"), "AIR")
+    with pytest.raises(TypeError):
+        ms.save_mindir(object(), str(tmp_path / "bad"))
