@@ -4,6 +4,8 @@ from .composite import (GradOperation, HyperMap, Map, MultitypeFuncGraph, Partia
                         clip_by_value, grad, jacfwd, jacrev, jvp, stop_gradient, value_and_grad, vjp)
 from .functional import *  # noqa: F401,F403
 from .operations import *  # noqa: F401,F403
+from . import function_ext as _function_ext
+globals().update({_n: getattr(_function_ext, _n) for _n in _function_ext.__all__ if _n not in globals()})
 from .primitive import (Primitive, PrimitiveWithCheck, PrimitiveWithInfer, constexpr, prim_attr_register)
 from . import functional as F  # noqa: N812
 from . import operations as P  # noqa: N812
@@ -43,3 +45,17 @@ def reshard(tensor, layout):
 def _wrap_reshard(t):
     from .primitive import _wrap_out
     return _wrap_out(t)
+
+
+_SPARSE_PREFIXES = ("coo_", "csr_", "make_", "row_tensor_", "dense_to_sparse_")
+_SPARSE_NAMES = ("coo2csr", "csr2coo", "coalesce")
+
+
+def __getattr__(name):
+    # the sparse functions need common.api (COOTensor / CSRTensor), which itself imports ops: resolved on first use
+    if name.startswith(_SPARSE_PREFIXES) or name in _SPARSE_NAMES:
+        import importlib
+        mod = importlib.import_module(__name__ + ".sparse_func")
+        if name in mod.__all__:
+            return getattr(mod, name)
+    raise AttributeError("module %r has no attribute %r" % (__name__, name))
