@@ -47,12 +47,17 @@ def _wrap_reshard(t):
     return _wrap_out(t)
 
 
+from .operations import _COMM_NAMES  # noqa: E402
 _SPARSE_PREFIXES = ("coo_", "csr_", "make_", "row_tensor_", "dense_to_sparse_")
 _SPARSE_NAMES = ("coo2csr", "csr2coo", "coalesce")
 
 
 def __getattr__(name):
     # the sparse functions need common.api (COOTensor / CSRTensor), which itself imports ops: resolved on first use
+    if name in _COMM_NAMES:
+        # the communication primitives import the communication package, which imports ops: resolved on first use
+        import importlib
+        return getattr(importlib.import_module(__name__ + ".comm_ops"), name)
     if name.startswith(_SPARSE_PREFIXES) or name in _SPARSE_NAMES:
         import importlib
         mod = importlib.import_module(__name__ + ".sparse_func")

@@ -261,10 +261,10 @@ def _scatter_nd_op(name, reduce):
                 cur = out[key]
                 out[key] = {"mul": cur * u[j], "div": cur / u[j], "max": torch.maximum(cur, u[j]),
                             "min": torch.minimum(cur, u[j])}[reduce]
-        if isinstance(input_x, torch.Tensor) and getattr(input_x, "requires_grad", False) is False and \
-                name.startswith("scatter_nd_"):
+        if name.startswith("scatter_nd_") and type(input_x).__name__ == "Parameter":
             with torch.no_grad():
-                _t(input_x).copy_(out)                       # Parameter form: in place, as the reference's
+                _t(input_x).copy_(out)                       # Parameter form: updated in place, as the reference's
+            return _w(_t(input_x))
         return _w(out)
     fn.__name__ = name
     return fn

@@ -1346,7 +1346,24 @@ __all__ = [n for n, v in list(globals().items()) if isinstance(v, type) and issu
 
 
 from .operations_ext import *  # noqa: E402,F401,F403  (second-tier primitives)
+from .operations_more import *  # noqa: E402,F401,F403  (third tier: the long tail)
 from .llm_ops import *  # noqa: E402,F401,F403  (fused decoder primitives)
 from . import llm_ops as _llm_ops  # noqa: E402
 
-__all__ = __all__ + list(_llm_ops.__all__)
+from . import operations_ext as _ops_ext, operations_more as _ops_more  # noqa: E402
+
+__all__ = list(dict.fromkeys(__all__ + list(_ops_ext.__all__) + list(_ops_more.__all__) + list(_llm_ops.__all__)))
+
+
+
+_COMM_NAMES = ("AllGather", "AllReduce", "AlltoAll", "AlltoAllV", "Barrier", "BatchISendIRecv", "Broadcast",
+               "CollectiveGather", "CollectiveScatter", "NeighborExchange", "NeighborExchangeV2", "Receive", "Reduce",
+               "ReduceOp", "ReduceScatter", "Send", "AShardIdentity")
+
+
+def __getattr__(name):
+    # the communication primitives import the communication package, which imports ops: resolved on first use
+    if name in _COMM_NAMES:
+        import importlib
+        return getattr(importlib.import_module(__package__ + ".comm_ops"), name)
+    raise AttributeError("module %r has no attribute %r" % (__name__, name))
