@@ -209,8 +209,104 @@ def slice_shape(self):
     return tuple(self.shape)
 
 
+def approximate_equal(self, other, tolerance=1e-5):
+    return _w((_p(self) - _p(torch.as_tensor(other))).abs() < tolerance)
+
+
+def argmax_with_value(self, axis=0, keep_dims=False):
+    r = torch.max(_p(self), axis, keep_dims)
+    return _w(r.indices.to(torch.int32)), _w(r.values)
+
+
+def argmin_with_value(self, axis=0, keep_dims=False):
+    r = torch.min(_p(self), axis, keep_dims)
+    return _w(r.indices.to(torch.int32)), _w(r.values)
+
+
+def cauchy(self, median=0.0, sigma=1.0):
+    return _w(torch.empty_like(_p(self)).cauchy_(median, sigma))
+
+
+def log_normal(self, mean=1.0, std=2.0):
+    return _w(torch.empty_like(_p(self)).log_normal_(mean, std))
+
+
+def uniform(self, from_=0.0, to=1.0, generator=None):
+    return _w(torch.empty_like(_p(self)).uniform_(from_, to))
+
+
+def eigvals(self):
+    return _w(torch.linalg.eigvals(_p(self)))
+
+
+def fill_diagonal(self, fill_value, wrap=False):
+    return _w(_p(self).clone().fill_diagonal_(fill_value, wrap))
+
+
+def fold(self, output_size, kernel_size, dilation=1, padding=0, stride=1):
+    return _w(torch.nn.functional.fold(_p(self), tuple(int(v) for v in torch.as_tensor(output_size).tolist()),
+                                       kernel_size, dilation, padding, stride))
+
+
+def inv(self):
+    return _w(torch.reciprocal(_p(self)))
+
+
+def invert(self):
+    return _w(torch.bitwise_not(_p(self)))
+
+
+def log_matrix_determinant(self):
+    sign, logabs = torch.linalg.slogdet(_p(self))
+    return _w(sign), _w(logabs)
+
+
+def reverse(self, axis):
+    return _w(torch.flip(_p(self), tuple(axis) if isinstance(axis, (tuple, list)) else (axis,)))
+
+
+def reverse_sequence(self, seq_lengths, seq_dim=0, batch_dim=0):
+    from ..ops.function_ext import reverse_sequence as _rs
+    return _rs(self, seq_lengths, seq_dim, batch_dim)
+
+
+def xdivy(self, y):
+    a = _p(self)
+    b = _p(torch.as_tensor(y))
+    return _w(torch.where(a == 0, torch.zeros_like(a / b), a / b))
+
+
+def value(self):
+    """The tensor held by a Parameter (a Tensor is its own value)."""
+    return _w(_p(self).detach())
+
+
+def is_persistent_data(self):
+    return False
+
+
+def slice_num_of_persistent_data(self):
+    return 1
+
+
+def slice_shape_of_persistent_data(self):
+    return tuple(self.shape)
+
+
+def asnumpy_of_slice_persistent_data(self, param_key, slice_index):
+    return _p(self).detach().cpu().numpy()
+
+
 def _install():
-    methods = dict(itemset=itemset, fills=fills, ptp=ptp, to_tensor=to_tensor, init_check=init_check, choose=choose,
+    methods = dict(approximate_equal=approximate_equal, argmax_with_value=argmax_with_value,
+                   argmin_with_value=argmin_with_value, cauchy=cauchy, log_normal=log_normal, uniform=uniform,
+                   eigvals=eigvals, fill_diagonal=fill_diagonal, fold=fold, inv=inv, invert=invert,
+                   log_matrix_determinant=log_matrix_determinant, reverse=reverse, reverse_sequence=reverse_sequence,
+                   xdivy=xdivy, value=value, is_persistent_data=is_persistent_data,
+                   slice_num_of_persistent_data=slice_num_of_persistent_data,
+                   slice_shape_of_persistent_data=slice_shape_of_persistent_data,
+                   asnumpy_of_slice_persistent_data=asnumpy_of_slice_persistent_data,
+                   itemset=itemset, fills=fills, ptp=ptp, to_tensor=to_tensor, init_check=init_check, choose=choose,
                    searchsorted=searchsorted, gather_nd=gather_nd, inplace_update=inplace_update,
                    random_categorical=random_categorical, one_hot=one_hot, unique_with_pad=unique_with_pad,
                    col2im=col2im, soft_shrink=soft_shrink, pinv=pinv, matrix_determinant=matrix_determinant,

@@ -100,7 +100,9 @@ def _fill_submodules():
     for name in ("relu", "gelu", "silu", "softmax", "log_softmax", "dropout", "layer_norm", "linear", "embedding",
                  "cross_entropy", "mse_loss", "l1_loss", "sigmoid", "tanh", "one_hot", "pad", "max_pool2d",
                  "avg_pool2d", "batch_norm", "group_norm", "normalize", "softplus", "leaky_relu", "elu",
-                 "binary_cross_entropy_with_logits", "interpolate", "unfold", "fold", "grid_sample"):
+                 "binary_cross_entropy_with_logits", "interpolate", "unfold", "fold", "grid_sample",
+                 "binary_cross_entropy", "conv_transpose2d", "conv2d", "max_unpool2d", "hardswish", "hardsigmoid",
+                 "mish", "prelu", "selu", "softshrink", "hardshrink", "logsigmoid", "adaptive_avg_pool2d"):
         if hasattr(torch.nn.functional, name):
             setattr(functional, name, _wrap(getattr(torch.nn.functional, name)))
     nn.functional = functional
