@@ -779,3 +779,144 @@ class SparseTensorDenseMatmul(Cell):
 
 __all__ += ["MatMul", "Range", "CentralCrop", "ImageGradients", "PSNR", "SSIM", "MSSSIM", "TimeDistributed",
             "ParameterUpdate", "Jvp", "Vjp", "VirtualDatasetCellTriple", "SparseToDense", "SparseTensorDenseMatmul"]
+
+
+# ------------------------------------------------------------------------------------------------ combined / THOR layers
+_fn_cell("MaxUnpool1d", lambda x, idx, k, s, p: F.max_unpool1d(x, idx.long(), k, s, p),
+         ("kernel_size", "stride", "padding"), (1, None, 0))
+_fn_cell("MaxUnpool3d", lambda x, idx, k, s, p: F.max_unpool3d(x, idx.long(), k, s, p),
+         ("kernel_size", "stride", "padding"), (1, None, 0))
+
+
+class FractionalMaxPool3d(Cell):
+    def __init__(self, kernel_size, output_size=None, output_ratio=None, return_indices=False, _random_samples=None):
+        super().__init__()
+        self.args = (kernel_size, output_size, output_ratio, return_indices, _random_samples)
+
+    def construct(self, x):
+        k, o, r, ri, rs = self.args
+        return _wrap_out(F.fractional_max_pool3d(x, k, o, r, ri, rs))
+
+
+class DropoutExt(Dropout):
+    """``Dropout`` with the probability of zeroing as its only argument."""
+
+    def __init__(self, p=0.5):
+        super().__init__(p=p)
+
+
+class Conv2dBnAct(Cell):
+    """Conv2d, then optionally BatchNorm2d, then optionally an activation (``'relu'``, ``'leakyrelu'`` with
+    ``alpha``, any name ``get_activation`` knows, or a Cell).  Parity: nn/layer/combined.py (Conv2dBnAct)."""
+
+    def __init__(self, in_channels, out_channels, kernel_size, stride=1, pad_mode="same", padding=0, dilation=1,
+                 group=1, has_bias=False, weight_init="normal", bias_init="zeros", has_bn=False, momentum=0.997,
+                 eps=1e-5, activation=None, alpha=0.2, after_fake=True, dtype=mstype.float32):
+        super().__init__()
+        from .layer import BatchNorm2d, Conv2d, LeakyReLU, get_activation
+        self.conv = Conv2d(in_channels, out_channels, kernel_size, stride, pad_mode, padding, dilation, group,
+                           has_bias, weight_init, bias_init, dtype=dtype)
+        self.has_bn = has_bn
+        if has_bn:
+            self.batchnorm = BatchNorm2d(out_channels, eps, momentum)
+        if activation == "leakyrelu":
+            self.activation = LeakyReLU(alpha)
+        else:
+            self.activation = get_activation(activation) if isinstance(activation, str) else activation
+        self.has_act = self.activation is not None
+
+    def construct(self, x):
+        x = self.conv(x)
+        if self.has_bn:
+            x = self.batchnorm(x)
+        return self.activation(x) if self.has_act else x
+
+
+class DenseBnAct(Cell):
+    """Dense, then optionally BatchNorm1d, then optionally an activation.  Parity: nn/layer/combined.py."""
+
+    def __init__(self, in_channels, out_channels, weight_init="normal", bias_init="zeros", has_bias=True,
+                 has_bn=False, momentum=0.9, eps=1e-5, activation=None, alpha=0.2, after_fake=True,
+                 dtype=mstype.float32):
+        super().__init__()
+        from .layer import BatchNorm1d, LeakyReLU, get_activation
+        self.dense = Dense(in_channels, out_channels, weight_init, bias_init, has_bias, dtype=dtype)
+        self.has_bn = has_bn
+        if has_bn:
+            self.batchnorm = BatchNorm1d(out_channels, eps, momentum)
+        if activation == "leakyrelu":
+            self.activation = LeakyReLU(alpha)
+        else:
+            self.activation = get_activation(activation) if isinstance(activation, str) else activation
+        self.has_act = self.activation is not None
+
+    def construct(self, x):
+        x = self.dense(x)
+        if self.has_bn:
+            x = self.batchnorm(x)
+        return self.activation(x) if self.has_act else x
+
+
+class DenseThor(Dense):
+    """``Dense`` as the THOR optimizer's layer type: carries the Kronecker factors ``matrix_a`` (input second
+    moment) and ``matrix_g`` (output-gradient second moment) as non-trainable parameters; ``nn.THOR`` fills them
+    from hooks on any Dense layer, this class only provides the named state the reference's checkpoints hold.
+    Parity: nn/layer/thor_layer.py (DenseThor)."""
+
+    def __init__(self, in_channels, out_channels, weight_init="normal", bias_init="zeros", has_bias=True,
+                 activation=None):
+        super().__init__(in_channels, out_channels, weight_init, bias_init, has_bias, activation)
+        self.thor = True
+        self.matrix_a = Parameter(torch.eye(in_channels), name="matrix_a", requires_grad=False)
+        self.matrix_g = Parameter(torch.eye(out_channels), name="matrix_g", requires_grad=False)
+
+
+def _thor_conv():
+    from .layer import Conv2d
+
+    class Conv2dThor(Conv2d):
+        """``Conv2d`` with the THOR factor state (``matrix_a`` over in_channels * kh * kw, ``matrix_g`` over
+        out_channels).  Parity: nn/layer/thor_layer.py (Conv2dThor)."""
+
+        def __init__(self, in_channels, out_channels, kernel_size, stride=1, pad_mode="same", padding=0, dilation=1,
+                     group=1, has_bias=False, weight_init="normal", bias_init="zeros"):
+            super().__init__(in_channels, out_channels, kernel_size, stride, pad_mode, padding, dilation, group,
+                             has_bias, weight_init, bias_init)
+            self.thor = True
+            a_dim = in_channels * self.kernel_size[0] * self.kernel_size[1]
+            self.matrix_a = Parameter(torch.eye(a_dim), name="matrix_a", requires_grad=False)
+            self.matrix_g = Parameter(torch.eye(out_channels), name="matrix_g", requires_grad=False)
+    return Conv2dThor
+
+
+def _thor_embeddings():
+    from .layer import Embedding, EmbeddingLookup
+
+    class EmbeddingThor(Embedding):
+        """``Embedding`` with the THOR factor state: ``matrix_a`` is diagonal (token frequencies, [vocab_size]),
+        ``matrix_g`` is [embedding_size, embedding_size].  Parity: nn/layer/thor_layer.py (EmbeddingThor)."""
+
+        def __init__(self, vocab_size, embedding_size, use_one_hot=False, embedding_table="normal",
+                     dtype=mstype.float32, padding_idx=None):
+            super().__init__(vocab_size, embedding_size, use_one_hot, embedding_table, dtype, padding_idx)
+            self.thor = True
+            self.matrix_a = Parameter(torch.ones(vocab_size), name="matrix_a", requires_grad=False)
+            self.matrix_g = Parameter(torch.eye(embedding_size), name="matrix_g", requires_grad=False)
+
+    class EmbeddingLookupThor(EmbeddingLookup):
+        """``EmbeddingLookup`` with the THOR factor state.  Parity: nn/layer/thor_layer.py (EmbeddingLookupThor)."""
+
+        def __init__(self, vocab_size, embedding_size, param_init="normal", target="CPU", slice_mode="batch_slice",
+                     manual_shapes=None, max_norm=None, sparse=True, vocab_cache_size=0):
+            super().__init__(vocab_size, embedding_size, param_init, target, slice_mode, manual_shapes, max_norm,
+                             sparse, vocab_cache_size)
+            self.thor = True
+            self.matrix_a = Parameter(torch.ones(vocab_size), name="matrix_a", requires_grad=False)
+            self.matrix_g = Parameter(torch.eye(embedding_size), name="matrix_g", requires_grad=False)
+    return EmbeddingThor, EmbeddingLookupThor
+
+
+Conv2dThor = _thor_conv()
+EmbeddingThor, EmbeddingLookupThor = _thor_embeddings()
+__all__ += ["FractionalMaxPool3d", "DropoutExt", "Conv2dBnAct", "DenseBnAct", "DenseThor", "Conv2dThor",
+            "EmbeddingThor", "EmbeddingLookupThor"]

@@ -316,3 +316,19 @@ class SampledSoftmaxLoss(LossBase):
         all_logits = torch.cat([true_logit, samp_logit], 1).float()
         target = torch.cat([torch.full_like(true_logit, 1.0 / self.num_true), torch.zeros_like(samp_logit)], 1).float()
         return self.get_loss(-(target * torch.log_softmax(all_logits, -1)).sum(-1))
+
+
+class TripletMarginWithDistanceLoss(LossBase):
+    """max(d(a, p) - d(a, n) + margin, 0) with a caller-supplied distance (pairwise L2 by default); ``swap`` uses
+    min(d(a, n), d(p, n)) as the negative distance.  Parity: nn/loss/loss.py (TripletMarginWithDistanceLoss)."""
+
+    def __init__(self, distance_function=None, swap=False, reduction="mean", margin=1.0):
+        super().__init__(reduction)
+        self.distance_function, self.swap, self.margin = distance_function, swap, margin
+
+    def construct(self, x, positive, negative):
+        d = self.distance_function or (lambda a, b: _wrap_out(F.pairwise_distance(a, b)))
+        dp, dn = d(x, positive), d(x, negative)
+        if self.swap:
+            dn = torch.minimum(dn, d(positive, negative))
+        return self.get_loss(_wrap_out(torch.clamp(dp - dn + self.margin, min=0)))

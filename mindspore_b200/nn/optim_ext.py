@@ -12,7 +12,7 @@ from ..ops.primitive import _wrap_out
 from .cell import Cell
 from .optim import Adam, Momentum, Optimizer, _to_plain
 
-__all__ = ["ConvertNetUtils", "ConvertModelUtils", "LazyAdam", "AdamOffload", "THOR", "thor", "AdaSumByGradWrapCell", "AdaSumByDeltaWeightWrapCell"]
+__all__ = ["opt_init_args_register", "ConvertNetUtils", "ConvertModelUtils", "LazyAdam", "AdamOffload", "THOR", "thor", "AdaSumByGradWrapCell", "AdaSumByDeltaWeightWrapCell"]
 
 
 class LazyAdam(Adam):
@@ -237,3 +237,24 @@ class ConvertModelUtils:
         if not isinstance(optimizer, THOR):
             return model
         return Model(network, loss_fn, optimizer, metrics, amp_level=amp_level, loss_scale_manager=loss_scale_manager)
+
+
+def opt_init_args_register(fn):
+    """Decorator for an optimizer's ``__init__``: records the constructor arguments (tensors and parameter lists
+    left out) as ``self.init_args``, which checkpoint tools and ``boost`` read back.  Parity:
+    nn/optim/optimizer.py (opt_init_args_register)."""
+    import functools
+    import inspect
+
+    @functools.wraps(fn)
+    def deco(self, *args, **kwargs):
+        bound = inspect.signature(fn).bind(self, *args, **kwargs)
+        bound.apply_defaults()
+        keep = {}
+        for k, v in list(bound.arguments.items())[1:]:
+            if k in ("params", "parameters") or isinstance(v, torch.Tensor):
+                continue
+            keep[k] = v
+        object.__setattr__(self, "init_args", keep)
+        return fn(self, *args, **kwargs)
+    return deco

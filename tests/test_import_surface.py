@@ -128,3 +128,31 @@ def test_save_mindir_and_convert_model(tmp_path):
         ms.convert_model(str(tmp_path / "m.mindir"), str(tmp_path / "m.x"), "AIR")
     with pytest.raises(TypeError):
         ms.save_mindir(object(), str(tmp_path / "bad"))
+
+
+def test_remaining_nn_names():
+    x = ms.Tensor(torch.randn(2, 3, 8, 8))
+    y = nn.Conv2dBnAct(3, 4, 3, has_bn=True, activation="relu")(x)
+    assert y.shape == (2, 4, 8, 8) and float(y.min()) >= 0
+    assert nn.DenseBnAct(5, 2, has_bn=True, activation="leakyrelu")(ms.Tensor(torch.randn(4, 5))).shape == (4, 2)
+    d = nn.DenseThor(4, 3)
+    assert sorted(p.name for p in d.get_parameters()) == ["bias", "matrix_a", "matrix_g", "weight"]
+    assert [p.name for p in d.trainable_params()] == ["weight", "bias"] or \
+        sorted(p.name for p in d.trainable_params()) == ["bias", "weight"]
+    assert nn.Conv2dThor(3, 4, 3).matrix_a.shape == (27, 27) and nn.EmbeddingThor(10, 4).matrix_g.shape == (4, 4)
+    assert nn.EmbeddingLookupThor(10, 4).matrix_a.shape == (10,)
+    loss = nn.TripletMarginWithDistanceLoss(margin=1.0)(ms.Tensor(torch.zeros(2, 3)), ms.Tensor(torch.zeros(2, 3)),
+                                                        ms.Tensor(torch.full((2, 3), 0.1)))
+    assert abs(float(loss) - (1 - 0.1 * 3 ** 0.5)) < 1e-3
+    pooled, idx = torch.nn.functional.max_pool1d(torch.arange(8.).reshape(1, 1, 8), 2, return_indices=True)
+    assert nn.MaxUnpool1d(2)(ms.Tensor(pooled), ms.Tensor(idx)).shape == (1, 1, 8)
+    assert nn.FractionalMaxPool3d(2, output_size=(2, 2, 2))(ms.Tensor(torch.randn(1, 1, 5, 5, 5))).shape == (1, 1, 2, 2, 2)
+    drop = nn.DropoutExt(0.25)
+    assert drop.p == 0.25
+
+    class Opt:
+        @nn.opt_init_args_register
+        def __init__(self, params, learning_rate=0.1, beta=ms.Tensor([0.9])):
+            self.lr = learning_rate
+
+    assert Opt([1, 2], learning_rate=0.5).init_args == {"learning_rate": 0.5}
