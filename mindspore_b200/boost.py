@@ -244,3 +244,60 @@ class GroupLossScaleManager(Cell):
                     self.scales[i] *= self.scale_factor
                     self._good[i] = 0
         return list(self.scales)
+
+
+def _accumulate(accumulation_step, grad_sum, grad):
+    with torch.no_grad():
+        grad_sum.as_subclass(torch.Tensor).add_(grad.detach().as_subclass(torch.Tensor).to(grad_sum.dtype)
+                                                / float(accumulation_step))
+    return True
+
+
+def _clear(grad_sum, zero=None):
+    with torch.no_grad():
+        grad_sum.as_subclass(torch.Tensor).zero_()
+    return True
+
+
+class _PerTensor:
+    """Applies a function to every tensor of the sequences it is mapped over (what ``HyperMap`` does with the
+    reference's MultitypeFuncGraph objects of the same names)."""
+
+    def __init__(self, name, fn):
+        self.name, self.fn = name, fn
+
+    def __call__(self, *args):
+        return self.fn(*args)
+
+    def register(self, *types):
+        return lambda f: f
+
+
+gradient_accumulation_op = _PerTensor("gradient_accumulation_op", _accumulate)
+gradient_clear_op = _PerTensor("gradient_clear_op", _clear)
+
+
+class CommonHeadLastFN(Cell):
+    """Classifier head of the gradient-freezing networks: L2-normalised features times L2-normalised weight rows
+    (a cosine classifier), scaled by a learnable-free multiplier.  Parity: boost/base.py (CommonHeadLastFN)."""
+
+    def __init__(self, in_channels, out_channels, weight_init="normal", bias_init="zeros", has_bias=True):
+        super().__init__()
+        from .common.initializer import initializer
+        from .common.parameter import Parameter
+        self.weight = Parameter(initializer(weight_init, (out_channels, in_channels), torch.float32), name="weight")
+        self.bias = Parameter(initializer(bias_init, (out_channels,), torch.float32), name="bias") if has_bias else None
+        self.multiplier = 20.0
+
+    def construct(self, x):
+        from .common.tensor import as_tensor
+        t = x.as_subclass(torch.Tensor)
+        w = self.weight.as_subclass(torch.Tensor)
+        out = torch.nn.functional.linear(torch.nn.functional.normalize(t, dim=1),
+                                         torch.nn.functional.normalize(w, dim=1)) * self.multiplier
+        if self.bias is not None:
+            out = out + self.bias.as_subclass(torch.Tensor)
+        return as_tensor(out)
+
+
+__all__ += ["gradient_accumulation_op", "gradient_clear_op", "CommonHeadLastFN"]

@@ -7,3 +7,4 @@ from . import transforms, vision
 from . import samplers  # noqa: E402
 from .samplers import *  # noqa: E402,F401,F403
 from .sources import *  # noqa: E402,F401,F403
+from .sources_ext import *  # noqa: E402,F401,F403

@@ -144,8 +144,14 @@ def _scheduler(name):
     return _S
 
 
-lr_scheduler = types.SimpleNamespace(**{n: _scheduler(n) for n in (
+lr_scheduler = types.ModuleType(__name__ + ".lr_scheduler")
+lr_scheduler.__dict__.update({n: _scheduler(n) for n in (
     "StepLR", "LinearLR", "ExponentialLR", "PolynomialLR", "ChainedScheduler", "MultiplicativeLR", "ConstantLR",
     "SequentialLR", "ReduceLROnPlateau", "CyclicLR", "CosineAnnealingWarmRestarts", "CosineAnnealingLR", "LambdaLR",
     "MultiStepLR")})
 lr_scheduler.LRScheduler = torch.optim.lr_scheduler.LRScheduler
+lr_scheduler.__all__ = [n for n in vars(lr_scheduler) if not n.startswith("_")]
+import sys as _sys  # noqa: E402
+
+_sys.modules[lr_scheduler.__name__] = lr_scheduler        # `from ...experimental.optim.lr_scheduler import StepLR`
+__path__ = []                                             # lets the import system look below this module

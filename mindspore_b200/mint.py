@@ -123,3 +123,15 @@ _fill_submodules()
 
 arctan2 = _wrap(torch.arctan2)
 inverse = _wrap(torch.linalg.inv)
+
+
+
+def _register_submodules():
+    import sys
+    for m in (special, distributed, nn, optim, linalg, functional):
+        sys.modules.setdefault(m.__name__, m)
+    globals().setdefault("__path__", [])                  # `import mindspore_b200.mint.nn.functional` resolves
+    nn.__dict__.setdefault("__path__", [])
+
+
+_register_submodules()

@@ -289,3 +289,24 @@ polyder polyint bartlett blackman hamming hanning kaiser""".split():
     if _n not in globals() and hasattr(_onp, _n):
         globals()[_n] = _host(_n)
 mgrid, ogrid = _onp.mgrid, _onp.ogrid
+
+
+# ---------------------------------------------------------------------------------------------------- numpy.fft
+def _fft_namespace():
+    import types as _types
+
+    import torch as _torch
+
+    from .ops import function_ext as _fx
+    mod = _types.ModuleType(__name__ + ".fft")
+    for _n in ("fft", "ifft", "fft2", "ifft2", "fftn", "ifftn", "fftshift", "ifftshift", "rfft", "irfft"):
+        setattr(mod, _n, getattr(_fx, _n))
+    mod.__all__ = ["fft", "ifft", "fft2", "ifft2", "fftn", "ifftn", "fftshift", "ifftshift", "rfft", "irfft"]
+    import sys as _sys
+    _sys.modules[mod.__name__] = mod
+    return mod
+
+
+fft = _fft_namespace()
+fft2, ifft2, fftn, ifftn, fftshift, ifftshift, ifft = (fft.fft2, fft.ifft2, fft.fftn, fft.ifftn, fft.fftshift,
+                                                       fft.ifftshift, fft.ifft)

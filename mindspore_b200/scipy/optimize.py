@@ -8,7 +8,7 @@ import torch
 
 from ..ops.primitive import _wrap_out
 
-__all__ = ["minimize", "line_search", "OptimizeResults"]
+__all__ = ["minimize", "line_search", "OptimizeResults", "linear_sum_assignment"]
 
 OptimizeResults = namedtuple("OptimizeResults", "x success status fun jac hess_inv nfev njev nit")
 LineSearchResults = namedtuple("LineSearchResults", "a_k f_k g_k nfev ngev failed")
@@ -126,3 +126,19 @@ def minimize(func, x0, args=(), method="BFGS", jac=None, hess=None, hessp=None, 
     success = status == 0 and float(g.abs().max()) <= gtol
     return OptimizeResults(_wrap_out(x), success, status, _wrap_out(f), _wrap_out(g),
                            _wrap_out(H) if m == "BFGS" else None, nfev, nfev, nit)
+
+
+def linear_sum_assignment(cost_matrix, maximize, dimension_limit=None):
+    """Rows and columns of the minimum- (or maximum-) cost assignment of a rectangular cost matrix;
+    ``dimension_limit`` restricts the problem to the first columns.  Solved on the host (Jonker-Volgenant, SciPy)."""
+    import scipy.optimize as _so
+    c = cost_matrix.detach().as_subclass(torch.Tensor).cpu() if isinstance(cost_matrix, torch.Tensor) else \
+        torch.as_tensor(cost_matrix)
+    if dimension_limit is not None:
+        lim = int(dimension_limit)
+        if lim > c.shape[1]:
+            raise ValueError("dimension_limit %d exceeds the %d columns of the cost matrix" % (lim, c.shape[1]))
+        c = c[:, :lim]
+    mx = bool(maximize) if not isinstance(maximize, torch.Tensor) else bool(maximize.item())
+    rows, cols = _so.linear_sum_assignment(c.numpy(), maximize=mx)
+    return _wrap_out(torch.as_tensor(rows, dtype=torch.int64)), _wrap_out(torch.as_tensor(cols, dtype=torch.int64))

@@ -214,3 +214,5 @@ def init_status():
     import torch
     from ..common.tensor import Tensor
     return Tensor(torch.zeros(8, dtype=torch.float32))
+
+from .loss_scale_manager import DynamicLossScaleManager, FixedLossScaleManager, LossScaleManager  # noqa: E402,F401
