@@ -39,7 +39,77 @@ class _Config:
         return self.num_parallel_workers
 
 
+class ErrorSamplesMode:
+    """What a pipeline does with a row whose transform raised: stop with the error, replace the row, or skip it."""
+    RETURN, REPLACE, SKIP = 0, 1, 2
+
+
+def _setting(name, default, check=None):
+    """A getter / setter pair of one more pipeline setting (stored on the config object)."""
+    def setter(self, value):
+        if check is not None:
+            check(value)
+        self._settings[name] = value
+
+    def getter(self):
+        return self._settings.get(name, default)
+    return setter, getter
+
+
+def _positive(label):
+    def check(v):
+        if isinstance(v, bool) or not isinstance(v, (int, float)) or v <= 0:
+            raise ValueError("%s must be a positive number, but got %r" % (label, v))
+    return check
+
+
+def _boolean(label):
+    def check(v):
+        if not isinstance(v, bool):
+            raise TypeError("%s must be a bool, but got %r" % (label, v))
+    return check
+
+
+_Config._settings = {}
+for _name, _default, _check in (
+        ("numa_enable", False, _boolean("numa_enable")),
+        ("monitor_sampling_interval", 1000, _positive("monitor_sampling_interval")),
+        ("auto_num_workers", False, _boolean("auto_num_workers")),
+        ("callback_timeout", 60, _positive("callback_timeout")),
+        ("enable_autotune", False, None), ("autotune_interval", 0, None),
+        ("enable_shared_mem", True, _boolean("enable_shared_mem")),
+        ("sending_batches", 0, None), ("auto_offload", False, _boolean("auto_offload")),
+        ("enable_watchdog", True, _boolean("enable_watchdog")),
+        ("multiprocessing_timeout_interval", 300, _positive("multiprocessing_timeout_interval")),
+        ("dynamic_shape", False, _boolean("dynamic_shape")), ("fast_recovery", True, _boolean("fast_recovery")),
+        ("debug_mode", False, None), ("error_samples_mode", ErrorSamplesMode.RETURN, None)):
+    _set, _get = _setting(_name, _default, _check)
+    setattr(_Config, "set_" + _name, _set)
+    setattr(_Config, "get_" + _name, _get)
+
+
+def _config_load(self, file):
+    """Reads settings from a JSON file with the reference's keys (numParallelWorkers, opConnectorSize /
+    prefetchSize, seed, monitorSamplingInterval, ...)."""
+    import json
+    with open(file) as f:
+        cfg = json.load(f)
+    if "numParallelWorkers" in cfg:
+        self.set_num_parallel_workers(cfg["numParallelWorkers"])
+    if "opConnectorSize" in cfg or "prefetchSize" in cfg:
+        self.set_prefetch_size(cfg.get("prefetchSize", cfg.get("opConnectorSize")))
+    if "seed" in cfg:
+        self.set_seed(cfg["seed"])
+    if "monitorSamplingInterval" in cfg:
+        self.set_monitor_sampling_interval(cfg["monitorSamplingInterval"])
+    if "callbackTimeout" in cfg:
+        self.set_callback_timeout(cfg["callbackTimeout"])
+
+
+_Config.load = _config_load
+_Config.ErrorSamplesMode = ErrorSamplesMode
 config = _Config()
+config._settings = {}
 
 
 def _to_np(v):
@@ -103,15 +173,10 @@ class Dataset:
 
     # ------------------------------------------------------------------ iteration
     def create_dict_iterator(self, num_epochs=-1, output_numpy=False, do_copy=True):
-        import mindspore_b200 as ms
-        for row in self._rows():
-            yield row if output_numpy else {k: ms.Tensor(v) for k, v in row.items()}
+        return DictIterator(self, num_epochs, output_numpy, do_copy)
 
     def create_tuple_iterator(self, columns=None, num_epochs=-1, output_numpy=False, do_copy=True):
-        import mindspore_b200 as ms
-        cols = columns or self._columns
-        for row in self._rows():
-            yield tuple(row[c] if output_numpy else ms.Tensor(row[c]) for c in cols)
+        return TupleIterator(self, columns, num_epochs, output_numpy, do_copy)
 
     def __iter__(self):
         return self.create_tuple_iterator()
@@ -135,6 +200,86 @@ class Dataset:
 
 
 # ---------------------------------------------------------------------------------------------------- sources
+class Iterator:
+    """One pass over a dataset per ``for`` loop (at most ``num_epochs`` passes; -1 = any number).  ``get_offload``
+    style helpers of the reference that concern its C++ runtime are absent."""
+
+    def __init__(self, dataset, num_epochs=-1, output_numpy=False, do_copy=True):
+        self.dataset, self.num_epochs, self.output_numpy, self.do_copy = dataset, num_epochs, output_numpy, do_copy
+        self._epochs_started, self._gen = 0, None
+
+    def _convert(self, row):
+        raise NotImplementedError
+
+    def __iter__(self):
+        if 0 <= self.num_epochs <= self._epochs_started:
+            raise RuntimeError("The iterator was created for %d epoch(s) and all of them have been consumed"
+                               % self.num_epochs)
+        self._epochs_started += 1
+        self._gen = (self._convert(row) for row in self.dataset._rows())
+        return self
+
+    def __next__(self):
+        if self._gen is None:
+            iter(self)
+        return next(self._gen)
+
+    def stop(self):
+        self._gen = iter(())
+
+    release = stop
+
+    def get_output_shapes(self):
+        return self.dataset.output_shapes()
+
+    def get_output_types(self):
+        return self.dataset.output_types()
+
+    def get_col_names(self):
+        return self.dataset.get_col_names()
+
+
+class DictIterator(Iterator):
+    def _convert(self, row):
+        if self.output_numpy:
+            return row
+        import mindspore_b200 as ms
+        return {k: ms.Tensor(v) for k, v in row.items()}
+
+
+class TupleIterator(Iterator):
+    def __init__(self, dataset, columns=None, num_epochs=-1, output_numpy=False, do_copy=True):
+        super().__init__(dataset, num_epochs, output_numpy, do_copy)
+        self.columns = columns
+
+    def _convert(self, row):
+        cols = self.columns or self.dataset._columns
+        if self.output_numpy:
+            return tuple(row[c] for c in cols)
+        import mindspore_b200 as ms
+        return tuple(ms.Tensor(row[c]) for c in cols)
+
+
+class DummyIterator:
+    """Yields the same row forever (used to measure a training loop without its input pipeline)."""
+
+    def __init__(self, dataset, mode, output_numpy=False):
+        first = next(iter(dataset.create_dict_iterator(1, output_numpy) if mode == "dict"
+                          else dataset.create_tuple_iterator(None, 1, output_numpy)))
+        self.row = first
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        return self.row
+
+
+def check_iterator_cleanup():
+    """Whether iterators are being torn down (never, here: there are no background C++ pipelines to stop)."""
+    return False
+
+
 class GeneratorDataset(Dataset):
     """Source over a generator function, an iterable, or a random-access object (``__getitem__`` + ``__len__``)."""
 

@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import numpy as np
 
-__all__ = ["Sampler", "SequentialSampler", "RandomSampler", "DistributedSampler", "SubsetSampler", "SubsetRandomSampler",
+__all__ = ["BuiltinSampler", "IterSampler", "select_sampler", "Sampler", "SequentialSampler", "RandomSampler", "DistributedSampler", "SubsetSampler", "SubsetRandomSampler",
            "WeightedRandomSampler", "PKSampler"]
 
 
@@ -141,3 +141,36 @@ class PKSampler(Sampler):
             out.append(rows[:self.num_val])
         idx = np.stack([r for r in out if len(r) == self.num_val], 1).reshape(-1) if out else np.array([], dtype=np.int64)
         return self._cut(idx)
+
+
+
+BuiltinSampler = Sampler
+
+
+class IterSampler(Sampler):
+    """Wraps any iterable of indices as a sampler."""
+
+    def __init__(self, sampler, num_samples=None):
+        super().__init__(num_samples)
+        self.inner = sampler
+
+    def indices(self):
+        return self._cut(np.array([int(i) for i in self.inner], dtype=np.int64))
+
+
+def select_sampler(num_samples, input_sampler, shuffle, num_shards, shard_id):
+    """The sampler a source dataset uses for the given combination of arguments (the reference's rule:
+    an explicit sampler excludes shuffle / sharding; sharding gives a DistributedSampler; otherwise random or
+    sequential by ``shuffle``, random being the default)."""
+    if input_sampler is not None:
+        if shuffle is not None or num_shards is not None or shard_id is not None:
+            raise RuntimeError("sampler and shuffle / sharding cannot be specified at the same time")
+        if not isinstance(input_sampler, Sampler):
+            return IterSampler(input_sampler, num_samples)
+        return input_sampler
+    if num_shards is not None:
+        return DistributedSampler(num_shards, shard_id, shuffle=shuffle if shuffle is not None else True,
+                                  num_samples=num_samples)
+    if shuffle is None or shuffle:
+        return RandomSampler(num_samples=num_samples)
+    return SequentialSampler(num_samples=num_samples)

@@ -150,3 +150,54 @@ class RandomOrder:
         for k in _np.random.permutation(len(self.t)):
             x = self.t[k](x)
         return x
+
+
+
+class TensorOperation:
+    """Base of transforms: a callable applied to the columns of a row."""
+
+    def __call__(self, *inputs):
+        return self.execute(*inputs) if hasattr(self, "execute") else self._run(*inputs)
+
+
+class PyTensorOperation(TensorOperation):
+    """Base of transforms written in Python."""
+
+
+class CompoundOperation(TensorOperation):
+    """Base of transforms that hold other transforms (``Compose``, ``RandomApply`` ...)."""
+
+    def __init__(self, transforms=None):
+        self.transforms = list(transforms or [])
+
+
+class Plugin(TensorOperation):
+    """Runs ``plugin_func(args)`` from a shared library through ctypes: the symbol takes (input pointer, element
+    count, output pointer) over float32 data and returns the number of output elements."""
+
+    def __init__(self, lib_path, func_name, user_args=None):
+        import ctypes
+        self.lib = ctypes.CDLL(lib_path)
+        self.fn = getattr(self.lib, func_name)
+        self.fn.restype = ctypes.c_longlong
+        self.user_args = user_args
+
+    def __call__(self, x):
+        import ctypes
+
+        import numpy as np
+        a = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.empty_like(a)
+        n = self.fn(a.ctypes.data_as(ctypes.c_void_p), ctypes.c_longlong(a.size), out.ctypes.data_as(ctypes.c_void_p))
+        return out.reshape(-1)[:n].reshape(a.shape) if n == a.size else out.reshape(-1)[:n]
+
+
+def not_random(func):
+    """Marks a transform as deterministic."""
+    func.random = False
+    return func
+
+
+def clean_unused_executors():
+    """Releases executor objects kept for eager transform calls (none are cached here)."""
+    return None

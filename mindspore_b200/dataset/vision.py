@@ -437,3 +437,13 @@ class CutMixBatch:
             x[:, y0:y1, x0:x1] = x[perm][:, y0:y1, x0:x1]
         lam = 1 - (y1 - y0) * (x1 - x0) / (h * w)
         return x, lam * y + (1 - lam) * y[perm]
+
+
+
+def __getattr__(name):
+    # the remaining transforms live in vision_ext (which imports this module)
+    import importlib
+    ext = importlib.import_module(__package__ + ".vision_ext")
+    if name in ext.__all__:
+        return getattr(ext, name)
+    raise AttributeError("module %r has no attribute %r" % (__name__, name))

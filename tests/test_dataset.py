@@ -203,3 +203,39 @@ def test_concat_filter_flat_map_padded_and_bucket_batches(tmp_path):
     back = ds.MindDataset(path, shuffle=False)
     rows = list(back.create_dict_iterator(output_numpy=True, num_epochs=1))
     assert [int(r["x"]) for r in rows] == [0, 1, 2, 3] and float(rows[3]["y"]) == 1.5
+
+
+def test_config_settings_iterators_and_sampler_selection(tmp_path):
+    import json
+    cfg = ds.config
+    cfg.set_enable_shared_mem(False)
+    assert cfg.get_enable_shared_mem() is False and cfg.get_callback_timeout() == 60
+    with pytest.raises(TypeError):
+        cfg.set_numa_enable(1)
+    with pytest.raises(ValueError):
+        cfg.set_monitor_sampling_interval(0)
+    cfg.set_error_samples_mode(cfg.ErrorSamplesMode.SKIP)
+    assert cfg.get_error_samples_mode() == 2
+    (tmp_path / "c.json").write_text(json.dumps({"numParallelWorkers": 3, "seed": 11, "prefetchSize": 5}))
+    old = (cfg.get_num_parallel_workers(), cfg.get_seed(), cfg.get_prefetch_size())
+    cfg.load(str(tmp_path / "c.json"))
+    assert (cfg.get_num_parallel_workers(), cfg.get_seed(), cfg.get_prefetch_size()) == (3, 11, 5)
+    cfg.set_num_parallel_workers(old[0]), cfg.set_seed(old[1]), cfg.set_prefetch_size(old[2])
+    cfg.set_enable_shared_mem(True)
+    data = ds.NumpySlicesDataset({"x": np.arange(4)}, shuffle=False)
+    it = data.create_dict_iterator(num_epochs=2, output_numpy=True)
+    assert isinstance(it, ds.DictIterator) and it.get_col_names() == ["x"]
+    assert [int(r["x"]) for r in it] == [0, 1, 2, 3] and [int(r["x"]) for r in it] == [0, 1, 2, 3]
+    with pytest.raises(RuntimeError):
+        list(it)                                               # a third epoch was not asked for
+    tup = data.create_tuple_iterator(output_numpy=True)
+    assert int(next(tup)[0]) == 0 and isinstance(tup, ds.TupleIterator)
+    dummy = ds.DummyIterator(data, "dict", output_numpy=True)
+    assert int(next(dummy)["x"]) == 0 and int(next(dummy)["x"]) == 0
+    from mindspore_b200.dataset import samplers
+    assert isinstance(samplers.select_sampler(None, None, None, None, None), samplers.RandomSampler)
+    assert isinstance(samplers.select_sampler(None, None, False, None, None), samplers.SequentialSampler)
+    assert isinstance(samplers.select_sampler(None, None, None, 2, 0), samplers.DistributedSampler)
+    assert samplers.select_sampler(2, [3, 1, 2], None, None, None).bind(4).indices().tolist() == [3, 1]
+    with pytest.raises(RuntimeError):
+        samplers.select_sampler(None, samplers.SequentialSampler(), True, None, None)
