@@ -310,3 +310,216 @@ def _fft_namespace():
 fft = _fft_namespace()
 fft2, ifft2, fftn, ifftn, fftshift, ifftshift, ifft = (fft.fft2, fft.ifft2, fft.fftn, fft.ifftn, fft.fftshift,
                                                        fft.ifftshift, fft.ifft)
+
+
+# ---------------------------------------------------------------------------------------------------- remaining names
+def _p(x):
+    t = _t(x)
+    return t.as_subclass(torch.Tensor) if isinstance(t, torch.Tensor) else t
+
+
+def append(arr, values, axis=None):
+    a, v = _p(arr), _p(values)
+    if axis is None:
+        return _w(torch.cat([a.reshape(-1), v.reshape(-1).to(a.dtype)]))
+    return _w(torch.cat([a, v.to(a.dtype)], axis))
+
+
+def array_str(a):
+    return str(_p(a).cpu().numpy())
+
+
+def size(a, axis=None):
+    t = _p(a)
+    return t.numel() if axis is None else t.shape[axis]
+
+
+def diagonal(a, offset=0, axis1=0, axis2=1):
+    return _w(torch.diagonal(_p(a), offset, axis1, axis2))
+
+
+def copy_(a):
+    return _w(_p(a).clone())
+
+
+def intersect1d(ar1, ar2, assume_unique=False, return_indices=False):
+    a, b = _p(ar1).reshape(-1), _p(ar2).reshape(-1)
+    ua = a if assume_unique else torch.unique(a)
+    ub = b if assume_unique else torch.unique(b)
+    common = torch.sort(ua[torch.isin(ua, ub)]).values
+    if not return_indices:
+        return _w(common)
+    first = lambda src: torch.stack([torch.nonzero(src == c)[0, 0] for c in common]) if common.numel() else \
+        torch.zeros(0, dtype=torch.int64)
+    return _w(common), _w(first(a)), _w(first(b))
+
+
+def isin(element, test_elements, invert=False):
+    return _w(torch.isin(_p(element), _p(test_elements), invert=invert))
+
+
+def in1d(ar1, ar2, invert=False):
+    return _w(torch.isin(_p(ar1).reshape(-1), _p(ar2), invert=invert))
+
+
+def setdiff1d(ar1, ar2, assume_unique=False):
+    a = _p(ar1).reshape(-1)
+    a = a if assume_unique else torch.unique(a)
+    return _w(a[~torch.isin(a, _p(ar2))])
+
+
+def isscalar(element):
+    return isinstance(element, (int, float, complex, bool, str, bytes, _np.generic)) or (
+        isinstance(element, torch.Tensor) and element.dim() == 0 and False)
+
+
+def sometrue(a, axis=None, keepdims=False):
+    t = _p(a).bool()
+    return _w(t.any() if axis is None else t.any(axis, keepdims))
+
+
+def matrix_power(a, n):
+    return _w(torch.linalg.matrix_power(_p(a), n))
+
+
+def multi_dot(arrays):
+    return _w(torch.linalg.multi_dot([_p(a) if _p(a).dim() else _p(a).reshape(1) for a in arrays]))
+
+
+def positive(a, dtype=None):
+    return _w(_p(a).to(dtype) if dtype is not None else _p(a).clone())
+
+
+def promote_types(type1, type2):
+    from .common import dtype as _mstype
+    t1 = _mstype.to_torch(type1) if not isinstance(type1, torch.dtype) else type1
+    t2 = _mstype.to_torch(type2) if not isinstance(type2, torch.dtype) else type2
+    return torch.promote_types(t1, t2)
+
+
+def result_type(*arrays_and_dtypes):
+    out = None
+    for a in arrays_and_dtypes:
+        dt = a if isinstance(a, torch.dtype) else _p(a).dtype if isinstance(a, (torch.Tensor, list, tuple, _np.ndarray)) \
+            else torch.as_tensor(a).dtype
+        out = dt if out is None else torch.promote_types(out, dt)
+    return out
+
+
+def divmod_(x1, x2, dtype=None):
+    a, b = _p(x1), _p(x2)
+    q, r = torch.floor_divide(a, b), torch.remainder(a, b)
+    return (_w(q.to(dtype)), _w(r.to(dtype))) if dtype is not None else (_w(q), _w(r))
+
+
+def sum_(a, axis=None, dtype=None, keepdims=False, initial=None):
+    t = _p(a)
+    out = t.sum(dtype=dtype) if axis is None and not keepdims else t.sum(
+        axis if axis is not None else tuple(range(t.dim())), keepdims, dtype=dtype)
+    return _w(out + initial if initial is not None else out)
+
+
+def unwrap(p, discont=3.141592653589793, axis=-1):
+    t = _p(p)
+    d = torch.diff(t, dim=axis)
+    dm = torch.remainder(d + _np.pi, 2 * _np.pi) - _np.pi
+    dm = torch.where((dm == -_np.pi) & (d > 0), torch.full_like(dm, _np.pi), dm)
+    corr = torch.where(d.abs() < discont, torch.zeros_like(d), dm - d)
+    first = t.narrow(axis, 0, 1)
+    return _w(torch.cat([first, t.narrow(axis, 1, t.shape[axis] - 1) + torch.cumsum(corr, axis)], axis))
+
+
+def histogram_bin_edges(a, bins=10, range=None, weights=None):  # noqa: A002
+    return _w(torch.as_tensor(_np.histogram_bin_edges(_p(a).cpu().numpy(), bins, range)))
+
+
+def tri_indices(n, k=0, m=None, upper=True):
+    m = n if m is None else m
+    fn = torch.triu_indices if upper else torch.tril_indices
+    idx = fn(n, m, k)
+    return _w(idx[0]), _w(idx[1])
+
+
+def tril_indices_from(arr, k=0):
+    t = _p(arr)
+    idx = torch.tril_indices(t.shape[-2], t.shape[-1], k)
+    return _w(idx[0]), _w(idx[1])
+
+
+def triu_indices_from(arr, k=0):
+    t = _p(arr)
+    idx = torch.triu_indices(t.shape[-2], t.shape[-1], k)
+    return _w(idx[0]), _w(idx[1])
+
+
+def roll_along_axis(a, shift, axis):
+    return _w(torch.roll(_p(a), shift, axis))
+
+
+def convert_neg_indices(indices, ndim):
+    t = _p(indices)
+    return _w(torch.where(t < 0, t + ndim, t))
+
+
+class NdGrid:
+    """``mgrid`` / ``ogrid``: ``grid[0:3, 0:2]`` -> dense (``sparse=False``) or open coordinate arrays; a complex
+    step ``5j`` means that many points including the end."""
+
+    def __init__(self, sparse=False):
+        self.sparse = sparse
+
+    def __getitem__(self, keys):
+        keys = keys if isinstance(keys, tuple) else (keys,)
+        axes = []
+        for k in keys:
+            start = 0 if k.start is None else k.start
+            step = 1 if k.step is None else k.step
+            if isinstance(step, complex):
+                axes.append(torch.linspace(float(start), float(k.stop), int(abs(step))))
+            else:
+                axes.append(torch.arange(start, k.stop, step))
+        if len(axes) == 1:
+            return _w(axes[0])
+        if self.sparse:
+            return tuple(_w(a.reshape([-1 if i == j else 1 for j in builtins.range(len(axes))]))
+                         for i, a in enumerate(axes))
+        return _w(torch.stack(torch.meshgrid(*axes, indexing="ij")))
+
+
+class MGridClass(NdGrid):
+    def __init__(self):
+        super().__init__(False)
+
+
+class OGridClass(NdGrid):
+    def __init__(self):
+        super().__init__(True)
+
+
+mgrid, ogrid = MGridClass(), OGridClass()
+asarray_const = asfarray_const = lambda a, dtype=None: _w(_t(a, dtype))  # noqa: E731
+empty_compile = lambda dtype, shape: _w(torch.empty(tuple(shape), dtype=dtype))  # noqa: E731
+
+
+class UniqueNet:
+    """Callable form of ``unique`` (a Cell in the reference, kept for import compatibility)."""
+
+    def __call__(self, x):
+        out, inv = torch.unique(_p(x), return_inverse=True)
+        return _w(out), _w(inv)
+
+
+def comput_avg(a, axis=None, weights=None):
+    return average(a, axis, weights) if "average" in globals() else _w(_p(a).float().mean())
+
+
+def compute_weights_for_mean(x, x_avg, axis):
+    t = _p(x)
+    n = t.numel() if axis is None else t.shape[axis]
+    return _w(torch.full_like(_p(x_avg), 1.0 / n))
+
+
+def check_gradient_arguments(f, axis, edge_order):
+    if edge_order != 1:
+        raise NotImplementedError("edge_order != 1 not implemented")
+    return axis if axis is not None else tuple(builtins.range(_p(f).dim()))

@@ -156,3 +156,34 @@ def test_remaining_nn_names():
             self.lr = learning_rate
 
     assert Opt([1, 2], learning_rate=0.5).init_args == {"learning_rate": 0.5}
+
+
+def test_numpy_and_scipy_fft_names():
+    import scipy.fft as sfft
+
+    import mindspore_b200.numpy as mnp
+    from mindspore_b200.scipy import fft as F
+    x = np.random.RandomState(0).randn(3, 8).astype(np.float32)
+    for kind in (1, 2, 3, 4):
+        for norm in (None, "ortho"):
+            if kind == 1 and norm:
+                continue
+            np.testing.assert_allclose(F.dct(ms.Tensor(x), kind, norm=norm).numpy(), sfft.dct(x, kind, norm=norm),
+                                       rtol=1e-4, atol=1e-4)
+            np.testing.assert_allclose(F.idct(ms.Tensor(x), kind, norm=norm).numpy(), sfft.idct(x, kind, norm=norm),
+                                       rtol=1e-4, atol=1e-4)
+    assert mnp.append(ms.Tensor([1, 2]), [3]).tolist() == [1, 2, 3]
+    assert mnp.intersect1d([1, 3, 4, 3], [3, 1, 1]).tolist() == [1, 3]
+    assert mnp.setdiff1d([1, 2, 3, 2, 4], [3, 4, 5]).tolist() == [1, 2]
+    assert mnp.isin([1, 2], [2]).tolist() == [False, True] and mnp.in1d([[1, 2]], [1]).tolist() == [True, False]
+    assert mnp.mgrid[0:3, 0:2].shape == (2, 3, 2) and [a.shape for a in mnp.ogrid[0:3, 0:2]] == [(3, 1), (1, 2)]
+    assert mnp.mgrid[0:1:5j].tolist() == [0, 0.25, 0.5, 0.75, 1.0]
+    p = np.array([0, 0.5, 6.5, 7.0], np.float32)
+    np.testing.assert_allclose(mnp.unwrap(ms.Tensor(p)).numpy(), np.unwrap(p), rtol=1e-5)
+    assert mnp.promote_types(ms.int32, ms.float32) == torch.float32
+    q, r = mnp.divmod_(ms.Tensor([7, -7]), 2)
+    assert q.tolist() == [3, -4] and r.tolist() == [1, 1]
+    assert mnp.fft.fft(ms.Tensor([1., 0., 0., 0.])).shape == (4,) and mnp.size(ms.Tensor([[1, 2]]), 1) == 2
+    assert mnp.matrix_power(ms.Tensor([[1., 1.], [0., 1.]]), 3).tolist() == [[1, 3], [0, 1]]
+    rows, cols = mnp.tril_indices_from(ms.Tensor(np.zeros((3, 3))))
+    assert rows.tolist() == [0, 1, 1, 2, 2, 2] and cols.tolist() == [0, 0, 1, 0, 1, 2]
