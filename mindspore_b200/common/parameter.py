@@ -126,6 +126,32 @@ class Parameter(Tensor):
         self._unique = v
 
     @property
+    def cache_shape(self):
+        """Shape of the cache-enabled (embedding-cache) form of this parameter, if any."""
+        return self.__dict__.get("_cache_shape", ())
+
+    @cache_shape.setter
+    def cache_shape(self, value):
+        if not isinstance(value, (tuple, list)):
+            raise TypeError("'cache_shape' must be a tuple or list, but got %s" % type(value))
+        self.__dict__["_cache_shape"] = tuple(value)
+
+    @property
+    def key(self):
+        """Unique key of the parameter (process-wide)."""
+        return self.__dict__.setdefault("_key", id(self))
+
+    @key.setter
+    def key(self, value):
+        self.__dict__["_key"] = int(value)
+
+    def set_param_fl(self, push_to_server=False, pull_from_server=False, requires_aggr=True):
+        """Federated-learning flags: whether the value is pushed to / pulled from a server and aggregated."""
+        self.__dict__["push_weight_to_server"] = bool(push_to_server)
+        self.__dict__["pull_weight_from_server"] = bool(pull_from_server)
+        self.__dict__["requires_aggr"] = bool(requires_aggr)
+
+    @property
     def sliced(self):
         return self._sliced
 

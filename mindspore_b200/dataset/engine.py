@@ -130,6 +130,77 @@ class Dataset:
     def _rows(self):
         raise NotImplementedError
 
+    # ------------------------------------------------------------------ introspection / sync
+    def get_class_indexing(self):
+        """Class name -> index mapping of the source dataset at the root of this pipeline (if it has one)."""
+        node = self
+        while getattr(node, "parent", None) is not None:
+            node = node.parent
+        fn = type(node).__dict__.get("get_class_indexing")
+        if fn is None or node is self:
+            raise NotImplementedError("%s has no class indexing" % type(node).__name__)
+        return fn(node)
+
+    def to_json(self, filename=""):
+        from .sources_ext import serialize
+        return serialize(self, filename)
+
+    def is_shuffled(self):
+        node = self
+        while node is not None:
+            if type(node).__name__ == "_Shuffle" or getattr(node, "_shuffle", False):
+                return True
+            node = getattr(node, "parent", None)
+        return False
+
+    def is_sharded(self):
+        node = self
+        while node is not None:
+            if type(node).__name__ == "_Shard" or (getattr(node, "_num_shards", None) or 1) > 1:
+                return True
+            node = getattr(node, "parent", None)
+        return False
+
+    def set_init_step(self, init_step):
+        """Rows to skip at the start of the first epoch (resuming in the middle of an epoch)."""
+        self._init_step = int(init_step)
+
+    def get_init_step(self):
+        return getattr(self, "_init_step", 0)
+
+    def sync_wait(self, condition_name, num_batch=1, callback=None):
+        """Marks a synchronisation point: iteration blocks after every ``num_batch`` rows until
+        ``sync_update(condition_name)`` is called (typically from the training loop)."""
+        return _SyncWait(self, condition_name, num_batch, callback)
+
+    def sync_update(self, condition_name, num_batch=None, data=None):
+        node, found = self, False
+        while node is not None:
+            if isinstance(node, _SyncWait) and node.condition_name == condition_name:
+                node.release(num_batch, data)
+                found = True
+            node = getattr(node, "parent", None)
+        if not found:
+            raise RuntimeError("sync_update: condition %r is not defined in this pipeline" % (condition_name,))
+
+    def get_sync_notifiers(self):
+        out, node = {}, self
+        while node is not None:
+            if isinstance(node, _SyncWait):
+                out[node.condition_name] = node.release
+            node = getattr(node, "parent", None)
+        return out
+
+    def is_sync(self):
+        return bool(self.get_sync_notifiers())
+
+    def disable_sync(self):
+        node = self
+        while node is not None:
+            if isinstance(node, _SyncWait):
+                node.enabled = False
+            node = getattr(node, "parent", None)
+
     def get_dataset_size(self):
         return self.parent.get_dataset_size()
 
@@ -200,6 +271,30 @@ class Dataset:
 
 
 # ---------------------------------------------------------------------------------------------------- sources
+class _SyncWait(Dataset):
+    def __init__(self, parent, condition_name, num_batch, callback):
+        super().__init__(parent, parent.get_col_names())
+        import threading
+        self.condition_name, self.num_batch, self.callback, self.enabled = condition_name, num_batch, callback, True
+        self._sem = threading.Semaphore(num_batch)
+
+    def release(self, num_batch=None, data=None):
+        if self.callback is not None and data is not None:
+            self.callback(data)
+        for _ in range(num_batch or self.num_batch):
+            self._sem.release()
+
+    def get_dataset_size(self):
+        return self.parent.get_dataset_size()
+
+    def _rows(self):
+        for row in self.parent._rows():
+            if self.enabled and not self._sem.acquire(timeout=config.get_callback_timeout()):
+                raise RuntimeError("sync_wait(%r): no sync_update within %s s" % (self.condition_name,
+                                                                               config.get_callback_timeout()))
+            yield row
+
+
 class Iterator:
     """One pass over a dataset per ``for`` loop (at most ``num_epochs`` passes; -1 = any number).  ``get_offload``
     style helpers of the reference that concern its C++ runtime are absent."""

@@ -490,6 +490,63 @@ class Cell:
         return getattr(self, "_param_prefix", "")
 
     @property
+    def create_time(self):
+        """Nanosecond timestamp taken when this property (or the compile cache key) first needed it."""
+        t = self.__dict__.get("_create_time")
+        if t is None:
+            import time as _time
+            t = _time.time_ns()
+            object.__setattr__(self, "_create_time", t)
+        return t
+
+    @property
+    def pipeline_segment(self):
+        return self.__dict__.get("_pipeline_segment", -1)
+
+    @pipeline_segment.setter
+    def pipeline_segment(self, value):
+        if not isinstance(value, int) or isinstance(value, bool):
+            raise TypeError("'pipeline_segment' must be int type, but got type : %s" % type(value))
+        if value < 0:
+            raise ValueError("'pipeline_segment' can not be less than 0, but got %d" % value)
+        object.__setattr__(self, "_pipeline_segment", value)
+
+    @property
+    def parallel_parameter_merge_net_dict(self):
+        return self.__dict__.setdefault("_parallel_parameter_merge_net_dict", {})
+
+    @parallel_parameter_merge_net_dict.setter
+    def parallel_parameter_merge_net_dict(self, value):
+        if not isinstance(value, dict):
+            raise TypeError("'parallel_parameter_merge_net_dict' must be dict type, but got %s" % type(value))
+        object.__setattr__(self, "_parallel_parameter_merge_net_dict", value)
+
+    @property
+    def jit_config_dict(self):
+        return self.__dict__.get("_jit_config_dict", {})
+
+    def set_parallel_input_with_inputs(self, *inputs):
+        from ..utils.log import logger
+        logger.warning("'set_parallel_input_with_inputs' function is deprecated.")
+
+    def auto_parallel_compile_and_run(self):
+        from ..utils.log import logger
+        logger.warning("'auto_parallel_compile_and_run' function is deprecated.")
+        return False
+
+    def check_names_and_refresh_name(self):
+        """Parameter names must be unique within a network; raises otherwise."""
+        names = [p.name for _, p in self.parameters_and_names()]
+        dup = sorted({n for n in names if names.count(n) > 1})
+        if dup:
+            raise ValueError("The value of parameter names %s duplicate; parameter names must be unique" % dup)
+
+    def set_param_fl(self, push_to_server=False, pull_from_server=False, requires_aggr=True):
+        """Federated-learning flags on every parameter of the cell."""
+        for p in self.get_parameters():
+            p.set_param_fl(push_to_server, pull_from_server, requires_aggr)
+
+    @property
     def bprop_debug(self):
         return getattr(self, "_bprop_debug", False)
 

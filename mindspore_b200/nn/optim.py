@@ -224,6 +224,31 @@ class Optimizer(Cell):
             return float(spec)
         raise TypeError("learning_rate must be float, Tensor, Iterable or LearningRateSchedule, got %s" % type(spec))
 
+    def get_lr_parameter(self, param):
+        """The learning rate (current value) that applies to ``param`` (or to each of a list of parameters)."""
+        def one(p):
+            if not self.is_group_lr:
+                return self.get_lr()
+            for i, q in enumerate(self._parameters):
+                if q is p or q.name == getattr(p, "name", None):
+                    return self.get_lr()[i]
+            raise ValueError("The parameter %s is not in the optimizer" % getattr(p, "name", p))
+        if isinstance(param, (list, tuple)):
+            return [one(p) for p in param]
+        return one(param)
+
+    @property
+    def target(self):
+        """Where the update runs: 'GPU' for CUDA parameters, else 'CPU'."""
+        ps = self._parameters
+        return self.__dict__.get("_target") or ("GPU" if ps and ps[0].is_cuda else "CPU")
+
+    @target.setter
+    def target(self, value):
+        if value not in ("CPU", "GPU", "Ascend"):
+            raise ValueError("The value must be 'CPU', 'Ascend' or 'GPU', but got value %r" % (value,))
+        object.__setattr__(self, "_target", value)
+
     def get_lr(self):
         step = self._step_host
         if self.is_group_lr:

@@ -90,6 +90,19 @@ class Profiler:
                  "share": round(v[1] / total, 4)} for k, v in agg.items()]
         return sorted(rows, key=lambda r: -r["total_us"])
 
+    @classmethod
+    def offline_analyse(cls, path, pretty=False, step_list=None, data_simplification=True):
+        """Re-reads what a finished run wrote under ``path`` (``kernel_time_<rank>.csv``) and returns the kernel
+        rows per rank: nothing is re-collected."""
+        out = {}
+        for name in sorted(os.listdir(path)):
+            if name.startswith("kernel_time_") and name.endswith(".csv"):
+                with open(os.path.join(path, name), newline="") as f:
+                    out[int(name[len("kernel_time_"):-4])] = list(csv.DictReader(f))
+        if not out:
+            raise RuntimeError("offline_analyse: no kernel_time_<rank>.csv under %s" % path)
+        return out
+
     def analyse(self, offline_path=None, pretty=False, step_list=None, mode="sync"):
         os.makedirs(self.output_path, exist_ok=True)
         kernels = self.op_analyse()

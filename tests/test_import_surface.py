@@ -187,3 +187,49 @@ def test_numpy_and_scipy_fft_names():
     assert mnp.matrix_power(ms.Tensor([[1., 1.], [0., 1.]]), 3).tolist() == [[1, 3], [0, 1]]
     rows, cols = mnp.tril_indices_from(ms.Tensor(np.zeros((3, 3))))
     assert rows.tolist() == [0, 1, 1, 2, 2, 2] and cols.tolist() == [0, 0, 1, 0, 1, 2]
+
+
+def test_small_methods_of_core_classes(tmp_path):
+    import threading
+
+    import mindspore_b200.dataset as ds
+    net = _Mlp()
+    assert net.create_time == net.create_time and net.pipeline_segment == -1
+    net.pipeline_segment = 2
+    assert net.pipeline_segment == 2
+    with pytest.raises(ValueError):
+        net.pipeline_segment = -3
+    net.check_names_and_refresh_name()
+    net.set_param_fl(push_to_server=True)
+    assert net.fc1.weight.push_weight_to_server is True and net.fc1.weight.requires_aggr is True
+    p = net.fc1.weight
+    assert p.key == p.key and p.cache_shape == ()
+    p.cache_shape = [4, 2]
+    assert p.cache_shape == (4, 2)
+    opt = nn.SGD(net.trainable_params(), learning_rate=0.25)
+    assert float(opt.get_lr_parameter(p)) == 0.25 and opt.target == "CPU"
+    with pytest.raises(ValueError):
+        opt.target = "TPU"
+    data = ds.NumpySlicesDataset({"x": np.arange(6)}, shuffle=False)
+    assert not data.is_shuffled() and data.shuffle(4).is_shuffled() and data.shard(2, 0).is_sharded()
+    assert data.batch(2).to_json()["op_type"] == "Batch"
+    data.set_init_step(3)
+    assert data.get_init_step() == 3
+    gated = data.sync_wait("go", num_batch=2)
+    assert gated.is_sync() and list(gated.get_sync_notifiers()) == ["go"]
+    seen = []
+    t = threading.Thread(target=lambda: seen.extend(int(r["x"]) for r in gated.create_dict_iterator(output_numpy=True)))
+    ds.config.set_callback_timeout(5)
+    t.start()
+    for _ in range(2):
+        gated.sync_update("go")
+    t.join(10)
+    ds.config.set_callback_timeout(60)
+    assert seen == [0, 1, 2, 3, 4, 5]
+    with pytest.raises(RuntimeError):
+        data.sync_update("nope")
+    out = tmp_path / "prof"
+    out.mkdir()
+    (out / "kernel_time_0.csv").write_text("name,calls,total_us,mean_us,share\nk,2,10.0,5.0,1.0\n")
+    rows = ms.Profiler.offline_analyse(str(out))
+    assert rows[0][0]["name"] == "k" and rows[0][0]["calls"] == "2"
