@@ -170,32 +170,51 @@ def _read_tensor(tp):
 
 
 # ---------------------------------------------------------------------------------------------------- attributes
-def _fill_attr(ap, v):
-    """Python value -> AttributeProto (type tag + payload)."""
+def _fill_attr(ap, v, in_sequence=False):
+    """Python value -> AttributeProto (type tag + payload).  A scalar that is an element of a tuple / list goes
+    into the repeated field of its kind (``ints`` / ``floats`` / ``doubles`` / ``strings``, one entry), a top-level
+    scalar into ``i`` / ``f`` / ``d`` / ``s``: the two forms the reference's exporter writes
+    (ccsrc/transform/express_ir/mindir_exporter.cc SetScalarToAttributeProto_irs / _ir)."""
     if v is None:
         ap.type = A_NONE
     elif isinstance(v, (bool, np.bool_)):
-        ap.type, ap.i = A_BOOL, int(bool(v))
+        ap.type = A_BOOL
+        if in_sequence:
+            ap.ints.append(int(bool(v)))
+        else:
+            ap.i = int(bool(v))
     elif isinstance(v, (int, np.integer)):
-        ap.type, ap.i = A_INT64, int(v)
+        ap.type = A_INT64
+        if in_sequence:
+            ap.ints.append(int(v))
+        else:
+            ap.i = int(v)
     elif isinstance(v, (float, np.floating)):
         f32 = float(np.float32(v))
-        if f32 == float(v) or v != v:
-            ap.type, ap.f = A_FLOAT, float(v)
+        single = f32 == float(v) or v != v
+        ap.type = A_FLOAT if single else A_DOUBLE
+        if in_sequence:
+            (ap.floats if single else ap.doubles).append(float(v))
+        elif single:
+            ap.f = float(v)
         else:
-            ap.type, ap.d = A_DOUBLE, float(v)
+            ap.d = float(v)
     elif isinstance(v, str):
-        ap.type, ap.s = A_STRING, v.encode()
+        ap.type = A_STRING
+        if in_sequence:
+            ap.strings.append(v.encode())
+        else:
+            ap.s = v.encode()
     elif isinstance(v, (tuple, list, torch.Size)):
         ap.type = A_LIST if isinstance(v, list) else A_TUPLE
         for item in v:
-            _fill_attr(ap.values.add(), item)
+            _fill_attr(ap.values.add(), item, True)
     elif isinstance(v, dict):
         ap.type = A_DICT
         for k, item in v.items():
             sub = ap.values.add()
             sub.name = str(k)
-            _fill_attr(sub, item)
+            _fill_attr(sub, item, True)
     elif isinstance(v, torch.dtype):
         ap.type = A_TENSORS                       # a type value: one tensor entry that carries only a data type
         tp = ap.tensors.add()
@@ -217,16 +236,17 @@ def _read_attr(ap):
     t = ap.type
     if t == A_NONE:
         return None
+    # scalars: the single-value field, or (elements of sequences) one entry of the repeated field of their kind
     if t == A_BOOL:
-        return bool(ap.i)
+        return bool(ap.ints[0]) if len(ap.ints) and not ap.HasField("i") else bool(ap.i)
     if t in _INT_ATTR:
-        return int(ap.i)
+        return int(ap.ints[0]) if len(ap.ints) and not ap.HasField("i") else int(ap.i)
     if t == A_FLOAT:
-        return float(ap.f)
+        return float(ap.floats[0]) if len(ap.floats) and not ap.HasField("f") else float(ap.f)
     if t == A_DOUBLE:
-        return float(ap.d)
+        return float(ap.doubles[0]) if len(ap.doubles) and not ap.HasField("d") else float(ap.d)
     if t == A_STRING:
-        return ap.s.decode()
+        return (ap.strings[0] if len(ap.strings) and not ap.HasField("s") else ap.s).decode()
     if t in (A_TUPLE, A_LIST):
         vals = [_read_attr(x) for x in ap.values]
         return vals if t == A_LIST else tuple(vals)

@@ -289,8 +289,7 @@ def _write(path, recs, enc_key, enc_mode, crc_check):
                 for off in range(0, max(len(raw), 1), step):
                     block = encode_value(name, dims, tname, raw[off:off + step])
                     if enc is not None:
-                        block = enc(block)
-                        block = len(block).to_bytes(8, "little") + block
+                        block = enc(block)                # self-delimiting: blocks are simply concatenated
                     if crc_check:
                         crc = binascii.crc32(block, crc)
                     f.write(block)
@@ -350,13 +349,16 @@ def _read_file(path, dec_key, dec_mode, crc_check):
         logger.warning("crc_check is on but %s carries no crc trailer", path)
     if dec_key is not None:
         from . import crypto
-        out, pos = bytearray(), 0
-        while pos < len(data):
-            ln = int.from_bytes(data[pos:pos + 8], "little")
-            pos += 8
-            out += crypto.decrypt(bytes(data[pos:pos + ln]), dec_key, dec_mode)
-            pos += ln
-        data = bytes(out)
+        if crypto.is_cipher(data):
+            data = crypto.decrypt(data, dec_key, dec_mode)
+        else:                                             # files of earlier versions: u64 length + blob, repeated
+            out, pos = bytearray(), 0
+            while pos < len(data):
+                ln = int.from_bytes(data[pos:pos + 8], "little")
+                pos += 8
+                out += crypto.decrypt(bytes(data[pos:pos + ln]), dec_key, dec_mode)
+                pos += ln
+            data = bytes(out)
     return data
 
 

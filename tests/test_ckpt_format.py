@@ -207,3 +207,37 @@ def test_native_scanner_matches_python_decoder(tmp_path):
     b = [(t, d, n, bytes(c)) for t, d, n, c in S.decode_stream(raw, native=False)]
     assert a == b and [r[0] for r in a] == ["a", "s", "note"]
     assert S._decode_native(raw) is not None, "the host library's scanner was not used"
+
+
+def test_encrypted_container_layout_and_legacy_blobs(tmp_path):
+    """magic | tag (GCM) | block size | iv length | iv | cipher length | cipher, blocks concatenated."""
+    import struct
+
+    from mindspore_b200.train import crypto
+    key = b"0123456789ABCDEF"
+    blob = crypto.encrypt(b"x" * 100, key, "AES-GCM")
+    magic, = struct.unpack_from("<I", blob, 0)
+    block, iv_len = struct.unpack_from("<ii", blob, 20)
+    cipher_len, = struct.unpack_from("<i", blob, 28 + 16)
+    assert magic == 0x7F3A5ED8 and iv_len == 16 and cipher_len == 100 and block == 4 + 16 + 4 + 100
+    assert len(blob) == 4 + 16 + 4 + block
+    cbc = crypto.encrypt(b"x" * 100, key, "AES-CBC")
+    assert struct.unpack_from("<I", cbc, 0)[0] == 0x7F3A5ED9 and struct.unpack_from("<i", cbc, 4 + 8 + 16)[0] == 112
+    assert crypto.decrypt(blob + crypto.encrypt(b"y", key), key) == b"x" * 100 + b"y"
+    with pytest.raises(ValueError):
+        crypto.decrypt(blob, key, "AES-CBC")                       # wrong mode for this magic
+    with pytest.raises(ValueError):
+        crypto.decrypt(blob, b"F" * 16)
+    with pytest.raises(ValueError):
+        crypto.decrypt(blob[:-3], key)
+    # a blob of the earlier layout (12-byte nonce | ciphertext | tag, no magic) is still read
+    from cryptography.hazmat.primitives.ciphers.aead import AESGCM
+    nonce = b"\x01" * 12
+    assert crypto.decrypt(nonce + AESGCM(key).encrypt(nonce, b"old", None), key) == b"old"
+    net = ms.nn.Dense(3, 2)
+    path = str(tmp_path / "enc.ckpt")
+    ms.save_checkpoint(net, path, enc_key=key, enc_mode="AES-GCM")
+    raw = open(path, "rb").read()
+    assert struct.unpack_from("<I", raw, 0)[0] == 0x7F3A5ED8
+    back = ms.load_checkpoint(path, dec_key=key, dec_mode="AES-GCM")
+    assert {"bias", "weight"} <= set(back)

@@ -80,7 +80,7 @@ def test_export_uses_the_reference_protobuf_layout(tmp_path):
     conv = next(p for p in model.primitives if p.op_type == "Conv2D")
     attrs = {a.name: a for a in conv.attribute}
     assert attrs["out_channel"].type == MP.A_INT64 and attrs["out_channel"].i == 6
-    assert attrs["kernel_size"].type == MP.A_TUPLE and [v.i for v in attrs["kernel_size"].values] == [5, 5]
+    assert attrs["kernel_size"].type == MP.A_TUPLE and [list(v.ints) for v in attrs["kernel_size"].values] == [[5], [5]]
     assert attrs["pad_mode"].type == MP.A_STRING and attrs["pad_mode"].s == b"valid"
     assert all(n.op_type.startswith("REF::") or n.op_type == "Constant" for n in model.graph.node)
     w = next(t for t in model.graph.parameter if t.name == "conv1.weight")
@@ -179,3 +179,51 @@ def test_attribute_values_round_trip():
     a = A()
     MP._fill_attr(a, t)
     assert torch.equal(MP._read_attr(a), t)
+
+
+# Two MindIR files as the reference's exporter wrote them (an Add of two inputs, a ReLU), base64: reading them shows
+# that the protobuf layout, the primitive references and the attribute encoding agree with the reference's writer.
+_REFERENCE_ADD_MINDIR = (
+    "CgUwLjEuMBIJTWluZFNwb3JlKgUxLjEuMDqiAwqRAgoaNl80X2NvbnN0cnVjdF93cmFwcGVyLjQ6eF8KGjZfNF9jb25zdHJ1Y3Rf"
+    "d3JhcHBlci40OnlfEhs2XzRfY29uc3RydWN0X3dyYXBwZXIuNDo2OjIaGzZfNF9jb25zdHJ1Y3Rfd3JhcHBlci40OjU6MSIDQWRk"
+    "Kh9iDggCCAIQAToGc2hhcGUxeg1zaGFwZTpzaGFwZTEsKjQKC2lucHV0X25hbWVzWgF4WgF5ehxzY2FsYXI6TGlzdFt2YWx1ZTEs"
+    "dmFsdWUyLF0sgAEIKjAKDG91dHB1dF9uYW1lc1oGb3V0cHV0ehVzY2FsYXI6TGlzdFt2YWx1ZTEsXSyAAQg6D0RlZmF1bHQvQWRk"
+    "LW9wNRIXNl80X2NvbnN0cnVjdF93cmFwcGVyLjQqJAoaNl80X2NvbnN0cnVjdF93cmFwcGVyLjQ6eF8SBggCCAIQASokCho2XzRf"
+    "Y29uc3RydWN0X3dyYXBwZXIuNDp5XxIGCAIIAhABMiUKGzZfNF9jb25zdHJ1Y3Rfd3JhcHBlci40OjY6MhIGCAIIAhABOgA=")
+_REFERENCE_RELU_MINDIR = (
+    "CgUwLjEuMBIJTWluZFNwb3JlKggxLjUuMHJjMTqYAwqSAgofMzk0XzM5MV9jb25zdHJ1Y3Rfd3JhcHBlci4xMDI6eBIjMzk0XzM5"
+    "MV9jb25zdHJ1Y3Rfd3JhcHBlci4xMDI6MTAzOjEaIzM5NF8zOTFfY29uc3RydWN0X3dyYXBwZXIuMTAyOjEwMzoxIgRSZUxVKiNi"
+    "EggBCAEIAggCEAE6BnNoYXBlMXoNc2hhcGU6c2hhcGUxLCoqCgtpbnB1dF9uYW1lc1oBeHoVc2NhbGFyOkxpc3RbdmFsdWUxLF0s"
+    "gAEIKjAKDG91dHB1dF9uYW1lc1oGb3V0cHV0ehVzY2FsYXI6TGlzdFt2YWx1ZTEsXSyAAQg6HERlZmF1bHQvcmVsdS1SZUxVL1Jl"
+    "TFUtb3AxODgSHTM5NF8zOTFfY29uc3RydWN0X3dyYXBwZXIuMTAyKi0KHzM5NF8zOTFfY29uc3RydWN0X3dyYXBwZXIuMTAyOngS"
+    "CggBCAEIAggCEAEyMQojMzk0XzM5MV9jb25zdHJ1Y3Rfd3JhcHBlci4xMDI6MTAzOjESCggBCAEIAggCEAE6AA==")
+
+
+def test_files_written_by_the_reference_exporter_load_and_run(tmp_path):
+    import base64
+    for name, blob in (("add", _REFERENCE_ADD_MINDIR), ("relu", _REFERENCE_RELU_MINDIR)):
+        (tmp_path / (name + ".mindir")).write_bytes(base64.b64decode(blob))
+    add = nn.GraphCell(ms.load(str(tmp_path / "add.mindir")))
+    np.testing.assert_allclose(add(ms.Tensor([1.0, -2.0]), ms.Tensor([2.0, 0.5])).numpy(), [3.0, -1.5])
+    relu = nn.GraphCell(ms.load(str(tmp_path / "relu.mindir")))
+    x = np.array([[-1.0, 2.0], [0.5, -3.0]], np.float32)
+    np.testing.assert_allclose(relu(ms.Tensor(x)).numpy(), np.maximum(x, 0))
+
+
+def test_tuple_attribute_elements_use_the_repeated_fields():
+    """Scalars inside a tuple attribute are written as one entry of ints / floats / strings (how the reference's
+    exporter stores e.g. kernel_size), top-level scalars as i / f / s; both forms are read."""
+    from mindspore_b200.graph import mindir_proto as MP
+    ap = MP.messages()["AttributeProto"]()
+    MP._fill_attr(ap, (5, 2.5, "same", True))
+    assert [list(v.ints) for v in ap.values] == [[5], [], [], [1]] and list(ap.values[1].floats) == [2.5]
+    assert list(ap.values[2].strings) == [b"same"] and not ap.values[0].HasField("i")
+    assert MP._read_attr(ap) == (5, 2.5, "same", True)
+    top = MP.messages()["AttributeProto"]()
+    MP._fill_attr(top, 16)
+    assert top.i == 16 and not list(top.ints) and MP._read_attr(top) == 16
+    legacy = MP.messages()["AttributeProto"]()
+    legacy.type = MP.A_TUPLE
+    v = legacy.values.add()
+    v.type, v.i = MP.A_INT64, 7                              # the single-value field inside a tuple is accepted too
+    assert MP._read_attr(legacy) == (7,)
