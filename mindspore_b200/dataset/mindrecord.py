@@ -1,4 +1,9 @@
-"""Record files: a schema'd, indexed, optionally sharded and encrypted container of rows (the role of MindRecord).
+"""Record files: a schema'd, indexed, optionally sharded and encrypted container of rows (MindRecord).
+
+Files are written in, and read from, the reference's MindRecord layout (``mindrecord_format.py``: JSON header, raw
+and blob pages, msgpack rows, SQLite index beside each shard), so datasets written by the reference open here.
+With an encryption key or a hash mode set, the writer uses the private container described next instead (the
+reference encrypts record files with a tool of its own, which is not reproduced); the reader takes both.
 
 Layout of one shard ``<name>`` (``<name>0 .. <name>N-1`` with ``shard_num = N``): magic ``MSB200RECORD\\0``, u32 header
 length, JSON header {schema, row offsets, row count, index fields, per-row index values, shard list}, then the rows;
@@ -171,13 +176,48 @@ class FileWriter:
                 raise RuntimeError("%s already exists (pass overwrite=True)" % f)
         self.schema, self.desc, self.index_fields = None, None, []
         self.rows = [[] for _ in range(shard_num)]
+        self.row_dicts = [[] for _ in range(shard_num)]
         self.index_values = [[] for _ in range(shard_num)]
         self._count = 0
         self._committed = False
+        self._header_size, self._page_size = None, None
+
+    def set_header_size(self, header_size):
+        """Bytes reserved for the header (16 KB .. 128 MB; default 16 MB)."""
+        if not isinstance(header_size, int) or not (1 << 14) <= header_size <= (1 << 27):
+            raise ValueError("header_size must be an int in [16 KB, 128 MB], but got %r" % (header_size,))
+        self._header_size = header_size
+        return SUCCESS
+
+    def set_page_size(self, page_size):
+        """Bytes per page (32 KB .. 256 MB; default 32 MB): the largest row must fit one page."""
+        if not isinstance(page_size, int) or not (1 << 15) <= page_size <= (1 << 28):
+            raise ValueError("page_size must be an int in [32 KB, 256 MB], but got %r" % (page_size,))
+        self._page_size = page_size
+        return SUCCESS
 
     @classmethod
     def open_for_append(cls, file_name):
         """Re-opens a committed file (any shard of it) so that more rows can be added; ``commit`` rewrites it."""
+        from . import mindrecord_format as F
+        if F.looks_like_mindrecord(file_name):
+            paths = F.shard_paths(file_name)
+            first = F.ShardFile(paths[0])
+            w = cls.__new__(cls)
+            w.file_name, w.shard_num, w.files = file_name, len(paths), paths
+            w.schema = first.schema
+            w.desc = first.header["schema"][0].get("desc")
+            w.index_fields = [f["index_field"] for f in first.header.get("index_fields", [])]
+            w.rows, w.row_dicts, w.index_values, w._count, w._committed = [], [], [], 0, False
+            w._header_size, w._page_size = first.header["header_size"], first.header["page_size"]
+            for path in paths:
+                sf = F.ShardFile(path)
+                dicts = [sf.read(i) for i in range(len(sf))]
+                w.row_dicts.append(dicts)
+                w.rows.append([b""] * len(dicts))
+                w.index_values.append([[_index_value(d, f) for f in w.index_fields] for d in dicts])
+                w._count += len(dicts)
+            return w
         head, _ = _unseal(file_name)
         shards = head.get("shards") or [os.path.basename(file_name)]
         folder = os.path.dirname(os.path.abspath(file_name))
@@ -185,10 +225,12 @@ class FileWriter:
         w.file_name, w.shard_num = file_name, len(shards)
         w.files = [os.path.join(folder, s) for s in shards]
         w.schema, w.desc, w.index_fields = head["schema"], head.get("desc"), head.get("index_fields", [])
-        w.rows, w.index_values, w._count, w._committed = [], [], 0, False
+        w.rows, w.row_dicts, w.index_values, w._count, w._committed = [], [], [], 0, False
+        w._header_size, w._page_size = None, None
         for f in w.files:
             h, body = _unseal(f)
             offs = h["offsets"] + [len(body)]
+            w.row_dicts.append(None)                      # rows of the private container stay encoded
             w.rows.append([bytes(body[offs[i]:offs[i + 1]]) for i in range(h["count"])])
             w.index_values.append(list(h.get("index_values", [])))
             w._count += h["count"]
@@ -222,12 +264,24 @@ class FileWriter:
         for row in raw_data:
             shard = self._count % self.shard_num
             self.rows[shard].append(_encode_row(self.schema, row))
+            if self.row_dicts[shard] is not None:
+                self.row_dicts[shard].append(dict(row))
             self.index_values[shard].append([_index_value(row, f) for f in self.index_fields])
             self._count += 1
         return SUCCESS
 
+    def _private_container(self):
+        return _config["enc_key"] is not None or _config["hash_mode"] is not None or any(
+            d is None for d in self.row_dicts)
+
     def commit(self):
         names = [os.path.basename(f) for f in self.files]
+        if not self._private_container():
+            from . import mindrecord_format as F
+            F.write_dataset(self.files, self.schema, self.desc, self.index_fields, self.row_dicts,
+                            self._header_size or F.DEFAULT_HEADER_SIZE, self._page_size or F.DEFAULT_PAGE_SIZE)
+            self._committed = True
+            return SUCCESS
         for path, rows, idx in zip(self.files, self.rows, self.index_values):
             offsets, pos = [], 0
             for r in rows:
@@ -252,18 +306,34 @@ class _Shard:
         self.count = self.head["count"]
 
 
+class _ReferenceShard:
+    """A shard in the MindRecord layout, behind the interface the reader uses."""
+
+    def __init__(self, path):
+        from . import mindrecord_format as F
+        self.file = F.ShardFile(path)
+        self.count = len(self.file)
+        index = [f["index_field"] for f in self.file.header.get("index_fields", [])]
+        self.head = {"schema": self.file.schema, "index_fields": index,
+                     "desc": self.file.header["schema"][0].get("desc")}
+
+
 class FileReader:
     """Reads one or several record files.  Given one shard of a sharded file it opens all of them."""
 
     def __init__(self, file_name, num_consumer=4, columns=None, operator=None):
+        from . import mindrecord_format as F
         paths = [file_name] if isinstance(file_name, str) else list(file_name)
-        if len(paths) == 1:
+        reference = F.looks_like_mindrecord(paths[0])
+        if isinstance(file_name, str) and reference:
+            paths = F.shard_paths(paths[0])                 # a list of files is taken as given
+        elif isinstance(file_name, str):
             head, _ = _unseal(paths[0])
             shards = head.get("shards")
             if shards and len(shards) > 1:
                 folder = os.path.dirname(os.path.abspath(paths[0]))
                 paths = [os.path.join(folder, s) for s in shards]
-        self.shards = [_Shard(p) for p in paths]
+        self.shards = [_ReferenceShard(p) if reference else _Shard(p) for p in paths]
         self._schema = self.shards[0].head["schema"]
         self.index_fields = self.shards[0].head.get("index_fields", [])
         self.count = sum(s.count for s in self.shards)
@@ -285,6 +355,8 @@ class FileReader:
     def read(self, i):
         si, k = self._where[i]
         sh = self.shards[si]
+        if isinstance(sh, _ReferenceShard):
+            return sh.file.read(k, self.columns)
         pos = sh.offsets[k]
         body, row = sh.body, {}
         for name, spec in self._schema.items():
@@ -306,6 +378,8 @@ class FileReader:
 
     def index_value(self, i, field):
         si, k = self._where[i]
+        if isinstance(self.shards[si], _ReferenceShard):
+            return self.shards[si].file.index_values(k, [field])[0]
         return self.shards[si].head["index_values"][k][self.index_fields.index(field)]
 
     def get_next(self):

@@ -30,7 +30,8 @@ def test_sharded_write_read_append_and_dataset(tmp_path):
     w.add_index(["label", "name"])
     w.write_raw_data(_rows(10))
     assert w.commit() == MR.SUCCESS
-    assert sorted(os.listdir(tmp_path)) == ["data.mr0", "data.mr1", "data.mr2"]
+    assert sorted(os.listdir(tmp_path)) == ["data.mr0", "data.mr0.db", "data.mr1", "data.mr1.db", "data.mr2",
+                                            "data.mr2.db"]
     r = MR.FileReader(path + "1")                       # any shard opens them all
     assert len(r) == 10 and r.schema() == SCHEMA
     ids = sorted(int(row["id"]) for row in r.get_next())
@@ -211,5 +212,87 @@ def test_tfrecord_converter_decodes_examples_without_tensorflow(tmp_path):
                     {"label": {"type": "int64"}, "vec": {"type": "float32", "shape": [2]}, "name": {"type": "string"}},
                     ).transform()
     rows = list(MR.FileReader(str(tmp_path / "tf.mr")).get_next())
-    assert [int(r["label"][0]) for r in rows] == [5, 6, 7]
+    assert [int(np.asarray(r["label"]).reshape(-1)[0]) for r in rows] == [5, 6, 7]
     assert rows[2]["vec"].tolist() == [2.0, 2.5] and str(rows[1]["name"]) == "n1"
+
+
+# Shard 0 of a four-shard dataset as the reference's writer produced it (format version 2.0, header 16 KB, pages of
+# 32 KB; zlib + base64): four rows with an int32 label and four blob fields.
+_REFERENCE_SHARD = (
+    "eNrt0kGL00AUwPGue1n07M3DMue4NE2pS/HSxcuCIIgguCxhkpluA2lakqxaS2n2W/gFvPvdBK910kyapvYkqJf/79CZefPmzeu0"
+    "16edraWYaKl06mfRFy2G7sC77DsiSpT+7I8jHatMDG+W+wExFLEMdCwckYUTPZV+ZGLd1a0j5vJOb9N1ovx09mm706/iVZad28vc"
+    "waUN5Iu5CYir12+u/FejdyOxF69PlgXv0tn93ARsV9XGbDzOdG57yCYyVfWRLJdpvuuku3LarXX3WnNbrQ367cbejt7/zb5uW5d7"
+    "vRflw1Svuy0YxLOg+TmETFO58KVpppoFu1m4mylhiiqdhab7JJ77tlpTdrkrY6amu/J73jx3zSn7naMk93pi1Vyyl+c6B5mDfpMZ"
+    "lpl2K1jkOmu21H6R3vEi1b+rKWH7WDWvKJVKdZbp6jHC+Hqqgoup+Y+mOpylqls+wm9R92i0dzTqiSO/WB5leRSaO5P7OHbER51m"
+    "0SwxDfYuumLVAQAAAAAAAAAAAAAAAAAAAAAAAAAAAIA/8+yktXxZfpShjbE2Y2HGwozrMlBvFtXmxgQ7xfacjWx9rYvVpTdWnVDY"
+    "dWHX6zrh8GDRPrixiZ1i128roxzLhTleZXx/+uSD5/04uP4siefnSubSrs9/2oQHOz6u++KNeCPe6J++EQAAAAAAAAAAAAAAAAAA"
+    "AAAAAAAAAAAAAAAAAAAAAAAAAAAAAAAAAAAAAAAAAPA/ndnx4VssAx0frk8O1o8O1qe/AHIt4Xw=")
+
+
+def test_a_file_written_by_the_reference_reads_back(tmp_path):
+    import base64
+    import zlib
+
+    from mindspore_b200.dataset import mindrecord_format as F
+    path = tmp_path / "aclImdb.mindrecord0"
+    path.write_bytes(zlib.decompress(base64.b64decode(_REFERENCE_SHARD)))
+    assert F.looks_like_mindrecord(str(path))
+    assert [os.path.basename(p) for p in F.shard_paths(str(path))] == ["aclImdb.mindrecord%d" % k for k in range(4)]
+    reader = MR.FileReader([str(path)])                       # this shard alone
+    assert len(reader) == 4 and reader.index_fields == ["label"]
+    assert reader.schema()["array_b"] == {"shape": [1, -1], "type": "int64"}
+    rows = list(reader.get_next())
+    assert [int(r["label"]) for r in rows] == [0, 1, 2, 3]
+    r = rows[1]
+    assert r["array_a"].dtype == np.int32 and r["array_a"][:6].tolist() == [0, 1, -1, 127, -128, 128]
+    assert r["array_b"].shape == (1, 19) and r["array_d"].tolist() == [[-10, -127], [10, 127]]
+    assert bytes(r["array_c"]) == b"nlp data"
+
+
+def test_written_files_follow_the_reference_layout(tmp_path):
+    import json
+    import sqlite3
+    import struct
+
+    import msgpack
+
+    from mindspore_b200.dataset import mindrecord_format as F
+    path = str(tmp_path / "lay.mindrecord")
+    w = MR.FileWriter(path)
+    w.set_header_size(1 << 14)
+    w.set_page_size(1 << 15)
+    w.add_schema({"label": {"type": "int32"}, "ids": {"type": "int64", "shape": [-1]}, "img": {"type": "bytes"}}, "lay")
+    w.add_index(["label"])
+    w.write_raw_data([{"label": i, "ids": np.array([i, 300 * i, -70000 * i]), "img": bytes([i]) * 5} for i in range(3)])
+    w.commit()
+    data = open(path, "rb").read()
+    (n,) = struct.unpack("<Q", data[:8])
+    head = json.loads(data[8:8 + n])
+    assert head["header_size"] == 1 << 14 and head["page_size"] == 1 << 15 and head["version"] == "3.0"
+    assert head["schema"][0]["blob_fields"] == ["ids", "img"] and head["shard_addresses"] == ["lay.mindrecord"]
+    kinds = [p["page_type"] for p in head["page"]]
+    assert kinds == ["BLOB_DATA", "RAW_DATA"]
+    raw_at = (1 << 14) + (1 << 15)                             # page 1
+    (m,) = struct.unpack("<Q", data[raw_at:raw_at + 8])
+    assert msgpack.unpackb(data[raw_at + 8:raw_at + 8 + m]) == {"label": 0}
+    blob_at = 1 << 14                                          # page 0: u64 length, then per field u64 BE length + bytes
+    (b,) = struct.unpack("<Q", data[blob_at:blob_at + 8])
+    (ids_len,) = struct.unpack(">Q", data[blob_at + 8:blob_at + 16])
+    ids = data[blob_at + 16:blob_at + 16 + ids_len]
+    assert struct.unpack(">I", ids[:4])[0] == 3 and F.uncompress_ints(ids, np.int64).tolist() == [0, 0, 0]
+    assert len(data) == raw_at + head["page"][1]["page_size"]  # the file ends with the last page's data
+    con = sqlite3.connect(path + ".db")
+    rows = list(con.execute("SELECT ROW_ID, PAGE_ID_RAW, PAGE_OFFSET_RAW, PAGE_ID_BLOB, label_0 FROM INDEXES"))
+    assert rows[0] == (0, 1, 0, 0, 0) and [r[4] for r in rows] == [0, 1, 2]
+    assert list(con.execute("SELECT NAME FROM SHARD_NAME")) == [("lay.mindrecord",)]
+    back = list(MR.FileReader(path).get_next())
+    assert back[2]["ids"].tolist() == [2, 600, -140000] and bytes(back[2]["img"]) == b"\x02" * 5
+    a = np.array([0, -1, 127, -128, 128, -32768, 32768, 2 ** 31 - 1, -2 ** 31, 2 ** 31, -2 ** 62], np.int64)
+    assert (F.uncompress_ints(F.compress_ints(a), np.int64) == a).all()
+    assert len(F.compress_ints(np.zeros(8, np.int64))) == 4 + 2 + 8
+    with pytest.raises(ValueError):
+        w2 = MR.FileWriter(str(tmp_path / "big.mindrecord"))
+        w2.set_page_size(1 << 15)
+        w2.add_schema({"img": {"type": "bytes"}})
+        w2.write_raw_data([{"img": b"x" * (1 << 16)}])
+        w2.commit()
