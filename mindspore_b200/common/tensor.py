@@ -74,6 +74,16 @@ class Tensor(torch.Tensor):
 
     @staticmethod
     def __new__(cls, input_data=None, dtype=None, shape=None, init=None, const_arg=False, device=None):
+        if input_data is None and init is None and dtype is not None and (
+                shape is None or any(d is None or not isinstance(d, int) for d in shape)):
+            # a placeholder of an input signature: dimensions that are None or a Symbol are known at run time only
+            # (shape=None: the rank too).  It holds no storage; unknown dimensions show as their smallest value.
+            dims = [2, 2] if shape is None else [d if isinstance(d, int) else getattr(d, "min", 1) for d in shape]
+            obj = torch.Tensor._make_subclass(cls, torch.empty(dims, dtype=dtype, device="meta"), False)
+            obj.const_arg = const_arg
+            obj.symbolic_shape = None if shape is None else tuple(shape)
+            obj.dynamic_rank = shape is None
+            return obj
         if input_data is None:
             if init is None or shape is None:
                 if shape is not None and dtype is not None and init is None:

@@ -91,6 +91,8 @@ def graph_to_text(fg):
         meta = {k: v for k, v in n.meta.items() if k in ("strategy", "layout", "stage", "micro", "fusion",
                                                         "forward_comm", "primitive", "vjp_of", "requires_vjp")}
         ann = ("  # " + ", ".join("%s=%s" % kv for kv in meta.items())) if meta else ""
+        if "abstract" in n.meta:
+            ann = "  : %r%s" % (n.meta["abstract"], ann)
         if n.op == "placeholder":
             lines.append("%%%s = Input %s%s" % (n.name, n.meta.get("example", ""), ann))
         elif n.op == "get_attr":

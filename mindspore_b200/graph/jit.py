@@ -468,6 +468,10 @@ def _compile(fn, inputs, kwargs, name, owner=None):
         annotate_graph(fg, owner)
         if level:
             dump_graph(fg, os.path.join(path, "%s_step_parallel_end.ir" % name))
+    if level:
+        from .abstract import annotate_graph
+        annotate_graph(fg, inputs)
+        dump_graph(fg, os.path.join(path, "%s_validate.ir" % name))
     cg = CompiledGraph(fg, out)
     from .flops import note_compiled
     note_compiled("train" if (owner is None or getattr(owner, "training", True)) else "predict", fg)
@@ -536,6 +540,10 @@ def compile_cell(cell, inputs, kwargs):
     key = _signature(inputs, kwargs, cell.training)
     cg = cell._compiled.get(key)
     if cg is None:
+        declared = getattr(cell, "_dynamic_inputs", None)
+        if declared:
+            from .abstract import check_signature
+            check_signature(declared, inputs, "set_inputs")
         cg = _compile(cell._run_construct_traced, inputs, kwargs, type(cell).__name__, owner=cell)
         cell._compiled[key] = cg
     return cg
@@ -581,6 +589,9 @@ def jit(fn=None, mode="PSJit", input_signature=None, hash_args=None, jit_config=
             from ..nn.cell import Cell
             if _trace_state.is_tracing() or os.environ.get("MS_JIT") == "0":
                 return f(*args, **kwargs)
+            if input_signature is not None:
+                from .abstract import check_signature
+                check_signature(input_signature, args[1:] if args and isinstance(args[0], Cell) else args)
             key = _signature(args, kwargs, None)
             cg = cache.get(key)
             Cell._graph_depth += 1
@@ -594,7 +605,16 @@ def jit(fn=None, mode="PSJit", input_signature=None, hash_args=None, jit_config=
             finally:
                 Cell._graph_depth -= 1
 
+        def infer_outputs(*abstract_args, **kw):
+            """Abstract outputs for abstract / placeholder inputs (the input signature when none are given)."""
+            from .abstract import infer
+            if not abstract_args and input_signature is not None:
+                abstract_args = tuple(input_signature) if isinstance(input_signature, (tuple, list)) else (
+                    input_signature,)
+            return infer(f, *abstract_args, **kw)
+
         wrapper.__jit_cache__ = cache
+        wrapper.infer = infer_outputs
         return wrapper
 
     return deco(fn) if fn is not None else deco

@@ -210,6 +210,14 @@ class Cell:
     def get_inputs(self):
         return getattr(self, "_dynamic_inputs", None)
 
+    def infer_outputs(self, *inputs):
+        """Abstract outputs (shapes with symbolic dimensions, dtypes) of ``construct`` for abstract / placeholder
+        inputs, without running a kernel; the ``set_inputs`` declaration when no inputs are given."""
+        from ..graph.abstract import infer
+        if not inputs:
+            inputs = getattr(self, "_dynamic_inputs", None) or ()
+        return infer(lambda *a: self._run_construct(a, {}), *inputs)
+
     def set_jit_config(self, jit_config):
         self._jit_config = jit_config
 

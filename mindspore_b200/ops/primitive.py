@@ -187,6 +187,12 @@ class Primitive:
     def __setstate__(self, d):
         self.__dict__.update(d)
 
+    def infer(self, *args, **kwargs):
+        """The abstract result (shape with symbolic dimensions, dtype) for abstract or placeholder inputs, without
+        running a kernel.  Parity (role): the InferShape / InferType pair of every primitive in core/ops."""
+        from ..graph.abstract import infer
+        return infer(self, *args, **kwargs)
+
     def check_elim(self, *args):
         return (False, None)
 
@@ -199,16 +205,61 @@ class Primitive:
 
 
 class PrimitiveWithInfer(Primitive):
-    """Kept for API compatibility; shape/type inference comes from running on meta tensors."""
+    """A primitive that answers shape / dtype questions before it runs.  The defaults evaluate the primitive on
+    storage-less tensors (``graph/abstract.py``); a subclass may override ``infer_shape`` / ``infer_dtype`` /
+    ``infer_value`` and ``__infer__`` then uses those.  Parity: ops/primitive.py PrimitiveWithInfer."""
 
-    def infer_shape(self, *args):
-        return None
+    def infer_shape(self, *shapes):
+        """Output shape(s) for input shapes (lists; -1 marks a dynamic dimension, which stays -1 where it flows)."""
+        from ..graph.abstract import AbstractTensor
+        out = self.infer(*[AbstractTensor([None if d == -1 else d for d in s], torch.float32) for s in shapes])
+        return _shapes_of(out)
 
-    def infer_dtype(self, *args):
-        return None
+    def infer_dtype(self, *dtypes):
+        """Output dtype(s) for input dtypes; the primitive is tried on inputs of rank 0 to 4."""
+        from ..graph.abstract import AbstractTensor, InferenceError
+        err = None
+        for rank in range(5):
+            try:
+                out = self.infer(*[AbstractTensor([2] * rank, d) for d in dtypes])
+                return _dtypes_of(out)
+            except InferenceError as e:
+                err = e
+        raise err
 
     def infer_value(self, *args):
         return None
+
+    def __infer__(self, *inputs):
+        """``inputs``: dicts with ``shape`` / ``dtype`` / ``value``; returns the same form for the output."""
+        from ..graph.abstract import AbstractTensor
+        own = type(self)
+        if own.infer_shape is not PrimitiveWithInfer.infer_shape or own.infer_dtype is not PrimitiveWithInfer.infer_dtype:
+            shape = self.infer_shape(*[i["shape"] for i in inputs])
+            dtype = self.infer_dtype(*[i["dtype"] for i in inputs])
+            return {"shape": shape, "dtype": dtype, "value": self.infer_value(*[i.get("value") for i in inputs])}
+        out = self.infer(*[AbstractTensor([None if d == -1 else d for d in i["shape"]], i["dtype"]) for i in inputs])
+        return {"shape": _shapes_of(out), "dtype": _dtypes_of(out), "value": None}
+
+
+def _shapes_of(a):
+    from ..graph.abstract import AbstractSequence, AbstractTensor
+    if isinstance(a, AbstractTensor):
+        return a.shape_list
+    if isinstance(a, AbstractSequence):
+        return a.kind(_shapes_of(e) for e in a.elements)
+    return None
+
+
+def _dtypes_of(a):
+    from ..graph.abstract import AbstractScalar, AbstractSequence, AbstractTensor
+    if isinstance(a, AbstractTensor):
+        return a.dtype
+    if isinstance(a, AbstractSequence):
+        return a.kind(_dtypes_of(e) for e in a.elements)
+    if isinstance(a, AbstractScalar):
+        return a.type
+    return None
 
 
 class PrimitiveWithCheck(Primitive):
