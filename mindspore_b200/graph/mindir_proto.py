@@ -16,7 +16,8 @@ Writer: ``save_model_proto(fg, path)`` stores a traced forward graph the way the
 Reader: ``load_model_proto(bytes)`` accepts that layout and the older one in which a node's ``op_type`` is the
 primitive name itself and the attributes sit on the node (core/load_mindir/load_model.cc:1770-1780 distinguishes the
 two by the ``REF::`` prefix).  Primitives are looked up by name in ``mindspore_b200.ops``; an operator this build does
-not define is reported by name.  Sub-graphs (``functions``), closures and monads are outside this reader.
+not define is reported by name.  A model with sub-graphs (``functions``: the branches of an ``if``, the recursion of
+a ``while``, closures) loads as one node run by an interpreter of the file's nodes (``_Program``).
 
 The message classes are built at import time from a description of the schema (field names, numbers and types are
 the file format), so no generated ``_pb2`` module and no ``protoc`` are needed."""
@@ -451,6 +452,12 @@ def _lowerings():
         torch.mean: reduce("ReduceMean"), T.mean: reduce("ReduceMean"), torch.sum: reduce("ReduceSum"),
         T.sum: reduce("ReduceSum"), F.embedding: embedding, torch.embedding: embedding,
     }
+    table[T.detach] = table[torch.detach] = unary("StopGradient")
+    for short, dunder, prim_name in (("gt", "__gt__", "Greater"), ("lt", "__lt__", "Less"),
+                                     ("ge", "__ge__", "GreaterEqual"), ("le", "__le__", "LessEqual"),
+                                     ("eq", "__eq__", "Equal"), ("ne", "__ne__", "NotEqual")):
+        for fn in (getattr(torch, short), getattr(T, short), getattr(T, dunder)):
+            table[fn] = binary(prim_name)
     return table
 
 
@@ -466,8 +473,13 @@ _LOWER = None
 
 # ---------------------------------------------------------------------------------------------------- writer
 def build_model_proto(fg, producer_version="2.4.0"):
+    """One ModelProto for a traced graph.  A ``Switch`` node becomes two entries of ``functions`` (its branches),
+    two ``Partial`` nodes that bind the operands, a ``Switch`` primitive that picks one and a call of its result; a
+    ``While`` node becomes the recursive header / body / exit functions that the reference's parser makes of a
+    ``while`` statement (ccsrc/pipeline/jit/ps/parse/parse.cc: ParseWhile)."""
     import torch.fx as fx
     from . import autodiff
+    from .control_flow import Switch, While
     M = messages()
     model = M["ModelProto"]()
     model.ir_version = "0.1.1"
@@ -476,107 +488,233 @@ def build_model_proto(fg, producer_version="2.4.0"):
     model.model_version = "1"
     model.little_endian = True
     model.mind_ir_version = 2
-    gp = model.graph
-    gname = fg.name or "graph"
-    gp.name = gname
+    main = model.graph
     counter = [0]
-    names = {}
+    written_params = set()
+    graph_names = set()
 
-    def fresh():
-        counter[0] += 1
-        return "%s:%d" % (gname, counter[0])
+    def unique_graph_name(base):
+        name, k = base, 0
+        while name in graph_names:
+            k += 1
+            name = "%s_%d" % (base, k)
+        graph_names.add(name)
+        return name
 
-    def constant(value):
-        node = gp.node.add()
-        node.name = fresh()
-        node.output.append(node.name)
-        node.op_type = "Constant"
-        ap = node.attribute.add()
-        ap.name = "value"
-        _fill_attr(ap, value)
-        return node.name
+    def write_graph(fg, gp, gname):
+        gp.name = gname
+        names = {}
 
-    def operand(a):
-        if isinstance(a, fx.Node):
-            return names[a]
-        if isinstance(a, _Ref):
-            return a.name
-        return constant(a)
+        def fresh():
+            counter[0] += 1
+            return "%s:%d" % (gname, counter[0])
 
-    def call(prim_name, attrs, inputs, scope=""):
-        pp = model.primitives.add()
-        pp.name = "%s:%d" % (prim_name, len(model.primitives))
-        pp.op_type = prim_name
-        pp.prim_type = 1
-        for k, v in attrs.items():
-            ap = pp.attribute.add()
-            ap.name = k
-            try:
-                _fill_attr(ap, v)
-            except MindIRError:
-                del pp.attribute[-1]              # callables and the like are not part of a primitive's record
-        ins = [operand(a) for a in inputs]        # constants are written before the node that reads them
-        node = gp.node.add()
-        node.name = fresh()
-        node.output.append(node.name)
-        node.op_type = "REF::" + pp.name
-        node.domain = scope
-        node.input.extend(ins)
-        return node.name
+        def constant(value):
+            node = gp.node.add()
+            node.name = fresh()
+            node.output.append(node.name)
+            node.op_type = "Constant"
+            ap = node.attribute.add()
+            ap.name = "value"
+            _fill_attr(ap, value)
+            return node.name
 
-    for n in fg.graph.nodes:
-        if n.op == "placeholder":
-            vi = gp.input.add()
-            vi.name = n.name
-            names[n] = n.name
-            if "shape" in n.meta and "dtype" in n.meta and n.meta["dtype"] in _DT:
-                tp = vi.tensor.add()
-                tp.dims.extend(int(d) for d in n.meta["shape"])
-                tp.data_type = _DT[n.meta["dtype"]]
-        elif n.op == "get_attr":
-            if "param" in n.meta:
-                pname = n.target.split("::", 1)[1]
-                _fill_tensor(gp.parameter.add(), n.meta["param"], pname)
-                names[n] = pname
+        def operand(a):
+            if isinstance(a, fx.Node):
+                return names[a]
+            if isinstance(a, _Ref):
+                return a.name
+            return constant(a)
+
+        def raw_node(op_type, ins, scope=""):
+            node = gp.node.add()
+            node.name = fresh()
+            node.output.append(node.name)
+            node.op_type = op_type
+            node.domain = scope
+            node.input.extend(ins)
+            return node.name
+
+        def call(prim_name, attrs, inputs, scope=""):
+            pp = model.primitives.add()
+            pp.name = "%s:%d" % (prim_name, len(model.primitives))
+            pp.op_type = prim_name
+            pp.prim_type = 1
+            for k, v in attrs.items():
+                ap = pp.attribute.add()
+                ap.name = k
+                try:
+                    _fill_attr(ap, v)
+                except MindIRError:
+                    del pp.attribute[-1]          # callables and the like are not part of a primitive's record
+            ins = [operand(a) for a in inputs]    # constants are written before the node that reads them
+            return raw_node("REF::" + pp.name, ins, scope)
+
+        def function(sub, base):
+            """Writes a traced sub-graph as an entry of ``functions`` and returns its name (a node input that is a
+            function's name refers to the function itself)."""
+            name = unique_graph_name(base)
+            write_graph(sub, model.functions.add(), name)
+            return name
+
+        def synthetic(name, n_inputs, body):
+            """A function that this exporter composes itself under a name reserved by the caller:
+            ``body(node, prim, const, input names)`` returns the name of the output."""
+            sub = model.functions.add()
+            sub.name = name
+            ins = []
+            for k in range(n_inputs):
+                vi = sub.input.add()
+                vi.name = "%s:x%d" % (name, k)
+                ins.append(vi.name)
+
+            def sub_node(op_type, inputs):
+                counter[0] += 1
+                node = sub.node.add()
+                node.name = "%s:%d" % (name, counter[0])
+                node.output.append(node.name)
+                node.op_type = op_type
+                node.input.extend(inputs)
+                return node.name
+
+            def sub_call(prim_name, inputs):
+                pp = model.primitives.add()
+                pp.name = "%s:%d" % (prim_name, len(model.primitives))
+                pp.op_type = prim_name
+                pp.prim_type = 1
+                return sub_node("REF::" + pp.name, inputs)
+
+            def sub_const(value):
+                counter[0] += 1
+                node = sub.node.add()
+                node.name = "%s:%d" % (name, counter[0])
+                node.output.append(node.name)
+                node.op_type = "Constant"
+                ap = node.attribute.add()
+                ap.name = "value"
+                _fill_attr(ap, value)
+                return node.name
+
+            sub.output.add().name = body(sub_node, sub_call, sub_const, ins)
+
+        def switch(n):
+            sw = n.target
+            pred, vals = n.args[0], [operand(a) for a in n.args[1:]]
+            ops_ = vals[:sw.n_operands]
+            caps = (vals[sw.n_operands:sw.n_operands + sw.n_true_caps], vals[sw.n_operands + sw.n_true_caps:])
+            partials = []
+            for branch, label in ((0, "cond_true"), (1, "cond_false")):
+                sub = sw.graphs[branch]
+                fname = function(sub, "%s_%s" % (gname, label))
+                ins = [ops_[i] for i in sub.operand_positions] + caps[branch]
+                partials.append(call("Partial", {}, [_Ref(fname)] + [_Ref(i) for i in ins]))
+            chosen = call("Switch", {}, [pred, _Ref(partials[0]), _Ref(partials[1])])
+            return raw_node("REF::" + chosen, [])
+
+        def loop(n):
+            wl = n.target
+            if wl.max_iterations is not None:
+                raise MindIRError("a While node with max_iterations has no MindIR form")
+            cg, bg = wl.graphs
+            vals = [operand(a) for a in n.args]
+            ns, nc, nb = wl.n_state, wl.n_cond_caps, wl.n_body_caps
+            cond_name = function(cg, gname + "_while_cond")
+            body_name = function(bg, gname + "_while_body")
+            header_name = unique_graph_name(gname + "_while_header")
+            step_name = unique_graph_name(gname + "_while_step")
+            exit_name = unique_graph_name(gname + "_while_exit")
+            total = ns + nc + nb
+
+            def exit_body(node, prim, const, ins):
+                return prim("MakeTuple", ins)
+            synthetic(exit_name, ns, exit_body)
+
+            def step_body(node, prim, const, ins):
+                state, b_caps = ins[:ns], ins[ns + nc:]
+                out = node("REF::" + body_name, [state[i] for i in bg.operand_positions] + b_caps)
+                if isinstance(bg.example_outputs, (tuple, list)):
+                    nxt = [prim("TupleGetItem", [out, const(k)]) for k in range(ns)]
+                else:
+                    nxt = [out]
+                return node("REF::" + header_name, nxt + ins[ns:])
+
+            def header_body(node, prim, const, ins):
+                state, c_caps = ins[:ns], ins[ns:ns + nc]
+                c = node("REF::" + cond_name, [state[i] for i in cg.operand_positions] + c_caps)
+                again = prim("Partial", [step_name] + ins)
+                leave = prim("Partial", [exit_name] + state)
+                chosen = prim("Switch", [c, again, leave])
+                return node("REF::" + chosen, [])
+            synthetic(header_name, total, header_body)
+            synthetic(step_name, total, step_body)
+            return raw_node("REF::" + header_name, vals)
+
+        for n in fg.graph.nodes:
+            if n.op == "placeholder":
+                vi = gp.input.add()
+                vi.name = n.name if gp is main else "%s:%s" % (gname, n.name)
+                names[n] = vi.name
+                shape, dtype = n.meta.get("shape"), n.meta.get("dtype")
+                if shape is None and isinstance(n.meta.get("example"), tuple) and len(n.meta["example"]) == 2:
+                    shape, dtype = n.meta["example"]
+                if shape is not None and dtype in _DT:
+                    tp = vi.tensor.add()
+                    tp.dims.extend(int(d) for d in shape)
+                    tp.data_type = _DT[dtype]
+            elif n.op == "get_attr":
+                if "param" in n.meta:
+                    pname = n.target.split("::", 1)[1]
+                    if pname not in written_params:           # weights live in the main graph; functions name them
+                        written_params.add(pname)
+                        _fill_tensor(main.parameter.add(), n.meta["param"], pname)
+                    names[n] = pname
+                else:
+                    names[n] = constant(n.meta["const"])
+            elif n.op == "call_function":
+                if n.target is autodiff.vjp:
+                    raise MindIRError("only forward graphs can be exported (found a gradient node)")
+                if isinstance(n.target, Switch):
+                    names[n] = switch(n)
+                    continue
+                if isinstance(n.target, While):
+                    names[n] = loop(n)
+                    continue
+                is_prim = hasattr(n.target, "name") and hasattr(n.target, "attrs")
+                if n.kwargs and (is_prim or n.target in _BUILTIN_PRIMS or n.target is operator.getitem):
+                    raise MindIRError("node %s passes keyword arguments, which MindIR nodes cannot carry" % n.name)
+                if n.target is operator.getitem:
+                    if not isinstance(n.args[1], int):
+                        raise MindIRError("node %s slices a tensor; only tuple indexing is stored" % n.name)
+                    names[n] = call("TupleGetItem", {}, [n.args[0], int(n.args[1])])
+                elif n.target in _BUILTIN_PRIMS:
+                    names[n] = call(_BUILTIN_PRIMS[n.target], {}, list(n.args))
+                elif is_prim:
+                    attrs = dict(n.target.attrs)
+                    if getattr(n.target, "in_strategy", None) is not None:
+                        attrs["in_strategy"] = n.target.in_strategy
+                    if getattr(n.target, "out_strategy", None) is not None:
+                        attrs["out_strategy"] = n.target.out_strategy
+                    names[n] = call(n.target.name, attrs, list(n.args), str(n.meta.get("scope", "")))
+                else:
+                    global _LOWER
+                    if _LOWER is None:
+                        _LOWER = _lowerings()
+                    rule = _LOWER.get(n.target)
+                    if rule is None:
+                        raise MindIRError("node %s calls %r, which is neither a primitive nor a function with a "
+                                          "lowering to primitives" % (n.name, n.target))
+                    names[n] = rule(call, tuple(n.args), dict(n.kwargs), n)
+            elif n.op == "output":
+                res = n.args[0]
+                if isinstance(res, (tuple, list)):
+                    out_name = call("MakeTuple", {}, list(res))
+                else:
+                    out_name = operand(res)
+                gp.output.add().name = out_name
             else:
-                names[n] = constant(n.meta["const"])
-        elif n.op == "call_function":
-            if n.target is autodiff.vjp:
-                raise MindIRError("only forward graphs can be exported (found a gradient node)")
-            is_prim = hasattr(n.target, "name") and hasattr(n.target, "attrs")
-            if n.kwargs and (is_prim or n.target in _BUILTIN_PRIMS or n.target is operator.getitem):
-                raise MindIRError("node %s passes keyword arguments, which MindIR nodes cannot carry" % n.name)
-            if n.target is operator.getitem:
-                if not isinstance(n.args[1], int):
-                    raise MindIRError("node %s slices a tensor; only tuple indexing is stored" % n.name)
-                names[n] = call("TupleGetItem", {}, [n.args[0], int(n.args[1])])
-            elif n.target in _BUILTIN_PRIMS:
-                names[n] = call(_BUILTIN_PRIMS[n.target], {}, list(n.args))
-            elif hasattr(n.target, "name") and hasattr(n.target, "attrs"):
-                attrs = dict(n.target.attrs)
-                if getattr(n.target, "in_strategy", None) is not None:
-                    attrs["in_strategy"] = n.target.in_strategy
-                if getattr(n.target, "out_strategy", None) is not None:
-                    attrs["out_strategy"] = n.target.out_strategy
-                names[n] = call(n.target.name, attrs, list(n.args), str(n.meta.get("scope", "")))
-            else:
-                global _LOWER
-                if _LOWER is None:
-                    _LOWER = _lowerings()
-                rule = _LOWER.get(n.target)
-                if rule is None:
-                    raise MindIRError("node %s calls %r, which is neither a primitive nor a function with a "
-                                      "lowering to primitives" % (n.name, n.target))
-                names[n] = rule(call, tuple(n.args), dict(n.kwargs), n)
-        elif n.op == "output":
-            res = n.args[0]
-            if isinstance(res, (tuple, list)):
-                out_name = call("MakeTuple", {}, list(res))
-            else:
-                out_name = operand(res)
-            gp.output.add().name = out_name
-        else:
-            raise MindIRError("node kind %s is not supported in graph files" % n.op)
+                raise MindIRError("node kind %s is not supported in graph files" % n.op)
+
+    write_graph(fg, main, unique_graph_name(fg.name or "graph"))
     return model
 
 
@@ -620,6 +758,155 @@ def _make_tuple(*items):
     return tuple(items)
 
 
+class _TailCall:
+    """A call in tail position, handed back to the caller's loop: a ``while`` written as recursion between the header
+    and the step function runs in constant Python stack depth."""
+
+    def __init__(self, callee, args):
+        self.callee, self.args = callee, args
+
+
+class _Closure:
+    """A function of the model together with the frame in which its name was read (its free variables)."""
+
+    def __init__(self, program, gp, frame):
+        self.program, self.gp, self.frame = program, gp, frame
+
+    def __call__(self, *args):
+        return _resolve(self.program.run(self.gp, args, self.frame))
+
+
+class _BoundCall:
+    """``Partial(fn, a, b)``: the callee and its leading arguments."""
+
+    def __init__(self, callee, bound):
+        self.callee, self.bound = callee, tuple(bound)
+
+    def __call__(self, *args):
+        return _resolve(_TailCall(self.callee, self.bound + tuple(args)))
+
+
+def _resolve(res):
+    while isinstance(res, _TailCall):
+        callee, args = res.callee, res.args
+        while isinstance(callee, _BoundCall):
+            callee, args = callee.callee, callee.bound + tuple(args)
+        if isinstance(callee, _Closure):
+            res = callee.program.run(callee.gp, args, callee.frame)
+        else:
+            res = callee(*args)
+    return res
+
+
+class _Program:
+    """Interpreter for a model with ``functions``: nodes run in file order; a node input that names a function is
+    that function as a value (with the current frame, so nodes of enclosing graphs stay readable by name); a node
+    whose ``op_type`` names a function or an earlier node calls it.  ``Switch`` reads its condition on the host and
+    returns one of its two operands, ``Partial`` binds leading arguments.  Parity (role): the ANF graphs that
+    core/load_mindir/anf_model_parser.cc rebuilds and the VM that runs Switch / Partial / calls of them."""
+
+    def __init__(self, model, weight_names):
+        self.primitives = {p.name: p for p in model.primitives}
+        self.functions = {f.name: f for f in model.functions}
+        self.main = model.graph
+        self.weight_names = list(weight_names)
+        self._prim_cache = {}
+        self._constants = {}
+        self.__name__ = "MindIRProgram"
+
+    def __call__(self, *values):
+        n_in = len(values) - len(self.weight_names)
+        globals_frame = ({name: v for name, v in zip(self.weight_names, values[n_in:])}, None)
+        return _resolve(self.run(self.main, values[:n_in], globals_frame))
+
+    def primitive(self, key):
+        hit = self._prim_cache.get(key)
+        if hit is None:
+            pp = self.primitives[key]
+            attrs = {a.name: _read_attr(a) for a in pp.attribute}
+            special = pp.op_type in ("TupleGetItem", "MakeTuple", "MakeList", "Depend", "UpdateState", "Load",
+                                     "Return", "Switch", "Partial", "SwitchLayer")
+            hit = self._prim_cache[key] = (pp.op_type, None if special else _make_primitive(pp.op_type, attrs))
+        return hit
+
+    def lookup(self, name, frame):
+        f = frame
+        while f is not None:
+            if name in f[0]:
+                return f[0][name]
+            f = f[1]
+        if name in self.functions:
+            return _Closure(self, self.functions[name], frame)
+        raise MindIRError("node input %r is not defined before its use" % name)
+
+    def run(self, gp, args, outer):
+        values = {}
+        frame = (values, outer)
+        declared = [vi.name for vi in gp.input if vi.name not in self.weight_names]
+        if len(declared) != len(args):
+            raise MindIRError("graph %s takes %d inputs, but %d were given" % (gp.name, len(declared), len(args)))
+        values.update(zip(declared, args))
+        out_name = gp.output[0].name if gp.output else None
+        for nd in gp.node:
+            name = nd.output[0] if nd.output else nd.name
+            if nd.op_type == "Constant":
+                key = (gp.name, name)
+                if key not in self._constants:
+                    self._constants[key] = _read_attr(nd.attribute[0]) if nd.attribute else None
+                values[name] = self._constants[key]
+                continue
+            ins = [self.lookup(i, frame) for i in nd.input]
+            ins = [a for a in ins if a is not _MONAD]
+            key = nd.op_type[5:] if nd.op_type.startswith("REF::") else None
+            if key is None or key in self.primitives:
+                if key is None:
+                    op_type, prim = nd.op_type, None
+                    if op_type not in ("TupleGetItem", "MakeTuple", "MakeList", "Depend", "UpdateState", "Load",
+                                       "Return", "Switch", "Partial", "SwitchLayer"):
+                        ck = ("node", gp.name, name)
+                        if ck not in self._prim_cache:
+                            self._prim_cache[ck] = _make_primitive(op_type,
+                                                                   {a.name: _read_attr(a) for a in nd.attribute})
+                        prim = self._prim_cache[ck]
+                else:
+                    op_type, prim = self.primitive(key)
+                if op_type == "TupleGetItem":
+                    values[name] = ins[0][int(ins[1])]
+                elif op_type == "MakeTuple":
+                    values[name] = tuple(ins)
+                elif op_type == "MakeList":
+                    values[name] = list(ins)
+                elif op_type in ("Depend", "UpdateState", "Load"):
+                    values[name] = ins[0] if ins else _MONAD
+                elif op_type == "Return":
+                    values[name] = ins[0]
+                elif op_type == "Switch":
+                    cond = ins[0]
+                    if isinstance(cond, torch.Tensor):
+                        cond = bool(cond.detach().as_subclass(torch.Tensor).reshape(-1)[0].item())
+                    values[name] = ins[1] if cond else ins[2]
+                elif op_type == "SwitchLayer":
+                    index = ins[0]
+                    if isinstance(index, torch.Tensor):
+                        index = int(index.detach().as_subclass(torch.Tensor).reshape(-1)[0].item())
+                    values[name] = ins[1][index]
+                elif op_type == "Partial":
+                    values[name] = _BoundCall(ins[0], ins[1:])
+                else:
+                    values[name] = prim(*ins)
+                continue
+            callee = self.lookup(key, frame)
+            if not callable(callee):
+                raise MindIRError("node %s calls %s, which is not a function of the model" % (nd.name, key))
+            if name == out_name:
+                return _TailCall(callee, tuple(ins))
+            values[name] = _resolve(_TailCall(callee, tuple(ins)))
+        if out_name is None:
+            raise MindIRError("graph %s has no output" % gp.name)
+        outs = [self.lookup(o.name, frame) for o in gp.output]
+        return outs[0] if len(outs) == 1 else tuple(outs)
+
+
 def load_model_proto(data):
     from ..common.parameter import Parameter
     from ..common.tensor import Tensor
@@ -629,9 +916,6 @@ def load_model_proto(data):
         model.ParseFromString(bytes(data))
     except Exception as e:  # noqa: BLE001
         raise MindIRError("not a MindIR protobuf file: %s" % e)
-    if model.functions:
-        raise MindIRError("the file holds %d sub-graphs (control flow / closures); this reader takes single-graph "
-                          "models" % len(model.functions))
     gp = model.graph
     prims = {p.name: p for p in model.primitives}
     fg = FuncGraph(gp.name or "graph")
@@ -663,6 +947,17 @@ def load_model_proto(data):
         if name not in env:
             raise MindIRError("node input %r is not defined before its use" % name)
         return env[name]
+
+    if model.functions:
+        # control flow: the whole model is ONE node of the graph, run by the interpreter; the weights stay
+        # parameters of the loaded graph (they are the node's trailing operands)
+        weights = [tp.name for tp in gp.parameter]
+        operands = [env[vi.name] for vi in gp.input if vi.name not in param_names] + [env[w] for w in weights]
+        node = g.create_node("call_function", _Program(model, weights), tuple(operands), {})
+        node.meta["primitive"] = "MindIRProgram"
+        fg.output_node = g.output(node)
+        fg.input_positions = list(range(n_in))
+        return LoadedGraph(fg)
 
     for nd in gp.node:
         out_name = nd.output[0] if nd.output else nd.name

@@ -671,6 +671,8 @@ class GraphCell(Cell):
         super().__init__(auto_prefix=True)
         self.graph = graph
         self._use_graph = False
+        for name, p in getattr(graph, "params", {}).items():     # the weights of the file train like a cell's own
+            self.insert_param_to_cell(name, p, check_name_contain_dot=False)
         if params_init:
             for name, value in params_init.items():
                 graph.set_param(name, value)

@@ -227,3 +227,113 @@ def test_tuple_attribute_elements_use_the_repeated_fields():
     v = legacy.values.add()
     v.type, v.i = MP.A_INT64, 7                              # the single-value field inside a tuple is accepted too
     assert MP._read_attr(legacy) == (7,)
+
+
+class _Branchy(nn.Cell):
+    """A tensor-valued ``if`` and a ``while`` whose trip count depends on the data."""
+
+    def __init__(self):
+        super().__init__()
+        self.fc = nn.Dense(4, 4)
+
+    def construct(self, x, n):
+        from mindspore_b200.graph.control_flow import cond, while_loop
+        h = self.fc(x)
+        h = cond(h.sum() > 0, lambda v: ops.ReLU()(v) + 1.0, lambda v: v * 2.0, h)
+        i0 = ops.ZerosLike()(n)
+        _, out = while_loop(lambda i, v: i < n, lambda i, v: (i + 1, v + self.fc(v)), (i0, h))
+        return out
+
+
+def test_control_flow_exports_as_functions_and_runs_from_the_file(tmp_path):
+    from mindspore_b200.graph.mindir_proto import messages
+    net = _Branchy()
+    x = ms.Tensor(np.random.RandomState(0).randn(3, 4).astype(np.float32))
+    n = ms.Tensor(np.array(3, np.int64))
+    path = str(tmp_path / "branchy")
+    ms.export(net, x, n, file_name=path, file_format="MINDIR", container="proto")
+    model = messages()["ModelProto"]()
+    model.ParseFromString(open(path + ".mindir", "rb").read())
+    names = [f.name for f in model.functions]
+    assert any("cond_true" in f for f in names) and any("cond_false" in f for f in names)
+    assert any("while_header" in f for f in names) and any("while_step" in f for f in names)
+    kinds = {p.op_type for p in model.primitives}
+    assert {"Switch", "Partial"} <= kinds
+    graph = ms.load(path + ".mindir")
+    cell = nn.GraphCell(graph)
+    for xv, nv in ((x, 3), (-x, 0), (x * 0.1, 5)):                 # both branches, several trip counts
+        nt = ms.Tensor(np.array(nv, np.int64))
+        want = net(xv, nt)
+        got = cell(xv, nt)
+        assert np.allclose(got.detach().numpy(), want.detach().numpy(), atol=1e-5)
+    assert sorted(p.name for p in cell.get_parameters()) == sorted(p.name for p in net.get_parameters())
+    # long loops run in constant stack depth
+    long_n = ms.Tensor(np.array(3000, np.int64))
+    small = ms.Tensor(np.zeros((3, 4), np.float32))
+    assert cell(small, long_n).shape == (3, 4)
+
+
+def test_a_model_with_closures_in_the_reference_conventions(tmp_path):
+    """Built field by field the way the reference's exporter names things: a function reads a node of the main graph
+    (a free variable), is called by name (``REF::<function>``) and through a Switch of two function values."""
+    from mindspore_b200.graph.mindir_proto import _fill_attr, load_model_proto, messages
+    M = messages()
+    model = M["ModelProto"]()
+    model.ir_version, model.producer_name, model.mind_ir_version = "0.1.1", "MindSpore", 2
+
+    def prim(op):
+        pp = model.primitives.add()
+        pp.name, pp.op_type, pp.prim_type = "%s:%d" % (op, len(model.primitives)), op, 1
+        return "REF::" + pp.name
+
+    def node(gp, name, op_type, inputs):
+        nd = gp.node.add()
+        nd.name = name
+        nd.output.append(name)
+        nd.op_type = op_type
+        nd.input.extend(inputs)
+        return name
+
+    def const(gp, name, value):
+        nd = gp.node.add()
+        nd.name = name
+        nd.output.append(name)
+        nd.op_type = "Constant"
+        ap = nd.attribute.add()
+        ap.name = "value"
+        _fill_attr(ap, value)
+        return name
+
+    g = model.graph
+    g.name = "main_1"
+    for nm in ("x", "y"):
+        vi = g.input.add()
+        vi.name = nm
+        tp = vi.tensor.add()
+        tp.dims.extend([2])
+        tp.data_type = 1
+    s = node(g, "main_1:s:1", prim("Add"), ["x", "y"])                      # free variable of both functions
+    zero = const(g, "main_1:c:2", 0.0)
+    total = node(g, "main_1:t:3", prim("ReduceSum"), ["x"])
+    c = node(g, "main_1:c:4", prim("Greater"), [total, zero])
+    sw = node(g, "main_1:sw:5", prim("Switch"), [c, "then_2", "else_3"])
+    picked = node(g, "main_1:call:6", "REF::" + sw, [])
+    direct = node(g, "main_1:call:7", "REF::scale_4", [picked])
+    g.output.add().name = direct
+    f = model.functions.add()
+    f.name = "then_2"
+    f.output.add().name = node(f, "then_2:m:1", prim("Mul"), [s, "x"])
+    f = model.functions.add()
+    f.name = "else_3"
+    f.output.add().name = node(f, "else_3:m:1", prim("Sub"), [s, "x"])
+    f = model.functions.add()
+    f.name = "scale_4"
+    f.input.add().name = "scale_4:v"
+    two = const(f, "scale_4:c:1", 2.0)
+    f.output.add().name = node(f, "scale_4:m:2", prim("Mul"), ["scale_4:v", two])
+
+    cell = nn.GraphCell(load_model_proto(model.SerializeToString()))
+    x = ms.Tensor(np.array([1.0, 2.0], np.float32))
+    y = ms.Tensor(np.array([0.5, 0.5], np.float32))
+    assert np.allclose(cell(x, y).numpy(), ((x + y) * x * 2).numpy())
+    assert np.allclose(cell(-x, y).numpy(), (((-x) + y) - (-x)) .numpy() * 2)
