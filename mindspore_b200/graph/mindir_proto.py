@@ -79,17 +79,15 @@ _SCHEMA = {
 _messages = None
 
 
-def messages():
-    """{message name: class} built from ``_SCHEMA`` (package ``mind_ir``)."""
-    global _messages
-    if _messages is not None:
-        return _messages
+def build_messages(schema, package, file_name):
+    """{message name: class} for a schema given as {message: [(field, number, kind)]}; ``kind`` is a scalar type, the
+    name of another message of the schema, or either followed by ``*`` for a repeated field."""
     from google.protobuf import descriptor_pb2, descriptor_pool, message_factory
     fdp = descriptor_pb2.FileDescriptorProto()
-    fdp.name = "mindspore_b200/mind_ir.proto"
-    fdp.package = "mind_ir"
+    fdp.name = file_name
+    fdp.package = package
     fdp.syntax = "proto2"
-    for mname, fields in _SCHEMA.items():
+    for mname, fields in schema.items():
         m = fdp.message_type.add()
         m.name = mname
         for fname, number, kind in fields:
@@ -102,17 +100,26 @@ def messages():
                 f.type = _T[kind]
             else:
                 f.type = _T["msg"]
-                f.type_name = ".mind_ir." + kind
+                f.type_name = ".%s.%s" % (package, kind)
     pool = descriptor_pool.DescriptorPool()
-    fd = pool.Add(fdp) if hasattr(pool, "Add") and not hasattr(pool, "AddSerializedFile") else \
+    if hasattr(pool, "AddSerializedFile"):
         pool.AddSerializedFile(fdp.SerializeToString())
+    else:
+        pool.Add(fdp)
     get = getattr(message_factory, "GetMessageClass", None)
     out = {}
-    for mname in _SCHEMA:
-        desc = pool.FindMessageTypeByName("mind_ir." + mname)
+    for mname in schema:
+        desc = pool.FindMessageTypeByName("%s.%s" % (package, mname))
         out[mname] = get(desc) if get else message_factory.MessageFactory(pool).GetPrototype(desc)
-    _messages = out
     return out
+
+
+def messages():
+    """{message name: class} built from ``_SCHEMA`` (package ``mind_ir``)."""
+    global _messages
+    if _messages is None:
+        _messages = build_messages(_SCHEMA, "mind_ir", "mindspore_b200/mind_ir.proto")
+    return _messages
 
 
 # AttributeProto.AttributeType / TensorProto.DataType values used here
@@ -453,6 +460,32 @@ def _lowerings():
         T.sum: reduce("ReduceSum"), F.embedding: embedding, torch.embedding: embedding,
     }
     table[T.detach] = table[torch.detach] = unary("StopGradient")
+
+    def getitem(emit, a, k, n):
+        """``x[i, 2:5, ::2]`` with ints and slices of positive step -> StridedSlice (shrink mask for the ints)."""
+        index = a[1] if isinstance(a[1], tuple) else (a[1],)
+        shape = tuple(int(d) for d in a[0].meta["shape"])
+        if len(index) > len(shape) or not all(isinstance(i, (int, slice)) for i in index):
+            raise MindIRError("node %s indexes a tensor with %r; ints and slices are lowered" % (n.name, a[1]))
+        begin, end, strides, shrink = [], [], [], 0
+        for axis, i in enumerate(index):
+            if isinstance(i, int):
+                i = i % shape[axis]
+                begin.append(i)
+                end.append(i + 1)
+                strides.append(1)
+                shrink |= 1 << axis
+                continue
+            if not all(isinstance(v, (int, type(None))) for v in (i.start, i.stop, i.step)) or (i.step or 1) <= 0:
+                raise MindIRError("node %s slices with %r; constant slices of positive step are lowered"
+                                  % (n.name, i))
+            lo, hi, st = i.indices(shape[axis])
+            begin.append(lo)
+            end.append(hi)
+            strides.append(st)
+        attrs = {"begin_mask": 0, "end_mask": 0, "ellipsis_mask": 0, "new_axis_mask": 0, "shrink_axis_mask": shrink}
+        return emit("StridedSlice", attrs, [a[0], tuple(begin), tuple(end), tuple(strides)])
+    table[T.__getitem__] = getitem
     for short, dunder, prim_name in (("gt", "__gt__", "Greater"), ("lt", "__lt__", "Less"),
                                      ("ge", "__ge__", "GreaterEqual"), ("le", "__le__", "LessEqual"),
                                      ("eq", "__eq__", "Equal"), ("ne", "__ne__", "NotEqual")):

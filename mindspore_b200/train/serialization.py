@@ -559,12 +559,12 @@ def export(net, *inputs, file_name, file_format, **kwargs):
     """Exports ``net`` traced on ``inputs``.  MINDIR: one ``<file_name>.mindir`` file holding the forward graph and the
     weights, in the reference's protobuf layout (``graph/mindir_proto.py``) when every node is a primitive, else in
     this framework's own container (``graph/mindir.py``; ``container="native"`` forces it, ``container="proto"``
-    insists on protobuf); ``enc_key`` / ``enc_mode`` encrypt it like a checkpoint.  ONNX and AIR target other
-    runtimes and are not produced."""
+    insists on protobuf); ``enc_key`` / ``enc_mode`` encrypt it like a checkpoint.  ONNX: ``<file_name>.onnx`` at opset
+    17 (``graph/onnx_proto.py``).  AIR targets the Ascend graph engine and is not produced."""
     if file_format not in ("MINDIR", "ONNX", "AIR"):
         raise ValueError("For 'export', 'file_format' must be one of AIR, ONNX, MINDIR, but got %r" % file_format)
-    if file_format != "MINDIR":
-        raise NotImplementedError("only MINDIR export is available in this build")
+    if file_format == "AIR":
+        raise NotImplementedError("AIR files feed the Ascend graph engine and are not produced by this build")
     from ..graph import jit as _jit
     from ..graph import mindir
     was_training = getattr(net, "training", False)
@@ -573,6 +573,9 @@ def export(net, *inputs, file_name, file_format, **kwargs):
         g = _jit.trace_cell(net, inputs)
     finally:
         net.set_train(was_training)
+    if file_format == "ONNX":
+        from ..graph import onnx_proto
+        return onnx_proto.save_onnx(g, file_name if file_name.endswith(".onnx") else file_name + ".onnx")
     path = file_name if file_name.endswith(".mindir") else file_name + ".mindir"
     container = kwargs.get("container", "auto")
     if container not in ("auto", "proto", "native"):
