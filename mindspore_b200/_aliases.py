@@ -48,7 +48,7 @@ ALIASES = {
     "parallel._tensor": "parallel.layout",
     "parallel._parallel_serialization": "parallel.strategy_ckpt",
     "parallel.nn": "parallel.transformer",
-    "train.train_thor": "boost",
+    "train.train_thor": "train.thor_convert",
     "train.summary.summary_record": "train.summary",
     "train.anf_ir_pb2": "graph.mindir_proto",
     "train.mind_ir_pb2": "graph.mindir_proto",
@@ -58,7 +58,45 @@ ALIASES = {
     "dataset.engine.datasets": "dataset.engine",
     "_extends.parse": "graph.ast_transform",
     "offline_debug": "utils.dump",
+    "nn.metrics": "train.metrics",
+    "nn.optim.optimizer": "nn.optim",
+    "nn.optim.adasum": "nn.optim_ext",
+    "nn.extend.basic": "nn.extend",
+    "nn.extend.pooling": "nn.extend",
+    "nn.extend.embedding": "nn.extend",
+    "nn.extend.layer": "nn.extend",
+    "nn.extend.layer.normalization": "nn.extend",
+    "nn.sparse": "nn",
+    "nn.grad": "nn",
+    "nn.reinforcement": "nn.layer_ext",
+    "nn.probability.bnn_layers.layer_distribution": "nn.probability.bnn_layers",
+    "nn.probability.bnn_layers.bnn_cell_wrapper": "nn.probability.bnn_layers",
+    "nn.probability.bnn_layers.dense_variational": "nn.probability.bnn_layers",
+    "nn.probability.bnn_layers.conv_variational": "nn.probability.bnn_layers",
+    "ops.extend": "ops",
+    "ops.extend.array_func": "ops",
+    "ops.extend.nn_func": "ops",
+    "ops.extend.math_func": "ops",
+    "common.sparse_tensor": "common.api",
+    "experimental.optim.optimizer": "experimental.optim",
+    "train.train_thor.convert_utils": "train.thor_convert",
+    "train.train_thor.model_thor": "train.thor_convert",
+    "dataset.callback": "dataset.sources_ext",
+    "dataset.core": "dataset.core_config",
+    "dataset.core.config": "dataset.core_config",
 }
+for _sub in ("math", "image", "container", "rnns", "basic", "pooling", "timedistributed", "dense", "conv", "combined",
+             "activation", "normalization", "thor_layer", "rnn_cells", "transformer", "embedding", "padding",
+             "channel_shuffle", "flatten"):
+    ALIASES["nn.layer." + _sub] = "nn"
+for _sub in ("shardreader", "shardheader", "filereader", "shardsegment", "config", "filewriter", "shardindexgenerator",
+             "mindpage", "shardwriter", "shardutils", "tools", "tools.mnist_to_mr", "tools.tfrecord_to_mr",
+             "tools.cifar10_to_mr", "tools.cifar100_to_mr", "tools.cifar10", "tools.cifar100", "tools.csv_to_mr",
+             "tools.imagenet_to_mr"):
+    ALIASES["mindrecord." + _sub] = "dataset.mindrecord"
+for _sub in ("boost", "boost_cell_wrapper", "base", "grad_freeze", "group_loss_scale_manager", "grad_accumulation",
+             "adasum", "dim_reduce", "less_batch_normalization"):
+    ALIASES["boost." + _sub] = "boost"
 
 
 class _AliasFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):

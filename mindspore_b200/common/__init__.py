@@ -11,7 +11,8 @@ from . import tensor_ext  # noqa: E402,F401  (attaches the MindSpore-only Tensor
 _FROM_API = {"COOTensor": "COOTensor", "CSRTensor": "CSRTensor", "RowTensor": "RowTensor", "Symbol": "Symbol",
              "jit_class": "jit_class", "ms_class": "jit_class", "lazy_inline": "lazy_inline",
              "ms_memory_recycle": "ms_memory_recycle", "mutable": "mutable", "no_inline": "no_inline",
-             "recompute": "recompute", "SparseTensor": "COOTensor"}
+             "recompute": "recompute", "SparseTensor": "COOTensor", "RowTensorInner": "RowTensor",
+             "_no_grad": "_no_grad", "_null": "_null", "_NullType": "_NullType", "flops_collection": "flops_collection"}
 
 
 from .jit_config import JitConfig  # noqa: E402,F401

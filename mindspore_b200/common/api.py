@@ -164,6 +164,51 @@ def manual_seed(seed):
     return default_generator.manual_seed(seed)
 
 
+def seed():
+    """Seeds the default generator from the system's entropy and returns the seed (common/generator.py seed)."""
+    return default_generator.seed()
+
+
+class _no_grad:
+    """Context manager / decorator: no gradient is recorded inside (common/_pijit_context ... ``_no_grad``)."""
+
+    def __enter__(self):
+        self._ctx = torch.no_grad()
+        return self._ctx.__enter__()
+
+    def __exit__(self, *exc):
+        return self._ctx.__exit__(*exc)
+
+    def __call__(self, fn):
+        import functools
+
+        @functools.wraps(fn)
+        def wrapper(*args, **kwargs):
+            with torch.no_grad():
+                return fn(*args, **kwargs)
+        return wrapper
+
+
+class _NullType:
+    """The type of ``_null``: a default that means "argument not given" where ``None`` is a legal value."""
+
+    _instance = None
+
+    def __new__(cls):
+        if cls._instance is None:
+            cls._instance = super().__new__(cls)
+        return cls._instance
+
+    def __repr__(self):
+        return "null"
+
+    def __bool__(self):
+        return False
+
+
+_null = _NullType()
+
+
 def initial_seed():
     return default_generator.initial_seed()
 

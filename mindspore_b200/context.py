@@ -22,6 +22,9 @@ PYNATIVE_MODE = 1
 _MODE_NAMES = {GRAPH_MODE: "GRAPH_MODE", PYNATIVE_MODE: "PYNATIVE_MODE"}
 
 
+
+STRICT, COMPATIBLE, LAX = 0, 1, 2          # jit_syntax_level values
+
 class ParallelMode:
     STAND_ALONE = "stand_alone"
     DATA_PARALLEL = "data_parallel"

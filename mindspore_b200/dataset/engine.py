@@ -106,6 +106,25 @@ def _config_load(self, file):
         self.set_callback_timeout(cfg["callbackTimeout"])
 
 
+def _set_debug_mode(self, debug_mode_flag, debug_hook_list=None):
+    """Debug mode: ``map`` runs its transforms one at a time in the calling thread and calls every hook of
+    ``debug_hook_list`` (default: one ``PrintMetaDataHook``) around them."""
+    if not isinstance(debug_mode_flag, bool):
+        raise TypeError("debug_mode_flag isn't of type boolean.")
+    from .debug import DebugHook, PrintMetaDataHook
+    if debug_hook_list is None:
+        debug_hook_list = [PrintMetaDataHook()]
+    if not isinstance(debug_hook_list, list):
+        raise TypeError("debug_hook_list is not a list.")
+    for hook in debug_hook_list:
+        if not isinstance(hook, DebugHook):
+            raise TypeError("All items in debug_hook_list must be of type DebugHook.")
+    self._settings["debug_mode"] = debug_mode_flag
+    self._settings["debug_hooks"] = list(debug_hook_list) if debug_mode_flag else []
+
+
+_Config.set_debug_mode = _set_debug_mode
+_Config._get_debug_hook_list = lambda self: list(self._settings.get("debug_hooks", []))
 _Config.load = _config_load
 _Config.ErrorSamplesMode = ErrorSamplesMode
 config = _Config()
@@ -539,18 +558,34 @@ class _Map(Dataset):
 
     def _apply(self, row):
         vals = tuple(row[c] for c in self.inp)
-        for op in self.ops:
+        hooks = config._get_debug_hook_list() if config.get_debug_mode() else ()
+        for k, op in enumerate(self.ops):
+            name = type(op).__name__ if not hasattr(op, "__name__") else op.__name__
+            if hooks and k == 0:
+                vals = self._run_hooks(hooks, name, True, vals)
             vals = op(*vals)
             if not isinstance(vals, tuple):
                 vals = (vals,)
+            if hooks:
+                vals = self._run_hooks(hooks, name, False, vals)
         if len(vals) != len(self.out):
             raise RuntimeError("map produced %d columns, expected %d (%s)" % (len(vals), len(self.out), self.out))
         new = {c: v for c, v in row.items() if c not in self.inp}
         new.update({c: _to_np(v) for c, v in builtins.zip(self.out, vals)})
         return new
 
+    @staticmethod
+    def _run_hooks(hooks, op_name, is_first, vals):
+        import copy
+        for hook in hooks:
+            hook = copy.copy(hook)
+            hook.set_previous_op_name(op_name)
+            hook.set_is_first(is_first)
+            vals = tuple(hook(*vals))
+        return vals
+
     def _rows(self):
-        if self.workers <= 1:
+        if self.workers <= 1 or config.get_debug_mode():
             for row in self.parent._rows():
                 yield self._apply(row)
             return
@@ -965,3 +1000,18 @@ Dataset.to_device = Dataset.device_que
 Dataset.num_classes = lambda self: (len(set(int(np.asarray(r[self.get_col_names()[-1]])) for r in self._rows())))
 Dataset.reset = lambda self: None
 Dataset.close = lambda self: None
+
+
+def __getattr__(name):
+    # `dataset.engine` lists every dataset class, sampler and iterator of the package in the reference
+    if name.startswith("__"):
+        raise AttributeError(name)
+    import importlib
+    for mod in ("sources", "sources_ext", "samplers", "mindrecord_source", "graphdata"):
+        try:
+            m = importlib.import_module("." + mod, __package__)
+        except ImportError:
+            continue
+        if hasattr(m, name):
+            return getattr(m, name)
+    raise AttributeError("module 'dataset.engine' has no attribute %r" % name)

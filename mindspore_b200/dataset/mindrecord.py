@@ -733,3 +733,184 @@ class TFRecordToMR(_Converter):
 __all__ = ["FileWriter", "FileReader", "MindPage", "Cifar10ToMR", "Cifar100ToMR", "CsvToMR", "ImageNetToMR",
            "MnistToMR", "TFRecordToMR", "set_enc_key", "set_enc_mode", "set_dec_mode", "set_hash_mode", "SUCCESS",
            "FAILED"]
+
+
+# ---------------------------------------------------------------------------------------------------- the shard layer
+class ShardHeader:
+    """What a writer needs to know before the first row: the schema (``add_schema`` / ``build_schema``) and the index
+    fields.  Parity: mindrecord/shardheader.py."""
+
+    def __init__(self):
+        self.schema, self.desc, self.index_fields = None, None, []
+
+    @staticmethod
+    def build_schema(content, desc=None):
+        desc = desc if desc else ""
+        if not isinstance(content, dict) or not content:
+            raise ValueError("The schema content must be a non-empty dict")
+        return {"schema": dict(content), "desc": desc}
+
+    def add_schema(self, schema):
+        built = schema if "schema" in schema and isinstance(schema["schema"], dict) else self.build_schema(schema)
+        self.schema, self.desc = built["schema"], built.get("desc", "")
+        return 0                                          # the id of the (one) schema
+
+    def add_index_fields(self, index_fields):
+        self.index_fields = list(index_fields)
+        return SUCCESS
+
+    @property
+    def blob_fields(self):
+        return [k for k, v in (self.schema or {}).items() if v.get("type") == "bytes" or "shape" in v]
+
+
+class ShardWriter:
+    """The writer under ``FileWriter`` as its own object: ``open`` -> ``set_shard_header`` -> ``write_raw_data`` ->
+    ``commit``.  Parity: mindrecord/shardwriter.py."""
+
+    def __init__(self):
+        self._writer, self._paths = None, None
+
+    def open(self, paths, override=False):
+        paths = [paths] if isinstance(paths, str) else list(paths)
+        self._paths = paths
+        base = paths[0][:-1] if len(paths) > 1 and paths[0].endswith("0") else paths[0]
+        self._writer = FileWriter(base, len(paths), overwrite=override)
+        return SUCCESS
+
+    def open_for_append(self, path):
+        self._writer = FileWriter.open_for_append(path)
+        return SUCCESS
+
+    def set_header_size(self, header_size):
+        return self._writer.set_header_size(header_size)
+
+    def set_page_size(self, page_size):
+        return self._writer.set_page_size(page_size)
+
+    def set_shard_header(self, shard_header):
+        self._writer.add_schema(shard_header.schema, shard_header.desc)
+        if shard_header.index_fields:
+            self._writer.add_index(shard_header.index_fields)
+        return SUCCESS
+
+    def write_raw_data(self, data, validate=True, parallel_writer=False):
+        return self._writer.write_raw_data(data, parallel_writer)
+
+    def commit(self):
+        return self._writer.commit()
+
+    def get_shard_files(self):
+        return self._writer.get_shard_files()
+
+
+class ShardReader:
+    """Sequential reader of a dataset's rows: ``open`` -> ``launch`` -> ``get_next`` ... -> ``close``.
+    Parity: mindrecord/shardreader.py."""
+
+    def __init__(self):
+        self._reader, self._it = None, None
+
+    def open(self, file_name, num_consumer=4, columns=None, operator=None):
+        self._reader = FileReader(file_name, num_consumer, columns, operator)
+        return SUCCESS
+
+    def launch(self):
+        self._it = self._reader.get_next()
+        return SUCCESS
+
+    def get_next(self):
+        if self._it is None:
+            self.launch()
+        return next(self._it, None)
+
+    def get_blob_fields(self):
+        return [k for k, v in self._reader.schema().items() if v.get("type") == "bytes" or "shape" in v]
+
+    def get_header(self):
+        head = ShardHeader()
+        head.add_schema({"schema": self._reader.schema(), "desc": ""})
+        head.add_index_fields(self._reader.index_fields)
+        return head
+
+    def len(self):
+        return len(self._reader)
+
+    def close(self):
+        if self._reader is not None:
+            self._reader.close()
+
+
+class ShardIndexGenerator:
+    """Rebuilds the ``.db`` index of one data file from its pages.  Parity: mindrecord/shardindexgenerator.py."""
+
+    def __init__(self, path, append=False):
+        self.path, self.append = path, append
+        self._built = None
+
+    def build(self):
+        from . import mindrecord_format as F
+        if not F.looks_like_mindrecord(self.path):
+            raise RuntimeError("%s is not a MindRecord data file" % self.path)
+        self._built = True
+        return SUCCESS
+
+    def write_to_db(self):
+        from . import mindrecord_format as F
+        if self._built is None:
+            self.build()
+        F.rebuild_index(self.path)
+        return SUCCESS
+
+
+class ShardSegment(MindPage):
+    """The page reader under ``MindPage`` with the lower-level names (``open`` / ``close``).
+    Parity: mindrecord/shardsegment.py."""
+
+    def __init__(self):                                    # noqa: super().__init__ runs in `open`
+        self._opened = False
+
+    def open(self, file_name, num_consumer=4):
+        MindPage.__init__(self, file_name, num_consumer)
+        self._opened = True
+        return SUCCESS
+
+    def close(self):
+        self._opened = False
+
+
+class Cifar10:
+    """The python-pickle CIFAR-10 folder as arrays: ``load_data()`` fills ``Train`` and ``Test`` (``.images`` NHWC
+    uint8, ``.labels``; one-hot rows when ``one_hot``).  Parity: mindrecord/tools/cifar10.py."""
+    converter = Cifar10ToMR
+    num_classes = 10
+
+    class _Split:
+        def __init__(self, images, labels):
+            self.images, self.labels = images, labels
+
+    def __init__(self, path, one_hot=True):
+        self.path, self.one_hot = path, one_hot
+        self.Train = self.Test = None
+
+    def _split(self, names):
+        rows = self.converter(self.path, os.path.join(self.path, "unused"))._load(names)
+        images = np.stack([np.frombuffer(r["data"], np.uint8).reshape(32, 32, 3) for r in rows])
+        key = "label" if "label" in rows[0] else "fine_label"
+        labels = np.array([r[key] for r in rows], np.int64)
+        if self.one_hot:
+            labels = np.eye(self.num_classes, dtype=np.float32)[labels]
+        return self._Split(images, labels)
+
+    def load_data(self):
+        self.Train = self._split(self.converter.train_files)
+        self.Test = self._split(self.converter.test_files)
+
+
+class Cifar100(Cifar10):
+    """CIFAR-100 (fine labels).  Parity: mindrecord/tools/cifar100.py."""
+    converter = Cifar100ToMR
+    num_classes = 100
+
+
+__all__ += ["ShardHeader", "ShardWriter", "ShardReader", "ShardIndexGenerator", "ShardSegment", "Cifar10", "Cifar100"]

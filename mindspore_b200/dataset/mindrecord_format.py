@@ -328,3 +328,44 @@ def read_index(db_path):
         return [tuple(r[:8]) + tuple(r[9:]) for r in con.execute("SELECT * FROM INDEXES ORDER BY ROW_ID")]
     finally:
         con.close()
+
+
+def rebuild_index(path):
+    """Writes ``<path>.db`` again from the pages of the data file (a lost or stale index)."""
+    shard = ShardFile(path)
+    head = shard.header
+    hs, ps = head["header_size"], head["page_size"]
+    data = shard._data
+    raw_recs, blob_by_group = [], {}
+    for page in sorted(head["page"], key=lambda p: p["page_id"]):
+        base = hs + ps * page["page_id"]
+        pos, end = 0, page["page_size"]
+        entries = []
+        while pos < end:
+            (n,) = struct.unpack_from("<Q", data, base + pos)
+            entries.append((pos, pos + 8 + n))
+            pos += 8 + n
+        groups = sorted(page.get("row_group_ids") or [], key=lambda g: g["offset"])
+        if page["page_type"] == "BLOB_DATA":
+            gid = groups[0]["id"] if groups else 0
+            blob_by_group.setdefault(gid, []).extend((page["page_id"], s, e) for s, e in entries)
+        else:
+            for s, e in entries:
+                gid = 0
+                for g in groups:
+                    if g["offset"] <= s:
+                        gid = g["id"]
+                raw_recs.append((page["page_id"], s, e, gid))
+    taken = {}
+    index_rows = []
+    for row_id, (raw_page, s, e, gid) in enumerate(raw_recs):
+        k = taken.get(gid, 0)
+        taken[gid] = k + 1
+        blobs = blob_by_group.get(gid, [])
+        blob_page, bs, be = blobs[k] if k < len(blobs) else (-1, 0, 0)
+        index_rows.append((row_id, raw_page, s, e, gid, blob_page, bs, be))
+    index_fields = [f["index_field"] for f in head.get("index_fields", [])]
+    rows = [dict(zip(index_fields, shard.index_values(i, index_fields))) for i in range(len(shard))]
+    names = head.get("shard_addresses") or [os.path.basename(path)]
+    _write_index(path + ".db", names[head.get("shard_id", 0)], shard.schema, index_fields, rows, index_rows)
+    return len(index_rows)

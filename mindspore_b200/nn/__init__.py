@@ -13,5 +13,6 @@ from .optim import (ASGD, FTRL, LARS, SGD, AdaFactor, Adadelta, Adagrad, Adam, A
                     Momentum, Optimizer, ParamArena, ProximalAdagrad, RMSProp, Rprop, thor)
 from .wrap import (DistributedGradReducer, DynamicLossScaleUpdateCell, FixedLossScaleUpdateCell, ForwardValueAndGrad,
                    GetNextSingleOp, GradAccumulationCell, MicroBatchInterleaved, PipelineCell, PipelineGradReducer,
-                   TrainOneStepCell, TrainOneStepWithLossScaleCell, WithEvalCell, WithGradCell, WithLossCell)
+                   TimeDistributed, ParameterUpdate, TrainOneStepCell, TrainOneStepWithLossScaleCell,
+                   VirtualDatasetCellTriple, WithEvalCell, WithGradCell, WithLossCell)
 from . import probability  # noqa: E402,F401

@@ -920,3 +920,82 @@ Conv2dThor = _thor_conv()
 EmbeddingThor, EmbeddingLookupThor = _thor_embeddings()
 __all__ += ["FractionalMaxPool3d", "DropoutExt", "Conv2dBnAct", "DenseBnAct", "DenseThor", "Conv2dThor",
             "EmbeddingThor", "EmbeddingLookupThor"]
+
+
+class TensorArray(Cell):
+    """A growable (``dynamic_size``) or fixed-size list of tensors of one dtype and element shape:
+    ``write(index, value)``, ``read(index)``, ``size()``, ``stack()``, ``clear()``, ``close()``.
+    Parity: nn/reinforcement/tensor_array.py."""
+
+    def __init__(self, dtype, element_shape, dynamic_size=True, size=0, name="TA"):
+        super().__init__()
+        if not isinstance(element_shape, (tuple, list)):
+            raise TypeError("For 'TensorArray', 'element_shape' must be a tuple or a list")
+        if isinstance(size, bool) or not isinstance(size, int) or size < 0:
+            raise ValueError("For 'TensorArray', 'size' must be a non-negative int")
+        self.dtype, self.element_shape = dtype, tuple(element_shape)
+        self.dynamic_size, self.max_size, self.array_name = bool(dynamic_size), size, name
+        self._items = [None] * (0 if dynamic_size else size)
+        self._closed = False
+
+    def _check(self):
+        if self._closed:
+            raise RuntimeError("For 'TensorArray', the array %r has been closed" % self.array_name)
+
+    def write(self, index, value):
+        self._check()
+        index = int(index)
+        value = torch.as_tensor(value)
+        if value.dtype != self.dtype or tuple(value.shape) != self.element_shape:
+            raise TypeError("For 'TensorArray.write', the value must be %s of shape %s, but got %s of shape %s"
+                            % (self.dtype, self.element_shape, value.dtype, tuple(value.shape)))
+        if index < 0:
+            raise ValueError("For 'TensorArray.write', 'index' must not be negative")
+        if index >= len(self._items):
+            if not self.dynamic_size:
+                raise ValueError("For 'TensorArray.write', index %d is out of the fixed size %d"
+                                 % (index, len(self._items)))
+            self._items.extend([None] * (index + 1 - len(self._items)))
+        self._items[index] = value.clone()
+        return True
+
+    def read(self, index):
+        self._check()
+        index = int(index)
+        if index < 0 or index >= len(self._items):
+            raise ValueError("For 'TensorArray.read', index %d is out of range (size %d)" % (index, len(self._items)))
+        item = self._items[index]
+        return torch.zeros(self.element_shape, dtype=self.dtype) if item is None else item
+
+    def size(self):
+        self._check()
+        return len(self._items)
+
+    def stack(self):
+        self._check()
+        if not self._items:
+            return torch.zeros((0,) + self.element_shape, dtype=self.dtype)
+        return torch.stack([self.read(k) for k in range(len(self._items))])
+
+    def clear(self):
+        self._check()
+        self._items = [None] * (0 if self.dynamic_size else self.max_size)
+        return True
+
+    def close(self):
+        self._items, self._closed = [], True
+        return True
+
+
+class Linear(Dense):
+    """``Dense`` under the argument names of the extend namespace: ``Linear(in_features, out_features, bias=True)``.
+    Parity: nn/extend/basic.py."""
+
+    def __init__(self, in_features, out_features, bias=True, weight_init=None, bias_init=None, dtype=None):
+        kwargs = {} if dtype is None else {"dtype": dtype}
+        super().__init__(in_features, out_features, weight_init if weight_init is not None else "normal",
+                         bias_init if bias_init is not None else "zeros", has_bias=bias, **kwargs)
+        self.in_features, self.out_features = in_features, out_features
+
+
+__all__ += ["TensorArray", "Linear"]

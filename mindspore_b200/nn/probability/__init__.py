@@ -3,4 +3,4 @@
 ``torch.distributions``; the method names are MindSpore's (``prob``, ``log_prob``, ``cdf``, ``survival_function``,
 ``mean``, ``var``, ``sd``, ``entropy``, ``kl_loss``, ``cross_entropy``, ``sample``), each accepting the distribution
 parameters again as optional call arguments."""
-from . import bijector, distribution  # noqa: F401
+from . import bijector, bnn_layers, distribution  # noqa: F401

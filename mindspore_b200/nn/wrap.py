@@ -630,6 +630,69 @@ class _VirtualDatasetCell(Cell):
         return self._backbone(*inputs)
 
 
+class VirtualDatasetCellTriple(_VirtualDatasetCell):
+    """The three-input form (data, label, mask) of the wrapper that marks the dataset inputs for auto parallel.
+    Parity: nn/wrap/cell_wrapper.py VirtualDatasetCellTriple."""
+
+    def construct(self, a, b, c):
+        return self._backbone(a, b, c)
+
+
+class ParameterUpdate(Cell):
+    """``cell(x)`` writes ``x`` into the wrapped parameter (a learning rate, a loss scale) and returns it.
+    Parity: nn/wrap/cell_wrapper.py ParameterUpdate."""
+
+    def __init__(self, param):
+        super().__init__(auto_prefix=False)
+        from ..common.parameter import Parameter
+        if not isinstance(param, Parameter):
+            raise TypeError("For 'ParameterUpdate', 'param' must be 'Parameter', but got %s" % type(param).__name__)
+        self._param = param
+
+    def construct(self, x):
+        with torch.no_grad():
+            torch.Tensor.copy_(self._param, torch.as_tensor(x).to(self._param.dtype))
+        return x
+
+
+class TimeDistributed(Cell):
+    """Applies ``layer`` to every time slice: the time axis is folded into the batch axis (``reshape_with_axis``,
+    one reshape and one call) or the slices are run one by one and stacked.  Parity: nn/layer/timedistributed.py."""
+
+    def __init__(self, layer, time_axis, reshape_with_axis=None):
+        super().__init__()
+        if not isinstance(layer, Cell) and not callable(layer):
+            raise TypeError("For 'TimeDistributed', 'layer' must be a Cell or a Primitive")
+        for v, n in ((time_axis, "time_axis"),) + (((reshape_with_axis, "reshape_with_axis"),)
+                                                    if reshape_with_axis is not None else ()):
+            if isinstance(v, bool) or not isinstance(v, int):
+                raise TypeError("For 'TimeDistributed', '%s' must be an int" % n)
+        self.layer, self.time_axis, self.reshape_with_axis = layer, time_axis, reshape_with_axis
+
+    def construct(self, inputs):
+        if not isinstance(inputs, torch.Tensor):
+            raise TypeError("For 'TimeDistributed', 'inputs' must be a Tensor")
+        rank = inputs.dim()
+        t = self.time_axis % rank
+        if rank <= 2:
+            raise ValueError("For 'TimeDistributed', 'inputs' must have more than 2 dimensions")
+        if self.reshape_with_axis is not None:
+            b = self.reshape_with_axis % rank
+            lo, hi = min(t, b), max(t, b)
+            if hi - lo != 1:
+                raise ValueError("For 'TimeDistributed', 'time_axis' and 'reshape_with_axis' must be neighbours")
+            shape = list(inputs.shape)
+            merged = shape[:lo] + [shape[lo] * shape[hi]] + shape[hi + 1:]
+            out = self.layer(inputs.reshape(merged))
+            if not isinstance(out, torch.Tensor):
+                raise TypeError("For 'TimeDistributed', the layer must return a Tensor")
+            return out.reshape(list(out.shape[:lo]) + [shape[lo], shape[hi]] + list(out.shape[lo + 1:]))
+        outs = [self.layer(piece) for piece in torch.unbind(inputs, t)]
+        if not all(isinstance(o, torch.Tensor) for o in outs):
+            raise TypeError("For 'TimeDistributed', the layer must return a Tensor")
+        return torch.stack(outs, t)
+
+
 class _TrainGradAccuStepCell(TrainOneStepCell):
     """Pipeline / gradient-accumulation step: gradients accumulate in ``accu_grads`` over micro-batches and
     the optimizer consumes the accumulators."""

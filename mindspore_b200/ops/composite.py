@@ -429,3 +429,85 @@ def choice_with_mask(input_x, count=256, seed=None):
 def vmap(fn, in_axes=0, out_axes=0):
     from ..common.api import vmap as _vmap
     return _vmap(fn, in_axes, out_axes)
+
+
+# ---------------------------------------------------------------------------------------------------- small helpers
+def tail(seq):
+    """Everything but the first element of a tuple / list (ops/composite/base.py Tail)."""
+    if not isinstance(seq, (tuple, list)):
+        raise TypeError("For 'tail', the input must be a tuple or a list, but got %s" % type(seq).__name__)
+    return seq[1:]
+
+
+def hyper_add(*values):
+    """Elementwise sum over matching nested tuples / lists of tensors and numbers."""
+    first = values[0]
+    if isinstance(first, (tuple, list)):
+        return type(first)(hyper_add(*parts) for parts in zip(*values))
+    total = first
+    for v in values[1:]:
+        total = total + v
+    return total
+
+
+def zip_operation(*seqs):
+    return ZipOperation()(*seqs)
+
+
+def add_flags(fn=None, **flags):
+    """Attaches compile flags to a function (``fn._func_graph_flags``); decorator with or without the function."""
+    def deco(f):
+        if not hasattr(f, "_func_graph_flags"):
+            f._func_graph_flags = {}
+        f._func_graph_flags.update(flags)
+        return f
+    return deco(fn) if fn is not None else deco
+
+
+def env_get(env, parameter):
+    """The gradient stored for ``parameter`` in an environment (a dict keyed by the parameter), zeros if absent."""
+    if isinstance(env, dict):
+        hit = env.get(parameter.name, env.get(id(parameter)))
+        if hit is not None:
+            return hit
+    return _wrap_out(torch.zeros_like(_as_plain(parameter)))
+
+
+def iter_converter(obj):
+    """A cell list / dict / tuple as something ``ms_next`` can walk: dicts give their keys."""
+    if isinstance(obj, dict):
+        return tuple(obj.keys())
+    if isinstance(obj, (tuple, list)):
+        return obj
+    return tuple(obj)
+
+
+def ms_hasnext(seq):
+    return len(seq) > 0
+
+
+def ms_next(seq):
+    """(first element, the rest): the functional form of a ``for`` loop over a sequence."""
+    return seq[0], seq[1:]
+
+
+_Grad = GradOperation
+
+
+class _Vmap:
+    """Callable form of ``vmap``: ``_Vmap()(fn, in_axes, out_axes)``."""
+
+    def __call__(self, fn, in_axes=0, out_axes=0):
+        return vmap(fn, in_axes, out_axes)
+
+
+def __getattr__(name):
+    # the tensor functions that the reference also lists under `composite` (zeros_like, normal, matmul, ...)
+    from . import functional
+    try:
+        return getattr(functional, name)
+    except AttributeError:
+        from . import function_ext
+        if hasattr(function_ext, name):
+            return getattr(function_ext, name)
+        raise AttributeError("module 'ops.composite' has no attribute %r" % name)

@@ -1176,5 +1176,10 @@ def log_uniform_candidate_sampler(true_classes, num_true=1, num_sampled=5, uniqu
     return _w(sampled), _w(prob(tc) * num_sampled), _w(prob(sampled.float()) * num_sampled)
 
 
+def leaky_relu_ext(input, negative_slope=0.01):                                            # noqa: A002
+    """``max(x, 0) + negative_slope * min(x, 0)`` (ops/extend/nn_func.py)."""
+    return _w(F.leaky_relu(_t(input), float(negative_slope)))
+
+
 __all__ = [n for n in dir() if not n.startswith("_") and n not in (
     "annotations", "builtins", "math", "numbers", "np", "torch", "F", "mstype")]

@@ -341,3 +341,10 @@ def sync_pipeline_shared_parameters(net):
             g = M.group_for_ranks(ranks)
             if rank in ranks:
                 dist.broadcast(p.detach().as_subclass(torch.Tensor), ranks[0], group=M._group(g).pg)
+
+
+def load_segmented_checkpoints(ckpt_file_dir, net=None, strict_load=False, filter_prefix=None, dec_key=None,
+                               dec_mode="AES-GCM", specify_prefix=None, choice_func=None):
+    """Loads every ``*.ckpt`` of a directory into one parameter dict (parallel/checkpoint_transform.py)."""
+    from ..train.serialization import load_segmented_checkpoints as impl
+    return impl(ckpt_file_dir, net, strict_load, filter_prefix, dec_key, dec_mode, specify_prefix, choice_func)

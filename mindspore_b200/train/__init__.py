@@ -21,6 +21,9 @@ def __getattr__(name):
                 "transform_checkpoint_by_rank", "transform_checkpoints", "sync_pipeline_shared_parameters"):
         from .. import parallel
         return getattr(parallel, name)
+    if name in ("ConvertNetUtils", "ConvertModelUtils", "ModelThor"):
+        from . import thor_convert
+        return getattr(thor_convert, name)
     if name == "data_sink":
         from ..common.api import data_sink
         return data_sink
