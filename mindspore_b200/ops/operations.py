@@ -1347,18 +1347,20 @@ __all__ = [n for n, v in list(globals().items()) if isinstance(v, type) and issu
 
 from .operations_ext import *  # noqa: E402,F401,F403  (second-tier primitives)
 from .operations_more import *  # noqa: E402,F401,F403  (third tier: the long tail)
+from .operations_tail import *  # noqa: E402,F401,F403  (recurrent cells over packed weights, replay buffer, ...)
 from .llm_ops import *  # noqa: E402,F401,F403  (fused decoder primitives)
 from . import llm_ops as _llm_ops  # noqa: E402
 
-from . import operations_ext as _ops_ext, operations_more as _ops_more  # noqa: E402
+from . import operations_ext as _ops_ext, operations_more as _ops_more, operations_tail as _ops_tail  # noqa: E402
 
-__all__ = list(dict.fromkeys(__all__ + list(_ops_ext.__all__) + list(_ops_more.__all__) + list(_llm_ops.__all__)))
+__all__ = list(dict.fromkeys(__all__ + list(_ops_ext.__all__) + list(_ops_more.__all__) + list(_ops_tail.__all__) +
+                             list(_llm_ops.__all__)))
 
 
 
 _COMM_NAMES = ("AllGather", "AllReduce", "AlltoAll", "AlltoAllV", "Barrier", "BatchISendIRecv", "Broadcast",
                "CollectiveGather", "CollectiveScatter", "NeighborExchange", "NeighborExchangeV2", "Receive", "Reduce",
-               "ReduceOp", "ReduceScatter", "Send", "AShardIdentity")
+               "ReduceOp", "ReduceScatter", "Send", "AShardIdentity", "_AllSwap")
 
 
 def __getattr__(name):
@@ -1366,4 +1368,7 @@ def __getattr__(name):
     if name in _COMM_NAMES:
         import importlib
         return getattr(importlib.import_module(__package__ + ".comm_ops"), name)
+    if name == "Partial":
+        import importlib
+        return importlib.import_module(__package__ + ".composite").Partial
     raise AttributeError("module %r has no attribute %r" % (__name__, name))
