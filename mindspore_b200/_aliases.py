@@ -57,7 +57,8 @@ ALIASES = {
     "profiler.profiling": "profiler",
     "dataset.engine.datasets": "dataset.engine",
     "_extends.parse": "graph.ast_transform",
-    "offline_debug": "utils.dump",
+    "offline_debug": "utils.offline_debug",
+    "offline_debug.dbg_services": "utils.offline_debug",
     "nn.metrics": "train.metrics",
     "nn.optim.optimizer": "nn.optim",
     "nn.optim.adasum": "nn.optim_ext",

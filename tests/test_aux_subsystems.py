@@ -149,3 +149,78 @@ def test_timed_synchronize_polls_and_gives_up():
     with pytest.raises(hal.StreamSyncTimeout, match="did not finish within 2.0 s"):
         hal.wait_event(lambda: False, 2.0, what="device 0", clock=lambda: now[0], sleep=sleep)
     hal.synchronize(timeout=1.0)          # no GPU here: returns at once
+
+
+def test_offline_debugger_reads_dumps_and_checks_watchpoints(tmp_path, monkeypatch):
+    import json
+
+    from mindspore_b200 import nn
+    from mindspore_b200.offline_debug import dbg_services as D
+    from mindspore_b200.utils import dump
+    cfg = tmp_path / "dump.json"
+    cfg.write_text(json.dumps({"common_dump_settings": {"path": str(tmp_path / "out"), "net_name": "Net",
+                                                        "iteration": "all"}}))
+    monkeypatch.setenv("MINDSPORE_DUMP_CONFIG", str(cfg))
+    dump.reset()
+
+    class Net(nn.Cell):
+        def __init__(self):
+            super().__init__()
+            self.fc = nn.Dense(3, 2)
+            self.act = nn.ReLU()
+
+        def construct(self, x):
+            return self.act(self.fc(x))
+
+    net = Net()
+    dump.set_dump(net.fc)
+    dump.set_dump(net.act)
+    x = ms.Tensor(np.array([[1.0, -2.0, 3.0]], np.float32))
+    net(x)                                            # iteration 0
+    dump.next_iteration()
+    net(x)                                            # iteration 1: the same values
+    dump.next_iteration()
+    net(x * float("inf"))                             # iteration 2: overflow
+    dump.set_dump(net.fc, False)
+    dump.set_dump(net.act, False)
+    dump.reset()
+
+    dbg = D.DbgServices(str(tmp_path / "out"))
+    with pytest.raises(RuntimeError):
+        dbg.check_watchpoints(0)
+    dbg.initialize("Net")
+    info = D.TensorInfo("Dense", 0, 0, 0, 0)
+    (data,) = dbg.read_tensors([info])
+    want = net.fc(x).detach().numpy()
+    assert data.shape == [1, 2] and np.allclose(np.frombuffer(data.data_ptr, np.float32).reshape(1, 2), want)
+    (base,) = dbg.read_tensor_base([info])
+    (stat,) = dbg.read_tensor_stats([info])
+    assert base.data_size == 8 and stat.count == 2 and abs(stat.max_value - want.max()) < 1e-6
+    assert "nan_count = 0" in str(stat)
+    (missing,) = dbg.read_tensor_base([D.TensorInfo("Nothing", 0, 0, 0, 0)])
+    assert missing.data_size == 0
+
+    everywhere = {"*": {"rank_id": [0], "root_graph_id": [0], "is_output": True}}
+    dbg.add_watchpoint(1, D.GENERAL_OVERFLOW, everywhere, [])
+    dbg.add_watchpoint(2, D.MIN_LT, {"ReLU": {"is_output": True}}, [D.Parameter("param", False, 0.5)])
+    dbg.add_watchpoint(3, D.NOT_CHANGED, {"Dense": {}}, [D.Parameter("rtol", False, 1e-6)])
+    dbg.add_watchpoint(4, D.ALL_ZERO, everywhere, [D.Parameter("zero_percentage_ge", False, 100.0)])
+    hits0 = dbg.check_watchpoints(0)
+    relu = net(x).detach().numpy()
+    expect_min = relu.min() < 0.5
+    assert [h.watchpoint_id for h in hits0 if h.name == "ReLU" and h.watchpoint_id == 2] == ([2] if expect_min else [])
+    if expect_min:
+        hit = next(h for h in hits0 if h.watchpoint_id == 2)
+        assert hit.parameters[0].hit and abs(hit.parameters[0].actual_value - relu.min()) < 1e-6
+    assert not any(h.watchpoint_id in (1, 3) for h in hits0)
+    assert any(h.watchpoint_id == 4 for h in hits0) == bool((relu == 0).all())
+    hits1 = dbg.check_watchpoints(1)
+    assert [h.name for h in hits1 if h.watchpoint_id == 3] == ["Dense"]
+    hits2 = dbg.check_watchpoints(2)
+    assert {h.name for h in hits2 if h.watchpoint_id == 1} >= {"Dense"}
+    dbg.remove_watchpoint(1)
+    assert not any(h.watchpoint_id == 1 for h in dbg.check_watchpoints(2))
+    with pytest.raises(ValueError):
+        dbg.add_watchpoint(9, 99, everywhere, [])
+    with pytest.raises(ValueError):
+        dbg.remove_watchpoint(1)
