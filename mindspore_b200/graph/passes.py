@@ -133,6 +133,12 @@ def run_default_passes(fg, tag, save_level=0, path="."):
     for _ in range(4):
         if not pm.run(fg, tag, save_level, path):
             break
+    from .. import context as _context
+    if _context.get_context("enable_graph_kernel"):
+        from .graph_kernel import fuse_elementwise
+        pk = PassManager("graph_kernel")
+        pk.add("fuse_elementwise", fuse_elementwise)
+        pk.run(fg, tag + "_graph_kernel", save_level, path)
     pb = PassManager("opt_b")
     pb.add("merge_comm", O.merge_comm)
     pb.add("allreduce_fusion", O.allreduce_fusion)
