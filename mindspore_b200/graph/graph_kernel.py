@@ -3,7 +3,8 @@
 An elementwise chain in a transformer step (bias + residual + activation + scale ...) is bandwidth bound: every
 primitive reads and writes the whole tensor through HBM.  ``fuse_elementwise(fg)`` groups connected elementwise
 primitive nodes of equal shape and dtype into clusters, replaces each cluster by one ``FusedElementwise`` node, and
-that node runs a kernel generated for exactly this expression: every input is read once with 16-byte vector loads,
+that node runs a kernel generated for exactly this expression: every input is read once with 16-byte vector loads
+(two per thread in flight),
 the expression is evaluated in fp32 registers, every output is written once.  The kernel text is compiled for
 sm_100a with nvcc into a shared object (cached by the hash of its source), loaded through ctypes and launched on the
 current stream; a grid of 148 SMs x 8 blocks walks the tensor with a grid-stride loop.  On CPU tensors, and for the
@@ -153,10 +154,20 @@ def kernel_source(steps, outputs, n_inputs, dtype):
 
     params = ", ".join(["const T* __restrict__ in%d" % k for k in range(n_inputs)] +
                        ["T* __restrict__ out%d" % k for k in range(len(outputs))])
-    vec_loads = "\n".join("        V vi%d = reinterpret_cast<const V*>(in%d)[i];" % (k, k) for k in range(n_inputs))
-    vec_decl = "\n".join("        V vo%d;" % k for k in range(len(outputs)))
-    vec_body = body(lambda k: "vi%d.e[j]" % k, lambda k, v: "vo%d.e[j] = %s;" % (k, v), "            ")
-    vec_store = "\n".join("        reinterpret_cast<V*>(out%d)[i] = vo%d;" % (k, k) for k in range(len(outputs)))
+    n_out = len(outputs)
+    vec_params = ", ".join(["const V& vi%d" % k for k in range(n_inputs)] + ["V& vo%d" % k for k in range(n_out)])
+    vec_body = body(lambda k: "vi%d.e[j]" % k, lambda k, v: "vo%d.e[j] = %s;" % (k, v), "        ")
+
+    def vec_block(tag, at, indent):
+        """Loads of one vector position, the call of the expression, the stores."""
+        loads = ["V %si%d = reinterpret_cast<const V*>(in%d)[%s];" % (tag, k, k, at) for k in range(n_inputs)]
+        call = ["V %s;" % ", ".join("%so%d" % (tag, k) for k in range(n_out)),
+                "gk_vec(%s);" % ", ".join(["%si%d" % (tag, k) for k in range(n_inputs)] +
+                                          ["%so%d" % (tag, k) for k in range(n_out)])]
+        stores = ["reinterpret_cast<V*>(out%d)[%s] = %so%d;" % (k, at, tag, k) for k in range(n_out)]
+        return ["\n".join(indent + ln for ln in part) for part in (loads, call + stores)]
+    first_loads, first_rest = vec_block("a", "i", "        ")
+    second_loads, second_rest = vec_block("b", "k", "            ")
     tail_body = body(lambda k: "in%d[i]" % k, lambda k, v: "out%d[i] = %s;" % (k, v), "        ")
     args = ", ".join(["(const T*)ins[%d]" % k for k in range(n_inputs)] +
                      ["(T*)outs[%d]" % k for k in range(len(outputs))])
@@ -168,17 +179,25 @@ def kernel_source(steps, outputs, n_inputs, dtype):
 typedef %(ctype)s T;
 struct __align__(16) V { T e[%(vec)d]; };
 
-// one 16-byte vector per thread and iteration; the last n %% %(vec)d elements go through the scalar tail
+__device__ __forceinline__ void gk_vec(%(vec_params)s) {
+#pragma unroll
+    for (int j = 0; j < %(vec)d; ++j) {
+%(vec_body)s
+    }
+}
+
+// two 16-byte vectors per thread and iteration (both sets of loads are issued before the arithmetic: the kernel is
+// bound by memory latency); the last n %% %(vec)d elements go through the scalar tail
 __global__ void __launch_bounds__(256) gk_kernel(%(params)s, long long n_vec, long long n) {
     long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
-%(vec_loads)s
-%(vec_decl)s
-#pragma unroll
-        for (int j = 0; j < %(vec)d; ++j) {
-%(vec_body)s
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += 2 * stride) {
+        long long k = i + stride;
+%(first_loads)s
+        if (k < n_vec) {
+%(second_loads)s
+%(second_rest)s
         }
-%(vec_store)s
+%(first_rest)s
     }
     for (long long i = n_vec * %(vec)d + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
 %(tail_body)s
@@ -189,15 +208,16 @@ extern "C" __attribute__((visibility("default")))
 int msb_gk_launch(void** ins, void** outs, long long n, void* stream) {
     // unaligned operands (a view into a larger buffer) take the scalar path for every element
     long long n_vec = ((%(align)s) & 15ull) ? 0 : n / %(vec)d;
-    long long work = n_vec > 0 ? n_vec : n;
+    long long work = n_vec > 0 ? (n_vec + 1) / 2 : n;
     long long blocks = (work + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
     if (blocks < 1) blocks = 1;
     gk_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(%(args)s, n_vec, n);
     return (int)cudaGetLastError();
 }
-""" % {"ctype": ctype, "vec": vec, "params": params, "vec_loads": vec_loads, "vec_decl": vec_decl,
-       "vec_body": vec_body, "vec_store": vec_store, "tail_body": tail_body, "args": args, "align": align}
+""" % {"ctype": ctype, "vec": vec, "params": params, "vec_params": vec_params, "vec_body": vec_body,
+       "first_loads": first_loads, "first_rest": first_rest, "second_loads": second_loads,
+       "second_rest": second_rest, "tail_body": tail_body, "args": args, "align": align}
 
 
 def _tokens(expr):
