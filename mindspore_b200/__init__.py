@@ -4,7 +4,8 @@ PyTorch is the tensor / eager substrate; hot ops are hand-written sm_100a kernel
 (``mindspore_b200/csrc/cuda``), the planner / runtime pieces are C++ (``mindspore_b200/csrc/host``).
 """
 from . import common, communication, context, dataset, nn, ops, parallel, train
-from .common import (Parameter, ParameterTuple, Tensor, dtype, get_seed, initializer, set_seed)
+from .common import Parameter, ParameterTuple, Tensor, dtype, get_seed, set_seed
+from .common.initializer import initializer  # noqa: F401
 from .common.dtype import *  # noqa: F401,F403
 from .common.dtype import Type, dtype_to_nptype, pytype_to_dtype
 from .context import (GRAPH_MODE, PYNATIVE_MODE, ParallelMode, get_auto_parallel_context, get_context,

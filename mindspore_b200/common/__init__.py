@@ -1,6 +1,6 @@
 from . import dtype
 from .dtype import *  # noqa: F401,F403
-from .initializer import initializer
+from . import initializer  # noqa: F401  (the module: `common.initializer.Normal`, `common.initializer.initializer`)
 from .parameter import Parameter, ParameterTuple
 from .seed import get_seed, set_seed
 from .tensor import Tensor, as_tensor

@@ -332,6 +332,20 @@ class CSRTensor:
         counts = (self.indptr[1:] - self.indptr[:-1]).long()
         return torch.repeat_interleave(torch.arange(self.shape[0], device=counts.device), counts)
 
+    @property
+    def itemsize(self):
+        return self.values.element_size()
+
+    def add(self, b, alpha, beta):
+        """``alpha * self + beta * b`` for two CSR matrices of one shape (CSRTensor.add)."""
+        if not isinstance(b, CSRTensor) or tuple(b.shape) != tuple(self.shape):
+            raise ValueError("For 'CSRTensor.add', 'b' must be a CSRTensor of the same shape")
+        dense = float(torch.as_tensor(alpha)) * self.to_dense().as_subclass(torch.Tensor) + \
+            float(torch.as_tensor(beta)) * b.to_dense().as_subclass(torch.Tensor)
+        sp = dense.to_sparse_csr()
+        return CSRTensor(sp.crow_indices().to(self.indptr.dtype), sp.col_indices().to(self.indices.dtype),
+                         sp.values(), self.shape)
+
     def to_coo(self):
         return COOTensor(torch.stack([self._rows(), self.indices.long()], 1), self.values, self.shape)
 
@@ -517,3 +531,6 @@ def __getattr__(name):
         from ..graph.flops import flops_collection
         return flops_collection
     raise AttributeError("module %r has no attribute %r" % (__name__, name))
+
+
+COOTensor.itemsize = property(lambda self: self.values.element_size())

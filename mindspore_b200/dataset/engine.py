@@ -998,6 +998,41 @@ Dataset.save = _ds_save
 Dataset.device_que = lambda self, send_epoch_end=True, create_data_info_queue=False, queue_name="": self
 Dataset.to_device = Dataset.device_que
 Dataset.num_classes = lambda self: (len(set(int(np.asarray(r[self.get_col_names()[-1]])) for r in self._rows())))
+def _source_of(ds):
+    """The leaf (source) dataset of a pipeline."""
+    while getattr(ds, "parent", None) is not None:
+        ds = ds.parent
+    return ds
+
+
+def _use_sampler(self, new_sampler):
+    """Replaces the sampler of the source dataset (``None`` removes it).  Parity: MappableDataset.use_sampler."""
+    src = _source_of(self)
+    if not hasattr(src, "source") or not getattr(src, "random_access", False):
+        raise RuntimeError("use_sampler needs a random-access source dataset")
+    if new_sampler is not None:
+        if not hasattr(new_sampler, "indices"):
+            from .samplers import SubsetSampler
+            new_sampler = SubsetSampler(list(new_sampler))
+        new_sampler.bind(len(src.source), getattr(src.source, "labels", None))
+    src.sampler = new_sampler
+
+
+def _add_sampler(self, new_sampler):
+    """Puts ``new_sampler`` on top of the current one: it draws from what the current sampler yields.
+    Parity: MappableDataset.add_sampler."""
+    src = _source_of(self)
+    old = getattr(src, "sampler", None)
+    if old is not None:
+        new_sampler.add_child(old)
+    _use_sampler(self, new_sampler)
+
+
+Dataset.use_sampler = _use_sampler
+Dataset.add_sampler = _add_sampler
+Dataset.input_indexs = property(lambda self: getattr(self, "_input_indexs", ()),
+                                lambda self, value: setattr(self, "_input_indexs", value))
+Dataset.copy_batch_size = lambda self, value: setattr(self, "_batch_size_copy", value)
 Dataset.reset = lambda self: None
 Dataset.close = lambda self: None
 

@@ -236,6 +236,12 @@ class FileWriter:
             w._count += h["count"]
         return w
 
+    def init_append(self, file_name):
+        """Turns this writer into one that appends to the committed dataset ``file_name`` (filewriter.py
+        ``_init_append``'s public form)."""
+        self.__dict__.update(type(self).open_for_append(file_name).__dict__)
+        return SUCCESS
+
     def add_schema(self, content, desc=None):
         if not isinstance(content, dict) or not content:
             raise ValueError("schema must be a non-empty dict of field -> {'type': ..., 'shape': ...}")

@@ -92,9 +92,10 @@ class SubsetSampler(Sampler):
         self._subset = np.asarray(list(indices), dtype=np.int64)
 
     def indices(self):
-        if len(self._subset) and (self._subset.min() < 0 or self._subset.max() >= self.dataset_size):
-            raise ValueError("SubsetSampler: index out of range for a dataset of %d rows" % self.dataset_size)
-        return self._cut(self._subset)
+        base = self._base()                       # with a child sampler the subset indexes what the child yields
+        if len(self._subset) and (self._subset.min() < 0 or self._subset.max() >= len(base)):
+            raise ValueError("SubsetSampler: index out of range for %d rows" % len(base))
+        return self._cut(base[self._subset] if self.child is not None else self._subset)
 
 
 class SubsetRandomSampler(SubsetSampler):

@@ -227,3 +227,35 @@ def test_reference_import_paths_resolve():
     with ms.common._no_grad():
         y = ms.Parameter(ms.Tensor(np.ones(2, np.float32)), name="p") * 2
     assert not y.requires_grad and repr(ms.common._null) == "null" and not ms.common._null
+
+
+def test_sampler_replacement_sparse_add_and_append(tmp_path):
+    import mindspore_b200.dataset as ds
+    from mindspore_b200.common import initializer as init
+    from mindspore_b200.dataset import mindrecord as MR
+    data = ds.NumpySlicesDataset({"x": np.arange(10)}, shuffle=False)
+    data.use_sampler(ds.SequentialSampler(2, 3))
+    assert [int(r["x"]) for r in data.create_dict_iterator(output_numpy=True)] == [2, 3, 4]
+    data.add_sampler(ds.SubsetSampler([2, 0]))                   # draws from what the sequential sampler yields
+    assert [int(r["x"]) for r in data.create_dict_iterator(output_numpy=True)] == [4, 2]
+    data.use_sampler(None)
+    assert len([1 for _ in data.create_dict_iterator(output_numpy=True)]) == 10
+
+    a = ms.CSRTensor(ms.Tensor(np.array([0, 1, 2]), ms.int64), ms.Tensor(np.array([0, 1]), ms.int64),
+                     ms.Tensor(np.array([1.0, 2.0], np.float32)), (2, 2))
+    b = ms.CSRTensor(ms.Tensor(np.array([0, 1, 1]), ms.int64), ms.Tensor(np.array([1]), ms.int64),
+                     ms.Tensor(np.array([5.0], np.float32)), (2, 2))
+    out = a.add(b, 2.0, 1.0)
+    assert out.to_dense().tolist() == [[2.0, 5.0], [0.0, 4.0]] and a.itemsize == 4
+    assert init.initializer(init.Normal(0.1), (2, 3)).shape == (2, 3) and callable(ms.initializer)
+
+    path = str(tmp_path / "a.mindrecord")
+    w = MR.FileWriter(path)
+    w.add_schema({"id": {"type": "int64"}})
+    w.write_raw_data([{"id": 0}, {"id": 1}])
+    w.commit()
+    again = MR.FileWriter(str(tmp_path / "unused.mindrecord"))
+    again.init_append(path)
+    again.write_raw_data([{"id": 2}])
+    again.commit()
+    assert [int(r["id"]) for r in MR.FileReader(path).get_next()] == [0, 1, 2]
