@@ -100,7 +100,7 @@ while step < total:
             raise ClusterError("a node was lost or a new generation was opened")
         train_step(step + 1)
     except (ClusterError, RuntimeError) as e:
-        if recoveries >= 2:
+        if recoveries >= 4:                          # (a loaded test machine may miss a heartbeat window)
             raise
         recoveries += 1
         step = recover()
@@ -145,7 +145,7 @@ def test_job_reforms_after_a_rank_left_between_steps(tmp_path):
     script = tmp_path / "worker.py"
     script.write_text(WORKER % {"root": ROOT})
     total, die_after = 6, 3
-    with Scheduler(0, expected_workers=3, node_timeout_s=1.0, persist_path=str(tmp_path / "sched.state")) as sched:
+    with Scheduler(0, expected_workers=3, node_timeout_s=3.0, persist_path=str(tmp_path / "sched.state")) as sched:
         def launch(node, die):
             return subprocess.Popen([sys.executable, str(script), str(sched.port), node, str(tmp_path), str(die),
                                      str(total)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
